@@ -1,0 +1,258 @@
+/* C ABI of libmkda: hand-written sm_100a kernels for chunked Kimi Delta Attention (per-channel gate) and the
+ * gated delta rule (scalar gate), forward and backward.
+ *
+ * Conventions
+ *  - Every entry point takes a pointer to a plain parameter struct and a CUDA stream (passed as void*), launches
+ *    on that stream and returns 0 on success or a negative MKDA_ERR_* code; mkda_last_error() gives the text.
+ *    Nothing is allocated or freed by the library: every buffer (inputs, outputs, workspaces) belongs to the caller.
+ *    Inputs are never written.  No exception crosses this boundary.
+ *  - Tokens are addressed in the flattened [TT = B*T] space.  Per-token tensors are row-major
+ *    [TT, heads, 128] (or [TT, heads, 64] for the chunk-local matrices, [TT, heads] for scalars).
+ *  - A "chunk" is up to 64 consecutive tokens of ONE sequence; chunk ids are sequence-major.  chunk_start[c] is the
+ *    flattened index of its first token and chunk_len[c] (1..64) its number of valid rows.  This is the layout the
+ *    reference builds in mogan_kda/utils/index.py:93-116 (prepare_chunk_indices / prepare_chunk_offsets).
+ *  - A "segment" is a run of consecutive chunks of one sequence processed by one serial recurrence
+ *    (seg_chunk_off[s] .. seg_chunk_off[s+1]); without context parallelism a segment is a whole sequence.
+ *  - Key dim = value dim = 128, chunk = 64 (mogan_kda/ops/kimi_delta_rule/chunk/__init__.py:18,46).
+ *  - States are fp32 [.., HV, 128(K), 128(V)]; with state_v_first the caller-visible ones are [.., HV, V, K]
+ *    (mogan_kda/ops/kimi_delta_rule/chunk/__init__.py:38-40).  Per-chunk states h / dh are always [K, V].
+ */
+#ifndef MKDA_H_
+#define MKDA_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { MKDA_F32 = 0, MKDA_BF16 = 1, MKDA_F16 = 2 };
+enum { MKDA_GATE_PRECOMPUTED = 0, MKDA_GATE_EDA = 1, MKDA_GATE_KIMI = 2, MKDA_GATE_GDN = 3 };
+enum { MKDA_ACT_SILU = 0, MKDA_ACT_SIGMOID = 1 };
+enum { MKDA_OK = 0, MKDA_ERR_ARG = -1, MKDA_ERR_LAUNCH = -2 };
+
+/* Chunk / segment tables shared by all kernels (device pointers, int32). */
+typedef struct {
+    int TT;                    /* flattened tokens */
+    int NC;                    /* chunks */
+    int NS;                    /* segments */
+    int HK;                    /* q/k heads */
+    int HV;                    /* v heads (HV % HK == 0) */
+    const int* chunk_start;    /* [NC] */
+    const int* chunk_len;      /* [NC] */
+    const int* seg_chunk_off;  /* [NS+1] */
+} MkdaLayout;
+
+/* Fused gate activation + chunk-local cumsum (log2 domain) + optional beta activation.
+ * Replaces kda_gate_cumsum_fwd (mogan_kda/ops/kimi_delta_rule/gate.py:378-406), _beta
+ * (mogan_kda/ops/kimi_delta_rule/chunk/__init__.py:184-189) and, for a scalar gate, chunk_local_cumsum
+ * (mogan_kda/ops/utils/cumsum.py:296-373) with the result broadcast over the 128 channels. */
+typedef struct {
+    MkdaLayout L;
+    const void* x; int x_dtype; int scalar_gate;   /* [TT,HV,128] or [TT,HV] */
+    const float* A_log;                            /* [HV] or NULL (=0) */
+    const float* dt_bias;                          /* [HV*128] ([HV] if scalar_gate) or NULL */
+    int mode; float lower_bound;
+    const void* beta_raw; int beta_dtype;          /* [TT,HV] or NULL (skip beta) */
+    int beta_sigmoid; float beta_scale;
+    float* beta_out;                               /* [TT,HV] fp32 */
+    float* g_c;                                    /* [TT,HV,128] fp32 */
+} MkdaGateFwd;
+int mkda_gate_cumsum_fwd(const MkdaGateFwd* p, void* stream);
+
+/* Gate backward with the chunk-local reverse cumsum folded in; per-chunk partials for the parameter gradients.
+ * Replaces kda_gate_bwd (mogan_kda/ops/kimi_delta_rule/gate.py:409-459, dg_is_prime=True) and K5
+ * (mogan_kda/ops/kimi_delta_rule/chunk/__init__.py:120-124). */
+typedef struct {
+    MkdaLayout L;
+    const void* x; int x_dtype; int scalar_gate;
+    const float* A_log; const float* dt_bias;
+    int mode; float lower_bound;
+    const float* dgp;          /* [TT,HV,128] gradient w.r.t. the log2 cumsum as produced by mkda_bwd_intra */
+    void* dx; int dx_dtype;    /* [TT,HV,128] or [TT,HV] */
+    float* part_bias;          /* [NC,HV,128] ([NC,HV] scalar) partial sums of d/d(x+bias), or NULL */
+    float* part_alog;          /* same shape, partial sums of d/dA_log, or NULL */
+} MkdaGateBwd;
+int mkda_gate_bwd(const MkdaGateBwd* p, void* stream);
+
+/* out[j] = sum_r sum_{i<group} in[r*cols + j*group + i], fixed summation tree (deterministic).  Second stage of
+ * every parameter-gradient reduction (mogan_kda/ops/kimi_delta_rule/gate.py:452-458, epilogue.py:204). */
+typedef struct {
+    const float* in; int rows; int cols; int group;
+    float* out;                /* [cols/group] */
+} MkdaReduce;
+int mkda_reduce_partials(const MkdaReduce* p, void* stream);
+
+/* rstd[r] = rsqrt(sum_c x[r,c]^2 + eps) for rows of 128.  Replaces l2norm_fwd (mogan_kda/utils/math.py:22-35);
+ * the normalised rows themselves are never materialised (consumers multiply by rstd in fp32). */
+typedef struct {
+    const void* x; int dtype; int rows; float eps;
+    float* rstd;
+} MkdaL2Norm;
+int mkda_l2norm_rstd(const MkdaL2Norm* p, void* stream);
+
+/* Chunk-parallel WY preparation.  Per (chunk, v-head): decayed K K^T and Q K^T with per-16-row anchoring, the
+ * unit-lower-triangular inverse, and the two products the recurrence consumes.
+ * Replaces kkt_solve_kda (mogan_kda/ops/kimi_delta_rule/chunk/hopper/kkt_solve_kda.py:546-623) and bwd_w_kda
+ * (.../hopper/bwd_prep.py:317-347). */
+typedef struct {
+    MkdaLayout L;
+    const void* q; const void* k; const void* v; int qkv_dtype;
+    const float* q_rstd; const float* k_rstd;      /* [TT,HK] or NULL */
+    const float* g_c; const float* beta;           /* [TT,HV,128], [TT,HV] */
+    float scale;
+    float* A;      /* [TT,HV,64]  rows of (I + strictlower(diag(beta) Gamma))^-1 */
+    float* Aqk;    /* [TT,HV,64]  rows of scale * lower(Q K^T with decay) */
+    float* nw;     /* [TT,HV,128] -A diag(beta) (k 2^g) */
+    float* u;      /* [TT,HV,128]  A (beta v) */
+} MkdaIntraFwd;
+int mkda_intra_fwd(const MkdaIntraFwd* p, void* stream);
+
+/* Serial state recurrence per (segment, v-head, 64-column block):  Vd = u + nw S;  S <- diag(gl) S + kbar^T Vd.
+ * Column blocks 0,1 carry the state; with want_transition, blocks 2,3 carry the segment's K x K transition
+ * matrix (same recurrence with u = 0 started from the identity).  Replaces the state part of fused_fwd_kda
+ * (mogan_kda/ops/kimi_delta_rule/chunk/hopper/fused_fwd.py:523-616) and, for context parallelism, the role of
+ * fused_gdr_h (mogan_kda/ops/gated_delta_rule/chunk/blackwell/prepare_h.py:336-403). */
+typedef struct {
+    MkdaLayout L;
+    const float* nw; const float* u;
+    const void* k; int k_dtype; const float* k_rstd;
+    const float* g_c;
+    const float* h0;           /* [*,HV,128,128] or NULL */
+    const int* seg_h0;         /* [NS] row of h0 for each segment, -1 = start from zero; NULL = identity map */
+    int state_v_first;         /* layout of h0 / ht */
+    float* h;                  /* [NC,HV,128,128] state entering each chunk, or NULL */
+    float* Vd;                 /* [TT,HV,128] or NULL */
+    float* ht;                 /* [NS,HV,128,128] state leaving each segment, or NULL */
+    int want_transition;
+    float* mt;                 /* [NS,HV,128,128] transition (row = output K index), needs want_transition */
+} MkdaRecurFwd;
+int mkda_recur_fwd(const MkdaRecurFwd* p, void* stream);
+
+/* Chunk-parallel output  o = scale (q 2^g) h + Aqk Vd  with the optional gated RMSNorm epilogue fused.
+ * Replaces the output part of fused_fwd_kda and rmsnorm_gated_fwd
+ * (mogan_kda/ops/kimi_delta_rule/epilogue.py:183-190). */
+typedef struct {
+    MkdaLayout L;
+    const void* q; int q_dtype; const float* q_rstd;
+    const float* g_c; const float* Aqk; const float* Vd; const float* h;
+    float scale;
+    int has_norm; const void* norm_w; int norm_w_dtype;   /* [128] or NULL (=1) */
+    const void* gate; int gate_dtype;                     /* [TT,HV,128] */
+    int act; float eps;
+    float* o_raw;              /* [TT,HV,128] fp32 pre-norm output kept for the backward, or NULL */
+    void* out; int out_dtype;  /* [TT,HV,128] */
+} MkdaOutFwd;
+int mkda_out_fwd(const MkdaOutFwd* p, void* stream);
+
+/* Gated RMSNorm backward.  Replaces rmsnorm_gated_bwd (mogan_kda/ops/kimi_delta_rule/epilogue.py:193-205). */
+typedef struct {
+    int rows;                  /* TT*HV */
+    const void* dy; int dy_dtype;
+    const float* o_raw;
+    const void* norm_w; int norm_w_dtype;
+    const void* gate; int gate_dtype;
+    int act; float eps;
+    float* d_o;                /* [rows,128] fp32 */
+    void* dgate; int dgate_dtype;
+    float* part_w;             /* [ceil(rows/64),128] partial sums of d weight, or NULL */
+} MkdaEpilogueBwd;
+int mkda_epilogue_bwd(const MkdaEpilogueBwd* p, void* stream);
+
+/* Reverse state chain per (segment, v-head, 64-column block).
+ * Replaces bwd_dh_kda (mogan_kda/ops/kimi_delta_rule/chunk/hopper/bwd_dh.py:390-448). */
+typedef struct {
+    MkdaLayout L;
+    const void* d_o; int do_dtype;                 /* [TT,HV,128] */
+    const void* q; const void* k; int qk_dtype; const float* q_rstd; const float* k_rstd;
+    const float* g_c; const float* Aqk; const float* nw;
+    float scale;
+    const float* dht;          /* [*,HV,128,128] or NULL */
+    const int* seg_dht;        /* [NS] row of dht per segment, -1 = zero; NULL = identity map */
+    int state_v_first;         /* layout of dht / dh0 */
+    float* dh;                 /* [NC,HV,128,128] gradient of the state leaving each chunk */
+    float* dVd;                /* [TT,HV,128] */
+    float* dh0;                /* [NS,HV,128,128] gradient of the state entering each segment, or NULL */
+} MkdaBwdDh;
+int mkda_bwd_dh(const MkdaBwdDh* p, void* stream);
+
+/* Chunk-parallel gradients through Vd = A diag(beta)(V - k~ S).
+ * Replaces K3a of bwd_post_kda (mogan_kda/ops/kimi_delta_rule/chunk/hopper/bwd_post.py:72-400). */
+typedef struct {
+    MkdaLayout L;
+    const void* k; const void* v; int kv_dtype; const float* k_rstd;
+    const float* g_c; const float* beta; const float* A; const float* h;
+    const void* d_o; int do_dtype; const float* dVd;
+    float* Vd;                 /* [TT,HV,128] recomputed */
+    float* dX;                 /* [TT,HV,128] = dv (fp32) */
+    float* dbeta_w;            /* [TT,HV] */
+    float* dAqk; float* dL;    /* [TT,HV,64] */
+} MkdaBwdWy;
+int mkda_bwd_wy(const MkdaBwdWy* p, void* stream);
+
+/* Chunk-parallel gradients through the states: row-local parts of dq, dk and of the gate gradient.
+ * Replaces K3b of bwd_post_kda (mogan_kda/ops/kimi_delta_rule/chunk/hopper/bwd_post.py:412-766). */
+typedef struct {
+    MkdaLayout L;
+    const void* q; const void* k; int qk_dtype; const float* q_rstd; const float* k_rstd;
+    const float* g_c;
+    const void* d_o; int do_dtype; const float* dX; const float* Vd;
+    const float* h; const float* dh;
+    float scale;
+    float* dq_p; float* dk_p; float* dg_p;         /* [TT,HV,128] */
+} MkdaBwdSgrad;
+int mkda_bwd_sgrad(const MkdaBwdSgrad* p, void* stream);
+
+/* Chunk-parallel gradients through the decayed K K^T / Q K^T blocks.
+ * Replaces bwd_intra_kda (mogan_kda/ops/kimi_delta_rule/chunk/hopper/bwd_intra.py:529-600) plus the beta
+ * activation derivative (mogan_kda/ops/kimi_delta_rule/chunk/__init__.py:256-258). */
+typedef struct {
+    MkdaLayout L;
+    const void* q; const void* k; int qk_dtype; const float* q_rstd; const float* k_rstd;
+    const float* g_c; const float* beta;
+    const float* dAqk; const float* dL;
+    const float* dq_p; const float* dk_p; const float* dg_p; const float* dbeta_w;
+    float scale;
+    const void* beta_raw; int beta_dtype; int beta_sigmoid; float beta_scale;
+    float* dq_v; float* dk_v;  /* [TT,HV,128] per v-head */
+    float* dgp;                /* [TT,HV,128] gradient w.r.t. the log2 cumsum */
+    void* dbeta; int dbeta_dtype;                  /* [TT,HV] gradient w.r.t. the raw beta input */
+} MkdaBwdIntra;
+int mkda_bwd_intra(const MkdaBwdIntra* p, void* stream);
+
+/* Sum over the v-heads sharing a q/k head, then L2-norm backward; writes dq or dk in the input dtype.
+ * Replaces group_reduce_vector (mogan_kda/ops/utils/group_reduce.py:60-79) and l2norm_bwd
+ * (mogan_kda/utils/math.py:38-72). */
+typedef struct {
+    int TT; int HK; int HV;
+    const float* d_v;          /* [TT,HV,128] */
+    const void* x; int x_dtype; const float* rstd;  /* raw q or k and its rstd (NULL = no L2 norm) */
+    void* dx; int dx_dtype;    /* [TT,HK,128] */
+} MkdaQkGrad;
+int mkda_qk_grad_finish(const MkdaQkGrad* p, void* stream);
+
+/* Prefix combine of per-segment (state, transition) pairs along each sequence:
+ *   forward : S_in[s+1] = M_s S_in[s] + H_s        (reverse = 0, segments of a group in increasing order)
+ *   backward: G_out[s-1] = M_s^T G_out[s] + D_s    (reverse = 1, decreasing order)
+ * Groups are runs of segments (grp_seg_off) that belong to one sequence; `carry` is the value entering the first
+ * (last, when reversed) segment of each group or NULL for zero.  Replaces correct_initial_states /
+ * correct_terminal_states (mogan_kda/ops/gated_delta_rule/chunk/blackwell/cp_fwd.py:552-681). */
+typedef struct {
+    int NG; int HV;
+    const int* grp_seg_off;    /* [NG+1] */
+    const float* hs;           /* [NS,HV,128,128] per-segment local result ([K,V]) */
+    const float* ms;           /* [NS,HV,128,128] per-segment transition */
+    const float* carry;        /* [NG,HV,128,128] ([K,V]) or NULL */
+    int reverse;
+    float* s_in;               /* [NS,HV,128,128] value entering each segment ([K,V]) */
+    float* s_out;              /* [NG,HV,128,128] value leaving the last (first) segment of each group, or NULL */
+} MkdaCombine;
+int mkda_state_combine(const MkdaCombine* p, void* stream);
+
+const char* mkda_last_error(void);
+int mkda_abi_version(void);
+/* sizeof() of every parameter struct, in declaration order, so bindings can verify their mirror of this header. */
+int mkda_struct_sizes(int* out, int n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MKDA_H_ */

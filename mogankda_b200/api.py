@@ -1,0 +1,235 @@
+"""Public API: ``chunk_kda``, ``chunk_delta_rule``, ``chunk_gated_delta_rule``.
+
+Same names, keyword surface, shapes, dtypes and error behaviour as the reference entry points
+(mogan_kda/ops/kimi_delta_rule/chunk/__init__.py:297-355 and
+mogan_kda/ops/gated_delta_rule/chunk/__init__.py:313-469); the work is done by the sm_100a kernels of libmkda.
+
+Differences that are extensions, not changes of meaning:
+  * q / k / v may also be float32 (the reference kernels take bf16 / fp16 only); outputs follow the input dtype.
+  * context parallelism exists for the per-channel gate as well (``cp_context`` from ``mogankda_b200.cp``).
+  * a scalar gate [B,T,HV] goes through the same kernels with the decay broadcast over the key channels.
+"""
+import torch
+
+from . import ops
+from .index import get_layout
+
+CHUNK_SIZE = 64
+# Sequences longer than this many chunks are cut into segments of exactly this many chunks whose serial recurrences
+# run concurrently (state + transition pre-pass, prefix combine, main pass).  A constant, so that a prefix of a
+# sequence is always processed exactly like the same tokens inside the longer sequence.
+AUTO_SEGMENT_CHUNKS = 32
+
+
+class _DeltaRuleFunction(torch.autograd.Function):
+    """forward: gate + cumsum (+beta) -> L2 statistics -> WY preparation -> state pass -> output (+epilogue).
+    backward: epilogue -> reverse state chain -> WY / state gradients -> intra-chunk gradients -> gate / L2 / GVA."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, x, beta, A_log, dt_bias, initial_state, ep_w, ep_gate, cfg):
+        B, T, HK, K = q.shape
+        HV = v.shape[2]
+        dev = q.device
+        lay = get_layout(B, T, cfg["cu_seqlens"], dev, cfg["seg_chunks"])
+        cp = cfg["cp_context"]
+        scale = cfg["scale"]
+        q_rstd = k_rstd = None
+        if cfg["l2"]:
+            q_rstd, k_rstd = ops.l2norm_rstd(q), ops.l2norm_rstd(k)
+        g_c, beta_e = ops.gate_cumsum_fwd(lay, x, cfg["gate_mode"], A_log, dt_bias, cfg["lower_bound"], HV,
+                                          beta_raw=beta, beta_sigmoid=cfg["beta_mode"] == "sigmoid",
+                                          beta_scale=cfg["beta_scale"])
+        A, Aqk, nw, u = ops.intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV)
+        vf = cfg["state_v_first"]
+        need_ht = cfg["output_final_state"]
+        ms = None
+        if lay.segmented or cp is not None:
+            # pre-pass from zero: per-segment (state, transition); then the true entering state of every segment
+            _, _, hs, ms = ops.recur_fwd(lay, nw, u, k, k_rstd, g_c, HK, HV, store_h=False, store_vd=False,
+                                         want_transition=True)
+            carry = None
+            if initial_state is not None:
+                carry = initial_state.transpose(-1, -2).contiguous() if vf else initial_state
+            if cp is not None:
+                carry = cp.forward_carry(hs, ms, carry, lay, HV)
+            s_in, _ = ops.state_combine(lay.grp_seg_off, lay.NG, lay.NS, HV, hs, ms, carry=carry, want_out=False)
+            h, Vd, ht_seg, _ = ops.recur_fwd(lay, nw, u, k, k_rstd, g_c, HK, HV, h0=s_in, state_v_first=False,
+                                             want_ht=need_ht)
+            ht = None
+            if need_ht:
+                ht = ht_seg.index_select(0, torch.nonzero(lay.seg_last >= 0).flatten())
+                if vf:
+                    ht = ht.transpose(-1, -2).contiguous()
+        else:
+            h, Vd, ht, _ = ops.recur_fwd(lay, nw, u, k, k_rstd, g_c, HK, HV, h0=initial_state, state_v_first=vf,
+                                         want_ht=need_ht)
+        norm = None
+        if cfg["has_ep"]:
+            norm = dict(weight=ep_w, gate=ep_gate, act=cfg["ep_act"], eps=cfg["ep_eps"])
+        need_bwd = any(ctx.needs_input_grad[:10])
+        out_dtype = torch.float32 if cfg["has_ep"] else q.dtype
+        out, o_raw = ops.out_fwd(lay, q, q_rstd, g_c, Aqk, Vd, h, scale, HK, HV, out_dtype, norm=norm,
+                                 keep_raw=cfg["has_ep"] and need_bwd)
+        if need_bwd:
+            ctx.save_for_backward(q, k, v, x, beta, A_log, dt_bias, initial_state, ep_w, ep_gate, q_rstd, k_rstd,
+                                  g_c, beta_e, A, Aqk, nw, h, o_raw, ms)
+        ctx.cfg, ctx.lay, ctx.dims = cfg, lay, (B, T, HK, HV)
+        ctx.set_materialize_grads(False)
+        return out.view(B, T, HV, 128), ht
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, dy, dht):
+        (q, k, v, x, beta, A_log, dt_bias, initial_state, ep_w, ep_gate, q_rstd, k_rstd, g_c, beta_e, A, Aqk, nw, h,
+         o_raw, ms) = ctx.saved_tensors
+        cfg, lay = ctx.cfg, ctx.lay
+        B, T, HK, HV = ctx.dims
+        scale, vf, cp = cfg["scale"], cfg["state_v_first"], cfg["cp_context"]
+        if dy is None:
+            dy = torch.zeros(B, T, HV, 128, dtype=torch.float32 if cfg["has_ep"] else q.dtype, device=q.device)
+        dy = dy.contiguous()
+        dw = dgate = None
+        if cfg["has_ep"]:
+            d_o, dgate, dw = ops.epilogue_bwd(dy, o_raw, ep_w, ep_gate, cfg["ep_act"], cfg["ep_eps"])
+            if dw is not None:
+                dw = dw.to(ep_w.dtype)
+        else:
+            d_o = dy
+        if dht is not None:
+            dht = dht.float().contiguous()
+        need_dh0 = initial_state is not None and ctx.needs_input_grad[7]
+        if lay.segmented or cp is not None:
+            dh, dVd, dloc = ops.bwd_dh(lay, d_o, q, k, q_rstd, k_rstd, g_c, Aqk, nw, scale, HK, HV)
+            carry = None
+            if dht is not None:
+                carry = dht.transpose(-1, -2).contiguous() if vf else dht
+            if cp is not None:
+                carry = cp.backward_carry(dloc, ms, carry, lay, HV)
+            g_in, dh0 = ops.state_combine(lay.grp_seg_off, lay.NG, lay.NS, HV, dloc, ms, carry=carry, reverse=True,
+                                          want_out=need_dh0 or cp is not None)
+            ops.bwd_dh(lay, d_o, q, k, q_rstd, k_rstd, g_c, Aqk, nw, scale, HK, HV, dht=g_in, want_dh0=False,
+                       dh=dh, dVd=dVd)
+            if cp is not None:
+                dh0 = cp.finish_backward(dh0)
+            if dh0 is not None and vf:
+                dh0 = dh0.transpose(-1, -2).contiguous()
+        else:
+            dh, dVd, dh0 = ops.bwd_dh(lay, d_o, q, k, q_rstd, k_rstd, g_c, Aqk, nw, scale, HK, HV, dht=dht,
+                                      state_v_first=vf, want_dh0=need_dh0)
+        Vd, dX, dbeta_w, dAqk, dL = ops.bwd_wy(lay, k, v, k_rstd, g_c, beta_e, A, h, d_o, dVd, HK, HV)
+        dq_p, dk_p, dg_p = ops.bwd_sgrad(lay, q, k, q_rstd, k_rstd, g_c, d_o, dX, Vd, h, dh, scale, HK, HV)
+        dq_v, dk_v, dgp, dbeta = ops.bwd_intra(lay, q, k, q_rstd, k_rstd, g_c, beta_e, dAqk, dL, dq_p, dk_p, dg_p,
+                                               dbeta_w, scale, HK, HV, beta, cfg["beta_mode"] == "sigmoid",
+                                               cfg["beta_scale"])
+        dx, d_bias, d_alog = ops.gate_bwd(lay, x, dgp, cfg["gate_mode"], A_log, dt_bias, cfg["lower_bound"], HV,
+                                          want_bias=dt_bias is not None and ctx.needs_input_grad[6],
+                                          want_alog=A_log is not None and ctx.needs_input_grad[5])
+        dq = ops.qk_grad_finish(dq_v, q, q_rstd, HK, HV).view_as(q)
+        dk = ops.qk_grad_finish(dk_v, k, k_rstd, HK, HV).view_as(k)
+        dv = dX.view(B, T, HV, 128).to(v.dtype)
+        if d_alog is not None:
+            d_alog = d_alog.view_as(A_log).to(A_log.dtype)
+        if d_bias is not None:
+            d_bias = d_bias.view_as(dt_bias).to(dt_bias.dtype)
+        if not need_dh0:
+            dh0 = None
+        return (dq, dk, dv, dx, dbeta.view_as(beta), d_alog, d_bias, dh0, dw, dgate, None)
+
+
+def _check_common(q, k, v, g, beta, initial_state, cu_seqlens):
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise RuntimeError("mogankda_b200 runs on CUDA tensors only (no CPU fallback)")
+    assert q.dtype == k.dtype == v.dtype, "q, k, v must share a dtype"
+    assert q.dtype in (torch.bfloat16, torch.float16, torch.float32), "q, k, v must be bfloat16, float16 or float32"
+    assert q.shape == k.shape and q.dim() == 4 and v.dim() == 4, "q, k [B,T,HK,K]; v [B,T,HV,V]"
+    assert q.shape[-1] == v.shape[-1] == 128, "head dims must be 128"
+    assert v.shape[:2] == q.shape[:2], "q and v disagree on [B,T]"
+    assert v.shape[2] % q.shape[2] == 0, "GVA needs HV % HK == 0"
+    assert g.shape[:3] == v.shape[:3] and (g.dim() == 3 or (g.dim() == 4 and g.shape[3] == 128)), \
+        "g must be [B,T,HV] or [B,T,HV,128]"
+    assert beta.shape == v.shape[:3], "beta must be [B,T,HV]"
+    if cu_seqlens is not None:
+        if q.shape[0] != 1:
+            raise ValueError(f"The batch size is expected to be 1 rather than {q.shape[0]} when using `cu_seqlens`.")
+        n = cu_seqlens.numel() - 1
+    else:
+        n = q.shape[0]
+    if initial_state is not None:
+        assert initial_state.dtype == torch.float32, "initial_state must be float32"
+        if initial_state.shape[0] != n:
+            raise ValueError(f"The number of initial states is expected to be equal to the number of input "
+                             f"sequences, i.e., {n} rather than {initial_state.shape[0]}.")
+        assert tuple(initial_state.shape[1:]) == (v.shape[2], 128, 128), "initial_state must be [N,HV,128,128]"
+
+
+def chunk_delta_rule(q, k, v, g, beta, *, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None,
+                     state_v_first=False, gate_mode="precomputed", A_log=None, dt_bias=None, lower_bound=-5.0,
+                     beta_mode="precomputed", beta_scale=1.0, use_qk_l2norm_in_kernel=False, output_norm=None,
+                     auto_cp=True, cp_context=None):
+    """Unified delta rule (mogan_kda/ops/kimi_delta_rule/chunk/__init__.py:297-349).
+
+    q, k [B,T,HK,128]; v [B,T,HV,128]; g [B,T,HV,128] per-channel or [B,T,HV] scalar gate input (raw pre-activation
+    unless ``gate_mode="precomputed"``, then the natural-log per-token decay, contract g >= -5); beta [B,T,HV].
+    Returns ``(o, final_state)``: o in q.dtype, or float32 when ``output_norm`` is given.
+    """
+    _check_common(q, k, v, g, beta, initial_state, cu_seqlens)
+    if gate_mode not in ops.GATE_MODES:
+        raise ValueError(f"unknown gate_mode {gate_mode!r}")
+    if beta_mode not in ("precomputed", "sigmoid"):
+        raise ValueError(f"unknown beta_mode {beta_mode!r}")
+    if gate_mode == "gdn":
+        assert A_log is not None, "gate_mode='gdn' needs A_log"
+        if lower_bound is None and g.dim() == 4:
+            lower_bound = -5.0          # the per-channel kernels rely on g >= -5 (reference :338-339)
+    if gate_mode == "eda":
+        assert A_log is not None and lower_bound is not None, "gate_mode='eda' needs A_log and lower_bound"
+    if gate_mode == "kimi":
+        assert lower_bound is not None, "gate_mode='kimi' needs lower_bound"
+    ep = output_norm
+    if ep is not None and ep.get("act", "silu") not in ops.ACTS:
+        raise ValueError(f"unknown act {ep.get('act')!r}")
+    if cp_context is not None and cu_seqlens is not None and cu_seqlens.numel() != 2:
+        raise ValueError("cross-GPU context parallelism handles one sequence per call")
+    if cp_context is not None and q.shape[0] != 1:
+        raise ValueError("inter-card CP requires B==1 (varlen).")
+    B, T = q.shape[:2]
+    cfg = dict(scale=float(q.shape[-1] ** -0.5 if scale is None else scale), output_final_state=output_final_state,
+               cu_seqlens=cu_seqlens, state_v_first=state_v_first, gate_mode=gate_mode, lower_bound=lower_bound,
+               beta_mode=beta_mode, beta_scale=float(beta_scale), l2=use_qk_l2norm_in_kernel, has_ep=ep is not None,
+               ep_act=None if ep is None else ep.get("act", "silu"),
+               ep_eps=None if ep is None else ep.get("eps", 1e-6),
+               seg_chunks=AUTO_SEGMENT_CHUNKS if (cp_context is not None or _needs_segments(B, T, cu_seqlens, auto_cp)) else 0,
+               cp_context=cp_context)
+    ep_gate = None if ep is None else ep["gate"].contiguous()
+    ep_w = None if ep is None else ep.get("weight")
+    return _DeltaRuleFunction.apply(q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(),
+                                    beta.contiguous(), A_log, dt_bias, initial_state, ep_w, ep_gate, cfg)
+
+
+def _needs_segments(B, T, cu_seqlens, auto_cp):
+    """Cut long sequences when the uncut layout could not fill the GPU: decided from shapes only (no device read)."""
+    if not auto_cp:
+        return False
+    return T > AUTO_SEGMENT_CHUNKS * CHUNK_SIZE
+
+
+def chunk_kda(q, k, v, g, beta, **kwargs):
+    """Kimi Delta Attention: ``chunk_delta_rule`` restricted to a per-channel gate g [B,T,HV,128]
+    (mogan_kda/ops/kimi_delta_rule/chunk/__init__.py:352-355)."""
+    assert g.dim() == 4, "chunk_kda needs a per-channel gate g [B, T, HV, K]; use chunk_gated_delta_rule for scalar gates"
+    return chunk_delta_rule(q, k, v, g, beta, **kwargs)
+
+
+def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
+                           use_qk_l2norm_in_kernel=False, cu_seqlens=None, head_first=False, state_v_first=False,
+                           auto_cp=True, enable_fwd_cp_cache=True, cp_context=None, force_intra_cp=False):
+    """Scalar-gate delta rule (mogan_kda/ops/gated_delta_rule/chunk/__init__.py:313-469).  g [B,T,HV] is the per-token
+    natural-log decay, beta [B,T,HV] the effective beta."""
+    assert q.dtype == k.dtype == v.dtype
+    assert not head_first, "head_first=True is not supported."
+    assert v.shape[2] % k.shape[2] == 0, "num_qk_heads must be divisible to num_v_heads."
+    assert g.dim() == 3, "chunk_gated_delta_rule takes a scalar gate g [B, T, HV]"
+    return chunk_delta_rule(q, k, v, g, beta, scale=scale, initial_state=initial_state,
+                            output_final_state=output_final_state, cu_seqlens=cu_seqlens,
+                            state_v_first=state_v_first, use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel,
+                            auto_cp=auto_cp or force_intra_cp, cp_context=cp_context)

@@ -1,0 +1,49 @@
+// Error reporting and ABI self-description.
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/mkda.h"
+#include "host.h"
+
+namespace mkda {
+
+static thread_local char g_err[512] = "";
+
+int set_error(int code, const char* msg) {
+    snprintf(g_err, sizeof(g_err), "%s", msg);
+    return code;
+}
+
+int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
+        return MKDA_ERR_LAUNCH;
+    }
+    return MKDA_OK;
+}
+
+int ensure_smem(const void* func, int bytes, const char* what) {
+    cudaError_t e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) {
+        snprintf(g_err, sizeof(g_err), "%s: cannot reserve %d bytes of shared memory: %s", what, bytes, cudaGetErrorString(e));
+        (void)cudaGetLastError();
+        return MKDA_ERR_LAUNCH;
+    }
+    return MKDA_OK;
+}
+
+}  // namespace mkda
+
+extern "C" const char* mkda_last_error(void) { return mkda::g_err; }
+extern "C" int mkda_abi_version(void) { return 1; }
+extern "C" int mkda_struct_sizes(int* out, int n) {
+    const int sizes[] = {
+        (int)sizeof(MkdaLayout),   (int)sizeof(MkdaGateFwd),  (int)sizeof(MkdaGateBwd),     (int)sizeof(MkdaReduce),
+        (int)sizeof(MkdaL2Norm),   (int)sizeof(MkdaIntraFwd), (int)sizeof(MkdaRecurFwd),    (int)sizeof(MkdaOutFwd),
+        (int)sizeof(MkdaEpilogueBwd), (int)sizeof(MkdaBwdDh), (int)sizeof(MkdaBwdWy),       (int)sizeof(MkdaBwdSgrad),
+        (int)sizeof(MkdaBwdIntra), (int)sizeof(MkdaQkGrad),   (int)sizeof(MkdaCombine)};
+    const int cnt = (int)(sizeof(sizes) / sizeof(sizes[0]));
+    for (int i = 0; i < n && i < cnt; ++i) out[i] = sizes[i];
+    return cnt;
+}

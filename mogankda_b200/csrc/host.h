@@ -1,0 +1,10 @@
+// Host-side helpers shared by the launchers: error text behind mkda_last_error() and launch checking.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace mkda {
+int set_error(int code, const char* msg);
+int check_launch(const char* what);
+// Raises the dynamic shared memory limit of `func` once per process; returns 0 or an error code.
+int ensure_smem(const void* func, int bytes, const char* what);
+}  // namespace mkda

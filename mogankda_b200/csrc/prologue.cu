@@ -1,0 +1,332 @@
+// HBM-bound elementwise / scan kernels around the chunk contractions:
+//   gate activation + chunk-local cumsum (forward), gate backward with the reverse cumsum folded in,
+//   L2-norm statistics, GVA group sum + L2-norm backward, gated RMSNorm backward, deterministic partial reductions.
+// All of them move each tensor once with 128-bit accesses; one warp covers one 128-wide row.
+#include "common.cuh"
+#include "host.h"
+
+namespace mkda {
+
+__device__ __forceinline__ float4 splat4(float a) { return make_float4(a, a, a, a); }
+__device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ float4 mul4(float4 a, float4 b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); }
+__device__ __forceinline__ float4 scale4(float4 a, float s) { return make_float4(a.x * s, a.y * s, a.z * s, a.w * s); }
+__device__ __forceinline__ float hsum4(float4 a) { return (a.x + a.y) + (a.z + a.w); }
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// natural-log decay for one element; s = x + dt_bias, E = exp(A_log), lb = lower bound (< 0)
+__device__ __forceinline__ float gate_value(int mode, float s, float E, float lb) {
+    if (mode == MKDA_GATE_GDN) return fmaxf(-E * softplusf_(s), lb);
+    if (mode == MKDA_GATE_KIMI) return lb * sigmoidf_(E * s);
+    if (mode == MKDA_GATE_EDA) return lb + (-lb) * expf(-(E / fabsf(lb)) * softplusf_(s));
+    return s;
+}
+// d gate / d s  and  d gate / d A_log
+__device__ __forceinline__ void gate_grad(int mode, float s, float E, float lb, float& ds, float& dA) {
+    if (mode == MKDA_GATE_GDN) {
+        const float sp = softplusf_(s);
+        const float keep = (-E * sp >= lb) ? 1.f : 0.f;    // clamp passes no gradient
+        ds = keep * (-E) * sigmoidf_(s);
+        dA = keep * (-E) * sp;
+    } else if (mode == MKDA_GATE_KIMI) {
+        const float u = E * s, sg = sigmoidf_(u), d = lb * sg * (1.f - sg);
+        ds = d * E;
+        dA = d * u;
+    } else if (mode == MKDA_GATE_EDA) {
+        const float sp = softplusf_(s), c = E / fabsf(lb), w = expf(-c * sp), d = lb * w * c;
+        ds = d * sigmoidf_(s);
+        dA = d * sp;
+    } else {
+        ds = 1.f;
+        dA = 0.f;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// forward: grid (NC, HV), 128 threads.  Warp w owns rows 16w..16w+15 of the chunk, lane l channels 4l..4l+3.
+// The chunk-local inclusive sum is (sum of the earlier warps' totals, in warp order) + (running sum inside the
+// warp): the association depends only on the row index, never on later rows.
+// ---------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) gate_cumsum_fwd_kernel(const MkdaGateFwd p) {
+    const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV;
+    const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ float4 tot[4][32];
+    const float E = p.A_log ? expf(p.A_log[h]) : 1.f;
+    float4 bias = splat4(0.f);
+    if (p.dt_bias) bias = p.scalar_gate ? splat4(p.dt_bias[h]) : *reinterpret_cast<const float4*>(p.dt_bias + h * 128 + 4 * lane);
+    float4 run = splat4(0.f);
+    float4 vals[16];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+        const int row = warp * 16 + r;
+        float4 gv = splat4(0.f);
+        if (row < len) {
+            const size_t th = (size_t)(start + row) * HV + h;
+            float4 xv = p.scalar_gate ? splat4(ld1(p.x, p.x_dtype, th)) : ld4(p.x, p.x_dtype, th * 128 + 4 * lane);
+            xv = add4(xv, bias);
+            gv.x = gate_value(p.mode, xv.x, E, p.lower_bound);
+            gv.y = gate_value(p.mode, xv.y, E, p.lower_bound);
+            gv.z = gate_value(p.mode, xv.z, E, p.lower_bound);
+            gv.w = gate_value(p.mode, xv.w, E, p.lower_bound);
+        }
+        run = add4(run, gv);
+        vals[r] = run;
+    }
+    tot[warp][lane] = run;
+    __syncthreads();
+    float4 pre = splat4(0.f);
+    for (int w = 0; w < warp; ++w) pre = add4(pre, tot[w][lane]);
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+        const int row = warp * 16 + r;
+        if (row < len) {
+            const size_t th = (size_t)(start + row) * HV + h;
+            *reinterpret_cast<float4*>(p.g_c + th * 128 + 4 * lane) = scale4(add4(pre, vals[r]), RCP_LN2);
+        }
+    }
+    if (p.beta_raw && threadIdx.x < len) {
+        const size_t th = (size_t)(start + threadIdx.x) * HV + h;
+        const float b = ld1(p.beta_raw, p.beta_dtype, th);
+        p.beta_out[th] = p.beta_sigmoid ? p.beta_scale * sigmoidf_(b) : b;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// backward: same tiling; suffix sums instead of prefix sums.
+// ---------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) gate_bwd_kernel(const MkdaGateBwd p) {
+    const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV;
+    const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ float4 tot[4][32];
+    __shared__ float4 red[2][4][32];
+    float4 vals[16];
+    float4 run = splat4(0.f);
+#pragma unroll
+    for (int r = 15; r >= 0; --r) {
+        const int row = warp * 16 + r;
+        float4 v = splat4(0.f);
+        if (row < len) v = *reinterpret_cast<const float4*>(p.dgp + ((size_t)(start + row) * HV + h) * 128 + 4 * lane);
+        run = add4(run, v);
+        vals[r] = run;
+    }
+    tot[warp][lane] = run;
+    __syncthreads();
+    float4 post = splat4(0.f);
+    for (int w = 3; w > warp; --w) post = add4(post, tot[w][lane]);
+    const float E = p.A_log ? expf(p.A_log[h]) : 1.f;
+    float4 bias = splat4(0.f);
+    if (p.dt_bias) bias = p.scalar_gate ? splat4(p.dt_bias[h]) : *reinterpret_cast<const float4*>(p.dt_bias + h * 128 + 4 * lane);
+    float4 pa = splat4(0.f), pb = splat4(0.f);
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+        const int row = warp * 16 + r;
+        if (row >= len) continue;                       // warp-uniform
+        const size_t th = (size_t)(start + row) * HV + h;
+        float4 dg = add4(vals[r], post);
+        if (p.scalar_gate) {
+            const float dgs = warp_sum(hsum4(dg));
+            const float s = ld1(p.x, p.x_dtype, th) + bias.x;
+            float ds, dA;
+            gate_grad(p.mode, s, E, p.lower_bound, ds, dA);
+            const float dxs = dgs * ds;
+            if (lane == 0) st1(p.dx, p.dx_dtype, th, dxs);
+            pb.x += dxs;
+            pa.x += dgs * dA;
+        } else {
+            float4 xv = add4(ld4(p.x, p.x_dtype, th * 128 + 4 * lane), bias);
+            float4 ds, dA;
+            gate_grad(p.mode, xv.x, E, p.lower_bound, ds.x, dA.x);
+            gate_grad(p.mode, xv.y, E, p.lower_bound, ds.y, dA.y);
+            gate_grad(p.mode, xv.z, E, p.lower_bound, ds.z, dA.z);
+            gate_grad(p.mode, xv.w, E, p.lower_bound, ds.w, dA.w);
+            const float4 dxv = mul4(dg, ds);
+            st4(p.dx, p.dx_dtype, th * 128 + 4 * lane, dxv);
+            pb = add4(pb, dxv);
+            pa = add4(pa, mul4(dg, dA));
+        }
+    }
+    if (!p.part_bias && !p.part_alog) return;
+    red[0][warp][lane] = pb;
+    red[1][warp][lane] = pa;
+    __syncthreads();
+    if (warp == 0) {
+        float4 sb = red[0][0][lane], sa = red[1][0][lane];
+        for (int w = 1; w < 4; ++w) { sb = add4(sb, red[0][w][lane]); sa = add4(sa, red[1][w][lane]); }
+        const size_t ch = (size_t)c * HV + h;
+        if (p.scalar_gate) {
+            if (lane == 0) {
+                if (p.part_bias) p.part_bias[ch] = sb.x;
+                if (p.part_alog) p.part_alog[ch] = sa.x;
+            }
+        } else {
+            if (p.part_bias) *reinterpret_cast<float4*>(p.part_bias + ch * 128 + 4 * lane) = sb;
+            if (p.part_alog) *reinterpret_cast<float4*>(p.part_alog + ch * 128 + 4 * lane) = sa;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// deterministic second-stage reductions
+// ---------------------------------------------------------------------------------------------------------
+// group == 1: block (32, 8); thread (x, y) sums rows y, y+8, ... of column j, then the 8 partials are added in order.
+__global__ void __launch_bounds__(256) reduce_cols_kernel(const float* __restrict__ in, int rows, int cols, float* __restrict__ out) {
+    __shared__ float part[8][33];
+    const int j = blockIdx.x * 32 + threadIdx.x;
+    float s = 0.f;
+    if (j < cols)
+        for (int r = threadIdx.y; r < rows; r += 8) s += in[(size_t)r * cols + j];
+    part[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && j < cols) {
+        float t = part[0][threadIdx.x];
+        for (int y = 1; y < 8; ++y) t += part[y][threadIdx.x];
+        out[j] = t;
+    }
+}
+// group > 1: one block of 128 threads per output; thread i sums elements i, i+128, ... of each row's group.
+__global__ void __launch_bounds__(128) reduce_groups_kernel(const float* __restrict__ in, int rows, int cols, int group, float* __restrict__ out) {
+    __shared__ float part[128];
+    const int j = blockIdx.x;
+    float s = 0.f;
+    for (int r = 0; r < rows; ++r)
+        for (int i = threadIdx.x; i < group; i += 128) s += in[(size_t)r * cols + (size_t)j * group + i];
+    part[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = 64; o > 0; o >>= 1) {
+        if (threadIdx.x < o) part[threadIdx.x] += part[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[j] = part[0];
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// L2-norm statistics: one warp per row of 128.
+// ---------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) l2norm_rstd_kernel(const MkdaL2Norm p) {
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= p.rows) return;
+    const float4 v = ld4(p.x, p.dtype, (size_t)row * 128 + 4 * lane);
+    const float ss = warp_sum(hsum4(mul4(v, v)));
+    if (lane == 0) p.rstd[row] = 1.f / sqrtf(ss + p.eps);
+}
+
+// GVA group sum (fixed order) + L2-norm backward: one warp per (token, q/k head).
+__global__ void __launch_bounds__(128) qk_grad_finish_kernel(const MkdaQkGrad p) {
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= p.TT * p.HK) return;
+    const int tok = row / p.HK, hk = row % p.HK, G = p.HV / p.HK;
+    float4 s = splat4(0.f);
+    for (int g = 0; g < G; ++g)
+        s = add4(s, *reinterpret_cast<const float4*>(p.d_v + ((size_t)tok * p.HV + hk * G + g) * 128 + 4 * lane));
+    if (p.rstd) {
+        const float rs = p.rstd[row];
+        const float4 y = scale4(ld4(p.x, p.x_dtype, (size_t)row * 128 + 4 * lane), rs);
+        const float dot = warp_sum(hsum4(mul4(s, y)));
+        s = make_float4((s.x - dot * y.x) * rs, (s.y - dot * y.y) * rs, (s.z - dot * y.z) * rs, (s.w - dot * y.w) * rs);
+    }
+    st4(p.dx, p.dx_dtype, (size_t)row * 128 + 4 * lane, s);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// gated RMSNorm backward: block of 4 warps covers 64 rows (warp w rows w, w+4, ...); per-block weight partials.
+//   n = o rs, rs = rsqrt(mean o^2 + eps);  y = n w a(z);  dn = dy w a;  do = rs (dn - n mean(dn n));
+//   dz = dy n w a'(z);  dw = sum dy n a
+// ---------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) epilogue_bwd_kernel(const MkdaEpilogueBwd p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ float4 red[4][32];
+    float4 w = splat4(1.f);
+    if (p.norm_w) w = ld4(p.norm_w, p.norm_w_dtype, 4 * lane);
+    float4 dw = splat4(0.f);
+    for (int i = 0; i < 16; ++i) {
+        const int row = blockIdx.x * 64 + i * 4 + warp;
+        if (row >= p.rows) break;
+        const size_t off = (size_t)row * 128 + 4 * lane;
+        const float4 o = *reinterpret_cast<const float4*>(p.o_raw + off);
+        const float4 dy = ld4(p.dy, p.dy_dtype, off);
+        const float4 z = ld4(p.gate, p.gate_dtype, off);
+        const float rs = 1.f / sqrtf(warp_sum(hsum4(mul4(o, o))) * (1.f / 128.f) + p.eps);
+        float a[4], da[4];
+        const float zz[4] = {z.x, z.y, z.z, z.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float sg = sigmoidf_(zz[e]);
+            if (p.act == MKDA_ACT_SILU) { a[e] = zz[e] * sg; da[e] = sg * (1.f + zz[e] * (1.f - sg)); }
+            else { a[e] = sg; da[e] = sg * (1.f - sg); }
+        }
+        const float4 n = scale4(o, rs);
+        const float4 av = make_float4(a[0], a[1], a[2], a[3]), dav = make_float4(da[0], da[1], da[2], da[3]);
+        const float4 dn = mul4(mul4(dy, w), av);
+        const float m = warp_sum(hsum4(mul4(dn, n))) * (1.f / 128.f);
+        const float4 dov = make_float4(rs * (dn.x - n.x * m), rs * (dn.y - n.y * m), rs * (dn.z - n.z * m), rs * (dn.w - n.w * m));
+        *reinterpret_cast<float4*>(p.d_o + off) = dov;
+        st4(p.dgate, p.dgate_dtype, off, mul4(mul4(mul4(dy, n), w), dav));
+        dw = add4(dw, mul4(mul4(dy, n), av));
+    }
+    if (!p.part_w) return;
+    red[warp][lane] = dw;
+    __syncthreads();
+    if (warp == 0) {
+        float4 s = red[0][lane];
+        for (int k = 1; k < 4; ++k) s = add4(s, red[k][lane]);
+        *reinterpret_cast<float4*>(p.part_w + (size_t)blockIdx.x * 128 + 4 * lane) = s;
+    }
+}
+
+}  // namespace mkda
+
+using namespace mkda;
+
+extern "C" int mkda_gate_cumsum_fwd(const MkdaGateFwd* p, void* stream) {
+    if (!p || !p->x || !p->g_c || p->L.NC < 0) return set_error(MKDA_ERR_ARG, "gate_cumsum_fwd: null argument");
+    if (p->mode != MKDA_GATE_PRECOMPUTED && !(p->lower_bound < 0.f)) return set_error(MKDA_ERR_ARG, "gate_cumsum_fwd: lower_bound must be < 0");
+    if (p->beta_raw && !p->beta_out) return set_error(MKDA_ERR_ARG, "gate_cumsum_fwd: beta_out missing");
+    if (p->L.NC == 0) return MKDA_OK;
+    gate_cumsum_fwd_kernel<<<dim3(p->L.NC, p->L.HV), 128, 0, (cudaStream_t)stream>>>(*p);
+    return check_launch("gate_cumsum_fwd");
+}
+
+extern "C" int mkda_gate_bwd(const MkdaGateBwd* p, void* stream) {
+    if (!p || !p->x || !p->dgp || !p->dx) return set_error(MKDA_ERR_ARG, "gate_bwd: null argument");
+    if (p->L.NC == 0) return MKDA_OK;
+    gate_bwd_kernel<<<dim3(p->L.NC, p->L.HV), 128, 0, (cudaStream_t)stream>>>(*p);
+    return check_launch("gate_bwd");
+}
+
+extern "C" int mkda_reduce_partials(const MkdaReduce* p, void* stream) {
+    if (!p || !p->in || !p->out || p->group < 1 || p->cols % p->group) return set_error(MKDA_ERR_ARG, "reduce_partials: bad argument");
+    if (p->cols == 0) return MKDA_OK;
+    if (p->group == 1)
+        reduce_cols_kernel<<<(p->cols + 31) / 32, dim3(32, 8), 0, (cudaStream_t)stream>>>(p->in, p->rows, p->cols, p->out);
+    else
+        reduce_groups_kernel<<<p->cols / p->group, 128, 0, (cudaStream_t)stream>>>(p->in, p->rows, p->cols, p->group, p->out);
+    return check_launch("reduce_partials");
+}
+
+extern "C" int mkda_l2norm_rstd(const MkdaL2Norm* p, void* stream) {
+    if (!p || !p->x || !p->rstd) return set_error(MKDA_ERR_ARG, "l2norm_rstd: null argument");
+    if (p->rows == 0) return MKDA_OK;
+    l2norm_rstd_kernel<<<(p->rows + 3) / 4, 128, 0, (cudaStream_t)stream>>>(*p);
+    return check_launch("l2norm_rstd");
+}
+
+extern "C" int mkda_qk_grad_finish(const MkdaQkGrad* p, void* stream) {
+    if (!p || !p->d_v || !p->dx || (p->rstd && !p->x) || p->HK <= 0 || p->HV % p->HK) return set_error(MKDA_ERR_ARG, "qk_grad_finish: bad argument");
+    const int rows = p->TT * p->HK;
+    if (rows == 0) return MKDA_OK;
+    qk_grad_finish_kernel<<<(rows + 3) / 4, 128, 0, (cudaStream_t)stream>>>(*p);
+    return check_launch("qk_grad_finish");
+}
+
+extern "C" int mkda_epilogue_bwd(const MkdaEpilogueBwd* p, void* stream) {
+    if (!p || !p->dy || !p->o_raw || !p->gate || !p->d_o || !p->dgate) return set_error(MKDA_ERR_ARG, "epilogue_bwd: null argument");
+    if (p->rows == 0) return MKDA_OK;
+    epilogue_bwd_kernel<<<(p->rows + 63) / 64, 128, 0, (cudaStream_t)stream>>>(*p);
+    return check_launch("epilogue_bwd");
+}

@@ -1,0 +1,297 @@
+"""One Python wrapper per kernel entry point: allocate the outputs with torch, fill the parameter struct, launch on
+the current CUDA stream.  Same division of labour as the reference's kernel wrappers (e.g.
+mogan_kda/ops/kimi_delta_rule/chunk/hopper/kkt_solve_kda.py:546-623): the kernels never allocate.
+
+Every function here requires CUDA tensors; there is no CPU path.
+"""
+import torch
+
+from . import _lib
+from ._lib import STRUCTS
+from .index import Layout
+
+_DT = {torch.float32: _lib.MKDA_F32, torch.bfloat16: _lib.MKDA_BF16, torch.float16: _lib.MKDA_F16}
+GATE_MODES = {"precomputed": _lib.MKDA_GATE_PRECOMPUTED, "eda": _lib.MKDA_GATE_EDA, "kimi": _lib.MKDA_GATE_KIMI,
+              "gdn": _lib.MKDA_GATE_GDN}
+ACTS = {"silu": _lib.MKDA_ACT_SILU, "swish": _lib.MKDA_ACT_SILU, "sigmoid": _lib.MKDA_ACT_SIGMOID}
+
+
+def _dt(t):
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}; expected float32, bfloat16 or float16") from None
+
+
+def _ptr(t, dtype=None):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise RuntimeError("mogankda_b200 kernels need CUDA tensors (there is no CPU fallback)")
+    if not t.is_contiguous():
+        raise RuntimeError("kernel operands must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError(f"expected {dtype}, got {t.dtype}")
+    return t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _layout_struct(lay: Layout, HK, HV, segments=True):
+    L = STRUCTS["MkdaLayout"]()
+    L.TT, L.NC, L.HK, L.HV = lay.TT, lay.NC, HK, HV
+    L.chunk_start, L.chunk_len = _ptr(lay.chunk_start), _ptr(lay.chunk_len)
+    if segments:
+        L.NS, L.seg_chunk_off = lay.NS, _ptr(lay.seg_chunk_off)
+    else:
+        L.NS, L.seg_chunk_off = lay.N, _ptr(lay.seq_chunk_off)
+    return L
+
+
+def _f32(t):
+    return None if t is None else t.float().contiguous()
+
+
+def gate_cumsum_fwd(lay, x, mode, A_log, dt_bias, lower_bound, HV, beta_raw=None, beta_sigmoid=False, beta_scale=1.0):
+    """x [B,T,HV,128] or [B,T,HV] -> (g_c fp32 [TT,HV,128], beta_e fp32 [TT,HV] or None)."""
+    scalar = x.dim() == 3
+    p = STRUCTS["MkdaGateFwd"]()
+    p.L = _layout_struct(lay, 1, HV)
+    alloc = torch.empty if lay.covers_all else torch.zeros
+    g_c = alloc(lay.TT, HV, 128, dtype=torch.float32, device=x.device)
+    p.x, p.x_dtype, p.scalar_gate = _ptr(x), _dt(x), int(scalar)
+    A_log, dt_bias = _f32(A_log), _f32(dt_bias)
+    p.A_log, p.dt_bias = _ptr(A_log), _ptr(dt_bias)
+    p.mode = GATE_MODES[mode]
+    p.lower_bound = float("-inf") if lower_bound is None else float(lower_bound)
+    if mode in ("eda", "kimi") and lower_bound is None:
+        raise ValueError(f"gate_mode={mode!r} needs lower_bound")
+    if mode == "gdn" and lower_bound is None:
+        p.lower_bound = -3.0e38
+    beta_e = None
+    if beta_raw is not None:
+        beta_e = alloc(lay.TT, HV, dtype=torch.float32, device=x.device)
+        p.beta_raw, p.beta_dtype = _ptr(beta_raw), _dt(beta_raw)
+        p.beta_sigmoid, p.beta_scale, p.beta_out = int(beta_sigmoid), float(beta_scale), _ptr(beta_e)
+    p.g_c = _ptr(g_c)
+    _lib.call("mkda_gate_cumsum_fwd", p, _stream())
+    return g_c, beta_e
+
+
+def reduce_partials(part, rows, cols, group=1):
+    out = torch.empty(cols // group, dtype=torch.float32, device=part.device)
+    p = STRUCTS["MkdaReduce"]()
+    p.rows, p.cols, p.group = rows, cols, group
+    setattr(p, "in", _ptr(part, torch.float32))
+    p.out = _ptr(out)
+    _lib.call("mkda_reduce_partials", p, _stream())
+    return out
+
+
+def gate_bwd(lay, x, dgp, mode, A_log, dt_bias, lower_bound, HV, want_bias, want_alog):
+    """-> (dx [like x], ddt_bias flat fp32 or None, dA_log fp32 [HV] or None)."""
+    scalar = x.dim() == 3
+    p = STRUCTS["MkdaGateBwd"]()
+    p.L = _layout_struct(lay, 1, HV)
+    dx = (torch.empty_like if lay.covers_all else torch.zeros_like)(x)
+    p.x, p.x_dtype, p.scalar_gate = _ptr(x), _dt(x), int(scalar)
+    A_log, dt_bias = _f32(A_log), _f32(dt_bias)
+    p.A_log, p.dt_bias = _ptr(A_log), _ptr(dt_bias)
+    p.mode = GATE_MODES[mode]
+    p.lower_bound = -3.0e38 if lower_bound is None else float(lower_bound)
+    p.dgp, p.dx, p.dx_dtype = _ptr(dgp, torch.float32), _ptr(dx), _dt(dx)
+    width = HV if scalar else HV * 128
+    part_b = part_a = None
+    if mode != "precomputed":
+        if want_bias:
+            part_b = torch.empty(lay.NC, width, dtype=torch.float32, device=x.device)
+            p.part_bias = _ptr(part_b)
+        if want_alog:
+            part_a = torch.empty(lay.NC, width, dtype=torch.float32, device=x.device)
+            p.part_alog = _ptr(part_a)
+    _lib.call("mkda_gate_bwd", p, _stream())
+    d_bias = reduce_partials(part_b, lay.NC, width) if part_b is not None else None
+    d_alog = reduce_partials(part_a, lay.NC, width, 1 if scalar else 128) if part_a is not None else None
+    return dx, d_bias, d_alog
+
+
+def l2norm_rstd(x, eps=1e-6):
+    """x [..., 128] -> rstd fp32 [rows]."""
+    rows = x.numel() // 128
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    p = STRUCTS["MkdaL2Norm"]()
+    p.x, p.dtype, p.rows, p.eps, p.rstd = _ptr(x), _dt(x), rows, eps, _ptr(rstd)
+    _lib.call("mkda_l2norm_rstd", p, _stream())
+    return rstd
+
+
+def intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV):
+    dev = q.device
+    z = lambda w: torch.empty(lay.TT, HV, w, dtype=torch.float32, device=dev)      # noqa: E731
+    A, Aqk, nw, u = z(64), z(64), z(128), z(128)
+    p = STRUCTS["MkdaIntraFwd"]()
+    p.L = _layout_struct(lay, HK, HV)
+    p.q, p.k, p.v, p.qkv_dtype = _ptr(q), _ptr(k), _ptr(v), _dt(q)
+    p.q_rstd, p.k_rstd = _ptr(q_rstd), _ptr(k_rstd)
+    p.g_c, p.beta, p.scale = _ptr(g_c, torch.float32), _ptr(beta_e, torch.float32), scale
+    p.A, p.Aqk, p.nw, p.u = _ptr(A), _ptr(Aqk), _ptr(nw), _ptr(u)
+    _lib.call("mkda_intra_fwd", p, _stream())
+    return A, Aqk, nw, u
+
+
+def recur_fwd(lay, nw, u, k, k_rstd, g_c, HK, HV, *, h0=None, seg_h0=None, state_v_first=False, store_h=True,
+              store_vd=True, want_ht=True, want_transition=False, segments=True):
+    """Runs the serial state pass over the layout's segments (or whole sequences with ``segments=False``).
+    Returns (h [NC,HV,128,128] or None, Vd [TT,HV,128] or None, ht [NS,HV,128,128] or None, mt or None)."""
+    dev = nw.device
+    NS = lay.NS if segments else lay.N
+    p = STRUCTS["MkdaRecurFwd"]()
+    p.L = _layout_struct(lay, HK, HV, segments)
+    p.nw, p.u, p.k, p.k_dtype, p.k_rstd = _ptr(nw), _ptr(u), _ptr(k), _dt(k), _ptr(k_rstd)
+    p.g_c = _ptr(g_c)
+    p.h0, p.seg_h0, p.state_v_first = _ptr(h0, torch.float32), _ptr(seg_h0, torch.int32), int(state_v_first)
+    h = torch.empty(lay.NC, HV, 128, 128, dtype=torch.float32, device=dev) if store_h else None
+    Vd = torch.empty(lay.TT, HV, 128, dtype=torch.float32, device=dev) if store_vd else None
+    ht = torch.empty(NS, HV, 128, 128, dtype=torch.float32, device=dev) if want_ht else None
+    mt = torch.empty(NS, HV, 128, 128, dtype=torch.float32, device=dev) if want_transition else None
+    p.h, p.Vd, p.ht, p.want_transition, p.mt = _ptr(h), _ptr(Vd), _ptr(ht), int(want_transition), _ptr(mt)
+    _lib.call("mkda_recur_fwd", p, _stream())
+    return h, Vd, ht, mt
+
+
+def out_fwd(lay, q, q_rstd, g_c, Aqk, Vd, h, scale, HK, HV, out_dtype, norm=None, keep_raw=False):
+    """norm = None or dict(weight, gate, act, eps).  Returns (out [TT,HV,128], o_raw fp32 or None)."""
+    dev = q.device
+    alloc = torch.empty if lay.covers_all else torch.zeros
+    out = alloc(lay.TT, HV, 128, dtype=out_dtype, device=dev)
+    o_raw = alloc(lay.TT, HV, 128, dtype=torch.float32, device=dev) if keep_raw else None
+    p = STRUCTS["MkdaOutFwd"]()
+    p.L = _layout_struct(lay, HK, HV)
+    p.q, p.q_dtype, p.q_rstd = _ptr(q), _dt(q), _ptr(q_rstd)
+    p.g_c, p.Aqk, p.Vd, p.h, p.scale = _ptr(g_c), _ptr(Aqk), _ptr(Vd), _ptr(h), scale
+    if norm is not None:
+        w, gate = norm.get("weight"), norm["gate"]
+        p.has_norm = 1
+        if w is not None:
+            p.norm_w, p.norm_w_dtype = _ptr(w), _dt(w)
+        p.gate, p.gate_dtype = _ptr(gate), _dt(gate)
+        p.act, p.eps = ACTS[norm.get("act", "silu")], float(norm.get("eps", 1e-6))
+    p.o_raw, p.out, p.out_dtype = _ptr(o_raw), _ptr(out), _dt(out)
+    _lib.call("mkda_out_fwd", p, _stream())
+    return out, o_raw
+
+
+def epilogue_bwd(dy, o_raw, weight, gate, act, eps):
+    """-> (do fp32 [rows,128], dgate [like gate], dweight fp32 [128] or None)."""
+    rows = o_raw.numel() // 128
+    dev = o_raw.device
+    d_o = torch.empty(rows, 128, dtype=torch.float32, device=dev)
+    dgate = torch.empty_like(gate)
+    nblk = (rows + 63) // 64
+    part = torch.empty(nblk, 128, dtype=torch.float32, device=dev) if weight is not None else None
+    p = STRUCTS["MkdaEpilogueBwd"]()
+    p.rows = rows
+    p.dy, p.dy_dtype, p.o_raw = _ptr(dy), _dt(dy), _ptr(o_raw, torch.float32)
+    if weight is not None:
+        p.norm_w, p.norm_w_dtype = _ptr(weight), _dt(weight)
+    p.gate, p.gate_dtype, p.act, p.eps = _ptr(gate), _dt(gate), ACTS[act], float(eps)
+    p.d_o, p.dgate, p.dgate_dtype, p.part_w = _ptr(d_o), _ptr(dgate), _dt(dgate), _ptr(part)
+    _lib.call("mkda_epilogue_bwd", p, _stream())
+    dw = reduce_partials(part, nblk, 128) if part is not None else None
+    return d_o, dgate, dw
+
+
+def bwd_dh(lay, d_o, q, k, q_rstd, k_rstd, g_c, Aqk, nw, scale, HK, HV, *, dht=None, seg_dht=None,
+           state_v_first=False, want_dh0=True, segments=True, dh=None, dVd=None):
+    dev = nw.device
+    NS = lay.NS if segments else lay.N
+    p = STRUCTS["MkdaBwdDh"]()
+    p.L = _layout_struct(lay, HK, HV, segments)
+    p.d_o, p.do_dtype = _ptr(d_o), _dt(d_o)
+    p.q, p.k, p.qk_dtype, p.q_rstd, p.k_rstd = _ptr(q), _ptr(k), _dt(q), _ptr(q_rstd), _ptr(k_rstd)
+    p.g_c, p.Aqk, p.nw, p.scale = _ptr(g_c), _ptr(Aqk), _ptr(nw), scale
+    p.dht, p.seg_dht, p.state_v_first = _ptr(dht, torch.float32), _ptr(seg_dht, torch.int32), int(state_v_first)
+    if dh is None:
+        dh = torch.empty(lay.NC, HV, 128, 128, dtype=torch.float32, device=dev)
+    if dVd is None:
+        dVd = torch.empty(lay.TT, HV, 128, dtype=torch.float32, device=dev)
+    dh0 = torch.empty(NS, HV, 128, 128, dtype=torch.float32, device=dev) if want_dh0 else None
+    p.dh, p.dVd, p.dh0 = _ptr(dh), _ptr(dVd), _ptr(dh0)
+    _lib.call("mkda_bwd_dh", p, _stream())
+    return dh, dVd, dh0
+
+
+def bwd_wy(lay, k, v, k_rstd, g_c, beta_e, A, h, d_o, dVd, HK, HV):
+    dev = k.device
+    z = lambda *s: torch.empty(lay.TT, HV, *s, dtype=torch.float32, device=dev)      # noqa: E731
+    alloc = torch.empty if lay.covers_all else torch.zeros
+    Vd, dAqk, dL, dbeta_w = z(128), z(64), z(64), z()
+    dX = alloc(lay.TT, HV, 128, dtype=torch.float32, device=dev)
+    p = STRUCTS["MkdaBwdWy"]()
+    p.L = _layout_struct(lay, HK, HV)
+    p.k, p.v, p.kv_dtype, p.k_rstd = _ptr(k), _ptr(v), _dt(k), _ptr(k_rstd)
+    p.g_c, p.beta, p.A, p.h = _ptr(g_c), _ptr(beta_e), _ptr(A), _ptr(h)
+    p.d_o, p.do_dtype, p.dVd = _ptr(d_o), _dt(d_o), _ptr(dVd)
+    p.Vd, p.dX, p.dbeta_w, p.dAqk, p.dL = _ptr(Vd), _ptr(dX), _ptr(dbeta_w), _ptr(dAqk), _ptr(dL)
+    _lib.call("mkda_bwd_wy", p, _stream())
+    return Vd, dX, dbeta_w, dAqk, dL
+
+
+def bwd_sgrad(lay, q, k, q_rstd, k_rstd, g_c, d_o, dX, Vd, h, dh, scale, HK, HV):
+    dev = q.device
+    z = lambda: torch.empty(lay.TT, HV, 128, dtype=torch.float32, device=dev)      # noqa: E731
+    dq_p, dk_p, dg_p = z(), z(), z()
+    p = STRUCTS["MkdaBwdSgrad"]()
+    p.L = _layout_struct(lay, HK, HV)
+    p.q, p.k, p.qk_dtype, p.q_rstd, p.k_rstd = _ptr(q), _ptr(k), _dt(q), _ptr(q_rstd), _ptr(k_rstd)
+    p.g_c, p.d_o, p.do_dtype, p.dX, p.Vd = _ptr(g_c), _ptr(d_o), _dt(d_o), _ptr(dX), _ptr(Vd)
+    p.h, p.dh, p.scale = _ptr(h), _ptr(dh), scale
+    p.dq_p, p.dk_p, p.dg_p = _ptr(dq_p), _ptr(dk_p), _ptr(dg_p)
+    _lib.call("mkda_bwd_sgrad", p, _stream())
+    return dq_p, dk_p, dg_p
+
+
+def bwd_intra(lay, q, k, q_rstd, k_rstd, g_c, beta_e, dAqk, dL, dq_p, dk_p, dg_p, dbeta_w, scale, HK, HV,
+              beta_raw, beta_sigmoid, beta_scale):
+    dev = q.device
+    alloc = torch.empty if lay.covers_all else torch.zeros
+    z = lambda: alloc(lay.TT, HV, 128, dtype=torch.float32, device=dev)      # noqa: E731
+    dq_v, dk_v, dgp = z(), z(), z()
+    dbeta = alloc(lay.TT, HV, dtype=beta_raw.dtype, device=dev)
+    p = STRUCTS["MkdaBwdIntra"]()
+    p.L = _layout_struct(lay, HK, HV)
+    p.q, p.k, p.qk_dtype, p.q_rstd, p.k_rstd = _ptr(q), _ptr(k), _dt(q), _ptr(q_rstd), _ptr(k_rstd)
+    p.g_c, p.beta, p.dAqk, p.dL = _ptr(g_c), _ptr(beta_e), _ptr(dAqk), _ptr(dL)
+    p.dq_p, p.dk_p, p.dg_p, p.dbeta_w, p.scale = _ptr(dq_p), _ptr(dk_p), _ptr(dg_p), _ptr(dbeta_w), scale
+    p.beta_raw, p.beta_dtype = _ptr(beta_raw), _dt(beta_raw)
+    p.beta_sigmoid, p.beta_scale = int(beta_sigmoid), float(beta_scale)
+    p.dq_v, p.dk_v, p.dgp, p.dbeta, p.dbeta_dtype = _ptr(dq_v), _ptr(dk_v), _ptr(dgp), _ptr(dbeta), _dt(dbeta)
+    _lib.call("mkda_bwd_intra", p, _stream())
+    return dq_v, dk_v, dgp, dbeta
+
+
+def qk_grad_finish(d_v, x, rstd, HK, HV):
+    """d_v fp32 [TT,HV,128] -> gradient w.r.t. the raw q or k, [TT,HK,128] in x.dtype."""
+    TT = d_v.shape[0]
+    dx = torch.empty(TT, HK, 128, dtype=x.dtype, device=x.device)
+    p = STRUCTS["MkdaQkGrad"]()
+    p.TT, p.HK, p.HV = TT, HK, HV
+    p.d_v, p.x, p.x_dtype, p.rstd = _ptr(d_v, torch.float32), _ptr(x), _dt(x), _ptr(rstd)
+    p.dx, p.dx_dtype = _ptr(dx), _dt(dx)
+    _lib.call("mkda_qk_grad_finish", p, _stream())
+    return dx
+
+
+def state_combine(grp_seg_off, NG, NS, HV, hs, ms, carry=None, reverse=False, want_out=True):
+    """-> (s_in [NS,HV,128,128], s_out [NG,HV,128,128] or None); all in [K,V] orientation."""
+    dev = hs.device
+    s_in = torch.empty(NS, HV, 128, 128, dtype=torch.float32, device=dev)
+    s_out = torch.empty(NG, HV, 128, 128, dtype=torch.float32, device=dev) if want_out else None
+    p = STRUCTS["MkdaCombine"]()
+    p.NG, p.HV, p.grp_seg_off = NG, HV, _ptr(grp_seg_off, torch.int32)
+    p.hs, p.ms, p.carry, p.reverse = _ptr(hs, torch.float32), _ptr(ms, torch.float32), _ptr(carry, torch.float32), int(reverse)
+    p.s_in, p.s_out = _ptr(s_in), _ptr(s_out)
+    _lib.call("mkda_state_combine", p, _stream())
+    return s_in, s_out
