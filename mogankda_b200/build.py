@@ -69,7 +69,7 @@ def build(force=False, variant="", prec=None, verbose=False):
             print(log)
     out = lib_path(variant)
     if force or jobs or not _newer(out, objs):
-        subprocess.check_call([nvcc, "-shared", "-o", out, *objs])
+        subprocess.check_call([nvcc, "-shared", "-Wno-deprecated-gpu-targets", "-o", out, *objs])
     return out
 
 

@@ -99,6 +99,8 @@ def l2norm(x):
 def _scan_tokens(q, k, v, g, beta, S):
     """q (scaled), k, g [B,T,HV,K]; v [B,T,HV,V]; beta [B,T,HV]; S [B,HV,K,V]."""
     out = []
+    if q.shape[1] == 0:
+        return v.new_zeros(v.shape), S
     for t in range(q.shape[1]):
         S = S * g[:, t].exp().unsqueeze(-1)
         kt = k[:, t]

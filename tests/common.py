@@ -1,0 +1,87 @@
+"""Shared helpers of the GPU parity tests: seeded inputs in the style of the reference's generator
+(tests/kda_common.py:133-162), runners for the CUDA path and the fp64 oracle, and the error metric."""
+import torch
+
+from oracle import kda_oracle as orc
+
+TOL = 2e-3                     # rel-err bar for fp32-typed results (max|a-b|/max|b| and mean|a-b|/mean|b|)
+BF16_MAX = 2.0 ** -8           # worst-case relative rounding of one bf16 store
+BF16_MEAN = 1.6e-3             # mean relative rounding of a bf16 store (log-uniform mantissas: 2^-9 / 1.44 ~ 1.36e-3)
+VARLEN_CU = (0, 1, 98, 354, 504, 704)
+
+
+def tolerances(t):
+    """(max_rel, mean_rel) allowed for a result stored in t.dtype: the 2e-3 bar plus, for 16-bit outputs, the
+    quantum of the store itself (the oracle is never rounded)."""
+    if t.dtype == torch.float32:
+        return TOL, TOL
+    return TOL + BF16_MAX, TOL + BF16_MEAN
+
+
+def check(name, got, ref):
+    assert got is not None, f"{name}: missing"
+    assert got.shape == ref.shape, f"{name}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
+    assert torch.isfinite(got.float()).all(), f"{name}: non-finite values"
+    mx, mn = orc.rel_err(got, ref.to(got.device))
+    tmx, tmn = tolerances(got)
+    assert mx <= tmx and mn <= tmn, f"{name}: max_rel {mx:.3e} (tol {tmx:.1e}) mean_rel {mn:.3e} (tol {tmn:.1e})"
+    return mx, mn
+
+
+def make_inputs(*, B=1, T=256, HK=2, HV=4, cu=None, dtype=torch.float32, gate="eda", scalar=False, beta="sigmoid",
+                l2=True, epi="silu", h0=True, seed=0, device="cuda", x_dtype=torch.float32):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    r = lambda *s: torch.randn(*s, generator=g)                       # noqa: E731
+    N = B if cu is None else len(cu) - 1
+    q, k = r(B, T, HK, 128), r(B, T, HK, 128)
+    if not l2:
+        q, k = torch.nn.functional.normalize(q, dim=-1), torch.nn.functional.normalize(k, dim=-1)
+    lv = dict(q=q.to(dtype), k=k.to(dtype), v=r(B, T, HV, 128).to(dtype))
+    gshape = (B, T, HV) if scalar else (B, T, HV, 128)
+    if gate == "precomputed":
+        lv["g"] = -5.0 * torch.sigmoid(r(*gshape))
+    else:
+        lv["g"] = r(*gshape).to(x_dtype)
+        hi = 0.8 if gate == "gdn" else 4.0
+        lv["A_log"] = (torch.rand(HV, generator=g) * (hi - 0.2) + 0.2).log()
+        lv["dt_bias"] = r(*gshape[2:]) * 0.5 - 1.0
+    lv["beta"] = r(B, T, HV) if beta == "sigmoid" else torch.sigmoid(r(B, T, HV))
+    if h0:
+        lv["h0"] = r(N, HV, 128, 128) * 0.1
+    if epi:
+        lv["ep_w"] = 1.0 + 0.1 * r(128)
+        lv["ep_gate"] = r(B, T, HV, 128).to(dtype)
+    lv = {n: t.to(device) for n, t in lv.items()}
+    do = r(B, T, HV, 128).to(device)
+    if not epi:
+        do = do.to(dtype).float()      # autograd hands the kernel dO in the dtype of o: give the oracle the same values
+    dht = (r(N, HV, 128, 128) * 0.1).to(device)
+    cu_t = None if cu is None else torch.tensor(cu, dtype=torch.int32, device=device)
+    opts = dict(gate_mode=gate, lower_bound=-5.0, beta_mode=beta, beta_scale=2.0 if beta == "sigmoid" else 1.0,
+                use_qk_l2norm_in_kernel=l2, cu_seqlens=cu_t, output_final_state=True)
+    return lv, do, dht, opts, (epi or None)
+
+
+def run(fn, lv, do, dht, opts, epi, *, f64=False, vfirst=False, grads=True, **extra):
+    """Calls ``fn`` (the CUDA API or an oracle with the same keywords); returns dict(o, ht, d<leaf>...)."""
+    lv = {n: (t.double() if f64 else t).clone().requires_grad_(grads) for n, t in lv.items()}
+    kw = dict(opts, A_log=lv.get("A_log"), dt_bias=lv.get("dt_bias"), state_v_first=vfirst, **extra)
+    h0 = lv.get("h0")
+    if h0 is not None and vfirst:
+        h0 = h0.transpose(-1, -2).contiguous()
+    kw["initial_state"] = h0
+    if epi:
+        kw["output_norm"] = dict(weight=lv["ep_w"], gate=lv["ep_gate"], act=epi, eps=1e-6)
+    o, ht = fn(lv["q"], lv["k"], lv["v"], lv["g"], lv["beta"], **kw)
+    res = dict(o=o, ht=ht)
+    if grads:
+        d = dht.transpose(-1, -2) if vfirst else dht
+        loss = (o.double() * do.double()).sum() + (ht.double() * d.double()).sum()
+        for n, gr in zip(lv, torch.autograd.grad(loss, list(lv.values()))):
+            res["d" + n] = gr
+    return res
+
+
+def compare(got, ref):
+    for n, r in ref.items():
+        check(n, got[n], r)

@@ -1,0 +1,71 @@
+"""CPU: the C-ABI library builds, loads, exports every symbol include/mkda.h declares and agrees with the header on
+struct layout; host-side argument checks fail loudly (no compute is launched here)."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from mogankda_b200 import build, _lib
+    build.build()
+    return _lib.load()
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "mkda.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return re.findall(r"^\s*(?:int|const char\*)\s+(mkda_\w+)\s*\(", text, flags=re.M)
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = _declared_functions()
+    assert len(names) >= 17
+    for n in names:
+        assert hasattr(lib, n), n
+
+
+def test_struct_sizes_match_header(lib):
+    from mogankda_b200 import _lib
+    n = len(_lib.STRUCT_ORDER)
+    sizes = (ctypes.c_int * n)()
+    assert lib.mkda_struct_sizes(sizes, n) == n
+    for i, name in enumerate(_lib.STRUCT_ORDER):
+        assert sizes[i] == ctypes.sizeof(_lib.STRUCTS[name]), name
+    assert lib.mkda_abi_version() == 1
+
+
+def test_null_arguments_are_rejected_without_launch(lib):
+    from mogankda_b200 import _lib
+    p = _lib.STRUCTS["MkdaIntraFwd"]()
+    rc = lib.mkda_intra_fwd(ctypes.byref(p), None)
+    assert rc == _lib.MKDA_ERR_ARG
+    assert b"intra_fwd" in lib.mkda_last_error()
+
+
+def test_cpu_tensors_fail_loudly():
+    import mogankda_b200 as mk
+    q = torch.randn(1, 64, 2, 128)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        mk.chunk_kda(q, q, q, -torch.rand(1, 64, 2, 128), torch.rand(1, 64, 2))
+
+
+def test_api_argument_errors():
+    import mogankda_b200 as mk
+    q = torch.randn(1, 64, 2, 128)
+    with pytest.raises(AssertionError):
+        mk.chunk_kda(q, q, q, -torch.rand(1, 64, 2), torch.rand(1, 64, 2))          # scalar gate into chunk_kda
+    with pytest.raises(AssertionError):
+        mk.chunk_gated_delta_rule(q, q, q, -torch.rand(1, 64, 2), torch.rand(1, 64, 2), head_first=True)
+
+
+def test_product_does_not_import_the_oracle():
+    pkg = os.path.join(ROOT, "mogankda_b200")
+    for fn in os.listdir(pkg):
+        if fn.endswith(".py"):
+            assert "oracle" not in open(os.path.join(pkg, fn)).read(), fn

@@ -1,0 +1,48 @@
+"""CPU: chunk / segment tables (host logic) against the oracle's table and hand-checked cases."""
+import pytest
+
+from mogankda_b200.index import build_tables
+from oracle import kda_oracle as orc
+
+VARLEN = [0, 1, 98, 354, 504, 704]          # lengths 1, 97, 256, 150, 200 (the reference's standard ragged layout)
+
+
+@pytest.mark.parametrize("B,T,cu", [(2, 300, None), (1, 704, VARLEN), (1, 64, None), (1, 65, None), (3, 1, None)])
+def test_chunks_match_oracle(B, T, cu):
+    import torch
+    tb = build_tables(B, T, cu)
+    ref = orc.chunk_table(B, T, None if cu is None else torch.tensor(cu))
+    assert tb["chunk_start"] == ref["start"] and tb["chunk_len"] == ref["length"]
+    assert tb["seq_chunk_off"] == ref["seq_off"]
+    assert tb["seg_chunk_off"] == ref["seq_off"]          # no cutting: segments are the sequences
+    assert tb["covers_all"]
+
+
+def test_segments_have_fixed_length_and_cover_each_sequence():
+    tb = build_tables(1, 10000, [0, 100, 5000, 10000], seg_chunks=32)
+    # doc 0: 2 chunks -> 1 segment; doc 1: 77 chunks -> 3 segments; doc 2: 79 chunks -> 3 segments
+    assert tb["grp_seg_off"] == [0, 1, 4, 7]
+    so = tb["seg_chunk_off"]
+    assert so == [0, 2, 34, 66, 79, 111, 143, 158]
+    assert tb["seg_first"] == [0, 1, -1, -1, 2, -1, -1]
+    assert tb["seg_last"] == [0, -1, -1, 1, -1, -1, 2]
+    # a prefix of doc 1 is cut at the same places
+    tp = build_tables(1, 4000, [0, 100, 4000], seg_chunks=32)
+    assert tp["seg_chunk_off"] == [0, 2, 34, 63] and tp["seg_chunk_off"][:3] == so[:3]
+
+
+def test_padding_tokens_and_empty_sequences():
+    tb = build_tables(1, 200, [0, 50, 50, 130])
+    assert not tb["covers_all"]
+    assert tb["seq_chunk_off"] == [0, 1, 1, 3]
+    assert tb["seg_chunk_off"] == [0, 1, 1, 3]
+    assert tb["chunk_len"] == [50, 64, 16]
+
+
+def test_bad_cu_seqlens():
+    with pytest.raises(ValueError):
+        build_tables(2, 100, [0, 100])
+    with pytest.raises(ValueError):
+        build_tables(1, 100, [0, 120])
+    with pytest.raises(ValueError):
+        build_tables(1, 100, [0, 60, 40])

@@ -1,0 +1,149 @@
+"""GPU: every C-ABI kernel on its own, fed the oracle's fp64 intermediates (rounded to fp32) so that one kernel's error
+is isolated -- the same scheme as the reference's per-kernel tests (tests/test_kda_bwd_kernels.py:26-29)."""
+import pytest
+import torch
+
+from mogankda_b200 import ops
+from mogankda_b200.index import get_layout
+from oracle import kda_oracle as orc
+from tests.common import VARLEN_CU, make_inputs
+
+pytestmark = pytest.mark.gpu
+KTOL = 1e-3          # per-kernel bar (plain TF32 contractions measure ~3e-4, the compensated ones ~1e-6)
+
+
+def _err(name, got, ref, tol=KTOL):
+    assert got.shape == ref.shape, (name, got.shape, ref.shape)
+    mx, mn = orc.rel_err(got, ref.to(got.device))
+    assert mx <= tol and mn <= tol, f"{name}: max_rel {mx:.3e} mean_rel {mn:.3e}"
+
+
+@pytest.fixture(scope="module", params=["varlen-f32", "dense-bf16"])
+def world(request):
+    if request.param == "varlen-f32":
+        kw = dict(cu=VARLEN_CU, T=704, dtype=torch.float32, gate="eda", seed=21)
+    else:
+        kw = dict(B=2, T=300, dtype=torch.bfloat16, gate="kimi", seed=22)
+    lv, do, dht, opts, _ = make_inputs(HK=2, HV=4, **kw)
+    B, T = lv["q"].shape[:2]
+    cu = opts["cu_seqlens"]
+    qn, kn = orc.l2norm(lv["q"]), orc.l2norm(lv["k"])
+    gd = orc.gate_log_decay(lv["g"], opts["gate_mode"], lv["A_log"], lv["dt_bias"], -5.0)
+    be = orc.beta_value(lv["beta"], "sigmoid", 2.0)
+    bw = orc.chunked_backward(qn, kn, lv["v"], gd, be, do, dht=dht, initial_state=lv["h0"], cu_seqlens=cu)
+    lay = get_layout(B, T, cu, lv["q"].device)
+    f32 = lambda t: t.float().contiguous()                            # noqa: E731
+    w = dict(lv=lv, do=do.reshape(B * T, 4, 128), dht=dht, opts=opts, bw=bw, fw=bw["fwd"], lay=lay, TT=B * T, f32=f32,
+             be=f32(be.reshape(B * T, 4)), scale=128 ** -0.5)
+    w["q_rstd"], w["k_rstd"] = ops.l2norm_rstd(lv["q"]), ops.l2norm_rstd(lv["k"])
+    return w
+
+
+def test_gate_cumsum_and_beta(world):
+    lv, o = world["lv"], world["opts"]
+    g_c, beta_e = ops.gate_cumsum_fwd(world["lay"], lv["g"], o["gate_mode"], lv["A_log"], lv["dt_bias"], -5.0, 4,
+                                      beta_raw=lv["beta"], beta_sigmoid=True, beta_scale=2.0)
+    _err("g_c", g_c, world["fw"]["g_c"], 2e-5)
+    _err("beta", beta_e, world["be"], 2e-6)
+
+
+def test_l2norm_statistics(world):
+    q = world["lv"]["q"]
+    _err("rstd", world["q_rstd"], torch.rsqrt((q.double() ** 2).sum(-1) + 1e-6).reshape(-1), 2e-6)
+
+
+def test_intra_fwd(world):
+    lv, fw, f32 = world["lv"], world["fw"], world["f32"]
+    A, Aqk, nw, u = ops.intra_fwd(world["lay"], lv["q"], lv["k"], lv["v"], world["q_rstd"], world["k_rstd"],
+                                  f32(fw["g_c"]), world["be"], world["scale"], 2, 4)
+    for n, t in dict(A=A, Aqk=Aqk, nw=nw, u=u).items():
+        _err(n, t, fw[n])
+    idx = torch.arange(64, device="cuda")
+    lay = world["lay"]
+    for c in range(lay.NC):                       # exactly zero above the diagonal (reference: test_kkt_solve_kda.py:115-118)
+        s, n = int(lay.chunk_start[c]), int(lay.chunk_len[c])
+        rows = idx[:n, None]
+        assert (A[s:s + n][:, :, :].permute(0, 2, 1)[(idx[None, :] > rows)[:, :, None].expand(n, 64, 4)] == 0).all()
+        assert (Aqk[s:s + n].permute(0, 2, 1)[(idx[None, :] > rows)[:, :, None].expand(n, 64, 4)] == 0).all()
+
+
+def test_recurrence_and_output(world):
+    lv, fw, f32, lay = world["lv"], world["fw"], world["f32"], world["lay"]
+    h, Vd, ht, _ = ops.recur_fwd(lay, f32(fw["nw"]), f32(fw["u"]), lv["k"], world["k_rstd"], f32(fw["g_c"]), 2, 4,
+                                 h0=lv["h0"])
+    _err("h", h, fw["h"]); _err("Vd", Vd, fw["Vd"]); _err("ht", ht, fw["ht"])
+    o, _ = ops.out_fwd(lay, lv["q"], world["q_rstd"], f32(fw["g_c"]), f32(fw["Aqk"]), f32(fw["Vd"]), f32(fw["h"]),
+                       world["scale"], 2, 4, torch.float32)
+    _err("o", o, fw["o"])
+
+
+def test_transition_matrix_reproduces_the_state_pass(world):
+    """State leaving a segment = transition @ state entering + state reached from zero (what the prefix combine uses)."""
+    lv, fw, f32, lay = world["lv"], world["fw"], world["f32"], world["lay"]
+    args = (lay, f32(fw["nw"]), f32(fw["u"]), lv["k"], world["k_rstd"], f32(fw["g_c"]), 2, 4)
+    _, _, hs, ms = ops.recur_fwd(*args, store_h=False, store_vd=False, want_transition=True)
+    _, _, ht, _ = ops.recur_fwd(*args, h0=lv["h0"], store_h=False, store_vd=False)
+    _err("M h0 + h", ms.double() @ lv["h0"].double() + hs.double(), ht)
+    s_in, s_out = ops.state_combine(lay.grp_seg_off, lay.NG, lay.NS, 4, hs, ms, carry=lv["h0"])
+    assert torch.equal(s_in, lv["h0"])
+    _err("combine", s_out, fw["ht"])
+
+
+def test_bwd_dh(world):
+    lv, fw, bw, f32 = world["lv"], world["fw"], world["bw"], world["f32"]
+    dh, dVd, dh0 = ops.bwd_dh(world["lay"], world["do"], lv["q"], lv["k"], world["q_rstd"], world["k_rstd"],
+                              f32(fw["g_c"]), f32(fw["Aqk"]), f32(fw["nw"]), world["scale"], 2, 4, dht=world["dht"])
+    _err("dh", dh, bw["dh"]); _err("dVd", dVd, bw["dVd"]); _err("dh0", dh0, bw["dh0"])
+
+
+def test_bwd_wy_and_sgrad(world):
+    lv, fw, bw, f32, lay = world["lv"], world["fw"], world["bw"], world["f32"], world["lay"]
+    Vd, dX, dbw, dAqk, dL = ops.bwd_wy(lay, lv["k"], lv["v"], world["k_rstd"], f32(fw["g_c"]), world["be"], f32(fw["A"]),
+                                       f32(fw["h"]), world["do"], f32(bw["dVd"]), 2, 4)
+    for n, t in dict(Vd=Vd, dX=dX, dbeta_w=dbw, dAqk=dAqk, dL=dL).items():
+        _err(n, t, bw[n])
+    dq_p, dk_p, dg_p = ops.bwd_sgrad(lay, lv["q"], lv["k"], world["q_rstd"], world["k_rstd"], f32(fw["g_c"]),
+                                     world["do"], f32(bw["dX"]), f32(bw["Vd"]), f32(fw["h"]), f32(bw["dh"]),
+                                     world["scale"], 2, 4)
+    for n, t in dict(dq_p=dq_p, dk_p=dk_p, dg_p=dg_p).items():
+        _err(n, t, bw[n])
+
+
+def test_bwd_intra_gate_and_finish(world):
+    lv, fw, bw, f32, lay, o = world["lv"], world["fw"], world["bw"], world["f32"], world["lay"], world["opts"]
+    dq_v, dk_v, dgp, dbeta = ops.bwd_intra(lay, lv["q"], lv["k"], world["q_rstd"], world["k_rstd"], f32(fw["g_c"]),
+                                           world["be"], f32(bw["dAqk"]), f32(bw["dL"]), f32(bw["dq_p"]), f32(bw["dk_p"]),
+                                           f32(bw["dg_p"]), f32(bw["dbeta_w"]), world["scale"], 2, 4, lv["beta"], False, 1.0)
+    _err("dq_v", dq_v, bw["dq_v"]); _err("dk_v", dk_v, bw["dk_v"]); _err("dgp", dgp, bw["dgp"])
+    _err("dbeta", dbeta, bw["dbeta"].reshape(world["TT"], 4))
+    # gate backward (reverse cumsum folded in) against autograd of the oracle's gate
+    x = lv["g"].double().requires_grad_(True)
+    A = lv["A_log"].double().requires_grad_(True)
+    b = lv["dt_bias"].double().requires_grad_(True)
+    gd = orc.gate_log_decay(x, o["gate_mode"], A, b, -5.0)
+    rx, rA, rb = torch.autograd.grad((gd * bw["dg"]).sum(), [x, A, b])
+    dx, d_bias, d_alog = ops.gate_bwd(lay, lv["g"], f32(bw["dgp"]), o["gate_mode"], lv["A_log"], lv["dt_bias"], -5.0, 4,
+                                      True, True)
+    _err("dx", dx, rx, 2e-4); _err("ddt_bias", d_bias.view_as(rb), rb, 5e-4); _err("dA_log", d_alog, rA, 5e-4)
+    # GVA sum + L2-norm backward against autograd of the oracle's l2norm
+    qd = lv["q"].double().requires_grad_(True)
+    B, T = lv["q"].shape[:2]
+    up = bw["dq_v"].reshape(B, T, 2, 2, 128).sum(3)
+    (rq,) = torch.autograd.grad((orc.l2norm(qd) * up).sum(), [qd])
+    dq = ops.qk_grad_finish(f32(bw["dq_v"]), lv["q"], world["q_rstd"], 2, 4)
+    tol = 1e-5 if lv["q"].dtype == torch.float32 else 2.0 ** -8
+    _err("dq", dq.view_as(rq), rq, tol)
+
+
+def test_epilogue_backward(world):
+    lv, fw, f32 = world["lv"], world["fw"], world["f32"]
+    o = fw["o"].clone().requires_grad_(True)
+    w = lv["ep_w"].double().requires_grad_(True)
+    z = lv["ep_gate"].double().reshape(-1, 4, 128).requires_grad_(True)
+    dy = world["do"]
+    for act in ("silu", "sigmoid"):
+        y = orc.gated_rmsnorm(o, w, z, act)
+        ro, rw, rz = torch.autograd.grad((y * dy.double()).sum(), [o, w, z])
+        d_o, dgate, dw = ops.epilogue_bwd(dy.contiguous(), f32(fw["o"]), lv["ep_w"], lv["ep_gate"], act, 1e-6)
+        _err("do", d_o.view_as(ro), ro, 1e-5); _err("dw", dw, rw, 1e-5)
+        _err("dgate", dgate.reshape(rz.shape), rz, 1e-5 if dgate.dtype == torch.float32 else 2.0 ** -8)
