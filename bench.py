@@ -1,0 +1,392 @@
+#!/usr/bin/env python
+"""Benchmark of one KDA / GDN layer forward + backward through the public API.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload packed|1b|longdoc|gdn] [--impl reference]
+
+Default workload = the configuration the headline metric is quoted on: 8 rows x 8192 tokens of packed short documents
+(lognormal lengths, median 500, sigma 1.0, cut at row boundaries) per GPU, HK=16 / HV=32 / D=128, bf16 q/k/v, eda
+gate + sigmoid beta (x2) + in-kernel L2 + silu gated-RMSNorm epilogue, loss = o.sum().  Data is synthetic and seeded;
+no dataset is involved.  With N > 1 (launched by torchrun) every rank runs its own packed batch (weak scaling, no
+collective on the data path); ``--workload longdoc`` instead shards ONE document across the ranks with context
+parallelism (one NCCL all-gather of per-rank (state, transition) pairs per pass).
+
+One JSON line is printed by rank 0.  ``value`` is measured with inputs resident in HBM; ``e2e`` is the same metric
+with pinned host inputs copied in and the loss read back inside the timed region.  ``roofline`` describes the kernel
+that took the largest share of the timed region, timed with CUDA events on the launching stream.
+``--impl reference`` times the CPU restatement of the reference's torch oracle (tests/ref_kda.py of the reference) on
+the host cores on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HK, HV, D = 16, 32, 128
+
+
+# ----------------------------------------------------------------------------------------------------------
+# synthetic workloads
+# ----------------------------------------------------------------------------------------------------------
+def packed_cu(rows=8, row_len=8192, median=500.0, sigma=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    cu = [0]
+    for r in range(rows):
+        end = (r + 1) * row_len
+        while cu[-1] < end:
+            n = int(math.exp(math.log(median) + sigma * torch.randn((), generator=g).item()))
+            cu.append(min(cu[-1] + max(n, 1), end))
+    return cu
+
+
+def make_workload(name, rank, device, pin=False):
+    """Returns (host tensors dict, options dict, description)."""
+    g = torch.Generator().manual_seed(rank)
+    r = lambda *s: torch.randn(*s, generator=g)                               # noqa: E731
+    if name in ("packed", "1b"):
+        if name == "packed":
+            hk, hv, cu = HK, HV, packed_cu(seed=rank)
+            T = cu[-1]
+        else:
+            hk, hv, cu, T = 8, 16, [0, 3000, 5000, 8192], 8192
+        t = dict(q=r(1, T, hk, D).bfloat16(), k=r(1, T, hk, D).bfloat16(), v=r(1, T, hv, D).bfloat16(),
+                 g=r(1, T, hv, D), beta=r(1, T, hv), ep_gate=r(1, T, hv, D).bfloat16(),
+                 A_log=torch.zeros(hv), dt_bias=torch.zeros(hv, D), ep_w=torch.ones(D),
+                 cu=torch.tensor(cu, dtype=torch.int32))
+        opts = dict(gate_mode="eda", lower_bound=-5.0, beta_mode="sigmoid", beta_scale=2.0, l2=True, epi="silu")
+        desc = (f"packed short documents: {len(cu) - 1} docs in 8x8192 tokens, lognormal(median 500, sigma 1.0)"
+                if name == "packed" else "1B shape: T=8192, docs 3000/2000/3192")
+        dims = dict(tokens=T, HK=hk, HV=hv, docs=len(cu) - 1)
+    elif name == "longdoc":
+        T = 65536
+        t = dict(q=r(1, T, HK, D).bfloat16(), k=r(1, T, HK, D).bfloat16(), v=r(1, T, HV, D).bfloat16(),
+                 g=r(1, T, HV, D), beta=r(1, T, HV), A_log=r(HV) * 0.1, dt_bias=r(HV, D) * 0.1)
+        opts = dict(gate_mode="kimi", lower_bound=-5.0, beta_mode="sigmoid", beta_scale=1.0, l2=True, epi=None)
+        desc, dims = "one 65536-token document per GPU-shard, kimi gate", dict(tokens=T, HK=HK, HV=HV, docs=1)
+    elif name == "gdn":
+        B, T, H = 4, 16384, 16
+        A_log, x = r(H) * 0.1, r(B, T, H)
+        gdec = torch.clamp(-A_log.exp() * torch.nn.functional.softplus(x), min=-5.0)
+        t = dict(q=r(B, T, H, D).bfloat16(), k=r(B, T, H, D).bfloat16(), v=r(B, T, H, D).bfloat16(), g=gdec,
+                 beta=torch.sigmoid(r(B, T, H)), h0=r(B, H, D, D) * 0.02)
+        opts = dict(gate_mode="precomputed", beta_mode="precomputed", beta_scale=1.0, l2=False, epi=None, gdn=True)
+        desc, dims = "scalar gate, B=4 x T=16384, H=16, [V,K] initial state", dict(tokens=B * T, HK=H, HV=H, docs=B)
+    else:
+        raise SystemExit(f"unknown workload {name}")
+    if pin:
+        t = {n: x.pin_memory() for n, x in t.items()}
+    return t, opts, desc, dims
+
+
+GRAD_LEAVES = ("q", "k", "v", "g", "beta", "A_log", "dt_bias", "ep_w", "ep_gate", "h0")
+
+
+def layer_step(mk, dev, opts, cp=None):
+    """One forward + backward of the layer on device tensors ``dev``; returns the loss tensor."""
+    lv = {n: (x.detach().requires_grad_(True) if n in GRAD_LEAVES and x.is_floating_point() else x) for n, x in dev.items()}
+    if opts.get("gdn"):
+        o, ht = mk.chunk_gated_delta_rule(lv["q"], lv["k"], lv["v"], lv["g"], lv["beta"], initial_state=lv["h0"],
+                                          output_final_state=True, state_v_first=True)
+        loss = o.float().sum() + ht.sum()
+    else:
+        norm = None
+        if opts["epi"]:
+            norm = dict(weight=lv["ep_w"], gate=lv["ep_gate"], act=opts["epi"], eps=1e-6)
+        o, _ = mk.chunk_kda(lv["q"], lv["k"], lv["v"], lv["g"], lv["beta"], cu_seqlens=lv.get("cu"),
+                            gate_mode=opts["gate_mode"], A_log=lv.get("A_log"), dt_bias=lv.get("dt_bias"),
+                            lower_bound=opts["lower_bound"], beta_mode=opts["beta_mode"], beta_scale=opts["beta_scale"],
+                            use_qk_l2norm_in_kernel=opts["l2"], output_norm=norm, cp_context=cp)
+        loss = o.float().sum()
+    loss.backward()
+    return loss
+
+
+# ----------------------------------------------------------------------------------------------------------
+# roofline bookkeeping: algorithmic FLOPs per token per v-head of each contraction kernel (full tiles, no
+# precision-split or recompute multipliers, no triangular discount) and algorithmic bytes of the streaming kernels.
+# ----------------------------------------------------------------------------------------------------------
+C_, K_, V_ = 64, 128, 128
+F_CK, F_KV, F_CC = 2 * C_ * K_, 2 * K_ * V_, 2 * C_ * C_
+KERNEL_FLOPS = {                      # per token per v-head
+    "mkda_intra_fwd": 3 * F_CK,                       # Gamma, Q K^T, A (beta [k~ | v]) counted as one C x C x (K|V) product pair
+    "mkda_recur_fwd": 2 * F_KV,                       # nw S, kbar^T Vd
+    "mkda_out_fwd": F_KV + F_CK,                      # q~ S, Aqk Vd
+    "mkda_bwd_dh": F_CK + 3 * F_KV,                   # Aqk^T dO, kbar dS', q~^T dO, nw^T dVd
+    "mkda_bwd_wy": F_KV + 4 * F_CK + 2 * F_CC,        # k~ S, A W, dO Vd^T, A^T dVd, dVd W^T, two C^3 products
+    "mkda_bwd_sgrad": 3 * F_KV,                       # dO S^T, dX S^T, Vd dS'^T
+    "mkda_bwd_intra": 4 * F_CK,                       # row / column terms through Gamma and Q K^T
+}
+# DRAM traffic per token per v-head measured by ncu (profiles/), bytes; filled in as captures are taken.
+KERNEL_TRAFFIC = {}
+
+
+class LaunchRecorder:
+    """Wraps the C-ABI call so that every kernel launch is counted and bracketed by CUDA events on its stream."""
+
+    def __init__(self, lib_module):
+        self.lib, self.orig, self.events, self.count, self.timing = lib_module, lib_module.call, [], 0, False
+
+    def __enter__(self):
+        def call(name, params, stream):
+            self.count += 1
+            if not self.timing:
+                return self.orig(name, params, stream)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            self.orig(name, params, stream)
+            e1.record()
+            self.events.append((name, e0, e1))
+        self.lib.call = call
+        return self
+
+    def __exit__(self, *exc):
+        self.lib.call = self.orig
+
+    def totals(self):
+        out = {}
+        for name, e0, e1 in self.events:
+            ms, n = out.get(name, (0.0, 0))
+            out[name] = (ms + e0.elapsed_time(e1), n + 1)
+        return out
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.path = gpu_index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.idx), "-lms", "100"], stdout=open(self.path, "w"),
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        os.unlink(self.path)
+        if not sm:
+            return None
+        busy = sorted(sm)[len(sm) // 2:]
+        return dict(sm_mhz=statistics.median(busy), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm=p["hbm_gbs"], tensor=p["bf16_tflops_sustained"], source="measured")
+    return dict(hbm=6650.0, tensor=1400.0, source="fallback")
+
+
+def cpu_baseline(seconds=12.0):
+    """The CPU restatement of the reference's torch oracle on benchmark config 1 (T=256, HK2/HV4, fp32, precomputed
+    gate), forward + backward, all host threads."""
+    from oracle import kda_oracle as orc
+    torch.manual_seed(0)
+    B, T, hk, hv = 1, 256, 2, 4
+    q = torch.nn.functional.normalize(torch.randn(B, T, hk, D), dim=-1)
+    k = torch.nn.functional.normalize(torch.randn(B, T, hk, D), dim=-1)
+    v, g, beta = torch.randn(B, T, hv, D), -0.5 * torch.rand(B, T, hv, D), torch.sigmoid(torch.randn(B, T, hv))
+    times = []
+    t_end = time.time() + seconds
+    while len(times) < 2 or (time.time() < t_end and len(times) < 20):
+        lv = [x.clone().requires_grad_(True) for x in (q, k, v, g, beta)]
+        t0 = time.time()
+        o, _ = orc.recurrent_delta_rule(*lv, output_final_state=True)
+        o.sum().backward()
+        times.append(time.time() - t0)
+    med = statistics.median(times[1:])
+    return dict(value=T / med / 1e6, unit="Mtok/s", cores=torch.get_num_threads(), kind="port",
+                sample=f"config 1 (B=1,T=256,HK=2,HV=4,D=128 fp32, token-by-token fp64 recurrence + autograd), median of {len(times) - 1} runs after 1 warm-up")
+
+
+def reference_arm(args, world, rank):
+    """CPU arm: the oracle port on a bounded sample (the first 128 tokens of each of the first documents) of the
+    default workload's shape (HK16/HV32/D128, eda gate, sigmoid beta x2, L2, silu epilogue)."""
+    if rank != 0:
+        return
+    from oracle import kda_oracle as orc
+    torch.set_num_threads(os.cpu_count() or 1)
+    t, opts, desc, dims = make_workload(args.workload if args.workload != "longdoc" else "packed", 0, "cpu")
+    T = 128
+    cut = {n: (x[:, :T].contiguous() if x.dim() >= 3 else x) for n, x in t.items()}
+
+    def step():
+        lv = {n: (x.float().requires_grad_(True) if x.is_floating_point() else x) for n, x in cut.items()}
+        if opts.get("gdn"):
+            o, _ = orc.recurrent_delta_rule(lv["q"], lv["k"], lv["v"], lv["g"], lv["beta"], initial_state=lv["h0"],
+                                            state_v_first=True, output_final_state=True)
+        else:
+            norm = dict(weight=lv["ep_w"], gate=lv["ep_gate"], act=opts["epi"]) if opts["epi"] else None
+            o, _ = orc.recurrent_delta_rule(lv["q"], lv["k"], lv["v"], lv["g"], lv["beta"], gate_mode=opts["gate_mode"],
+                                            A_log=lv.get("A_log"), dt_bias=lv.get("dt_bias"), lower_bound=-5.0,
+                                            beta_mode=opts["beta_mode"], beta_scale=opts["beta_scale"],
+                                            use_qk_l2norm_in_kernel=opts["l2"], output_norm=norm)
+        o.sum().backward()
+
+    ntok = cut["q"].shape[0] * T
+    for _ in range(min(args.warmup, 1)):
+        step()
+    t0 = time.time()
+    for _ in range(args.steps):
+        step()
+    dt = (time.time() - t0) / args.steps
+    val = ntok / dt / 1e6
+    sample = f"first {T} tokens of every batch row of the workload, full head count, token-by-token fp64 recurrence + autograd"
+    print(json.dumps({
+        "impl": "reference", "metric": "KDA fwd+bwd Mtok/s per layer", "value": val, "unit": "Mtok/s",
+        "n_gpus": world, "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": args.workload, **dims, "D": D, "sample_tokens": ntok},
+        "cpu_baseline": dict(value=val, unit="Mtok/s", cores=torch.get_num_threads(), kind="port", sample=sample),
+        "e2e": {"value": val, "unit": "Mtok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="packed")
+    ap.add_argument("--impl", default="mogankda_b200")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        args.steps = min(args.steps, 5)
+        return reference_arm(args, world, rank)
+    args.warmup = max(args.warmup, 3)
+
+    import torch.distributed as dist
+    import mogankda_b200 as mk
+    from mogankda_b200 import _lib
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    cp = None
+    if args.workload == "longdoc" and world > 1:
+        from mogankda_b200.cp import ContextParallel
+        cp = ContextParallel(dist.group.WORLD)
+
+    host, opts, desc, dims = make_workload(args.workload, rank, device, pin=True)
+    dev = {n: x.to(device) for n, x in host.items()}
+    tokens_per_step = dims["tokens"]
+    h2d = sum(x.numel() * x.element_size() for x in host.values())
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with LaunchRecorder(_lib) as rec:
+        for _ in range(args.warmup):
+            layer_step(mk, dev, opts, cp)
+        barrier()
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        rec.count, rec.timing = 0, True
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            layer_step(mk, dev, opts, cp)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        launches = rec.count
+        rec.timing = False
+        per_kernel = rec.totals()
+        # end to end: pinned host inputs in, loss out, every step
+        for _ in range(2):
+            layer_step(mk, {n: x.to(device, non_blocking=True) for n, x in host.items()}, opts, cp).item()
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(args.steps):
+            layer_step(mk, {n: x.to(device, non_blocking=True) for n, x in host.items()}, opts, cp).item()
+        f1.record()
+        barrier()
+        ms_e2e = f0.elapsed_time(f1)
+        clocks = sampler.stop() if rank == 0 else None
+
+    tms = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = tms.tolist()
+    if rank == 0:
+        peaks = measured_peaks()
+        total_tokens = tokens_per_step * world * args.steps
+        value = total_tokens / (ms * 1e-3) / 1e6
+        top = max(per_kernel.items(), key=lambda kv: kv[1][0])
+        name, (kms, n) = top
+        per_launch_s = kms / n * 1e-3
+        units = tokens_per_step * dims["HV"]
+        if name in KERNEL_FLOPS:
+            ach = KERNEL_FLOPS[name] * units / per_launch_s / 1e12
+            roof = dict(kernel=name, bound="tensor", achieved=ach, peak=peaks["tensor"], unit="TFLOP/s",
+                        frac=ach / peaks["tensor"], traffic=KERNEL_TRAFFIC.get(name), peak_source=peaks["source"],
+                        share_of_step=kms / ms, launch_ms=per_launch_s * 1e3)
+        else:
+            roof = dict(kernel=name, bound="hbm", achieved=None, peak=peaks["hbm"], unit="GB/s", frac=None,
+                        traffic=None, peak_source=peaks["source"], share_of_step=kms / ms, launch_ms=per_launch_s * 1e3)
+        line = {
+            "metric": "KDA fwd+bwd Mtok/s per layer", "value": value, "unit": "Mtok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong" if cp is not None else "weak", "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {desc}", **dims, "D": D,
+                       "parallelism": ("cp%d" % world) if cp is not None else ("dp%d" % world),
+                       "l2": "per-step working set (> 10 GB of inputs and intermediates) exceeds the 126 MB L2"},
+            "e2e": {"value": total_tokens / (ms_e2e * 1e-3) / 1e6, "unit": "Mtok/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": 4},
+            "gpu_launches": launches, "roofline": roof, "clocks": clocks,
+            "kernels_ms_per_step": {k: round(v[0] / args.steps, 4) for k, v in sorted(per_kernel.items(), key=lambda kv: -kv[1][0])},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
