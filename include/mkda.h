@@ -247,6 +247,17 @@ typedef struct {
 } MkdaCombine;
 int mkda_state_combine(const MkdaCombine* p, void* stream);
 
+/* Self-test of the tensor-core path: D[128,N] = A[128,K] B[N,K]^T (fp32 in, bf16 hi/lo split, fp32 out); N, K in
+ * {64, 128}.  No counterpart in the reference; used by the tests to validate the tcgen05 plumbing in isolation. */
+typedef struct {
+    const float* A; const float* B; float* D; int N; int K;
+    int mode;      /* bit 0: stage B MN-major, bit 1: stage A MN-major (exercises both operand views) */
+} MkdaSelfTest;
+int mkda_selftest_umma(const MkdaSelfTest* p, void* stream);
+
+/* 0 if no bounded wait inside a tensor-core kernel has ever timed out on the current device, else 1 (synchronises). */
+int mkda_device_status(void);
+
 const char* mkda_last_error(void);
 int mkda_abi_version(void);
 /* sizeof() of every parameter struct, in declaration order, so bindings can verify their mirror of this header. */

@@ -198,7 +198,8 @@ def chunk_delta_rule(q, k, v, g, beta, *, scale=None, initial_state=None, output
                beta_mode=beta_mode, beta_scale=float(beta_scale), l2=use_qk_l2norm_in_kernel, has_ep=ep is not None,
                ep_act=None if ep is None else ep.get("act", "silu"),
                ep_eps=None if ep is None else ep.get("eps", 1e-6),
-               seg_chunks=AUTO_SEGMENT_CHUNKS if (cp_context is not None or _needs_segments(B, T, cu_seqlens, auto_cp)) else 0,
+               seg_chunks=AUTO_SEGMENT_CHUNKS if (cp_context is not None or
+                                                  _needs_segments(B, T, v.shape[2], cu_seqlens, auto_cp)) else 0,
                cp_context=cp_context)
     ep_gate = None if ep is None else ep["gate"].contiguous()
     ep_w = None if ep is None else ep.get("weight")
@@ -206,11 +207,17 @@ def chunk_delta_rule(q, k, v, g, beta, *, scale=None, initial_state=None, output
                                     beta.contiguous(), A_log, dt_bias, initial_state, ep_w, ep_gate, cfg)
 
 
-def _needs_segments(B, T, cu_seqlens, auto_cp):
-    """Cut long sequences when the uncut layout could not fill the GPU: decided from shapes only (no device read)."""
-    if not auto_cp:
+SERIAL_CTAS_WANTED = 2 * 148          # serial CTAs (2 per sequence and v-head) needed to fill a B200 twice over
+
+
+def _needs_segments(B, T, HV, cu_seqlens, auto_cp):
+    """Cut long sequences when the uncut layout cannot fill the GPU.  Decided from shapes only (no device read): the
+    serial kernels run 2 CTAs per (sequence, v-head), so a batch with many sequences or heads is left alone.  The role
+    of the reference's intra-card CP decision (mogan_kda/ops/gated_delta_rule/chunk/cp/context.py:252-283)."""
+    if not auto_cp or T <= AUTO_SEGMENT_CHUNKS * CHUNK_SIZE:
         return False
-    return T > AUTO_SEGMENT_CHUNKS * CHUNK_SIZE
+    n_seq = B if cu_seqlens is None else cu_seqlens.numel() - 1
+    return 2 * n_seq * HV < SERIAL_CTAS_WANTED
 
 
 def chunk_kda(q, k, v, g, beta, **kwargs):

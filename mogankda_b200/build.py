@@ -20,6 +20,8 @@ SOURCES = {
     "recur.cu": ("MKDA_PREC_STATE", "MKDA_PREC_OUT", "MKDA_PREC_DH"),
     "bwd_post.cu": ("MKDA_PREC_WY", "MKDA_PREC_SGRAD"),
     "intra_bwd.cu": ("MKDA_PREC_INTRA_BWD",),
+    "selftest.cu": (),
+    "tc_chunk.cu": (),
 }
 PREC_MACROS = ("MKDA_PREC_INTRA", "MKDA_PREC_STATE", "MKDA_PREC_OUT", "MKDA_PREC_DH", "MKDA_PREC_WY", "MKDA_PREC_SGRAD",
                "MKDA_PREC_INTRA_BWD")

@@ -1,5 +1,6 @@
 // Error reporting and ABI self-description.
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "../../include/mkda.h"
@@ -23,6 +24,11 @@ int check_launch(const char* what) {
     return MKDA_OK;
 }
 
+bool legacy_kernels() {
+    static const bool v = [] { const char* e = getenv("MKDA_LEGACY"); return e && e[0] == '1'; }();
+    return v;
+}
+
 int ensure_smem(const void* func, int bytes, const char* what) {
     cudaError_t e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e != cudaSuccess) {
@@ -35,6 +41,16 @@ int ensure_smem(const void* func, int bytes, const char* what) {
 
 }  // namespace mkda
 
+namespace mkda {
+int selftest_status(unsigned int* out);
+}
+extern "C" int mkda_device_status(void) {
+    unsigned int f = 0, any = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (mkda::selftest_status(&f) == 0) any |= f;
+    if (mkda::tc_chunk_status(&f) == 0) any |= f;
+    return (int)any;
+}
 extern "C" const char* mkda_last_error(void) { return mkda::g_err; }
 extern "C" int mkda_abi_version(void) { return 1; }
 extern "C" int mkda_struct_sizes(int* out, int n) {
@@ -42,7 +58,7 @@ extern "C" int mkda_struct_sizes(int* out, int n) {
         (int)sizeof(MkdaLayout),   (int)sizeof(MkdaGateFwd),  (int)sizeof(MkdaGateBwd),     (int)sizeof(MkdaReduce),
         (int)sizeof(MkdaL2Norm),   (int)sizeof(MkdaIntraFwd), (int)sizeof(MkdaRecurFwd),    (int)sizeof(MkdaOutFwd),
         (int)sizeof(MkdaEpilogueBwd), (int)sizeof(MkdaBwdDh), (int)sizeof(MkdaBwdWy),       (int)sizeof(MkdaBwdSgrad),
-        (int)sizeof(MkdaBwdIntra), (int)sizeof(MkdaQkGrad),   (int)sizeof(MkdaCombine)};
+        (int)sizeof(MkdaBwdIntra), (int)sizeof(MkdaQkGrad),   (int)sizeof(MkdaCombine), (int)sizeof(MkdaSelfTest)};
     const int cnt = (int)(sizeof(sizes) / sizeof(sizes[0]));
     for (int i = 0; i < n && i < cnt; ++i) out[i] = sizes[i];
     return cnt;

@@ -2,9 +2,15 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include "../../include/mkda.h"
+
 namespace mkda {
 int set_error(int code, const char* msg);
 int check_launch(const char* what);
 // Raises the dynamic shared memory limit of `func` once per process; returns 0 or an error code.
 int ensure_smem(const void* func, int bytes, const char* what);
+// Development switch: MKDA_LEGACY=1 selects the warp-level mma.sync kernels instead of the tcgen05 ones.
+bool legacy_kernels();
+int launch_out_fwd_tc(const MkdaOutFwd* p, cudaStream_t stream);
+int tc_chunk_status(unsigned int* out);
 }  // namespace mkda

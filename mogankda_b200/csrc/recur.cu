@@ -460,6 +460,7 @@ extern "C" int mkda_out_fwd(const MkdaOutFwd* p, void* stream) {
     if (!p || !p->q || !p->g_c || !p->Aqk || !p->Vd || !p->h || !p->out) return set_error(MKDA_ERR_ARG, "out_fwd: null argument");
     if (p->has_norm && !p->gate) return set_error(MKDA_ERR_ARG, "out_fwd: the gated norm needs a gate tensor");
     if (p->L.NC == 0) return MKDA_OK;
+    if (!legacy_kernels()) return launch_out_fwd_tc(p, (cudaStream_t)stream);
     auto kern = out_fwd_kernel<MKDA_PREC_OUT>;
     if (int e = ensure_smem((const void*)kern, OUT_SMEM, "out_fwd")) return e;
     kern<<<dim3(p->L.NC, p->L.HV), 256, OUT_SMEM, (cudaStream_t)stream>>>(*p);

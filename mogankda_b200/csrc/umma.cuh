@@ -1,0 +1,226 @@
+// Blackwell tensor-core plumbing used by the *_tc kernels: tcgen05.mma with shared-memory operands in the K-major
+// 128-byte-swizzle canonical layout, fp32 accumulators in tensor memory (TMEM), completion through an mbarrier.
+//
+// Operand precision: every fp32 operand value a is split into two bf16 tiles, hi = bf16(a) and lo = bf16(a - hi), and a
+// product is issued as three kind::f16 MMAs (lo*hi + hi*lo + hi*hi) accumulating in fp32.  That carries ~16 mantissa
+// bits per operand (relative error ~2^-16 per product) for 1.5x the tensor time of one TF32 MMA, in the same
+// shared-memory footprint as an fp32 tile.
+//
+// Every wait is bounded: after WAIT_LIMIT polls the waiter records a timeout in a global status word and goes on
+// (results are then garbage but the kernel terminates and frees its TMEM).
+#pragma once
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace mkda {
+namespace umma {
+
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+static __device__ unsigned int g_timeout_flag;      // one per translation unit, read back by mkda_device_status()
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// ---- operand tiles -------------------------------------------------------------------------------------------
+// A tile holds R rows (multiple of 8) by KT bf16 columns (multiple of 64), K-major.  It is stored as KT/64 column
+// blocks of R x 64 (each row 128 bytes, 8-row groups 1024 bytes apart, 16-byte chunks XOR-swizzled with the row
+// index).  The tile base must be 1024-byte aligned.
+__device__ __forceinline__ uint32_t tile_chunk_offset(int R, int r, int k8) {   // k8 = index of the 8-element chunk
+    const int blk = k8 >> 3, c = k8 & 7;
+    return (uint32_t)(blk * R * 128 + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
+}
+__host__ __device__ constexpr int tile_bytes(int R, int KT) { return R * KT * 2; }
+
+// split 8 fp32 values into bf16 hi / lo chunks and store them at (row r, chunk k8) of the two tiles
+__device__ __forceinline__ void store_split8(uint8_t* hi, uint8_t* lo, int R, int r, int k8, const float (&v)[8]) {
+    uint32_t h[4], l[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat16 a = __float2bfloat16_rn(v[2 * i]), b = __float2bfloat16_rn(v[2 * i + 1]);
+        const __nv_bfloat16 c = __float2bfloat16_rn(v[2 * i] - __bfloat162float(a));
+        const __nv_bfloat16 d = __float2bfloat16_rn(v[2 * i + 1] - __bfloat162float(b));
+        h[i] = (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+        l[i] = (uint32_t)__bfloat16_as_ushort(c) | ((uint32_t)__bfloat16_as_ushort(d) << 16);
+    }
+    const uint32_t off = tile_chunk_offset(R, r, k8);
+    *reinterpret_cast<uint4*>(hi + off) = make_uint4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<uint4*>(lo + off) = make_uint4(l[0], l[1], l[2], l[3]);
+}
+
+// ---- descriptors ---------------------------------------------------------------------------------------------
+// shared-memory matrix descriptor: K-major, SWIZZLE_128B, 8-row groups 1024 B apart (SBO = 64 x 16 B), version 1
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo16 = 1u) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo16 & 0x3FFFu) << 16) | ((uint64_t)64 << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M x N tile
+__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn = 0, int b_mn = 0) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// An operand as the MMA sees it.  The same physical tile (rows x 64-column blocks, see tile_chunk_offset) can be read
+//   K-major : operand(mn = tile row, k = tile column);  `blk` = bytes between 64-column blocks (= rows * 128)
+//   MN-major: operand(mn = tile column, k = tile row);  `blk` = bytes between 64-column blocks, which the hardware
+//             takes as the distance between 64-element groups of the MN axis (leading byte offset)
+// `hi` / `lo` are shared-memory byte addresses of the first row / column the operand uses; lo = 0 means the values
+// are exact in bf16 (no second tile).
+struct Opnd {
+    uint32_t hi, lo, blk;
+    int mn;
+};
+__device__ __forceinline__ Opnd opnd_k(const void* hi, const void* lo, int rows, int first_row = 0) {
+    Opnd o;
+    o.hi = smem_u32(hi) + first_row * 128;
+    o.lo = lo ? smem_u32(lo) + first_row * 128 : 0u;
+    o.blk = rows * 128;
+    o.mn = 0;
+    return o;
+}
+// MN-major view starting at tile row `first_row` (k origin, multiple of 8) and tile column `first_col` (multiple of 64)
+__device__ __forceinline__ Opnd opnd_mn(const void* hi, const void* lo, int rows, int first_row = 0, int first_col = 0) {
+    Opnd o;
+    const uint32_t off = (first_col >> 6) * rows * 128 + first_row * 128;
+    o.hi = smem_u32(hi) + off;
+    o.lo = lo ? smem_u32(lo) + off : 0u;
+    o.blk = rows * 128;
+    o.mn = 1;
+    return o;
+}
+__device__ __forceinline__ uint64_t opnd_desc(const Opnd& o, uint32_t base, int ks) {
+    if (o.mn) return make_desc(base + ks * 2048, o.blk >> 4);
+    return make_desc(base + (ks >> 2) * o.blk + (ks & 3) * 32);
+}
+
+// D[M x N] (+)= A[M x 16] * B[N x 16]^T, one elected thread
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// D (+)= A * B^T over KT columns with the three-product split.  a_hi/a_lo/b_hi/b_lo are shared-memory byte addresses
+// of tiles with RA / RB rows.  `first` = 0 overwrites D with the first product.
+__device__ __forceinline__ void gemm_split(uint32_t tmem_d, uint32_t a_hi, uint32_t a_lo, int RA, uint32_t b_hi,
+                                           uint32_t b_lo, int RB, int KT, uint32_t idesc, uint32_t accumulate) {
+    for (int ks = 0; ks < KT / 16; ++ks) {
+        const uint32_t ao = (uint32_t)((ks >> 2) * RA * 128 + (ks & 3) * 32);
+        const uint32_t bo = (uint32_t)((ks >> 2) * RB * 128 + (ks & 3) * 32);
+        const uint64_t dah = make_desc(a_hi + ao), dal = make_desc(a_lo + ao);
+        const uint64_t dbh = make_desc(b_hi + bo), dbl = make_desc(b_lo + bo);
+        mma_bf16(tmem_d, dal, dbh, idesc, accumulate);
+        mma_bf16(tmem_d, dah, dbl, idesc, 1u);
+        mma_bf16(tmem_d, dah, dbh, idesc, 1u);
+        accumulate = 1u;
+    }
+}
+// same, when the B operand is exactly representable in bf16 (no lo tile): two products
+__device__ __forceinline__ void gemm_split_a(uint32_t tmem_d, uint32_t a_hi, uint32_t a_lo, int RA, uint32_t b_hi, int RB,
+                                             int KT, uint32_t idesc, uint32_t accumulate) {
+    for (int ks = 0; ks < KT / 16; ++ks) {
+        const uint32_t ao = (uint32_t)((ks >> 2) * RA * 128 + (ks & 3) * 32);
+        const uint32_t bo = (uint32_t)((ks >> 2) * RB * 128 + (ks & 3) * 32);
+        const uint64_t dbh = make_desc(b_hi + bo);
+        mma_bf16(tmem_d, make_desc(a_lo + ao), dbh, idesc, accumulate);
+        mma_bf16(tmem_d, make_desc(a_hi + ao), dbh, idesc, 1u);
+        accumulate = 1u;
+    }
+}
+
+// D[M x N] (+)= A B^T over KT (multiple of 16) with the hi/lo split; products whose lo tile is absent are skipped.
+__device__ __forceinline__ void gemm(uint32_t tmem_d, const Opnd& a, const Opnd& b, int M, int N, int KT, uint32_t accumulate) {
+    const uint32_t idesc = idesc_bf16(M, N, a.mn, b.mn);
+    for (int ks = 0; ks < KT / 16; ++ks) {
+        const uint64_t dah = opnd_desc(a, a.hi, ks), dbh = opnd_desc(b, b.hi, ks);
+        if (a.lo) { mma_bf16(tmem_d, opnd_desc(a, a.lo, ks), dbh, idesc, accumulate); accumulate = 1u; }
+        if (b.lo) { mma_bf16(tmem_d, dah, opnd_desc(b, b.lo, ks), idesc, accumulate); accumulate = 1u; }
+        mma_bf16(tmem_d, dah, dbh, idesc, accumulate);
+        accumulate = 1u;
+    }
+}
+
+// ---- synchronisation -----------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+// make generic-proxy shared-memory writes visible to the tensor core (async proxy)
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// arrive on `bar` once every tcgen05 operation issued so far by this thread has completed
+__device__ __forceinline__ void commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    atomicExch(&g_timeout_flag, 1u);
+    return false;
+}
+
+// ---- tensor memory -------------------------------------------------------------------------------------------
+// one full warp allocates `ncols` (power of two >= 32) columns and publishes the base address through `slot`
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(slot)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// 32 lanes x 32 columns: thread t of the warp receives columns [col, col+32) of TMEM lane (quadrant base + t)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        :: "r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+           "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+           "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+           "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+           "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+           "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+           "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+           "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+// TMEM address of (lane quadrant of this warp, column)
+__device__ __forceinline__ uint32_t tmem_addr(uint32_t base, int warp, int col) {
+    return base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)col;
+}
+
+}  // namespace umma
+}  // namespace mkda
