@@ -309,6 +309,7 @@ extern "C" int mkda_bwd_wy(const MkdaBwdWy* p, void* stream) {
         !p->dbeta_w || !p->dAqk || !p->dL)
         return set_error(MKDA_ERR_ARG, "bwd_wy: null argument");
     if (p->L.NC == 0) return MKDA_OK;
+    if (!legacy_kernels()) return launch_bwd_wy_tc(p, (cudaStream_t)stream);
     auto kern = bwd_wy_kernel<MKDA_PREC_WY>;
     if (int e = ensure_smem((const void*)kern, WY_SMEM, "bwd_wy")) return e;
     kern<<<dim3(p->L.NC, p->L.HV), 256, WY_SMEM, (cudaStream_t)stream>>>(*p);
@@ -319,6 +320,7 @@ extern "C" int mkda_bwd_sgrad(const MkdaBwdSgrad* p, void* stream) {
     if (!p || !p->q || !p->k || !p->g_c || !p->d_o || !p->dX || !p->Vd || !p->h || !p->dh || !p->dq_p || !p->dk_p || !p->dg_p)
         return set_error(MKDA_ERR_ARG, "bwd_sgrad: null argument");
     if (p->L.NC == 0) return MKDA_OK;
+    if (!legacy_kernels()) return launch_bwd_sgrad_tc(p, (cudaStream_t)stream);
     auto kern = bwd_sgrad_kernel<MKDA_PREC_SGRAD>;
     if (int e = ensure_smem((const void*)kern, SG_SMEM, "bwd_sgrad")) return e;
     kern<<<dim3(p->L.NC, p->L.HV), 256, SG_SMEM, (cudaStream_t)stream>>>(*p);

@@ -12,5 +12,7 @@ int ensure_smem(const void* func, int bytes, const char* what);
 // Development switch: MKDA_LEGACY=1 selects the warp-level mma.sync kernels instead of the tcgen05 ones.
 bool legacy_kernels();
 int launch_out_fwd_tc(const MkdaOutFwd* p, cudaStream_t stream);
+int launch_bwd_sgrad_tc(const MkdaBwdSgrad* p, cudaStream_t stream);
+int launch_bwd_wy_tc(const MkdaBwdWy* p, cudaStream_t stream);
 int tc_chunk_status(unsigned int* out);
 }  // namespace mkda

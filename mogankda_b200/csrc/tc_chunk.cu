@@ -6,6 +6,8 @@
 #include "host.h"
 #include "umma.cuh"
 
+#include <type_traits>
+
 namespace mkda {
 
 using umma::smem_u32;
@@ -50,6 +52,34 @@ __device__ __forceinline__ void zero8(float (&v)[8]) {
     for (int e = 0; e < 8; ++e) v[e] = 0.f;
 }
 
+// Batched staging: a thread first issues the global loads of all CNT of its chunks (independent, so they are all in
+// flight together), then splits and stores them.  Chunk n of thread t is linear index t + n * NTHR; ALONG_K maps the
+// index to (row = i / (KT/8), chunk = i % (KT/8)), otherwise to (chunk = i / R, row = i % R).
+template <int CNT, int NTHR, bool ALONG_K, class F>
+__device__ __forceinline__ void load_chunks(float (&v)[CNT][8], int R, int KT, F f) {
+    const int nk8 = KT >> 3;
+#pragma unroll
+    for (int n = 0; n < CNT; ++n) {
+        const int i = threadIdx.x + n * NTHR;
+        const int r = ALONG_K ? i / nk8 : i % R, k8 = ALONG_K ? i % nk8 : i / R;
+        f(r, k8, v[n]);
+    }
+}
+template <int CNT, int NTHR, bool ALONG_K>
+__device__ __forceinline__ void store_chunks(uint8_t* hi, uint8_t* lo, const float (&v)[CNT][8], int R, int KT) {
+    const int nk8 = KT >> 3;
+#pragma unroll
+    for (int n = 0; n < CNT; ++n) {
+        const int i = threadIdx.x + n * NTHR;
+        const int r = ALONG_K ? i / nk8 : i % R, k8 = ALONG_K ? i % nk8 : i / R;
+        store_split8(hi, lo, R, r, k8, v[n]);
+    }
+}
+__device__ __forceinline__ void scale8(float (&v)[8], float m) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] *= m;
+}
+
 struct TcShared {
     uint64_t bar;
     uint32_t tmem;
@@ -82,6 +112,7 @@ __device__ __forceinline__ void tc_end(TcShared* sh, uint32_t tmem, uint32_t tme
 constexpr int OUT_TC_SMEM = 2 * tile_bytes(128, 128) + 2 * tile_bytes(64, 128) + 2 * tile_bytes(128, 64) + 2 * tile_bytes(64, 64) + 1024;
 constexpr int OLD = 132;   // leading dimension of the fp32 [tok][v] staging tile
 
+template <int QDT, int GDT>
 __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ TcShared sh;
@@ -111,7 +142,7 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
     stage_along_k<512>(b1h, b1l, 64, 128, [&](int r, int k8, float (&v)[8]) {
         if (r >= len) { zero8(v); return; }
         const size_t th = (size_t)(start + r) * HV + h, tk = (size_t)(start + r) * HK + hk;
-        load8(p.q, p.q_dtype, tk * 128 + k8 * 8, v);
+        load8(p.q, QDT, tk * 128 + k8 * 8, v);
         float g[8];
         load8(p.g_c, MKDA_F32, th * 128 + k8 * 8, g);
         const float m = p.scale * (p.q_rstd ? p.q_rstd[tk] : 1.f);
@@ -159,7 +190,7 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
 #pragma unroll
             for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
             const float rs = 1.f / sqrtf(ss * (1.f / 128.f) + p.eps);
-            const float4 z = ld4(p.gate, p.gate_dtype, off);
+            const float4 z = ld4(p.gate, GDT, off);
             const float zz[4] = {z.x, z.y, z.z, z.w};
             float a[4];
 #pragma unroll
@@ -178,10 +209,403 @@ int tc_chunk_status(unsigned int* out) {
     return cudaMemcpyFromSymbol(out, umma::g_timeout_flag, sizeof(unsigned int)) == cudaSuccess ? 0 : -1;
 }
 
-int launch_out_fwd_tc(const MkdaOutFwd* p, cudaStream_t stream) {
-    if (int e = ensure_smem((const void*)out_fwd_tc_kernel, OUT_TC_SMEM, "out_fwd")) return e;
-    out_fwd_tc_kernel<<<dim3(p->L.NC, p->L.HV), 512, OUT_TC_SMEM, stream>>>(*p);
+template <int QDT, int GDT>
+static int launch_out_fwd_tc_t(const MkdaOutFwd* p, cudaStream_t stream) {
+    auto kern = out_fwd_tc_kernel<QDT, GDT>;
+    if (int e = ensure_smem((const void*)kern, OUT_TC_SMEM, "out_fwd")) return e;
+    kern<<<dim3(p->L.NC, p->L.HV), 512, OUT_TC_SMEM, stream>>>(*p);
     return check_launch("out_fwd");
+}
+// dispatch on runtime dtypes to kernels specialised at compile time (keeps every load loop free of branches)
+#define MKDA_DISPATCH2(FN, A, B, ...)                                                                        \
+    switch ((A) * 3 + (B)) {                                                                                 \
+        case 0: return FN<0, 0>(__VA_ARGS__); case 1: return FN<0, 1>(__VA_ARGS__); case 2: return FN<0, 2>(__VA_ARGS__); \
+        case 3: return FN<1, 0>(__VA_ARGS__); case 4: return FN<1, 1>(__VA_ARGS__); case 5: return FN<1, 2>(__VA_ARGS__); \
+        case 6: return FN<2, 0>(__VA_ARGS__); case 7: return FN<2, 1>(__VA_ARGS__); case 8: return FN<2, 2>(__VA_ARGS__); \
+        default: return set_error(MKDA_ERR_ARG, "unsupported dtype");                                        \
+    }
+int launch_out_fwd_tc(const MkdaOutFwd* p, cudaStream_t stream) {
+    MKDA_DISPATCH2(launch_out_fwd_tc_t, p->q_dtype, p->has_norm ? p->gate_dtype : 0, p, stream)
+}
+
+}  // namespace mkda
+
+namespace mkda {
+
+// ---------------------------------------------------------------------------------------------------------
+// bwd_sgrad on the tensor cores.  With the K index on the MMA M axis:
+//   Dq[kidx x tok] = S dO^T      Dk[kidx x tok] = S dX^T      Db[kidx x tok] = dS' Vd^T      dgl = rowsum_v(S * dS')
+// followed by the row-local epilogue (one thread per K index walks its tokens, all global accesses coalesced over K).
+// ---------------------------------------------------------------------------------------------------------
+constexpr int SG_TC_SMEM = 4 * tile_bytes(128, 128) + 4 * tile_bytes(64, 128) + 1024;
+
+template <int QKDT, int DODT>
+__global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ TcShared sh;
+    __shared__ uint64_t bar2;
+    __shared__ float sDgl[DK];
+    __shared__ float sCol[4][DK];
+    uint8_t* base = tc_begin(smem_raw, &sh, 256);
+    uint8_t* sSh = base;
+    uint8_t* sSl = sSh + tile_bytes(128, 128);
+    uint8_t* sDh = sSl + tile_bytes(128, 128);
+    uint8_t* sDl = sDh + tile_bytes(128, 128);
+    uint8_t* sOh = sDl + tile_bytes(128, 128);      // dO, later Vd
+    uint8_t* sOl = sOh + tile_bytes(64, 128);
+    uint8_t* sXh = sOl + tile_bytes(64, 128);
+    uint8_t* sXl = sXh + tile_bytes(64, 128);
+    if (threadIdx.x == 0) { umma::mbar_init(&bar2, 1); umma::fence_barrier_init(); }
+
+    const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV, HK = p.L.HK;
+    const int hk = h / (HV / HK);
+    const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const size_t sbase = ((size_t)c * HV + h) * DK * DV;
+
+    // token-row loader: rows past the end are read from the last valid row and zeroed (keeps the loads branch-free)
+    auto rows = [&](const void* src, auto dt) {
+        return [=](int r, int k8, float (&v)[8]) {
+            const int rr = r < len ? r : len - 1;
+            load8(src, decltype(dt)::value, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, v);
+            if (r >= len) zero8(v);
+        };
+    };
+    using F32T = std::integral_constant<int, MKDA_F32>;
+    {
+        float vS[4][8], vO[2][8], vX[2][8];
+        load_chunks<4, 512, true>(vS, 128, 128, [&](int r, int k8, float (&v)[8]) { load8(p.h, MKDA_F32, sbase + (size_t)r * DV + k8 * 8, v); });
+        load_chunks<2, 512, true>(vO, 64, 128, rows(p.d_o, std::integral_constant<int, DODT>{}));
+        load_chunks<2, 512, true>(vX, 64, 128, rows(p.dX, F32T{}));
+        store_chunks<4, 512, true>(sSh, sSl, vS, 128, 128);
+        store_chunks<2, 512, true>(sOh, sOl, vO, 64, 128);
+        store_chunks<2, 512, true>(sXh, sXl, vX, 64, 128);
+    }
+    const uint32_t tmem = tc_operands_ready(&sh);
+    if (tid == 0) {
+        const umma::Opnd aS = umma::opnd_k(sSh, sSl, 128);
+        umma::gemm(tmem + 0, aS, umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
+        umma::gemm(tmem + 64, aS, umma::opnd_k(sXh, sXl, 64), 128, 64, 128, 0u);
+        umma::commit(&sh.bar);
+    }
+    {   // dS' tile + dgl (S is re-read from its operand tile: hi + lo carries 16 mantissa bits); Vd is fetched now and
+        // stored once the first two products no longer need the dO tile
+        float vD[4][8], vV[2][8];
+        load_chunks<4, 512, true>(vD, 128, 128, [&](int r, int k8, float (&v)[8]) { load8(p.dh, MKDA_F32, sbase + (size_t)r * DV + k8 * 8, v); });
+        load_chunks<2, 512, true>(vV, 64, 128, rows(p.Vd, F32T{}));
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
+            const uint32_t off = umma::tile_chunk_offset(128, r, k8);
+            const uint4 sh4 = *reinterpret_cast<const uint4*>(sSh + off), sl4 = *reinterpret_cast<const uint4*>(sSl + off);
+            const uint32_t hw[4] = {sh4.x, sh4.y, sh4.z, sh4.w}, lw[4] = {sl4.x, sl4.y, sl4.z, sl4.w};
+            float pr = 0.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float s0 = __uint_as_float(hw[e] << 16) + __uint_as_float(lw[e] << 16);
+                const float s1 = __uint_as_float(hw[e] & 0xffff0000u) + __uint_as_float(lw[e] & 0xffff0000u);
+                pr += s0 * vD[n][2 * e] + s1 * vD[n][2 * e + 1];
+            }
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) pr += __shfl_xor_sync(0xffffffffu, pr, o);
+            if ((lane & 15) == 0) sDgl[r] = pr;
+        }
+        store_chunks<4, 512, true>(sDh, sDl, vD, 128, 128);
+        umma::mbar_wait(&sh.bar, 0);          // S dO^T and S dX^T done: the dO tile can be replaced by Vd
+        umma::fence_after_sync();
+        store_chunks<2, 512, true>(sOh, sOl, vV, 64, 128);
+    }
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    if (tid == 0) {
+        umma::gemm(tmem + 128, umma::opnd_k(sDh, sDl, 128), umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
+        umma::commit(&bar2);
+    }
+    // epilogue inputs are fetched while the last product runs
+    const int kk = (warp & 3) * 32 + lane, t0 = (warp >> 2) * 16;
+    const float gL = p.g_c[((size_t)(start + len - 1) * HV + h) * 128 + kk];
+    float kv[16], gv[16], qv[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int t = t0 + j < len ? t0 + j : len - 1;
+        const size_t tk = (size_t)(start + t) * HK + hk;
+        kv[j] = ld1(p.k, QKDT, tk * 128 + kk) * (p.k_rstd ? p.k_rstd[tk] : 1.f);
+        qv[j] = ld1(p.q, QKDT, tk * 128 + kk) * (p.q_rstd ? p.q_rstd[tk] : 1.f);
+        gv[j] = p.g_c[((size_t)(start + t) * HV + h) * 128 + kk];
+    }
+    umma::mbar_wait(&bar2, 0);
+    umma::fence_after_sync();
+
+    // ---- epilogue: thread = K index kk, 16 tokens per warp group ---------------------------------------------------
+    float aq[16], ak[16], ab[16];
+    umma::tmem_ld16(umma::tmem_addr(tmem, warp, t0), aq);
+    umma::tmem_ld16(umma::tmem_addr(tmem, warp, 64 + t0), ak);
+    umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + t0), ab);
+    float cs = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+        if (t0 + j < len) cs += kv[j] * exp2f(gL - gv[j]) * ab[j];
+    sCol[warp >> 2][kk] = cs;
+    __syncthreads();
+    const float extra = ((sCol[0][kk] + sCol[1][kk]) + (sCol[2][kk] + sCol[3][kk])) + exp2f(gL) * sDgl[kk];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int t = t0 + j;
+        if (t >= len) continue;
+        const size_t off = ((size_t)(start + t) * HV + h) * 128 + kk;
+        const float up = exp2f(gv[j]), re = exp2f(gL - gv[j]);
+        const float dqt = p.scale * aq[j], dkt = -ak[j], dkb = ab[j];
+        float dg = qv[j] * up * dqt + kv[j] * up * dkt - kv[j] * re * dkb;
+        if (t == len - 1) dg += extra;
+        p.dq_p[off] = dqt * up;
+        p.dk_p[off] = dkt * up + dkb * re;
+        p.dg_p[off] = dg;
+    }
+    tc_end(&sh, tmem, 256);
+}
+
+template <int QKDT, int DODT>
+static int launch_bwd_sgrad_tc_t(const MkdaBwdSgrad* p, cudaStream_t stream) {
+    auto kern = bwd_sgrad_tc_kernel<QKDT, DODT>;
+    if (int e = ensure_smem((const void*)kern, SG_TC_SMEM, "bwd_sgrad")) return e;
+    kern<<<dim3(p->L.NC, p->L.HV), 512, SG_TC_SMEM, stream>>>(*p);
+    return check_launch("bwd_sgrad");
+}
+int launch_bwd_sgrad_tc(const MkdaBwdSgrad* p, cudaStream_t stream) {
+    MKDA_DISPATCH2(launch_bwd_sgrad_tc_t, p->qk_dtype, p->do_dtype, p, stream)
+}
+
+}  // namespace mkda
+
+namespace mkda {
+
+// reconstruct 8 fp32 values from the hi / lo tiles at (row r, chunk k8)
+__device__ __forceinline__ void load_tile8(const uint8_t* hi, const uint8_t* lo, int R, int r, int k8, float (&v)[8]) {
+    const uint32_t off = umma::tile_chunk_offset(R, r, k8);
+    const uint4 a = *reinterpret_cast<const uint4*>(hi + off), b = *reinterpret_cast<const uint4*>(lo + off);
+    const uint32_t hw[4] = {a.x, a.y, a.z, a.w}, lw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        v[2 * e] = __uint_as_float(hw[e] << 16) + __uint_as_float(lw[e] << 16);
+        v[2 * e + 1] = __uint_as_float(hw[e] & 0xffff0000u) + __uint_as_float(lw[e] & 0xffff0000u);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// bwd_wy on the tensor cores.  Six dependent products, each with a 128-wide axis on M (TMEM columns in brackets):
+//   G1 [0]    X^T[v x tok]  = V^T - S^T k~^T                       (A = S tile read MN-major)
+//   G2 [64]   Vd^T[v x i]   = X^T (A diag(beta))^T
+//   G4 [256]  dW^T[v x j]   = dVd^T A                              (both operands MN-major views of natural tiles)
+//   G3 [128]  [dO; dVd] [Vd; X]^T  -> rows 0..63 / cols 0..63 = dO Vd^T, rows 64..127 / cols 64..127 = dVd X^T
+//   G5 [320]  Y[a x j]      = (dVd X^T diag(beta)) A^T
+//   G6 [384]  Z[i x j]      = A^T Y          dL = -strictlower(Z)
+// dbeta_w[j] = sum_v dW[j][v] X[j][v] is evaluated as sum_i A[i][j] (dVd X^T)[i][j], which needs no extra product.
+// Shared-memory tiles are recycled as soon as the product reading them has completed.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int WY_TC_SMEM = 192 * 1024 + 1024;
+
+template <int KVDT, int DODT>
+__global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ TcShared sh;
+    __shared__ float sBeta[CH];
+    __shared__ float sRed[2][CH];
+    uint8_t* base = tc_begin(smem_raw, &sh, 512);
+    uint8_t* sSh = base;                      // S [kidx][v]; later [dO; dVd] [tok][v]
+    uint8_t* sSl = sSh + 32768;
+    uint8_t* sKh = sSl + 32768;               // k~ [tok][kidx]; later dA diag(beta) [a][b]
+    uint8_t* sKl = sKh + 16384;
+    uint8_t* sVh = sKl + 16384;               // Vd^T [v][i] | X^T [v][j] (hi), then the same pair (lo)
+    uint8_t* sXh = sVh + 16384;
+    uint8_t* sVl = sXh + 16384;
+    uint8_t* sXl = sVl + 16384;
+    uint8_t* sAh = sXl + 16384;               // A [i][j]
+    uint8_t* sAl = sAh + 8192;
+    uint8_t* sBh = sAl + 8192;                // A diag(beta) [i][j]; later Y [a][j]
+    uint8_t* sBl = sBh + 8192;
+
+    const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV, HK = p.L.HK;
+    const int hk = h / (HV / HK);
+    const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;      // TMEM lane owned by this thread, 16-column group
+    const size_t sbase = ((size_t)c * HV + h) * DK * DV;
+    uint32_t phase = 0;
+
+    if (tid < CH) sBeta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
+    {
+        float vS[4][8], vK[2][8], vG[2][8], vA[1][8];
+        load_chunks<4, 512, true>(vS, 128, 128, [&](int r, int k8, float (&v)[8]) { load8(p.h, MKDA_F32, sbase + (size_t)r * DV + k8 * 8, v); });
+        load_chunks<2, 512, true>(vK, 64, 128, [&](int r, int k8, float (&v)[8]) {
+            const int rr = r < len ? r : len - 1;
+            load8(p.k, KVDT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, v);
+        });
+        load_chunks<2, 512, true>(vG, 64, 128, [&](int r, int k8, float (&v)[8]) {
+            const int rr = r < len ? r : len - 1;
+            load8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, v);
+        });
+        load_chunks<1, 512, true>(vA, 64, 64, [&](int r, int k8, float (&v)[8]) {
+            const int rr = r < len ? r : len - 1;
+            load8(p.A, MKDA_F32, ((size_t)(start + rr) * HV + h) * 64 + k8 * 8, v);
+        });
+        store_chunks<4, 512, true>(sSh, sSl, vS, 128, 128);
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4;
+            const int rr = r < len ? r : len - 1;
+            const float rk = r < len ? (p.k_rstd ? p.k_rstd[(size_t)(start + rr) * HK + hk] : 1.f) : 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) vK[n][e] *= rk * exp2f(vG[n][e]);
+        }
+        store_chunks<2, 512, true>(sKh, sKl, vK, 64, 128);
+        {
+            const int r = tid >> 3, k8 = tid & 7;
+            if (r >= len) zero8(vA[0]);
+            store_split8(sAh, sAl, 64, r, k8, vA[0]);
+            __syncthreads();                                      // sBeta
+#pragma unroll
+            for (int e = 0; e < 8; ++e) vA[0][e] *= sBeta[k8 * 8 + e];
+            store_split8(sBh, sBl, 64, r, k8, vA[0]);
+        }
+    }
+    const uint32_t tmem = tc_operands_ready(&sh);
+    if (tid == 0) {
+        umma::gemm(tmem + 0, umma::opnd_mn(sSh, sSl, 128), umma::opnd_k(sKh, sKl, 64), 128, 64, 128, 0u);
+        umma::commit(&sh.bar);
+    }
+    {   // fetch what the next stages need while G1 runs: [dO; dVd] rows and this thread's V column
+        float vT[4][8];
+        load_chunks<4, 512, true>(vT, 128, 128, [&](int r, int k8, float (&v)[8]) {
+            const int t = r & 63, tt = t < len ? t : len - 1;
+            const size_t off = ((size_t)(start + tt) * HV + h) * 128 + k8 * 8;
+            if (r < 64) load8(p.d_o, DODT, off, v); else load8(p.dVd, MKDA_F32, off, v);
+            if (t >= len) zero8(v);
+        });
+        float vv[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int t = cg * 16 + j, tt = t < len ? t : len - 1;
+            vv[j] = ld1(p.v, KVDT, ((size_t)(start + tt) * HV + h) * 128 + row);
+            if (t >= len) vv[j] = 0.f;
+        }
+        umma::mbar_wait(&sh.bar, phase); phase ^= 1;
+        umma::fence_after_sync();
+        float d[16], x0[8], x1[8];
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, cg * 16), d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { x0[j] = vv[j] - d[j]; x1[j] = vv[8 + j] - d[8 + j]; }
+        store_split8(sXh, sXl, 128, row, 2 * cg, x0);
+        store_split8(sXh, sXl, 128, row, 2 * cg + 1, x1);
+        store_chunks<4, 512, true>(sSh, sSl, vT, 128, 128);      // S is dead: the region now holds [dO; dVd]
+    }
+    tc_operands_ready(&sh);
+    if (tid == 0) {
+        umma::gemm(tmem + 64, umma::opnd_k(sXh, sXl, 128), umma::opnd_k(sBh, sBl, 64), 128, 64, 64, 0u);
+        umma::gemm(tmem + 256, umma::opnd_mn(sSh, sSl, 128, 64), umma::opnd_mn(sAh, sAl, 64), 128, 64, 64, 0u);
+        umma::commit(&sh.bar);
+    }
+    umma::mbar_wait(&sh.bar, phase); phase ^= 1;
+    umma::fence_after_sync();
+    {
+        float vd[16], dw[16], a0[8], a1[8];
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 64 + cg * 16), vd);
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 256 + cg * 16), dw);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int t = cg * 16 + j;
+            if (t < len) {
+                const size_t off = ((size_t)(start + t) * HV + h) * 128 + row;
+                p.Vd[off] = vd[j];
+                p.dX[off] = sBeta[t] * dw[j];
+            }
+            if (j < 8) a0[j] = vd[j]; else a1[j - 8] = vd[j];
+        }
+        store_split8(sVh, sVl, 128, row, 2 * cg, a0);
+        store_split8(sVh, sVl, 128, row, 2 * cg + 1, a1);
+    }
+    tc_operands_ready(&sh);
+    if (tid == 0) {
+        umma::gemm(tmem + 128, umma::opnd_k(sSh, sSl, 128), umma::opnd_mn(sVh, sVl, 128), 128, 128, 128, 0u);
+        umma::commit(&sh.bar);
+    }
+    umma::mbar_wait(&sh.bar, phase); phase ^= 1;
+    umma::fence_after_sync();
+    if (q < 2) {                                   // rows i = row: dAqk = lower(dO Vd^T)
+        float d[16];
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + cg * 16), d);
+        if (row < len) {
+            float* dst = p.dAqk + ((size_t)(start + row) * HV + h) * 64 + cg * 16;
+#pragma unroll
+            for (int j = 0; j < 16; j += 4)
+                *reinterpret_cast<float4*>(dst + j) = make_float4(cg * 16 + j <= row ? d[j] : 0.f, cg * 16 + j + 1 <= row ? d[j + 1] : 0.f,
+                                                                  cg * 16 + j + 2 <= row ? d[j + 2] : 0.f, cg * 16 + j + 3 <= row ? d[j + 3] : 0.f);
+        }
+    } else {                                       // rows i = row - 64: dVd X^T -> dbeta_w partials and dA diag(beta)
+        const int i = row - 64;
+        float d[16], a0[8], a1[8];
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + 64 + cg * 16), d);
+        load_tile8(sAh, sAl, 64, i, 2 * cg, a0);
+        load_tile8(sAh, sAl, 64, i, 2 * cg + 1, a1);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            float pr = d[j] * (j < 8 ? a0[j] : a1[j - 8]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) pr += __shfl_xor_sync(0xffffffffu, pr, o);
+            if (lane == 0) sRed[q - 2][cg * 16 + j] = pr;
+            const float da = d[j] * sBeta[cg * 16 + j];
+            if (j < 8) a0[j] = da; else a1[j - 8] = da;
+        }
+        store_split8(sKh, sKl, 128, i, 2 * cg, a0);
+        store_split8(sKh, sKl, 128, i, 2 * cg + 1, a1);
+    }
+    tc_operands_ready(&sh);
+    if (tid < len) p.dbeta_w[(size_t)(start + tid) * HV + h] = sRed[0][tid] + sRed[1][tid];
+    if (tid == 0) {
+        umma::gemm(tmem + 320, umma::opnd_k(sKh, sKl, 128), umma::opnd_k(sAh, sAl, 64), 128, 64, 64, 0u);
+        umma::commit(&sh.bar);
+    }
+    umma::mbar_wait(&sh.bar, phase); phase ^= 1;
+    umma::fence_after_sync();
+    if (q < 2) {
+        float y[16], a0[8], a1[8];
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 320 + cg * 16), y);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { a0[j] = y[j]; a1[j] = y[8 + j]; }
+        store_split8(sBh, sBl, 64, row, 2 * cg, a0);
+        store_split8(sBh, sBl, 64, row, 2 * cg + 1, a1);
+    }
+    tc_operands_ready(&sh);
+    if (tid == 0) {
+        umma::gemm(tmem + 384, umma::opnd_mn(sAh, sAl, 64), umma::opnd_mn(sBh, sBl, 64), 128, 64, 64, 0u);
+        umma::commit(&sh.bar);
+    }
+    umma::mbar_wait(&sh.bar, phase); phase ^= 1;
+    umma::fence_after_sync();
+    if (q < 2) {
+        float z[16];
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 384 + cg * 16), z);      // warp-collective: never under a per-lane condition
+        if (row < len) {
+        float* dst = p.dL + ((size_t)(start + row) * HV + h) * 64 + cg * 16;
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+            *reinterpret_cast<float4*>(dst + j) = make_float4(cg * 16 + j < row ? -z[j] : 0.f, cg * 16 + j + 1 < row ? -z[j + 1] : 0.f,
+                                                              cg * 16 + j + 2 < row ? -z[j + 2] : 0.f, cg * 16 + j + 3 < row ? -z[j + 3] : 0.f);
+        }
+    }
+    tc_end(&sh, tmem, 512);
+}
+
+template <int KVDT, int DODT>
+static int launch_bwd_wy_tc_t(const MkdaBwdWy* p, cudaStream_t stream) {
+    auto kern = bwd_wy_tc_kernel<KVDT, DODT>;
+    if (int e = ensure_smem((const void*)kern, WY_TC_SMEM, "bwd_wy")) return e;
+    kern<<<dim3(p->L.NC, p->L.HV), 512, WY_TC_SMEM, stream>>>(*p);
+    return check_launch("bwd_wy");
+}
+int launch_bwd_wy_tc(const MkdaBwdWy* p, cudaStream_t stream) {
+    MKDA_DISPATCH2(launch_bwd_wy_tc_t, p->kv_dtype, p->do_dtype, p, stream)
 }
 
 }  // namespace mkda

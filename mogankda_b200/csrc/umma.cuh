@@ -6,7 +6,7 @@
 // bits per operand (relative error ~2^-16 per product) for 1.5x the tensor time of one TF32 MMA, in the same
 // shared-memory footprint as an fp32 tile.
 //
-// Every wait is bounded: after WAIT_LIMIT polls the waiter records a timeout in a global status word and goes on
+// Every wait is bounded in time: on expiry the waiter records a timeout in a global status word and goes on
 // (results are then garbage but the kernel terminates and frees its TMEM).
 #pragma once
 #include <cuda_bf16.h>
@@ -15,7 +15,6 @@
 namespace mkda {
 namespace umma {
 
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
 static __device__ unsigned int g_timeout_flag;      // one per translation unit, read back by mkda_device_status()
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -154,12 +153,17 @@ __device__ __forceinline__ void commit(uint64_t* bar) {
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    // Bounded by wall time (SM clock): ~70 ms for the first wait that fails on a device, ~35 us afterwards, so a broken
+    // launch drains quickly instead of serialising one long timeout per CTA.  test_wait never blocks.
+    const long long limit = *(volatile unsigned int*)&g_timeout_flag ? (1ll << 16) : (1ll << 27);
+    const long long t0 = clock64();
+    for (;;) {
         uint32_t ok;
         asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
         if (ok) return true;
+        if (clock64() - t0 > limit) break;
     }
     atomicExch(&g_timeout_flag, 1u);
     return false;
