@@ -15,4 +15,7 @@ int launch_out_fwd_tc(const MkdaOutFwd* p, cudaStream_t stream);
 int launch_bwd_sgrad_tc(const MkdaBwdSgrad* p, cudaStream_t stream);
 int launch_bwd_wy_tc(const MkdaBwdWy* p, cudaStream_t stream);
 int tc_chunk_status(unsigned int* out);
+int launch_recur_fwd_tc(const MkdaRecurFwd* p, cudaStream_t stream);
+int launch_bwd_dh_tc(const MkdaBwdDh* p, cudaStream_t stream);
+int tc_recur_status(unsigned int* out);
 }  // namespace mkda

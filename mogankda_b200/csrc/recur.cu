@@ -450,6 +450,7 @@ extern "C" int mkda_recur_fwd(const MkdaRecurFwd* p, void* stream) {
     if (!p || !p->nw || !p->u || !p->k || !p->g_c) return set_error(MKDA_ERR_ARG, "recur_fwd: null argument");
     if (p->want_transition && !p->mt) return set_error(MKDA_ERR_ARG, "recur_fwd: want_transition needs mt");
     if (p->L.NS == 0) return MKDA_OK;
+    if (!legacy_kernels()) return launch_recur_fwd_tc(p, (cudaStream_t)stream);
     auto kern = recur_fwd_kernel<MKDA_PREC_STATE>;
     if (int e = ensure_smem((const void*)kern, RECUR_SMEM, "recur_fwd")) return e;
     kern<<<dim3(p->want_transition ? 4 : 2, p->L.HV, p->L.NS), 256, RECUR_SMEM, (cudaStream_t)stream>>>(*p);
@@ -471,6 +472,7 @@ extern "C" int mkda_bwd_dh(const MkdaBwdDh* p, void* stream) {
     if (!p || !p->d_o || !p->q || !p->k || !p->g_c || !p->Aqk || !p->nw || !p->dh || !p->dVd)
         return set_error(MKDA_ERR_ARG, "bwd_dh: null argument");
     if (p->L.NS == 0) return MKDA_OK;
+    if (!legacy_kernels()) return launch_bwd_dh_tc(p, (cudaStream_t)stream);
     auto kern = bwd_dh_kernel<MKDA_PREC_DH>;
     if (int e = ensure_smem((const void*)kern, BWD_DH_SMEM, "bwd_dh")) return e;
     kern<<<dim3(2, p->L.HV, p->L.NS), 256, BWD_DH_SMEM, (cudaStream_t)stream>>>(*p);

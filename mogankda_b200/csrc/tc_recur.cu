@@ -1,0 +1,438 @@
+// Serial state recurrences on the Blackwell tensor cores.
+//
+// One CTA (16 warps) per (v-head, segment) carries the whole 128 x 128 state, TRANSPOSED, in tensor memory:
+// St[v lanes][K-index columns] fp32.  With that orientation every operand that has to be regenerated from the
+// accumulators (the state itself, Vd^T) is written by its owning thread as plain 16-byte row chunks of a K-major tile,
+// and every operand that comes from global memory is staged untransposed and read through a K-major or MN-major view.
+// Per chunk:   Vd^T[v x tok] = u^T + St nw^T          St <- St diag(gl) + Vd^T kbar
+// The next chunk's global operands are fetched into registers while the current chunk's products run.
+#include "common.cuh"
+#include "host.h"
+#include "umma.cuh"
+
+namespace mkda {
+
+using umma::store_split8;
+
+__device__ __forceinline__ void ld8(const void* base, int dtype, size_t idx, float (&v)[8]) {
+    const float4 a = ld4(base, dtype, idx), b = ld4(base, dtype, idx + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+struct RecurShared {
+    uint64_t bar;
+    uint32_t tmem;
+    float gl[2][DK];
+};
+
+__device__ __forceinline__ void publish_operands() {
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+}
+
+constexpr int RECUR_TC_SMEM = 64 * 1024 + 4 * 32 * 1024 + 1024;
+
+template <int KDT>
+__global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ RecurShared sh;
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sAh = base;                         // St as A(m = v, k = K index) [128][128]; later Vd^T [128][64]
+    uint8_t* sAl = sAh + 32768;
+    uint8_t* sW[2] = {sAl + 32768, sAl + 32768 + 65536};            // nw [tok][K index], hi then lo (16 KB each)
+    uint8_t* sK[2] = {sW[0] + 32768, sW[1] + 32768};                 // kbar [tok][K index]
+
+    const bool trans = blockIdx.x == 1;
+    const int h = blockIdx.y, seg = blockIdx.z, HV = p.L.HV, HK = p.L.HK;
+    const int hk = h / (HV / HK);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
+    const bool vf = p.state_v_first != 0;
+
+    if (warp == 0) umma::tmem_alloc(&sh.tmem, 256);
+    if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem = sh.tmem;
+    uint32_t phase = 0;
+
+    {   // initial state: columns [32 cg, 32 cg + 32) of row `row`
+        float s[32];
+        const int h0row = p.seg_h0 ? p.seg_h0[seg] : seg;
+        const float* h0 = (!trans && p.h0 && h0row >= 0) ? p.h0 + ((size_t)h0row * HV + h) * DK * DV : nullptr;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const int kk = cg * 32 + j;
+            float v = 0.f;
+            if (trans) v = (kk == row) ? 1.f : 0.f;
+            else if (h0) v = vf ? h0[(size_t)row * DK + kk] : h0[(size_t)kk * DV + row];
+            s[j] = v;
+        }
+        umma::tmem_st32(umma::tmem_addr(tmem, warp, cg * 32), s);
+        umma::tmem_wait_st();
+    }
+
+    const int c_beg = p.L.seg_chunk_off[seg], c_end = p.L.seg_chunk_off[seg + 1];
+    // staging of one chunk's global operands: thread owns chunks i = tid, tid + 512 -> (token r = i / 16, k8 = i % 16)
+    auto load_w = [&](int c, float (&w)[2][8]) {
+        const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
+            ld8(p.nw, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, w[n]);
+        }
+    };
+    auto store_w = [&](int c, int buf, float (&w)[2][8]) {
+        const int len = p.L.chunk_len[c];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
+            if (r >= len) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) w[n][e] = 0.f;
+            }
+            store_split8(sW[buf], sW[buf] + 16384, 64, r, k8, w[n]);
+        }
+    };
+    auto load_k = [&](int c, float (&k)[2][8], float (&g)[2][8], float (&gL)[2][8], float (&rs)[2]) {
+        const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
+            const size_t tk = (size_t)(start + rr) * HK + hk;
+            ld8(p.k, KDT, tk * 128 + k8 * 8, k[n]);
+            ld8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, g[n]);
+            ld8(p.g_c, MKDA_F32, ((size_t)(start + len - 1) * HV + h) * 128 + k8 * 8, gL[n]);
+            rs[n] = p.k_rstd ? p.k_rstd[tk] : 1.f;
+        }
+    };
+    auto store_k = [&](int c, int buf, float (&k)[2][8], float (&g)[2][8], float (&gL)[2][8], float (&rs)[2]) {
+        const int len = p.L.chunk_len[c];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
+            const float m = r < len ? rs[n] : 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) k[n][e] *= m * exp2f(gL[n][e] - g[n][e]);
+            store_split8(sK[buf], sK[buf] + 16384, 64, r, k8, k[n]);
+            if (r == 0) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sh.gl[buf][k8 * 8 + e] = exp2f(gL[n][e]);
+            }
+        }
+    };
+
+    if (c_beg < c_end) {
+        float w[2][8], k[2][8], g[2][8], gL[2][8], rs[2];
+        load_w(c_beg, w);
+        load_k(c_beg, k, g, gL, rs);
+        store_w(c_beg, 0, w);
+        store_k(c_beg, 0, k, g, gL, rs);
+    }
+    for (int c = c_beg; c < c_end; ++c) {
+        const int buf = (c - c_beg) & 1, start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+        const bool more = c + 1 < c_end;
+        float w[2][8], uu[16];
+        if (more) load_w(c + 1, w);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int t = cg * 16 + j, tt = t < len ? t : len - 1;
+            uu[j] = trans ? 0.f : p.u[((size_t)(start + tt) * HV + h) * 128 + row];
+            if (t >= len) uu[j] = 0.f;
+        }
+        __syncthreads();                                   // sh.gl[buf] and the tiles of `buf` are complete
+        {   // state entering the chunk: operand tile, optional global copy, decay
+            float s[32];
+            umma::tmem_ld32(umma::tmem_addr(tmem, warp, cg * 32), s);
+            float* hc = (p.h && !trans) ? p.h + ((size_t)c * HV + h) * DK * DV + row : nullptr;   // [K][V]: coalesced over v
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float v8[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v8[e] = s[i * 8 + e];
+                store_split8(sAh, sAl, 128, row, cg * 4 + i, v8);
+                if (hc) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) hc[(size_t)(cg * 32 + i * 8 + e) * DV] = v8[e];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) s[j] *= sh.gl[buf][cg * 32 + j];
+            umma::tmem_st32(umma::tmem_addr(tmem, warp, cg * 32), s);
+            umma::tmem_wait_st();
+        }
+        publish_operands();
+        if (tid == 0) {
+            umma::gemm(tmem + 128, umma::opnd_k(sAh, sAl, 128), umma::opnd_k(sW[buf], sW[buf] + 16384, 64), 128, 64, 128, 0u);
+            umma::commit(&sh.bar);
+        }
+        float k[2][8], g[2][8], gL[2][8], rs[2];
+        if (more) {
+            store_w(c + 1, buf ^ 1, w);
+            load_k(c + 1, k, g, gL, rs);
+        }
+        umma::mbar_wait(&sh.bar, phase); phase ^= 1;
+        umma::fence_after_sync();
+        {   // Vd^T = u^T + St nw^T: global copy [tok][v] and operand tile A(m = v, k = tok)
+            float d[16], a0[8], a1[8];
+            umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + cg * 16), d);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float vd = d[j] + uu[j];
+                const int t = cg * 16 + j;
+                if (p.Vd && !trans && t < len) p.Vd[((size_t)(start + t) * HV + h) * 128 + row] = vd;
+                if (j < 8) a0[j] = vd; else a1[j - 8] = vd;
+            }
+            store_split8(sAh, sAl, 128, row, 2 * cg, a0);
+            store_split8(sAh, sAl, 128, row, 2 * cg + 1, a1);
+        }
+        publish_operands();
+        if (tid == 0) {
+            umma::gemm(tmem, umma::opnd_k(sAh, sAl, 128), umma::opnd_mn(sK[buf], sK[buf] + 16384, 64), 128, 128, 64, 1u);
+            umma::commit(&sh.bar);
+        }
+        if (more) store_k(c + 1, buf ^ 1, k, g, gL, rs);
+        umma::mbar_wait(&sh.bar, phase); phase ^= 1;
+        umma::fence_after_sync();
+    }
+    {   // state leaving the segment
+        float s[32];
+        umma::tmem_ld32(umma::tmem_addr(tmem, warp, cg * 32), s);
+        float* out = nullptr;
+        if (trans) { if (p.mt) out = p.mt + ((size_t)seg * HV + h) * DK * DK; }
+        else if (p.ht) out = p.ht + ((size_t)seg * HV + h) * DK * DV;
+        if (out) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int kk = cg * 32 + j;
+                // transition: M[K out][K in] with this thread holding row `row` = K in; state: [K][V] or [V][K]
+                if (trans || !vf) out[(size_t)kk * DV + row] = s[j];
+                else out[(size_t)row * DK + kk] = s[j];
+            }
+        }
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) umma::tmem_dealloc(tmem, 256);
+}
+
+int tc_recur_status(unsigned int* out) {
+    return cudaMemcpyFromSymbol(out, umma::g_timeout_flag, sizeof(unsigned int)) == cudaSuccess ? 0 : -1;
+}
+
+template <int KDT>
+static int launch_recur_fwd_tc_t(const MkdaRecurFwd* p, cudaStream_t stream) {
+    auto kern = recur_fwd_tc_kernel<KDT>;
+    if (int e = ensure_smem((const void*)kern, RECUR_TC_SMEM, "recur_fwd")) return e;
+    kern<<<dim3(p->want_transition ? 2 : 1, p->L.HV, p->L.NS), 512, RECUR_TC_SMEM, stream>>>(*p);
+    return check_launch("recur_fwd");
+}
+int launch_recur_fwd_tc(const MkdaRecurFwd* p, cudaStream_t stream) {
+    switch (p->k_dtype) {
+        case MKDA_F32: return launch_recur_fwd_tc_t<MKDA_F32>(p, stream);
+        case MKDA_BF16: return launch_recur_fwd_tc_t<MKDA_BF16>(p, stream);
+        case MKDA_F16: return launch_recur_fwd_tc_t<MKDA_F16>(p, stream);
+    }
+    return set_error(MKDA_ERR_ARG, "recur_fwd: unsupported dtype");
+}
+
+}  // namespace mkda
+
+namespace mkda {
+
+// ---------------------------------------------------------------------------------------------------------
+// Reverse state-gradient chain on the tensor cores.  dSt[v lanes][K-index columns] (transposed, fp32, TMEM) is the
+// gradient of the state leaving the current chunk; per chunk, walking backwards:
+//   dVd^T[v x j] = dO^T Aqk + dSt kbar^T
+//   dSt <- dSt diag(gl) + dO^T (scale q 2^g) + dVd^T nw
+// dO, Aqk, kbar, q~ and nw are staged untransposed; the views (K-major / MN-major) supply the transposes.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int DH_TC_SMEM = 64 * 1024 + 32 * 1024 + 16 * 1024 + 3 * 32 * 1024 + 1024;
+
+template <int QKDT, int DODT>
+__global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ RecurShared sh;
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sAh = base;                         // dSt as A(m = v, k = K index); later dVd^T [128][64]
+    uint8_t* sAl = sAh + 32768;
+    uint8_t* sDo = sAl + 32768;                  // dO [i][v]          hi 16 KB, lo 16 KB
+    uint8_t* sAq = sDo + 32768;                  // Aqk [i][j]         hi 8 KB, lo 8 KB
+    uint8_t* sKb = sAq + 16384;                  // kbar [j][K index]
+    uint8_t* sQs = sKb + 32768;                  // scale q 2^g [i][K index]
+    uint8_t* sNw = sQs + 32768;                  // nw [j][K index]
+
+    const int h = blockIdx.y, seg = blockIdx.z, HV = p.L.HV, HK = p.L.HK;
+    const int hk = h / (HV / HK);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
+    const bool vf = p.state_v_first != 0;
+
+    if (warp == 0) umma::tmem_alloc(&sh.tmem, 256);
+    if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem = sh.tmem;
+    uint32_t phase = 0;
+
+    {
+        float s[32];
+        const int drow = p.seg_dht ? p.seg_dht[seg] : seg;
+        const float* src = (p.dht && drow >= 0) ? p.dht + ((size_t)drow * HV + h) * DK * DV : nullptr;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const int kk = cg * 32 + j;
+            s[j] = src ? (vf ? src[(size_t)row * DK + kk] : src[(size_t)kk * DV + row]) : 0.f;
+        }
+        umma::tmem_st32(umma::tmem_addr(tmem, warp, cg * 32), s);
+        umma::tmem_wait_st();
+    }
+    const int c_beg = p.L.seg_chunk_off[seg], c_end = p.L.seg_chunk_off[seg + 1];
+    for (int c = c_end - 1; c >= c_beg; --c) {
+        const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+        {   // batch 1: dO, Aqk, nw (plain copies)
+            float vo[2][8], vn[2][8], va[8];
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
+                const size_t off = ((size_t)(start + rr) * HV + h) * 128 + k8 * 8;
+                ld8(p.d_o, DODT, off, vo[n]);
+                ld8(p.nw, MKDA_F32, off, vn[n]);
+            }
+            {
+                const int r = tid >> 3, k8 = tid & 7, rr = r < len ? r : len - 1;
+                ld8(p.Aqk, MKDA_F32, ((size_t)(start + rr) * HV + h) * 64 + k8 * 8, va);
+                if (r >= len) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) va[e] = 0.f;
+                }
+                store_split8(sAq, sAq + 8192, 64, r, k8, va);
+            }
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
+                if (r >= len) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) { vo[n][e] = 0.f; vn[n][e] = 0.f; }
+                }
+                store_split8(sDo, sDo + 16384, 64, r, k8, vo[n]);
+                store_split8(sNw, sNw + 16384, 64, r, k8, vn[n]);
+            }
+        }
+        {   // batch 2: kbar = k 2^(gL - g), q~ = scale q 2^g
+            float vk[2][8], vq[2][8], vg[2][8], vl[2][8], rk[2], rq[2];
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
+                const size_t tk = (size_t)(start + rr) * HK + hk;
+                ld8(p.k, QKDT, tk * 128 + k8 * 8, vk[n]);
+                ld8(p.q, QKDT, tk * 128 + k8 * 8, vq[n]);
+                ld8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vg[n]);
+                ld8(p.g_c, MKDA_F32, ((size_t)(start + len - 1) * HV + h) * 128 + k8 * 8, vl[n]);
+                rk[n] = p.k_rstd ? p.k_rstd[tk] : 1.f;
+                rq[n] = p.scale * (p.q_rstd ? p.q_rstd[tk] : 1.f);
+            }
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
+                const float mk = r < len ? rk[n] : 0.f, mq = r < len ? rq[n] : 0.f;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    vk[n][e] *= mk * exp2f(vl[n][e] - vg[n][e]);
+                    vq[n][e] *= mq * exp2f(vg[n][e]);
+                }
+                store_split8(sKb, sKb + 16384, 64, r, k8, vk[n]);
+                store_split8(sQs, sQs + 16384, 64, r, k8, vq[n]);
+                if (r == 0) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) sh.gl[0][k8 * 8 + e] = exp2f(vl[n][e]);
+                }
+            }
+        }
+        __syncthreads();                                   // sh.gl
+        {   // gradient leaving the chunk: operand tile, global copy ([K][V]), decay
+            float s[32];
+            umma::tmem_ld32(umma::tmem_addr(tmem, warp, cg * 32), s);
+            float* dhc = p.dh + ((size_t)c * HV + h) * DK * DV + row;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float v8[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    v8[e] = s[i * 8 + e];
+                    dhc[(size_t)(cg * 32 + i * 8 + e) * DV] = v8[e];
+                }
+                store_split8(sAh, sAl, 128, row, cg * 4 + i, v8);
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) s[j] *= sh.gl[0][cg * 32 + j];
+            umma::tmem_st32(umma::tmem_addr(tmem, warp, cg * 32), s);
+            umma::tmem_wait_st();
+        }
+        publish_operands();
+        if (tid == 0) {
+            umma::gemm(tmem + 128, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sAq, sAq + 8192, 64), 128, 64, 64, 0u);
+            umma::gemm(tmem + 128, umma::opnd_k(sAh, sAl, 128), umma::opnd_k(sKb, sKb + 16384, 64), 128, 64, 128, 1u);
+            umma::commit(&sh.bar);
+        }
+        umma::mbar_wait(&sh.bar, phase); phase ^= 1;
+        umma::fence_after_sync();
+        {
+            float d[16], a0[8], a1[8];
+            umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + cg * 16), d);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int t = cg * 16 + j;
+                if (t < len) p.dVd[((size_t)(start + t) * HV + h) * 128 + row] = d[j];
+                if (j < 8) a0[j] = d[j]; else a1[j - 8] = d[j];
+            }
+            store_split8(sAh, sAl, 128, row, 2 * cg, a0);
+            store_split8(sAh, sAl, 128, row, 2 * cg + 1, a1);
+        }
+        publish_operands();
+        if (tid == 0) {
+            umma::gemm(tmem, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sQs, sQs + 16384, 64), 128, 128, 64, 1u);
+            umma::gemm(tmem, umma::opnd_k(sAh, sAl, 128), umma::opnd_mn(sNw, sNw + 16384, 64), 128, 128, 64, 1u);
+            umma::commit(&sh.bar);
+        }
+        umma::mbar_wait(&sh.bar, phase); phase ^= 1;
+        umma::fence_after_sync();
+    }
+    if (p.dh0) {
+        float s[32];
+        umma::tmem_ld32(umma::tmem_addr(tmem, warp, cg * 32), s);
+        float* out = p.dh0 + ((size_t)seg * HV + h) * DK * DV;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const int kk = cg * 32 + j;
+            if (vf) out[(size_t)row * DK + kk] = s[j]; else out[(size_t)kk * DV + row] = s[j];
+        }
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) umma::tmem_dealloc(tmem, 256);
+}
+
+template <int QKDT, int DODT>
+static int launch_bwd_dh_tc_t(const MkdaBwdDh* p, cudaStream_t stream) {
+    auto kern = bwd_dh_tc_kernel<QKDT, DODT>;
+    if (int e = ensure_smem((const void*)kern, DH_TC_SMEM, "bwd_dh")) return e;
+    kern<<<dim3(1, p->L.HV, p->L.NS), 512, DH_TC_SMEM, stream>>>(*p);
+    return check_launch("bwd_dh");
+}
+int launch_bwd_dh_tc(const MkdaBwdDh* p, cudaStream_t stream) {
+    switch (p->qk_dtype * 3 + p->do_dtype) {
+        case 0: return launch_bwd_dh_tc_t<0, 0>(p, stream); case 1: return launch_bwd_dh_tc_t<0, 1>(p, stream);
+        case 2: return launch_bwd_dh_tc_t<0, 2>(p, stream); case 3: return launch_bwd_dh_tc_t<1, 0>(p, stream);
+        case 4: return launch_bwd_dh_tc_t<1, 1>(p, stream); case 5: return launch_bwd_dh_tc_t<1, 2>(p, stream);
+        case 6: return launch_bwd_dh_tc_t<2, 0>(p, stream); case 7: return launch_bwd_dh_tc_t<2, 1>(p, stream);
+        case 8: return launch_bwd_dh_tc_t<2, 2>(p, stream);
+    }
+    return set_error(MKDA_ERR_ARG, "bwd_dh: unsupported dtype");
+}
+
+}  // namespace mkda
