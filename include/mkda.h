@@ -238,11 +238,11 @@ int mkda_qk_grad_finish(const MkdaQkGrad* p, void* stream);
 typedef struct {
     int NG; int HV;
     const int* grp_seg_off;    /* [NG+1] */
-    const float* hs;           /* [NS,HV,128,128] per-segment local result ([K,V]) */
+    const float* hs;           /* [NS,HV,128,128] per-segment local result ([K,V]); NULL = zero (composes transitions) */
     const float* ms;           /* [NS,HV,128,128] per-segment transition */
     const float* carry;        /* [NG,HV,128,128] ([K,V]) or NULL */
     int reverse;
-    float* s_in;               /* [NS,HV,128,128] value entering each segment ([K,V]) */
+    float* s_in;               /* [NS,HV,128,128] value entering each segment ([K,V]), or NULL */
     float* s_out;              /* [NG,HV,128,128] value leaving the last (first) segment of each group, or NULL */
 } MkdaCombine;
 int mkda_state_combine(const MkdaCombine* p, void* stream);

@@ -412,8 +412,10 @@ __global__ void __launch_bounds__(256, 1) combine_kernel(const MkdaCombine p) {
             const int cc = nt * 8 + 2 * t;
             *reinterpret_cast<float2*>(sX + kr0 * LDS + cc) = make_float2(X[nt][0], X[nt][1]);
             *reinterpret_cast<float2*>(sX + kr1 * LDS + cc) = make_float2(X[nt][2], X[nt][3]);
-            *reinterpret_cast<float2*>(p.s_in + base + (size_t)kr0 * DV + col0 + cc) = make_float2(X[nt][0], X[nt][1]);
-            *reinterpret_cast<float2*>(p.s_in + base + (size_t)kr1 * DV + col0 + cc) = make_float2(X[nt][2], X[nt][3]);
+            if (p.s_in) {
+                *reinterpret_cast<float2*>(p.s_in + base + (size_t)kr0 * DV + col0 + cc) = make_float2(X[nt][0], X[nt][1]);
+                *reinterpret_cast<float2*>(p.s_in + base + (size_t)kr1 * DV + col0 + cc) = make_float2(X[nt][2], X[nt][3]);
+            }
         }
         for (int j = tid; j < DK * 32; j += 256) {
             const int r = j >> 5, c4 = (j & 31) * 4;
@@ -422,8 +424,11 @@ __global__ void __launch_bounds__(256, 1) combine_kernel(const MkdaCombine p) {
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
             const int cc = col0 + nt * 8 + 2 * t;
-            const float2 a = *reinterpret_cast<const float2*>(p.hs + base + (size_t)kr0 * DV + cc);
-            const float2 b = *reinterpret_cast<const float2*>(p.hs + base + (size_t)kr1 * DV + cc);
+            float2 a = make_float2(0.f, 0.f), b = a;
+            if (p.hs) {
+                a = *reinterpret_cast<const float2*>(p.hs + base + (size_t)kr0 * DV + cc);
+                b = *reinterpret_cast<const float2*>(p.hs + base + (size_t)kr1 * DV + cc);
+            }
             X[nt][0] = a.x; X[nt][1] = a.y; X[nt][2] = b.x; X[nt][3] = b.y;
         }
         __syncthreads();
@@ -480,7 +485,7 @@ extern "C" int mkda_bwd_dh(const MkdaBwdDh* p, void* stream) {
 }
 
 extern "C" int mkda_state_combine(const MkdaCombine* p, void* stream) {
-    if (!p || !p->grp_seg_off || !p->hs || !p->ms || !p->s_in) return set_error(MKDA_ERR_ARG, "state_combine: null argument");
+    if (!p || !p->grp_seg_off || !p->ms || (!p->s_in && !p->s_out)) return set_error(MKDA_ERR_ARG, "state_combine: null argument");
     if (p->NG == 0) return MKDA_OK;
     auto kern = combine_kernel<MKDA_PREC_COMBINE>;
     if (int e = ensure_smem((const void*)kern, COMBINE_SMEM, "state_combine")) return e;

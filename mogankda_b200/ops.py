@@ -284,10 +284,11 @@ def qk_grad_finish(d_v, x, rstd, HK, HV):
     return dx
 
 
-def state_combine(grp_seg_off, NG, NS, HV, hs, ms, carry=None, reverse=False, want_out=True):
-    """-> (s_in [NS,HV,128,128], s_out [NG,HV,128,128] or None); all in [K,V] orientation."""
-    dev = hs.device
-    s_in = torch.empty(NS, HV, 128, 128, dtype=torch.float32, device=dev)
+def state_combine(grp_seg_off, NG, NS, HV, hs, ms, carry=None, reverse=False, want_out=True, want_in=True):
+    """-> (s_in [NS,HV,128,128] or None, s_out [NG,HV,128,128] or None); all in [K,V] orientation.
+    ``hs=None`` folds the transitions alone (with ``carry`` = identity this composes them)."""
+    dev = ms.device
+    s_in = torch.empty(NS, HV, 128, 128, dtype=torch.float32, device=dev) if want_in else None
     s_out = torch.empty(NG, HV, 128, 128, dtype=torch.float32, device=dev) if want_out else None
     p = STRUCTS["MkdaCombine"]()
     p.NG, p.HV, p.grp_seg_off = NG, HV, _ptr(grp_seg_off, torch.int32)

@@ -1,0 +1,90 @@
+"""GPU: context parallelism end to end.  The ranks are emulated one after the other in a single process (record /
+replay of the all-gather, see ReplayComm): no kernel ever waits on another kernel.  The NCCL path itself is exercised by
+``bench.py --workload longdoc`` under torchrun."""
+import os
+import pytest
+import torch
+
+import mogankda_b200 as mk
+from mogankda_b200.cp import ContextParallel
+from oracle import kda_oracle as orc
+from tests.common import check, make_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+class ReplayComm:
+    """Emulates W ranks in one process without concurrency.  What a rank contributes to each all-gather depends only on
+    its own slice (rank-level state / transition / state-gradient pairs), so the ranks are run twice: the first pass
+    records every contribution (and hands back zeros), the second replays the complete gathers."""
+
+    def __init__(self, world):
+        self.world, self.rec, self.replay = world, {}, False
+
+    def view(self, rank):
+        outer = self
+
+        class _V:
+            world = outer.world
+
+            def __init__(self):
+                self.rank, self.calls = rank, 0
+
+            def all_gather(self, flat_out, flat_in):
+                key = self.calls
+                self.calls += 1
+                if not outer.replay:
+                    outer.rec[(rank, key)] = flat_in.clone()
+                    flat_out.zero_()
+                else:
+                    flat_out.copy_(torch.cat([outer.rec[(r, key)] for r in range(outer.world)]))
+        return _V()
+
+
+def _problem(T, seed=31, dtype=torch.float32):
+    lv, do, dht, opts, _ = make_inputs(B=1, T=T, HK=1, HV=2, dtype=dtype, gate="kimi", epi=None, seed=seed)
+    return lv, do, dht, opts
+
+
+def _slice(lv, a, b):
+    return {n: (t[:, a:b].contiguous() if t.dim() >= 3 and t.shape[0] == 1 and t.shape[1] > 128 else t) for n, t in lv.items()}
+
+
+def _run_rank(ctx, lv, do, dht, opts, rank, world, a, b, out):
+    if True:
+        x = {n: t.clone().requires_grad_(True) for n, t in _slice(lv, a, b).items()}
+        o, ht = mk.chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], gate_mode="kimi", A_log=x["A_log"],
+                             dt_bias=x["dt_bias"], beta_mode="sigmoid", beta_scale=2.0, use_qk_l2norm_in_kernel=True,
+                             initial_state=x["h0"], output_final_state=True, cp_context=ctx)
+        loss = (o.double() * do[:, a:b].double()).sum()
+        if rank == world - 1:
+            loss = loss + (ht.double() * dht.double()).sum()
+        names = ("q", "k", "v", "g", "beta", "h0")
+        grads = torch.autograd.grad(loss, [x[n] for n in names], allow_unused=True)
+        out[rank] = dict(o=o.detach(), ht=ht.detach(), **{"d" + n: g for n, g in zip(names, grads)})
+
+
+@pytest.mark.parametrize("world,T", [(2, 640), (3, 64 * 45)])
+def test_context_parallel_matches_global_oracle(world, T):
+    lv, do, dht, opts = _problem(T)
+    ref = {}
+    x = {n: t.double().clone().requires_grad_(True) for n, t in lv.items()}
+    o, ht = orc.chunked_delta_rule(x["q"], x["k"], x["v"], x["g"], x["beta"], gate_mode="kimi", A_log=x["A_log"],
+                                   dt_bias=x["dt_bias"], beta_mode="sigmoid", beta_scale=2.0, use_qk_l2norm_in_kernel=True,
+                                   initial_state=x["h0"], output_final_state=True)
+    names = ("q", "k", "v", "g", "beta", "h0")
+    grads = torch.autograd.grad((o * do.double()).sum() + (ht * dht.double()).sum(), [x[n] for n in names])
+    ref = dict(o=o, ht=ht, **{"d" + n: g for n, g in zip(names, grads)})
+    per = (T // 64 // world) * 64
+    bounds = [(r * per, T if r == world - 1 else (r + 1) * per) for r in range(world)]
+    comm, out = ReplayComm(world), [None] * world
+    for replay in (False, True):
+        comm.replay = replay
+        for r, (a, b) in enumerate(bounds):
+            _run_rank(ContextParallel(comm=comm.view(r)), lv, do, dht, opts, r, world, a, b, out)
+    for r, (a, b) in enumerate(bounds):
+        check(f"o[{r}]", out[r]["o"], ref["o"][:, a:b])
+        for n in ("dq", "dk", "dv", "dg", "dbeta"):
+            check(f"{n}[{r}]", out[r][n], ref[n][:, a:b])
+    check("ht", out[-1]["ht"], ref["ht"])
+    check("dh0", out[0]["dh0"], ref["dh0"])
