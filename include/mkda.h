@@ -157,6 +157,38 @@ typedef struct {
 } MkdaEpilogueBwd;
 int mkda_epilogue_bwd(const MkdaEpilogueBwd* p, void* stream);
 
+/* Gated RMSNorm backward for callers that cannot allocate.  It has no counterpart in the reference (whose wrapper
+ * creates the per-block weight-gradient partials with torch.empty on every call).
+ *
+ * Who needs it: a host that fixed its device-memory plan before the step starts -- a runtime whose caching allocator is
+ * frozen after warm-up, an engine that carved one arena at start-up, a thread that must not take the allocator lock.
+ * Such a caller can still provide the inputs and the outputs, but it cannot produce the [ceil(rows/64), 128] fp32
+ * scratch that mkda_epilogue_bwd wants in `part_w`, nor the second launch's workspace.  This entry point keeps that
+ * scratch inside the library, in one file-scope device array of MKDA_NOALLOC_MAX_ROWS / 64 * 128 floats (2 MiB) that
+ * every GPU which loads the library holds until the process exits, and it also runs the second-stage reduction, so
+ * `dweight` [128] comes back finished.  It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ *  - rows > MKDA_NOALLOC_MAX_ROWS is rejected with MKDA_ERR_ARG ("... exceeds the built-in scratch ...").
+ *  - The first call on each device looks up the device address of the scratch array (cudaGetSymbolAddress, with that
+ *    device current) and caches it; make that first call before any stream capture is opened.
+ *  - All calls share the one array and it keeps whatever the last call left.  Nothing in it has to start at zero:
+ *    every row the reduction reads was written by the same call.  Two calls that overlap on the GPU (different
+ *    streams, or different host threads) race on it: serialise them.
+ *  - d_o, dgate, dweight are bit-identical to mkda_epilogue_bwd + mkda_reduce_partials on the same inputs. */
+#define MKDA_NOALLOC_MAX_ROWS 262144
+typedef struct {
+    int rows;                  /* TT*HV, at most MKDA_NOALLOC_MAX_ROWS */
+    const void* dy; int dy_dtype;
+    const float* o_raw;
+    const void* norm_w; int norm_w_dtype;
+    const void* gate; int gate_dtype;
+    int act; float eps;
+    float* d_o;                /* [rows,128] fp32 */
+    void* dgate; int dgate_dtype;
+    float* dweight;            /* [128] fp32, finished sum */
+} MkdaEpilogueBwdNoAlloc;
+int mkda_epilogue_bwd_noalloc(const MkdaEpilogueBwdNoAlloc* p, void* stream);
+
 /* Reverse state chain per (segment, v-head, 64-column block).
  * Replaces bwd_dh_kda (mogan_kda/ops/kimi_delta_rule/chunk/hopper/bwd_dh.py:390-448). */
 typedef struct {

@@ -13,7 +13,7 @@ HEADER = os.path.join(HERE, "..", "include", "mkda.h")
 ENTRY_POINTS = (
     "mkda_gate_cumsum_fwd", "mkda_gate_bwd", "mkda_reduce_partials", "mkda_l2norm_rstd", "mkda_intra_fwd",
     "mkda_recur_fwd", "mkda_out_fwd", "mkda_epilogue_bwd", "mkda_bwd_dh", "mkda_bwd_wy", "mkda_bwd_sgrad",
-    "mkda_bwd_intra", "mkda_qk_grad_finish", "mkda_state_combine", "mkda_selftest_umma",
+    "mkda_bwd_intra", "mkda_qk_grad_finish", "mkda_state_combine", "mkda_selftest_umma", "mkda_epilogue_bwd_noalloc",
 )
 ENUMS = {}
 STRUCTS = {}
@@ -22,6 +22,8 @@ STRUCTS = {}
 def _parse_header(path=HEADER):
     text = open(path).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    for name, val in re.findall(r"^#define\s+(MKDA_\w+)\s+(\d+)\s*$", text, flags=re.M):
+        ENUMS[name] = int(val)
     for body in re.findall(r"enum\s*\{(.*?)\}", text, flags=re.S):
         for item in body.split(","):
             if "=" in item:

@@ -324,6 +324,57 @@ extern "C" int mkda_qk_grad_finish(const MkdaQkGrad* p, void* stream) {
     return check_launch("qk_grad_finish");
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Allocation-free variant of the gated RMSNorm backward: the per-block weight-gradient partials live in a static device
+// array instead of a caller-provided buffer, and the second-stage reduction is launched here as well.
+// `g_noalloc_scratch` names the array for DEVICE code; on the host the same identifier is only a handle, so the host
+// asks the runtime for the array's device address (once per device) and passes that pointer to the kernels.
+// ---------------------------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_noalloc_scratch[(MKDA_NOALLOC_MAX_ROWS / 64) * 128];
+static float* g_noalloc_ptr[64] = {nullptr};          // device address of the scratch, per device ordinal
+
+static int noalloc_scratch(float** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+        return set_error(MKDA_ERR_LAUNCH, "epilogue_bwd_noalloc: cannot identify the current device");
+    if (!g_noalloc_ptr[dev]) {
+        float* ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess || !ptr) {
+            (void)cudaGetLastError();
+            return set_error(MKDA_ERR_LAUNCH, "epilogue_bwd_noalloc: cudaGetSymbolAddress failed for the built-in scratch");
+        }
+        g_noalloc_ptr[dev] = ptr;
+    }
+    *out = g_noalloc_ptr[dev];
+    return MKDA_OK;
+}
+
+extern "C" int mkda_epilogue_bwd_noalloc(const MkdaEpilogueBwdNoAlloc* p, void* stream) {
+    if (!p || !p->dy || !p->o_raw || !p->gate || !p->d_o || !p->dgate || !p->dweight)
+        return set_error(MKDA_ERR_ARG, "epilogue_bwd_noalloc: null argument");
+    if (p->rows < 0 || p->rows > MKDA_NOALLOC_MAX_ROWS)
+        return set_error(MKDA_ERR_ARG, "epilogue_bwd_noalloc: rows exceeds the built-in scratch (MKDA_NOALLOC_MAX_ROWS = 262144); "
+                                       "use mkda_epilogue_bwd with a caller-provided part_w");
+    float* scratch = nullptr;
+    if (int e = noalloc_scratch(&scratch)) return e;
+    const int nblk = (p->rows + 63) / 64;
+    if (nblk == 0) {
+        if (cudaMemsetAsync(p->dweight, 0, 128 * sizeof(float), (cudaStream_t)stream) != cudaSuccess)
+            return set_error(MKDA_ERR_LAUNCH, "epilogue_bwd_noalloc: memset failed");
+        return MKDA_OK;
+    }
+    MkdaEpilogueBwd q;
+    q.rows = p->rows; q.dy = p->dy; q.dy_dtype = p->dy_dtype; q.o_raw = p->o_raw; q.norm_w = p->norm_w;
+    q.norm_w_dtype = p->norm_w_dtype; q.gate = p->gate; q.gate_dtype = p->gate_dtype; q.act = p->act; q.eps = p->eps;
+    q.d_o = p->d_o; q.dgate = p->dgate; q.dgate_dtype = p->dgate_dtype;
+    q.part_w = scratch;                 // every block overwrites its whole row: nothing has to be cleared first
+    epilogue_bwd_kernel<<<nblk, 128, 0, (cudaStream_t)stream>>>(q);
+    if (int e = check_launch("epilogue_bwd_noalloc")) return e;
+    reduce_cols_kernel<<<4, dim3(32, 8), 0, (cudaStream_t)stream>>>(scratch, nblk, 128, p->dweight);
+    return check_launch("epilogue_bwd_noalloc (reduce)");
+}
+
 extern "C" int mkda_epilogue_bwd(const MkdaEpilogueBwd* p, void* stream) {
     if (!p || !p->dy || !p->o_raw || !p->gate || !p->d_o || !p->dgate) return set_error(MKDA_ERR_ARG, "epilogue_bwd: null argument");
     if (p->rows == 0) return MKDA_OK;
