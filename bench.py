@@ -372,7 +372,7 @@ def main():
         line = {
             "metric": "KDA fwd+bwd Mtok/s per layer", "value": value, "unit": "Mtok/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "strong" if cp is not None else "weak", "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+            "scaling": "weak", "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
             "config": {"workload": f"{args.workload}: {desc}", **dims, "D": D,
                        "parallelism": ("cp%d" % world) if cp is not None else ("dp%d" % world),
                        "l2": "per-step working set (> 10 GB of inputs and intermediates) exceeds the 126 MB L2"},
