@@ -23,6 +23,7 @@ SOURCES = {
     "selftest.cu": (),
     "tc_chunk.cu": (),
     "tc_recur.cu": (),
+    "tc_intra.cu": (),
 }
 PREC_MACROS = ("MKDA_PREC_INTRA", "MKDA_PREC_STATE", "MKDA_PREC_OUT", "MKDA_PREC_DH", "MKDA_PREC_WY", "MKDA_PREC_SGRAD",
                "MKDA_PREC_INTRA_BWD")

@@ -50,6 +50,7 @@ extern "C" int mkda_device_status(void) {
     if (mkda::selftest_status(&f) == 0) any |= f;
     if (mkda::tc_chunk_status(&f) == 0) any |= f;
     if (mkda::tc_recur_status(&f) == 0) any |= f;
+    if (mkda::tc_intra_status(&f) == 0) any |= f;
     return (int)any;
 }
 extern "C" const char* mkda_last_error(void) { return mkda::g_err; }

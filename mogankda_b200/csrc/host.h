@@ -18,4 +18,7 @@ int tc_chunk_status(unsigned int* out);
 int launch_recur_fwd_tc(const MkdaRecurFwd* p, cudaStream_t stream);
 int launch_bwd_dh_tc(const MkdaBwdDh* p, cudaStream_t stream);
 int tc_recur_status(unsigned int* out);
+int launch_intra_fwd_tc(const MkdaIntraFwd* p, cudaStream_t stream);
+int launch_bwd_intra_tc(const MkdaBwdIntra* p, cudaStream_t stream);
+int tc_intra_status(unsigned int* out);
 }  // namespace mkda

@@ -202,6 +202,7 @@ extern "C" int mkda_bwd_intra(const MkdaBwdIntra* p, void* stream) {
         return set_error(MKDA_ERR_ARG, "bwd_intra: null argument");
     if (p->beta_sigmoid && !p->beta_raw) return set_error(MKDA_ERR_ARG, "bwd_intra: sigmoid beta needs the raw input");
     if (p->L.NC == 0) return MKDA_OK;
+    if (!legacy_kernels()) return launch_bwd_intra_tc(p, (cudaStream_t)stream);
     auto kern = bwd_intra_kernel<MKDA_PREC_INTRA_BWD>;
     if (int e = ensure_smem((const void*)kern, INTRA_BWD_SMEM, "bwd_intra")) return e;
     kern<<<dim3(p->L.NC, p->L.HV), 256, INTRA_BWD_SMEM, (cudaStream_t)stream>>>(*p);

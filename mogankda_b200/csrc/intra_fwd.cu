@@ -183,6 +183,7 @@ extern "C" int mkda_intra_fwd(const MkdaIntraFwd* p, void* stream) {
         return set_error(MKDA_ERR_ARG, "intra_fwd: null argument");
     if (p->L.HK <= 0 || p->L.HV % p->L.HK) return set_error(MKDA_ERR_ARG, "intra_fwd: HV must be a multiple of HK");
     if (p->L.NC == 0) return MKDA_OK;
+    if (!legacy_kernels()) return launch_intra_fwd_tc(p, (cudaStream_t)stream);
     auto kern = intra_fwd_kernel<MKDA_PREC_INTRA>;
     if (int e = ensure_smem((const void*)kern, INTRA_SMEM, "intra_fwd")) return e;
     kern<<<dim3(p->L.NC, p->L.HV), 256, INTRA_SMEM, (cudaStream_t)stream>>>(*p);
