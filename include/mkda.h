@@ -68,7 +68,8 @@ typedef struct {
     int mode; float lower_bound;
     const float* dgp;          /* [TT,HV,128] gradient w.r.t. the log2 cumsum as produced by mkda_bwd_intra */
     void* dx; int dx_dtype;    /* [TT,HV,128] or [TT,HV] */
-    float* part_bias;          /* [NC,HV,128] ([NC,HV] scalar) partial sums of d/d(x+bias), or NULL */
+    int part_rows;             /* number of partial rows R (1 <= R <= NC): chunk c accumulates into row c % R */
+    float* part_bias;          /* [R,HV,128] ([R,HV] scalar) partial sums of d/d(x+bias), or NULL */
     float* part_alog;          /* same shape, partial sums of d/dA_log, or NULL */
 } MkdaGateBwd;
 int mkda_gate_bwd(const MkdaGateBwd* p, void* stream);

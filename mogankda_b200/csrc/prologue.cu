@@ -51,6 +51,7 @@ __device__ __forceinline__ void gate_grad(int mode, float s, float E, float lb, 
 // The chunk-local inclusive sum is (sum of the earlier warps' totals, in warp order) + (running sum inside the
 // warp): the association depends only on the row index, never on later rows.
 // ---------------------------------------------------------------------------------------------------------
+template <int XDT>
 __global__ void __launch_bounds__(128) gate_cumsum_fwd_kernel(const MkdaGateFwd p) {
     const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV;
     const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
@@ -59,16 +60,21 @@ __global__ void __launch_bounds__(128) gate_cumsum_fwd_kernel(const MkdaGateFwd 
     const float E = p.A_log ? expf(p.A_log[h]) : 1.f;
     float4 bias = splat4(0.f);
     if (p.dt_bias) bias = p.scalar_gate ? splat4(p.dt_bias[h]) : *reinterpret_cast<const float4*>(p.dt_bias + h * 128 + 4 * lane);
-    float4 run = splat4(0.f);
     float4 vals[16];
+    // all 16 rows of this warp are requested before the first one is used (rows past the end re-read the last one)
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+        const int row = warp * 16 + r, rr = row < len ? row : len - 1;
+        const size_t th = (size_t)(start + rr) * HV + h;
+        vals[r] = p.scalar_gate ? splat4(ld1(p.x, XDT, th)) : ld4(p.x, XDT, th * 128 + 4 * lane);
+    }
+    float4 run = splat4(0.f);
 #pragma unroll
     for (int r = 0; r < 16; ++r) {
         const int row = warp * 16 + r;
         float4 gv = splat4(0.f);
         if (row < len) {
-            const size_t th = (size_t)(start + row) * HV + h;
-            float4 xv = p.scalar_gate ? splat4(ld1(p.x, p.x_dtype, th)) : ld4(p.x, p.x_dtype, th * 128 + 4 * lane);
-            xv = add4(xv, bias);
+            const float4 xv = add4(vals[r], bias);
             gv.x = gate_value(p.mode, xv.x, E, p.lower_bound);
             gv.y = gate_value(p.mode, xv.y, E, p.lower_bound);
             gv.z = gate_value(p.mode, xv.z, E, p.lower_bound);
@@ -99,56 +105,65 @@ __global__ void __launch_bounds__(128) gate_cumsum_fwd_kernel(const MkdaGateFwd 
 // ---------------------------------------------------------------------------------------------------------
 // backward: same tiling; suffix sums instead of prefix sums.
 // ---------------------------------------------------------------------------------------------------------
+// CTA (g, h) walks chunks g, g + gridDim.x, ... and keeps the parameter-gradient partials in registers, so the second
+// stage only has gridDim.x rows to add (fixed assignment and order: deterministic).
+template <int XDT>
 __global__ void __launch_bounds__(128) gate_bwd_kernel(const MkdaGateBwd p) {
-    const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV;
-    const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+    const int h = blockIdx.y, HV = p.L.HV;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     __shared__ float4 tot[4][32];
     __shared__ float4 red[2][4][32];
-    float4 vals[16];
-    float4 run = splat4(0.f);
-#pragma unroll
-    for (int r = 15; r >= 0; --r) {
-        const int row = warp * 16 + r;
-        float4 v = splat4(0.f);
-        if (row < len) v = *reinterpret_cast<const float4*>(p.dgp + ((size_t)(start + row) * HV + h) * 128 + 4 * lane);
-        run = add4(run, v);
-        vals[r] = run;
-    }
-    tot[warp][lane] = run;
-    __syncthreads();
-    float4 post = splat4(0.f);
-    for (int w = 3; w > warp; --w) post = add4(post, tot[w][lane]);
     const float E = p.A_log ? expf(p.A_log[h]) : 1.f;
     float4 bias = splat4(0.f);
     if (p.dt_bias) bias = p.scalar_gate ? splat4(p.dt_bias[h]) : *reinterpret_cast<const float4*>(p.dt_bias + h * 128 + 4 * lane);
     float4 pa = splat4(0.f), pb = splat4(0.f);
+    for (int c = blockIdx.x; c < p.L.NC; c += gridDim.x) {
+        const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+        float4 vals[16], xs[16];
 #pragma unroll
-    for (int r = 0; r < 16; ++r) {
-        const int row = warp * 16 + r;
-        if (row >= len) continue;                       // warp-uniform
-        const size_t th = (size_t)(start + row) * HV + h;
-        float4 dg = add4(vals[r], post);
-        if (p.scalar_gate) {
-            const float dgs = warp_sum(hsum4(dg));
-            const float s = ld1(p.x, p.x_dtype, th) + bias.x;
-            float ds, dA;
-            gate_grad(p.mode, s, E, p.lower_bound, ds, dA);
-            const float dxs = dgs * ds;
-            if (lane == 0) st1(p.dx, p.dx_dtype, th, dxs);
-            pb.x += dxs;
-            pa.x += dgs * dA;
-        } else {
-            float4 xv = add4(ld4(p.x, p.x_dtype, th * 128 + 4 * lane), bias);
-            float4 ds, dA;
-            gate_grad(p.mode, xv.x, E, p.lower_bound, ds.x, dA.x);
-            gate_grad(p.mode, xv.y, E, p.lower_bound, ds.y, dA.y);
-            gate_grad(p.mode, xv.z, E, p.lower_bound, ds.z, dA.z);
-            gate_grad(p.mode, xv.w, E, p.lower_bound, ds.w, dA.w);
-            const float4 dxv = mul4(dg, ds);
-            st4(p.dx, p.dx_dtype, th * 128 + 4 * lane, dxv);
-            pb = add4(pb, dxv);
-            pa = add4(pa, mul4(dg, dA));
+        for (int r = 0; r < 16; ++r) {
+            const int row = warp * 16 + r, rr = row < len ? row : len - 1;
+            const size_t th = (size_t)(start + rr) * HV + h;
+            vals[r] = *reinterpret_cast<const float4*>(p.dgp + th * 128 + 4 * lane);
+            xs[r] = p.scalar_gate ? splat4(ld1(p.x, XDT, th)) : ld4(p.x, XDT, th * 128 + 4 * lane);
+        }
+        float4 run = splat4(0.f);
+#pragma unroll
+        for (int r = 15; r >= 0; --r) {
+            if (warp * 16 + r < len) run = add4(run, vals[r]);
+            vals[r] = run;
+        }
+        __syncthreads();                                   // previous chunk's readers of tot are done
+        tot[warp][lane] = run;
+        __syncthreads();
+        float4 post = splat4(0.f);
+        for (int w = 3; w > warp; --w) post = add4(post, tot[w][lane]);
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const int row = warp * 16 + r;
+            if (row >= len) continue;                       // warp-uniform
+            const size_t th = (size_t)(start + row) * HV + h;
+            const float4 dg = add4(vals[r], post);
+            if (p.scalar_gate) {
+                const float dgs = warp_sum(hsum4(dg));
+                float ds, dA;
+                gate_grad(p.mode, xs[r].x + bias.x, E, p.lower_bound, ds, dA);
+                const float dxs = dgs * ds;
+                if (lane == 0) st1(p.dx, p.dx_dtype, th, dxs);
+                pb.x += dxs;
+                pa.x += dgs * dA;
+            } else {
+                const float4 xv = add4(xs[r], bias);
+                float4 ds, dA;
+                gate_grad(p.mode, xv.x, E, p.lower_bound, ds.x, dA.x);
+                gate_grad(p.mode, xv.y, E, p.lower_bound, ds.y, dA.y);
+                gate_grad(p.mode, xv.z, E, p.lower_bound, ds.z, dA.z);
+                gate_grad(p.mode, xv.w, E, p.lower_bound, ds.w, dA.w);
+                const float4 dxv = mul4(dg, ds);
+                st4(p.dx, p.dx_dtype, th * 128 + 4 * lane, dxv);
+                pb = add4(pb, dxv);
+                pa = add4(pa, mul4(dg, dA));
+            }
         }
     }
     if (!p.part_bias && !p.part_alog) return;
@@ -158,7 +173,7 @@ __global__ void __launch_bounds__(128) gate_bwd_kernel(const MkdaGateBwd p) {
     if (warp == 0) {
         float4 sb = red[0][0][lane], sa = red[1][0][lane];
         for (int w = 1; w < 4; ++w) { sb = add4(sb, red[0][w][lane]); sa = add4(sa, red[1][w][lane]); }
-        const size_t ch = (size_t)c * HV + h;
+        const size_t ch = (size_t)blockIdx.x * HV + h;
         if (p.scalar_gate) {
             if (lane == 0) {
                 if (p.part_bias) p.part_bias[ch] = sb.x;
@@ -288,14 +303,29 @@ extern "C" int mkda_gate_cumsum_fwd(const MkdaGateFwd* p, void* stream) {
     if (p->mode != MKDA_GATE_PRECOMPUTED && !(p->lower_bound < 0.f)) return set_error(MKDA_ERR_ARG, "gate_cumsum_fwd: lower_bound must be < 0");
     if (p->beta_raw && !p->beta_out) return set_error(MKDA_ERR_ARG, "gate_cumsum_fwd: beta_out missing");
     if (p->L.NC == 0) return MKDA_OK;
-    gate_cumsum_fwd_kernel<<<dim3(p->L.NC, p->L.HV), 128, 0, (cudaStream_t)stream>>>(*p);
+    const dim3 grid(p->L.NC, p->L.HV);
+    switch (p->x_dtype) {
+        case MKDA_F32: gate_cumsum_fwd_kernel<MKDA_F32><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
+        case MKDA_BF16: gate_cumsum_fwd_kernel<MKDA_BF16><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
+        case MKDA_F16: gate_cumsum_fwd_kernel<MKDA_F16><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
+        default: return set_error(MKDA_ERR_ARG, "gate_cumsum_fwd: unsupported dtype");
+    }
     return check_launch("gate_cumsum_fwd");
 }
 
 extern "C" int mkda_gate_bwd(const MkdaGateBwd* p, void* stream) {
     if (!p || !p->x || !p->dgp || !p->dx) return set_error(MKDA_ERR_ARG, "gate_bwd: null argument");
     if (p->L.NC == 0) return MKDA_OK;
-    gate_bwd_kernel<<<dim3(p->L.NC, p->L.HV), 128, 0, (cudaStream_t)stream>>>(*p);
+    if (p->part_rows < 1) return set_error(MKDA_ERR_ARG, "gate_bwd: part_rows must be >= 1");
+    const dim3 grid(p->part_rows < p->L.NC ? p->part_rows : p->L.NC, p->L.HV);
+    if ((p->part_bias || p->part_alog) && (int)grid.x != p->part_rows)
+        return set_error(MKDA_ERR_ARG, "gate_bwd: part_rows must not exceed the number of chunks when partials are requested");
+    switch (p->x_dtype) {
+        case MKDA_F32: gate_bwd_kernel<MKDA_F32><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
+        case MKDA_BF16: gate_bwd_kernel<MKDA_BF16><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
+        case MKDA_F16: gate_bwd_kernel<MKDA_F16><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
+        default: return set_error(MKDA_ERR_ARG, "gate_bwd: unsupported dtype");
+    }
     return check_launch("gate_bwd");
 }
 

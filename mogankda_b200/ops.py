@@ -103,17 +103,19 @@ def gate_bwd(lay, x, dgp, mode, A_log, dt_bias, lower_bound, HV, want_bias, want
     p.lower_bound = -3.0e38 if lower_bound is None else float(lower_bound)
     p.dgp, p.dx, p.dx_dtype = _ptr(dgp, torch.float32), _ptr(dx), _dt(dx)
     width = HV if scalar else HV * 128
+    rows = max(1, min(lay.NC, 64))
+    p.part_rows = rows
     part_b = part_a = None
     if mode != "precomputed":
         if want_bias:
-            part_b = torch.empty(lay.NC, width, dtype=torch.float32, device=x.device)
+            part_b = torch.empty(rows, width, dtype=torch.float32, device=x.device)
             p.part_bias = _ptr(part_b)
         if want_alog:
-            part_a = torch.empty(lay.NC, width, dtype=torch.float32, device=x.device)
+            part_a = torch.empty(rows, width, dtype=torch.float32, device=x.device)
             p.part_alog = _ptr(part_a)
     _lib.call("mkda_gate_bwd", p, _stream())
-    d_bias = reduce_partials(part_b, lay.NC, width) if part_b is not None else None
-    d_alog = reduce_partials(part_a, lay.NC, width, 1 if scalar else 128) if part_a is not None else None
+    d_bias = reduce_partials(part_b, rows, width) if part_b is not None else None
+    d_alog = reduce_partials(part_a, rows, width, 1 if scalar else 128) if part_a is not None else None
     return dx, d_bias, d_alog
 
 
