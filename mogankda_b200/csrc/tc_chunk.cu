@@ -80,6 +80,13 @@ __device__ __forceinline__ void scale8(float (&v)[8], float m) {
     for (int e = 0; e < 8; ++e) v[e] *= m;
 }
 
+#ifdef MKDA_TRACE
+__device__ long long g_trace[64];
+#define TRACE(i) do { if (blockIdx.x == 200 && blockIdx.y == 3 && threadIdx.x == 0) g_trace[i] = clock64(); } while (0)
+#else
+#define TRACE(i) do {} while (0)
+#endif
+
 struct TcShared {
     uint64_t bar;
     uint32_t tmem;
@@ -205,6 +212,9 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
     tc_end(&sh, tmem, 64);
 }
 
+#ifdef MKDA_TRACE
+extern "C" int mkda_trace_read(long long* out) { return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 64) == cudaSuccess ? 0 : -1; }
+#endif
 int tc_chunk_status(unsigned int* out) {
     return cudaMemcpyFromSymbol(out, umma::g_timeout_flag, sizeof(unsigned int)) == cudaSuccess ? 0 : -1;
 }
@@ -246,6 +256,7 @@ __global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad
     __shared__ uint64_t bar2;
     __shared__ float sDgl[DK];
     __shared__ float sCol[4][DK];
+    TRACE(0);
     uint8_t* base = tc_begin(smem_raw, &sh, 256);
     uint8_t* sSh = base;
     uint8_t* sSl = sSh + tile_bytes(128, 128);
@@ -277,11 +288,14 @@ __global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad
         load_chunks<4, 512, true>(vS, 128, 128, [&](int r, int k8, float (&v)[8]) { load8(p.h, MKDA_F32, sbase + (size_t)r * DV + k8 * 8, v); });
         load_chunks<2, 512, true>(vO, 64, 128, rows(p.d_o, std::integral_constant<int, DODT>{}));
         load_chunks<2, 512, true>(vX, 64, 128, rows(p.dX, F32T{}));
+        TRACE(1);
         store_chunks<4, 512, true>(sSh, sSl, vS, 128, 128);
         store_chunks<2, 512, true>(sOh, sOl, vO, 64, 128);
         store_chunks<2, 512, true>(sXh, sXl, vX, 64, 128);
     }
+    TRACE(2);
     const uint32_t tmem = tc_operands_ready(&sh);
+    TRACE(3);
     if (tid == 0) {
         const umma::Opnd aS = umma::opnd_k(sSh, sSl, 128);
         umma::gemm(tmem + 0, aS, umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
@@ -310,8 +324,11 @@ __global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad
             for (int o = 8; o > 0; o >>= 1) pr += __shfl_xor_sync(0xffffffffu, pr, o);
             if ((lane & 15) == 0) sDgl[r] = pr;
         }
+        TRACE(4);
         store_chunks<4, 512, true>(sDh, sDl, vD, 128, 128);
-        umma::mbar_wait(&sh.bar, 0);          // S dO^T and S dX^T done: the dO tile can be replaced by Vd
+        TRACE(5);
+        umma::mbar_wait(&sh.bar, 0);
+        TRACE(6);          // S dO^T and S dX^T done: the dO tile can be replaced by Vd
         umma::fence_after_sync();
         store_chunks<2, 512, true>(sOh, sOl, vV, 64, 128);
     }
@@ -335,8 +352,10 @@ __global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad
         qv[j] = ld1(p.q, QKDT, tk * 128 + kk) * (p.q_rstd ? p.q_rstd[tk] : 1.f);
         gv[j] = p.g_c[((size_t)(start + t) * HV + h) * 128 + kk];
     }
+    TRACE(7);
     umma::mbar_wait(&bar2, 0);
     umma::fence_after_sync();
+    TRACE(8);
 
     // ---- epilogue: thread = K index kk, 16 tokens per warp group ---------------------------------------------------
     float aq[16], ak[16], ab[16];
@@ -347,6 +366,7 @@ __global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad
 #pragma unroll
     for (int j = 0; j < 16; ++j)
         if (t0 + j < len) cs += kv[j] * exp2f(gL - gv[j]) * ab[j];
+    TRACE(9);
     sCol[warp >> 2][kk] = cs;
     __syncthreads();
     const float extra = ((sCol[0][kk] + sCol[1][kk]) + (sCol[2][kk] + sCol[3][kk])) + exp2f(gL) * sDgl[kk];
@@ -363,7 +383,9 @@ __global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad
         p.dk_p[off] = dkt * up + dkb * re;
         p.dg_p[off] = dg;
     }
+    TRACE(10);
     tc_end(&sh, tmem, 256);
+    TRACE(11);
 }
 
 template <int QKDT, int DODT>
