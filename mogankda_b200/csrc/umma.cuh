@@ -30,15 +30,20 @@ __device__ __forceinline__ uint32_t tile_chunk_offset(int R, int r, int k8) {   
 __host__ __device__ constexpr int tile_bytes(int R, int KT) { return R * KT * 2; }
 
 // split 8 fp32 values into bf16 hi / lo chunks and store them at (row r, chunk k8) of the two tiles
+// two fp32 -> packed bf16x2 (lower half = a), one instruction
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+    return r;
+}
 __device__ __forceinline__ void store_split8(uint8_t* hi, uint8_t* lo, int R, int r, int k8, const float (&v)[8]) {
     uint32_t h[4], l[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const __nv_bfloat16 a = __float2bfloat16_rn(v[2 * i]), b = __float2bfloat16_rn(v[2 * i + 1]);
-        const __nv_bfloat16 c = __float2bfloat16_rn(v[2 * i] - __bfloat162float(a));
-        const __nv_bfloat16 d = __float2bfloat16_rn(v[2 * i + 1] - __bfloat162float(b));
-        h[i] = (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
-        l[i] = (uint32_t)__bfloat16_as_ushort(c) | ((uint32_t)__bfloat16_as_ushort(d) << 16);
+        h[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+        const float ra = v[2 * i] - __uint_as_float(h[i] << 16);
+        const float rb = v[2 * i + 1] - __uint_as_float(h[i] & 0xffff0000u);
+        l[i] = pack_bf16x2(ra, rb);
     }
     const uint32_t off = tile_chunk_offset(R, r, k8);
     *reinterpret_cast<uint4*>(hi + off) = make_uint4(h[0], h[1], h[2], h[3]);
