@@ -159,6 +159,13 @@ __device__ __forceinline__ void zero_acc(float (&acc)[NT][4]) {
     for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 }
 
+// 2^x in one MUFU instruction (max relative error ~2^-22); used where 2^x scales tensor-core operands
+__device__ __forceinline__ float ex2f_(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
 // stable scalar math (fp32, precise library versions)
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplusf_(float s) { return fmaxf(s, 0.f) + log1pf(expf(-fabsf(s))); }

@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
         load8(p.g_c, MKDA_F32, th * 128 + k8 * 8, g);
         const float m = p.scale * (p.q_rstd ? p.q_rstd[tk] : 1.f);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] *= m * exp2f(g[e]);
+        for (int e = 0; e < 8; ++e) v[e] *= m * ex2f_(g[e]);
     });
     // A2(v, j) = Vd[j][v]
     stage_along_rows<512>(a2h, a2l, 128, 64, [&](int r, int k8, float (&v)[8]) {
@@ -365,17 +365,17 @@ __global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad
     float cs = 0.f;
 #pragma unroll
     for (int j = 0; j < 16; ++j)
-        if (t0 + j < len) cs += kv[j] * exp2f(gL - gv[j]) * ab[j];
+        if (t0 + j < len) cs += kv[j] * ex2f_(gL - gv[j]) * ab[j];
     TRACE(9);
     sCol[warp >> 2][kk] = cs;
     __syncthreads();
-    const float extra = ((sCol[0][kk] + sCol[1][kk]) + (sCol[2][kk] + sCol[3][kk])) + exp2f(gL) * sDgl[kk];
+    const float extra = ((sCol[0][kk] + sCol[1][kk]) + (sCol[2][kk] + sCol[3][kk])) + ex2f_(gL) * sDgl[kk];
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
         const int t = t0 + j;
         if (t >= len) continue;
         const size_t off = ((size_t)(start + t) * HV + h) * 128 + kk;
-        const float up = exp2f(gv[j]), re = exp2f(gL - gv[j]);
+        const float up = ex2f_(gv[j]), re = ex2f_(gL - gv[j]);
         const float dqt = p.scale * aq[j], dkt = -ak[j], dkb = ab[j];
         float dg = qv[j] * up * dqt + kv[j] * up * dkt - kv[j] * re * dkb;
         if (t == len - 1) dg += extra;
@@ -479,7 +479,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
             const int rr = r < len ? r : len - 1;
             const float rk = r < len ? (p.k_rstd ? p.k_rstd[(size_t)(start + rr) * HK + hk] : 1.f) : 0.f;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) vK[n][e] *= rk * exp2f(vG[n][e]);
+            for (int e = 0; e < 8; ++e) vK[n][e] *= rk * ex2f_(vG[n][e]);
         }
         store_chunks<2, 512, true>(sKh, sKl, vK, 64, 128);
         {

@@ -145,17 +145,17 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         float ga[8], t8[8];
         lds8(sG + (16 * I0) * 128 + k8 * 8, ga);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * exp2f(vg[n][e] - ga[e]);
+        for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(vg[n][e] - ga[e]);
         store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + (r & 15), k8, t8);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) t8[e] = vq[n][e] * exp2f(vg[n][e] - ga[e]);
+        for (int e = 0; e < 8; ++e) t8[e] = vq[n][e] * ex2f_(vg[n][e] - ga[e]);
         store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + 16 + (r & 15), k8, t8);
 #pragma unroll
         for (int I = 0; I < 4; ++I) {
             if (I < I0) continue;
             if (I > I0) lds8(sG + (16 * I) * 128 + k8 * 8, ga);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * exp2f(ga[e] - vg[n][e]);
+            for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(ga[e] - vg[n][e]);
             store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
         }
     }
@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         const float b = sh.beta[r];          // 0 for rows past the end
         float t8[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) t8[e] = b * vk[n][e] * exp2f(vg[n][e]);
+        for (int e = 0; e < 8; ++e) t8[e] = b * vk[n][e] * ex2f_(vg[n][e]);
         store_split8(sBk, sBk + 16384, 64, r, k8, t8);
 #pragma unroll
         for (int e = 0; e < 8; ++e) t8[e] = b * vv[n][e];
@@ -311,17 +311,17 @@ __global__ void __launch_bounds__(512, 1) bwd_intra_tc_kernel(const MkdaBwdIntra
         float ga[8], t8[8];
         lds8(sG + (16 * I0) * 128 + k8 * 8, ga);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * exp2f(vg[n][e] - ga[e]);
+        for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(vg[n][e] - ga[e]);
         store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + (r & 15), k8, t8);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) t8[e] = vq[n][e] * exp2f(vg[n][e] - ga[e]);
+        for (int e = 0; e < 8; ++e) t8[e] = vq[n][e] * ex2f_(vg[n][e] - ga[e]);
         store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + 16 + (r & 15), k8, t8);
 #pragma unroll
         for (int I = 0; I < 4; ++I) {
             if (I < I0) continue;
             if (I > I0) lds8(sG + (16 * I) * 128 + k8 * 8, ga);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * exp2f(ga[e] - vg[n][e]);
+            for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(ga[e] - vg[n][e]);
             store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
         }
     }
@@ -385,12 +385,12 @@ __global__ void __launch_bounds__(512, 1) bwd_intra_tc_kernel(const MkdaBwdIntra
         float c16[16];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + 64 * I + 16 * cg), c16);
 #pragma unroll
-        for (int r = 0; r < 16; ++r) dkc[r] += c16[r] * exp2f(ga[I] - gg[r]);
+        for (int r = 0; r < 16; ++r) dkc[r] += c16[r] * ex2f_(ga[I] - gg[r]);
     }
 #pragma unroll
     for (int r = 0; r < 16; ++r) {
         const int i = 16 * cg + r;
-        const float e = exp2f(gg[r] - ga[cg]);
+        const float e = ex2f_(gg[r] - ga[cg]);
         const float dqr = v[r] * e, T = v[16 + r] * e, bt = sh.beta[i], dgn = sDiag[i];
         float bs = kq[r] * T;
 #pragma unroll

@@ -116,11 +116,11 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
             const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
             const float m = r < len ? rs[n] : 0.f;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) k[n][e] *= m * exp2f(gL[n][e] - g[n][e]);
+            for (int e = 0; e < 8; ++e) k[n][e] *= m * ex2f_(gL[n][e] - g[n][e]);
             store_split8(sK[buf], sK[buf] + 16384, 64, r, k8, k[n]);
             if (r == 0) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) sh.gl[buf][k8 * 8 + e] = exp2f(gL[n][e]);
+                for (int e = 0; e < 8; ++e) sh.gl[buf][k8 * 8 + e] = ex2f_(gL[n][e]);
             }
         }
     };
@@ -342,14 +342,14 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
                 const float mk = r < len ? rk[n] : 0.f, mq = r < len ? rq[n] : 0.f;
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    vk[n][e] *= mk * exp2f(vl[n][e] - vg[n][e]);
-                    vq[n][e] *= mq * exp2f(vg[n][e]);
+                    vk[n][e] *= mk * ex2f_(vl[n][e] - vg[n][e]);
+                    vq[n][e] *= mq * ex2f_(vg[n][e]);
                 }
                 store_split8(sKb, sKb + 16384, 64, r, k8, vk[n]);
                 store_split8(sQs, sQs + 16384, 64, r, k8, vq[n]);
                 if (r == 0) {
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) sh.gl[0][k8 * 8 + e] = exp2f(vl[n][e]);
+                    for (int e = 0; e < 8; ++e) sh.gl[0][k8 * 8 + e] = ex2f_(vl[n][e]);
                 }
             }
         }
