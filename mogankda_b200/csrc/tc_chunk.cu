@@ -80,13 +80,6 @@ __device__ __forceinline__ void scale8(float (&v)[8], float m) {
     for (int e = 0; e < 8; ++e) v[e] *= m;
 }
 
-#ifdef MKDA_TRACE
-__device__ long long g_trace[64];
-#define TRACE(i) do { if (blockIdx.x == 200 && blockIdx.y == 3 && threadIdx.x == 0) g_trace[i] = clock64(); } while (0)
-#else
-#define TRACE(i) do {} while (0)
-#endif
-
 struct TcShared {
     uint64_t bar;
     uint32_t tmem;
@@ -123,6 +116,7 @@ template <int QDT, int GDT>
 __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ TcShared sh;
+    MKDA_TRACE_AT(2, 0);
     uint8_t* base = tc_begin(smem_raw, &sh, 64);
     uint8_t* a1h = base;
     uint8_t* a1l = a1h + tile_bytes(128, 128);
@@ -139,66 +133,81 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
     const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    const float* hc = p.h + ((size_t)c * HV + h) * DK * DV;
-    // A1(v, kidx) = H[kidx][v]
-    stage_along_rows<512>(a1h, a1l, 128, 128, [&](int r, int k8, float (&v)[8]) {
+    const size_t sbase = ((size_t)c * HV + h) * DK * DV;
+    {   // every tile is staged untransposed; the transposes come from MN-major operand views
+        float vH[4][8], vQ[2][8], vG[2][8], vV[2][8], vA[1][8];
+        load_chunks<4, 512, true>(vH, 128, 128, [&](int r, int k8, float (&v)[8]) { load8(p.h, MKDA_F32, sbase + (size_t)r * DV + k8 * 8, v); });
+        load_chunks<2, 512, true>(vQ, 64, 128, [&](int r, int k8, float (&v)[8]) {
+            const int rr = r < len ? r : len - 1;
+            load8(p.q, QDT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, v);
+        });
+        load_chunks<2, 512, true>(vG, 64, 128, [&](int r, int k8, float (&v)[8]) {
+            const int rr = r < len ? r : len - 1;
+            load8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, v);
+        });
+        load_chunks<2, 512, true>(vV, 64, 128, [&](int r, int k8, float (&v)[8]) {
+            const int rr = r < len ? r : len - 1;
+            load8(p.Vd, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, v);
+            if (r >= len) zero8(v);
+        });
+        load_chunks<1, 512, true>(vA, 64, 64, [&](int r, int k8, float (&v)[8]) {
+            const int rr = r < len ? r : len - 1;
+            load8(p.Aqk, MKDA_F32, ((size_t)(start + rr) * HV + h) * 64 + k8 * 8, v);
+            if (r >= len) zero8(v);
+        });
+        store_chunks<4, 512, true>(a1h, a1l, vH, 128, 128);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = hc[(size_t)(k8 * 8 + e) * DV + r];
-    });
-    // B1(tok, kidx) = scale q rstd 2^g
-    stage_along_k<512>(b1h, b1l, 64, 128, [&](int r, int k8, float (&v)[8]) {
-        if (r >= len) { zero8(v); return; }
-        const size_t th = (size_t)(start + r) * HV + h, tk = (size_t)(start + r) * HK + hk;
-        load8(p.q, QDT, tk * 128 + k8 * 8, v);
-        float g[8];
-        load8(p.g_c, MKDA_F32, th * 128 + k8 * 8, g);
-        const float m = p.scale * (p.q_rstd ? p.q_rstd[tk] : 1.f);
+        for (int n = 0; n < 2; ++n) {
+            const int r = (tid + n * 512) >> 4, rr = r < len ? r : len - 1;
+            const float m = r < len ? p.scale * (p.q_rstd ? p.q_rstd[(size_t)(start + rr) * HK + hk] : 1.f) : 0.f;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] *= m * ex2f_(g[e]);
-    });
-    // A2(v, j) = Vd[j][v]
-    stage_along_rows<512>(a2h, a2l, 128, 64, [&](int r, int k8, float (&v)[8]) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const int j = k8 * 8 + e;
-            v[e] = j < len ? p.Vd[((size_t)(start + j) * HV + h) * 128 + r] : 0.f;
+            for (int e = 0; e < 8; ++e) vQ[n][e] *= m * ex2f_(vG[n][e]);
         }
-    });
-    // B2(i, j) = Aqk[i][j]
-    stage_along_k<512>(b2h, b2l, 64, 64, [&](int r, int k8, float (&v)[8]) {
-        if (r >= len) { zero8(v); return; }
-        load8(p.Aqk, MKDA_F32, ((size_t)(start + r) * HV + h) * 64 + k8 * 8, v);
-    });
+        store_chunks<2, 512, true>(b1h, b1l, vQ, 64, 128);
+        store_chunks<2, 512, true>(a2h, a2l, vV, 64, 128);
+        store_chunks<1, 512, true>(b2h, b2l, vA, 64, 64);
+    }
+    MKDA_TRACE_AT(2, 1);
     const uint32_t tmem = tc_operands_ready(&sh);
+    MKDA_TRACE_AT(2, 2);
     if (tid == 0) {
-        const uint32_t idesc = umma::idesc_bf16(128, 64);
-        umma::gemm_split(tmem, smem_u32(a1h), smem_u32(a1l), 128, smem_u32(b1h), smem_u32(b1l), 64, 128, idesc, 0u);
-        umma::gemm_split(tmem, smem_u32(a2h), smem_u32(a2l), 128, smem_u32(b2h), smem_u32(b2l), 64, 64, idesc, 1u);
+        umma::gemm(tmem, umma::opnd_mn(a1h, a1l, 128), umma::opnd_k(b1h, b1l, 64), 128, 64, 128, 0u);
+        umma::gemm(tmem, umma::opnd_mn(a2h, a2l, 64), umma::opnd_k(b2h, b2l, 64), 128, 64, 64, 1u);
         umma::commit(&sh.bar);
+    }
+    // the row pass (warp w owns rows w, w + 16, ...) fetches its gate values while the products run
+    float4 w = make_float4(1.f, 1.f, 1.f, 1.f), zg[4];
+    if (p.has_norm && p.norm_w) w = ld4(p.norm_w, p.norm_w_dtype, 4 * lane);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = warp + 16 * i, rr = r < len ? r : len - 1;
+        zg[i] = p.has_norm ? ld4(p.gate, GDT, ((size_t)(start + rr) * HV + h) * 128 + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     umma::mbar_wait(&sh.bar, 0);
     umma::fence_after_sync();
-    if (warp < 8) {   // TMEM [v lanes][tok cols] -> shared [tok][v]
-        float v[32];
-        const int t0 = (warp >> 2) * 32, vi = (warp & 3) * 32 + lane;
-        umma::tmem_ld32(umma::tmem_addr(tmem, warp, t0), v);
+    MKDA_TRACE_AT(2, 3);
+    {   // TMEM [v lanes][tok cols] -> shared [tok][v]
+        float v[16];
+        const int t0 = (warp >> 2) * 16, vi = (warp & 3) * 32 + lane;
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, t0), v);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) sO[(t0 + j) * OLD + vi] = v[j];
+        for (int j = 0; j < 16; ++j) sO[(t0 + j) * OLD + vi] = v[j];
     }
     __syncthreads();
-    float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
-    if (p.has_norm && p.norm_w) w = ld4(p.norm_w, p.norm_w_dtype, 4 * lane);
-    for (int r = warp; r < len; r += 16) {
+    MKDA_TRACE_AT(2, 4);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = warp + 16 * i;
+        if (r >= len) continue;                                   // warp-uniform
         float4 o = *reinterpret_cast<const float4*>(sO + r * OLD + 4 * lane);
         const size_t off = ((size_t)(start + r) * HV + h) * 128 + 4 * lane;
         if (p.o_raw) *reinterpret_cast<float4*>(p.o_raw + off) = o;
         if (p.has_norm) {
             float ss = (o.x * o.x + o.y * o.y) + (o.z * o.z + o.w * o.w);
 #pragma unroll
-            for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+            for (int sft = 16; sft > 0; sft >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, sft);
             const float rs = 1.f / sqrtf(ss * (1.f / 128.f) + p.eps);
-            const float4 z = ld4(p.gate, GDT, off);
-            const float zz[4] = {z.x, z.y, z.z, z.w};
+            const float zz[4] = {zg[i].x, zg[i].y, zg[i].z, zg[i].w};
             float a[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -209,11 +218,13 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
         }
         st4(p.out, p.out_dtype, off, o);
     }
+    MKDA_TRACE_AT(2, 5);
     tc_end(&sh, tmem, 64);
+    MKDA_TRACE_AT(2, 6);
 }
 
 #ifdef MKDA_TRACE
-extern "C" int mkda_trace_read(long long* out) { return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 64) == cudaSuccess ? 0 : -1; }
+extern "C" int mkda_trace_read_chunk(long long* out) { return cudaMemcpyFromSymbol(out, umma::g_trace, sizeof(long long) * 8 * 24) == cudaSuccess ? 0 : -1; }
 #endif
 int tc_chunk_status(unsigned int* out) {
     return cudaMemcpyFromSymbol(out, umma::g_timeout_flag, sizeof(unsigned int)) == cudaSuccess ? 0 : -1;
@@ -256,7 +267,7 @@ __global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad
     __shared__ uint64_t bar2;
     __shared__ float sDgl[DK];
     __shared__ float sCol[4][DK];
-    TRACE(0);
+    MKDA_TRACE_AT(0, 0);
     uint8_t* base = tc_begin(smem_raw, &sh, 256);
     uint8_t* sSh = base;
     uint8_t* sSl = sSh + tile_bytes(128, 128);
@@ -288,14 +299,14 @@ __global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad
         load_chunks<4, 512, true>(vS, 128, 128, [&](int r, int k8, float (&v)[8]) { load8(p.h, MKDA_F32, sbase + (size_t)r * DV + k8 * 8, v); });
         load_chunks<2, 512, true>(vO, 64, 128, rows(p.d_o, std::integral_constant<int, DODT>{}));
         load_chunks<2, 512, true>(vX, 64, 128, rows(p.dX, F32T{}));
-        TRACE(1);
+        MKDA_TRACE_AT(0, 1);
         store_chunks<4, 512, true>(sSh, sSl, vS, 128, 128);
         store_chunks<2, 512, true>(sOh, sOl, vO, 64, 128);
         store_chunks<2, 512, true>(sXh, sXl, vX, 64, 128);
     }
-    TRACE(2);
+    MKDA_TRACE_AT(0, 2);
     const uint32_t tmem = tc_operands_ready(&sh);
-    TRACE(3);
+    MKDA_TRACE_AT(0, 3);
     if (tid == 0) {
         const umma::Opnd aS = umma::opnd_k(sSh, sSl, 128);
         umma::gemm(tmem + 0, aS, umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
@@ -324,11 +335,11 @@ __global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad
             for (int o = 8; o > 0; o >>= 1) pr += __shfl_xor_sync(0xffffffffu, pr, o);
             if ((lane & 15) == 0) sDgl[r] = pr;
         }
-        TRACE(4);
+        MKDA_TRACE_AT(0, 4);
         store_chunks<4, 512, true>(sDh, sDl, vD, 128, 128);
-        TRACE(5);
+        MKDA_TRACE_AT(0, 5);
         umma::mbar_wait(&sh.bar, 0);
-        TRACE(6);          // S dO^T and S dX^T done: the dO tile can be replaced by Vd
+        MKDA_TRACE_AT(0, 6);          // S dO^T and S dX^T done: the dO tile can be replaced by Vd
         umma::fence_after_sync();
         store_chunks<2, 512, true>(sOh, sOl, vV, 64, 128);
     }
@@ -352,10 +363,10 @@ __global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad
         qv[j] = ld1(p.q, QKDT, tk * 128 + kk) * (p.q_rstd ? p.q_rstd[tk] : 1.f);
         gv[j] = p.g_c[((size_t)(start + t) * HV + h) * 128 + kk];
     }
-    TRACE(7);
+    MKDA_TRACE_AT(0, 7);
     umma::mbar_wait(&bar2, 0);
     umma::fence_after_sync();
-    TRACE(8);
+    MKDA_TRACE_AT(0, 8);
 
     // ---- epilogue: thread = K index kk, 16 tokens per warp group ---------------------------------------------------
     float aq[16], ak[16], ab[16];
@@ -366,7 +377,7 @@ __global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad
 #pragma unroll
     for (int j = 0; j < 16; ++j)
         if (t0 + j < len) cs += kv[j] * ex2f_(gL - gv[j]) * ab[j];
-    TRACE(9);
+    MKDA_TRACE_AT(0, 9);
     sCol[warp >> 2][kk] = cs;
     __syncthreads();
     const float extra = ((sCol[0][kk] + sCol[1][kk]) + (sCol[2][kk] + sCol[3][kk])) + ex2f_(gL) * sDgl[kk];
@@ -383,9 +394,9 @@ __global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad
         p.dk_p[off] = dkt * up + dkb * re;
         p.dg_p[off] = dg;
     }
-    TRACE(10);
+    MKDA_TRACE_AT(0, 10);
     tc_end(&sh, tmem, 256);
-    TRACE(11);
+    MKDA_TRACE_AT(0, 11);
 }
 
 template <int QKDT, int DODT>
@@ -434,6 +445,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     __shared__ TcShared sh;
     __shared__ float sBeta[CH];
     __shared__ float sRed[2][CH];
+    MKDA_TRACE_AT(1, 0);
     uint8_t* base = tc_begin(smem_raw, &sh, 512);
     uint8_t* sSh = base;                      // S [kidx][v]; later [dO; dVd] [tok][v]
     uint8_t* sSl = sSh + 32768;
@@ -472,6 +484,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
             const int rr = r < len ? r : len - 1;
             load8(p.A, MKDA_F32, ((size_t)(start + rr) * HV + h) * 64 + k8 * 8, v);
         });
+        MKDA_TRACE_AT(1, 1);
         store_chunks<4, 512, true>(sSh, sSl, vS, 128, 128);
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
@@ -492,6 +505,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
             store_split8(sBh, sBl, 64, r, k8, vA[0]);
         }
     }
+    MKDA_TRACE_AT(1, 2);
     const uint32_t tmem = tc_operands_ready(&sh);
     if (tid == 0) {
         umma::gemm(tmem + 0, umma::opnd_mn(sSh, sSl, 128), umma::opnd_k(sKh, sKl, 64), 128, 64, 128, 0u);
@@ -512,8 +526,10 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
             vv[j] = ld1(p.v, KVDT, ((size_t)(start + tt) * HV + h) * 128 + row);
             if (t >= len) vv[j] = 0.f;
         }
+        MKDA_TRACE_AT(1, 3);
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;
         umma::fence_after_sync();
+        MKDA_TRACE_AT(1, 4);
         float d[16], x0[8], x1[8];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, cg * 16), d);
 #pragma unroll
@@ -522,6 +538,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
         store_split8(sXh, sXl, 128, row, 2 * cg + 1, x1);
         store_chunks<4, 512, true>(sSh, sSl, vT, 128, 128);      // S is dead: the region now holds [dO; dVd]
     }
+    MKDA_TRACE_AT(1, 5);
     tc_operands_ready(&sh);
     if (tid == 0) {
         umma::gemm(tmem + 64, umma::opnd_k(sXh, sXl, 128), umma::opnd_k(sBh, sBl, 64), 128, 64, 64, 0u);
@@ -530,6 +547,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     }
     umma::mbar_wait(&sh.bar, phase); phase ^= 1;
     umma::fence_after_sync();
+    MKDA_TRACE_AT(1, 6);
     {
         float vd[16], dw[16], a0[8], a1[8];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 64 + cg * 16), vd);
@@ -547,6 +565,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
         store_split8(sVh, sVl, 128, row, 2 * cg, a0);
         store_split8(sVh, sVl, 128, row, 2 * cg + 1, a1);
     }
+    MKDA_TRACE_AT(1, 7);
     tc_operands_ready(&sh);
     if (tid == 0) {
         umma::gemm(tmem + 128, umma::opnd_k(sSh, sSl, 128), umma::opnd_mn(sVh, sVl, 128), 128, 128, 128, 0u);
@@ -554,6 +573,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     }
     umma::mbar_wait(&sh.bar, phase); phase ^= 1;
     umma::fence_after_sync();
+    MKDA_TRACE_AT(1, 8);
     if (q < 2) {                                   // rows i = row: dAqk = lower(dO Vd^T)
         float d[16];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + cg * 16), d);
@@ -582,6 +602,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
         store_split8(sKh, sKl, 128, i, 2 * cg, a0);
         store_split8(sKh, sKl, 128, i, 2 * cg + 1, a1);
     }
+    MKDA_TRACE_AT(1, 9);
     tc_operands_ready(&sh);
     if (tid < len) p.dbeta_w[(size_t)(start + tid) * HV + h] = sRed[0][tid] + sRed[1][tid];
     if (tid == 0) {
@@ -590,6 +611,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     }
     umma::mbar_wait(&sh.bar, phase); phase ^= 1;
     umma::fence_after_sync();
+    MKDA_TRACE_AT(1, 10);
     if (q < 2) {
         float y[16], a0[8], a1[8];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 320 + cg * 16), y);
@@ -605,6 +627,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     }
     umma::mbar_wait(&sh.bar, phase); phase ^= 1;
     umma::fence_after_sync();
+    MKDA_TRACE_AT(1, 11);
     if (q < 2) {
         float z[16];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 384 + cg * 16), z);      // warp-collective: never under a per-lane condition
@@ -616,7 +639,9 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
                                                               cg * 16 + j + 2 < row ? -z[j + 2] : 0.f, cg * 16 + j + 3 < row ? -z[j + 3] : 0.f);
         }
     }
+    MKDA_TRACE_AT(1, 12);
     tc_end(&sh, tmem, 512);
+    MKDA_TRACE_AT(1, 13);
 }
 
 template <int KVDT, int DODT>

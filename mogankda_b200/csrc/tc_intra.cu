@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
 
+    MKDA_TRACE_AT(3, 0);
     if (warp == 0) umma::tmem_alloc(&sh.tmem, 256);
     if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
     if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
@@ -134,10 +135,12 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
 #pragma unroll
         for (int e = 0; e < 8; ++e) { vk[n][e] *= rk[n]; vq[n][e] *= rq[n]; }
     }
+    MKDA_TRACE_AT(3, 1);
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem = sh.tmem;
+    MKDA_TRACE_AT(3, 2);
     // ---- operands ---------------------------------------------------------------------------------------------------
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
@@ -159,6 +162,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
             store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
         }
     }
+    MKDA_TRACE_AT(3, 3);
     publish();
     if (tid == 0) {
 #pragma unroll
@@ -174,8 +178,10 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
         ldg8(p.v, DT, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vv[n]);
     }
+    MKDA_TRACE_AT(3, 4);
     umma::mbar_wait(&sh.bar, 0);
     umma::fence_after_sync();
+    MKDA_TRACE_AT(3, 5);
     // phase-3 operands over the dead phase-1 tiles: beta k 2^g and beta v (rows past the end are zero)
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
@@ -202,7 +208,9 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         }
     }
     __syncthreads();
+    MKDA_TRACE_AT(3, 6);
     invert_unit_lower(sM, sInv, sh);
+    MKDA_TRACE_AT(3, 7);
     {   // A as the B operand of phase 3, plus the global copies of A and Aqk (full rows, coalesced)
         const int r = tid >> 3, k8 = tid & 7;
         float a8[8];
@@ -223,8 +231,10 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         umma::gemm(tmem + 192, umma::opnd_mn(sBv, sBv + 16384, 64), bA, 128, 64, 64, 0u);
         umma::commit(&sh.bar);
     }
+    MKDA_TRACE_AT(3, 8);
     umma::mbar_wait(&sh.bar, 1);
     umma::fence_after_sync();
+    MKDA_TRACE_AT(3, 9);
     {
         float a[16], b[16];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + 16 * cg), a);
@@ -239,6 +249,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
             }
         }
     }
+    MKDA_TRACE_AT(3, 10);
     umma::fence_before_sync();
     __syncthreads();
     if (warp == 0) umma::tmem_dealloc(tmem, 256);
@@ -272,6 +283,7 @@ __global__ void __launch_bounds__(512, 1) bwd_intra_tc_kernel(const MkdaBwdIntra
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
 
+    MKDA_TRACE_AT(4, 0);
     if (warp == 0) umma::tmem_alloc(&sh.tmem, 512);
     if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
     if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
@@ -301,10 +313,12 @@ __global__ void __launch_bounds__(512, 1) bwd_intra_tc_kernel(const MkdaBwdIntra
 #pragma unroll
         for (int e = 0; e < 8; ++e) { vk[n][e] *= rk[n]; vq[n][e] *= rq[n]; }
     }
+    MKDA_TRACE_AT(4, 1);
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem = sh.tmem;
+    MKDA_TRACE_AT(4, 2);
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
         const int i = tid + n * 512, r = i >> 4, k8 = i & 15, I0 = r >> 4;
@@ -325,6 +339,7 @@ __global__ void __launch_bounds__(512, 1) bwd_intra_tc_kernel(const MkdaBwdIntra
             store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
         }
     }
+    MKDA_TRACE_AT(4, 3);
     __syncthreads();                                   // the cumsum tile is dead: its space becomes the W tiles
     {
         const int i = tid >> 3, k8 = tid & 7;
@@ -343,6 +358,7 @@ __global__ void __launch_bounds__(512, 1) bwd_intra_tc_kernel(const MkdaBwdIntra
         store_split8(sDl, sDl + 8192, 64, i, k8, d8);
         store_split8(sBd, sBd + 8192, 64, i, k8, b8);
     }
+    MKDA_TRACE_AT(4, 4);
     publish();
     if (tid == 0) {
 #pragma unroll
@@ -373,8 +389,10 @@ __global__ void __launch_bounds__(512, 1) bwd_intra_tc_kernel(const MkdaBwdIntra
         const int a = 16 * I < len ? 16 * I : len - 1;
         ga[I] = p.g_c[((size_t)(start + a) * HV + h) * 128 + row];
     }
+    MKDA_TRACE_AT(4, 5);
     umma::mbar_wait(&sh.bar, 0);
     umma::fence_after_sync();
+    MKDA_TRACE_AT(4, 6);
     float v[32], dkc[16];
     umma::tmem_ld32(umma::tmem_addr(tmem, warp, 32 * cg), v);
 #pragma unroll
@@ -403,6 +421,7 @@ __global__ void __launch_bounds__(512, 1) bwd_intra_tc_kernel(const MkdaBwdIntra
             p.dgp[off] = pg[r] + qq[r] * dqr + kq[r] * bt * T - kq[r] * dkc[r];
         }
     }
+    MKDA_TRACE_AT(4, 7);
     __syncthreads();
     if (tid < len) {
         const size_t th = (size_t)(start + tid) * HV + h;
@@ -413,6 +432,7 @@ __global__ void __launch_bounds__(512, 1) bwd_intra_tc_kernel(const MkdaBwdIntra
         }
         st1(p.dbeta, p.dbeta_dtype, th, db);
     }
+    MKDA_TRACE_AT(4, 8);
     umma::fence_before_sync();
     __syncthreads();
     if (warp == 0) umma::tmem_dealloc(tmem, 512);
@@ -434,6 +454,9 @@ int launch_bwd_intra_tc(const MkdaBwdIntra* p, cudaStream_t stream) {
     return set_error(MKDA_ERR_ARG, "bwd_intra: unsupported dtype");
 }
 
+#ifdef MKDA_TRACE
+extern "C" int mkda_trace_read_intra(long long* out) { return cudaMemcpyFromSymbol(out, umma::g_trace, sizeof(long long) * 8 * 24) == cudaSuccess ? 0 : -1; }
+#endif
 int tc_intra_status(unsigned int* out) {
     return cudaMemcpyFromSymbol(out, umma::g_timeout_flag, sizeof(unsigned int)) == cudaSuccess ? 0 : -1;
 }

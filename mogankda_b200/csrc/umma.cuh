@@ -17,6 +17,14 @@ namespace umma {
 
 static __device__ unsigned int g_timeout_flag;      // one per translation unit, read back by mkda_device_status()
 
+// Optional phase tracing (development builds with -DMKDA_TRACE): CTA (200, 3) records clock64() at numbered points.
+#ifdef MKDA_TRACE
+static __device__ long long g_trace[8][24];
+#define MKDA_TRACE_AT(k, i) do { if (blockIdx.x == 200 && blockIdx.y == 3 && threadIdx.x == 0) ::mkda::umma::g_trace[k][i] = clock64(); } while (0)
+#else
+#define MKDA_TRACE_AT(k, i) do {} while (0)
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 // ---- operand tiles -------------------------------------------------------------------------------------------
@@ -132,13 +140,24 @@ __device__ __forceinline__ void gemm_split_a(uint32_t tmem_d, uint32_t a_hi, uin
 }
 
 // D[M x N] (+)= A B^T over KT (multiple of 16) with the hi/lo split; products whose lo tile is absent are skipped.
+// The four base descriptors are built once; a k-step only adds its byte offset (>> 4) to the start-address field, so
+// the issuing thread spends a handful of instructions per MMA (KT is a literal at every call site: the loop unrolls).
+__device__ __forceinline__ uint64_t opnd_base_desc(const Opnd& o, uint32_t addr) {
+    return o.mn ? make_desc(addr, o.blk >> 4) : make_desc(addr);
+}
+__device__ __forceinline__ uint32_t opnd_step16(const Opnd& o, int ks) {       // offset of k-step ks in 16-byte units
+    return o.mn ? (uint32_t)(ks * 128) : (uint32_t)(((ks >> 2) * o.blk + (ks & 3) * 32) >> 4);
+}
 __device__ __forceinline__ void gemm(uint32_t tmem_d, const Opnd& a, const Opnd& b, int M, int N, int KT, uint32_t accumulate) {
     const uint32_t idesc = idesc_bf16(M, N, a.mn, b.mn);
+    const uint64_t ah = opnd_base_desc(a, a.hi), al = opnd_base_desc(a, a.lo);
+    const uint64_t bh = opnd_base_desc(b, b.hi), bl = opnd_base_desc(b, b.lo);
+#pragma unroll
     for (int ks = 0; ks < KT / 16; ++ks) {
-        const uint64_t dah = opnd_desc(a, a.hi, ks), dbh = opnd_desc(b, b.hi, ks);
-        if (a.lo) { mma_bf16(tmem_d, opnd_desc(a, a.lo, ks), dbh, idesc, accumulate); accumulate = 1u; }
-        if (b.lo) { mma_bf16(tmem_d, dah, opnd_desc(b, b.lo, ks), idesc, accumulate); accumulate = 1u; }
-        mma_bf16(tmem_d, dah, dbh, idesc, accumulate);
+        const uint32_t ao = opnd_step16(a, ks), bo = opnd_step16(b, ks);
+        if (a.lo) { mma_bf16(tmem_d, al + ao, bh + bo, idesc, accumulate); accumulate = 1u; }
+        if (b.lo) { mma_bf16(tmem_d, ah + ao, bl + bo, idesc, accumulate); accumulate = 1u; }
+        mma_bf16(tmem_d, ah + ao, bh + bo, idesc, accumulate);
         accumulate = 1u;
     }
 }
