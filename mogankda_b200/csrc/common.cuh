@@ -166,9 +166,12 @@ __device__ __forceinline__ float ex2f_(float x) {
     return r;
 }
 
-// stable scalar math (fp32, precise library versions)
-__device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
-__device__ __forceinline__ float softplusf_(float s) { return fmaxf(s, 0.f) + log1pf(expf(-fabsf(s))); }
+// Stable scalar math on the MUFU unit (ex2 / lg2 / rcp approximations, relative error ~1e-7 each, absolute error of
+// softplus < 1e-7): the gate and epilogue kernels evaluate several of these per element and were ALU-bound with the
+// precise library versions.
+__device__ __forceinline__ float expf_(float x) { return ex2f_(x * RCP_LN2); }
+__device__ __forceinline__ float sigmoidf_(float z) { return __fdividef(1.f, 1.f + expf_(-z)); }
+__device__ __forceinline__ float softplusf_(float s) { return fmaxf(s, 0.f) + __log2f(1.f + expf_(-fabsf(s))) * LN2; }
 
 // Chunk geometry shared by all chunk-parallel kernels: flattened first token and number of valid rows.
 struct ChunkGeom {

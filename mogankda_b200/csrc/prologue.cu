@@ -22,7 +22,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 __device__ __forceinline__ float gate_value(int mode, float s, float E, float lb) {
     if (mode == MKDA_GATE_GDN) return fmaxf(-E * softplusf_(s), lb);
     if (mode == MKDA_GATE_KIMI) return lb * sigmoidf_(E * s);
-    if (mode == MKDA_GATE_EDA) return lb + (-lb) * expf(-(E / fabsf(lb)) * softplusf_(s));
+    if (mode == MKDA_GATE_EDA) return lb + (-lb) * expf_(-(E / fabsf(lb)) * softplusf_(s));
     return s;
 }
 // d gate / d s  and  d gate / d A_log
@@ -37,7 +37,7 @@ __device__ __forceinline__ void gate_grad(int mode, float s, float E, float lb, 
         ds = d * E;
         dA = d * u;
     } else if (mode == MKDA_GATE_EDA) {
-        const float sp = softplusf_(s), c = E / fabsf(lb), w = expf(-c * sp), d = lb * w * c;
+        const float sp = softplusf_(s), c = E / fabsf(lb), w = expf_(-c * sp), d = lb * w * c;
         ds = d * sigmoidf_(s);
         dA = d * sp;
     } else {
@@ -119,13 +119,11 @@ __global__ void __launch_bounds__(128) gate_bwd_kernel(const MkdaGateBwd p) {
     float4 pa = splat4(0.f), pb = splat4(0.f);
     for (int c = blockIdx.x; c < p.L.NC; c += gridDim.x) {
         const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
-        float4 vals[16], xs[16];
+        float4 vals[16];
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
             const int row = warp * 16 + r, rr = row < len ? row : len - 1;
-            const size_t th = (size_t)(start + rr) * HV + h;
-            vals[r] = *reinterpret_cast<const float4*>(p.dgp + th * 128 + 4 * lane);
-            xs[r] = p.scalar_gate ? splat4(ld1(p.x, XDT, th)) : ld4(p.x, XDT, th * 128 + 4 * lane);
+            vals[r] = *reinterpret_cast<const float4*>(p.dgp + ((size_t)(start + rr) * HV + h) * 128 + 4 * lane);
         }
         float4 run = splat4(0.f);
 #pragma unroll
@@ -139,30 +137,40 @@ __global__ void __launch_bounds__(128) gate_bwd_kernel(const MkdaGateBwd p) {
         float4 post = splat4(0.f);
         for (int w = 3; w > warp; --w) post = add4(post, tot[w][lane]);
 #pragma unroll
-        for (int r = 0; r < 16; ++r) {
-            const int row = warp * 16 + r;
-            if (row >= len) continue;                       // warp-uniform
-            const size_t th = (size_t)(start + row) * HV + h;
-            const float4 dg = add4(vals[r], post);
-            if (p.scalar_gate) {
-                const float dgs = warp_sum(hsum4(dg));
-                float ds, dA;
-                gate_grad(p.mode, xs[r].x + bias.x, E, p.lower_bound, ds, dA);
-                const float dxs = dgs * ds;
-                if (lane == 0) st1(p.dx, p.dx_dtype, th, dxs);
-                pb.x += dxs;
-                pa.x += dgs * dA;
-            } else {
-                const float4 xv = add4(xs[r], bias);
-                float4 ds, dA;
-                gate_grad(p.mode, xv.x, E, p.lower_bound, ds.x, dA.x);
-                gate_grad(p.mode, xv.y, E, p.lower_bound, ds.y, dA.y);
-                gate_grad(p.mode, xv.z, E, p.lower_bound, ds.z, dA.z);
-                gate_grad(p.mode, xv.w, E, p.lower_bound, ds.w, dA.w);
-                const float4 dxv = mul4(dg, ds);
-                st4(p.dx, p.dx_dtype, th * 128 + 4 * lane, dxv);
-                pb = add4(pb, dxv);
-                pa = add4(pa, mul4(dg, dA));
+        for (int half = 0; half < 2; ++half) {
+            float4 xs[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const int row = warp * 16 + half * 8 + r, rr = row < len ? row : len - 1;
+                const size_t th = (size_t)(start + rr) * HV + h;
+                xs[r] = p.scalar_gate ? splat4(ld1(p.x, XDT, th)) : ld4(p.x, XDT, th * 128 + 4 * lane);
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const int row = warp * 16 + half * 8 + r;
+                if (row >= len) continue;                       // warp-uniform
+                const size_t th = (size_t)(start + row) * HV + h;
+                const float4 dg = add4(vals[half * 8 + r], post);
+                if (p.scalar_gate) {
+                    const float dgs = warp_sum(hsum4(dg));
+                    float ds, dA;
+                    gate_grad(p.mode, xs[r].x + bias.x, E, p.lower_bound, ds, dA);
+                    const float dxs = dgs * ds;
+                    if (lane == 0) st1(p.dx, p.dx_dtype, th, dxs);
+                    pb.x += dxs;
+                    pa.x += dgs * dA;
+                } else {
+                    const float4 xv = add4(xs[r], bias);
+                    float4 ds, dA;
+                    gate_grad(p.mode, xv.x, E, p.lower_bound, ds.x, dA.x);
+                    gate_grad(p.mode, xv.y, E, p.lower_bound, ds.y, dA.y);
+                    gate_grad(p.mode, xv.z, E, p.lower_bound, ds.z, dA.z);
+                    gate_grad(p.mode, xv.w, E, p.lower_bound, ds.w, dA.w);
+                    const float4 dxv = mul4(dg, ds);
+                    st4(p.dx, p.dx_dtype, th * 128 + 4 * lane, dxv);
+                    pb = add4(pb, dxv);
+                    pa = add4(pa, mul4(dg, dA));
+                }
             }
         }
     }

@@ -103,7 +103,7 @@ def gate_bwd(lay, x, dgp, mode, A_log, dt_bias, lower_bound, HV, want_bias, want
     p.lower_bound = -3.0e38 if lower_bound is None else float(lower_bound)
     p.dgp, p.dx, p.dx_dtype = _ptr(dgp, torch.float32), _ptr(dx), _dt(dx)
     width = HV if scalar else HV * 128
-    rows = max(1, min(lay.NC, 64))
+    rows = max(1, min(lay.NC, 256))
     p.part_rows = rows
     part_b = part_a = None
     if mode != "precomputed":
