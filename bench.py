@@ -124,9 +124,22 @@ KERNEL_FLOPS = {                      # per token per v-head
     "mkda_bwd_wy": F_KV + 4 * F_CK + 2 * F_CC,        # k~ S, A W, dO Vd^T, A^T dVd, dVd W^T, two C^3 products
     "mkda_bwd_sgrad": 3 * F_KV,                       # dO S^T, dX S^T, Vd dS'^T
     "mkda_bwd_intra": 4 * F_CK,                       # row / column terms through Gamma and Q K^T
+    "mkda_bwd_tail": 3 * F_KV + 4 * F_CK,             # bwd_sgrad + bwd_intra in one kernel
 }
-# DRAM traffic per token per v-head measured by ncu (profiles/), bytes; filled in as captures are taken.
-KERNEL_TRAFFIC = {}
+# Algorithmic bytes per token per v-head: each kernel's own tensor I/O at the default workload (bf16 q/k/v/gate,
+# fp32 intermediates, HV = 2 HK), every operand counted once.
+KERNEL_BYTES = {
+    "mkda_gate_cumsum_fwd": 1024, "mkda_l2norm_rstd": 128, "mkda_intra_fwd": 2560, "mkda_recur_fwd": 3200,
+    "mkda_out_fwd": 3712, "mkda_epilogue_bwd": 2048, "mkda_bwd_dh": 3584, "mkda_bwd_wy": 4736, "mkda_bwd_sgrad": 5888,
+    "mkda_bwd_intra": 4352, "mkda_gate_bwd": 1536, "mkda_qk_grad_finish": 640,
+    "mkda_bwd_tail": 5888 + 4352 - 6 * 512,           # the three row-local partials are neither written nor re-read
+}
+# DRAM traffic per token per v-head measured by ncu on the 1B-shape case (profiles/counters_per_kernel_1b_shape.md),
+# bytes (dram read + write per launch / 131072 token-heads); it grows in proportion to tokens x heads.
+KERNEL_TRAFFIC = {
+    "mkda_intra_fwd": 2154, "mkda_recur_fwd": 2913, "mkda_out_fwd": 3512, "mkda_bwd_dh": 3304, "mkda_bwd_wy": 4500,
+    "mkda_gate_cumsum_fwd": 651, "mkda_epilogue_bwd": 1774, "mkda_qk_grad_finish": 653,
+}
 
 
 class LaunchRecorder:
@@ -361,18 +374,23 @@ def main():
         name, (kms, n) = top
         per_launch_s = kms / n * 1e-3
         units = tokens_per_step * dims["HV"]
-        if name in KERNEL_FLOPS:
+        # the roofline that bounds the kernel is the one with the larger time floor for its algorithmic work
+        t_hbm = KERNEL_BYTES.get(name, 0) * units / (peaks["hbm"] * 1e9)
+        t_tc = KERNEL_FLOPS.get(name, 0) * units / (peaks["tensor"] * 1e12)
+        traffic = KERNEL_TRAFFIC[name] * units if name in KERNEL_TRAFFIC else None
+        if t_tc > t_hbm:
             ach = KERNEL_FLOPS[name] * units / per_launch_s / 1e12
-            roof = dict(kernel=name, bound="tensor", achieved=ach, peak=peaks["tensor"], unit="TFLOP/s",
-                        frac=ach / peaks["tensor"], traffic=KERNEL_TRAFFIC.get(name), peak_source=peaks["source"],
-                        share_of_step=kms / ms, launch_ms=per_launch_s * 1e3)
+            roof = dict(kernel=name, bound="tensor", achieved=ach, peak=peaks["tensor"], unit="TFLOP/s", frac=ach / peaks["tensor"])
         else:
-            roof = dict(kernel=name, bound="hbm", achieved=None, peak=peaks["hbm"], unit="GB/s", frac=None,
-                        traffic=None, peak_source=peaks["source"], share_of_step=kms / ms, launch_ms=per_launch_s * 1e3)
+            ach = KERNEL_BYTES.get(name, 0) * units / per_launch_s / 1e9
+            roof = dict(kernel=name, bound="hbm", achieved=ach, peak=peaks["hbm"], unit="GB/s", frac=ach / peaks["hbm"])
+        roof.update(traffic=traffic, peak_source=peaks["source"] + " (sustained bf16 / copy)", share_of_step=kms / ms,
+                    launch_ms=per_launch_s * 1e3, alg_flops_per_launch=KERNEL_FLOPS.get(name, 0) * units,
+                    alg_bytes_per_launch=KERNEL_BYTES.get(name, 0) * units)
         line = {
             "metric": "KDA fwd+bwd Mtok/s per layer", "value": value, "unit": "Mtok/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16x3", "data": "synthetic",
             "config": {"workload": f"{args.workload}: {desc}", **dims, "D": D,
                        "parallelism": ("cp%d" % world) if cp is not None else ("dp%d" % world),
                        "l2": "per-step working set (> 10 GB of inputs and intermediates) exceeds the 126 MB L2"},

@@ -251,6 +251,23 @@ typedef struct {
 } MkdaBwdIntra;
 int mkda_bwd_intra(const MkdaBwdIntra* p, void* stream);
 
+/* mkda_bwd_sgrad followed by mkda_bwd_intra in one kernel: the row-local partials dq_p / dk_p / dg_p stay in tensor
+ * memory instead of going through HBM.  Same inputs and outputs as the two calls it replaces. */
+typedef struct {
+    MkdaLayout L;
+    const void* q; const void* k; int qk_dtype; const float* q_rstd; const float* k_rstd;
+    const float* g_c; const float* beta;
+    const void* d_o; int do_dtype; const float* dX; const float* Vd;
+    const float* h; const float* dh;
+    const float* dAqk; const float* dL; const float* dbeta_w;
+    float scale;
+    const void* beta_raw; int beta_dtype; int beta_sigmoid; float beta_scale;
+    float* dq_v; float* dk_v;  /* [TT,HV,128] per v-head */
+    float* dgp;                /* [TT,HV,128] gradient w.r.t. the log2 cumsum */
+    void* dbeta; int dbeta_dtype;
+} MkdaBwdTail;
+int mkda_bwd_tail(const MkdaBwdTail* p, void* stream);
+
 /* Sum over the v-heads sharing a q/k head, then L2-norm backward; writes dq or dk in the input dtype.
  * Replaces group_reduce_vector (mogan_kda/ops/utils/group_reduce.py:60-79) and l2norm_bwd
  * (mogan_kda/utils/math.py:38-72). */

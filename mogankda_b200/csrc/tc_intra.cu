@@ -454,6 +454,345 @@ int launch_bwd_intra_tc(const MkdaBwdIntra* p, cudaStream_t stream) {
     return set_error(MKDA_ERR_ARG, "bwd_intra: unsupported dtype");
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// bwd_tail = bwd_sgrad followed by bwd_intra for the same (chunk, v-head), in one CTA.  The three state products
+//   Dq^T[c][t] = S dO^T      Dk^T[c][t] = S dX^T      Db^T[c][t] = dS' Vd^T         (channels c on M, K = 128 over v)
+// stay in tensor memory while the CTA rebuilds the intra-chunk operands over the dead state tiles and issues the
+// row / column products of bwd_intra; one epilogue then combines all of them per (channel, row) and writes dq_v, dk_v and
+// dgp once.  Column products use N = 16 (I + 1) (only columns j < 16 (I + 1) of row block I are non-zero).
+// TMEM columns: Dq 0, Dk 64, Db 128, R_I 192 + 32 I, C_I 320 + {0, 16, 48, 96}.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int TAIL_SMEM = 192 * 1024 + 1024;
+__host__ __device__ constexpr int dcol_off(int I) { return 320 + (I == 0 ? 0 : I == 1 ? 16 : I == 2 ? 48 : 96); }
+
+template <int QKDT, int DODT>
+__global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ IntraShared sh;
+    __shared__ float sDiag[CH];
+    __shared__ float sRed[4][CH];
+    __shared__ float sDgl[DK];
+    __shared__ float sCol[4][DK];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // state phase
+    uint8_t* sSh = base;                               // S [kidx][v]
+    uint8_t* sSl = base + 32768;
+    uint8_t* sTh = base + 65536;                       // dS'
+    uint8_t* sTl = base + 98304;
+    uint8_t* sOh = base + 131072;                      // dO [tok][v], later Vd
+    uint8_t* sOl = base + 147456;
+    uint8_t* sXh = base + 163840;                      // dX
+    uint8_t* sXl = base + 180224;
+    // intra phase
+    uint8_t* sKQ = base + KQ_OFF;
+    uint8_t* sWq = base + OPND_BYTES;                  // scale strictlower(dAqk) [i][j], hi 8 KB + lo 8 KB
+    uint8_t* sDl = sWq + 16384;                        // strictlower(dL)
+    uint8_t* sBd = sDl + 16384;                        // diag(beta) strictlower(dL)
+    float* sG = reinterpret_cast<float*>(sXh);         // [64][128] fp32 cumsum tile, over the dX tile once it is dead
+
+    const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV, HK = p.L.HK;
+    const int hk = h / (HV / HK);
+    const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
+    const size_t sbase = ((size_t)c * HV + h) * DK * DV;
+
+    if (warp == 0) umma::tmem_alloc(&sh.tmem, 512);
+    if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
+    if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
+
+    // ---- state phase 1: S, dO, dX -------------------------------------------------------------------------------
+    {
+        float vS[4][8], vO[2][8], vX[2][8];
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const int i = tid + n * 512;
+            ldg8(p.h, MKDA_F32, sbase + (size_t)(i >> 4) * DV + (i & 15) * 8, vS[n]);
+        }
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4, rr = r < len ? r : len - 1;
+            const size_t off = ((size_t)(start + rr) * HV + h) * 128 + (i & 15) * 8;
+            ldg8(p.d_o, DODT, off, vO[n]);
+            ldg8(p.dX, MKDA_F32, off, vX[n]);
+        }
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const int i = tid + n * 512;
+            store_split8(sSh, sSl, 128, i >> 4, i & 15, vS[n]);
+        }
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4;
+            if (r >= len) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) vO[n][e] = vX[n][e] = 0.f;
+            }
+            store_split8(sOh, sOl, 64, r, i & 15, vO[n]);
+            store_split8(sXh, sXl, 64, r, i & 15, vX[n]);
+        }
+    }
+    publish();
+    const uint32_t tmem = sh.tmem;
+    if (tid == 0) {
+        const umma::Opnd aS = umma::opnd_k(sSh, sSl, 128);
+        umma::gemm(tmem + 0, aS, umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
+        umma::gemm(tmem + 64, aS, umma::opnd_k(sXh, sXl, 64), 128, 64, 128, 0u);
+        umma::commit(&sh.bar);
+    }
+    // ---- state phase 2: dS', Vd, and dgl[c] = sum_v S[c][v] dS'[c][v] (S re-read from its hi + lo tile) ---------------
+    {
+        float vD[4][8], vV[2][8];
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const int i = tid + n * 512;
+            ldg8(p.dh, MKDA_F32, sbase + (size_t)(i >> 4) * DV + (i & 15) * 8, vD[n]);
+        }
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4, rr = r < len ? r : len - 1;
+            ldg8(p.Vd, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + (i & 15) * 8, vV[n]);
+        }
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
+            const uint32_t off = umma::tile_chunk_offset(128, r, k8);
+            const uint4 sh4 = *reinterpret_cast<const uint4*>(sSh + off), sl4 = *reinterpret_cast<const uint4*>(sSl + off);
+            const uint32_t hw[4] = {sh4.x, sh4.y, sh4.z, sh4.w}, lw[4] = {sl4.x, sl4.y, sl4.z, sl4.w};
+            float pr = 0.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float s0 = __uint_as_float(hw[e] << 16) + __uint_as_float(lw[e] << 16);
+                const float s1 = __uint_as_float(hw[e] & 0xffff0000u) + __uint_as_float(lw[e] & 0xffff0000u);
+                pr += s0 * vD[n][2 * e] + s1 * vD[n][2 * e + 1];
+            }
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) pr += __shfl_xor_sync(0xffffffffu, pr, o);
+            if ((lane & 15) == 0) sDgl[r] = pr;
+            store_split8(sTh, sTl, 128, r, k8, vD[n]);
+        }
+        umma::mbar_wait(&sh.bar, 0);                   // S dO^T and S dX^T done: the dO tile can be replaced by Vd
+        umma::fence_after_sync();
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4;
+            if (r >= len) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) vV[n][e] = 0.f;
+            }
+            store_split8(sOh, sOl, 64, r, i & 15, vV[n]);
+        }
+    }
+    publish();
+    if (tid == 0) {
+        umma::gemm(tmem + 128, umma::opnd_k(sTh, sTl, 128), umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
+        umma::commit(&sh.bar);
+    }
+
+    // ---- intra phase: fetch k, q, g and the two 64 x 64 weights while the last state product runs ---------------------
+    float vk[2][8], vq[2][8], vg[2][8], rk[2], rq[2], wa[8], wl[8];
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+        const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
+        const size_t tk = (size_t)(start + rr) * HK + hk;
+        ldg8(p.k, QKDT, tk * 128 + k8 * 8, vk[n]);
+        ldg8(p.q, QKDT, tk * 128 + k8 * 8, vq[n]);
+        ldg8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vg[n]);
+        rk[n] = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
+        rq[n] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
+    }
+    {
+        const int i = tid >> 3, k8 = tid & 7, ii = i < len ? i : len - 1;
+        const size_t o = ((size_t)(start + ii) * HV + h) * 64 + k8 * 8;
+        ldg8(p.dAqk, MKDA_F32, o, wa);
+        ldg8(p.dL, MKDA_F32, o, wl);
+    }
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {                      // the dX tile is dead since the first wait
+        const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
+        *reinterpret_cast<float4*>(sG + r * 128 + k8 * 8) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
+        *reinterpret_cast<float4*>(sG + r * 128 + k8 * 8 + 4) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { vk[n][e] *= rk[n]; vq[n][e] *= rq[n]; }
+    }
+    __syncthreads();
+    umma::mbar_wait(&sh.bar, 1);                       // dS' Vd^T done: every state tile is dead
+    umma::fence_after_sync();
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+        const int i = tid + n * 512, r = i >> 4, k8 = i & 15, I0 = r >> 4;
+        float ga[8], t8[8];
+        lds8(sG + (16 * I0) * 128 + k8 * 8, ga);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(vg[n][e] - ga[e]);
+        store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + (r & 15), k8, t8);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) t8[e] = vq[n][e] * ex2f_(vg[n][e] - ga[e]);
+        store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + 16 + (r & 15), k8, t8);
+#pragma unroll
+        for (int I = 0; I < 4; ++I) {
+            if (I < I0) continue;
+            if (I > I0) lds8(sG + (16 * I) * 128 + k8 * 8, ga);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(ga[e] - vg[n][e]);
+            store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
+        }
+    }
+    __syncthreads();                                   // the cumsum tile is dead: the W tiles overlap it
+    {
+        const int i = tid >> 3, k8 = tid & 7;
+        const float bt = sh.beta[i];
+        float w8[8], d8[8], b8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int j = k8 * 8 + e;
+            const bool lo = j < i && i < len;
+            w8[e] = lo ? p.scale * wa[e] : 0.f;
+            d8[e] = lo ? wl[e] : 0.f;
+            b8[e] = bt * d8[e];
+            if (j == i) sDiag[i] = i < len ? p.scale * wa[e] : 0.f;
+        }
+        store_split8(sWq, sWq + 8192, 64, i, k8, w8);
+        store_split8(sDl, sDl + 8192, 64, i, k8, d8);
+        store_split8(sBd, sBd + 8192, 64, i, k8, b8);
+    }
+    publish();
+    if (tid == 0) {
+#pragma unroll
+        for (int I = 0; I < 4; ++I) {
+            const int nj = 16 * (I + 1);
+            const umma::Opnd aKc = umma::opnd_mn(base + kc_off(I), base + kc_off(I) + kc_bytes(I), nj);
+            umma::gemm(tmem + 192 + 32 * I, aKc, umma::opnd_k(sWq, sWq + 8192, 64, 16 * I), 128, 16, nj, 0u);
+            umma::gemm(tmem + 192 + 32 * I + 16, aKc, umma::opnd_k(sDl, sDl + 8192, 64, 16 * I), 128, 16, nj, 0u);
+            umma::gemm(tmem + dcol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I + 16), umma::opnd_mn(sWq, sWq + 8192, 64, 16 * I),
+                       128, nj, 16, 0u);
+            umma::gemm(tmem + dcol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I), umma::opnd_mn(sBd, sBd + 8192, 64, 16 * I),
+                       128, nj, 16, 1u);
+        }
+        umma::commit(&sh.bar);
+    }
+    // epilogue inputs for (channel `row`, rows 16 cg .. 16 cg + 15) are fetched while the products run
+    float kq[16], qq[16], gg[16], ga[4];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+        const int i = 16 * cg + r, ii = i < len ? i : len - 1;
+        const size_t tk = (size_t)(start + ii) * HK + hk;
+        kq[r] = ld1(p.k, QKDT, tk * 128 + row) * (p.k_rstd ? p.k_rstd[tk] : 1.f);
+        qq[r] = ld1(p.q, QKDT, tk * 128 + row) * (p.q_rstd ? p.q_rstd[tk] : 1.f);
+        gg[r] = p.g_c[((size_t)(start + ii) * HV + h) * 128 + row];
+    }
+#pragma unroll
+    for (int I = 0; I < 4; ++I) {
+        const int a = 16 * I < len ? 16 * I : len - 1;
+        ga[I] = p.g_c[((size_t)(start + a) * HV + h) * 128 + row];
+    }
+    const float gL = p.g_c[((size_t)(start + len - 1) * HV + h) * 128 + row];
+    umma::mbar_wait(&sh.bar, 0);
+    umma::fence_after_sync();
+
+    {   // column sum of the inter-chunk k gradient for the last row's gate term
+        float ab[16];
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + 16 * cg), ab);
+        float cs = 0.f;
+#pragma unroll
+        for (int r = 0; r < 16; ++r)
+            if (16 * cg + r < len) cs += kq[r] * ex2f_(gL - gg[r]) * ab[r];
+        sCol[cg][row] = cs;
+    }
+    __syncthreads();
+    const float extra = ((sCol[0][row] + sCol[1][row]) + (sCol[2][row] + sCol[3][row])) + ex2f_(gL) * sDgl[row];
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+        const int c0 = 16 * cg + 8 * hf;
+        float aq[8], ak[8], ab[8], vr[8], vt[8], dkc[8];
+        umma::tmem_ld8(umma::tmem_addr(tmem, warp, c0), aq);
+        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 64 + c0), ak);
+        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 128 + c0), ab);
+        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 192 + 32 * cg + 8 * hf), vr);
+        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 192 + 32 * cg + 16 + 8 * hf), vt);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) dkc[r] = 0.f;
+#pragma unroll
+        for (int I = 0; I < 4; ++I) {
+            if (I < cg) continue;                      // warp-uniform
+            float c8[8];
+            umma::tmem_ld8(umma::tmem_addr(tmem, warp, dcol_off(I) + c0), c8);
+#pragma unroll
+            for (int r = 0; r < 8; ++r) dkc[r] += c8[r] * ex2f_(ga[I] - gg[8 * hf + r]);
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const int i = c0 + r, rr = 8 * hf + r;
+            const float g = gg[rr], kv = kq[rr], qv = qq[rr];
+            const float up = ex2f_(g), re = ex2f_(gL - g), e = ex2f_(g - ga[cg]);
+            const float dqt = p.scale * aq[r], dkt = -ak[r], dkb = ab[r];
+            const float dqr = vr[r] * e, T = vt[r] * e, bt = sh.beta[i], dgn = sDiag[i];
+            float bs = kv * T;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, o);
+            if (lane == 0) sRed[q][i] = bs;
+            if (i < len) {
+                float dg = qv * up * dqt + kv * up * dkt - kv * re * dkb;
+                if (i == len - 1) dg += extra;
+                const size_t off = ((size_t)(start + i) * HV + h) * 128 + row;
+                p.dq_v[off] = dqt * up + dqr + dgn * kv;
+                p.dk_v[off] = (dkt * up + dkb * re) + bt * T + dkc[r] + dgn * qv;
+                p.dgp[off] = dg + qv * dqr + kv * bt * T - kv * dkc[r];
+            }
+        }
+    }
+    __syncthreads();
+    if (tid < len) {
+        const size_t th = (size_t)(start + tid) * HV + h;
+        float db = p.dbeta_w[th] + ((sRed[0][tid] + sRed[1][tid]) + (sRed[2][tid] + sRed[3][tid]));
+        if (p.beta_sigmoid) {
+            const float sg = sigmoidf_(ld1(p.beta_raw, p.beta_dtype, th));
+            db *= p.beta_scale * sg * (1.f - sg);
+        }
+        st1(p.dbeta, p.dbeta_dtype, th, db);
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) umma::tmem_dealloc(tmem, 512);
+}
+
+template <int QKDT, int DODT>
+static int launch_bwd_tail_tc_t(const MkdaBwdTail* p, cudaStream_t stream) {
+    auto kern = bwd_tail_tc_kernel<QKDT, DODT>;
+    if (int e = ensure_smem((const void*)kern, TAIL_SMEM, "bwd_tail")) return e;
+    kern<<<dim3(p->L.NC, p->L.HV), 512, TAIL_SMEM, stream>>>(*p);
+    return check_launch("bwd_tail");
+}
+template <int QKDT>
+static int launch_bwd_tail_tc_q(const MkdaBwdTail* p, cudaStream_t stream) {
+    switch (p->do_dtype) {
+        case MKDA_F32: return launch_bwd_tail_tc_t<QKDT, MKDA_F32>(p, stream);
+        case MKDA_BF16: return launch_bwd_tail_tc_t<QKDT, MKDA_BF16>(p, stream);
+        case MKDA_F16: return launch_bwd_tail_tc_t<QKDT, MKDA_F16>(p, stream);
+    }
+    return set_error(MKDA_ERR_ARG, "bwd_tail: unsupported dtype");
+}
+
+}  // namespace mkda
+
+extern "C" int mkda_bwd_tail(const MkdaBwdTail* p, void* stream) {
+    using namespace mkda;
+    if (!p || !p->q || !p->k || !p->g_c || !p->beta || !p->d_o || !p->dX || !p->Vd || !p->h || !p->dh || !p->dAqk || !p->dL ||
+        !p->dbeta_w || !p->dq_v || !p->dk_v || !p->dgp || !p->dbeta)
+        return set_error(MKDA_ERR_ARG, "bwd_tail: null argument");
+    if (p->beta_sigmoid && !p->beta_raw) return set_error(MKDA_ERR_ARG, "bwd_tail: sigmoid beta needs the raw input");
+    if (p->L.HK <= 0 || p->L.HV % p->L.HK) return set_error(MKDA_ERR_ARG, "bwd_tail: HV must be a multiple of HK");
+    if (p->L.NC == 0) return MKDA_OK;
+    switch (p->qk_dtype) {
+        case MKDA_F32: return launch_bwd_tail_tc_q<MKDA_F32>(p, (cudaStream_t)stream);
+        case MKDA_BF16: return launch_bwd_tail_tc_q<MKDA_BF16>(p, (cudaStream_t)stream);
+        case MKDA_F16: return launch_bwd_tail_tc_q<MKDA_F16>(p, (cudaStream_t)stream);
+    }
+    return set_error(MKDA_ERR_ARG, "bwd_tail: unsupported dtype");
+}
+
+namespace mkda {
+
 #ifdef MKDA_TRACE
 extern "C" int mkda_trace_read_intra(long long* out) { return cudaMemcpyFromSymbol(out, umma::g_trace, sizeof(long long) * 8 * 24) == cudaSuccess ? 0 : -1; }
 #endif

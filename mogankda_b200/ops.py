@@ -274,6 +274,27 @@ def bwd_intra(lay, q, k, q_rstd, k_rstd, g_c, beta_e, dAqk, dL, dq_p, dk_p, dg_p
     return dq_v, dk_v, dgp, dbeta
 
 
+def bwd_tail(lay, q, k, q_rstd, k_rstd, g_c, beta_e, d_o, dX, Vd, h, dh, dAqk, dL, dbeta_w, scale, HK, HV,
+             beta_raw, beta_sigmoid, beta_scale):
+    """bwd_sgrad + bwd_intra fused: the row-local partial gradients never leave the chip."""
+    dev = q.device
+    alloc = torch.empty if lay.covers_all else torch.zeros
+    z = lambda: alloc(lay.TT, HV, 128, dtype=torch.float32, device=dev)      # noqa: E731
+    dq_v, dk_v, dgp = z(), z(), z()
+    dbeta = alloc(lay.TT, HV, dtype=beta_raw.dtype, device=dev)
+    p = STRUCTS["MkdaBwdTail"]()
+    p.L = _layout_struct(lay, HK, HV)
+    p.q, p.k, p.qk_dtype, p.q_rstd, p.k_rstd = _ptr(q), _ptr(k), _dt(q), _ptr(q_rstd), _ptr(k_rstd)
+    p.g_c, p.beta = _ptr(g_c), _ptr(beta_e)
+    p.d_o, p.do_dtype, p.dX, p.Vd, p.h, p.dh = _ptr(d_o), _dt(d_o), _ptr(dX), _ptr(Vd), _ptr(h), _ptr(dh)
+    p.dAqk, p.dL, p.dbeta_w, p.scale = _ptr(dAqk), _ptr(dL), _ptr(dbeta_w), scale
+    p.beta_raw, p.beta_dtype = _ptr(beta_raw), _dt(beta_raw)
+    p.beta_sigmoid, p.beta_scale = int(beta_sigmoid), float(beta_scale)
+    p.dq_v, p.dk_v, p.dgp, p.dbeta, p.dbeta_dtype = _ptr(dq_v), _ptr(dk_v), _ptr(dgp), _ptr(dbeta), _dt(dbeta)
+    _lib.call("mkda_bwd_tail", p, _stream())
+    return dq_v, dk_v, dgp, dbeta
+
+
 def qk_grad_finish(d_v, x, rstd, HK, HV):
     """d_v fp32 [TT,HV,128] -> gradient w.r.t. the raw q or k, [TT,HK,128] in x.dtype."""
     TT = d_v.shape[0]

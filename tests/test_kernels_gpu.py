@@ -116,6 +116,13 @@ def test_bwd_intra_gate_and_finish(world):
                                            f32(bw["dg_p"]), f32(bw["dbeta_w"]), world["scale"], 2, 4, lv["beta"], False, 1.0)
     _err("dq_v", dq_v, bw["dq_v"]); _err("dk_v", dk_v, bw["dk_v"]); _err("dgp", dgp, bw["dgp"])
     _err("dbeta", dbeta, bw["dbeta"].reshape(world["TT"], 4))
+    # the fused sgrad + intra kernel gives the same outputs from the unfused kernels' inputs
+    t_q, t_k, t_g, t_b = ops.bwd_tail(lay, lv["q"], lv["k"], world["q_rstd"], world["k_rstd"], f32(fw["g_c"]), world["be"],
+                                      world["do"], f32(bw["dX"]), f32(bw["Vd"]), f32(fw["h"]), f32(bw["dh"]),
+                                      f32(bw["dAqk"]), f32(bw["dL"]), f32(bw["dbeta_w"]), world["scale"], 2, 4,
+                                      lv["beta"], False, 1.0)
+    _err("tail dq_v", t_q, bw["dq_v"]); _err("tail dk_v", t_k, bw["dk_v"]); _err("tail dgp", t_g, bw["dgp"])
+    _err("tail dbeta", t_b, bw["dbeta"].reshape(world["TT"], 4))
     # gate backward (reverse cumsum folded in) against autograd of the oracle's gate
     x = lv["g"].double().requires_grad_(True)
     A = lv["A_log"].double().requires_grad_(True)
