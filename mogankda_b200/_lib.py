@@ -66,7 +66,8 @@ _libs = {}
 
 
 def load(variant=""):
-    """Returns the loaded library (cached).  ``variant="_p3"`` selects the all-3xTF32 diagnostic build."""
+    """Returns the loaded library (cached).  ``variant`` is the file-name suffix of an alternative build placed beside
+    the default one (development builds, e.g. with phase tracing compiled in)."""
     if variant in _libs:
         return _libs[variant]
     path = os.path.join(HERE, f"libmkda{variant}.so")

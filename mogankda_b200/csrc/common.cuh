@@ -1,9 +1,9 @@
 // Shared device helpers for the KDA / GDN kernels (sm_100a).
 //
-// Numerics policy: every chunk contraction runs on the tensor cores with fp32-resident operands rounded to
-// TF32 at issue time and fp32 accumulation (PREC = 1), or with the error-compensated three-product split
-// (PREC = 3: a = hi + lo, a*b ~ lo_a*hi_b + hi_a*lo_b + hi_a*hi_b) where a contraction feeds a long dependency
-// chain.  Inputs may be fp32, bf16 or fp16 in global memory; they are widened to fp32 when staged.
+// Numerics policy: every contraction runs on the tensor cores with the error-compensated three-product split
+// (a = hi + lo, a*b ~ lo_a*hi_b + hi_a*lo_b + hi_a*hi_b) and fp32 accumulation: bf16 halves on tcgen05 in the chunk
+// kernels (umma.cuh), TF32 halves on mma.sync in the small prefix-combine kernel (PREC = 3 below; PREC = 1 is the plain
+// single product).  Inputs may be fp32, bf16 or fp16 in global memory; they are widened to fp32 when staged.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>

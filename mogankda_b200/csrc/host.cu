@@ -24,11 +24,6 @@ int check_launch(const char* what) {
     return MKDA_OK;
 }
 
-bool legacy_kernels() {
-    static const bool v = [] { const char* e = getenv("MKDA_LEGACY"); return e && e[0] == '1'; }();
-    return v;
-}
-
 int ensure_smem(const void* func, int bytes, const char* what) {
     cudaError_t e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e != cudaSuccess) {

@@ -254,8 +254,12 @@ int launch_out_fwd_tc(const MkdaOutFwd* p, cudaStream_t stream) {
 namespace mkda {
 
 // ---------------------------------------------------------------------------------------------------------
-// bwd_sgrad on the tensor cores.  With the K index on the MMA M axis:
-//   Dq[kidx x tok] = S dO^T      Dk[kidx x tok] = S dX^T      Db[kidx x tok] = dS' Vd^T      dgl = rowsum_v(S * dS')
+// bwd_sgrad.  With S / dS' the state entering / state-gradient leaving the chunk, up = 2^g, rest = 2^(g_L - g):
+//   dq~ = scale dO S^T     dk~ = -dX S^T     dkbar = Vd dS'^T     dgl = rowsum_v(S * dS')
+//   dq_p = dq~ up          dk_p = dk~ up + dkbar rest
+//   dg_p = q~ dq~ + k~ dk~ - kbar dkbar;   last valid row += colsum(kbar dkbar) + gl dgl
+// With the K index on the MMA M axis:
+//   Dq[kidx x tok] = S dO^T      Dk[kidx x tok] = S dX^T      Db[kidx x tok] = dS' Vd^T
 // followed by the row-local epilogue (one thread per K index walks its tokens, all global accesses coalesced over K).
 // ---------------------------------------------------------------------------------------------------------
 constexpr int SG_TC_SMEM = 4 * tile_bytes(128, 128) + 4 * tile_bytes(64, 128) + 1024;
@@ -427,7 +431,11 @@ __device__ __forceinline__ void load_tile8(const uint8_t* hi, const uint8_t* lo,
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// bwd_wy on the tensor cores.  Six dependent products, each with a 128-wide axis on M (TMEM columns in brackets):
+// bwd_wy.  With S the state entering the chunk, k~ = k 2^g, Ab = A diag(beta):
+//   X = V - k~ S        Vd = Ab X        dAqk = lower(dO Vd^T)
+//   dW = A^T dVd        dX = diag(beta) dW (= dV)       dbeta_w = rowsum(dW * X)
+//   dA = (dVd X^T) diag(beta)          dL = -strictlower(A^T dA A^T)
+// Six dependent products, each with a 128-wide axis on M (TMEM columns in brackets):
 //   G1 [0]    X^T[v x tok]  = V^T - S^T k~^T                       (A = S tile read MN-major)
 //   G2 [64]   Vd^T[v x i]   = X^T (A diag(beta))^T
 //   G4 [256]  dW^T[v x j]   = dVd^T A                              (both operands MN-major views of natural tiles)

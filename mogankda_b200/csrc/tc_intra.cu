@@ -1,8 +1,16 @@
 // Intra-chunk kernels on the Blackwell tensor cores: WY preparation (forward) and the gradients through the decayed
 // K K^T / Q K^T blocks (backward).  One CTA (16 warps) per (chunk, v-head).
 //
-// The per-channel decay 2^(g_i - g_j) does not factor out of the contraction over channels, so each 16-row block I is
-// anchored at its first row a = 16 I (see intra_fwd.cu for the range / prefix-invariance argument):
+// Forward:
+//   Gamma_ij = sum_c k_ic k_jc 2^(g_ic - g_jc)  (i > j)        Aqk_ij = scale sum_c q_ic k_jc 2^(g_ic - g_jc)  (i >= j)
+//   A  = (I + strictlower(diag(beta) Gamma))^-1
+//   nw = -A diag(beta) (k 2^g)                                  u = A diag(beta) v
+//
+// Range / prefix invariance: the per-channel decay 2^(g_i - g_j) does not factor out of the contraction over channels,
+// so each 16-row block I uses its first row a = 16 I as anchor: row operand k_i 2^(g_i - g_a) (<= 1), column operand
+// k_j 2^(g_a - g_j) (<= 1 for j < a, <= 2^(15*5/ln2) inside the diagonal block).  An output element (i, j) therefore
+// depends on rows i, j and a <= i only, never on later rows.  Rows past the end of the sequence are staged as zeros
+// (their g as the last valid row's), so they produce identity rows in A and are never stored.
 //   row operand     Kr[i] = k_i 2^(g_i - g_a(i)),  Qr[i] = q_i 2^(g_i - g_a(i))      one tile for all 64 rows
 //   column operand  Kc_I[j] = k_j 2^(g_aI - g_j),  j < 16 (I + 1)                    one tile per row block
 // With M = 128 mandatory, the column operand goes on M:  D_I[j][r] = Kc_I[j] . [Kr_I; Qr_I][r]  (N = 32, K = 128);
@@ -256,7 +264,13 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// bwd_intra on the tensor cores (math in intra_bwd.cu).  Channels go on M.  Per row block I (anchor a = 16 I):
+// bwd_intra.  With E_ij = 2^(g_i - g_j) per channel (i > j), Wq = scale strictlower(dAqk), dLs = strictlower(dL):
+//   dq_row_i = sum_j Wq_ij k_j E_ij                     T_i = sum_j dLs_ij k_j E_ij
+//   dk_col_j = sum_i (Wq_ij q_i + beta_i dLs_ij k_i) E_ij
+//   dq = dq_p + dq_row + scale dAqk_ii k       dk = dk_p + beta T + dk_col + scale dAqk_ii q
+//   dg' = dg_p + q dq_row + k beta T - k dk_col           dbeta_g = sum_c k T
+// E_ij is factored through the anchor a of i's 16-row block exactly as in the forward kernel.
+// Channels go on M.  Per row block I (anchor a = 16 I):
 //   row terms   R_I^T[c][r]  = sum_j Kc_I[j][c] W[16 I + r][j]       W = Wq (-> dq_row) or dLs (-> T); N = 16 each
 //   col terms   C_I^T[c][j]  = sum_{i in I} Qr[i][c] Wq[i][j] + Kr[i][c] (beta dLs)[i][j]              N = 64
 // then per thread (channel c, row block cg): dq_row = R 2^(g_i - g_a), T likewise, dk_col[j] = sum_{I >= cg} C_I 2^(g_aI - g_j).
@@ -500,6 +514,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     if (warp == 0) umma::tmem_alloc(&sh.tmem, 512);
     if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
     if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
+    MKDA_TRACE_AT(5, 0);
 
     // ---- state phase 1: S, dO, dX -------------------------------------------------------------------------------
     {
@@ -532,8 +547,10 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
             store_split8(sXh, sXl, 64, r, i & 15, vX[n]);
         }
     }
+    MKDA_TRACE_AT(5, 1);
     publish();
     const uint32_t tmem = sh.tmem;
+    MKDA_TRACE_AT(5, 2);
     if (tid == 0) {
         const umma::Opnd aS = umma::opnd_k(sSh, sSl, 128);
         umma::gemm(tmem + 0, aS, umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
@@ -572,6 +589,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
             store_split8(sTh, sTl, 128, r, k8, vD[n]);
         }
         umma::mbar_wait(&sh.bar, 0);                   // S dO^T and S dX^T done: the dO tile can be replaced by Vd
+    MKDA_TRACE_AT(5, 3);
         umma::fence_after_sync();
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
@@ -588,6 +606,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         umma::gemm(tmem + 128, umma::opnd_k(sTh, sTl, 128), umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
         umma::commit(&sh.bar);
     }
+    MKDA_TRACE_AT(5, 4);
 
     // ---- intra phase: fetch k, q, g and the two 64 x 64 weights while the last state product runs ---------------------
     float vk[2][8], vq[2][8], vg[2][8], rk[2], rq[2], wa[8], wl[8];
@@ -617,6 +636,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     }
     __syncthreads();
     umma::mbar_wait(&sh.bar, 1);                       // dS' Vd^T done: every state tile is dead
+    MKDA_TRACE_AT(5, 5);
     umma::fence_after_sync();
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
@@ -639,6 +659,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         }
     }
     __syncthreads();                                   // the cumsum tile is dead: the W tiles overlap it
+    MKDA_TRACE_AT(5, 6);
     {
         const int i = tid >> 3, k8 = tid & 7;
         const float bt = sh.beta[i];
@@ -687,7 +708,9 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         ga[I] = p.g_c[((size_t)(start + a) * HV + h) * 128 + row];
     }
     const float gL = p.g_c[((size_t)(start + len - 1) * HV + h) * 128 + row];
+    MKDA_TRACE_AT(5, 7);
     umma::mbar_wait(&sh.bar, 0);
+    MKDA_TRACE_AT(5, 8);
     umma::fence_after_sync();
 
     {   // column sum of the inter-chunk k gradient for the last row's gate term
@@ -701,6 +724,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     }
     __syncthreads();
     const float extra = ((sCol[0][row] + sCol[1][row]) + (sCol[2][row] + sCol[3][row])) + ex2f_(gL) * sDgl[row];
+    MKDA_TRACE_AT(5, 9);
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
         const int c0 = 16 * cg + 8 * hf;
@@ -741,6 +765,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
             }
         }
     }
+    MKDA_TRACE_AT(5, 10);
     __syncthreads();
     if (tid < len) {
         const size_t th = (size_t)(start + tid) * HV + h;
@@ -754,6 +779,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     umma::fence_before_sync();
     __syncthreads();
     if (warp == 0) umma::tmem_dealloc(tmem, 512);
+    MKDA_TRACE_AT(5, 11);
 }
 
 template <int QKDT, int DODT>
@@ -773,25 +799,14 @@ static int launch_bwd_tail_tc_q(const MkdaBwdTail* p, cudaStream_t stream) {
     return set_error(MKDA_ERR_ARG, "bwd_tail: unsupported dtype");
 }
 
-}  // namespace mkda
-
-extern "C" int mkda_bwd_tail(const MkdaBwdTail* p, void* stream) {
-    using namespace mkda;
-    if (!p || !p->q || !p->k || !p->g_c || !p->beta || !p->d_o || !p->dX || !p->Vd || !p->h || !p->dh || !p->dAqk || !p->dL ||
-        !p->dbeta_w || !p->dq_v || !p->dk_v || !p->dgp || !p->dbeta)
-        return set_error(MKDA_ERR_ARG, "bwd_tail: null argument");
-    if (p->beta_sigmoid && !p->beta_raw) return set_error(MKDA_ERR_ARG, "bwd_tail: sigmoid beta needs the raw input");
-    if (p->L.HK <= 0 || p->L.HV % p->L.HK) return set_error(MKDA_ERR_ARG, "bwd_tail: HV must be a multiple of HK");
-    if (p->L.NC == 0) return MKDA_OK;
+int launch_bwd_tail_tc(const MkdaBwdTail* p, cudaStream_t stream) {
     switch (p->qk_dtype) {
-        case MKDA_F32: return launch_bwd_tail_tc_q<MKDA_F32>(p, (cudaStream_t)stream);
-        case MKDA_BF16: return launch_bwd_tail_tc_q<MKDA_BF16>(p, (cudaStream_t)stream);
-        case MKDA_F16: return launch_bwd_tail_tc_q<MKDA_F16>(p, (cudaStream_t)stream);
+        case MKDA_F32: return launch_bwd_tail_tc_q<MKDA_F32>(p, stream);
+        case MKDA_BF16: return launch_bwd_tail_tc_q<MKDA_BF16>(p, stream);
+        case MKDA_F16: return launch_bwd_tail_tc_q<MKDA_F16>(p, stream);
     }
     return set_error(MKDA_ERR_ARG, "bwd_tail: unsupported dtype");
 }
-
-namespace mkda {
 
 #ifdef MKDA_TRACE
 extern "C" int mkda_trace_read_intra(long long* out) { return cudaMemcpyFromSymbol(out, umma::g_trace, sizeof(long long) * 8 * 24) == cudaSuccess ? 0 : -1; }
