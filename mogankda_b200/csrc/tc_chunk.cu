@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
     MKDA_TRACE_AT(2, 1);
     const uint32_t tmem = tc_operands_ready(&sh);
     MKDA_TRACE_AT(2, 2);
-    if (tid == 0) {
+    if (umma::mma_issuer()) {
         umma::gemm(tmem, umma::opnd_mn(a1h, a1l, 128), umma::opnd_k(b1h, b1l, 64), 128, 64, 128, 0u);
         umma::gemm(tmem, umma::opnd_mn(a2h, a2l, 64), umma::opnd_k(b2h, b2l, 64), 128, 64, 64, 1u);
         umma::commit(&sh.bar);
@@ -311,7 +311,7 @@ __global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad
     MKDA_TRACE_AT(0, 2);
     const uint32_t tmem = tc_operands_ready(&sh);
     MKDA_TRACE_AT(0, 3);
-    if (tid == 0) {
+    if (umma::mma_issuer()) {
         const umma::Opnd aS = umma::opnd_k(sSh, sSl, 128);
         umma::gemm(tmem + 0, aS, umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
         umma::gemm(tmem + 64, aS, umma::opnd_k(sXh, sXl, 64), 128, 64, 128, 0u);
@@ -351,7 +351,7 @@ __global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
-    if (tid == 0) {
+    if (umma::mma_issuer()) {
         umma::gemm(tmem + 128, umma::opnd_k(sDh, sDl, 128), umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
         umma::commit(&bar2);
     }
@@ -515,7 +515,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     }
     MKDA_TRACE_AT(1, 2);
     const uint32_t tmem = tc_operands_ready(&sh);
-    if (tid == 0) {
+    if (umma::mma_issuer()) {
         umma::gemm(tmem + 0, umma::opnd_mn(sSh, sSl, 128), umma::opnd_k(sKh, sKl, 64), 128, 64, 128, 0u);
         umma::commit(&sh.bar);
     }
@@ -548,7 +548,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     }
     MKDA_TRACE_AT(1, 5);
     tc_operands_ready(&sh);
-    if (tid == 0) {
+    if (umma::mma_issuer()) {
         umma::gemm(tmem + 64, umma::opnd_k(sXh, sXl, 128), umma::opnd_k(sBh, sBl, 64), 128, 64, 64, 0u);
         umma::gemm(tmem + 256, umma::opnd_mn(sSh, sSl, 128, 64), umma::opnd_mn(sAh, sAl, 64), 128, 64, 64, 0u);
         umma::commit(&sh.bar);
@@ -575,7 +575,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     }
     MKDA_TRACE_AT(1, 7);
     tc_operands_ready(&sh);
-    if (tid == 0) {
+    if (umma::mma_issuer()) {
         umma::gemm(tmem + 128, umma::opnd_k(sSh, sSl, 128), umma::opnd_mn(sVh, sVl, 128), 128, 128, 128, 0u);
         umma::commit(&sh.bar);
     }
@@ -613,7 +613,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     MKDA_TRACE_AT(1, 9);
     tc_operands_ready(&sh);
     if (tid < len) p.dbeta_w[(size_t)(start + tid) * HV + h] = sRed[0][tid] + sRed[1][tid];
-    if (tid == 0) {
+    if (umma::mma_issuer()) {
         umma::gemm(tmem + 320, umma::opnd_k(sKh, sKl, 128), umma::opnd_k(sAh, sAl, 64), 128, 64, 64, 0u);
         umma::commit(&sh.bar);
     }
@@ -629,7 +629,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
         store_split8(sBh, sBl, 64, row, 2 * cg + 1, a1);
     }
     tc_operands_ready(&sh);
-    if (tid == 0) {
+    if (umma::mma_issuer()) {
         umma::gemm(tmem + 384, umma::opnd_mn(sAh, sAl, 64), umma::opnd_mn(sBh, sBl, 64), 128, 64, 64, 0u);
         umma::commit(&sh.bar);
     }

@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     }
     MKDA_TRACE_AT(3, 3);
     publish();
-    if (tid == 0) {
+    if (umma::mma_issuer()) {
 #pragma unroll
         for (int I = 0; I < 4; ++I)
             umma::gemm(tmem + 32 * I, umma::opnd_k(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1)),
@@ -233,7 +233,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         }
     }
     publish();
-    if (tid == 0) {
+    if (umma::mma_issuer()) {
         const umma::Opnd bA = umma::opnd_k(sTA, sTA + 8192, 64);
         umma::gemm(tmem + 128, umma::opnd_mn(sBk, sBk + 16384, 64), bA, 128, 64, 64, 0u);
         umma::gemm(tmem + 192, umma::opnd_mn(sBv, sBv + 16384, 64), bA, 128, 64, 64, 0u);
@@ -374,7 +374,7 @@ __global__ void __launch_bounds__(512, 1) bwd_intra_tc_kernel(const MkdaBwdIntra
     }
     MKDA_TRACE_AT(4, 4);
     publish();
-    if (tid == 0) {
+    if (umma::mma_issuer()) {
 #pragma unroll
         for (int I = 0; I < 4; ++I) {
             const umma::Opnd aKc = umma::opnd_mn(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1));
@@ -551,7 +551,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     publish();
     const uint32_t tmem = sh.tmem;
     MKDA_TRACE_AT(5, 2);
-    if (tid == 0) {
+    if (umma::mma_issuer()) {
         const umma::Opnd aS = umma::opnd_k(sSh, sSl, 128);
         umma::gemm(tmem + 0, aS, umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
         umma::gemm(tmem + 64, aS, umma::opnd_k(sXh, sXl, 64), 128, 64, 128, 0u);
@@ -602,7 +602,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         }
     }
     publish();
-    if (tid == 0) {
+    if (umma::mma_issuer()) {
         umma::gemm(tmem + 128, umma::opnd_k(sTh, sTl, 128), umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
         umma::commit(&sh.bar);
     }
@@ -677,8 +677,10 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         store_split8(sDl, sDl + 8192, 64, i, k8, d8);
         store_split8(sBd, sBd + 8192, 64, i, k8, b8);
     }
+    MKDA_TRACE_AT(5, 12);
     publish();
-    if (tid == 0) {
+    MKDA_TRACE_AT(5, 13);
+    if (umma::mma_issuer()) {
 #pragma unroll
         for (int I = 0; I < 4; ++I) {
             const int nj = 16 * (I + 1);
@@ -692,6 +694,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         }
         umma::commit(&sh.bar);
     }
+    MKDA_TRACE_AT(5, 14);
     // epilogue inputs for (channel `row`, rows 16 cg .. 16 cg + 15) are fetched while the products run
     float kq[16], qq[16], gg[16], ga[4];
 #pragma unroll

@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
             umma::tmem_wait_st();
         }
         publish_operands();
-        if (tid == 0) {
+        if (umma::mma_issuer()) {
             umma::gemm(tmem + 128, umma::opnd_k(sAh, sAl, 128), umma::opnd_k(sW[buf], sW[buf] + 16384, 64), 128, 64, 128, 0u);
             umma::commit(&sh.bar);
         }
@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
             store_split8(sAh, sAl, 128, row, 2 * cg + 1, a1);
         }
         publish_operands();
-        if (tid == 0) {
+        if (umma::mma_issuer()) {
             umma::gemm(tmem, umma::opnd_k(sAh, sAl, 128), umma::opnd_mn(sK[buf], sK[buf] + 16384, 64), 128, 128, 64, 1u);
             umma::commit(&sh.bar);
         }
@@ -374,7 +374,7 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
             umma::tmem_wait_st();
         }
         publish_operands();
-        if (tid == 0) {
+        if (umma::mma_issuer()) {
             umma::gemm(tmem + 128, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sAq, sAq + 8192, 64), 128, 64, 64, 0u);
             umma::gemm(tmem + 128, umma::opnd_k(sAh, sAl, 128), umma::opnd_k(sKb, sKb + 16384, 64), 128, 64, 128, 1u);
             umma::commit(&sh.bar);
@@ -394,7 +394,7 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
             store_split8(sAh, sAl, 128, row, 2 * cg + 1, a1);
         }
         publish_operands();
-        if (tid == 0) {
+        if (umma::mma_issuer()) {
             umma::gemm(tmem, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sQs, sQs + 16384, 64), 128, 128, 64, 1u);
             umma::gemm(tmem, umma::opnd_k(sAh, sAl, 128), umma::opnd_mn(sNw, sNw + 16384, 64), 128, 128, 64, 1u);
             umma::commit(&sh.bar);

@@ -163,6 +163,17 @@ __device__ __forceinline__ void gemm(uint32_t tmem_d, const Opnd& a, const Opnd&
 }
 
 // ---- synchronisation -----------------------------------------------------------------------------------------
+// True in exactly one thread of warp 0 (call with warp 0 converged).  The warp index comes from a shuffle and the lane
+// from elect.sync, so the compiler sees a warp-uniform branch around the MMA issue and can keep the descriptors and
+// addresses in uniform registers, where tcgen05.mma takes them, instead of moving them over per instruction.
+__device__ __forceinline__ bool mma_issuer() {
+    const int w = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+    if (w != 0) return false;
+    __syncwarp();
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
 }
@@ -178,14 +189,15 @@ __device__ __forceinline__ void commit(uint64_t* bar) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_u32(bar);
     // Bounded by wall time (SM clock): ~70 ms for the first wait that fails on a device, ~35 us afterwards, so a broken
-    // launch drains quickly instead of serialising one long timeout per CTA.  test_wait never blocks.
+    // launch drains quickly instead of serialising one long timeout per CTA.  try_wait parks the thread for at most the
+    // hinted microsecond per attempt, so waiting warps do not compete for issue slots with the thread issuing MMAs.
     const long long limit = *(volatile unsigned int*)&g_timeout_flag ? (1ll << 16) : (1ll << 27);
     const long long t0 = clock64();
     for (;;) {
         uint32_t ok;
         asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(addr), "r"(parity), "r"(1000u) : "memory");
         if (ok) return true;
         if (clock64() - t0 > limit) break;
     }
