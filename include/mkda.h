@@ -66,7 +66,7 @@ typedef struct {
     const void* x; int x_dtype; int scalar_gate;
     const float* A_log; const float* dt_bias;
     int mode; float lower_bound;
-    const float* dgp;          /* [TT,HV,128] gradient w.r.t. the log2 cumsum as produced by mkda_bwd_intra */
+    const float* dgp;          /* [TT,HV,128] gradient w.r.t. the log2 cumsum as produced by mkda_bwd_tail */
     void* dx; int dx_dtype;    /* [TT,HV,128] or [TT,HV] */
     int part_rows;             /* number of partial rows R (1 <= R <= NC): chunk c accumulates into row c % R */
     float* part_bias;          /* [R,HV,128] ([R,HV] scalar) partial sums of d/d(x+bias), or NULL */
@@ -107,9 +107,18 @@ typedef struct {
 } MkdaIntraFwd;
 int mkda_intra_fwd(const MkdaIntraFwd* p, void* stream);
 
-/* Serial state recurrence per (segment, v-head, 64-column block):  Vd = u + nw S;  S <- diag(gl) S + kbar^T Vd.
- * Column blocks 0,1 carry the state; with want_transition, blocks 2,3 carry the segment's K x K transition
- * matrix (same recurrence with u = 0 started from the identity).  Replaces the state part of fused_fwd_kda
+/* State tile: how the per-chunk states `h` (state entering a chunk) and `dh` (gradient of the state leaving it) travel
+ * between the kernels.  One tile per (chunk, v-head), MKDA_STATE_TILE_BYTES each, is the tensor-core operand itself: the
+ * transposed state [v][K index] split into bf16 hi (first 32 KB) and lo = bf16(x - hi) (second 32 KB); each half is two
+ * column blocks (K index 0-63, 64-127) of 128 rows x 128 bytes, 8-row groups 1024 bytes apart, with the eight 16-byte
+ * chunks of a row XOR-swizzled by (row & 7).  Producers write it with one asynchronous copy from shared memory and
+ * consumers fetch it the same way; hi + lo carries 16 mantissa bits, which is what the products consume anyway.
+ * The buffers are typed float* only for size ([NC,HV,128,128] floats = NC*HV tiles). */
+#define MKDA_STATE_TILE_BYTES 65536
+
+/* Serial state recurrence per (segment, v-head):  Vd = u + nw S;  S <- diag(gl) S + kbar^T Vd.
+ * With want_transition a second CTA per (segment, v-head) carries the segment's K x K transition matrix (same
+ * recurrence with u = 0 started from the identity).  Replaces the state part of fused_fwd_kda
  * (mogan_kda/ops/kimi_delta_rule/chunk/hopper/fused_fwd.py:523-616) and, for context parallelism, the role of
  * fused_gdr_h (mogan_kda/ops/gated_delta_rule/chunk/blackwell/prepare_h.py:336-403). */
 typedef struct {
@@ -120,7 +129,7 @@ typedef struct {
     const float* h0;           /* [*,HV,128,128] or NULL */
     const int* seg_h0;         /* [NS] row of h0 for each segment, -1 = start from zero; NULL = identity map */
     int state_v_first;         /* layout of h0 / ht */
-    float* h;                  /* [NC,HV,128,128] state entering each chunk, or NULL */
+    float* h;                  /* [NC,HV] state tiles: state entering each chunk, or NULL */
     float* Vd;                 /* [TT,HV,128] or NULL */
     float* ht;                 /* [NS,HV,128,128] state leaving each segment, or NULL */
     int want_transition;
@@ -134,7 +143,8 @@ int mkda_recur_fwd(const MkdaRecurFwd* p, void* stream);
 typedef struct {
     MkdaLayout L;
     const void* q; int q_dtype; const float* q_rstd;
-    const float* g_c; const float* Aqk; const float* Vd; const float* h;
+    const float* g_c; const float* Aqk; const float* Vd;
+    const float* h;            /* [NC,HV] state tiles */
     float scale;
     int has_norm; const void* norm_w; int norm_w_dtype;   /* [128] or NULL (=1) */
     const void* gate; int gate_dtype;                     /* [TT,HV,128] */
@@ -201,7 +211,7 @@ typedef struct {
     const float* dht;          /* [*,HV,128,128] or NULL */
     const int* seg_dht;        /* [NS] row of dht per segment, -1 = zero; NULL = identity map */
     int state_v_first;         /* layout of dht / dh0 */
-    float* dh;                 /* [NC,HV,128,128] gradient of the state leaving each chunk */
+    float* dh;                 /* [NC,HV] state tiles: gradient of the state leaving each chunk */
     float* dVd;                /* [TT,HV,128] */
     float* dh0;                /* [NS,HV,128,128] gradient of the state entering each segment, or NULL */
 } MkdaBwdDh;
@@ -212,7 +222,8 @@ int mkda_bwd_dh(const MkdaBwdDh* p, void* stream);
 typedef struct {
     MkdaLayout L;
     const void* k; const void* v; int kv_dtype; const float* k_rstd;
-    const float* g_c; const float* beta; const float* A; const float* h;
+    const float* g_c; const float* beta; const float* A;
+    const float* h;            /* [NC,HV] state tiles */
     const void* d_o; int do_dtype; const float* dVd;
     float* Vd;                 /* [TT,HV,128] recomputed */
     float* dX;                 /* [TT,HV,128] = dv (fp32) */
@@ -221,44 +232,18 @@ typedef struct {
 } MkdaBwdWy;
 int mkda_bwd_wy(const MkdaBwdWy* p, void* stream);
 
-/* Chunk-parallel gradients through the states: row-local parts of dq, dk and of the gate gradient.
- * Replaces K3b of bwd_post_kda (mogan_kda/ops/kimi_delta_rule/chunk/hopper/bwd_post.py:412-766). */
-typedef struct {
-    MkdaLayout L;
-    const void* q; const void* k; int qk_dtype; const float* q_rstd; const float* k_rstd;
-    const float* g_c;
-    const void* d_o; int do_dtype; const float* dX; const float* Vd;
-    const float* h; const float* dh;
-    float scale;
-    float* dq_p; float* dk_p; float* dg_p;         /* [TT,HV,128] */
-} MkdaBwdSgrad;
-int mkda_bwd_sgrad(const MkdaBwdSgrad* p, void* stream);
-
-/* Chunk-parallel gradients through the decayed K K^T / Q K^T blocks.
- * Replaces bwd_intra_kda (mogan_kda/ops/kimi_delta_rule/chunk/hopper/bwd_intra.py:529-600) plus the beta
- * activation derivative (mogan_kda/ops/kimi_delta_rule/chunk/__init__.py:256-258). */
-typedef struct {
-    MkdaLayout L;
-    const void* q; const void* k; int qk_dtype; const float* q_rstd; const float* k_rstd;
-    const float* g_c; const float* beta;
-    const float* dAqk; const float* dL;
-    const float* dq_p; const float* dk_p; const float* dg_p; const float* dbeta_w;
-    float scale;
-    const void* beta_raw; int beta_dtype; int beta_sigmoid; float beta_scale;
-    float* dq_v; float* dk_v;  /* [TT,HV,128] per v-head */
-    float* dgp;                /* [TT,HV,128] gradient w.r.t. the log2 cumsum */
-    void* dbeta; int dbeta_dtype;                  /* [TT,HV] gradient w.r.t. the raw beta input */
-} MkdaBwdIntra;
-int mkda_bwd_intra(const MkdaBwdIntra* p, void* stream);
-
-/* mkda_bwd_sgrad followed by mkda_bwd_intra in one kernel: the row-local partials dq_p / dk_p / dg_p stay in tensor
- * memory instead of going through HBM.  Same inputs and outputs as the two calls it replaces. */
+/* Every gradient that is local to a (chunk, v-head) once the state gradients are known: through the states (row-local
+ * parts of dq, dk and of the gate gradient) and through the decayed K K^T / Q K^T blocks, plus the beta activation
+ * derivative.  Replaces K3b of bwd_post_kda (mogan_kda/ops/kimi_delta_rule/chunk/hopper/bwd_post.py:412-766),
+ * bwd_intra_kda (mogan_kda/ops/kimi_delta_rule/chunk/hopper/bwd_intra.py:529-600) and the beta derivative
+ * (mogan_kda/ops/kimi_delta_rule/chunk/__init__.py:256-258); the row-local partials the reference passes between the
+ * two kernels through HBM stay in tensor memory. */
 typedef struct {
     MkdaLayout L;
     const void* q; const void* k; int qk_dtype; const float* q_rstd; const float* k_rstd;
     const float* g_c; const float* beta;
     const void* d_o; int do_dtype; const float* dX; const float* Vd;
-    const float* h; const float* dh;
+    const float* h; const float* dh;               /* state tiles, see MKDA_STATE_TILE_BYTES */
     const float* dAqk; const float* dL; const float* dbeta_w;
     float scale;
     const void* beta_raw; int beta_dtype; int beta_sigmoid; float beta_scale;

@@ -40,22 +40,6 @@ extern "C" int mkda_bwd_wy(const MkdaBwdWy* p, void* stream) {
     return launch_bwd_wy_tc(p, (cudaStream_t)stream);
 }
 
-extern "C" int mkda_bwd_sgrad(const MkdaBwdSgrad* p, void* stream) {
-    if (!p || !p->q || !p->k || !p->g_c || !p->d_o || !p->dX || !p->Vd || !p->h || !p->dh || !p->dq_p || !p->dk_p || !p->dg_p)
-        return set_error(MKDA_ERR_ARG, "bwd_sgrad: null argument");
-    if (p->L.NC == 0) return MKDA_OK;
-    return launch_bwd_sgrad_tc(p, (cudaStream_t)stream);
-}
-
-extern "C" int mkda_bwd_intra(const MkdaBwdIntra* p, void* stream) {
-    if (!p || !p->q || !p->k || !p->g_c || !p->beta || !p->dAqk || !p->dL || !p->dq_p || !p->dk_p || !p->dg_p ||
-        !p->dbeta_w || !p->dq_v || !p->dk_v || !p->dgp || !p->dbeta)
-        return set_error(MKDA_ERR_ARG, "bwd_intra: null argument");
-    if (p->beta_sigmoid && !p->beta_raw) return set_error(MKDA_ERR_ARG, "bwd_intra: sigmoid beta needs the raw input");
-    if (p->L.NC == 0) return MKDA_OK;
-    return launch_bwd_intra_tc(p, (cudaStream_t)stream);
-}
-
 extern "C" int mkda_bwd_tail(const MkdaBwdTail* p, void* stream) {
     if (!p || !p->q || !p->k || !p->g_c || !p->beta || !p->d_o || !p->dX || !p->Vd || !p->h || !p->dh || !p->dAqk || !p->dL ||
         !p->dbeta_w || !p->dq_v || !p->dk_v || !p->dgp || !p->dbeta)

@@ -10,14 +10,12 @@ int check_launch(const char* what);
 // Raises the dynamic shared memory limit of `func` once per process; returns 0 or an error code.
 int ensure_smem(const void* func, int bytes, const char* what);
 int launch_out_fwd_tc(const MkdaOutFwd* p, cudaStream_t stream);
-int launch_bwd_sgrad_tc(const MkdaBwdSgrad* p, cudaStream_t stream);
 int launch_bwd_wy_tc(const MkdaBwdWy* p, cudaStream_t stream);
 int tc_chunk_status(unsigned int* out);
 int launch_recur_fwd_tc(const MkdaRecurFwd* p, cudaStream_t stream);
 int launch_bwd_dh_tc(const MkdaBwdDh* p, cudaStream_t stream);
 int tc_recur_status(unsigned int* out);
 int launch_intra_fwd_tc(const MkdaIntraFwd* p, cudaStream_t stream);
-int launch_bwd_intra_tc(const MkdaBwdIntra* p, cudaStream_t stream);
 int launch_bwd_tail_tc(const MkdaBwdTail* p, cudaStream_t stream);
 int tc_intra_status(unsigned int* out);
 }  // namespace mkda

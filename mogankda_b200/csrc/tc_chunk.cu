@@ -133,10 +133,10 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
     const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    const size_t sbase = ((size_t)c * HV + h) * DK * DV;
-    {   // every tile is staged untransposed; the transposes come from MN-major operand views
-        float vH[4][8], vQ[2][8], vG[2][8], vV[2][8], vA[1][8];
-        load_chunks<4, 512, true>(vH, 128, 128, [&](int r, int k8, float (&v)[8]) { load8(p.h, MKDA_F32, sbase + (size_t)r * DV + k8 * 8, v); });
+    __shared__ uint64_t ldbar;
+    if (tid == 0) umma::fetch_state_tile(&ldbar, a1h, p.h, (size_t)c * HV + h);     // S^T [v][K index], ready-made operand
+    {   // every other tile is staged untransposed; the transposes come from MN-major operand views
+        float vQ[2][8], vG[2][8], vV[2][8], vA[1][8];
         load_chunks<2, 512, true>(vQ, 64, 128, [&](int r, int k8, float (&v)[8]) {
             const int rr = r < len ? r : len - 1;
             load8(p.q, QDT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, v);
@@ -155,7 +155,6 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
             load8(p.Aqk, MKDA_F32, ((size_t)(start + rr) * HV + h) * 64 + k8 * 8, v);
             if (r >= len) zero8(v);
         });
-        store_chunks<4, 512, true>(a1h, a1l, vH, 128, 128);
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
             const int r = (tid + n * 512) >> 4, rr = r < len ? r : len - 1;
@@ -171,8 +170,9 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
     const uint32_t tmem = tc_operands_ready(&sh);
     MKDA_TRACE_AT(2, 2);
     if (umma::mma_issuer()) {
-        umma::gemm(tmem, umma::opnd_mn(a1h, a1l, 128), umma::opnd_k(b1h, b1l, 64), 128, 64, 128, 0u);
-        umma::gemm(tmem, umma::opnd_mn(a2h, a2l, 64), umma::opnd_k(b2h, b2l, 64), 128, 64, 64, 1u);
+        umma::gemm(tmem, umma::opnd_mn(a2h, a2l, 64), umma::opnd_k(b2h, b2l, 64), 128, 64, 64, 0u);
+        umma::mbar_wait(&ldbar, 0);                        // the state tile has landed
+        umma::gemm(tmem, umma::opnd_k(a1h, a1l, 128), umma::opnd_k(b1h, b1l, 64), 128, 64, 128, 1u);
         umma::commit(&sh.bar);
     }
     // the row pass (warp w owns rows w, w + 16, ...) fetches its gate values while the products run
@@ -253,166 +253,6 @@ int launch_out_fwd_tc(const MkdaOutFwd* p, cudaStream_t stream) {
 
 namespace mkda {
 
-// ---------------------------------------------------------------------------------------------------------
-// bwd_sgrad.  With S / dS' the state entering / state-gradient leaving the chunk, up = 2^g, rest = 2^(g_L - g):
-//   dq~ = scale dO S^T     dk~ = -dX S^T     dkbar = Vd dS'^T     dgl = rowsum_v(S * dS')
-//   dq_p = dq~ up          dk_p = dk~ up + dkbar rest
-//   dg_p = q~ dq~ + k~ dk~ - kbar dkbar;   last valid row += colsum(kbar dkbar) + gl dgl
-// With the K index on the MMA M axis:
-//   Dq[kidx x tok] = S dO^T      Dk[kidx x tok] = S dX^T      Db[kidx x tok] = dS' Vd^T
-// followed by the row-local epilogue (one thread per K index walks its tokens, all global accesses coalesced over K).
-// ---------------------------------------------------------------------------------------------------------
-constexpr int SG_TC_SMEM = 4 * tile_bytes(128, 128) + 4 * tile_bytes(64, 128) + 1024;
-
-template <int QKDT, int DODT>
-__global__ void __launch_bounds__(512, 1) bwd_sgrad_tc_kernel(const MkdaBwdSgrad p) {
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ TcShared sh;
-    __shared__ uint64_t bar2;
-    __shared__ float sDgl[DK];
-    __shared__ float sCol[4][DK];
-    MKDA_TRACE_AT(0, 0);
-    uint8_t* base = tc_begin(smem_raw, &sh, 256);
-    uint8_t* sSh = base;
-    uint8_t* sSl = sSh + tile_bytes(128, 128);
-    uint8_t* sDh = sSl + tile_bytes(128, 128);
-    uint8_t* sDl = sDh + tile_bytes(128, 128);
-    uint8_t* sOh = sDl + tile_bytes(128, 128);      // dO, later Vd
-    uint8_t* sOl = sOh + tile_bytes(64, 128);
-    uint8_t* sXh = sOl + tile_bytes(64, 128);
-    uint8_t* sXl = sXh + tile_bytes(64, 128);
-    if (threadIdx.x == 0) { umma::mbar_init(&bar2, 1); umma::fence_barrier_init(); }
-
-    const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV, HK = p.L.HK;
-    const int hk = h / (HV / HK);
-    const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const size_t sbase = ((size_t)c * HV + h) * DK * DV;
-
-    // token-row loader: rows past the end are read from the last valid row and zeroed (keeps the loads branch-free)
-    auto rows = [&](const void* src, auto dt) {
-        return [=](int r, int k8, float (&v)[8]) {
-            const int rr = r < len ? r : len - 1;
-            load8(src, decltype(dt)::value, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, v);
-            if (r >= len) zero8(v);
-        };
-    };
-    using F32T = std::integral_constant<int, MKDA_F32>;
-    {
-        float vS[4][8], vO[2][8], vX[2][8];
-        load_chunks<4, 512, true>(vS, 128, 128, [&](int r, int k8, float (&v)[8]) { load8(p.h, MKDA_F32, sbase + (size_t)r * DV + k8 * 8, v); });
-        load_chunks<2, 512, true>(vO, 64, 128, rows(p.d_o, std::integral_constant<int, DODT>{}));
-        load_chunks<2, 512, true>(vX, 64, 128, rows(p.dX, F32T{}));
-        MKDA_TRACE_AT(0, 1);
-        store_chunks<4, 512, true>(sSh, sSl, vS, 128, 128);
-        store_chunks<2, 512, true>(sOh, sOl, vO, 64, 128);
-        store_chunks<2, 512, true>(sXh, sXl, vX, 64, 128);
-    }
-    MKDA_TRACE_AT(0, 2);
-    const uint32_t tmem = tc_operands_ready(&sh);
-    MKDA_TRACE_AT(0, 3);
-    if (umma::mma_issuer()) {
-        const umma::Opnd aS = umma::opnd_k(sSh, sSl, 128);
-        umma::gemm(tmem + 0, aS, umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
-        umma::gemm(tmem + 64, aS, umma::opnd_k(sXh, sXl, 64), 128, 64, 128, 0u);
-        umma::commit(&sh.bar);
-    }
-    {   // dS' tile + dgl (S is re-read from its operand tile: hi + lo carries 16 mantissa bits); Vd is fetched now and
-        // stored once the first two products no longer need the dO tile
-        float vD[4][8], vV[2][8];
-        load_chunks<4, 512, true>(vD, 128, 128, [&](int r, int k8, float (&v)[8]) { load8(p.dh, MKDA_F32, sbase + (size_t)r * DV + k8 * 8, v); });
-        load_chunks<2, 512, true>(vV, 64, 128, rows(p.Vd, F32T{}));
-#pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
-            const uint32_t off = umma::tile_chunk_offset(128, r, k8);
-            const uint4 sh4 = *reinterpret_cast<const uint4*>(sSh + off), sl4 = *reinterpret_cast<const uint4*>(sSl + off);
-            const uint32_t hw[4] = {sh4.x, sh4.y, sh4.z, sh4.w}, lw[4] = {sl4.x, sl4.y, sl4.z, sl4.w};
-            float pr = 0.f;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float s0 = __uint_as_float(hw[e] << 16) + __uint_as_float(lw[e] << 16);
-                const float s1 = __uint_as_float(hw[e] & 0xffff0000u) + __uint_as_float(lw[e] & 0xffff0000u);
-                pr += s0 * vD[n][2 * e] + s1 * vD[n][2 * e + 1];
-            }
-#pragma unroll
-            for (int o = 8; o > 0; o >>= 1) pr += __shfl_xor_sync(0xffffffffu, pr, o);
-            if ((lane & 15) == 0) sDgl[r] = pr;
-        }
-        MKDA_TRACE_AT(0, 4);
-        store_chunks<4, 512, true>(sDh, sDl, vD, 128, 128);
-        MKDA_TRACE_AT(0, 5);
-        umma::mbar_wait(&sh.bar, 0);
-        MKDA_TRACE_AT(0, 6);          // S dO^T and S dX^T done: the dO tile can be replaced by Vd
-        umma::fence_after_sync();
-        store_chunks<2, 512, true>(sOh, sOl, vV, 64, 128);
-    }
-    umma::fence_async_smem();
-    umma::fence_before_sync();
-    __syncthreads();
-    umma::fence_after_sync();
-    if (umma::mma_issuer()) {
-        umma::gemm(tmem + 128, umma::opnd_k(sDh, sDl, 128), umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
-        umma::commit(&bar2);
-    }
-    // epilogue inputs are fetched while the last product runs
-    const int kk = (warp & 3) * 32 + lane, t0 = (warp >> 2) * 16;
-    const float gL = p.g_c[((size_t)(start + len - 1) * HV + h) * 128 + kk];
-    float kv[16], gv[16], qv[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const int t = t0 + j < len ? t0 + j : len - 1;
-        const size_t tk = (size_t)(start + t) * HK + hk;
-        kv[j] = ld1(p.k, QKDT, tk * 128 + kk) * (p.k_rstd ? p.k_rstd[tk] : 1.f);
-        qv[j] = ld1(p.q, QKDT, tk * 128 + kk) * (p.q_rstd ? p.q_rstd[tk] : 1.f);
-        gv[j] = p.g_c[((size_t)(start + t) * HV + h) * 128 + kk];
-    }
-    MKDA_TRACE_AT(0, 7);
-    umma::mbar_wait(&bar2, 0);
-    umma::fence_after_sync();
-    MKDA_TRACE_AT(0, 8);
-
-    // ---- epilogue: thread = K index kk, 16 tokens per warp group ---------------------------------------------------
-    float aq[16], ak[16], ab[16];
-    umma::tmem_ld16(umma::tmem_addr(tmem, warp, t0), aq);
-    umma::tmem_ld16(umma::tmem_addr(tmem, warp, 64 + t0), ak);
-    umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + t0), ab);
-    float cs = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j)
-        if (t0 + j < len) cs += kv[j] * ex2f_(gL - gv[j]) * ab[j];
-    MKDA_TRACE_AT(0, 9);
-    sCol[warp >> 2][kk] = cs;
-    __syncthreads();
-    const float extra = ((sCol[0][kk] + sCol[1][kk]) + (sCol[2][kk] + sCol[3][kk])) + ex2f_(gL) * sDgl[kk];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const int t = t0 + j;
-        if (t >= len) continue;
-        const size_t off = ((size_t)(start + t) * HV + h) * 128 + kk;
-        const float up = ex2f_(gv[j]), re = ex2f_(gL - gv[j]);
-        const float dqt = p.scale * aq[j], dkt = -ak[j], dkb = ab[j];
-        float dg = qv[j] * up * dqt + kv[j] * up * dkt - kv[j] * re * dkb;
-        if (t == len - 1) dg += extra;
-        p.dq_p[off] = dqt * up;
-        p.dk_p[off] = dkt * up + dkb * re;
-        p.dg_p[off] = dg;
-    }
-    MKDA_TRACE_AT(0, 10);
-    tc_end(&sh, tmem, 256);
-    MKDA_TRACE_AT(0, 11);
-}
-
-template <int QKDT, int DODT>
-static int launch_bwd_sgrad_tc_t(const MkdaBwdSgrad* p, cudaStream_t stream) {
-    auto kern = bwd_sgrad_tc_kernel<QKDT, DODT>;
-    if (int e = ensure_smem((const void*)kern, SG_TC_SMEM, "bwd_sgrad")) return e;
-    kern<<<dim3(p->L.NC, p->L.HV), 512, SG_TC_SMEM, stream>>>(*p);
-    return check_launch("bwd_sgrad");
-}
-int launch_bwd_sgrad_tc(const MkdaBwdSgrad* p, cudaStream_t stream) {
-    MKDA_DISPATCH2(launch_bwd_sgrad_tc_t, p->qk_dtype, p->do_dtype, p, stream)
-}
 
 }  // namespace mkda
 
@@ -436,7 +276,7 @@ __device__ __forceinline__ void load_tile8(const uint8_t* hi, const uint8_t* lo,
 //   dW = A^T dVd        dX = diag(beta) dW (= dV)       dbeta_w = rowsum(dW * X)
 //   dA = (dVd X^T) diag(beta)          dL = -strictlower(A^T dA A^T)
 // Six dependent products, each with a 128-wide axis on M (TMEM columns in brackets):
-//   G1 [0]    X^T[v x tok]  = V^T - S^T k~^T                       (A = S tile read MN-major)
+//   G1 [0]    X^T[v x tok]  = V^T - S^T k~^T                       (A = the saved state tile as it is)
 //   G2 [64]   Vd^T[v x i]   = X^T (A diag(beta))^T
 //   G4 [256]  dW^T[v x j]   = dVd^T A                              (both operands MN-major views of natural tiles)
 //   G3 [128]  [dO; dVd] [Vd; X]^T  -> rows 0..63 / cols 0..63 = dO Vd^T, rows 64..127 / cols 64..127 = dVd X^T
@@ -473,13 +313,16 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;      // TMEM lane owned by this thread, 16-column group
-    const size_t sbase = ((size_t)c * HV + h) * DK * DV;
     uint32_t phase = 0;
 
     if (tid < CH) sBeta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
+    __shared__ uint64_t ldbar;
+    if (tid == 0) umma::fetch_state_tile(&ldbar, sSh, p.h, (size_t)c * HV + h);      // S^T [v][K index], ready-made operand
+    // everything the first three stages need from global memory is requested up front: k, g, A, then [dO; dVd] rows and
+    // this thread's V column, which stay in registers until G1 has released the state tile
+    float vT[4][8], vv[16];
     {
-        float vS[4][8], vK[2][8], vG[2][8], vA[1][8];
-        load_chunks<4, 512, true>(vS, 128, 128, [&](int r, int k8, float (&v)[8]) { load8(p.h, MKDA_F32, sbase + (size_t)r * DV + k8 * 8, v); });
+        float vK[2][8], vG[2][8], vA[1][8];
         load_chunks<2, 512, true>(vK, 64, 128, [&](int r, int k8, float (&v)[8]) {
             const int rr = r < len ? r : len - 1;
             load8(p.k, KVDT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, v);
@@ -492,8 +335,17 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
             const int rr = r < len ? r : len - 1;
             load8(p.A, MKDA_F32, ((size_t)(start + rr) * HV + h) * 64 + k8 * 8, v);
         });
+        load_chunks<4, 512, true>(vT, 128, 128, [&](int r, int k8, float (&v)[8]) {
+            const int t = r & 63, tt = t < len ? t : len - 1;
+            const size_t off = ((size_t)(start + tt) * HV + h) * 128 + k8 * 8;
+            if (r < 64) load8(p.d_o, DODT, off, v); else load8(p.dVd, MKDA_F32, off, v);
+        });
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int t = cg * 16 + j, tt = t < len ? t : len - 1;
+            vv[j] = ld1(p.v, KVDT, ((size_t)(start + tt) * HV + h) * 128 + row);
+        }
         MKDA_TRACE_AT(1, 1);
-        store_chunks<4, 512, true>(sSh, sSl, vS, 128, 128);
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
             const int i = tid + n * 512, r = i >> 4;
@@ -516,24 +368,17 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     MKDA_TRACE_AT(1, 2);
     const uint32_t tmem = tc_operands_ready(&sh);
     if (umma::mma_issuer()) {
-        umma::gemm(tmem + 0, umma::opnd_mn(sSh, sSl, 128), umma::opnd_k(sKh, sKl, 64), 128, 64, 128, 0u);
+        umma::mbar_wait(&ldbar, 0);                        // the state tile has landed
+        umma::gemm(tmem + 0, umma::opnd_k(sSh, sSl, 128), umma::opnd_k(sKh, sKl, 64), 128, 64, 128, 0u);
         umma::commit(&sh.bar);
     }
-    {   // fetch what the next stages need while G1 runs: [dO; dVd] rows and this thread's V column
-        float vT[4][8];
-        load_chunks<4, 512, true>(vT, 128, 128, [&](int r, int k8, float (&v)[8]) {
-            const int t = r & 63, tt = t < len ? t : len - 1;
-            const size_t off = ((size_t)(start + tt) * HV + h) * 128 + k8 * 8;
-            if (r < 64) load8(p.d_o, DODT, off, v); else load8(p.dVd, MKDA_F32, off, v);
-            if (t >= len) zero8(v);
-        });
-        float vv[16];
+    {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const int t = cg * 16 + j, tt = t < len ? t : len - 1;
-            vv[j] = ld1(p.v, KVDT, ((size_t)(start + tt) * HV + h) * 128 + row);
-            if (t >= len) vv[j] = 0.f;
-        }
+        for (int n = 0; n < 4; ++n)
+            if ((((tid + n * 512) >> 4) & 63) >= len) zero8(vT[n]);
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (cg * 16 + j >= len) vv[j] = 0.f;
         MKDA_TRACE_AT(1, 3);
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;
         umma::fence_after_sync();

@@ -264,216 +264,27 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// bwd_intra.  With E_ij = 2^(g_i - g_j) per channel (i > j), Wq = scale strictlower(dAqk), dLs = strictlower(dL):
+// bwd_tail: every gradient that is local to a (chunk, v-head) once the state gradients are known.
+// State part.  With S / dS' the state entering / state-gradient leaving the chunk, up = 2^g, rest = 2^(g_L - g):
+//   dq~ = scale dO S^T     dk~ = -dX S^T     dkbar = Vd dS'^T     dgl = rowsum_v(S * dS')
+//   dq_p = dq~ up          dk_p = dk~ up + dkbar rest
+//   dg_p = q~ dq~ + k~ dk~ - kbar dkbar;   last valid row += colsum(kbar dkbar) + gl dgl
+// Intra-chunk part.  With E_ij = 2^(g_i - g_j) per channel (i > j), Wq = scale strictlower(dAqk), dLs = strictlower(dL):
 //   dq_row_i = sum_j Wq_ij k_j E_ij                     T_i = sum_j dLs_ij k_j E_ij
 //   dk_col_j = sum_i (Wq_ij q_i + beta_i dLs_ij k_i) E_ij
 //   dq = dq_p + dq_row + scale dAqk_ii k       dk = dk_p + beta T + dk_col + scale dAqk_ii q
 //   dg' = dg_p + q dq_row + k beta T - k dk_col           dbeta_g = sum_c k T
-// E_ij is factored through the anchor a of i's 16-row block exactly as in the forward kernel.
-// Channels go on M.  Per row block I (anchor a = 16 I):
+// E_ij is factored through the anchor a of i's 16-row block exactly as in the forward kernel.  Channels go on M.  Per row
+// block I (anchor a = 16 I):
 //   row terms   R_I^T[c][r]  = sum_j Kc_I[j][c] W[16 I + r][j]       W = Wq (-> dq_row) or dLs (-> T); N = 16 each
-//   col terms   C_I^T[c][j]  = sum_{i in I} Qr[i][c] Wq[i][j] + Kr[i][c] (beta dLs)[i][j]              N = 64
+//   col terms   C_I^T[c][j]  = sum_{i in I} Qr[i][c] Wq[i][j] + Kr[i][c] (beta dLs)[i][j]      N = 16 (I + 1)
 // then per thread (channel c, row block cg): dq_row = R 2^(g_i - g_a), T likewise, dk_col[j] = sum_{I >= cg} C_I 2^(g_aI - g_j).
-// All A operands are MN-major views of the untransposed Kc / [Kr; Qr] tiles.
-// ---------------------------------------------------------------------------------------------------------
-constexpr int INTRA_BWD_TC_SMEM = OPND_BYTES + 3 * 16384 + 1024;
-
-template <int DT>
-__global__ void __launch_bounds__(512, 1) bwd_intra_tc_kernel(const MkdaBwdIntra p) {
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ IntraShared sh;
-    __shared__ float sDiag[CH];
-    __shared__ float sRed[4][CH];
-    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sKQ = base + KQ_OFF;
-    uint8_t* sWq = base + OPND_BYTES;                  // scale strictlower(dAqk) [i][j], hi 8 KB + lo 8 KB
-    uint8_t* sDl = sWq + 16384;                        // strictlower(dL)
-    uint8_t* sBd = sDl + 16384;                        // diag(beta) strictlower(dL)
-    float* sG = reinterpret_cast<float*>(sWq);         // [64][128] fp32 cumsum tile while the Kc / KQ operands are built
-
-    const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV, HK = p.L.HK;
-    const int hk = h / (HV / HK);
-    const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
-
-    MKDA_TRACE_AT(4, 0);
-    if (warp == 0) umma::tmem_alloc(&sh.tmem, 512);
-    if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
-    if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
-
-    float vk[2][8], vq[2][8], vg[2][8], rk[2], rq[2], wa[8], wl[8];
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-        const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-        const size_t tk = (size_t)(start + rr) * HK + hk;
-        ldg8(p.k, DT, tk * 128 + k8 * 8, vk[n]);
-        ldg8(p.q, DT, tk * 128 + k8 * 8, vq[n]);
-        ldg8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vg[n]);
-        rk[n] = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
-        rq[n] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
-    }
-    {
-        const int i = tid >> 3, k8 = tid & 7, ii = i < len ? i : len - 1;
-        const size_t o = ((size_t)(start + ii) * HV + h) * 64 + k8 * 8;
-        ldg8(p.dAqk, MKDA_F32, o, wa);
-        ldg8(p.dL, MKDA_F32, o, wl);
-    }
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-        const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
-        *reinterpret_cast<float4*>(sG + r * 128 + k8 * 8) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
-        *reinterpret_cast<float4*>(sG + r * 128 + k8 * 8 + 4) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) { vk[n][e] *= rk[n]; vq[n][e] *= rq[n]; }
-    }
-    MKDA_TRACE_AT(4, 1);
-    umma::fence_before_sync();
-    __syncthreads();
-    umma::fence_after_sync();
-    const uint32_t tmem = sh.tmem;
-    MKDA_TRACE_AT(4, 2);
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-        const int i = tid + n * 512, r = i >> 4, k8 = i & 15, I0 = r >> 4;
-        float ga[8], t8[8];
-        lds8(sG + (16 * I0) * 128 + k8 * 8, ga);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(vg[n][e] - ga[e]);
-        store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + (r & 15), k8, t8);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) t8[e] = vq[n][e] * ex2f_(vg[n][e] - ga[e]);
-        store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + 16 + (r & 15), k8, t8);
-#pragma unroll
-        for (int I = 0; I < 4; ++I) {
-            if (I < I0) continue;
-            if (I > I0) lds8(sG + (16 * I) * 128 + k8 * 8, ga);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(ga[e] - vg[n][e]);
-            store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
-        }
-    }
-    MKDA_TRACE_AT(4, 3);
-    __syncthreads();                                   // the cumsum tile is dead: its space becomes the W tiles
-    {
-        const int i = tid >> 3, k8 = tid & 7;
-        const float bt = sh.beta[i];
-        float w8[8], d8[8], b8[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const int j = k8 * 8 + e;
-            const bool lo = j < i && i < len;
-            w8[e] = lo ? p.scale * wa[e] : 0.f;
-            d8[e] = lo ? wl[e] : 0.f;
-            b8[e] = bt * d8[e];
-            if (j == i) sDiag[i] = i < len ? p.scale * wa[e] : 0.f;
-        }
-        store_split8(sWq, sWq + 8192, 64, i, k8, w8);
-        store_split8(sDl, sDl + 8192, 64, i, k8, d8);
-        store_split8(sBd, sBd + 8192, 64, i, k8, b8);
-    }
-    MKDA_TRACE_AT(4, 4);
-    publish();
-    if (umma::mma_issuer()) {
-#pragma unroll
-        for (int I = 0; I < 4; ++I) {
-            const umma::Opnd aKc = umma::opnd_mn(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1));
-            umma::gemm(tmem + 32 * I, aKc, umma::opnd_k(sWq, sWq + 8192, 64, 16 * I), 128, 16, 16 * (I + 1), 0u);
-            umma::gemm(tmem + 32 * I + 16, aKc, umma::opnd_k(sDl, sDl + 8192, 64, 16 * I), 128, 16, 16 * (I + 1), 0u);
-            umma::gemm(tmem + 128 + 64 * I, umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I + 16), umma::opnd_mn(sWq, sWq + 8192, 64, 16 * I),
-                       128, 64, 16, 0u);
-            umma::gemm(tmem + 128 + 64 * I, umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I), umma::opnd_mn(sBd, sBd + 8192, 64, 16 * I),
-                       128, 64, 16, 1u);
-        }
-        umma::commit(&sh.bar);
-    }
-    // epilogue inputs for (channel `row`, rows 16 cg .. 16 cg + 15) are fetched while the products run
-    float kq[16], qq[16], gg[16], pq[16], pk[16], pg[16], ga[4];
-#pragma unroll
-    for (int r = 0; r < 16; ++r) {
-        const int i = 16 * cg + r, ii = i < len ? i : len - 1;
-        const size_t tk = (size_t)(start + ii) * HK + hk, off = ((size_t)(start + ii) * HV + h) * 128 + row;
-        kq[r] = ld1(p.k, DT, tk * 128 + row) * (p.k_rstd ? p.k_rstd[tk] : 1.f);
-        qq[r] = ld1(p.q, DT, tk * 128 + row) * (p.q_rstd ? p.q_rstd[tk] : 1.f);
-        gg[r] = p.g_c[off];
-        pq[r] = p.dq_p[off]; pk[r] = p.dk_p[off]; pg[r] = p.dg_p[off];
-    }
-#pragma unroll
-    for (int I = 0; I < 4; ++I) {
-        const int a = 16 * I < len ? 16 * I : len - 1;
-        ga[I] = p.g_c[((size_t)(start + a) * HV + h) * 128 + row];
-    }
-    MKDA_TRACE_AT(4, 5);
-    umma::mbar_wait(&sh.bar, 0);
-    umma::fence_after_sync();
-    MKDA_TRACE_AT(4, 6);
-    float v[32], dkc[16];
-    umma::tmem_ld32(umma::tmem_addr(tmem, warp, 32 * cg), v);
-#pragma unroll
-    for (int r = 0; r < 16; ++r) dkc[r] = 0.f;
-#pragma unroll
-    for (int I = 0; I < 4; ++I) {
-        if (I < cg) continue;                          // warp-uniform
-        float c16[16];
-        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + 64 * I + 16 * cg), c16);
-#pragma unroll
-        for (int r = 0; r < 16; ++r) dkc[r] += c16[r] * ex2f_(ga[I] - gg[r]);
-    }
-#pragma unroll
-    for (int r = 0; r < 16; ++r) {
-        const int i = 16 * cg + r;
-        const float e = ex2f_(gg[r] - ga[cg]);
-        const float dqr = v[r] * e, T = v[16 + r] * e, bt = sh.beta[i], dgn = sDiag[i];
-        float bs = kq[r] * T;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, o);
-        if (lane == 0) sRed[q][i] = bs;
-        if (i < len) {
-            const size_t off = ((size_t)(start + i) * HV + h) * 128 + row;
-            p.dq_v[off] = pq[r] + dqr + dgn * kq[r];
-            p.dk_v[off] = pk[r] + bt * T + dkc[r] + dgn * qq[r];
-            p.dgp[off] = pg[r] + qq[r] * dqr + kq[r] * bt * T - kq[r] * dkc[r];
-        }
-    }
-    MKDA_TRACE_AT(4, 7);
-    __syncthreads();
-    if (tid < len) {
-        const size_t th = (size_t)(start + tid) * HV + h;
-        float db = p.dbeta_w[th] + ((sRed[0][tid] + sRed[1][tid]) + (sRed[2][tid] + sRed[3][tid]));
-        if (p.beta_sigmoid) {
-            const float sg = sigmoidf_(ld1(p.beta_raw, p.beta_dtype, th));
-            db *= p.beta_scale * sg * (1.f - sg);
-        }
-        st1(p.dbeta, p.dbeta_dtype, th, db);
-    }
-    MKDA_TRACE_AT(4, 8);
-    umma::fence_before_sync();
-    __syncthreads();
-    if (warp == 0) umma::tmem_dealloc(tmem, 512);
-}
-
-template <int DT>
-static int launch_bwd_intra_tc_t(const MkdaBwdIntra* p, cudaStream_t stream) {
-    auto kern = bwd_intra_tc_kernel<DT>;
-    if (int e = ensure_smem((const void*)kern, INTRA_BWD_TC_SMEM, "bwd_intra")) return e;
-    kern<<<dim3(p->L.NC, p->L.HV), 512, INTRA_BWD_TC_SMEM, stream>>>(*p);
-    return check_launch("bwd_intra");
-}
-int launch_bwd_intra_tc(const MkdaBwdIntra* p, cudaStream_t stream) {
-    switch (p->qk_dtype) {
-        case MKDA_F32: return launch_bwd_intra_tc_t<MKDA_F32>(p, stream);
-        case MKDA_BF16: return launch_bwd_intra_tc_t<MKDA_BF16>(p, stream);
-        case MKDA_F16: return launch_bwd_intra_tc_t<MKDA_F16>(p, stream);
-    }
-    return set_error(MKDA_ERR_ARG, "bwd_intra: unsupported dtype");
-}
-
-// ---------------------------------------------------------------------------------------------------------
-// bwd_tail = bwd_sgrad followed by bwd_intra for the same (chunk, v-head), in one CTA.  The three state products
+// All A operands are MN-major views of the untransposed Kc / [Kr; Qr] tiles and of the saved state tiles.
+//
+// The three state products
 //   Dq^T[c][t] = S dO^T      Dk^T[c][t] = S dX^T      Db^T[c][t] = dS' Vd^T         (channels c on M, K = 128 over v)
 // stay in tensor memory while the CTA rebuilds the intra-chunk operands over the dead state tiles and issues the
-// row / column products of bwd_intra; one epilogue then combines all of them per (channel, row) and writes dq_v, dk_v and
-// dgp once.  Column products use N = 16 (I + 1) (only columns j < 16 (I + 1) of row block I are non-zero).
+// row / column products; one epilogue then combines all of them per (channel, row) and writes dq_v, dk_v and dgp once.
 // TMEM columns: Dq 0, Dk 64, Db 128, R_I 192 + 32 I, C_I 320 + {0, 16, 48, 96}.
 // ---------------------------------------------------------------------------------------------------------
 constexpr int TAIL_SMEM = 192 * 1024 + 1024;
@@ -487,11 +298,13 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     __shared__ float sRed[4][CH];
     __shared__ float sDgl[DK];
     __shared__ float sCol[4][DK];
+    __shared__ __align__(16) float sPart[16][DK];
+    __shared__ uint64_t ldS, ldD;
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     // state phase
-    uint8_t* sSh = base;                               // S [kidx][v]
+    uint8_t* sSh = base;                               // state tile S^T [v][K index] (hi, lo)
     uint8_t* sSl = base + 32768;
-    uint8_t* sTh = base + 65536;                       // dS'
+    uint8_t* sTh = base + 65536;                       // state tile dS'^T
     uint8_t* sTl = base + 98304;
     uint8_t* sOh = base + 131072;                      // dO [tok][v], later Vd
     uint8_t* sOl = base + 147456;
@@ -509,106 +322,41 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
-    const size_t sbase = ((size_t)c * HV + h) * DK * DV;
 
     if (warp == 0) umma::tmem_alloc(&sh.tmem, 512);
     if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
     if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
     MKDA_TRACE_AT(5, 0);
 
-    // ---- state phase 1: S, dO, dX -------------------------------------------------------------------------------
+    // ---- state phase: the two state tiles arrive by asynchronous copy; dO, dX, Vd go through registers ----------------
+    if (tid == 0) {
+        umma::fetch_state_tile(&ldS, sSh, p.h, (size_t)c * HV + h);
+        umma::fetch_state_tile(&ldD, sTh, p.dh, (size_t)c * HV + h);
+    }
+    float vV[2][8];
     {
-        float vS[4][8], vO[2][8], vX[2][8];
-#pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            const int i = tid + n * 512;
-            ldg8(p.h, MKDA_F32, sbase + (size_t)(i >> 4) * DV + (i & 15) * 8, vS[n]);
-        }
+        float vO[2][8], vX[2][8];
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
             const int i = tid + n * 512, r = i >> 4, rr = r < len ? r : len - 1;
             const size_t off = ((size_t)(start + rr) * HV + h) * 128 + (i & 15) * 8;
             ldg8(p.d_o, DODT, off, vO[n]);
             ldg8(p.dX, MKDA_F32, off, vX[n]);
-        }
-#pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            const int i = tid + n * 512;
-            store_split8(sSh, sSl, 128, i >> 4, i & 15, vS[n]);
+            ldg8(p.Vd, MKDA_F32, off, vV[n]);
         }
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
             const int i = tid + n * 512, r = i >> 4;
             if (r >= len) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) vO[n][e] = vX[n][e] = 0.f;
+                for (int e = 0; e < 8; ++e) vO[n][e] = vX[n][e] = vV[n][e] = 0.f;
             }
             store_split8(sOh, sOl, 64, r, i & 15, vO[n]);
             store_split8(sXh, sXl, 64, r, i & 15, vX[n]);
         }
     }
     MKDA_TRACE_AT(5, 1);
-    publish();
-    const uint32_t tmem = sh.tmem;
-    MKDA_TRACE_AT(5, 2);
-    if (umma::mma_issuer()) {
-        const umma::Opnd aS = umma::opnd_k(sSh, sSl, 128);
-        umma::gemm(tmem + 0, aS, umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
-        umma::gemm(tmem + 64, aS, umma::opnd_k(sXh, sXl, 64), 128, 64, 128, 0u);
-        umma::commit(&sh.bar);
-    }
-    // ---- state phase 2: dS', Vd, and dgl[c] = sum_v S[c][v] dS'[c][v] (S re-read from its hi + lo tile) ---------------
-    {
-        float vD[4][8], vV[2][8];
-#pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            const int i = tid + n * 512;
-            ldg8(p.dh, MKDA_F32, sbase + (size_t)(i >> 4) * DV + (i & 15) * 8, vD[n]);
-        }
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            const int i = tid + n * 512, r = i >> 4, rr = r < len ? r : len - 1;
-            ldg8(p.Vd, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + (i & 15) * 8, vV[n]);
-        }
-#pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
-            const uint32_t off = umma::tile_chunk_offset(128, r, k8);
-            const uint4 sh4 = *reinterpret_cast<const uint4*>(sSh + off), sl4 = *reinterpret_cast<const uint4*>(sSl + off);
-            const uint32_t hw[4] = {sh4.x, sh4.y, sh4.z, sh4.w}, lw[4] = {sl4.x, sl4.y, sl4.z, sl4.w};
-            float pr = 0.f;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float s0 = __uint_as_float(hw[e] << 16) + __uint_as_float(lw[e] << 16);
-                const float s1 = __uint_as_float(hw[e] & 0xffff0000u) + __uint_as_float(lw[e] & 0xffff0000u);
-                pr += s0 * vD[n][2 * e] + s1 * vD[n][2 * e + 1];
-            }
-#pragma unroll
-            for (int o = 8; o > 0; o >>= 1) pr += __shfl_xor_sync(0xffffffffu, pr, o);
-            if ((lane & 15) == 0) sDgl[r] = pr;
-            store_split8(sTh, sTl, 128, r, k8, vD[n]);
-        }
-        umma::mbar_wait(&sh.bar, 0);                   // S dO^T and S dX^T done: the dO tile can be replaced by Vd
-    MKDA_TRACE_AT(5, 3);
-        umma::fence_after_sync();
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            const int i = tid + n * 512, r = i >> 4;
-            if (r >= len) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) vV[n][e] = 0.f;
-            }
-            store_split8(sOh, sOl, 64, r, i & 15, vV[n]);
-        }
-    }
-    publish();
-    if (umma::mma_issuer()) {
-        umma::gemm(tmem + 128, umma::opnd_k(sTh, sTl, 128), umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
-        umma::commit(&sh.bar);
-    }
-    MKDA_TRACE_AT(5, 4);
-
-    // ---- intra phase: fetch k, q, g and the two 64 x 64 weights while the last state product runs ---------------------
+    // intra phase inputs (k, q, g and the two 64 x 64 weights) are requested now and consumed after the state products
     float vk[2][8], vq[2][8], vg[2][8], rk[2], rq[2], wa[8], wl[8];
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
@@ -625,6 +373,67 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         const size_t o = ((size_t)(start + ii) * HV + h) * 64 + k8 * 8;
         ldg8(p.dAqk, MKDA_F32, o, wa);
         ldg8(p.dL, MKDA_F32, o, wl);
+    }
+    publish();
+    const uint32_t tmem = sh.tmem;
+    MKDA_TRACE_AT(5, 2);
+    if (umma::mma_issuer()) {
+        umma::mbar_wait(&ldS, 0);
+        const umma::Opnd aS = umma::opnd_mn(sSh, sSl, 128);          // A(m = K index, k = v) of the [v][K index] tile
+        umma::gemm(tmem + 0, aS, umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
+        umma::gemm(tmem + 64, aS, umma::opnd_k(sXh, sXl, 64), 128, 64, 128, 0u);
+        umma::commit(&sh.bar);
+    }
+    {   // dgl[c] = sum_v S[c][v] dS'[c][v] from the two tiles: chunk (v row, 8 channels) per thread, four rows each
+        umma::mbar_wait(&ldS, 0);
+        umma::mbar_wait(&ldD, 0);
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const int i = tid + n * 512;
+            const uint32_t off = umma::tile_chunk_offset(128, i >> 4, i & 15);
+            const uint4 a4 = *reinterpret_cast<const uint4*>(sSh + off), b4 = *reinterpret_cast<const uint4*>(sSl + off);
+            const uint4 c4 = *reinterpret_cast<const uint4*>(sTh + off), d4 = *reinterpret_cast<const uint4*>(sTl + off);
+            const uint32_t ah[4] = {a4.x, a4.y, a4.z, a4.w}, al[4] = {b4.x, b4.y, b4.z, b4.w};
+            const uint32_t dh[4] = {c4.x, c4.y, c4.z, c4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float s0 = __uint_as_float(ah[e] << 16) + __uint_as_float(al[e] << 16);
+                const float s1 = __uint_as_float(ah[e] & 0xffff0000u) + __uint_as_float(al[e] & 0xffff0000u);
+                const float d0 = __uint_as_float(dh[e] << 16) + __uint_as_float(dl[e] << 16);
+                const float d1 = __uint_as_float(dh[e] & 0xffff0000u) + __uint_as_float(dl[e] & 0xffff0000u);
+                acc[2 * e] = fmaf(s0, d0, acc[2 * e]);
+                acc[2 * e + 1] = fmaf(s1, d1, acc[2 * e + 1]);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 16);
+        if (lane < 16) {
+            *reinterpret_cast<float4*>(&sPart[warp][lane * 8]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            *reinterpret_cast<float4*>(&sPart[warp][lane * 8 + 4]) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        }
+    }
+    umma::mbar_wait(&sh.bar, 0);                       // S dO^T and S dX^T done: the dO tile can be replaced by Vd
+    MKDA_TRACE_AT(5, 3);
+    umma::fence_after_sync();
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+        const int i = tid + n * 512;
+        store_split8(sOh, sOl, 64, i >> 4, i & 15, vV[n]);
+    }
+    publish();
+    if (umma::mma_issuer()) {
+        umma::gemm(tmem + 128, umma::opnd_mn(sTh, sTl, 128), umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
+        umma::commit(&sh.bar);
+    }
+    MKDA_TRACE_AT(5, 4);
+    if (tid < DK) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 16; ++w) t += sPart[w][tid];
+        sDgl[tid] = t;
     }
 #pragma unroll
     for (int n = 0; n < 2; ++n) {                      // the dX tile is dead since the first wait

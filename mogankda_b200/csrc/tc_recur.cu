@@ -144,20 +144,15 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
             if (t >= len) uu[j] = 0.f;
         }
         __syncthreads();                                   // sh.gl[buf] and the tiles of `buf` are complete
-        {   // state entering the chunk: operand tile, optional global copy, decay
+        {   // state entering the chunk: operand tile (optionally saved as it is by the issuing thread below), decay
             float s[32];
             umma::tmem_ld32(umma::tmem_addr(tmem, warp, cg * 32), s);
-            float* hc = (p.h && !trans) ? p.h + ((size_t)c * HV + h) * DK * DV + row : nullptr;   // [K][V]: coalesced over v
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 float v8[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) v8[e] = s[i * 8 + e];
                 store_split8(sAh, sAl, 128, row, cg * 4 + i, v8);
-                if (hc) {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) hc[(size_t)(cg * 32 + i * 8 + e) * DV] = v8[e];
-                }
             }
 #pragma unroll
             for (int j = 0; j < 32; ++j) s[j] *= sh.gl[buf][cg * 32 + j];
@@ -166,7 +161,12 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
         }
         publish_operands();
         if (umma::mma_issuer()) {
+            // The operand tile doubles as the saved state of this chunk: one asynchronous 64 KB copy.  The commit is issued
+            // after the copy has read the tile, so the barrier also covers it (the tile is overwritten with Vd^T next).
+            const bool save = p.h && !trans;
+            if (save) umma::bulk_store(reinterpret_cast<uint8_t*>(p.h) + ((size_t)c * HV + h) * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
             umma::gemm(tmem + 128, umma::opnd_k(sAh, sAl, 128), umma::opnd_k(sW[buf], sW[buf] + 16384, 64), 128, 64, 128, 0u);
+            if (save) umma::bulk_store_wait_read();
             umma::commit(&sh.bar);
         }
         float k[2][8], g[2][8], gL[2][8], rs[2];
@@ -354,18 +354,14 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
             }
         }
         __syncthreads();                                   // sh.gl
-        {   // gradient leaving the chunk: operand tile, global copy ([K][V]), decay
+        {   // gradient leaving the chunk: operand tile (saved as it is by the issuing thread below), decay
             float s[32];
             umma::tmem_ld32(umma::tmem_addr(tmem, warp, cg * 32), s);
-            float* dhc = p.dh + ((size_t)c * HV + h) * DK * DV + row;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 float v8[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    v8[e] = s[i * 8 + e];
-                    dhc[(size_t)(cg * 32 + i * 8 + e) * DV] = v8[e];
-                }
+                for (int e = 0; e < 8; ++e) v8[e] = s[i * 8 + e];
                 store_split8(sAh, sAl, 128, row, cg * 4 + i, v8);
             }
 #pragma unroll
@@ -376,7 +372,9 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
         publish_operands();
         if (umma::mma_issuer()) {
             umma::gemm(tmem + 128, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sAq, sAq + 8192, 64), 128, 64, 64, 0u);
+            umma::bulk_store(reinterpret_cast<uint8_t*>(p.dh) + ((size_t)c * HV + h) * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
             umma::gemm(tmem + 128, umma::opnd_k(sAh, sAl, 128), umma::opnd_k(sKb, sKb + 16384, 64), 128, 64, 128, 1u);
+            umma::bulk_store_wait_read();         // before the commit: the barrier then also covers the saved tile
             umma::commit(&sh.bar);
         }
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;

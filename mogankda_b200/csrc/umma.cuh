@@ -205,6 +205,35 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     return false;
 }
 
+// ---- bulk copies of whole operand tiles ---------------------------------------------------------------------------
+// Per-chunk states travel between kernels as ready-made operand tiles ("state tile": hi tile then lo tile of the
+// transposed state, rows = v, K-major over the K index, 2 x 32 KB), so a consumer fills its shared-memory operand with one
+// asynchronous copy and no register staging, and the producer writes it straight from the tile it built for its own MMA.
+constexpr uint32_t STATE_TILE_BYTES = 65536;
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// global -> shared, completion counted in bytes on `bar`; addresses 16-byte aligned, size a multiple of 16
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// shared -> global; the source must stay untouched until bulk_store_wait_read() returns in the issuing thread
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" :: "l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
+// One thread: initialise `bar` and start the asynchronous fetch of state tile `idx` of the array `tiles` into `smem_dst`
+// (1024-byte aligned).  Waiters use mbar_wait(bar, 0) after a CTA-wide barrier that follows this call.
+__device__ __forceinline__ void fetch_state_tile(uint64_t* bar, void* smem_dst, const void* tiles, size_t idx) {
+    mbar_init(bar, 1);
+    fence_barrier_init();
+    mbar_expect_tx(bar, STATE_TILE_BYTES);
+    bulk_load(smem_dst, static_cast<const uint8_t*>(tiles) + idx * STATE_TILE_BYTES, STATE_TILE_BYTES, bar);
+}
+
 // ---- tensor memory -------------------------------------------------------------------------------------------
 // one full warp allocates `ncols` (power of two >= 32) columns and publishes the base address through `slot`
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t ncols) {

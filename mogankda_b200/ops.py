@@ -241,42 +241,9 @@ def bwd_wy(lay, k, v, k_rstd, g_c, beta_e, A, h, d_o, dVd, HK, HV):
     return Vd, dX, dbeta_w, dAqk, dL
 
 
-def bwd_sgrad(lay, q, k, q_rstd, k_rstd, g_c, d_o, dX, Vd, h, dh, scale, HK, HV):
-    dev = q.device
-    z = lambda: torch.empty(lay.TT, HV, 128, dtype=torch.float32, device=dev)      # noqa: E731
-    dq_p, dk_p, dg_p = z(), z(), z()
-    p = STRUCTS["MkdaBwdSgrad"]()
-    p.L = _layout_struct(lay, HK, HV)
-    p.q, p.k, p.qk_dtype, p.q_rstd, p.k_rstd = _ptr(q), _ptr(k), _dt(q), _ptr(q_rstd), _ptr(k_rstd)
-    p.g_c, p.d_o, p.do_dtype, p.dX, p.Vd = _ptr(g_c), _ptr(d_o), _dt(d_o), _ptr(dX), _ptr(Vd)
-    p.h, p.dh, p.scale = _ptr(h), _ptr(dh), scale
-    p.dq_p, p.dk_p, p.dg_p = _ptr(dq_p), _ptr(dk_p), _ptr(dg_p)
-    _lib.call("mkda_bwd_sgrad", p, _stream())
-    return dq_p, dk_p, dg_p
-
-
-def bwd_intra(lay, q, k, q_rstd, k_rstd, g_c, beta_e, dAqk, dL, dq_p, dk_p, dg_p, dbeta_w, scale, HK, HV,
-              beta_raw, beta_sigmoid, beta_scale):
-    dev = q.device
-    alloc = torch.empty if lay.covers_all else torch.zeros
-    z = lambda: alloc(lay.TT, HV, 128, dtype=torch.float32, device=dev)      # noqa: E731
-    dq_v, dk_v, dgp = z(), z(), z()
-    dbeta = alloc(lay.TT, HV, dtype=beta_raw.dtype, device=dev)
-    p = STRUCTS["MkdaBwdIntra"]()
-    p.L = _layout_struct(lay, HK, HV)
-    p.q, p.k, p.qk_dtype, p.q_rstd, p.k_rstd = _ptr(q), _ptr(k), _dt(q), _ptr(q_rstd), _ptr(k_rstd)
-    p.g_c, p.beta, p.dAqk, p.dL = _ptr(g_c), _ptr(beta_e), _ptr(dAqk), _ptr(dL)
-    p.dq_p, p.dk_p, p.dg_p, p.dbeta_w, p.scale = _ptr(dq_p), _ptr(dk_p), _ptr(dg_p), _ptr(dbeta_w), scale
-    p.beta_raw, p.beta_dtype = _ptr(beta_raw), _dt(beta_raw)
-    p.beta_sigmoid, p.beta_scale = int(beta_sigmoid), float(beta_scale)
-    p.dq_v, p.dk_v, p.dgp, p.dbeta, p.dbeta_dtype = _ptr(dq_v), _ptr(dk_v), _ptr(dgp), _ptr(dbeta), _dt(dbeta)
-    _lib.call("mkda_bwd_intra", p, _stream())
-    return dq_v, dk_v, dgp, dbeta
-
-
 def bwd_tail(lay, q, k, q_rstd, k_rstd, g_c, beta_e, d_o, dX, Vd, h, dh, dAqk, dL, dbeta_w, scale, HK, HV,
              beta_raw, beta_sigmoid, beta_scale):
-    """bwd_sgrad + bwd_intra fused: the row-local partial gradients never leave the chip."""
+    """Gradients local to a (chunk, v-head): through the states and through the intra-chunk blocks, in one kernel."""
     dev = q.device
     alloc = torch.empty if lay.covers_all else torch.zeros
     z = lambda: alloc(lay.TT, HV, 128, dtype=torch.float32, device=dev)      # noqa: E731

@@ -85,3 +85,34 @@ def run(fn, lv, do, dht, opts, epi, *, f64=False, vfirst=False, grads=True, **ex
 def compare(got, ref):
     for n, r in ref.items():
         check(n, got[n], r)
+
+
+# ---- state tiles (include/mkda.h, MKDA_STATE_TILE_BYTES): an independent torch restatement of the layout ------------------
+def _state_tile_index():
+    """int64 [128 (K index), 128 (v)] -> position, in bf16 elements, inside one 32 KB half of a state tile."""
+    kk = torch.arange(128).view(128, 1)
+    v = torch.arange(128).view(1, 128)
+    blk, chunk, e = kk >> 6, (kk & 63) >> 3, kk & 7
+    byte = blk * 128 * 128 + (v >> 3) * 1024 + (v & 7) * 128 + ((chunk ^ (v & 7)) << 4) + e * 2
+    return (byte // 2).reshape(-1)
+
+
+def pack_state_tiles(S):
+    """fp [..., 128 (K index), 128 (v)] -> float32 tensor of the same shape holding the hi / lo operand tiles."""
+    S = S.float()
+    lead = S.shape[:-2]
+    hi = S.to(torch.bfloat16)
+    lo = (S - hi.float()).to(torch.bfloat16)
+    idx = _state_tile_index().to(S.device)
+    out = torch.empty(*lead, 2, 128 * 128, dtype=torch.bfloat16, device=S.device)
+    out[..., 0, idx] = hi.reshape(*lead, -1)
+    out[..., 1, idx] = lo.reshape(*lead, -1)
+    return out.view(torch.float32).reshape(*lead, 128, 128)
+
+
+def unpack_state_tiles(T):
+    """Inverse of pack_state_tiles: float32-typed tile buffer [..., 128, 128] -> fp32 [..., 128 (K index), 128 (v)]."""
+    lead = T.shape[:-2]
+    halves = T.contiguous().view(torch.bfloat16).reshape(*lead, 2, 128 * 128)
+    idx = _state_tile_index().to(T.device)
+    return (halves[..., 0, idx].float() + halves[..., 1, idx].float()).reshape(*lead, 128, 128)
