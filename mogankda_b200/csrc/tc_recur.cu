@@ -39,9 +39,9 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ RecurShared sh;
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sAh = base;                         // St as A(m = v, k = K index) [128][128]; later Vd^T [128][64]
+    uint8_t* sAh = base;                         // St as A(m = v, k = K index) [128][128]
     uint8_t* sAl = sAh + 32768;
-    uint8_t* sW[2] = {sAl + 32768, sAl + 32768 + 65536};            // nw [tok][K index], hi then lo (16 KB each)
+    uint8_t* sW[2] = {sAl + 32768, sAl + 32768 + 65536};            // nw [tok][K index], hi then lo (16 KB each); later Vd^T [v][tok]
     uint8_t* sK[2] = {sW[0] + 32768, sW[1] + 32768};                 // kbar [tok][K index]
 
     const bool trans = blockIdx.x == 1;
@@ -143,6 +143,7 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
             uu[j] = trans ? 0.f : p.u[((size_t)(start + tt) * HV + h) * 128 + row];
             if (t >= len) uu[j] = 0.f;
         }
+        if (tid == 0) umma::bulk_store_wait_read();         // the previous chunk's saved tile has left shared memory
         __syncthreads();                                   // sh.gl[buf] and the tiles of `buf` are complete
         {   // state entering the chunk: operand tile (optionally saved as it is by the issuing thread below), decay
             float s[32];
@@ -160,13 +161,12 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
             umma::tmem_wait_st();
         }
         publish_operands();
+        // The operand tile doubles as the saved state of this chunk: one asynchronous 64 KB copy, issued and later awaited
+        // by thread 0; nothing writes the tile again before the top of the next iteration.
+        if (tid == 0 && p.h && !trans)
+            umma::bulk_store(reinterpret_cast<uint8_t*>(p.h) + ((size_t)c * HV + h) * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
         if (umma::mma_issuer()) {
-            // The operand tile doubles as the saved state of this chunk: one asynchronous 64 KB copy.  The commit is issued
-            // after the copy has read the tile, so the barrier also covers it (the tile is overwritten with Vd^T next).
-            const bool save = p.h && !trans;
-            if (save) umma::bulk_store(reinterpret_cast<uint8_t*>(p.h) + ((size_t)c * HV + h) * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
             umma::gemm(tmem + 128, umma::opnd_k(sAh, sAl, 128), umma::opnd_k(sW[buf], sW[buf] + 16384, 64), 128, 64, 128, 0u);
-            if (save) umma::bulk_store_wait_read();
             umma::commit(&sh.bar);
         }
         float k[2][8], g[2][8], gL[2][8], rs[2];
@@ -186,18 +186,19 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
                 if (p.Vd && !trans && t < len) p.Vd[((size_t)(start + t) * HV + h) * 128 + row] = vd;
                 if (j < 8) a0[j] = vd; else a1[j - 8] = vd;
             }
-            store_split8(sAh, sAl, 128, row, 2 * cg, a0);
-            store_split8(sAh, sAl, 128, row, 2 * cg + 1, a1);
+            store_split8(sW[buf], sW[buf] + 16384, 128, row, 2 * cg, a0);       // the nw tile is dead: it becomes Vd^T
+            store_split8(sW[buf], sW[buf] + 16384, 128, row, 2 * cg + 1, a1);
         }
         publish_operands();
         if (umma::mma_issuer()) {
-            umma::gemm(tmem, umma::opnd_k(sAh, sAl, 128), umma::opnd_mn(sK[buf], sK[buf] + 16384, 64), 128, 128, 64, 1u);
+            umma::gemm(tmem, umma::opnd_k(sW[buf], sW[buf] + 16384, 128), umma::opnd_mn(sK[buf], sK[buf] + 16384, 64), 128, 128, 64, 1u);
             umma::commit(&sh.bar);
         }
         if (more) store_k(c + 1, buf ^ 1, k, g, gL, rs);
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;
         umma::fence_after_sync();
     }
+    if (tid == 0) umma::bulk_store_wait_read();
     {   // state leaving the segment
         float s[32];
         umma::tmem_ld32(umma::tmem_addr(tmem, warp, cg * 32), s);
@@ -257,11 +258,11 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ RecurShared sh;
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sAh = base;                         // dSt as A(m = v, k = K index); later dVd^T [128][64]
+    uint8_t* sAh = base;                         // dSt as A(m = v, k = K index)
     uint8_t* sAl = sAh + 32768;
     uint8_t* sDo = sAl + 32768;                  // dO [i][v]          hi 16 KB, lo 16 KB
     uint8_t* sAq = sDo + 32768;                  // Aqk [i][j]         hi 8 KB, lo 8 KB
-    uint8_t* sKb = sAq + 16384;                  // kbar [j][K index]
+    uint8_t* sKb = sAq + 16384;                  // kbar [j][K index]; later dVd^T [v][j]
     uint8_t* sQs = sKb + 32768;                  // scale q 2^g [i][K index]
     uint8_t* sNw = sQs + 32768;                  // nw [j][K index]
 
@@ -294,15 +295,23 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
     const int c_beg = p.L.seg_chunk_off[seg], c_end = p.L.seg_chunk_off[seg + 1];
     for (int c = c_end - 1; c >= c_beg; --c) {
         const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
-        {   // batch 1: dO, Aqk, nw (plain copies)
-            float vo[2][8], vn[2][8], va[8];
+        {   // all global operands of the chunk are requested together: dO, Aqk, nw (plain copies), then k, q, g for
+            // kbar = k 2^(gL - g) and q~ = scale q 2^g
+            float vo[2][8], vn[2][8], va[8], vk[2][8], vq[2][8], vg[2][8], vl[8], rk[2], rq[2];
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
                 const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
                 const size_t off = ((size_t)(start + rr) * HV + h) * 128 + k8 * 8;
+                const size_t tk = (size_t)(start + rr) * HK + hk;
                 ld8(p.d_o, DODT, off, vo[n]);
                 ld8(p.nw, MKDA_F32, off, vn[n]);
+                ld8(p.k, QKDT, tk * 128 + k8 * 8, vk[n]);
+                ld8(p.q, QKDT, tk * 128 + k8 * 8, vq[n]);
+                ld8(p.g_c, MKDA_F32, off, vg[n]);
+                rk[n] = p.k_rstd ? p.k_rstd[tk] : 1.f;
+                rq[n] = p.scale * (p.q_rstd ? p.q_rstd[tk] : 1.f);
             }
+            ld8(p.g_c, MKDA_F32, ((size_t)(start + len - 1) * HV + h) * 128 + (tid & 15) * 8, vl);
             {
                 const int r = tid >> 3, k8 = tid & 7, rr = r < len ? r : len - 1;
                 ld8(p.Aqk, MKDA_F32, ((size_t)(start + rr) * HV + h) * 64 + k8 * 8, va);
@@ -315,44 +324,27 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
                 const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
+                const float mk = r < len ? rk[n] : 0.f, mq = r < len ? rq[n] : 0.f;
                 if (r >= len) {
 #pragma unroll
                     for (int e = 0; e < 8; ++e) { vo[n][e] = 0.f; vn[n][e] = 0.f; }
                 }
                 store_split8(sDo, sDo + 16384, 64, r, k8, vo[n]);
                 store_split8(sNw, sNw + 16384, 64, r, k8, vn[n]);
-            }
-        }
-        {   // batch 2: kbar = k 2^(gL - g), q~ = scale q 2^g
-            float vk[2][8], vq[2][8], vg[2][8], vl[2][8], rk[2], rq[2];
-#pragma unroll
-            for (int n = 0; n < 2; ++n) {
-                const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-                const size_t tk = (size_t)(start + rr) * HK + hk;
-                ld8(p.k, QKDT, tk * 128 + k8 * 8, vk[n]);
-                ld8(p.q, QKDT, tk * 128 + k8 * 8, vq[n]);
-                ld8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vg[n]);
-                ld8(p.g_c, MKDA_F32, ((size_t)(start + len - 1) * HV + h) * 128 + k8 * 8, vl[n]);
-                rk[n] = p.k_rstd ? p.k_rstd[tk] : 1.f;
-                rq[n] = p.scale * (p.q_rstd ? p.q_rstd[tk] : 1.f);
-            }
-#pragma unroll
-            for (int n = 0; n < 2; ++n) {
-                const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
-                const float mk = r < len ? rk[n] : 0.f, mq = r < len ? rq[n] : 0.f;
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    vk[n][e] *= mk * ex2f_(vl[n][e] - vg[n][e]);
+                    vk[n][e] *= mk * ex2f_(vl[e] - vg[n][e]);
                     vq[n][e] *= mq * ex2f_(vg[n][e]);
                 }
                 store_split8(sKb, sKb + 16384, 64, r, k8, vk[n]);
                 store_split8(sQs, sQs + 16384, 64, r, k8, vq[n]);
                 if (r == 0) {
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) sh.gl[0][k8 * 8 + e] = ex2f_(vl[n][e]);
+                    for (int e = 0; e < 8; ++e) sh.gl[0][k8 * 8 + e] = ex2f_(vl[e]);
                 }
             }
         }
+        if (tid == 0) umma::bulk_store_wait_read();         // the previous chunk's saved tile has left shared memory
         __syncthreads();                                   // sh.gl
         {   // gradient leaving the chunk: operand tile (saved as it is by the issuing thread below), decay
             float s[32];
@@ -370,11 +362,12 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
             umma::tmem_wait_st();
         }
         publish_operands();
+        // the operand tile is also this chunk's saved gradient: one asynchronous 64 KB copy, awaited by the same thread
+        // before the tile is rebuilt in the next iteration
+        if (tid == 0) umma::bulk_store(reinterpret_cast<uint8_t*>(p.dh) + ((size_t)c * HV + h) * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
         if (umma::mma_issuer()) {
             umma::gemm(tmem + 128, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sAq, sAq + 8192, 64), 128, 64, 64, 0u);
-            umma::bulk_store(reinterpret_cast<uint8_t*>(p.dh) + ((size_t)c * HV + h) * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
             umma::gemm(tmem + 128, umma::opnd_k(sAh, sAl, 128), umma::opnd_k(sKb, sKb + 16384, 64), 128, 64, 128, 1u);
-            umma::bulk_store_wait_read();         // before the commit: the barrier then also covers the saved tile
             umma::commit(&sh.bar);
         }
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;
@@ -388,18 +381,19 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
                 if (t < len) p.dVd[((size_t)(start + t) * HV + h) * 128 + row] = d[j];
                 if (j < 8) a0[j] = d[j]; else a1[j - 8] = d[j];
             }
-            store_split8(sAh, sAl, 128, row, 2 * cg, a0);
-            store_split8(sAh, sAl, 128, row, 2 * cg + 1, a1);
+            store_split8(sKb, sKb + 16384, 128, row, 2 * cg, a0);              // the kbar tile is dead: it becomes dVd^T
+            store_split8(sKb, sKb + 16384, 128, row, 2 * cg + 1, a1);
         }
         publish_operands();
         if (umma::mma_issuer()) {
             umma::gemm(tmem, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sQs, sQs + 16384, 64), 128, 128, 64, 1u);
-            umma::gemm(tmem, umma::opnd_k(sAh, sAl, 128), umma::opnd_mn(sNw, sNw + 16384, 64), 128, 128, 64, 1u);
+            umma::gemm(tmem, umma::opnd_k(sKb, sKb + 16384, 128), umma::opnd_mn(sNw, sNw + 16384, 64), 128, 128, 64, 1u);
             umma::commit(&sh.bar);
         }
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;
         umma::fence_after_sync();
     }
+    if (tid == 0) umma::bulk_store_wait_read();
     if (p.dh0) {
         float s[32];
         umma::tmem_ld32(umma::tmem_addr(tmem, warp, cg * 32), s);
