@@ -102,12 +102,12 @@ template <int DT>
 __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ IntraShared sh;
+    __shared__ __align__(16) float sGa[4][DK];         // cumsum rows of the four block anchors
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sKQ = base + KQ_OFF;
     float* sM = reinterpret_cast<float*>(base + OPND_BYTES);
     float* sInv = sM + CH * MLD;
     float* sP = sInv + CH * MLD;
-    float* sG = sInv;                                  // [64][128] fp32 cumsum tile while the operands are built
     uint8_t* sBk = base;                               // phase 3: beta k~ [j][K index], hi 16 KB + lo 16 KB
     uint8_t* sBv = base + 32768;                       // beta v [j][v]
     uint8_t* sTA = base + 65536;                       // A [i][j], hi 8 KB + lo 8 KB
@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
     if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
 
-    // ---- phase 0: fetch k, q, g (2 (row, chunk) pairs per thread); park g in shared memory for the anchor look-ups ----
+    // ---- phase 0: fetch k, q, g (2 (row, chunk) pairs per thread); park the anchor rows of g in shared memory ----
     float vk[2][8], vq[2][8], vg[2][8], rk[2], rq[2];
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
@@ -138,8 +138,10 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
         const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
-        *reinterpret_cast<float4*>(sG + r * 128 + k8 * 8) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
-        *reinterpret_cast<float4*>(sG + r * 128 + k8 * 8 + 4) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
+        if ((r & 15) == 0) {
+            *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8]) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
+            *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8 + 4]) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) { vk[n][e] *= rk[n]; vq[n][e] *= rq[n]; }
     }
@@ -154,7 +156,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     for (int n = 0; n < 2; ++n) {
         const int i = tid + n * 512, r = i >> 4, k8 = i & 15, I0 = r >> 4;
         float ga[8], t8[8];
-        lds8(sG + (16 * I0) * 128 + k8 * 8, ga);
+        lds8(&sGa[I0][k8 * 8], ga);
 #pragma unroll
         for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(vg[n][e] - ga[e]);
         store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + (r & 15), k8, t8);
@@ -164,7 +166,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
 #pragma unroll
         for (int I = 0; I < 4; ++I) {
             if (I < I0) continue;
-            if (I > I0) lds8(sG + (16 * I) * 128 + k8 * 8, ga);
+            if (I > I0) lds8(&sGa[I][k8 * 8], ga);
 #pragma unroll
             for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(ga[e] - vg[n][e]);
             store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
@@ -203,7 +205,6 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         for (int e = 0; e < 8; ++e) t8[e] = b * vv[n][e];
         store_split8(sBv, sBv + 16384, 64, r, k8, t8);
     }
-    __syncthreads();                          // every thread is done with the cumsum tile (sP / sInv alias it)
     for (int i = tid; i < CH * MLD; i += 512) sInv[i] = 0.f;
     if (q < 2) {                              // lane = column j, cg = row block I: Gamma / Q K^T entries (16 I + r, j)
         float v[32];
@@ -300,22 +301,20 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     __shared__ float sCol[4][DK];
     __shared__ __align__(16) float sPart[16][DK];
     __shared__ uint64_t ldS, ldD;
+    __shared__ __align__(16) float sGa[4][DK];         // cumsum rows of the four block anchors
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     // state phase
     uint8_t* sSh = base;                               // state tile S^T [v][K index] (hi, lo)
     uint8_t* sSl = base + 32768;
     uint8_t* sTh = base + 65536;                       // state tile dS'^T
     uint8_t* sTl = base + 98304;
-    uint8_t* sOh = base + 131072;                      // dO [tok][v], later Vd
-    uint8_t* sOl = base + 147456;
-    uint8_t* sXh = base + 163840;                      // dX
-    uint8_t* sXl = base + 180224;
+    uint8_t* sOh = base + 131072;                      // [dO; dX] [2 x tok][v] as one 128-row tile (32 KB); rows 0-63 later Vd
+    uint8_t* sOl = base + 163840;
     // intra phase
     uint8_t* sKQ = base + KQ_OFF;
-    uint8_t* sWq = base + OPND_BYTES;                  // scale strictlower(dAqk) [i][j], hi 8 KB + lo 8 KB
-    uint8_t* sDl = sWq + 16384;                        // strictlower(dL)
-    uint8_t* sBd = sDl + 16384;                        // diag(beta) strictlower(dL)
-    float* sG = reinterpret_cast<float*>(sXh);         // [64][128] fp32 cumsum tile, over the dX tile once it is dead
+    uint8_t* sWD = base + OPND_BYTES;                  // 128-row tile [.][j]: rows 32 I + r = scale strictlower(dAqk)[16 I + r],
+                                                       // rows 32 I + 16 + r = strictlower(dL)[16 I + r]; hi 16 KB + lo 16 KB
+    uint8_t* sBd = sWD + 32768;                        // diag(beta) strictlower(dL) [i][j], hi 8 KB + lo 8 KB
 
     const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV, HK = p.L.HK;
     const int hk = h / (HV / HK);
@@ -351,8 +350,8 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
 #pragma unroll
                 for (int e = 0; e < 8; ++e) vO[n][e] = vX[n][e] = vV[n][e] = 0.f;
             }
-            store_split8(sOh, sOl, 64, r, i & 15, vO[n]);
-            store_split8(sXh, sXl, 64, r, i & 15, vX[n]);
+            store_split8(sOh, sOl, 128, r, i & 15, vO[n]);
+            store_split8(sOh, sOl, 128, 64 + r, i & 15, vX[n]);
         }
     }
     MKDA_TRACE_AT(5, 1);
@@ -380,8 +379,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     if (umma::mma_issuer()) {
         umma::mbar_wait(&ldS, 0);
         const umma::Opnd aS = umma::opnd_mn(sSh, sSl, 128);          // A(m = K index, k = v) of the [v][K index] tile
-        umma::gemm(tmem + 0, aS, umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
-        umma::gemm(tmem + 64, aS, umma::opnd_k(sXh, sXl, 64), 128, 64, 128, 0u);
+        umma::gemm(tmem + 0, aS, umma::opnd_k(sOh, sOl, 128), 128, 128, 128, 0u);      // Dq | Dk in one N = 128 product
         umma::commit(&sh.bar);
     }
     {   // dgl[c] = sum_v S[c][v] dS'[c][v] from the two tiles: chunk (v row, 8 channels) per thread, four rows each
@@ -421,11 +419,11 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
         const int i = tid + n * 512;
-        store_split8(sOh, sOl, 64, i >> 4, i & 15, vV[n]);
+        store_split8(sOh, sOl, 128, i >> 4, i & 15, vV[n]);
     }
     publish();
     if (umma::mma_issuer()) {
-        umma::gemm(tmem + 128, umma::opnd_mn(sTh, sTl, 128), umma::opnd_k(sOh, sOl, 64), 128, 64, 128, 0u);
+        umma::gemm(tmem + 128, umma::opnd_mn(sTh, sTl, 128), umma::opnd_k(sOh, sOl, 128), 128, 64, 128, 0u);
         umma::commit(&sh.bar);
     }
     MKDA_TRACE_AT(5, 4);
@@ -436,10 +434,12 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         sDgl[tid] = t;
     }
 #pragma unroll
-    for (int n = 0; n < 2; ++n) {                      // the dX tile is dead since the first wait
+    for (int n = 0; n < 2; ++n) {
         const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
-        *reinterpret_cast<float4*>(sG + r * 128 + k8 * 8) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
-        *reinterpret_cast<float4*>(sG + r * 128 + k8 * 8 + 4) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
+        if ((r & 15) == 0) {
+            *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8]) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
+            *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8 + 4]) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) { vk[n][e] *= rk[n]; vq[n][e] *= rq[n]; }
     }
@@ -451,7 +451,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     for (int n = 0; n < 2; ++n) {
         const int i = tid + n * 512, r = i >> 4, k8 = i & 15, I0 = r >> 4;
         float ga[8], t8[8];
-        lds8(sG + (16 * I0) * 128 + k8 * 8, ga);
+        lds8(&sGa[I0][k8 * 8], ga);
 #pragma unroll
         for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(vg[n][e] - ga[e]);
         store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + (r & 15), k8, t8);
@@ -461,13 +461,12 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
 #pragma unroll
         for (int I = 0; I < 4; ++I) {
             if (I < I0) continue;
-            if (I > I0) lds8(sG + (16 * I) * 128 + k8 * 8, ga);
+            if (I > I0) lds8(&sGa[I][k8 * 8], ga);
 #pragma unroll
             for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(ga[e] - vg[n][e]);
             store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
         }
     }
-    __syncthreads();                                   // the cumsum tile is dead: the W tiles overlap it
     MKDA_TRACE_AT(5, 6);
     {
         const int i = tid >> 3, k8 = tid & 7;
@@ -482,8 +481,8 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
             b8[e] = bt * d8[e];
             if (j == i) sDiag[i] = i < len ? p.scale * wa[e] : 0.f;
         }
-        store_split8(sWq, sWq + 8192, 64, i, k8, w8);
-        store_split8(sDl, sDl + 8192, 64, i, k8, d8);
+        store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + (i & 15), k8, w8);
+        store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + 16 + (i & 15), k8, d8);
         store_split8(sBd, sBd + 8192, 64, i, k8, b8);
     }
     MKDA_TRACE_AT(5, 12);
@@ -494,9 +493,9 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         for (int I = 0; I < 4; ++I) {
             const int nj = 16 * (I + 1);
             const umma::Opnd aKc = umma::opnd_mn(base + kc_off(I), base + kc_off(I) + kc_bytes(I), nj);
-            umma::gemm(tmem + 192 + 32 * I, aKc, umma::opnd_k(sWq, sWq + 8192, 64, 16 * I), 128, 16, nj, 0u);
-            umma::gemm(tmem + 192 + 32 * I + 16, aKc, umma::opnd_k(sDl, sDl + 8192, 64, 16 * I), 128, 16, nj, 0u);
-            umma::gemm(tmem + dcol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I + 16), umma::opnd_mn(sWq, sWq + 8192, 64, 16 * I),
+            // both row terms (dq_row | T) of the block in one N = 32 product
+            umma::gemm(tmem + 192 + 32 * I, aKc, umma::opnd_k(sWD, sWD + 16384, 128, 32 * I), 128, 32, nj, 0u);
+            umma::gemm(tmem + dcol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I + 16), umma::opnd_mn(sWD, sWD + 16384, 128, 32 * I),
                        128, nj, 16, 0u);
             umma::gemm(tmem + dcol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I), umma::opnd_mn(sBd, sBd + 8192, 64, 16 * I),
                        128, nj, 16, 1u);
