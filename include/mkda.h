@@ -155,6 +155,8 @@ typedef struct {
 int mkda_out_fwd(const MkdaOutFwd* p, void* stream);
 
 /* Gated RMSNorm backward.  Replaces rmsnorm_gated_bwd (mogan_kda/ops/kimi_delta_rule/epilogue.py:193-205). */
+/* CTA b of the gated RMSNorm backward walks the 64-row groups b, b + R, ... and writes one partial row. */
+#define MKDA_EPILOGUE_MAX_PART_ROWS 1184
 typedef struct {
     int rows;                  /* TT*HV */
     const void* dy; int dy_dtype;
@@ -164,7 +166,7 @@ typedef struct {
     int act; float eps;
     float* d_o;                /* [rows,128] fp32 */
     void* dgate; int dgate_dtype;
-    float* part_w;             /* [ceil(rows/64),128] partial sums of d weight, or NULL */
+    float* part_w;             /* [min(ceil(rows/64), MKDA_EPILOGUE_MAX_PART_ROWS),128] partial sums of d weight, or NULL */
 } MkdaEpilogueBwd;
 int mkda_epilogue_bwd(const MkdaEpilogueBwd* p, void* stream);
 
@@ -173,7 +175,7 @@ int mkda_epilogue_bwd(const MkdaEpilogueBwd* p, void* stream);
  *
  * Who needs it: a host that fixed its device-memory plan before the step starts -- a runtime whose caching allocator is
  * frozen after warm-up, an engine that carved one arena at start-up, a thread that must not take the allocator lock.
- * Such a caller can still provide the inputs and the outputs, but it cannot produce the [ceil(rows/64), 128] fp32
+ * Such a caller can still provide the inputs and the outputs, but it cannot produce the [R, 128] fp32
  * scratch that mkda_epilogue_bwd wants in `part_w`, nor the second launch's workspace.  This entry point keeps that
  * scratch inside the library, in one file-scope device array of MKDA_NOALLOC_MAX_ROWS / 64 * 128 floats (2 MiB) that
  * every GPU which loads the library holds until the process exits, and it also runs the second-stage reduction, so

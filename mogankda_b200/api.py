@@ -15,9 +15,9 @@ from . import ops
 from .index import get_layout
 
 CHUNK_SIZE = 64
-# Sequences longer than this many chunks are cut into segments of exactly this many chunks whose serial recurrences
-# run concurrently (state + transition pre-pass, prefix combine, main pass).  A constant, so that a prefix of a
-# sequence is always processed exactly like the same tokens inside the longer sequence.
+# When the segment chooser (index.wants_segments) decides to cut, sequences are cut into segments of exactly this many
+# chunks whose serial recurrences run concurrently (state + transition pre-pass, prefix combine, main pass).  A constant,
+# so that a prefix of a sequence is always cut exactly like the same tokens inside the longer sequence.
 AUTO_SEGMENT_CHUNKS = 32
 
 
@@ -30,7 +30,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
         B, T, HK, K = q.shape
         HV = v.shape[2]
         dev = q.device
-        lay = get_layout(B, T, cfg["cu_seqlens"], dev, cfg["seg_chunks"])
+        lay = get_layout(B, T, cfg["cu_seqlens"], dev, cfg["seg_chunks"], HV if cfg["seg_auto"] else 0)
         cp = cfg["cp_context"]
         scale = cfg["scale"]
         q_rstd = k_rstd = None
@@ -197,26 +197,13 @@ def chunk_delta_rule(q, k, v, g, beta, *, scale=None, initial_state=None, output
                beta_mode=beta_mode, beta_scale=float(beta_scale), l2=use_qk_l2norm_in_kernel, has_ep=ep is not None,
                ep_act=None if ep is None else ep.get("act", "silu"),
                ep_eps=None if ep is None else ep.get("eps", 1e-6),
-               seg_chunks=AUTO_SEGMENT_CHUNKS if (cp_context is not None or
-                                                  _needs_segments(B, T, v.shape[2], cu_seqlens, auto_cp)) else 0,
+               seg_chunks=AUTO_SEGMENT_CHUNKS if (cp_context is not None or auto_cp) else 0,
+               seg_auto=cp_context is None,          # without CP the chooser in index.wants_segments decides
                cp_context=cp_context)
     ep_gate = None if ep is None else ep["gate"].contiguous()
     ep_w = None if ep is None else ep.get("weight")
     return _DeltaRuleFunction.apply(q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(),
                                     beta.contiguous(), A_log, dt_bias, initial_state, ep_w, ep_gate, cfg)
-
-
-SERIAL_CTAS_WANTED = 2 * 148          # serial CTAs (2 per sequence and v-head) needed to fill a B200 twice over
-
-
-def _needs_segments(B, T, HV, cu_seqlens, auto_cp):
-    """Cut long sequences when the uncut layout cannot fill the GPU.  Decided from shapes only (no device read): the
-    serial kernels run 2 CTAs per (sequence, v-head), so a batch with many sequences or heads is left alone.  The role
-    of the reference's intra-card CP decision (mogan_kda/ops/gated_delta_rule/chunk/cp/context.py:252-283)."""
-    if not auto_cp or T <= AUTO_SEGMENT_CHUNKS * CHUNK_SIZE:
-        return False
-    n_seq = B if cu_seqlens is None else cu_seqlens.numel() - 1
-    return 2 * n_seq * HV < SERIAL_CTAS_WANTED
 
 
 def chunk_kda(q, k, v, g, beta, **kwargs):

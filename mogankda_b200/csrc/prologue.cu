@@ -197,14 +197,23 @@ __global__ void __launch_bounds__(128) gate_bwd_kernel(const MkdaGateBwd p) {
 // ---------------------------------------------------------------------------------------------------------
 // deterministic second-stage reductions
 // ---------------------------------------------------------------------------------------------------------
-// group == 1: block (32, 8); thread (x, y) sums rows y, y+8, ... of column j, then the 8 partials are added in order.
+// group == 1: block (32, 8); thread (x, y) sums rows y, y+8, ... of column j (four running sums, so that four loads are
+// in flight), then the 8 partials are added in order.
 __global__ void __launch_bounds__(256) reduce_cols_kernel(const float* __restrict__ in, int rows, int cols, float* __restrict__ out) {
     __shared__ float part[8][33];
     const int j = blockIdx.x * 32 + threadIdx.x;
-    float s = 0.f;
-    if (j < cols)
-        for (int r = threadIdx.y; r < rows; r += 8) s += in[(size_t)r * cols + j];
-    part[threadIdx.y][threadIdx.x] = s;
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    if (j < cols) {
+        int r = threadIdx.y;
+        for (; r + 24 < rows; r += 32) {
+            s0 += in[(size_t)r * cols + j];
+            s1 += in[(size_t)(r + 8) * cols + j];
+            s2 += in[(size_t)(r + 16) * cols + j];
+            s3 += in[(size_t)(r + 24) * cols + j];
+        }
+        for (; r < rows; r += 8) s0 += in[(size_t)r * cols + j];
+    }
+    part[threadIdx.y][threadIdx.x] = (s0 + s1) + (s2 + s3);
     __syncthreads();
     if (threadIdx.y == 0 && j < cols) {
         float t = part[0][threadIdx.x];
@@ -212,31 +221,51 @@ __global__ void __launch_bounds__(256) reduce_cols_kernel(const float* __restric
         out[j] = t;
     }
 }
-// group > 1: one block of 128 threads per output; thread i sums elements i, i+128, ... of each row's group.
+// group > 1: one block of 128 threads per output; warp w walks rows w, w+4, ... and its lanes the group's elements, again
+// with four running sums; lanes, then warps, are combined in a fixed order.
 __global__ void __launch_bounds__(128) reduce_groups_kernel(const float* __restrict__ in, int rows, int cols, int group, float* __restrict__ out) {
-    __shared__ float part[128];
-    const int j = blockIdx.x;
-    float s = 0.f;
-    for (int r = 0; r < rows; ++r)
-        for (int i = threadIdx.x; i < group; i += 128) s += in[(size_t)r * cols + (size_t)j * group + i];
-    part[threadIdx.x] = s;
-    __syncthreads();
-    for (int o = 64; o > 0; o >>= 1) {
-        if (threadIdx.x < o) part[threadIdx.x] += part[threadIdx.x + o];
-        __syncthreads();
+    __shared__ float part[4];
+    const int j = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    for (int i = lane; i < group; i += 32) {
+        const float* col = in + (size_t)j * group + i;
+        int r = warp;
+        for (; r + 12 < rows; r += 16) {
+            s0 += col[(size_t)r * cols];
+            s1 += col[(size_t)(r + 4) * cols];
+            s2 += col[(size_t)(r + 8) * cols];
+            s3 += col[(size_t)(r + 12) * cols];
+        }
+        for (; r < rows; r += 4) s0 += col[(size_t)r * cols];
     }
-    if (threadIdx.x == 0) out[j] = part[0];
+    const float s = warp_sum((s0 + s1) + (s2 + s3));
+    if (lane == 0) part[warp] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) out[j] = (part[0] + part[1]) + (part[2] + part[3]);
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// L2-norm statistics: one warp per row of 128.
+// L2-norm statistics: 16 lanes per row of 128, eight rows per warp.
 // ---------------------------------------------------------------------------------------------------------
+template <int DT>
 __global__ void __launch_bounds__(128) l2norm_rstd_kernel(const MkdaL2Norm p) {
-    const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (row >= p.rows) return;
-    const float4 v = ld4(p.x, p.dtype, (size_t)row * 128 + 4 * lane);
-    const float ss = warp_sum(hsum4(mul4(v, v)));
-    if (lane == 0) p.rstd[row] = 1.f / sqrtf(ss + p.eps);
+    const int lane = threadIdx.x & 31, sub = lane & 15;
+    const int row0 = (blockIdx.x * 4 + (threadIdx.x >> 5)) * 8 + (lane >> 4);
+    float4 a[4], b[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = row0 + 2 * i, rr = row < p.rows ? row : p.rows - 1;
+        a[i] = ld4(p.x, DT, (size_t)rr * 128 + 8 * sub);
+        b[i] = ld4(p.x, DT, (size_t)rr * 128 + 8 * sub + 4);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float ss = hsum4(mul4(a[i], a[i])) + hsum4(mul4(b[i], b[i]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const int row = row0 + 2 * i;
+        if (sub == 0 && row < p.rows) p.rstd[row] = 1.f / sqrtf(ss + p.eps);
+    }
 }
 
 // GVA group sum (fixed order) + L2-norm backward: one warp per (token, q/k head).
@@ -267,8 +296,10 @@ __global__ void __launch_bounds__(128) epilogue_bwd_kernel(const MkdaEpilogueBwd
     float4 w = splat4(1.f);
     if (p.norm_w) w = ld4(p.norm_w, p.norm_w_dtype, 4 * lane);
     float4 dw = splat4(0.f);
+    const int ngroups = (p.rows + 63) / 64;
+    for (int grp = blockIdx.x; grp < ngroups; grp += gridDim.x)
     for (int i = 0; i < 16; ++i) {
-        const int row = blockIdx.x * 64 + i * 4 + warp;
+        const int row = grp * 64 + i * 4 + warp;
         if (row >= p.rows) break;
         const size_t off = (size_t)row * 128 + 4 * lane;
         const float4 o = *reinterpret_cast<const float4*>(p.o_raw + off);
@@ -305,6 +336,12 @@ __global__ void __launch_bounds__(128) epilogue_bwd_kernel(const MkdaEpilogueBwd
 }  // namespace mkda
 
 using namespace mkda;
+
+// number of weight-gradient partial rows (= CTAs) of the gated RMSNorm backward
+static int epilogue_part_rows(int rows) {
+    const int groups = (rows + 63) / 64;
+    return groups < MKDA_EPILOGUE_MAX_PART_ROWS ? groups : MKDA_EPILOGUE_MAX_PART_ROWS;
+}
 
 extern "C" int mkda_gate_cumsum_fwd(const MkdaGateFwd* p, void* stream) {
     if (!p || !p->x || !p->g_c || p->L.NC < 0) return set_error(MKDA_ERR_ARG, "gate_cumsum_fwd: null argument");
@@ -350,7 +387,13 @@ extern "C" int mkda_reduce_partials(const MkdaReduce* p, void* stream) {
 extern "C" int mkda_l2norm_rstd(const MkdaL2Norm* p, void* stream) {
     if (!p || !p->x || !p->rstd) return set_error(MKDA_ERR_ARG, "l2norm_rstd: null argument");
     if (p->rows == 0) return MKDA_OK;
-    l2norm_rstd_kernel<<<(p->rows + 3) / 4, 128, 0, (cudaStream_t)stream>>>(*p);
+    const int grid = (p->rows + 31) / 32;
+    switch (p->dtype) {
+        case MKDA_F32: l2norm_rstd_kernel<MKDA_F32><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
+        case MKDA_BF16: l2norm_rstd_kernel<MKDA_BF16><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
+        case MKDA_F16: l2norm_rstd_kernel<MKDA_F16><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
+        default: return set_error(MKDA_ERR_ARG, "l2norm_rstd: unsupported dtype");
+    }
     return check_launch("l2norm_rstd");
 }
 
@@ -369,6 +412,7 @@ extern "C" int mkda_qk_grad_finish(const MkdaQkGrad* p, void* stream) {
 // asks the runtime for the array's device address (once per device) and passes that pointer to the kernels.
 // ---------------------------------------------------------------------------------------------------------
 static __device__ __align__(256) float g_noalloc_scratch[(MKDA_NOALLOC_MAX_ROWS / 64) * 128];
+static_assert(MKDA_NOALLOC_MAX_ROWS / 64 >= MKDA_EPILOGUE_MAX_PART_ROWS, "the built-in scratch must hold every partial row");
 static float* g_noalloc_ptr[64] = {nullptr};          // device address of the scratch, per device ordinal
 
 static int noalloc_scratch(float** out) {
@@ -396,7 +440,7 @@ extern "C" int mkda_epilogue_bwd_noalloc(const MkdaEpilogueBwdNoAlloc* p, void* 
                                        "use mkda_epilogue_bwd with a caller-provided part_w");
     float* scratch = nullptr;
     if (int e = noalloc_scratch(&scratch)) return e;
-    const int nblk = (p->rows + 63) / 64;
+    const int nblk = epilogue_part_rows(p->rows);
     if (nblk == 0) {
         if (cudaMemsetAsync(p->dweight, 0, 128 * sizeof(float), (cudaStream_t)stream) != cudaSuccess)
             return set_error(MKDA_ERR_LAUNCH, "epilogue_bwd_noalloc: memset failed");
@@ -416,6 +460,6 @@ extern "C" int mkda_epilogue_bwd_noalloc(const MkdaEpilogueBwdNoAlloc* p, void* 
 extern "C" int mkda_epilogue_bwd(const MkdaEpilogueBwd* p, void* stream) {
     if (!p || !p->dy || !p->o_raw || !p->gate || !p->d_o || !p->dgate) return set_error(MKDA_ERR_ARG, "epilogue_bwd: null argument");
     if (p->rows == 0) return MKDA_OK;
-    epilogue_bwd_kernel<<<(p->rows + 63) / 64, 128, 0, (cudaStream_t)stream>>>(*p);
+    epilogue_bwd_kernel<<<epilogue_part_rows(p->rows), 128, 0, (cudaStream_t)stream>>>(*p);
     return check_launch("epilogue_bwd");
 }

@@ -42,7 +42,7 @@ struct IntraShared {
     uint64_t bar;
     uint32_t tmem;
     float beta[CH];
-    float T[3][16][17];
+    float T[32][33];
 };
 
 constexpr int MLD = 68;
@@ -53,8 +53,10 @@ constexpr int KQ_OFF = 81920;                              // [128][128] hi 32 K
 constexpr int OPND_BYTES = KQ_OFF + 65536;                 // 144 KB
 constexpr int INTRA_TC_SMEM = OPND_BYTES + 3 * CH * MLD * 4 + 1024;
 
-// Blocked inverse of the unit lower-triangular 64 x 64 matrix sM into sInv (fp32, fixed summation order):
-// the four 16 x 16 diagonal blocks by forward substitution, then block row I = 1..3 from the rows above it.
+// Inverse of the unit lower-triangular 64 x 64 matrix sM into sInv (fp32, fixed summation order) by recursive halving:
+// the four 16 x 16 diagonal blocks by forward substitution, then the off-diagonal block of each 32 x 32 half and finally
+// the 32 x 32 block below the diagonal, each as  X = -B^-1 (C A^-1)  with A^-1 / B^-1 the inverses above / beside it.
+// Every entry depends on the rows up to its own only, and the order of the sums is fixed by the indices.
 __device__ __forceinline__ void invert_unit_lower(const float* __restrict__ sM, float* __restrict__ sInv, IntraShared& sh) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (warp < 4 && lane < 16) {
@@ -71,31 +73,43 @@ __device__ __forceinline__ void invert_unit_lower(const float* __restrict__ sM, 
         for (int r = 0; r < 16; ++r) sInv[(o + r) * MLD + o + lane] = x[r];
     }
     __syncthreads();
-    for (int I = 1; I < 4; ++I) {
-        const int J = tid >> 8, r = (tid >> 4) & 15, c = tid & 15;
-        const bool on = J < I;            // tid < 512 -> J in {0, 1}; block row 3 needs J = 2 as well, done by a second pass
-        for (int pass = 0; pass < 2; ++pass) {
-            const int JJ = J + 2 * pass;
-            if (JJ < I && (pass == 0 ? on : true)) {
-                float s = 0.f;
-                for (int kb = JJ; kb < I; ++kb)
+    {   // 16 x 16 blocks (1, 0) and (3, 2): thread = (half, r, c)
+        const int hb = tid >> 8, r = (tid >> 4) & 15, c = tid & 15;
+        const int ro = 32 * hb + 16, co = 32 * hb;            // block origin; A^-1 at (co, co), B^-1 at (ro, ro)
+        float t = 0.f;
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) s = fmaf(sM[(16 * I + r) * MLD + 16 * kb + e], sInv[(16 * kb + e) * MLD + 16 * JJ + c], s);
-                sh.T[JJ][r][c] = s;
-            }
-        }
+        for (int e = 0; e < 16; ++e) t = fmaf(sM[(ro + r) * MLD + co + e], sInv[(co + e) * MLD + co + c], t);
+        sh.T[16 * hb + r][c] = t;
         __syncthreads();
-        for (int pass = 0; pass < 2; ++pass) {
-            const int JJ = J + 2 * pass;
-            if (JJ < I) {
-                float s = 0.f;
+        float x = 0.f;
 #pragma unroll
-                for (int e = 0; e < 16; ++e) s = fmaf(sInv[(16 * I + r) * MLD + 16 * I + e], sh.T[JJ][e][c], s);
-                sInv[(16 * I + r) * MLD + 16 * JJ + c] = -s;
-            }
-        }
-        __syncthreads();
+        for (int e = 0; e < 16; ++e) x = fmaf(sInv[(ro + r) * MLD + ro + e], sh.T[16 * hb + e][c], x);
+        sInv[(ro + r) * MLD + co + c] = -x;
     }
+    __syncthreads();
+    {   // 32 x 32 block (rows 32.., columns 0..31): thread = (r, two columns)
+        const int r = tid >> 4, c = (tid & 15) * 2;
+        float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+            const float m = sM[(32 + r) * MLD + e];
+            t0 = fmaf(m, sInv[e * MLD + c], t0);
+            t1 = fmaf(m, sInv[e * MLD + c + 1], t1);
+        }
+        sh.T[r][c] = t0;
+        sh.T[r][c + 1] = t1;
+        __syncthreads();
+        float x0 = 0.f, x1 = 0.f;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+            const float m = sInv[(32 + r) * MLD + 32 + e];
+            x0 = fmaf(m, sh.T[e][c], x0);
+            x1 = fmaf(m, sh.T[e][c + 1], x1);
+        }
+        sInv[(32 + r) * MLD + c] = -x0;
+        sInv[(32 + r) * MLD + c + 1] = -x1;
+    }
+    __syncthreads();
 }
 
 template <int DT>

@@ -70,19 +70,45 @@ def build_tables(B, T, cu, seg_chunks=0):
                 covers_all=covered == B * T)
 
 
+SM_COUNT = 148               # B200
+
+
+def wants_segments(chunks_per_seq, HV, seg_chunks):
+    """Segment-parallelism chooser: should sequences be cut into segments of ``seg_chunks`` chunks?
+
+    The serial kernels run one CTA per (sequence or segment, v-head), one chunk step after another.  Uncut, their time is
+    the larger of the longest sequence (critical path) and the even share of all chunk steps over the SMs; cutting adds
+    a second serial pass (state + transition per segment) and a prefix combine, i.e. roughly doubles the serial work.
+    So: cut when the GPU cannot be filled at all, or when the critical path is more than twice the even share.  Decided
+    from the lengths alone (host), never from data; it plays the role of the reference's intra-card CP decision
+    (mogan_kda/ops/gated_delta_rule/chunk/cp/context.py:252-283, cp/autocp/decision.py:54-123)."""
+    longest = max(chunks_per_seq, default=0)
+    if seg_chunks <= 0 or longest <= seg_chunks:
+        return False
+    if len(chunks_per_seq) * HV < SM_COUNT:
+        return True
+    even_share = sum(chunks_per_seq) * HV / SM_COUNT
+    return longest > 2.0 * even_share
+
+
 _cache = {}
 _CACHE_MAX = 16
 
 
-def get_layout(B, T, cu_seqlens, device, seg_chunks=0):
-    """Device tables, cached on (shape, identity + version of ``cu_seqlens``, segment length) like the reference's
-    ``tensor_cache`` (mogan_kda/utils/index.py:19-90).  A cache miss reads ``cu_seqlens`` back to the host."""
-    key = (B, T, str(device), seg_chunks,
+def get_layout(B, T, cu_seqlens, device, seg_chunks=0, auto_heads=0):
+    """Device tables, cached on (shape, identity + version of ``cu_seqlens``, segment policy) like the reference's
+    ``tensor_cache`` (mogan_kda/utils/index.py:19-90).  A cache miss reads ``cu_seqlens`` back to the host.
+    ``auto_heads`` > 0 lets ``wants_segments`` decide, for that many v-heads, whether ``seg_chunks`` is applied."""
+    key = (B, T, str(device), seg_chunks, auto_heads,
            None if cu_seqlens is None else (cu_seqlens.data_ptr(), cu_seqlens._version, tuple(cu_seqlens.shape)))
     hit = _cache.get(key)
     if hit is not None:
         return hit
     cu = None if cu_seqlens is None else [int(x) for x in cu_seqlens.tolist()]
+    if auto_heads > 0:
+        lens = [T] * B if cu is None else [e - s for s, e in zip(cu[:-1], cu[1:])]
+        if not wants_segments([-(-n // CHUNK) for n in lens], auto_heads, seg_chunks):
+            seg_chunks = 0
     tb = build_tables(B, T, cu, seg_chunks)
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)      # noqa: E731
     lay = Layout(B=B, T=T, N=tb["N"], NC=len(tb["chunk_start"]), NS=len(tb["seg_first"]), NG=tb["N"],

@@ -191,7 +191,7 @@ def epilogue_bwd(dy, o_raw, weight, gate, act, eps):
     dev = o_raw.device
     d_o = torch.empty(rows, 128, dtype=torch.float32, device=dev)
     dgate = torch.empty_like(gate)
-    nblk = (rows + 63) // 64
+    nblk = min((rows + 63) // 64, _lib.MKDA_EPILOGUE_MAX_PART_ROWS)
     part = torch.empty(nblk, 128, dtype=torch.float32, device=dev) if weight is not None else None
     p = STRUCTS["MkdaEpilogueBwd"]()
     p.rows = rows

@@ -46,3 +46,18 @@ def test_bad_cu_seqlens():
         build_tables(1, 100, [0, 120])
     with pytest.raises(ValueError):
         build_tables(1, 100, [0, 60, 40])
+
+
+def test_segment_chooser():
+    from mogankda_b200.index import wants_segments
+    # nothing longer than a segment: never cut
+    assert not wants_segments([8, 20, 32], 32, 32)
+    # one long sequence, few heads: the GPU cannot be filled without cutting
+    assert wants_segments([1024], 32, 32)
+    # many documents of similar length fill the GPU on their own
+    assert not wants_segments([40] * 100, 32, 32)
+    # a packed batch dominated by one document: its chain is far longer than the even share
+    assert wants_segments([940] + [4] * 34, 32, 32)
+    # the same long document among enough other work is left alone
+    assert not wants_segments([100] + [30] * 300, 32, 32)
+    assert not wants_segments([], 32, 32) and not wants_segments([1000], 32, 0)
