@@ -228,7 +228,7 @@ typedef struct {
     const float* h;            /* [NC,HV] state tiles */
     const void* d_o; int do_dtype; const float* dVd;
     float* Vd;                 /* [TT,HV,128] recomputed */
-    float* dX;                 /* [TT,HV,128] = dv (fp32) */
+    float* dX;                 /* [TT,HV,128] = dv (fp32), an input of mkda_bwd_tail */
     float* dbeta_w;            /* [TT,HV] */
     float* dAqk; float* dL;    /* [TT,HV,64] */
 } MkdaBwdWy;
@@ -252,6 +252,7 @@ typedef struct {
     float* dq_v; float* dk_v;  /* [TT,HV,128] per v-head */
     float* dgp;                /* [TT,HV,128] gradient w.r.t. the log2 cumsum */
     void* dbeta; int dbeta_dtype;
+    void* dv; int dv_dtype;    /* [TT,HV,128] dX again in the dtype of v (written from the staged rows), or NULL */
 } MkdaBwdTail;
 int mkda_bwd_tail(const MkdaBwdTail* p, void* stream);
 

@@ -117,15 +117,15 @@ class _DeltaRuleFunction(torch.autograd.Function):
             dh, dVd, dh0 = ops.bwd_dh(lay, d_o, q, k, q_rstd, k_rstd, g_c, Aqk, nw, scale, HK, HV, dht=dht,
                                       state_v_first=vf, want_dh0=need_dh0)
         Vd, dX, dbeta_w, dAqk, dL = ops.bwd_wy(lay, k, v, k_rstd, g_c, beta_e, A, h, d_o, dVd, HK, HV)
-        dq_v, dk_v, dgp, dbeta = ops.bwd_tail(lay, q, k, q_rstd, k_rstd, g_c, beta_e, d_o, dX, Vd, h, dh, dAqk, dL,
-                                              dbeta_w, scale, HK, HV, beta, cfg["beta_mode"] == "sigmoid",
-                                              cfg["beta_scale"])
+        dq_v, dk_v, dgp, dbeta, dv = ops.bwd_tail(lay, q, k, q_rstd, k_rstd, g_c, beta_e, d_o, dX, Vd, h, dh, dAqk, dL,
+                                                  dbeta_w, scale, HK, HV, beta, cfg["beta_mode"] == "sigmoid",
+                                                  cfg["beta_scale"], dv_dtype=v.dtype)
         dx, d_bias, d_alog = ops.gate_bwd(lay, x, dgp, cfg["gate_mode"], A_log, dt_bias, cfg["lower_bound"], HV,
                                           want_bias=dt_bias is not None and ctx.needs_input_grad[6],
                                           want_alog=A_log is not None and ctx.needs_input_grad[5])
         dq = ops.qk_grad_finish(dq_v, q, q_rstd, HK, HV).view_as(q)
         dk = ops.qk_grad_finish(dk_v, k, k_rstd, HK, HV).view_as(k)
-        dv = dX.view(B, T, HV, 128).to(v.dtype)
+        dv = dv.view(B, T, HV, 128)
         if d_alog is not None:
             d_alog = d_alog.view_as(A_log).to(A_log.dtype)
         if d_bias is not None:

@@ -366,6 +366,11 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
             }
             store_split8(sOh, sOl, 128, r, i & 15, vO[n]);
             store_split8(sOh, sOl, 128, 64 + r, i & 15, vX[n]);
+            if (p.dv && r < len) {                     // dv in the dtype of v: the staged dX rows, 8 values per store
+                const size_t off = ((size_t)(start + r) * HV + h) * 128 + (i & 15) * 8;
+                st4(p.dv, p.dv_dtype, off, make_float4(vX[n][0], vX[n][1], vX[n][2], vX[n][3]));
+                st4(p.dv, p.dv_dtype, off + 4, make_float4(vX[n][4], vX[n][5], vX[n][6], vX[n][7]));
+            }
         }
     }
     MKDA_TRACE_AT(5, 1);

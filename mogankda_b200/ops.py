@@ -242,7 +242,7 @@ def bwd_wy(lay, k, v, k_rstd, g_c, beta_e, A, h, d_o, dVd, HK, HV):
 
 
 def bwd_tail(lay, q, k, q_rstd, k_rstd, g_c, beta_e, d_o, dX, Vd, h, dh, dAqk, dL, dbeta_w, scale, HK, HV,
-             beta_raw, beta_sigmoid, beta_scale):
+             beta_raw, beta_sigmoid, beta_scale, dv_dtype=torch.float32):
     """Gradients local to a (chunk, v-head): through the states and through the intra-chunk blocks, in one kernel."""
     dev = q.device
     alloc = torch.empty if lay.covers_all else torch.zeros
@@ -258,8 +258,12 @@ def bwd_tail(lay, q, k, q_rstd, k_rstd, g_c, beta_e, d_o, dX, Vd, h, dh, dAqk, d
     p.beta_raw, p.beta_dtype = _ptr(beta_raw), _dt(beta_raw)
     p.beta_sigmoid, p.beta_scale = int(beta_sigmoid), float(beta_scale)
     p.dq_v, p.dk_v, p.dgp, p.dbeta, p.dbeta_dtype = _ptr(dq_v), _ptr(dk_v), _ptr(dgp), _ptr(dbeta), _dt(dbeta)
+    dv = dX
+    if dv_dtype != torch.float32:      # dv in the dtype of v, written by the kernel from the rows it stages anyway
+        dv = alloc(lay.TT, HV, 128, dtype=dv_dtype, device=dev)
+        p.dv, p.dv_dtype = _ptr(dv), _dt(dv)
     _lib.call("mkda_bwd_tail", p, _stream())
-    return dq_v, dk_v, dgp, dbeta
+    return dq_v, dk_v, dgp, dbeta, dv
 
 
 def qk_grad_finish(d_v, x, rstd, HK, HV):

@@ -106,10 +106,11 @@ def test_bwd_wy(world):
 
 def test_bwd_tail_gate_and_finish(world):
     lv, fw, bw, f32, lay, o = world["lv"], world["fw"], world["bw"], world["f32"], world["lay"], world["opts"]
-    t_q, t_k, t_g, t_b = ops.bwd_tail(lay, lv["q"], lv["k"], world["q_rstd"], world["k_rstd"], f32(fw["g_c"]), world["be"],
+    t_q, t_k, t_g, t_b, t_v = ops.bwd_tail(lay, lv["q"], lv["k"], world["q_rstd"], world["k_rstd"], f32(fw["g_c"]), world["be"],
                                       world["do"], f32(bw["dX"]), f32(bw["Vd"]), pack_state_tiles(f32(fw["h"])),
                                       pack_state_tiles(f32(bw["dh"])), f32(bw["dAqk"]), f32(bw["dL"]), f32(bw["dbeta_w"]),
-                                      world["scale"], 2, 4, lv["beta"], False, 1.0)
+                                      world["scale"], 2, 4, lv["beta"], False, 1.0, dv_dtype=torch.bfloat16)
+    assert torch.equal(t_v, f32(bw["dX"]).reshape(t_v.shape).to(torch.bfloat16))
     _err("dq_v", t_q, bw["dq_v"]); _err("dk_v", t_k, bw["dk_v"]); _err("dgp", t_g, bw["dgp"])
     _err("dbeta", t_b, bw["dbeta"].reshape(world["TT"], 4))
     # gate backward (reverse cumsum folded in) against autograd of the oracle's gate
