@@ -122,23 +122,21 @@ KERNEL_FLOPS = {                      # per token per v-head
     "mkda_out_fwd": F_KV + F_CK,                      # q~ S, Aqk Vd
     "mkda_bwd_dh": F_CK + 3 * F_KV,                   # Aqk^T dO, kbar dS', q~^T dO, nw^T dVd
     "mkda_bwd_wy": F_KV + 4 * F_CK + 2 * F_CC,        # k~ S, A W, dO Vd^T, A^T dVd, dVd W^T, two C^3 products
-    "mkda_bwd_sgrad": 3 * F_KV,                       # dO S^T, dX S^T, Vd dS'^T
-    "mkda_bwd_intra": 4 * F_CK,                       # row / column terms through Gamma and Q K^T
-    "mkda_bwd_tail": 3 * F_KV + 4 * F_CK,             # bwd_sgrad + bwd_intra in one kernel
+    "mkda_bwd_tail": 3 * F_KV + 4 * F_CK,             # dO S^T, dX S^T, Vd dS'^T; row / column terms through Gamma and Q K^T
 }
 # Algorithmic bytes per token per v-head: each kernel's own tensor I/O at the default workload (bf16 q/k/v/gate,
 # fp32 intermediates, HV = 2 HK), every operand counted once.
 KERNEL_BYTES = {
     "mkda_gate_cumsum_fwd": 1024, "mkda_l2norm_rstd": 128, "mkda_intra_fwd": 2560, "mkda_recur_fwd": 3200,
-    "mkda_out_fwd": 3712, "mkda_epilogue_bwd": 2048, "mkda_bwd_dh": 3584, "mkda_bwd_wy": 4736, "mkda_bwd_sgrad": 5888,
-    "mkda_bwd_intra": 4352, "mkda_gate_bwd": 1536, "mkda_qk_grad_finish": 640,
-    "mkda_bwd_tail": 5888 + 4352 - 6 * 512,           # the three row-local partials are neither written nor re-read
+    "mkda_out_fwd": 3712, "mkda_epilogue_bwd": 2048, "mkda_bwd_dh": 3584, "mkda_bwd_wy": 4736,
+    "mkda_bwd_tail": 7168 + 256, "mkda_gate_bwd": 1536, "mkda_qk_grad_finish": 640,
 }
 # DRAM traffic per token per v-head measured by ncu on the 1B-shape case (profiles/counters_per_kernel_1b_shape.md),
 # bytes (dram read + write per launch / 131072 token-heads); it grows in proportion to tokens x heads.
 KERNEL_TRAFFIC = {
-    "mkda_intra_fwd": 2154, "mkda_recur_fwd": 2913, "mkda_out_fwd": 3512, "mkda_bwd_dh": 3304, "mkda_bwd_wy": 4500,
-    "mkda_gate_cumsum_fwd": 651, "mkda_epilogue_bwd": 1774, "mkda_qk_grad_finish": 653,
+    "mkda_intra_fwd": 2151, "mkda_recur_fwd": 2932, "mkda_out_fwd": 3503, "mkda_bwd_dh": 3327, "mkda_bwd_wy": 4499,
+    "mkda_bwd_tail": 6618, "mkda_gate_cumsum_fwd": 644, "mkda_epilogue_bwd": 1778, "mkda_qk_grad_finish": 654,
+    "mkda_l2norm_rstd": 128,
 }
 
 
@@ -286,7 +284,8 @@ def reference_arm(args, world, rank):
         "impl": "reference", "metric": "KDA fwd+bwd Mtok/s per layer", "value": val, "unit": "Mtok/s",
         "n_gpus": world, "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": args.workload, **dims, "D": D, "sample_tokens": ntok},
+        "config": {"workload": f"{args.workload}: {desc}", **dims, "D": D, "parallelism": "host cores (rank 0)",
+                   "sample_tokens": ntok},
         "cpu_baseline": dict(value=val, unit="Mtok/s", cores=torch.get_num_threads(), kind="port", sample=sample),
         "e2e": {"value": val, "unit": "Mtok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0}))
