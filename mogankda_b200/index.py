@@ -77,18 +77,17 @@ def wants_segments(chunks_per_seq, HV, seg_chunks):
     """Segment-parallelism chooser: should sequences be cut into segments of ``seg_chunks`` chunks?
 
     The serial kernels run one CTA per (sequence or segment, v-head), one chunk step after another.  Uncut, their time is
-    the larger of the longest sequence (critical path) and the even share of all chunk steps over the SMs; cutting adds
-    a second serial pass (state + transition per segment) and a prefix combine, i.e. roughly doubles the serial work.
-    So: cut when the GPU cannot be filled at all, or when the critical path is more than twice the even share.  Decided
-    from the lengths alone (host), never from data; it plays the role of the reference's intra-card CP decision
+    set by the longest sequence (critical path) unless there is so much work that the even share of all chunk steps over
+    the SMs is longer still.  Cutting spreads the steps evenly but adds the state + transition pre-pass in the forward
+    direction and a second pass in the backward direction, about 2.5 x the serial work over a layer step, plus the prefix
+    combine.  So: cut when the critical path is longer than 2.5 even shares.  Decided from the lengths alone (host), never
+    from data; it plays the role of the reference's intra-card CP decision
     (mogan_kda/ops/gated_delta_rule/chunk/cp/context.py:252-283, cp/autocp/decision.py:54-123)."""
     longest = max(chunks_per_seq, default=0)
     if seg_chunks <= 0 or longest <= seg_chunks:
         return False
-    if len(chunks_per_seq) * HV < SM_COUNT:
-        return True
     even_share = sum(chunks_per_seq) * HV / SM_COUNT
-    return longest > 2.0 * even_share
+    return longest > 2.5 * even_share
 
 
 _cache = {}

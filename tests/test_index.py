@@ -61,3 +61,5 @@ def test_segment_chooser():
     # the same long document among enough other work is left alone
     assert not wants_segments([100] + [30] * 300, 32, 32)
     assert not wants_segments([], 32, 32) and not wants_segments([1000], 32, 0)
+    # four 256-chunk sequences x 16 heads leave SMs idle, but cutting would cost more than it spreads
+    assert not wants_segments([256] * 4, 16, 32)
