@@ -161,10 +161,6 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
             umma::tmem_wait_st();
         }
         publish_operands();
-        // The operand tile doubles as the saved state of this chunk: one asynchronous 64 KB copy, issued and later awaited
-        // by thread 0; nothing writes the tile again before the top of the next iteration.
-        if (tid == 0 && p.h && !trans)
-            umma::bulk_store(reinterpret_cast<uint8_t*>(p.h) + ((size_t)c * HV + h) * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
         if (umma::mma_issuer()) {
             umma::gemm(tmem + 128, umma::opnd_k(sAh, sAl, 128), umma::opnd_k(sW[buf], sW[buf] + 16384, 64), 128, 64, 128, 0u);
             umma::commit(&sh.bar);
@@ -176,6 +172,11 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
         }
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;
         umma::fence_after_sync();
+        // The operand tile doubles as the saved state of this chunk: one asynchronous 64 KB copy, issued and later awaited
+        // by thread 0, started once the product that reads the tile is done; nothing writes the tile again before the top
+        // of the next iteration.
+        if (tid == 0 && p.h && !trans)
+            umma::bulk_store(reinterpret_cast<uint8_t*>(p.h) + ((size_t)c * HV + h) * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
         {   // Vd^T = u^T + St nw^T: global copy [tok][v] and operand tile A(m = v, k = tok)
             float d[16], a0[8], a1[8];
             umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + cg * 16), d);
@@ -362,9 +363,6 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
             umma::tmem_wait_st();
         }
         publish_operands();
-        // the operand tile is also this chunk's saved gradient: one asynchronous 64 KB copy, awaited by the same thread
-        // before the tile is rebuilt in the next iteration
-        if (tid == 0) umma::bulk_store(reinterpret_cast<uint8_t*>(p.dh) + ((size_t)c * HV + h) * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
         if (umma::mma_issuer()) {
             umma::gemm(tmem + 128, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sAq, sAq + 8192, 64), 128, 64, 64, 0u);
             umma::gemm(tmem + 128, umma::opnd_k(sAh, sAl, 128), umma::opnd_k(sKb, sKb + 16384, 64), 128, 64, 128, 1u);
@@ -372,6 +370,9 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
         }
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;
         umma::fence_after_sync();
+        // the operand tile is also this chunk's saved gradient: one asynchronous 64 KB copy, started once the products that
+        // read the tile are done and awaited by the same thread before the tile is rebuilt in the next iteration
+        if (tid == 0) umma::bulk_store(reinterpret_cast<uint8_t*>(p.dh) + ((size_t)c * HV + h) * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
         {
             float d[16], a0[8], a1[8];
             umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + cg * 16), d);

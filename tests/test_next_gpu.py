@@ -66,3 +66,25 @@ def test_chooser_cuts_a_skewed_packed_batch_and_results_agree():
     b = run(mk.chunk_kda, lv, do, dht, opts, None, auto_cp=False)
     for n in a:
         check(n, a[n], b[n].float())                                         # 16-bit results: both sides are rounded
+
+
+def test_api_errors_follow_the_reference_conventions():
+    """ValueError for API misuse, assert for dtype / shape (mogan_kda/ops/kimi_delta_rule/chunk/__init__.py:44-56,
+    mogan_kda/ops/gated_delta_rule/chunk/__init__.py:425-439)."""
+    lv, do, dht, opts, _ = make_inputs(B=2, T=64, gate="precomputed", beta="precomputed", epi=None, l2=False, h0=True)
+    args = (lv["q"], lv["k"], lv["v"], lv["g"], lv["beta"])
+    cu = torch.tensor([0, 64], dtype=torch.int32, device="cuda")
+    with pytest.raises(ValueError, match="batch size"):
+        mk.chunk_kda(*args, cu_seqlens=cu)                                   # varlen needs B == 1
+    with pytest.raises(ValueError, match="initial states"):
+        mk.chunk_kda(*args, initial_state=lv["h0"][:1])                      # one state per sequence
+    with pytest.raises(ValueError, match="gate_mode"):
+        mk.chunk_kda(*args, gate_mode="nope")
+    with pytest.raises(AssertionError):
+        mk.chunk_kda(*args, initial_state=lv["h0"].half())                   # states are float32
+    with pytest.raises(AssertionError):
+        mk.chunk_kda(lv["q"], lv["k"], lv["v"], lv["g"][..., 0], lv["beta"])  # chunk_kda wants a per-channel gate
+    with pytest.raises(AssertionError):
+        mk.chunk_gated_delta_rule(*args)                                     # ... and the scalar entry point a scalar one
+    with pytest.raises(AssertionError):
+        mk.chunk_delta_rule(*args, gate_mode="eda")                          # eda needs A_log
