@@ -115,6 +115,10 @@ int mkda_intra_fwd(const MkdaIntraFwd* p, void* stream);
  * consumers fetch it the same way; hi + lo carries 16 mantissa bits, which is what the products consume anyway.
  * The buffers are typed float* only for size ([NC,HV,128,128] floats = NC*HV tiles). */
 #define MKDA_STATE_TILE_BYTES 65536
+/* Chunk tile: the same idea for a [128][64 tokens] operand, MKDA_CHUNK_TILE_BYTES per (chunk, v-head): bf16 hi (16 KB)
+ * then lo (16 KB), 128 rows x 128 bytes each, same swizzle.  Used for Vd^T [v][token] between mkda_recur_fwd and mkda_out_fwd
+ * (token columns past the end of the chunk are zero). */
+#define MKDA_CHUNK_TILE_BYTES 32768
 
 /* Serial state recurrence per (segment, v-head):  Vd = u + nw S;  S <- diag(gl) S + kbar^T Vd.
  * With want_transition a second CTA per (segment, v-head) carries the segment's K x K transition matrix (same
@@ -130,7 +134,7 @@ typedef struct {
     const int* seg_h0;         /* [NS] row of h0 for each segment, -1 = start from zero; NULL = identity map */
     int state_v_first;         /* layout of h0 / ht */
     float* h;                  /* [NC,HV] state tiles: state entering each chunk, or NULL */
-    float* Vd;                 /* [TT,HV,128] or NULL */
+    float* Vd;                 /* [NC,HV] chunk tiles: Vd^T, or NULL */
     float* ht;                 /* [NS,HV,128,128] state leaving each segment, or NULL */
     int want_transition;
     float* mt;                 /* [NS,HV,128,128] transition (row = output K index), needs want_transition */
@@ -143,7 +147,8 @@ int mkda_recur_fwd(const MkdaRecurFwd* p, void* stream);
 typedef struct {
     MkdaLayout L;
     const void* q; int q_dtype; const float* q_rstd;
-    const float* g_c; const float* Aqk; const float* Vd;
+    const float* g_c; const float* Aqk;
+    const float* Vd;           /* [NC,HV] chunk tiles as written by mkda_recur_fwd */
     const float* h;            /* [NC,HV] state tiles */
     float scale;
     int has_norm; const void* norm_w; int norm_w_dtype;   /* [128] or NULL (=1) */

@@ -134,9 +134,16 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     __shared__ uint64_t ldbar;
-    if (tid == 0) umma::fetch_state_tile(&ldbar, a1h, p.h, (size_t)c * HV + h);     // S^T [v][K index], ready-made operand
-    {   // every other tile is staged untransposed; the transposes come from MN-major operand views
-        float vQ[2][8], vG[2][8], vV[2][8], vA[1][8];
+    if (tid == 0) {   // S^T [v][K index] and Vd^T [v][tok] arrive as ready-made operand tiles, both counted on one barrier
+        const size_t it = (size_t)c * HV + h;
+        umma::mbar_init(&ldbar, 1);
+        umma::fence_barrier_init();
+        umma::mbar_expect_tx(&ldbar, umma::STATE_TILE_BYTES + umma::CHUNK_TILE_BYTES);
+        umma::bulk_load(a1h, reinterpret_cast<const uint8_t*>(p.h) + it * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &ldbar);
+        umma::bulk_load(a2h, reinterpret_cast<const uint8_t*>(p.Vd) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &ldbar);
+    }
+    {   // the other tiles are staged untransposed through registers
+        float vQ[2][8], vG[2][8], vA[1][8];
         load_chunks<2, 512, true>(vQ, 64, 128, [&](int r, int k8, float (&v)[8]) {
             const int rr = r < len ? r : len - 1;
             load8(p.q, QDT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, v);
@@ -144,11 +151,6 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
         load_chunks<2, 512, true>(vG, 64, 128, [&](int r, int k8, float (&v)[8]) {
             const int rr = r < len ? r : len - 1;
             load8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, v);
-        });
-        load_chunks<2, 512, true>(vV, 64, 128, [&](int r, int k8, float (&v)[8]) {
-            const int rr = r < len ? r : len - 1;
-            load8(p.Vd, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, v);
-            if (r >= len) zero8(v);
         });
         load_chunks<1, 512, true>(vA, 64, 64, [&](int r, int k8, float (&v)[8]) {
             const int rr = r < len ? r : len - 1;
@@ -163,15 +165,14 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
             for (int e = 0; e < 8; ++e) vQ[n][e] *= m * ex2f_(vG[n][e]);
         }
         store_chunks<2, 512, true>(b1h, b1l, vQ, 64, 128);
-        store_chunks<2, 512, true>(a2h, a2l, vV, 64, 128);
         store_chunks<1, 512, true>(b2h, b2l, vA, 64, 64);
     }
     MKDA_TRACE_AT(2, 1);
     const uint32_t tmem = tc_operands_ready(&sh);
     MKDA_TRACE_AT(2, 2);
     if (umma::mma_issuer()) {
-        umma::gemm(tmem, umma::opnd_mn(a2h, a2l, 64), umma::opnd_k(b2h, b2l, 64), 128, 64, 64, 0u);
-        umma::mbar_wait(&ldbar, 0);                        // the state tile has landed
+        umma::mbar_wait(&ldbar, 0);                        // both tiles have landed
+        umma::gemm(tmem, umma::opnd_k(a2h, a2l, 128), umma::opnd_k(b2h, b2l, 64), 128, 64, 64, 0u);
         umma::gemm(tmem, umma::opnd_k(a1h, a1l, 128), umma::opnd_k(b1h, b1l, 64), 128, 64, 128, 1u);
         umma::commit(&sh.bar);
     }

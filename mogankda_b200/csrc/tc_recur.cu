@@ -177,20 +177,21 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
         // of the next iteration.
         if (tid == 0 && p.h && !trans)
             umma::bulk_store(reinterpret_cast<uint8_t*>(p.h) + ((size_t)c * HV + h) * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
-        {   // Vd^T = u^T + St nw^T: global copy [tok][v] and operand tile A(m = v, k = tok)
+        {   // Vd^T = u^T + St nw^T as the operand tile A(m = v, k = tok)
             float d[16], a0[8], a1[8];
             umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + cg * 16), d);
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const float vd = d[j] + uu[j];
-                const int t = cg * 16 + j;
-                if (p.Vd && !trans && t < len) p.Vd[((size_t)(start + t) * HV + h) * 128 + row] = vd;
                 if (j < 8) a0[j] = vd; else a1[j - 8] = vd;
             }
             store_split8(sW[buf], sW[buf] + 16384, 128, row, 2 * cg, a0);       // the nw tile is dead: it becomes Vd^T
             store_split8(sW[buf], sW[buf] + 16384, 128, row, 2 * cg + 1, a1);
         }
         publish_operands();
+        // the Vd^T operand tile is also what the output kernel consumes: saved as it is (columns past the end are zero)
+        if (tid == 0 && p.Vd && !trans)
+            umma::bulk_store(reinterpret_cast<uint8_t*>(p.Vd) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES, sW[buf], umma::CHUNK_TILE_BYTES);
         if (umma::mma_issuer()) {
             umma::gemm(tmem, umma::opnd_k(sW[buf], sW[buf] + 16384, 128), umma::opnd_mn(sK[buf], sK[buf] + 16384, 64), 128, 128, 64, 1u);
             umma::commit(&sh.bar);

@@ -212,6 +212,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 // transposed state, rows = v, K-major over the K index, 2 x 32 KB), so a consumer fills its shared-memory operand with one
 // asynchronous copy and no register staging, and the producer writes it straight from the tile it built for its own MMA.
 constexpr uint32_t STATE_TILE_BYTES = 65536;
+// "chunk tile": a [128][64 tokens] operand (hi 16 KB, lo 16 KB), e.g. Vd^T [v][tok], handed over the same way
+constexpr uint32_t CHUNK_TILE_BYTES = 32768;
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
 }

@@ -146,7 +146,7 @@ def intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV):
 def recur_fwd(lay, nw, u, k, k_rstd, g_c, HK, HV, *, h0=None, seg_h0=None, state_v_first=False, store_h=True,
               store_vd=True, want_ht=True, want_transition=False, segments=True):
     """Runs the serial state pass over the layout's segments (or whole sequences with ``segments=False``).
-    Returns (h [NC,HV,128,128] or None, Vd [TT,HV,128] or None, ht [NS,HV,128,128] or None, mt or None)."""
+    Returns (h [NC,HV] state tiles or None, Vd [NC,HV] chunk tiles or None, ht [NS,HV,128,128] or None, mt or None)."""
     dev = nw.device
     NS = lay.NS if segments else lay.N
     p = STRUCTS["MkdaRecurFwd"]()
@@ -155,7 +155,7 @@ def recur_fwd(lay, nw, u, k, k_rstd, g_c, HK, HV, *, h0=None, seg_h0=None, state
     p.g_c = _ptr(g_c)
     p.h0, p.seg_h0, p.state_v_first = _ptr(h0, torch.float32), _ptr(seg_h0, torch.int32), int(state_v_first)
     h = torch.empty(lay.NC, HV, 128, 128, dtype=torch.float32, device=dev) if store_h else None
-    Vd = torch.empty(lay.TT, HV, 128, dtype=torch.float32, device=dev) if store_vd else None
+    Vd = torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=dev) if store_vd else None    # chunk tiles
     ht = torch.empty(NS, HV, 128, 128, dtype=torch.float32, device=dev) if want_ht else None
     mt = torch.empty(NS, HV, 128, 128, dtype=torch.float32, device=dev) if want_transition else None
     p.h, p.Vd, p.ht, p.want_transition, p.mt = _ptr(h), _ptr(Vd), _ptr(ht), int(want_transition), _ptr(mt)

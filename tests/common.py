@@ -116,3 +116,45 @@ def unpack_state_tiles(T):
     halves = T.contiguous().view(torch.bfloat16).reshape(*lead, 2, 128 * 128)
     idx = _state_tile_index().to(T.device)
     return (halves[..., 0, idx].float() + halves[..., 1, idx].float()).reshape(*lead, 128, 128)
+
+
+# ---- chunk tiles (include/mkda.h, MKDA_CHUNK_TILE_BYTES): X^T [128][64 tokens] per (chunk, head) ----------------------------
+def _chunk_tile_index():
+    """int64 [128 (row), 64 (token)] -> position, in bf16 elements, inside one 16 KB half of a chunk tile."""
+    r = torch.arange(128).view(128, 1)
+    t = torch.arange(64).view(1, 64)
+    byte = (r >> 3) * 1024 + (r & 7) * 128 + (((t >> 3) ^ (r & 7)) << 4) + (t & 7) * 2
+    return (byte // 2).reshape(-1)
+
+
+def _chunk_rows(lay):
+    starts, lens = lay.chunk_start.tolist(), lay.chunk_len.tolist()
+    return [(c, s0, n) for c, (s0, n) in enumerate(zip(starts, lens))]
+
+
+def pack_chunk_tiles(X, lay):
+    """token-major fp [TT, H, 128] -> float32-typed chunk tiles [NC, H, 64, 128] (X^T per chunk, zero past the end)."""
+    X = X.float()
+    H = X.shape[1]
+    dense = torch.zeros(lay.NC, H, 128, 64, device=X.device)
+    for c, s0, n in _chunk_rows(lay):
+        dense[c, :, :, :n] = X[s0:s0 + n].permute(1, 2, 0)
+    hi = dense.to(torch.bfloat16)
+    lo = (dense - hi.float()).to(torch.bfloat16)
+    idx = _chunk_tile_index().to(X.device)
+    out = torch.empty(lay.NC, H, 2, 128 * 64, dtype=torch.bfloat16, device=X.device)
+    out[..., 0, idx] = hi.reshape(lay.NC, H, -1)
+    out[..., 1, idx] = lo.reshape(lay.NC, H, -1)
+    return out.view(torch.float32).reshape(lay.NC, H, 64, 128)
+
+
+def unpack_chunk_tiles(T, lay, TT):
+    """Inverse of pack_chunk_tiles -> fp32 [TT, H, 128] (tokens outside every chunk are zero)."""
+    H = T.shape[1]
+    halves = T.contiguous().view(torch.bfloat16).reshape(lay.NC, H, 2, 128 * 64)
+    idx = _chunk_tile_index().to(T.device)
+    dense = (halves[..., 0, idx].float() + halves[..., 1, idx].float()).reshape(lay.NC, H, 128, 64)
+    X = torch.zeros(TT, H, 128, device=T.device)
+    for c, s0, n in _chunk_rows(lay):
+        X[s0:s0 + n] = dense[c, :, :, :n].permute(2, 0, 1)
+    return X

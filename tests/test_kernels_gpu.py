@@ -6,7 +6,8 @@ import torch
 from mogankda_b200 import ops
 from mogankda_b200.index import get_layout
 from oracle import kda_oracle as orc
-from tests.common import VARLEN_CU, make_inputs, pack_state_tiles, unpack_state_tiles
+from tests.common import (VARLEN_CU, make_inputs, pack_chunk_tiles, pack_state_tiles, unpack_chunk_tiles,
+                          unpack_state_tiles)
 
 pytestmark = pytest.mark.gpu
 KTOL = 1e-3          # per-kernel bar (the compensated bf16 hi/lo products measure ~1e-5)
@@ -71,8 +72,8 @@ def test_recurrence_and_output(world):
     lv, fw, f32, lay = world["lv"], world["fw"], world["f32"], world["lay"]
     h, Vd, ht, _ = ops.recur_fwd(lay, f32(fw["nw"]), f32(fw["u"]), lv["k"], world["k_rstd"], f32(fw["g_c"]), 2, 4,
                                  h0=lv["h0"])
-    _err("h", unpack_state_tiles(h), fw["h"]); _err("Vd", Vd, fw["Vd"]); _err("ht", ht, fw["ht"])
-    o, _ = ops.out_fwd(lay, lv["q"], world["q_rstd"], f32(fw["g_c"]), f32(fw["Aqk"]), f32(fw["Vd"]),
+    _err("h", unpack_state_tiles(h), fw["h"]); _err("Vd", unpack_chunk_tiles(Vd, lay, world["TT"]), fw["Vd"]); _err("ht", ht, fw["ht"])
+    o, _ = ops.out_fwd(lay, lv["q"], world["q_rstd"], f32(fw["g_c"]), f32(fw["Aqk"]), pack_chunk_tiles(f32(fw["Vd"]), lay),
                        pack_state_tiles(f32(fw["h"])), world["scale"], 2, 4, torch.float32)
     _err("o", o, fw["o"])
 
