@@ -102,7 +102,7 @@ typedef struct {
     float scale;
     float* A;      /* [TT,HV,64]  rows of (I + strictlower(diag(beta) Gamma))^-1 */
     float* Aqk;    /* [TT,HV,64]  rows of scale * lower(Q K^T with decay) */
-    float* nw;     /* [TT,HV,128] -A diag(beta) (k 2^g) */
+    float* nw;     /* [NC,HV] chunk tiles: nw^T [K index][token], nw = -A (beta k 2^g) */
     float* u;      /* [TT,HV,128]  A (beta v) */
 } MkdaIntraFwd;
 int mkda_intra_fwd(const MkdaIntraFwd* p, void* stream);
@@ -117,7 +117,8 @@ int mkda_intra_fwd(const MkdaIntraFwd* p, void* stream);
 #define MKDA_STATE_TILE_BYTES 65536
 /* Chunk tile: the same idea for a [128][64 tokens] operand, MKDA_CHUNK_TILE_BYTES per (chunk, v-head): bf16 hi (16 KB)
  * then lo (16 KB), 128 rows x 128 bytes each, same swizzle.  Used for Vd^T [v][token] between mkda_recur_fwd and mkda_out_fwd
- * (token columns past the end of the chunk are zero). */
+ * (token columns past the end of the chunk are zero), and for nw^T [K index][token]
+ * between mkda_intra_fwd and the serial kernels. */
 #define MKDA_CHUNK_TILE_BYTES 32768
 
 /* Serial state recurrence per (segment, v-head):  Vd = u + nw S;  S <- diag(gl) S + kbar^T Vd.
@@ -127,7 +128,8 @@ int mkda_intra_fwd(const MkdaIntraFwd* p, void* stream);
  * fused_gdr_h (mogan_kda/ops/gated_delta_rule/chunk/blackwell/prepare_h.py:336-403). */
 typedef struct {
     MkdaLayout L;
-    const float* nw; const float* u;
+    const float* nw;           /* [NC,HV] chunk tiles as written by mkda_intra_fwd */
+    const float* u;            /* [TT,HV,128] */
     const void* k; int k_dtype; const float* k_rstd;
     const float* g_c;
     const float* h0;           /* [*,HV,128,128] or NULL */
@@ -213,7 +215,8 @@ typedef struct {
     MkdaLayout L;
     const void* d_o; int do_dtype;                 /* [TT,HV,128] */
     const void* q; const void* k; int qk_dtype; const float* q_rstd; const float* k_rstd;
-    const float* g_c; const float* Aqk; const float* nw;
+    const float* g_c; const float* Aqk;
+    const float* nw;           /* [NC,HV] chunk tiles as written by mkda_intra_fwd */
     float scale;
     const float* dht;          /* [*,HV,128,128] or NULL */
     const int* seg_dht;        /* [NS] row of dht per segment, -1 = zero; NULL = identity map */

@@ -258,21 +258,31 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     umma::mbar_wait(&sh.bar, 1);
     umma::fence_after_sync();
     MKDA_TRACE_AT(3, 9);
-    {
-        float a[16], b[16];
+    {   // nw^T [K index][tok] leaves as a ready-made chunk tile (the serial kernels fetch it with one bulk copy; token
+        // columns past the end are exact zeros: beta is 0 there)
+        float a[16], n0[8], n1[8];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + 16 * cg), a);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            if (j < 8) n0[j] = -a[j]; else n1[j - 8] = -a[j];
+        }
+        store_split8(base, base + 16384, 128, row, 2 * cg, n0);          // every operand tile is dead by now
+        store_split8(base, base + 16384, 128, row, 2 * cg + 1, n1);
+    }
+    umma::fence_async_smem();
+    __syncthreads();
+    if (tid == 0) umma::bulk_store(reinterpret_cast<uint8_t*>(p.nw) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES, base, umma::CHUNK_TILE_BYTES);
+    {   // u goes out row-wise while the tile is being copied
+        float b[16];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 192 + 16 * cg), b);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const int i = 16 * cg + j;
-            if (i < len) {
-                const size_t o = ((size_t)(start + i) * HV + h) * 128 + row;
-                p.nw[o] = -a[j];
-                p.u[o] = b[j];
-            }
+            if (i < len) p.u[((size_t)(start + i) * HV + h) * 128 + row] = b[j];
         }
     }
     MKDA_TRACE_AT(3, 10);
+    if (tid == 0) umma::bulk_store_wait_read();
     umma::fence_before_sync();
     __syncthreads();
     if (warp == 0) umma::tmem_dealloc(tmem, 256);

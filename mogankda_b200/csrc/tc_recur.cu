@@ -21,6 +21,7 @@ __device__ __forceinline__ void ld8(const void* base, int dtype, size_t idx, flo
 
 struct RecurShared {
     uint64_t bar;
+    uint64_t ldw[2];       // arrival of the nw chunk tiles (bulk copies)
     uint32_t tmem;
     float gl[2][DK];
 };
@@ -41,7 +42,7 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sAh = base;                         // St as A(m = v, k = K index) [128][128]
     uint8_t* sAl = sAh + 32768;
-    uint8_t* sW[2] = {sAl + 32768, sAl + 32768 + 65536};            // nw [tok][K index], hi then lo (16 KB each); later Vd^T [v][tok]
+    uint8_t* sW[2] = {sAl + 32768, sAl + 32768 + 65536};            // nw^T chunk tile [K index][tok] (hi, lo 16 KB each); later Vd^T [v][tok]
     uint8_t* sK[2] = {sW[0] + 32768, sW[1] + 32768};                 // kbar [tok][K index]
 
     const bool trans = blockIdx.x == 1;
@@ -52,7 +53,7 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
     const bool vf = p.state_v_first != 0;
 
     if (warp == 0) umma::tmem_alloc(&sh.tmem, 256);
-    if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
+    if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::mbar_init(&sh.ldw[0], 1); umma::mbar_init(&sh.ldw[1], 1); umma::fence_barrier_init(); }
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
@@ -77,25 +78,10 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
 
     const int c_beg = p.L.seg_chunk_off[seg], c_end = p.L.seg_chunk_off[seg + 1];
     // staging of one chunk's global operands: thread owns chunks i = tid, tid + 512 -> (token r = i / 16, k8 = i % 16)
-    auto load_w = [&](int c, float (&w)[2][8]) {
-        const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-            ld8(p.nw, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, w[n]);
-        }
-    };
-    auto store_w = [&](int c, int buf, float (&w)[2][8]) {
-        const int len = p.L.chunk_len[c];
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
-            if (r >= len) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) w[n][e] = 0.f;
-            }
-            store_split8(sW[buf], sW[buf] + 16384, 64, r, k8, w[n]);
-        }
+    // nw arrives as the ready-made chunk tile written by the intra-chunk kernel: one bulk copy per chunk
+    auto fetch_w = [&](int c, int buf) {
+        umma::mbar_expect_tx(&sh.ldw[buf], umma::CHUNK_TILE_BYTES);
+        umma::bulk_load(sW[buf], reinterpret_cast<const uint8_t*>(p.nw) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[buf]);
     };
     auto load_k = [&](int c, float (&k)[2][8], float (&g)[2][8], float (&gL)[2][8], float (&rs)[2]) {
         const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
@@ -126,25 +112,26 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
     };
 
     if (c_beg < c_end) {
-        float w[2][8], k[2][8], g[2][8], gL[2][8], rs[2];
-        load_w(c_beg, w);
+        float k[2][8], g[2][8], gL[2][8], rs[2];
+        if (tid == 0) fetch_w(c_beg, 0);
         load_k(c_beg, k, g, gL, rs);
-        store_w(c_beg, 0, w);
         store_k(c_beg, 0, k, g, gL, rs);
     }
     for (int c = c_beg; c < c_end; ++c) {
         const int buf = (c - c_beg) & 1, start = p.L.chunk_start[c], len = p.L.chunk_len[c];
         const bool more = c + 1 < c_end;
-        float w[2][8], uu[16];
-        if (more) load_w(c + 1, w);
+        float uu[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const int t = cg * 16 + j, tt = t < len ? t : len - 1;
             uu[j] = trans ? 0.f : p.u[((size_t)(start + tt) * HV + h) * 128 + row];
             if (t >= len) uu[j] = 0.f;
         }
-        if (tid == 0) umma::bulk_store_wait_read();         // the previous chunk's saved tile has left shared memory
-        __syncthreads();                                   // sh.gl[buf] and the tiles of `buf` are complete
+        if (tid == 0) {
+            umma::bulk_store_wait_read();                   // the previous chunk's saved tiles have left shared memory
+            if (more) fetch_w(c + 1, buf ^ 1);              // ... so the other nw / Vd^T buffer can take the next nw tile
+        }
+        __syncthreads();                                   // sh.gl[buf] and the kbar tile of `buf` are complete
         {   // state entering the chunk: operand tile (optionally saved as it is by the issuing thread below), decay
             float s[32];
             umma::tmem_ld32(umma::tmem_addr(tmem, warp, cg * 32), s);
@@ -162,14 +149,12 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
         }
         publish_operands();
         if (umma::mma_issuer()) {
-            umma::gemm(tmem + 128, umma::opnd_k(sAh, sAl, 128), umma::opnd_k(sW[buf], sW[buf] + 16384, 64), 128, 64, 128, 0u);
+            umma::mbar_wait(&sh.ldw[buf], ((c - c_beg) >> 1) & 1);            // this chunk's nw tile has landed
+            umma::gemm(tmem + 128, umma::opnd_k(sAh, sAl, 128), umma::opnd_mn(sW[buf], sW[buf] + 16384, 128), 128, 64, 128, 0u);
             umma::commit(&sh.bar);
         }
         float k[2][8], g[2][8], gL[2][8], rs[2];
-        if (more) {
-            store_w(c + 1, buf ^ 1, w);
-            load_k(c + 1, k, g, gL, rs);
-        }
+        if (more) load_k(c + 1, k, g, gL, rs);
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;
         umma::fence_after_sync();
         // The operand tile doubles as the saved state of this chunk: one asynchronous 64 KB copy, issued and later awaited
@@ -266,7 +251,7 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
     uint8_t* sAq = sDo + 32768;                  // Aqk [i][j]         hi 8 KB, lo 8 KB
     uint8_t* sKb = sAq + 16384;                  // kbar [j][K index]; later dVd^T [v][j]
     uint8_t* sQs = sKb + 32768;                  // scale q 2^g [i][K index]
-    uint8_t* sNw = sQs + 32768;                  // nw [j][K index]
+    uint8_t* sNw = sQs + 32768;                  // nw^T chunk tile [K index][j], fetched by bulk copy
 
     const int h = blockIdx.y, seg = blockIdx.z, HV = p.L.HV, HK = p.L.HK;
     const int hk = h / (HV / HK);
@@ -275,7 +260,7 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
     const bool vf = p.state_v_first != 0;
 
     if (warp == 0) umma::tmem_alloc(&sh.tmem, 256);
-    if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
+    if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::mbar_init(&sh.ldw[0], 1); umma::mbar_init(&sh.ldw[1], 1); umma::fence_barrier_init(); }
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
@@ -299,14 +284,17 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
         const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
         {   // all global operands of the chunk are requested together: dO, Aqk, nw (plain copies), then k, q, g for
             // kbar = k 2^(gL - g) and q~ = scale q 2^g
-            float vo[2][8], vn[2][8], va[8], vk[2][8], vq[2][8], vg[2][8], vl[8], rk[2], rq[2];
+            float vo[2][8], va[8], vk[2][8], vq[2][8], vg[2][8], vl[8], rk[2], rq[2];
+            if (tid == 0) {                                 // the nw tile's last reader, the previous chunk's second product, is done
+                umma::mbar_expect_tx(&sh.ldw[0], umma::CHUNK_TILE_BYTES);
+                umma::bulk_load(sNw, reinterpret_cast<const uint8_t*>(p.nw) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[0]);
+            }
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
                 const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
                 const size_t off = ((size_t)(start + rr) * HV + h) * 128 + k8 * 8;
                 const size_t tk = (size_t)(start + rr) * HK + hk;
                 ld8(p.d_o, DODT, off, vo[n]);
-                ld8(p.nw, MKDA_F32, off, vn[n]);
                 ld8(p.k, QKDT, tk * 128 + k8 * 8, vk[n]);
                 ld8(p.q, QKDT, tk * 128 + k8 * 8, vq[n]);
                 ld8(p.g_c, MKDA_F32, off, vg[n]);
@@ -329,10 +317,9 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
                 const float mk = r < len ? rk[n] : 0.f, mq = r < len ? rq[n] : 0.f;
                 if (r >= len) {
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) { vo[n][e] = 0.f; vn[n][e] = 0.f; }
+                    for (int e = 0; e < 8; ++e) vo[n][e] = 0.f;
                 }
                 store_split8(sDo, sDo + 16384, 64, r, k8, vo[n]);
-                store_split8(sNw, sNw + 16384, 64, r, k8, vn[n]);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     vk[n][e] *= mk * ex2f_(vl[e] - vg[n][e]);
@@ -389,7 +376,8 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
         publish_operands();
         if (umma::mma_issuer()) {
             umma::gemm(tmem, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sQs, sQs + 16384, 64), 128, 128, 64, 1u);
-            umma::gemm(tmem, umma::opnd_k(sKb, sKb + 16384, 128), umma::opnd_mn(sNw, sNw + 16384, 64), 128, 128, 64, 1u);
+            umma::mbar_wait(&sh.ldw[0], ((c_end - 1 - c) & 1));               // this chunk's nw tile has landed
+            umma::gemm(tmem, umma::opnd_k(sKb, sKb + 16384, 128), umma::opnd_k(sNw, sNw + 16384, 128), 128, 128, 64, 1u);
             umma::commit(&sh.bar);
         }
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;

@@ -132,7 +132,8 @@ def l2norm_rstd(x, eps=1e-6):
 def intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV):
     dev = q.device
     z = lambda w: torch.empty(lay.TT, HV, w, dtype=torch.float32, device=dev)      # noqa: E731
-    A, Aqk, nw, u = z(64), z(64), z(128), z(128)
+    A, Aqk, u = z(64), z(64), z(128)
+    nw = torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=q.device)      # chunk tiles: nw^T per (chunk, head)
     p = STRUCTS["MkdaIntraFwd"]()
     p.L = _layout_struct(lay, HK, HV)
     p.q, p.k, p.v, p.qkv_dtype = _ptr(q), _ptr(k), _ptr(v), _dt(q)

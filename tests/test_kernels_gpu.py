@@ -57,6 +57,7 @@ def test_intra_fwd(world):
     lv, fw, f32 = world["lv"], world["fw"], world["f32"]
     A, Aqk, nw, u = ops.intra_fwd(world["lay"], lv["q"], lv["k"], lv["v"], world["q_rstd"], world["k_rstd"],
                                   f32(fw["g_c"]), world["be"], world["scale"], 2, 4)
+    nw = unpack_chunk_tiles(nw, world["lay"], world["TT"])
     for n, t in dict(A=A, Aqk=Aqk, nw=nw, u=u).items():
         _err(n, t, fw[n])
     idx = torch.arange(64, device="cuda")
@@ -70,9 +71,11 @@ def test_intra_fwd(world):
 
 def test_recurrence_and_output(world):
     lv, fw, f32, lay = world["lv"], world["fw"], world["f32"], world["lay"]
-    h, Vd, ht, _ = ops.recur_fwd(lay, f32(fw["nw"]), f32(fw["u"]), lv["k"], world["k_rstd"], f32(fw["g_c"]), 2, 4,
+    h, Vd, ht, _ = ops.recur_fwd(lay, pack_chunk_tiles(f32(fw["nw"]), lay), f32(fw["u"]), lv["k"], world["k_rstd"],
+                                 f32(fw["g_c"]), 2, 4,
                                  h0=lv["h0"])
-    _err("h", unpack_state_tiles(h), fw["h"]); _err("Vd", unpack_chunk_tiles(Vd, lay, world["TT"]), fw["Vd"]); _err("ht", ht, fw["ht"])
+    _err("h", unpack_state_tiles(h), fw["h"]); _err("Vd", unpack_chunk_tiles(Vd, lay, world["TT"]), fw["Vd"])
+    _err("ht", ht, fw["ht"])
     o, _ = ops.out_fwd(lay, lv["q"], world["q_rstd"], f32(fw["g_c"]), f32(fw["Aqk"]), pack_chunk_tiles(f32(fw["Vd"]), lay),
                        pack_state_tiles(f32(fw["h"])), world["scale"], 2, 4, torch.float32)
     _err("o", o, fw["o"])
@@ -81,7 +84,7 @@ def test_recurrence_and_output(world):
 def test_transition_matrix_reproduces_the_state_pass(world):
     """State leaving a segment = transition @ state entering + state reached from zero (what the prefix combine uses)."""
     lv, fw, f32, lay = world["lv"], world["fw"], world["f32"], world["lay"]
-    args = (lay, f32(fw["nw"]), f32(fw["u"]), lv["k"], world["k_rstd"], f32(fw["g_c"]), 2, 4)
+    args = (lay, pack_chunk_tiles(f32(fw["nw"]), lay), f32(fw["u"]), lv["k"], world["k_rstd"], f32(fw["g_c"]), 2, 4)
     _, _, hs, ms = ops.recur_fwd(*args, store_h=False, store_vd=False, want_transition=True)
     _, _, ht, _ = ops.recur_fwd(*args, h0=lv["h0"], store_h=False, store_vd=False)
     _err("M h0 + h", ms.double() @ lv["h0"].double() + hs.double(), ht)
@@ -93,7 +96,8 @@ def test_transition_matrix_reproduces_the_state_pass(world):
 def test_bwd_dh(world):
     lv, fw, bw, f32 = world["lv"], world["fw"], world["bw"], world["f32"]
     dh, dVd, dh0 = ops.bwd_dh(world["lay"], world["do"], lv["q"], lv["k"], world["q_rstd"], world["k_rstd"],
-                              f32(fw["g_c"]), f32(fw["Aqk"]), f32(fw["nw"]), world["scale"], 2, 4, dht=world["dht"])
+                              f32(fw["g_c"]), f32(fw["Aqk"]), pack_chunk_tiles(f32(fw["nw"]), world["lay"]), world["scale"], 2, 4,
+                              dht=world["dht"])
     _err("dh", unpack_state_tiles(dh), bw["dh"]); _err("dVd", dVd, bw["dVd"]); _err("dh0", dh0, bw["dh0"])
 
 
