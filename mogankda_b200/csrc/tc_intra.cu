@@ -584,6 +584,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
 #pragma unroll
             for (int r = 0; r < 8; ++r) dkc[r] += c8[r] * ex2f_(ga[I] - gg[8 * hf + r]);
         }
+        float bsv[8];
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
             const int i = c0 + r, rr = 8 * hf + r;
@@ -591,10 +592,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
             const float up = ex2f_(g), re = ex2f_(gL - g), e = ex2f_(g - ga[cg]);
             const float dqt = p.scale * aq[r], dkt = -ak[r], dkb = ab[r];
             const float dqr = vr[r] * e, T = vt[r] * e, bt = sh.beta[i], dgn = sDiag[i];
-            float bs = kv * T;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, o);
-            if (lane == 0) sRed[q][i] = bs;
+            bsv[r] = kv * T;
             if (i < len) {
                 float dg = qv * up * dqt + kv * up * dkt - kv * re * dkb;
                 if (i == len - 1) dg += extra;
@@ -604,6 +602,25 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
                 p.dgp[off] = dg + qv * dqr + kv * bt * T - kv * dkc[r];
             }
         }
+        // sum over the 32 channels of this warp for the 8 rows at once: every exchange halves the number of rows a lane
+        // carries (9 shuffles instead of 40); the lane whose bits 4..2 spell the row ends up with its sum
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const float recv = __shfl_xor_sync(0xffffffffu, (lane & 16) ? bsv[r] : bsv[r + 4], 16);
+            bsv[r] = ((lane & 16) ? bsv[r + 4] : bsv[r]) + recv;
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const float recv = __shfl_xor_sync(0xffffffffu, (lane & 8) ? bsv[r] : bsv[r + 2], 8);
+            bsv[r] = ((lane & 8) ? bsv[r + 2] : bsv[r]) + recv;
+        }
+        {
+            const float recv = __shfl_xor_sync(0xffffffffu, (lane & 4) ? bsv[0] : bsv[1], 4);
+            bsv[0] = ((lane & 4) ? bsv[1] : bsv[0]) + recv;
+        }
+        bsv[0] += __shfl_xor_sync(0xffffffffu, bsv[0], 2);
+        bsv[0] += __shfl_xor_sync(0xffffffffu, bsv[0], 1);
+        if ((lane & 3) == 0) sRed[q][c0 + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = bsv[0];
     }
     MKDA_TRACE_AT(5, 10);
     __syncthreads();
