@@ -444,15 +444,25 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + 64 + cg * 16), d);
         load_tile8(sAh, sAl, 64, i, 2 * cg, a0);
         load_tile8(sAh, sAl, 64, i, 2 * cg + 1, a1);
+        float pr[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            float pr = d[j] * (j < 8 ? a0[j] : a1[j - 8]);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) pr += __shfl_xor_sync(0xffffffffu, pr, o);
-            if (lane == 0) sRed[q - 2][cg * 16 + j] = pr;
+            pr[j] = d[j] * (j < 8 ? a0[j] : a1[j - 8]);
             const float da = d[j] * sBeta[cg * 16 + j];
             if (j < 8) a0[j] = da; else a1[j - 8] = da;
         }
+        // sums over the 32 lanes for the 16 columns at once: every exchange halves the number of columns a lane carries
+        // (16 shuffles instead of 80); the lane whose bits 4..1 spell the column ends up with its sum
+#pragma unroll
+        for (int w = 8, bit = 16; w >= 1; w >>= 1, bit >>= 1) {
+#pragma unroll
+            for (int j = 0; j < w; ++j) {
+                const float recv = __shfl_xor_sync(0xffffffffu, (lane & bit) ? pr[j] : pr[j + w], bit);
+                pr[j] = ((lane & bit) ? pr[j + w] : pr[j]) + recv;
+            }
+        }
+        pr[0] += __shfl_xor_sync(0xffffffffu, pr[0], 1);
+        if ((lane & 1) == 0) sRed[q - 2][cg * 16 + ((lane >> 1) & 15)] = pr[0];
         store_split8(sKh, sKl, 128, i, 2 * cg, a0);
         store_split8(sKh, sKl, 128, i, 2 * cg + 1, a1);
     }
