@@ -134,8 +134,8 @@ KERNEL_BYTES = {
 # DRAM traffic per token per v-head measured by ncu on the 1B-shape case (profiles/counters_per_kernel_1b_shape.md),
 # bytes (dram read + write per launch / 131072 token-heads); it grows in proportion to tokens x heads.
 KERNEL_TRAFFIC = {
-    "mkda_intra_fwd": 2151, "mkda_recur_fwd": 2932, "mkda_out_fwd": 3503, "mkda_bwd_dh": 3327, "mkda_bwd_wy": 4499,
-    "mkda_bwd_tail": 6618, "mkda_gate_cumsum_fwd": 644, "mkda_epilogue_bwd": 1778, "mkda_qk_grad_finish": 654,
+    "mkda_intra_fwd": 2153, "mkda_recur_fwd": 2907, "mkda_out_fwd": 3508, "mkda_bwd_dh": 3328, "mkda_bwd_wy": 4500,
+    "mkda_bwd_tail": 6803, "mkda_gate_cumsum_fwd": 641, "mkda_epilogue_bwd": 1781, "mkda_qk_grad_finish": 650,
     "mkda_l2norm_rstd": 128,
 }
 
