@@ -100,8 +100,8 @@ typedef struct {
     const float* q_rstd; const float* k_rstd;      /* [TT,HK] or NULL */
     const float* g_c; const float* beta;           /* [TT,HV,128], [TT,HV] */
     float scale;
-    float* A;      /* [TT,HV,64]  rows of (I + strictlower(diag(beta) Gamma))^-1 */
-    float* Aqk;    /* [TT,HV,64]  rows of scale * lower(Q K^T with decay) */
+    float* A;      /* [NC,HV] quarter tiles: (I + strictlower(diag(beta) Gamma))^-1 */
+    float* Aqk;    /* [NC,HV] quarter tiles: scale * lower(Q K^T with decay) */
     float* nw;     /* [NC,HV] chunk tiles: nw^T [K index][token], nw = -A (beta k 2^g) */
     float* u;      /* [TT,HV,128]  A (beta v) */
 } MkdaIntraFwd;
@@ -120,6 +120,10 @@ int mkda_intra_fwd(const MkdaIntraFwd* p, void* stream);
  * (token columns past the end of the chunk are zero), and for nw^T [K index][token]
  * between mkda_intra_fwd and the serial kernels. */
 #define MKDA_CHUNK_TILE_BYTES 32768
+/* Quarter tile: a [64][64] operand, MKDA_QUARTER_TILE_BYTES per (chunk, v-head): bf16 hi (8 KB) then lo (8 KB), 64 rows x
+ * 128 bytes, same swizzle.  Used for the intra-chunk matrices A and Aqk, [row i][column j]; rows past the end of the chunk
+ * are identity rows in A and zero rows in Aqk. */
+#define MKDA_QUARTER_TILE_BYTES 16384
 
 /* Serial state recurrence per (segment, v-head):  Vd = u + nw S;  S <- diag(gl) S + kbar^T Vd.
  * With want_transition a second CTA per (segment, v-head) carries the segment's K x K transition matrix (same
@@ -149,7 +153,8 @@ int mkda_recur_fwd(const MkdaRecurFwd* p, void* stream);
 typedef struct {
     MkdaLayout L;
     const void* q; int q_dtype; const float* q_rstd;
-    const float* g_c; const float* Aqk;
+    const float* g_c;
+    const float* Aqk;          /* [NC,HV] quarter tiles as written by mkda_intra_fwd */
     const float* Vd;           /* [NC,HV] chunk tiles as written by mkda_recur_fwd */
     const float* h;            /* [NC,HV] state tiles */
     float scale;
@@ -215,7 +220,8 @@ typedef struct {
     MkdaLayout L;
     const void* d_o; int do_dtype;                 /* [TT,HV,128] */
     const void* q; const void* k; int qk_dtype; const float* q_rstd; const float* k_rstd;
-    const float* g_c; const float* Aqk;
+    const float* g_c;
+    const float* Aqk;          /* [NC,HV] quarter tiles as written by mkda_intra_fwd */
     const float* nw;           /* [NC,HV] chunk tiles as written by mkda_intra_fwd */
     float scale;
     const float* dht;          /* [*,HV,128,128] or NULL */
@@ -232,7 +238,8 @@ int mkda_bwd_dh(const MkdaBwdDh* p, void* stream);
 typedef struct {
     MkdaLayout L;
     const void* k; const void* v; int kv_dtype; const float* k_rstd;
-    const float* g_c; const float* beta; const float* A;
+    const float* g_c; const float* beta;
+    const float* A;            /* [NC,HV] quarter tiles as written by mkda_intra_fwd */
     const float* h;            /* [NC,HV] state tiles */
     const void* d_o; int do_dtype; const float* dVd;
     float* Vd;                 /* [TT,HV,128] recomputed */

@@ -134,16 +134,17 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     __shared__ uint64_t ldbar;
-    if (tid == 0) {   // S^T [v][K index] and Vd^T [v][tok] arrive as ready-made operand tiles, both counted on one barrier
+    if (tid == 0) {   // S^T [v][K index], Vd^T [v][tok] and Aqk [i][j] arrive as ready-made operand tiles on one barrier
         const size_t it = (size_t)c * HV + h;
         umma::mbar_init(&ldbar, 1);
         umma::fence_barrier_init();
-        umma::mbar_expect_tx(&ldbar, umma::STATE_TILE_BYTES + umma::CHUNK_TILE_BYTES);
+        umma::mbar_expect_tx(&ldbar, umma::STATE_TILE_BYTES + umma::CHUNK_TILE_BYTES + umma::QUARTER_TILE_BYTES);
+        umma::bulk_load(b2h, reinterpret_cast<const uint8_t*>(p.Aqk) + it * umma::QUARTER_TILE_BYTES, umma::QUARTER_TILE_BYTES, &ldbar);
         umma::bulk_load(a1h, reinterpret_cast<const uint8_t*>(p.h) + it * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &ldbar);
         umma::bulk_load(a2h, reinterpret_cast<const uint8_t*>(p.Vd) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &ldbar);
     }
     {   // the other tiles are staged untransposed through registers
-        float vQ[2][8], vG[2][8], vA[1][8];
+        float vQ[2][8], vG[2][8];
         load_chunks<2, 512, true>(vQ, 64, 128, [&](int r, int k8, float (&v)[8]) {
             const int rr = r < len ? r : len - 1;
             load8(p.q, QDT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, v);
@@ -151,11 +152,6 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
         load_chunks<2, 512, true>(vG, 64, 128, [&](int r, int k8, float (&v)[8]) {
             const int rr = r < len ? r : len - 1;
             load8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, v);
-        });
-        load_chunks<1, 512, true>(vA, 64, 64, [&](int r, int k8, float (&v)[8]) {
-            const int rr = r < len ? r : len - 1;
-            load8(p.Aqk, MKDA_F32, ((size_t)(start + rr) * HV + h) * 64 + k8 * 8, v);
-            if (r >= len) zero8(v);
         });
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
@@ -165,7 +161,6 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
             for (int e = 0; e < 8; ++e) vQ[n][e] *= m * ex2f_(vG[n][e]);
         }
         store_chunks<2, 512, true>(b1h, b1l, vQ, 64, 128);
-        store_chunks<1, 512, true>(b2h, b2l, vA, 64, 64);
     }
     MKDA_TRACE_AT(2, 1);
     const uint32_t tmem = tc_operands_ready(&sh);
@@ -318,12 +313,19 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
 
     if (tid < CH) sBeta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
     __shared__ uint64_t ldbar;
-    if (tid == 0) umma::fetch_state_tile(&ldbar, sSh, p.h, (size_t)c * HV + h);      // S^T [v][K index], ready-made operand
+    if (tid == 0) {   // S^T [v][K index] and A [i][j] arrive as ready-made operand tiles on one barrier
+        const size_t it = (size_t)c * HV + h;
+        umma::mbar_init(&ldbar, 1);
+        umma::fence_barrier_init();
+        umma::mbar_expect_tx(&ldbar, umma::STATE_TILE_BYTES + umma::QUARTER_TILE_BYTES);
+        umma::bulk_load(sAh, reinterpret_cast<const uint8_t*>(p.A) + it * umma::QUARTER_TILE_BYTES, umma::QUARTER_TILE_BYTES, &ldbar);
+        umma::bulk_load(sSh, reinterpret_cast<const uint8_t*>(p.h) + it * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &ldbar);
+    }
     // everything the first three stages need from global memory is requested up front: k, g, A, then [dO; dVd] rows and
     // this thread's V column, which stay in registers until G1 has released the state tile
     float vT[4][8], vv[16];
     {
-        float vK[2][8], vG[2][8], vA[1][8];
+        float vK[2][8], vG[2][8];
         load_chunks<2, 512, true>(vK, 64, 128, [&](int r, int k8, float (&v)[8]) {
             const int rr = r < len ? r : len - 1;
             load8(p.k, KVDT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, v);
@@ -331,10 +333,6 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
         load_chunks<2, 512, true>(vG, 64, 128, [&](int r, int k8, float (&v)[8]) {
             const int rr = r < len ? r : len - 1;
             load8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, v);
-        });
-        load_chunks<1, 512, true>(vA, 64, 64, [&](int r, int k8, float (&v)[8]) {
-            const int rr = r < len ? r : len - 1;
-            load8(p.A, MKDA_F32, ((size_t)(start + rr) * HV + h) * 64 + k8 * 8, v);
         });
         load_chunks<4, 512, true>(vT, 128, 128, [&](int r, int k8, float (&v)[8]) {
             const int t = r & 63, tt = t < len ? t : len - 1;
@@ -356,15 +354,6 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
             for (int e = 0; e < 8; ++e) vK[n][e] *= rk * ex2f_(vG[n][e]);
         }
         store_chunks<2, 512, true>(sKh, sKl, vK, 64, 128);
-        {
-            const int r = tid >> 3, k8 = tid & 7;
-            if (r >= len) zero8(vA[0]);
-            store_split8(sAh, sAl, 64, r, k8, vA[0]);
-            __syncthreads();                                      // sBeta
-#pragma unroll
-            for (int e = 0; e < 8; ++e) vA[0][e] *= sBeta[k8 * 8 + e];
-            store_split8(sBh, sBl, 64, r, k8, vA[0]);
-        }
     }
     MKDA_TRACE_AT(1, 2);
     const uint32_t tmem = tc_operands_ready(&sh);
@@ -372,6 +361,15 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
         umma::mbar_wait(&ldbar, 0);                        // the state tile has landed
         umma::gemm(tmem + 0, umma::opnd_k(sSh, sSl, 128), umma::opnd_k(sKh, sKl, 64), 128, 64, 128, 0u);
         umma::commit(&sh.bar);
+    }
+    {   // A diag(beta) from the A tile that came with the state tile (rows past the end are identity rows: their beta is 0)
+        umma::mbar_wait(&ldbar, 0);
+        const int r = tid >> 3, k8 = tid & 7;
+        float a8[8];
+        load_tile8(sAh, sAl, 64, r, k8, a8);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a8[e] *= sBeta[k8 * 8 + e];
+        store_split8(sBh, sBl, 64, r, k8, a8);
     }
     {
 #pragma unroll

@@ -125,6 +125,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     uint8_t* sBk = base;                               // phase 3: beta k~ [j][K index], hi 16 KB + lo 16 KB
     uint8_t* sBv = base + 32768;                       // beta v [j][v]
     uint8_t* sTA = base + 65536;                       // A [i][j], hi 8 KB + lo 8 KB
+    uint8_t* sTQ = base + 81920;                       // Aqk [i][j], hi 8 KB + lo 8 KB (only copied out)
 
     const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV, HK = p.L.HK;
     const int hk = h / (HV / HK);
@@ -234,20 +235,21 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     MKDA_TRACE_AT(3, 6);
     invert_unit_lower(sM, sInv, sh);
     MKDA_TRACE_AT(3, 7);
-    {   // A as the B operand of phase 3, plus the global copies of A and Aqk (full rows, coalesced)
+    {   // A as the B operand of phase 3; A and Aqk also leave as ready-made [row][column] operand tiles (rows past the end:
+        // identity rows of A, zero rows of Aqk)
         const int r = tid >> 3, k8 = tid & 7;
-        float a8[8];
+        float a8[8], q8[8];
         lds8(sInv + r * MLD + k8 * 8, a8);
+        lds8(sP + r * MLD + k8 * 8, q8);
         store_split8(sTA, sTA + 8192, 64, r, k8, a8);
-        if (r < len) {
-            const size_t o = ((size_t)(start + r) * HV + h) * 64 + k8 * 8;
-            *reinterpret_cast<float4*>(p.A + o) = make_float4(a8[0], a8[1], a8[2], a8[3]);
-            *reinterpret_cast<float4*>(p.A + o + 4) = make_float4(a8[4], a8[5], a8[6], a8[7]);
-            *reinterpret_cast<float4*>(p.Aqk + o) = *reinterpret_cast<const float4*>(sP + r * MLD + k8 * 8);
-            *reinterpret_cast<float4*>(p.Aqk + o + 4) = *reinterpret_cast<const float4*>(sP + r * MLD + k8 * 8 + 4);
-        }
+        store_split8(sTQ, sTQ + 8192, 64, r, k8, q8);
     }
     publish();
+    if (tid == 0) {
+        const size_t it = (size_t)c * HV + h;
+        umma::bulk_store(reinterpret_cast<uint8_t*>(p.A) + it * umma::QUARTER_TILE_BYTES, sTA, umma::QUARTER_TILE_BYTES);
+        umma::bulk_store(reinterpret_cast<uint8_t*>(p.Aqk) + it * umma::QUARTER_TILE_BYTES, sTQ, umma::QUARTER_TILE_BYTES);
+    }
     if (umma::mma_issuer()) {
         const umma::Opnd bA = umma::opnd_k(sTA, sTA + 8192, 64);
         umma::gemm(tmem + 128, umma::opnd_mn(sBk, sBk + 16384, 64), bA, 128, 64, 64, 0u);

@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
     uint8_t* sAh = base;                         // dSt as A(m = v, k = K index)
     uint8_t* sAl = sAh + 32768;
     uint8_t* sDo = sAl + 32768;                  // dO [i][v]          hi 16 KB, lo 16 KB
-    uint8_t* sAq = sDo + 32768;                  // Aqk [i][j]         hi 8 KB, lo 8 KB
+    uint8_t* sAq = sDo + 32768;                  // Aqk [i][j] quarter tile (hi 8 KB, lo 8 KB), fetched by bulk copy
     uint8_t* sKb = sAq + 16384;                  // kbar [j][K index]; later dVd^T [v][j]
     uint8_t* sQs = sKb + 32768;                  // scale q 2^g [i][K index]
     uint8_t* sNw = sQs + 32768;                  // nw^T chunk tile [K index][j], fetched by bulk copy
@@ -284,10 +284,13 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
         const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
         {   // all global operands of the chunk are requested together: dO, Aqk, nw (plain copies), then k, q, g for
             // kbar = k 2^(gL - g) and q~ = scale q 2^g
-            float vo[2][8], va[8], vk[2][8], vq[2][8], vg[2][8], vl[8], rk[2], rq[2];
-            if (tid == 0) {                                 // the nw tile's last reader, the previous chunk's second product, is done
-                umma::mbar_expect_tx(&sh.ldw[0], umma::CHUNK_TILE_BYTES);
-                umma::bulk_load(sNw, reinterpret_cast<const uint8_t*>(p.nw) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[0]);
+            float vo[2][8], vk[2][8], vq[2][8], vg[2][8], vl[8], rk[2], rq[2];
+            if (tid == 0) {                                 // the last readers of both tiles, the previous chunk's products, are done
+                const size_t it = (size_t)c * HV + h;
+                umma::mbar_expect_tx(&sh.ldw[1], umma::QUARTER_TILE_BYTES);           // Aqk: needed by the first product
+                umma::bulk_load(sAq, reinterpret_cast<const uint8_t*>(p.Aqk) + it * umma::QUARTER_TILE_BYTES, umma::QUARTER_TILE_BYTES, &sh.ldw[1]);
+                umma::mbar_expect_tx(&sh.ldw[0], umma::CHUNK_TILE_BYTES);             // nw: needed by the second one
+                umma::bulk_load(sNw, reinterpret_cast<const uint8_t*>(p.nw) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[0]);
             }
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
@@ -302,15 +305,6 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
                 rq[n] = p.scale * (p.q_rstd ? p.q_rstd[tk] : 1.f);
             }
             ld8(p.g_c, MKDA_F32, ((size_t)(start + len - 1) * HV + h) * 128 + (tid & 15) * 8, vl);
-            {
-                const int r = tid >> 3, k8 = tid & 7, rr = r < len ? r : len - 1;
-                ld8(p.Aqk, MKDA_F32, ((size_t)(start + rr) * HV + h) * 64 + k8 * 8, va);
-                if (r >= len) {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) va[e] = 0.f;
-                }
-                store_split8(sAq, sAq + 8192, 64, r, k8, va);
-            }
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
                 const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
@@ -355,6 +349,7 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
         // before the tile is rebuilt in the next iteration (measured: starting it here is faster than after the products)
         if (tid == 0) umma::bulk_store(reinterpret_cast<uint8_t*>(p.dh) + ((size_t)c * HV + h) * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
         if (umma::mma_issuer()) {
+            umma::mbar_wait(&sh.ldw[1], ((c_end - 1 - c) & 1));               // this chunk's Aqk tile has landed
             umma::gemm(tmem + 128, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sAq, sAq + 8192, 64), 128, 64, 64, 0u);
             umma::gemm(tmem + 128, umma::opnd_k(sAh, sAl, 128), umma::opnd_k(sKb, sKb + 16384, 64), 128, 64, 128, 1u);
             umma::commit(&sh.bar);

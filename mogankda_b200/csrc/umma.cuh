@@ -214,6 +214,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 constexpr uint32_t STATE_TILE_BYTES = 65536;
 // "chunk tile": a [128][64 tokens] operand (hi 16 KB, lo 16 KB), e.g. Vd^T [v][tok], handed over the same way
 constexpr uint32_t CHUNK_TILE_BYTES = 32768;
+// "quarter tile": a [64][64] operand (hi 8 KB, lo 8 KB): the intra-chunk matrices A and Aqk [row][column]
+constexpr uint32_t QUARTER_TILE_BYTES = 16384;
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
 }

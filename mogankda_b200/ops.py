@@ -132,7 +132,9 @@ def l2norm_rstd(x, eps=1e-6):
 def intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV):
     dev = q.device
     z = lambda w: torch.empty(lay.TT, HV, w, dtype=torch.float32, device=dev)      # noqa: E731
-    A, Aqk, u = z(64), z(64), z(128)
+    u = z(128)
+    A = torch.empty(lay.NC, HV, 32, 128, dtype=torch.float32, device=q.device)       # quarter tiles per (chunk, head)
+    Aqk = torch.empty(lay.NC, HV, 32, 128, dtype=torch.float32, device=q.device)
     nw = torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=q.device)      # chunk tiles: nw^T per (chunk, head)
     p = STRUCTS["MkdaIntraFwd"]()
     p.L = _layout_struct(lay, HK, HV)

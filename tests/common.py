@@ -158,3 +158,39 @@ def unpack_chunk_tiles(T, lay, TT):
     for c, s0, n in _chunk_rows(lay):
         X[s0:s0 + n] = dense[c, :, :, :n].permute(2, 0, 1)
     return X
+
+
+# ---- quarter tiles (include/mkda.h, MKDA_QUARTER_TILE_BYTES): a [64][64] matrix per (chunk, head) ------------------------
+def _quarter_tile_index():
+    i = torch.arange(64).view(64, 1)
+    j = torch.arange(64).view(1, 64)
+    byte = (i >> 3) * 1024 + (i & 7) * 128 + (((j >> 3) ^ (i & 7)) << 4) + (j & 7) * 2
+    return (byte // 2).reshape(-1)
+
+
+def pack_quarter_tiles(X, lay):
+    """token-major rows fp [TT, H, 64] -> float32-typed quarter tiles [NC, H, 32, 128] (row i of chunk c = token start+i)."""
+    X = X.float()
+    H = X.shape[1]
+    dense = torch.zeros(lay.NC, H, 64, 64, device=X.device)
+    for c, s0, n in _chunk_rows(lay):
+        dense[c, :, :n] = X[s0:s0 + n].permute(1, 0, 2)
+    hi = dense.to(torch.bfloat16)
+    lo = (dense - hi.float()).to(torch.bfloat16)
+    idx = _quarter_tile_index().to(X.device)
+    out = torch.empty(lay.NC, H, 2, 64 * 64, dtype=torch.bfloat16, device=X.device)
+    out[..., 0, idx] = hi.reshape(lay.NC, H, -1)
+    out[..., 1, idx] = lo.reshape(lay.NC, H, -1)
+    return out.view(torch.float32).reshape(lay.NC, H, 32, 128)
+
+
+def unpack_quarter_tiles(T, lay, TT):
+    """Inverse of pack_quarter_tiles -> fp32 [TT, H, 64] (rows past the end of a chunk are dropped)."""
+    H = T.shape[1]
+    halves = T.contiguous().view(torch.bfloat16).reshape(lay.NC, H, 2, 64 * 64)
+    idx = _quarter_tile_index().to(T.device)
+    dense = (halves[..., 0, idx].float() + halves[..., 1, idx].float()).reshape(lay.NC, H, 64, 64)
+    X = torch.zeros(TT, H, 64, device=T.device)
+    for c, s0, n in _chunk_rows(lay):
+        X[s0:s0 + n] = dense[c, :, :n].permute(1, 0, 2)
+    return X

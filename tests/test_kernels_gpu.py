@@ -6,8 +6,8 @@ import torch
 from mogankda_b200 import ops
 from mogankda_b200.index import get_layout
 from oracle import kda_oracle as orc
-from tests.common import (VARLEN_CU, make_inputs, pack_chunk_tiles, pack_state_tiles, unpack_chunk_tiles,
-                          unpack_state_tiles)
+from tests.common import (VARLEN_CU, make_inputs, pack_chunk_tiles, pack_quarter_tiles, pack_state_tiles,
+                          unpack_chunk_tiles, unpack_quarter_tiles, unpack_state_tiles)
 
 pytestmark = pytest.mark.gpu
 KTOL = 1e-3          # per-kernel bar (the compensated bf16 hi/lo products measure ~1e-5)
@@ -58,6 +58,7 @@ def test_intra_fwd(world):
     A, Aqk, nw, u = ops.intra_fwd(world["lay"], lv["q"], lv["k"], lv["v"], world["q_rstd"], world["k_rstd"],
                                   f32(fw["g_c"]), world["be"], world["scale"], 2, 4)
     nw = unpack_chunk_tiles(nw, world["lay"], world["TT"])
+    A, Aqk = unpack_quarter_tiles(A, world["lay"], world["TT"]), unpack_quarter_tiles(Aqk, world["lay"], world["TT"])
     for n, t in dict(A=A, Aqk=Aqk, nw=nw, u=u).items():
         _err(n, t, fw[n])
     idx = torch.arange(64, device="cuda")
@@ -76,7 +77,8 @@ def test_recurrence_and_output(world):
                                  h0=lv["h0"])
     _err("h", unpack_state_tiles(h), fw["h"]); _err("Vd", unpack_chunk_tiles(Vd, lay, world["TT"]), fw["Vd"])
     _err("ht", ht, fw["ht"])
-    o, _ = ops.out_fwd(lay, lv["q"], world["q_rstd"], f32(fw["g_c"]), f32(fw["Aqk"]), pack_chunk_tiles(f32(fw["Vd"]), lay),
+    o, _ = ops.out_fwd(lay, lv["q"], world["q_rstd"], f32(fw["g_c"]), pack_quarter_tiles(f32(fw["Aqk"]), lay),
+                       pack_chunk_tiles(f32(fw["Vd"]), lay),
                        pack_state_tiles(f32(fw["h"])), world["scale"], 2, 4, torch.float32)
     _err("o", o, fw["o"])
 
@@ -96,14 +98,16 @@ def test_transition_matrix_reproduces_the_state_pass(world):
 def test_bwd_dh(world):
     lv, fw, bw, f32 = world["lv"], world["fw"], world["bw"], world["f32"]
     dh, dVd, dh0 = ops.bwd_dh(world["lay"], world["do"], lv["q"], lv["k"], world["q_rstd"], world["k_rstd"],
-                              f32(fw["g_c"]), f32(fw["Aqk"]), pack_chunk_tiles(f32(fw["nw"]), world["lay"]), world["scale"], 2, 4,
+                              f32(fw["g_c"]), pack_quarter_tiles(f32(fw["Aqk"]), world["lay"]),
+                              pack_chunk_tiles(f32(fw["nw"]), world["lay"]), world["scale"], 2, 4,
                               dht=world["dht"])
     _err("dh", unpack_state_tiles(dh), bw["dh"]); _err("dVd", dVd, bw["dVd"]); _err("dh0", dh0, bw["dh0"])
 
 
 def test_bwd_wy(world):
     lv, fw, bw, f32, lay = world["lv"], world["fw"], world["bw"], world["f32"], world["lay"]
-    Vd, dX, dbw, dAqk, dL = ops.bwd_wy(lay, lv["k"], lv["v"], world["k_rstd"], f32(fw["g_c"]), world["be"], f32(fw["A"]),
+    Vd, dX, dbw, dAqk, dL = ops.bwd_wy(lay, lv["k"], lv["v"], world["k_rstd"], f32(fw["g_c"]), world["be"],
+                                       pack_quarter_tiles(f32(fw["A"]), lay),
                                        pack_state_tiles(f32(fw["h"])), world["do"], f32(bw["dVd"]), 2, 4)
     for n, t in dict(Vd=Vd, dX=dX, dbeta_w=dbw, dAqk=dAqk, dL=dL).items():
         _err(n, t, bw[n])
