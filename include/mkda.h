@@ -104,6 +104,9 @@ typedef struct {
     float* Aqk;    /* [NC,HV] quarter tiles: scale * lower(Q K^T with decay) */
     float* nw;     /* [NC,HV] chunk tiles: nw^T [K index][token], nw = -A (beta k 2^g) */
     float* u;      /* [TT,HV,128]  A (beta v) */
+    float* kbar;   /* [NC,HV] row tiles: k 2^(gL - g) with gL the cumsum at the chunk's last token */
+    float* qs;     /* [NC,HV] row tiles: scale q 2^g */
+    float* gl;     /* [NC,HV,128] 2^gL, the decay of the state over the whole chunk */
 } MkdaIntraFwd;
 int mkda_intra_fwd(const MkdaIntraFwd* p, void* stream);
 
@@ -118,7 +121,9 @@ int mkda_intra_fwd(const MkdaIntraFwd* p, void* stream);
 /* Chunk tile: the same idea for a [128][64 tokens] operand, MKDA_CHUNK_TILE_BYTES per (chunk, v-head): bf16 hi (16 KB)
  * then lo (16 KB), 128 rows x 128 bytes each, same swizzle.  Used for Vd^T [v][token] between mkda_recur_fwd and mkda_out_fwd
  * (token columns past the end of the chunk are zero), and for nw^T [K index][token]
- * between mkda_intra_fwd and the serial kernels. */
+ * between mkda_intra_fwd and the serial kernels.
+ * Row tile: the same 32 KB for a [64 tokens][128] operand (rows = tokens; hi 16 KB then lo 16 KB, each two column blocks of
+ * 64 rows x 128 bytes): the scaled operands kbar and qs, token rows past the end of the chunk are zero. */
 #define MKDA_CHUNK_TILE_BYTES 32768
 /* Quarter tile: a [64][64] operand, MKDA_QUARTER_TILE_BYTES per (chunk, v-head): bf16 hi (8 KB) then lo (8 KB), 64 rows x
  * 128 bytes, same swizzle.  Used for the intra-chunk matrices A and Aqk, [row i][column j]; rows past the end of the chunk
@@ -134,8 +139,8 @@ typedef struct {
     MkdaLayout L;
     const float* nw;           /* [NC,HV] chunk tiles as written by mkda_intra_fwd */
     const float* u;            /* [TT,HV,128] */
-    const void* k; int k_dtype; const float* k_rstd;
-    const float* g_c;
+    const float* kbar;         /* [NC,HV] row tiles as written by mkda_intra_fwd */
+    const float* gl;           /* [NC,HV,128] as written by mkda_intra_fwd */
     const float* h0;           /* [*,HV,128,128] or NULL */
     const int* seg_h0;         /* [NS] row of h0 for each segment, -1 = start from zero; NULL = identity map */
     int state_v_first;         /* layout of h0 / ht */
@@ -147,17 +152,15 @@ typedef struct {
 } MkdaRecurFwd;
 int mkda_recur_fwd(const MkdaRecurFwd* p, void* stream);
 
-/* Chunk-parallel output  o = scale (q 2^g) h + Aqk Vd  with the optional gated RMSNorm epilogue fused.
+/* Chunk-parallel output  o = qs h + Aqk Vd  (qs = scale q 2^g) with the optional gated RMSNorm epilogue fused.
  * Replaces the output part of fused_fwd_kda and rmsnorm_gated_fwd
  * (mogan_kda/ops/kimi_delta_rule/epilogue.py:183-190). */
 typedef struct {
     MkdaLayout L;
-    const void* q; int q_dtype; const float* q_rstd;
-    const float* g_c;
+    const float* qs;           /* [NC,HV] row tiles (scale q 2^g) as written by mkda_intra_fwd */
     const float* Aqk;          /* [NC,HV] quarter tiles as written by mkda_intra_fwd */
     const float* Vd;           /* [NC,HV] chunk tiles as written by mkda_recur_fwd */
     const float* h;            /* [NC,HV] state tiles */
-    float scale;
     int has_norm; const void* norm_w; int norm_w_dtype;   /* [128] or NULL (=1) */
     const void* gate; int gate_dtype;                     /* [TT,HV,128] */
     int act; float eps;
@@ -219,11 +222,11 @@ int mkda_epilogue_bwd_noalloc(const MkdaEpilogueBwdNoAlloc* p, void* stream);
 typedef struct {
     MkdaLayout L;
     const void* d_o; int do_dtype;                 /* [TT,HV,128] */
-    const void* q; const void* k; int qk_dtype; const float* q_rstd; const float* k_rstd;
-    const float* g_c;
+    const float* kbar;         /* [NC,HV] row tiles as written by mkda_intra_fwd */
+    const float* qs;           /* [NC,HV] row tiles as written by mkda_intra_fwd */
+    const float* gl;           /* [NC,HV,128] as written by mkda_intra_fwd */
     const float* Aqk;          /* [NC,HV] quarter tiles as written by mkda_intra_fwd */
     const float* nw;           /* [NC,HV] chunk tiles as written by mkda_intra_fwd */
-    float scale;
     const float* dht;          /* [*,HV,128,128] or NULL */
     const int* seg_dht;        /* [NS] row of dht per segment, -1 = zero; NULL = identity map */
     int state_v_first;         /* layout of dht / dh0 */

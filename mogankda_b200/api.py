@@ -39,13 +39,13 @@ class _DeltaRuleFunction(torch.autograd.Function):
         g_c, beta_e = ops.gate_cumsum_fwd(lay, x, cfg["gate_mode"], A_log, dt_bias, cfg["lower_bound"], HV,
                                           beta_raw=beta, beta_sigmoid=cfg["beta_mode"] == "sigmoid",
                                           beta_scale=cfg["beta_scale"])
-        A, Aqk, nw, u = ops.intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV)
+        A, Aqk, nw, u, kbar, qs, gl = ops.intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV)
         vf = cfg["state_v_first"]
         need_ht = cfg["output_final_state"]
         ms = None
         if lay.segmented or cp is not None:
             # pre-pass from zero: per-segment (state, transition); then the true entering state of every segment
-            _, _, hs, ms = ops.recur_fwd(lay, nw, u, k, k_rstd, g_c, HK, HV, store_h=False, store_vd=False,
+            _, _, hs, ms = ops.recur_fwd(lay, nw, u, kbar, gl, HK, HV, store_h=False, store_vd=False,
                                          want_transition=True)
             carry = None
             if initial_state is not None:
@@ -53,7 +53,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
             if cp is not None:
                 carry = cp.forward_carry(hs, ms, carry, lay, HV)
             s_in, _ = ops.state_combine(lay.grp_seg_off, lay.NG, lay.NS, HV, hs, ms, carry=carry, want_out=False)
-            h, Vd, ht_seg, _ = ops.recur_fwd(lay, nw, u, k, k_rstd, g_c, HK, HV, h0=s_in, state_v_first=False,
+            h, Vd, ht_seg, _ = ops.recur_fwd(lay, nw, u, kbar, gl, HK, HV, h0=s_in, state_v_first=False,
                                              want_ht=need_ht)
             ht = None
             if need_ht:
@@ -61,18 +61,18 @@ class _DeltaRuleFunction(torch.autograd.Function):
                 if vf:
                     ht = ht.transpose(-1, -2).contiguous()
         else:
-            h, Vd, ht, _ = ops.recur_fwd(lay, nw, u, k, k_rstd, g_c, HK, HV, h0=initial_state, state_v_first=vf,
+            h, Vd, ht, _ = ops.recur_fwd(lay, nw, u, kbar, gl, HK, HV, h0=initial_state, state_v_first=vf,
                                          want_ht=need_ht)
         norm = None
         if cfg["has_ep"]:
             norm = dict(weight=ep_w, gate=ep_gate, act=cfg["ep_act"], eps=cfg["ep_eps"])
         need_bwd = any(ctx.needs_input_grad[:10])
         out_dtype = torch.float32 if cfg["has_ep"] else q.dtype
-        out, o_raw = ops.out_fwd(lay, q, q_rstd, g_c, Aqk, Vd, h, scale, HK, HV, out_dtype, norm=norm,
+        out, o_raw = ops.out_fwd(lay, qs, Aqk, Vd, h, HK, HV, out_dtype, norm=norm,
                                  keep_raw=cfg["has_ep"] and need_bwd)
         if need_bwd:
             ctx.save_for_backward(q, k, v, x, beta, A_log, dt_bias, initial_state, ep_w, ep_gate, q_rstd, k_rstd,
-                                  g_c, beta_e, A, Aqk, nw, h, o_raw, ms)
+                                  g_c, beta_e, A, Aqk, nw, h, o_raw, ms, kbar, qs, gl)
         ctx.cfg, ctx.lay, ctx.dims = cfg, lay, (B, T, HK, HV)
         ctx.set_materialize_grads(False)
         return out.view(B, T, HV, 128), ht
@@ -81,7 +81,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
     @torch.autograd.function.once_differentiable
     def backward(ctx, dy, dht):
         (q, k, v, x, beta, A_log, dt_bias, initial_state, ep_w, ep_gate, q_rstd, k_rstd, g_c, beta_e, A, Aqk, nw, h,
-         o_raw, ms) = ctx.saved_tensors
+         o_raw, ms, kbar, qs, gl) = ctx.saved_tensors
         cfg, lay = ctx.cfg, ctx.lay
         B, T, HK, HV = ctx.dims
         scale, vf, cp = cfg["scale"], cfg["state_v_first"], cfg["cp_context"]
@@ -99,7 +99,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
             dht = dht.float().contiguous()
         need_dh0 = initial_state is not None and ctx.needs_input_grad[7]
         if lay.segmented or cp is not None:
-            dh, dVd, dloc = ops.bwd_dh(lay, d_o, q, k, q_rstd, k_rstd, g_c, Aqk, nw, scale, HK, HV)
+            dh, dVd, dloc = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV)
             carry = None
             if dht is not None:
                 carry = dht.transpose(-1, -2).contiguous() if vf else dht
@@ -107,14 +107,14 @@ class _DeltaRuleFunction(torch.autograd.Function):
                 carry = cp.backward_carry(dloc, ms, carry, lay, HV)
             g_in, dh0 = ops.state_combine(lay.grp_seg_off, lay.NG, lay.NS, HV, dloc, ms, carry=carry, reverse=True,
                                           want_out=need_dh0 or cp is not None)
-            ops.bwd_dh(lay, d_o, q, k, q_rstd, k_rstd, g_c, Aqk, nw, scale, HK, HV, dht=g_in, want_dh0=False,
+            ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, dht=g_in, want_dh0=False,
                        dh=dh, dVd=dVd)
             if cp is not None:
                 dh0 = cp.finish_backward(dh0)
             if dh0 is not None and vf:
                 dh0 = dh0.transpose(-1, -2).contiguous()
         else:
-            dh, dVd, dh0 = ops.bwd_dh(lay, d_o, q, k, q_rstd, k_rstd, g_c, Aqk, nw, scale, HK, HV, dht=dht,
+            dh, dVd, dh0 = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, dht=dht,
                                       state_v_first=vf, want_dh0=need_dh0)
         Vd, dX, dbeta_w, dAqk, dL = ops.bwd_wy(lay, k, v, k_rstd, g_c, beta_e, A, h, d_o, dVd, HK, HV)
         dq_v, dk_v, dgp, dbeta, dv = ops.bwd_tail(lay, q, k, q_rstd, k_rstd, g_c, beta_e, d_o, dX, Vd, h, dh, dAqk, dL,

@@ -4,7 +4,7 @@
 using namespace mkda;
 
 extern "C" int mkda_intra_fwd(const MkdaIntraFwd* p, void* stream) {
-    if (!p || !p->q || !p->k || !p->v || !p->g_c || !p->beta || !p->A || !p->Aqk || !p->nw || !p->u)
+    if (!p || !p->q || !p->k || !p->v || !p->g_c || !p->beta || !p->A || !p->Aqk || !p->nw || !p->u || !p->kbar || !p->qs || !p->gl)
         return set_error(MKDA_ERR_ARG, "intra_fwd: null argument");
     if (p->L.HK <= 0 || p->L.HV % p->L.HK) return set_error(MKDA_ERR_ARG, "intra_fwd: HV must be a multiple of HK");
     if (p->L.NC == 0) return MKDA_OK;
@@ -12,21 +12,21 @@ extern "C" int mkda_intra_fwd(const MkdaIntraFwd* p, void* stream) {
 }
 
 extern "C" int mkda_recur_fwd(const MkdaRecurFwd* p, void* stream) {
-    if (!p || !p->nw || !p->u || !p->k || !p->g_c) return set_error(MKDA_ERR_ARG, "recur_fwd: null argument");
+    if (!p || !p->nw || !p->u || !p->kbar || !p->gl) return set_error(MKDA_ERR_ARG, "recur_fwd: null argument");
     if (p->want_transition && !p->mt) return set_error(MKDA_ERR_ARG, "recur_fwd: want_transition needs mt");
     if (p->L.NS == 0) return MKDA_OK;
     return launch_recur_fwd_tc(p, (cudaStream_t)stream);
 }
 
 extern "C" int mkda_out_fwd(const MkdaOutFwd* p, void* stream) {
-    if (!p || !p->q || !p->g_c || !p->Aqk || !p->Vd || !p->h || !p->out) return set_error(MKDA_ERR_ARG, "out_fwd: null argument");
+    if (!p || !p->qs || !p->Aqk || !p->Vd || !p->h || !p->out) return set_error(MKDA_ERR_ARG, "out_fwd: null argument");
     if (p->has_norm && !p->gate) return set_error(MKDA_ERR_ARG, "out_fwd: the gated norm needs a gate tensor");
     if (p->L.NC == 0) return MKDA_OK;
     return launch_out_fwd_tc(p, (cudaStream_t)stream);
 }
 
 extern "C" int mkda_bwd_dh(const MkdaBwdDh* p, void* stream) {
-    if (!p || !p->d_o || !p->q || !p->k || !p->g_c || !p->Aqk || !p->nw || !p->dh || !p->dVd)
+    if (!p || !p->d_o || !p->kbar || !p->qs || !p->gl || !p->Aqk || !p->nw || !p->dh || !p->dVd)
         return set_error(MKDA_ERR_ARG, "bwd_dh: null argument");
     if (p->L.NS == 0) return MKDA_OK;
     return launch_bwd_dh_tc(p, (cudaStream_t)stream);

@@ -106,61 +106,42 @@ __device__ __forceinline__ void tc_end(TcShared* sh, uint32_t tmem, uint32_t tme
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// output:  O^T[v x tok] = H^T (scale q 2^g)^T + Vd^T Aqk^T, then the row-wise epilogue (gated RMSNorm) from a shared
+// output:  O^T[v x tok] = H^T qs^T + Vd^T Aqk^T (qs = scale q 2^g), then the row-wise epilogue (gated RMSNorm) from a shared
 // [tok][v] staging tile so that all global stores are full 512-byte rows.
 // ---------------------------------------------------------------------------------------------------------
 constexpr int OUT_TC_SMEM = 2 * tile_bytes(128, 128) + 2 * tile_bytes(64, 128) + 2 * tile_bytes(128, 64) + 2 * tile_bytes(64, 64) + 1024;
 constexpr int OLD = 132;   // leading dimension of the fp32 [tok][v] staging tile
 
-template <int QDT, int GDT>
+template <int GDT>
 __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ TcShared sh;
     MKDA_TRACE_AT(2, 0);
     uint8_t* base = tc_begin(smem_raw, &sh, 64);
-    uint8_t* a1h = base;
+    uint8_t* a1h = base;                                    // S^T [v][K index]
     uint8_t* a1l = a1h + tile_bytes(128, 128);
-    uint8_t* b1h = a1l + tile_bytes(128, 128);
+    uint8_t* b1h = a1l + tile_bytes(128, 128);              // scale q 2^g [tok][K index]
     uint8_t* b1l = b1h + tile_bytes(64, 128);
-    uint8_t* a2h = b1l + tile_bytes(64, 128);
+    uint8_t* a2h = b1l + tile_bytes(64, 128);               // Vd^T [v][tok]
     uint8_t* a2l = a2h + tile_bytes(128, 64);
-    uint8_t* b2h = a2l + tile_bytes(128, 64);
+    uint8_t* b2h = a2l + tile_bytes(128, 64);               // Aqk [i][j]
     uint8_t* b2l = b2h + tile_bytes(64, 64);
     float* sO = reinterpret_cast<float*>(base);            // reused after the MMAs: [64][OLD]
 
-    const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV, HK = p.L.HK;
-    const int hk = h / (HV / HK);
+    const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV;
     const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     __shared__ uint64_t ldbar;
-    if (tid == 0) {   // S^T [v][K index], Vd^T [v][tok] and Aqk [i][j] arrive as ready-made operand tiles on one barrier
+    if (tid == 0) {   // all four operands arrive as ready-made tiles: no register staging, no conversion
         const size_t it = (size_t)c * HV + h;
         umma::mbar_init(&ldbar, 1);
         umma::fence_barrier_init();
-        umma::mbar_expect_tx(&ldbar, umma::STATE_TILE_BYTES + umma::CHUNK_TILE_BYTES + umma::QUARTER_TILE_BYTES);
+        umma::mbar_expect_tx(&ldbar, umma::STATE_TILE_BYTES + 2 * umma::CHUNK_TILE_BYTES + umma::QUARTER_TILE_BYTES);
         umma::bulk_load(b2h, reinterpret_cast<const uint8_t*>(p.Aqk) + it * umma::QUARTER_TILE_BYTES, umma::QUARTER_TILE_BYTES, &ldbar);
-        umma::bulk_load(a1h, reinterpret_cast<const uint8_t*>(p.h) + it * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &ldbar);
         umma::bulk_load(a2h, reinterpret_cast<const uint8_t*>(p.Vd) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &ldbar);
-    }
-    {   // the other tiles are staged untransposed through registers
-        float vQ[2][8], vG[2][8];
-        load_chunks<2, 512, true>(vQ, 64, 128, [&](int r, int k8, float (&v)[8]) {
-            const int rr = r < len ? r : len - 1;
-            load8(p.q, QDT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, v);
-        });
-        load_chunks<2, 512, true>(vG, 64, 128, [&](int r, int k8, float (&v)[8]) {
-            const int rr = r < len ? r : len - 1;
-            load8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, v);
-        });
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            const int r = (tid + n * 512) >> 4, rr = r < len ? r : len - 1;
-            const float m = r < len ? p.scale * (p.q_rstd ? p.q_rstd[(size_t)(start + rr) * HK + hk] : 1.f) : 0.f;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) vQ[n][e] *= m * ex2f_(vG[n][e]);
-        }
-        store_chunks<2, 512, true>(b1h, b1l, vQ, 64, 128);
+        umma::bulk_load(b1h, reinterpret_cast<const uint8_t*>(p.qs) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &ldbar);
+        umma::bulk_load(a1h, reinterpret_cast<const uint8_t*>(p.h) + it * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &ldbar);
     }
     MKDA_TRACE_AT(2, 1);
     const uint32_t tmem = tc_operands_ready(&sh);
@@ -226,9 +207,9 @@ int tc_chunk_status(unsigned int* out) {
     return cudaMemcpyFromSymbol(out, umma::g_timeout_flag, sizeof(unsigned int)) == cudaSuccess ? 0 : -1;
 }
 
-template <int QDT, int GDT>
+template <int GDT>
 static int launch_out_fwd_tc_t(const MkdaOutFwd* p, cudaStream_t stream) {
-    auto kern = out_fwd_tc_kernel<QDT, GDT>;
+    auto kern = out_fwd_tc_kernel<GDT>;
     if (int e = ensure_smem((const void*)kern, OUT_TC_SMEM, "out_fwd")) return e;
     kern<<<dim3(p->L.NC, p->L.HV), 512, OUT_TC_SMEM, stream>>>(*p);
     return check_launch("out_fwd");
@@ -242,7 +223,12 @@ static int launch_out_fwd_tc_t(const MkdaOutFwd* p, cudaStream_t stream) {
         default: return set_error(MKDA_ERR_ARG, "unsupported dtype");                                        \
     }
 int launch_out_fwd_tc(const MkdaOutFwd* p, cudaStream_t stream) {
-    MKDA_DISPATCH2(launch_out_fwd_tc_t, p->q_dtype, p->has_norm ? p->gate_dtype : 0, p, stream)
+    switch (p->has_norm ? p->gate_dtype : 0) {
+        case MKDA_F32: return launch_out_fwd_tc_t<MKDA_F32>(p, stream);
+        case MKDA_BF16: return launch_out_fwd_tc_t<MKDA_BF16>(p, stream);
+        case MKDA_F16: return launch_out_fwd_tc_t<MKDA_F16>(p, stream);
+    }
+    return set_error(MKDA_ERR_ARG, "out_fwd: unsupported dtype");
 }
 
 }  // namespace mkda

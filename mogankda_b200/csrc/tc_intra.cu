@@ -51,7 +51,8 @@ __host__ __device__ constexpr int kc_off(int I) { return I == 0 ? 0 : I == 1 ? 8
 __host__ __device__ constexpr int kc_bytes(int I) { return 16 * (I + 1) * 128 * 2; }          // one of hi / lo
 constexpr int KQ_OFF = 81920;                              // [128][128] hi 32 KB, lo 32 KB
 constexpr int OPND_BYTES = KQ_OFF + 65536;                 // 144 KB
-constexpr int INTRA_TC_SMEM = OPND_BYTES + 3 * CH * MLD * 4 + 1024;
+constexpr int INTRA_TC_SMEM = OPND_BYTES + 65536 + 1024;      // operands + (two 32 KB hand-over tiles, later sM / sInv / sP)
+static_assert(3 * CH * MLD * 4 <= 65536, "sM / sInv / sP must fit under the hand-over tiles");
 
 // Inverse of the unit lower-triangular 64 x 64 matrix sM into sInv (fp32, fixed summation order) by recursive halving:
 // the four 16 x 16 diagonal blocks by forward substitution, then the off-diagonal block of each 32 x 32 half and finally
@@ -116,7 +117,7 @@ template <int DT>
 __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ IntraShared sh;
-    __shared__ __align__(16) float sGa[4][DK];         // cumsum rows of the four block anchors
+    __shared__ __align__(16) float sGa[5][DK];         // cumsum rows of the four block anchors, [4] = last valid row
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sKQ = base + KQ_OFF;
     float* sM = reinterpret_cast<float*>(base + OPND_BYTES);
@@ -126,6 +127,8 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     uint8_t* sBv = base + 32768;                       // beta v [j][v]
     uint8_t* sTA = base + 65536;                       // A [i][j], hi 8 KB + lo 8 KB
     uint8_t* sTQ = base + 81920;                       // Aqk [i][j], hi 8 KB + lo 8 KB (only copied out)
+    uint8_t* sKB = base + OPND_BYTES;                  // kbar [tok][K index] hi + lo (32 KB), only copied out; under sM ...
+    uint8_t* sQS = sKB + 32768;                        // scale q 2^g [tok][K index] hi + lo (32 KB), likewise
 
     const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV, HK = p.L.HK;
     const int hk = h / (HV / HK);
@@ -157,6 +160,10 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
             *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8]) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
             *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8 + 4]) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
         }
+        if (r == len - 1) {
+            *reinterpret_cast<float4*>(&sGa[4][k8 * 8]) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
+            *reinterpret_cast<float4*>(&sGa[4][k8 * 8 + 4]) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) { vk[n][e] *= rk[n]; vq[n][e] *= rq[n]; }
     }
@@ -187,8 +194,35 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
             store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
         }
     }
+    // The state kernels' scaled operands, as ready-made tiles: kbar = k 2^(gL - g) (gL = last valid row) and scale q 2^g,
+    // plus gl = 2^gL.  Rows past the end are zero (their k / q were zeroed above).
+    {
+        float gLv[8];
+        lds8(&sGa[4][(tid & 15) * 8], gLv);
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
+            float t8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(gLv[e] - vg[n][e]);
+            store_split8(sKB, sKB + 16384, 64, r, k8, t8);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) t8[e] = p.scale * vq[n][e] * ex2f_(vg[n][e]);
+            store_split8(sQS, sQS + 16384, 64, r, k8, t8);
+        }
+        if (tid < 16) {
+            float* dst = p.gl + ((size_t)c * HV + h) * 128 + tid * 8;
+            *reinterpret_cast<float4*>(dst) = make_float4(ex2f_(gLv[0]), ex2f_(gLv[1]), ex2f_(gLv[2]), ex2f_(gLv[3]));
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(ex2f_(gLv[4]), ex2f_(gLv[5]), ex2f_(gLv[6]), ex2f_(gLv[7]));
+        }
+    }
     MKDA_TRACE_AT(3, 3);
     publish();
+    if (tid == 0) {
+        const size_t it = (size_t)c * HV + h;
+        umma::bulk_store(reinterpret_cast<uint8_t*>(p.kbar) + it * umma::CHUNK_TILE_BYTES, sKB, umma::CHUNK_TILE_BYTES);
+        umma::bulk_store(reinterpret_cast<uint8_t*>(p.qs) + it * umma::CHUNK_TILE_BYTES, sQS, umma::CHUNK_TILE_BYTES);
+    }
     if (umma::mma_issuer()) {
 #pragma unroll
         for (int I = 0; I < 4; ++I)
@@ -220,6 +254,8 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         for (int e = 0; e < 8; ++e) t8[e] = b * vv[n][e];
         store_split8(sBv, sBv + 16384, 64, r, k8, t8);
     }
+    if (tid == 0) umma::bulk_store_wait_read();    // the two tiles under sM / sInv / sP have left shared memory
+    __syncthreads();
     for (int i = tid; i < CH * MLD; i += 512) sInv[i] = 0.f;
     if (q < 2) {                              // lane = column j, cg = row block I: Gamma / Q K^T entries (16 I + r, j)
         float v[32];

@@ -35,7 +35,6 @@ __device__ __forceinline__ void publish_operands() {
 
 constexpr int RECUR_TC_SMEM = 64 * 1024 + 4 * 32 * 1024 + 1024;
 
-template <int KDT>
 __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ RecurShared sh;
@@ -43,11 +42,10 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
     uint8_t* sAh = base;                         // St as A(m = v, k = K index) [128][128]
     uint8_t* sAl = sAh + 32768;
     uint8_t* sW[2] = {sAl + 32768, sAl + 32768 + 65536};            // nw^T chunk tile [K index][tok] (hi, lo 16 KB each); later Vd^T [v][tok]
-    uint8_t* sK[2] = {sW[0] + 32768, sW[1] + 32768};                 // kbar [tok][K index]
+    uint8_t* sK[2] = {sW[0] + 32768, sW[1] + 32768};                 // kbar row tile [tok][K index], fetched by bulk copy
 
     const bool trans = blockIdx.x == 1;
     const int h = blockIdx.y, seg = blockIdx.z, HV = p.L.HV, HK = p.L.HK;
-    const int hk = h / (HV / HK);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
     const bool vf = p.state_v_first != 0;
@@ -77,46 +75,19 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
     }
 
     const int c_beg = p.L.seg_chunk_off[seg], c_end = p.L.seg_chunk_off[seg + 1];
-    // staging of one chunk's global operands: thread owns chunks i = tid, tid + 512 -> (token r = i / 16, k8 = i % 16)
-    // nw arrives as the ready-made chunk tile written by the intra-chunk kernel: one bulk copy per chunk
-    auto fetch_w = [&](int c, int buf) {
-        umma::mbar_expect_tx(&sh.ldw[buf], umma::CHUNK_TILE_BYTES);
-        umma::bulk_load(sW[buf], reinterpret_cast<const uint8_t*>(p.nw) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[buf]);
-    };
-    auto load_k = [&](int c, float (&k)[2][8], float (&g)[2][8], float (&gL)[2][8], float (&rs)[2]) {
-        const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-            const size_t tk = (size_t)(start + rr) * HK + hk;
-            ld8(p.k, KDT, tk * 128 + k8 * 8, k[n]);
-            ld8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, g[n]);
-            ld8(p.g_c, MKDA_F32, ((size_t)(start + len - 1) * HV + h) * 128 + k8 * 8, gL[n]);
-            rs[n] = p.k_rstd ? p.k_rstd[tk] : 1.f;
+    // nw^T and kbar arrive as the ready-made tiles written by the intra-chunk kernel: two bulk copies per chunk on one
+    // barrier (thread 0); the 128 decay factors of the chunk are copied by the first four warps
+    auto fetch = [&](int c, int buf) {
+        const size_t it = (size_t)c * HV + h;
+        if (tid == 0) {
+            umma::mbar_expect_tx(&sh.ldw[buf], 2 * umma::CHUNK_TILE_BYTES);
+            umma::bulk_load(sW[buf], reinterpret_cast<const uint8_t*>(p.nw) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[buf]);
+            umma::bulk_load(sK[buf], reinterpret_cast<const uint8_t*>(p.kbar) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[buf]);
         }
-    };
-    auto store_k = [&](int c, int buf, float (&k)[2][8], float (&g)[2][8], float (&gL)[2][8], float (&rs)[2]) {
-        const int len = p.L.chunk_len[c];
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
-            const float m = r < len ? rs[n] : 0.f;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) k[n][e] *= m * ex2f_(gL[n][e] - g[n][e]);
-            store_split8(sK[buf], sK[buf] + 16384, 64, r, k8, k[n]);
-            if (r == 0) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) sh.gl[buf][k8 * 8 + e] = ex2f_(gL[n][e]);
-            }
-        }
+        if (tid < DK) sh.gl[buf][tid] = p.gl[it * 128 + tid];
     };
 
-    if (c_beg < c_end) {
-        float k[2][8], g[2][8], gL[2][8], rs[2];
-        if (tid == 0) fetch_w(c_beg, 0);
-        load_k(c_beg, k, g, gL, rs);
-        store_k(c_beg, 0, k, g, gL, rs);
-    }
+    if (c_beg < c_end) fetch(c_beg, 0);
     for (int c = c_beg; c < c_end; ++c) {
         const int buf = (c - c_beg) & 1, start = p.L.chunk_start[c], len = p.L.chunk_len[c];
         const bool more = c + 1 < c_end;
@@ -127,11 +98,9 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
             uu[j] = trans ? 0.f : p.u[((size_t)(start + tt) * HV + h) * 128 + row];
             if (t >= len) uu[j] = 0.f;
         }
-        if (tid == 0) {
-            umma::bulk_store_wait_read();                   // the previous chunk's saved tiles have left shared memory
-            if (more) fetch_w(c + 1, buf ^ 1);              // ... so the other nw / Vd^T buffer can take the next nw tile
-        }
-        __syncthreads();                                   // sh.gl[buf] and the kbar tile of `buf` are complete
+        if (tid == 0) umma::bulk_store_wait_read();         // the previous chunk's saved tiles have left shared memory
+        if (more) fetch(c + 1, buf ^ 1);                    // ... so the other buffers (last read by chunk c - 1) take the next tiles
+        __syncthreads();                                   // sh.gl[buf] is complete
         {   // state entering the chunk: operand tile (optionally saved as it is by the issuing thread below), decay
             float s[32];
             umma::tmem_ld32(umma::tmem_addr(tmem, warp, cg * 32), s);
@@ -149,12 +118,10 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
         }
         publish_operands();
         if (umma::mma_issuer()) {
-            umma::mbar_wait(&sh.ldw[buf], ((c - c_beg) >> 1) & 1);            // this chunk's nw tile has landed
+            umma::mbar_wait(&sh.ldw[buf], ((c - c_beg) >> 1) & 1);            // this chunk's nw and kbar tiles have landed
             umma::gemm(tmem + 128, umma::opnd_k(sAh, sAl, 128), umma::opnd_mn(sW[buf], sW[buf] + 16384, 128), 128, 64, 128, 0u);
             umma::commit(&sh.bar);
         }
-        float k[2][8], g[2][8], gL[2][8], rs[2];
-        if (more) load_k(c + 1, k, g, gL, rs);
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;
         umma::fence_after_sync();
         // The operand tile doubles as the saved state of this chunk: one asynchronous 64 KB copy, issued and later awaited
@@ -181,7 +148,6 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
             umma::gemm(tmem, umma::opnd_k(sW[buf], sW[buf] + 16384, 128), umma::opnd_mn(sK[buf], sK[buf] + 16384, 64), 128, 128, 64, 1u);
             umma::commit(&sh.bar);
         }
-        if (more) store_k(c + 1, buf ^ 1, k, g, gL, rs);
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;
         umma::fence_after_sync();
     }
@@ -211,20 +177,11 @@ int tc_recur_status(unsigned int* out) {
     return cudaMemcpyFromSymbol(out, umma::g_timeout_flag, sizeof(unsigned int)) == cudaSuccess ? 0 : -1;
 }
 
-template <int KDT>
-static int launch_recur_fwd_tc_t(const MkdaRecurFwd* p, cudaStream_t stream) {
-    auto kern = recur_fwd_tc_kernel<KDT>;
+int launch_recur_fwd_tc(const MkdaRecurFwd* p, cudaStream_t stream) {
+    auto kern = recur_fwd_tc_kernel;
     if (int e = ensure_smem((const void*)kern, RECUR_TC_SMEM, "recur_fwd")) return e;
     kern<<<dim3(p->want_transition ? 2 : 1, p->L.HV, p->L.NS), 512, RECUR_TC_SMEM, stream>>>(*p);
     return check_launch("recur_fwd");
-}
-int launch_recur_fwd_tc(const MkdaRecurFwd* p, cudaStream_t stream) {
-    switch (p->k_dtype) {
-        case MKDA_F32: return launch_recur_fwd_tc_t<MKDA_F32>(p, stream);
-        case MKDA_BF16: return launch_recur_fwd_tc_t<MKDA_BF16>(p, stream);
-        case MKDA_F16: return launch_recur_fwd_tc_t<MKDA_F16>(p, stream);
-    }
-    return set_error(MKDA_ERR_ARG, "recur_fwd: unsupported dtype");
 }
 
 }  // namespace mkda
@@ -240,7 +197,7 @@ namespace mkda {
 // ---------------------------------------------------------------------------------------------------------
 constexpr int DH_TC_SMEM = 64 * 1024 + 32 * 1024 + 16 * 1024 + 3 * 32 * 1024 + 1024;
 
-template <int QKDT, int DODT>
+template <int DODT>
 __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ RecurShared sh;
@@ -249,12 +206,11 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
     uint8_t* sAl = sAh + 32768;
     uint8_t* sDo = sAl + 32768;                  // dO [i][v]          hi 16 KB, lo 16 KB
     uint8_t* sAq = sDo + 32768;                  // Aqk [i][j] quarter tile (hi 8 KB, lo 8 KB), fetched by bulk copy
-    uint8_t* sKb = sAq + 16384;                  // kbar [j][K index]; later dVd^T [v][j]
-    uint8_t* sQs = sKb + 32768;                  // scale q 2^g [i][K index]
+    uint8_t* sKb = sAq + 16384;                  // kbar row tile [j][K index] (bulk copy); later dVd^T [v][j]
+    uint8_t* sQs = sKb + 32768;                  // scale q 2^g row tile [i][K index] (bulk copy)
     uint8_t* sNw = sQs + 32768;                  // nw^T chunk tile [K index][j], fetched by bulk copy
 
     const int h = blockIdx.y, seg = blockIdx.z, HV = p.L.HV, HK = p.L.HK;
-    const int hk = h / (HV / HK);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
     const bool vf = p.state_v_first != 0;
@@ -282,49 +238,33 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
     const int c_beg = p.L.seg_chunk_off[seg], c_end = p.L.seg_chunk_off[seg + 1];
     for (int c = c_end - 1; c >= c_beg; --c) {
         const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
-        {   // all global operands of the chunk are requested together: dO, Aqk, nw (plain copies), then k, q, g for
-            // kbar = k 2^(gL - g) and q~ = scale q 2^g
-            float vo[2][8], vk[2][8], vq[2][8], vg[2][8], vl[8], rk[2], rq[2];
-            if (tid == 0) {                                 // the last readers of both tiles, the previous chunk's products, are done
-                const size_t it = (size_t)c * HV + h;
-                umma::mbar_expect_tx(&sh.ldw[1], umma::QUARTER_TILE_BYTES);           // Aqk: needed by the first product
+        {   // Five of the six operands arrive as ready-made tiles (their last readers, the previous chunk's products, are
+            // done): Aqk and kbar for the first product on one barrier, scale q 2^g and nw^T for the second on the other.
+            // Only dO goes through registers.
+            const size_t it = (size_t)c * HV + h;
+            if (tid == 0) {
+                umma::mbar_expect_tx(&sh.ldw[1], umma::QUARTER_TILE_BYTES + umma::CHUNK_TILE_BYTES);
                 umma::bulk_load(sAq, reinterpret_cast<const uint8_t*>(p.Aqk) + it * umma::QUARTER_TILE_BYTES, umma::QUARTER_TILE_BYTES, &sh.ldw[1]);
-                umma::mbar_expect_tx(&sh.ldw[0], umma::CHUNK_TILE_BYTES);             // nw: needed by the second one
+                umma::bulk_load(sKb, reinterpret_cast<const uint8_t*>(p.kbar) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[1]);
+                umma::mbar_expect_tx(&sh.ldw[0], 2 * umma::CHUNK_TILE_BYTES);
+                umma::bulk_load(sQs, reinterpret_cast<const uint8_t*>(p.qs) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[0]);
                 umma::bulk_load(sNw, reinterpret_cast<const uint8_t*>(p.nw) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[0]);
             }
+            if (tid < DK) sh.gl[0][tid] = p.gl[it * 128 + tid];
+            float vo[2][8];
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
                 const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-                const size_t off = ((size_t)(start + rr) * HV + h) * 128 + k8 * 8;
-                const size_t tk = (size_t)(start + rr) * HK + hk;
-                ld8(p.d_o, DODT, off, vo[n]);
-                ld8(p.k, QKDT, tk * 128 + k8 * 8, vk[n]);
-                ld8(p.q, QKDT, tk * 128 + k8 * 8, vq[n]);
-                ld8(p.g_c, MKDA_F32, off, vg[n]);
-                rk[n] = p.k_rstd ? p.k_rstd[tk] : 1.f;
-                rq[n] = p.scale * (p.q_rstd ? p.q_rstd[tk] : 1.f);
+                ld8(p.d_o, DODT, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vo[n]);
             }
-            ld8(p.g_c, MKDA_F32, ((size_t)(start + len - 1) * HV + h) * 128 + (tid & 15) * 8, vl);
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
                 const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
-                const float mk = r < len ? rk[n] : 0.f, mq = r < len ? rq[n] : 0.f;
                 if (r >= len) {
 #pragma unroll
                     for (int e = 0; e < 8; ++e) vo[n][e] = 0.f;
                 }
                 store_split8(sDo, sDo + 16384, 64, r, k8, vo[n]);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    vk[n][e] *= mk * ex2f_(vl[e] - vg[n][e]);
-                    vq[n][e] *= mq * ex2f_(vg[n][e]);
-                }
-                store_split8(sKb, sKb + 16384, 64, r, k8, vk[n]);
-                store_split8(sQs, sQs + 16384, 64, r, k8, vq[n]);
-                if (r == 0) {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) sh.gl[0][k8 * 8 + e] = ex2f_(vl[e]);
-                }
             }
         }
         if (tid == 0) umma::bulk_store_wait_read();         // the previous chunk's saved tile has left shared memory
@@ -349,7 +289,7 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
         // before the tile is rebuilt in the next iteration (measured: starting it here is faster than after the products)
         if (tid == 0) umma::bulk_store(reinterpret_cast<uint8_t*>(p.dh) + ((size_t)c * HV + h) * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
         if (umma::mma_issuer()) {
-            umma::mbar_wait(&sh.ldw[1], ((c_end - 1 - c) & 1));               // this chunk's Aqk tile has landed
+            umma::mbar_wait(&sh.ldw[1], ((c_end - 1 - c) & 1));               // this chunk's Aqk and kbar tiles have landed
             umma::gemm(tmem + 128, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sAq, sAq + 8192, 64), 128, 64, 64, 0u);
             umma::gemm(tmem + 128, umma::opnd_k(sAh, sAl, 128), umma::opnd_k(sKb, sKb + 16384, 64), 128, 64, 128, 1u);
             umma::commit(&sh.bar);
@@ -371,7 +311,7 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
         publish_operands();
         if (umma::mma_issuer()) {
             umma::gemm(tmem, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sQs, sQs + 16384, 64), 128, 128, 64, 1u);
-            umma::mbar_wait(&sh.ldw[0], ((c_end - 1 - c) & 1));               // this chunk's nw tile has landed
+            umma::mbar_wait(&sh.ldw[0], ((c_end - 1 - c) & 1));               // this chunk's q and nw tiles have landed
             umma::gemm(tmem, umma::opnd_k(sKb, sKb + 16384, 128), umma::opnd_k(sNw, sNw + 16384, 128), 128, 128, 64, 1u);
             umma::commit(&sh.bar);
         }
@@ -394,20 +334,18 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
     if (warp == 0) umma::tmem_dealloc(tmem, 256);
 }
 
-template <int QKDT, int DODT>
+template <int DODT>
 static int launch_bwd_dh_tc_t(const MkdaBwdDh* p, cudaStream_t stream) {
-    auto kern = bwd_dh_tc_kernel<QKDT, DODT>;
+    auto kern = bwd_dh_tc_kernel<DODT>;
     if (int e = ensure_smem((const void*)kern, DH_TC_SMEM, "bwd_dh")) return e;
     kern<<<dim3(1, p->L.HV, p->L.NS), 512, DH_TC_SMEM, stream>>>(*p);
     return check_launch("bwd_dh");
 }
 int launch_bwd_dh_tc(const MkdaBwdDh* p, cudaStream_t stream) {
-    switch (p->qk_dtype * 3 + p->do_dtype) {
-        case 0: return launch_bwd_dh_tc_t<0, 0>(p, stream); case 1: return launch_bwd_dh_tc_t<0, 1>(p, stream);
-        case 2: return launch_bwd_dh_tc_t<0, 2>(p, stream); case 3: return launch_bwd_dh_tc_t<1, 0>(p, stream);
-        case 4: return launch_bwd_dh_tc_t<1, 1>(p, stream); case 5: return launch_bwd_dh_tc_t<1, 2>(p, stream);
-        case 6: return launch_bwd_dh_tc_t<2, 0>(p, stream); case 7: return launch_bwd_dh_tc_t<2, 1>(p, stream);
-        case 8: return launch_bwd_dh_tc_t<2, 2>(p, stream);
+    switch (p->do_dtype) {
+        case MKDA_F32: return launch_bwd_dh_tc_t<MKDA_F32>(p, stream);
+        case MKDA_BF16: return launch_bwd_dh_tc_t<MKDA_BF16>(p, stream);
+        case MKDA_F16: return launch_bwd_dh_tc_t<MKDA_F16>(p, stream);
     }
     return set_error(MKDA_ERR_ARG, "bwd_dh: unsupported dtype");
 }

@@ -135,18 +135,21 @@ def intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV):
     u = z(128)
     A = torch.empty(lay.NC, HV, 32, 128, dtype=torch.float32, device=q.device)       # quarter tiles per (chunk, head)
     Aqk = torch.empty(lay.NC, HV, 32, 128, dtype=torch.float32, device=q.device)
-    nw = torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=q.device)      # chunk tiles: nw^T per (chunk, head)
+    tile = lambda: torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=dev)      # noqa: E731  (32 KB per chunk, head)
+    nw, kbar, qs = tile(), tile(), tile()          # nw^T chunk tiles; kbar and scale q 2^g row tiles
+    gl = torch.empty(lay.NC, HV, 128, dtype=torch.float32, device=dev)
     p = STRUCTS["MkdaIntraFwd"]()
     p.L = _layout_struct(lay, HK, HV)
     p.q, p.k, p.v, p.qkv_dtype = _ptr(q), _ptr(k), _ptr(v), _dt(q)
     p.q_rstd, p.k_rstd = _ptr(q_rstd), _ptr(k_rstd)
     p.g_c, p.beta, p.scale = _ptr(g_c, torch.float32), _ptr(beta_e, torch.float32), scale
     p.A, p.Aqk, p.nw, p.u = _ptr(A), _ptr(Aqk), _ptr(nw), _ptr(u)
+    p.kbar, p.qs, p.gl = _ptr(kbar), _ptr(qs), _ptr(gl)
     _lib.call("mkda_intra_fwd", p, _stream())
-    return A, Aqk, nw, u
+    return A, Aqk, nw, u, kbar, qs, gl
 
 
-def recur_fwd(lay, nw, u, k, k_rstd, g_c, HK, HV, *, h0=None, seg_h0=None, state_v_first=False, store_h=True,
+def recur_fwd(lay, nw, u, kbar, gl, HK, HV, *, h0=None, seg_h0=None, state_v_first=False, store_h=True,
               store_vd=True, want_ht=True, want_transition=False, segments=True):
     """Runs the serial state pass over the layout's segments (or whole sequences with ``segments=False``).
     Returns (h [NC,HV] state tiles or None, Vd [NC,HV] chunk tiles or None, ht [NS,HV,128,128] or None, mt or None)."""
@@ -154,8 +157,7 @@ def recur_fwd(lay, nw, u, k, k_rstd, g_c, HK, HV, *, h0=None, seg_h0=None, state
     NS = lay.NS if segments else lay.N
     p = STRUCTS["MkdaRecurFwd"]()
     p.L = _layout_struct(lay, HK, HV, segments)
-    p.nw, p.u, p.k, p.k_dtype, p.k_rstd = _ptr(nw), _ptr(u), _ptr(k), _dt(k), _ptr(k_rstd)
-    p.g_c = _ptr(g_c)
+    p.nw, p.u, p.kbar, p.gl = _ptr(nw), _ptr(u), _ptr(kbar), _ptr(gl)
     p.h0, p.seg_h0, p.state_v_first = _ptr(h0, torch.float32), _ptr(seg_h0, torch.int32), int(state_v_first)
     h = torch.empty(lay.NC, HV, 128, 128, dtype=torch.float32, device=dev) if store_h else None
     Vd = torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=dev) if store_vd else None    # chunk tiles
@@ -166,16 +168,15 @@ def recur_fwd(lay, nw, u, k, k_rstd, g_c, HK, HV, *, h0=None, seg_h0=None, state
     return h, Vd, ht, mt
 
 
-def out_fwd(lay, q, q_rstd, g_c, Aqk, Vd, h, scale, HK, HV, out_dtype, norm=None, keep_raw=False):
+def out_fwd(lay, qs, Aqk, Vd, h, HK, HV, out_dtype, norm=None, keep_raw=False):
     """norm = None or dict(weight, gate, act, eps).  Returns (out [TT,HV,128], o_raw fp32 or None)."""
-    dev = q.device
+    dev = qs.device
     alloc = torch.empty if lay.covers_all else torch.zeros
     out = alloc(lay.TT, HV, 128, dtype=out_dtype, device=dev)
     o_raw = alloc(lay.TT, HV, 128, dtype=torch.float32, device=dev) if keep_raw else None
     p = STRUCTS["MkdaOutFwd"]()
     p.L = _layout_struct(lay, HK, HV)
-    p.q, p.q_dtype, p.q_rstd = _ptr(q), _dt(q), _ptr(q_rstd)
-    p.g_c, p.Aqk, p.Vd, p.h, p.scale = _ptr(g_c), _ptr(Aqk), _ptr(Vd), _ptr(h), scale
+    p.qs, p.Aqk, p.Vd, p.h = _ptr(qs), _ptr(Aqk), _ptr(Vd), _ptr(h)
     if norm is not None:
         w, gate = norm.get("weight"), norm["gate"]
         p.has_norm = 1
@@ -208,15 +209,14 @@ def epilogue_bwd(dy, o_raw, weight, gate, act, eps):
     return d_o, dgate, dw
 
 
-def bwd_dh(lay, d_o, q, k, q_rstd, k_rstd, g_c, Aqk, nw, scale, HK, HV, *, dht=None, seg_dht=None,
+def bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, *, dht=None, seg_dht=None,
            state_v_first=False, want_dh0=True, segments=True, dh=None, dVd=None):
     dev = nw.device
     NS = lay.NS if segments else lay.N
     p = STRUCTS["MkdaBwdDh"]()
     p.L = _layout_struct(lay, HK, HV, segments)
     p.d_o, p.do_dtype = _ptr(d_o), _dt(d_o)
-    p.q, p.k, p.qk_dtype, p.q_rstd, p.k_rstd = _ptr(q), _ptr(k), _dt(q), _ptr(q_rstd), _ptr(k_rstd)
-    p.g_c, p.Aqk, p.nw, p.scale = _ptr(g_c), _ptr(Aqk), _ptr(nw), scale
+    p.kbar, p.qs, p.gl, p.Aqk, p.nw = _ptr(kbar), _ptr(qs), _ptr(gl), _ptr(Aqk), _ptr(nw)
     p.dht, p.seg_dht, p.state_v_first = _ptr(dht, torch.float32), _ptr(seg_dht, torch.int32), int(state_v_first)
     if dh is None:
         dh = torch.empty(lay.NC, HV, 128, 128, dtype=torch.float32, device=dev)

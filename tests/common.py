@@ -194,3 +194,51 @@ def unpack_quarter_tiles(T, lay, TT):
     for c, s0, n in _chunk_rows(lay):
         X[s0:s0 + n] = dense[c, :, :n].permute(1, 0, 2)
     return X
+
+
+# ---- row tiles (include/mkda.h): a [64 tokens][128] operand per (chunk, head), e.g. kbar and scale q 2^g ---------------------
+def _row_tile_index():
+    t = torch.arange(64).view(64, 1)
+    k = torch.arange(128).view(1, 128)
+    byte = (k >> 6) * 64 * 128 + (t >> 3) * 1024 + (t & 7) * 128 + ((((k & 63) >> 3) ^ (t & 7)) << 4) + (k & 7) * 2
+    return (byte // 2).reshape(-1)
+
+
+def pack_row_tiles(X, lay):
+    """token-major fp [TT, H, 128] -> float32-typed row tiles [NC, H, 64, 128] (zero rows past the end of a chunk)."""
+    X = X.float()
+    H = X.shape[1]
+    dense = torch.zeros(lay.NC, H, 64, 128, device=X.device)
+    for c, s0, n in _chunk_rows(lay):
+        dense[c, :, :n] = X[s0:s0 + n].permute(1, 0, 2)
+    hi = dense.to(torch.bfloat16)
+    lo = (dense - hi.float()).to(torch.bfloat16)
+    idx = _row_tile_index().to(X.device)
+    out = torch.empty(lay.NC, H, 2, 64 * 128, dtype=torch.bfloat16, device=X.device)
+    out[..., 0, idx] = hi.reshape(lay.NC, H, -1)
+    out[..., 1, idx] = lo.reshape(lay.NC, H, -1)
+    return out.view(torch.float32).reshape(lay.NC, H, 64, 128)
+
+
+def unpack_row_tiles(T, lay, TT):
+    H = T.shape[1]
+    halves = T.contiguous().view(torch.bfloat16).reshape(lay.NC, H, 2, 64 * 128)
+    idx = _row_tile_index().to(T.device)
+    dense = (halves[..., 0, idx].float() + halves[..., 1, idx].float()).reshape(lay.NC, H, 64, 128)
+    X = torch.zeros(TT, H, 128, device=T.device)
+    for c, s0, n in _chunk_rows(lay):
+        X[s0:s0 + n] = dense[c, :, :n].permute(1, 0, 2)
+    return X
+
+
+def scaled_operands(qn, kn, g_c, lay, scale):
+    """fp64 reference of the state kernels' scaled operands from normalised q / k [TT,HK,128] and the log2 cumsum g_c
+    [TT,HV,128]: kbar = k 2^(gL - g), qs = scale q 2^g (token-major [TT,HV,128]) and gl = 2^gL [NC,HV,128]."""
+    G = g_c.shape[1] // qn.shape[1]
+    qe, ke, g = qn.double().repeat_interleave(G, 1), kn.double().repeat_interleave(G, 1), g_c.double()
+    kbar, gl = torch.zeros_like(g), torch.zeros(lay.NC, g.shape[1], 128, dtype=torch.float64, device=g.device)
+    for c, s0, n in _chunk_rows(lay):
+        gL = g[s0 + n - 1]
+        kbar[s0:s0 + n] = ke[s0:s0 + n] * torch.exp2(gL - g[s0:s0 + n])
+        gl[c] = torch.exp2(gL)
+    return kbar, scale * qe * torch.exp2(g), gl

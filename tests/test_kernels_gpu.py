@@ -6,8 +6,9 @@ import torch
 from mogankda_b200 import ops
 from mogankda_b200.index import get_layout
 from oracle import kda_oracle as orc
-from tests.common import (VARLEN_CU, make_inputs, pack_chunk_tiles, pack_quarter_tiles, pack_state_tiles,
-                          unpack_chunk_tiles, unpack_quarter_tiles, unpack_state_tiles)
+from tests.common import (VARLEN_CU, make_inputs, pack_chunk_tiles, pack_quarter_tiles, pack_row_tiles, pack_state_tiles,
+                          scaled_operands, unpack_chunk_tiles, unpack_quarter_tiles, unpack_row_tiles,
+                          unpack_state_tiles)
 
 pytestmark = pytest.mark.gpu
 KTOL = 1e-3          # per-kernel bar (the compensated bf16 hi/lo products measure ~1e-5)
@@ -37,6 +38,9 @@ def world(request):
     w = dict(lv=lv, do=do.reshape(B * T, 4, 128), dht=dht, opts=opts, bw=bw, fw=bw["fwd"], lay=lay, TT=B * T, f32=f32,
              be=f32(be.reshape(B * T, 4)), scale=128 ** -0.5)
     w["q_rstd"], w["k_rstd"] = ops.l2norm_rstd(lv["q"]), ops.l2norm_rstd(lv["k"])
+    # the state kernels' scaled operands (reference values, then in the hand-over formats)
+    kbar, qs, gl = scaled_operands(qn.reshape(B * T, 2, 128), kn.reshape(B * T, 2, 128), w["fw"]["g_c"], lay, w["scale"])
+    w.update(kbar=kbar, qs=qs, gl=gl, kbar_t=pack_row_tiles(kbar, lay), qs_t=pack_row_tiles(qs, lay), gl_t=f32(gl))
     return w
 
 
@@ -55,8 +59,11 @@ def test_l2norm_statistics(world):
 
 def test_intra_fwd(world):
     lv, fw, f32 = world["lv"], world["fw"], world["f32"]
-    A, Aqk, nw, u = ops.intra_fwd(world["lay"], lv["q"], lv["k"], lv["v"], world["q_rstd"], world["k_rstd"],
-                                  f32(fw["g_c"]), world["be"], world["scale"], 2, 4)
+    A, Aqk, nw, u, kbar, qs, gl = ops.intra_fwd(world["lay"], lv["q"], lv["k"], lv["v"], world["q_rstd"], world["k_rstd"],
+                                                f32(fw["g_c"]), world["be"], world["scale"], 2, 4)
+    _err("kbar", unpack_row_tiles(kbar, world["lay"], world["TT"]), world["kbar"])
+    _err("qs", unpack_row_tiles(qs, world["lay"], world["TT"]), world["qs"])
+    _err("gl", gl, world["gl"])
     nw = unpack_chunk_tiles(nw, world["lay"], world["TT"])
     A, Aqk = unpack_quarter_tiles(A, world["lay"], world["TT"]), unpack_quarter_tiles(Aqk, world["lay"], world["TT"])
     for n, t in dict(A=A, Aqk=Aqk, nw=nw, u=u).items():
@@ -72,21 +79,19 @@ def test_intra_fwd(world):
 
 def test_recurrence_and_output(world):
     lv, fw, f32, lay = world["lv"], world["fw"], world["f32"], world["lay"]
-    h, Vd, ht, _ = ops.recur_fwd(lay, pack_chunk_tiles(f32(fw["nw"]), lay), f32(fw["u"]), lv["k"], world["k_rstd"],
-                                 f32(fw["g_c"]), 2, 4,
-                                 h0=lv["h0"])
+    h, Vd, ht, _ = ops.recur_fwd(lay, pack_chunk_tiles(f32(fw["nw"]), lay), f32(fw["u"]), world["kbar_t"], world["gl_t"],
+                                 2, 4, h0=lv["h0"])
     _err("h", unpack_state_tiles(h), fw["h"]); _err("Vd", unpack_chunk_tiles(Vd, lay, world["TT"]), fw["Vd"])
     _err("ht", ht, fw["ht"])
-    o, _ = ops.out_fwd(lay, lv["q"], world["q_rstd"], f32(fw["g_c"]), pack_quarter_tiles(f32(fw["Aqk"]), lay),
-                       pack_chunk_tiles(f32(fw["Vd"]), lay),
-                       pack_state_tiles(f32(fw["h"])), world["scale"], 2, 4, torch.float32)
+    o, _ = ops.out_fwd(lay, world["qs_t"], pack_quarter_tiles(f32(fw["Aqk"]), lay), pack_chunk_tiles(f32(fw["Vd"]), lay),
+                       pack_state_tiles(f32(fw["h"])), 2, 4, torch.float32)
     _err("o", o, fw["o"])
 
 
 def test_transition_matrix_reproduces_the_state_pass(world):
     """State leaving a segment = transition @ state entering + state reached from zero (what the prefix combine uses)."""
     lv, fw, f32, lay = world["lv"], world["fw"], world["f32"], world["lay"]
-    args = (lay, pack_chunk_tiles(f32(fw["nw"]), lay), f32(fw["u"]), lv["k"], world["k_rstd"], f32(fw["g_c"]), 2, 4)
+    args = (lay, pack_chunk_tiles(f32(fw["nw"]), lay), f32(fw["u"]), world["kbar_t"], world["gl_t"], 2, 4)
     _, _, hs, ms = ops.recur_fwd(*args, store_h=False, store_vd=False, want_transition=True)
     _, _, ht, _ = ops.recur_fwd(*args, h0=lv["h0"], store_h=False, store_vd=False)
     _err("M h0 + h", ms.double() @ lv["h0"].double() + hs.double(), ht)
@@ -97,10 +102,9 @@ def test_transition_matrix_reproduces_the_state_pass(world):
 
 def test_bwd_dh(world):
     lv, fw, bw, f32 = world["lv"], world["fw"], world["bw"], world["f32"]
-    dh, dVd, dh0 = ops.bwd_dh(world["lay"], world["do"], lv["q"], lv["k"], world["q_rstd"], world["k_rstd"],
-                              f32(fw["g_c"]), pack_quarter_tiles(f32(fw["Aqk"]), world["lay"]),
-                              pack_chunk_tiles(f32(fw["nw"]), world["lay"]), world["scale"], 2, 4,
-                              dht=world["dht"])
+    dh, dVd, dh0 = ops.bwd_dh(world["lay"], world["do"], world["kbar_t"], world["qs_t"], world["gl_t"],
+                              pack_quarter_tiles(f32(fw["Aqk"]), world["lay"]),
+                              pack_chunk_tiles(f32(fw["nw"]), world["lay"]), 2, 4, dht=world["dht"])
     _err("dh", unpack_state_tiles(dh), bw["dh"]); _err("dVd", dVd, bw["dVd"]); _err("dh0", dh0, bw["dh0"])
 
 
