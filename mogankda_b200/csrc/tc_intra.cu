@@ -194,6 +194,23 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
             store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
         }
     }
+    MKDA_TRACE_AT(3, 3);
+    publish();
+    if (umma::mma_issuer()) {
+#pragma unroll
+        for (int I = 0; I < 4; ++I)
+            umma::gemm(tmem + 32 * I, umma::opnd_k(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1)),
+                       umma::opnd_k(sKQ, sKQ + 32768, 128, 32 * I), 128, 32, 128, 0u);
+        umma::commit(&sh.bar);
+    }
+    // v for phase 3 is fetched while the products run
+    float vv[2][8];
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+        const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
+        ldg8(p.v, DT, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vv[n]);
+    }
+    // ... and so are the hand-over tiles, built and sent off in the shadow of the products
     // The state kernels' scaled operands, as ready-made tiles: kbar = k 2^(gL - g) (gL = last valid row) and scale q 2^g,
     // plus gl = 2^gL.  Rows past the end are zero (their k / q were zeroed above).
     {
@@ -216,26 +233,12 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
             *reinterpret_cast<float4*>(dst + 4) = make_float4(ex2f_(gLv[4]), ex2f_(gLv[5]), ex2f_(gLv[6]), ex2f_(gLv[7]));
         }
     }
-    MKDA_TRACE_AT(3, 3);
-    publish();
+    umma::fence_async_smem();
+    __syncthreads();
     if (tid == 0) {
         const size_t it = (size_t)c * HV + h;
         umma::bulk_store(reinterpret_cast<uint8_t*>(p.kbar) + it * umma::CHUNK_TILE_BYTES, sKB, umma::CHUNK_TILE_BYTES);
         umma::bulk_store(reinterpret_cast<uint8_t*>(p.qs) + it * umma::CHUNK_TILE_BYTES, sQS, umma::CHUNK_TILE_BYTES);
-    }
-    if (umma::mma_issuer()) {
-#pragma unroll
-        for (int I = 0; I < 4; ++I)
-            umma::gemm(tmem + 32 * I, umma::opnd_k(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1)),
-                       umma::opnd_k(sKQ, sKQ + 32768, 128, 32 * I), 128, 32, 128, 0u);
-        umma::commit(&sh.bar);
-    }
-    // v for phase 3 is fetched while the products run
-    float vv[2][8];
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-        const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-        ldg8(p.v, DT, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vv[n]);
     }
     MKDA_TRACE_AT(3, 4);
     umma::mbar_wait(&sh.bar, 0);
