@@ -127,15 +127,15 @@ KERNEL_FLOPS = {                      # per token per v-head
 # Algorithmic bytes per token per v-head: each kernel's own tensor I/O at the default workload (bf16 q/k/v/gate,
 # fp32 intermediates, HV = 2 HK), every operand counted once.
 KERNEL_BYTES = {
-    "mkda_gate_cumsum_fwd": 1024, "mkda_l2norm_rstd": 128, "mkda_intra_fwd": 2560, "mkda_recur_fwd": 3200,
-    "mkda_out_fwd": 3712, "mkda_epilogue_bwd": 2048, "mkda_bwd_dh": 3584, "mkda_bwd_wy": 4736,
+    "mkda_gate_cumsum_fwd": 1024, "mkda_l2norm_rstd": 128, "mkda_intra_fwd": 3592, "mkda_recur_fwd": 3080,
+    "mkda_out_fwd": 3584, "mkda_epilogue_bwd": 2048, "mkda_bwd_dh": 4104, "mkda_bwd_wy": 4736,
     "mkda_bwd_tail": 7168 + 256, "mkda_gate_bwd": 1536, "mkda_qk_grad_finish": 640,
 }
 # DRAM traffic per token per v-head measured by ncu on the 1B-shape case (profiles/counters_per_kernel_1b_shape.md),
 # bytes (dram read + write per launch / 131072 token-heads); it grows in proportion to tokens x heads.
 KERNEL_TRAFFIC = {
-    "mkda_intra_fwd": 2153, "mkda_recur_fwd": 2907, "mkda_out_fwd": 3508, "mkda_bwd_dh": 3328, "mkda_bwd_wy": 4500,
-    "mkda_bwd_tail": 6803, "mkda_gate_cumsum_fwd": 641, "mkda_epilogue_bwd": 1781, "mkda_qk_grad_finish": 650,
+    "mkda_intra_fwd": 3169, "mkda_recur_fwd": 2771, "mkda_out_fwd": 3371, "mkda_bwd_dh": 3612, "mkda_bwd_wy": 4498,
+    "mkda_bwd_tail": 6815, "mkda_gate_cumsum_fwd": 641, "mkda_epilogue_bwd": 1773, "mkda_qk_grad_finish": 653,
     "mkda_l2norm_rstd": 128,
 }
 
