@@ -128,7 +128,7 @@ KERNEL_FLOPS = {                      # per token per v-head
 # fp32 intermediates, HV = 2 HK), every operand counted once.
 KERNEL_BYTES = {
     "mkda_gate_cumsum_fwd": 1024, "mkda_l2norm_rstd": 128, "mkda_intra_fwd": 3592, "mkda_recur_fwd": 3080,
-    "mkda_out_fwd": 3584, "mkda_epilogue_bwd": 2048, "mkda_bwd_dh": 4104, "mkda_bwd_wy": 4736,
+    "mkda_out_fwd": 3584, "mkda_epilogue_bwd": 2048, "mkda_bwd_dh": 3848, "mkda_bwd_wy": 4736,
     "mkda_bwd_tail": 7168 + 256, "mkda_gate_bwd": 1536, "mkda_qk_grad_finish": 640,
 }
 # DRAM traffic per token per v-head measured by ncu on the 1B-shape case (profiles/counters_per_kernel_1b_shape.md),
