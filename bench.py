@@ -381,6 +381,8 @@ def main():
         barrier()
         ms_e2e = f0.elapsed_time(f1)
         clocks = sampler.stop() if rank == 0 else None
+        if _lib.device_status() != 0:
+            raise SystemExit("a bounded wait inside a tensor-core kernel expired: the run is invalid")
 
     tms = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)
     if world > 1:

@@ -101,3 +101,13 @@ def call(name, params, stream):
     rc = getattr(lib, name)(ctypes.byref(params), ctypes.c_void_p(stream))
     if rc != 0:
         raise MkdaError(f"{name} failed ({rc}): {lib.mkda_last_error().decode()}")
+
+
+def device_status():
+    """Synchronises the current device and returns 0 unless a bounded wait inside a tensor-core kernel ever expired (the
+    kernels then ran on to their exit and their results are not to be trusted)."""
+    lib = load(_variant)
+    lib.mkda_device_status.restype = ctypes.c_int
+    lib.mkda_device_status.argtypes = []
+    return int(lib.mkda_device_status())
+

@@ -24,3 +24,12 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _no_expired_device_waits(request):
+    """After every GPU test: no bounded wait inside a tensor-core kernel may have expired."""
+    yield
+    if "gpu" in request.keywords:
+        from mogankda_b200 import _lib
+        assert _lib.device_status() == 0, "a bounded wait inside a tensor-core kernel expired (see mkda_device_status)"
