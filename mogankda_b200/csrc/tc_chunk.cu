@@ -1,7 +1,8 @@
-// Chunk-parallel kernels on the Blackwell tensor cores (tcgen05.mma, TMEM accumulators): one CTA (8 warps) per
-// (chunk, v-head).  Every product puts a 128-wide state dimension (K or V index) on the MMA M axis and the 64 chunk rows
-// on N, so all accumulators are [128 lanes x 64 columns] fp32 tiles in tensor memory.  Operands are produced by the CUDA
-// cores (gate scaling, L2 statistics, bf16 hi/lo split) straight into the swizzled K-major tile layout; see umma.cuh.
+// Chunk-parallel kernels on the Blackwell tensor cores (tcgen05.mma, TMEM accumulators): one CTA (16 warps) per
+// (chunk, v-head).  Every product puts a 128-wide dimension (K or V index, or two stacked 64-row operands) on the MMA M
+// axis and the chunk rows on N, so all accumulators are [128 lanes x 64 / 128 columns] fp32 tiles in tensor memory.
+// Operands either arrive as ready-made tiles by bulk copy (states, Vd, nw, A, Aqk, the scaled q / k) or are produced by
+// the CUDA cores (gate scaling, L2 statistics, bf16 hi/lo split) straight into the swizzled tile layout; see umma.cuh.
 #include "common.cuh"
 #include "host.h"
 #include "umma.cuh"

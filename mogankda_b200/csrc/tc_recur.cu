@@ -3,9 +3,10 @@
 // One CTA (16 warps) per (v-head, segment) carries the whole 128 x 128 state, TRANSPOSED, in tensor memory:
 // St[v lanes][K-index columns] fp32.  With that orientation every operand that has to be regenerated from the
 // accumulators (the state itself, Vd^T) is written by its owning thread as plain 16-byte row chunks of a K-major tile,
-// and every operand that comes from global memory is staged untransposed and read through a K-major or MN-major view.
+// and every operand that comes from global memory is a ready-made tile written by the intra-chunk kernel (nw^T, kbar,
+// scale q 2^g, Aqk), fetched by bulk copy and read through a K-major or MN-major view; only u and dO pass through registers.
 // Per chunk:   Vd^T[v x tok] = u^T + St nw^T          St <- St diag(gl) + Vd^T kbar
-// The next chunk's global operands are fetched into registers while the current chunk's products run.
+// The forward kernel double-buffers its tiles: the next chunk's copies are in flight while the current products run.
 #include "common.cuh"
 #include "host.h"
 #include "umma.cuh"

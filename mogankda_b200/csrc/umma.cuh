@@ -113,34 +113,6 @@ __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64
         :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-// D (+)= A * B^T over KT columns with the three-product split.  a_hi/a_lo/b_hi/b_lo are shared-memory byte addresses
-// of tiles with RA / RB rows.  `first` = 0 overwrites D with the first product.
-__device__ __forceinline__ void gemm_split(uint32_t tmem_d, uint32_t a_hi, uint32_t a_lo, int RA, uint32_t b_hi,
-                                           uint32_t b_lo, int RB, int KT, uint32_t idesc, uint32_t accumulate) {
-    for (int ks = 0; ks < KT / 16; ++ks) {
-        const uint32_t ao = (uint32_t)((ks >> 2) * RA * 128 + (ks & 3) * 32);
-        const uint32_t bo = (uint32_t)((ks >> 2) * RB * 128 + (ks & 3) * 32);
-        const uint64_t dah = make_desc(a_hi + ao), dal = make_desc(a_lo + ao);
-        const uint64_t dbh = make_desc(b_hi + bo), dbl = make_desc(b_lo + bo);
-        mma_bf16(tmem_d, dal, dbh, idesc, accumulate);
-        mma_bf16(tmem_d, dah, dbl, idesc, 1u);
-        mma_bf16(tmem_d, dah, dbh, idesc, 1u);
-        accumulate = 1u;
-    }
-}
-// same, when the B operand is exactly representable in bf16 (no lo tile): two products
-__device__ __forceinline__ void gemm_split_a(uint32_t tmem_d, uint32_t a_hi, uint32_t a_lo, int RA, uint32_t b_hi, int RB,
-                                             int KT, uint32_t idesc, uint32_t accumulate) {
-    for (int ks = 0; ks < KT / 16; ++ks) {
-        const uint32_t ao = (uint32_t)((ks >> 2) * RA * 128 + (ks & 3) * 32);
-        const uint32_t bo = (uint32_t)((ks >> 2) * RB * 128 + (ks & 3) * 32);
-        const uint64_t dbh = make_desc(b_hi + bo);
-        mma_bf16(tmem_d, make_desc(a_lo + ao), dbh, idesc, accumulate);
-        mma_bf16(tmem_d, make_desc(a_hi + ao), dbh, idesc, 1u);
-        accumulate = 1u;
-    }
-}
-
 // D[M x N] (+)= A B^T over KT (multiple of 16) with the hi/lo split; products whose lo tile is absent are skipped.
 // The four base descriptors are built once; a k-step only adds its byte offset (>> 4) to the start-address field, so
 // the issuing thread spends a handful of instructions per MMA (KT is a literal at every call site: the loop unrolls).
