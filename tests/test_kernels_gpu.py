@@ -157,3 +157,20 @@ def test_epilogue_backward(world):
         d_o, dgate, dw = ops.epilogue_bwd(dy.contiguous(), f32(fw["o"]), lv["ep_w"], lv["ep_gate"], act, 1e-6)
         _err("do", d_o.view_as(ro), ro, 1e-5); _err("dw", dw, rw, 1e-5)
         _err("dgate", dgate.reshape(rz.shape), rz, 1e-5 if dgate.dtype == torch.float32 else 2.0 ** -8)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2, 3])
+@pytest.mark.parametrize("N,K", [(64, 64), (64, 128), (128, 64), (128, 128)])
+def test_tensor_core_plumbing_in_isolation(mode, N, K):
+    """mkda_selftest_umma: D = A B^T through the same tile layout, descriptors and three-product bf16 split the kernels
+    use, with the operands staged K-major or MN-major (mode bits); the error must be at the 2^-16 level of the split."""
+    from mogankda_b200 import _lib
+    torch.manual_seed(7 + mode)
+    A, B = torch.randn(128, K, device="cuda"), torch.randn(N, K, device="cuda")
+    D = torch.zeros(128, N, device="cuda")
+    p = _lib.STRUCTS["MkdaSelfTest"]()
+    p.A, p.B, p.D, p.N, p.K, p.mode = A.data_ptr(), B.data_ptr(), D.data_ptr(), N, K, mode
+    _lib.call("mkda_selftest_umma", p, torch.cuda.current_stream().cuda_stream)
+    ref = A.double() @ B.double().T
+    err = ((D.double() - ref).abs().max() / ref.abs().max()).item()
+    assert err < 5e-5, err
