@@ -42,7 +42,7 @@ struct IntraShared {
     uint64_t bar;
     uint32_t tmem;
     float beta[CH];
-    float T[32][33];
+    __align__(16) float T[32][34];
 };
 
 constexpr int MLD = 68;
@@ -79,36 +79,57 @@ __device__ __forceinline__ void invert_unit_lower(const float* __restrict__ sM, 
         const int ro = 32 * hb + 16, co = 32 * hb;            // block origin; A^-1 at (co, co), B^-1 at (ro, ro)
         float t = 0.f;
 #pragma unroll
-        for (int e = 0; e < 16; ++e) t = fmaf(sM[(ro + r) * MLD + co + e], sInv[(co + e) * MLD + co + c], t);
+        for (int e4 = 0; e4 < 16; e4 += 4) {
+            const float4 m4 = *reinterpret_cast<const float4*>(sM + (ro + r) * MLD + co + e4);
+            t = fmaf(m4.x, sInv[(co + e4) * MLD + co + c], t);
+            t = fmaf(m4.y, sInv[(co + e4 + 1) * MLD + co + c], t);
+            t = fmaf(m4.z, sInv[(co + e4 + 2) * MLD + co + c], t);
+            t = fmaf(m4.w, sInv[(co + e4 + 3) * MLD + co + c], t);
+        }
         sh.T[16 * hb + r][c] = t;
         __syncthreads();
         float x = 0.f;
 #pragma unroll
-        for (int e = 0; e < 16; ++e) x = fmaf(sInv[(ro + r) * MLD + ro + e], sh.T[16 * hb + e][c], x);
+        for (int e4 = 0; e4 < 16; e4 += 4) {
+            const float4 m4 = *reinterpret_cast<const float4*>(sInv + (ro + r) * MLD + ro + e4);
+            x = fmaf(m4.x, sh.T[16 * hb + e4][c], x);
+            x = fmaf(m4.y, sh.T[16 * hb + e4 + 1][c], x);
+            x = fmaf(m4.z, sh.T[16 * hb + e4 + 2][c], x);
+            x = fmaf(m4.w, sh.T[16 * hb + e4 + 3][c], x);
+        }
         sInv[(ro + r) * MLD + co + c] = -x;
     }
     __syncthreads();
-    {   // 32 x 32 block (rows 32.., columns 0..31): thread = (r, two columns)
+    {   // 32 x 32 block (rows 32.., columns 0..31): thread = (r, two columns); 128- and 64-bit shared loads keep the
+        // load count per product term low (this step is bound by shared-memory load issue)
         const int r = tid >> 4, c = (tid & 15) * 2;
         float t0 = 0.f, t1 = 0.f;
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-            const float m = sM[(32 + r) * MLD + e];
-            t0 = fmaf(m, sInv[e * MLD + c], t0);
-            t1 = fmaf(m, sInv[e * MLD + c + 1], t1);
+        for (int e4 = 0; e4 < 32; e4 += 4) {
+            const float4 m4 = *reinterpret_cast<const float4*>(sM + (32 + r) * MLD + e4);
+            const float m[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 a = *reinterpret_cast<const float2*>(sInv + (e4 + k) * MLD + c);
+                t0 = fmaf(m[k], a.x, t0);
+                t1 = fmaf(m[k], a.y, t1);
+            }
         }
-        sh.T[r][c] = t0;
-        sh.T[r][c + 1] = t1;
+        *reinterpret_cast<float2*>(&sh.T[r][c]) = make_float2(t0, t1);
         __syncthreads();
         float x0 = 0.f, x1 = 0.f;
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-            const float m = sInv[(32 + r) * MLD + 32 + e];
-            x0 = fmaf(m, sh.T[e][c], x0);
-            x1 = fmaf(m, sh.T[e][c + 1], x1);
+        for (int e4 = 0; e4 < 32; e4 += 4) {
+            const float4 m4 = *reinterpret_cast<const float4*>(sInv + (32 + r) * MLD + 32 + e4);
+            const float m[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 a = *reinterpret_cast<const float2*>(&sh.T[e4 + k][c]);
+                x0 = fmaf(m[k], a.x, x0);
+                x1 = fmaf(m[k], a.y, x1);
+            }
         }
-        sInv[(32 + r) * MLD + c] = -x0;
-        sInv[(32 + r) * MLD + c + 1] = -x1;
+        *reinterpret_cast<float2*>(sInv + (32 + r) * MLD + c) = make_float2(-x0, -x1);
     }
     __syncthreads();
 }
@@ -259,7 +280,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     }
     if (tid == 0) umma::bulk_store_wait_read();    // the two tiles under sM / sInv / sP have left shared memory
     __syncthreads();
-    for (int i = tid; i < CH * MLD; i += 512) sInv[i] = 0.f;
+    for (int i = tid; i < CH * MLD / 4; i += 512) reinterpret_cast<float4*>(sInv)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (q < 2) {                              // lane = column j, cg = row block I: Gamma / Q K^T entries (16 I + r, j)
         float v[32];
         umma::tmem_ld32(umma::tmem_addr(tmem, warp, 32 * cg), v);

@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
     uint8_t* sK[2] = {sW[0] + 32768, sW[1] + 32768};                 // kbar row tile [tok][K index], fetched by bulk copy
 
     const bool trans = blockIdx.x == 1;
-    const int h = blockIdx.y, seg = blockIdx.z, HV = p.L.HV, HK = p.L.HK;
+    const int h = blockIdx.y, seg = blockIdx.z, HV = p.L.HV;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
     const bool vf = p.state_v_first != 0;
@@ -211,7 +211,7 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
     uint8_t* sQs = sKb + 32768;                  // scale q 2^g row tile [i][K index] (bulk copy)
     uint8_t* sNw = sQs + 32768;                  // nw^T chunk tile [K index][j], fetched by bulk copy
 
-    const int h = blockIdx.y, seg = blockIdx.z, HV = p.L.HV, HK = p.L.HK;
+    const int h = blockIdx.y, seg = blockIdx.z, HV = p.L.HV;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
     const bool vf = p.state_v_first != 0;
