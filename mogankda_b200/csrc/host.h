@@ -9,6 +9,8 @@ int set_error(int code, const char* msg);
 int check_launch(const char* what);
 // Raises the dynamic shared memory limit of `func` once per process; returns 0 or an error code.
 int ensure_smem(const void* func, int bytes, const char* what);
+// Number of SMs of the current device (cached per device).
+int sm_count();
 int launch_out_fwd_tc(const MkdaOutFwd* p, cudaStream_t stream);
 int launch_bwd_wy_tc(const MkdaBwdWy* p, cudaStream_t stream);
 int tc_chunk_status(unsigned int* out);
