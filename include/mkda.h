@@ -245,7 +245,7 @@ typedef struct {
     const float* A;            /* [NC,HV] quarter tiles as written by mkda_intra_fwd */
     const float* h;            /* [NC,HV] state tiles */
     const void* d_o; int do_dtype; const float* dVd;
-    float* Vd;                 /* [TT,HV,128] recomputed */
+    const float* Vd;           /* [NC,HV] chunk tiles as written by mkda_recur_fwd in the forward pass */
     float* dX;                 /* [TT,HV,128] = dv (fp32), an input of mkda_bwd_tail */
     float* dbeta_w;            /* [TT,HV] */
     float* dAqk; float* dL;    /* [TT,HV,64] */
@@ -262,7 +262,8 @@ typedef struct {
     MkdaLayout L;
     const void* q; const void* k; int qk_dtype; const float* q_rstd; const float* k_rstd;
     const float* g_c; const float* beta;
-    const void* d_o; int do_dtype; const float* dX; const float* Vd;
+    const void* d_o; int do_dtype; const float* dX;
+    const float* Vd;           /* [NC,HV] chunk tiles as written by mkda_recur_fwd in the forward pass */
     const float* h; const float* dh;               /* state tiles, see MKDA_STATE_TILE_BYTES */
     const float* dAqk; const float* dL; const float* dbeta_w;
     float scale;

@@ -72,7 +72,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
                                  keep_raw=cfg["has_ep"] and need_bwd)
         if need_bwd:
             ctx.save_for_backward(q, k, v, x, beta, A_log, dt_bias, initial_state, ep_w, ep_gate, q_rstd, k_rstd,
-                                  g_c, beta_e, A, Aqk, nw, h, o_raw, ms, kbar, qs, gl)
+                                  g_c, beta_e, A, Aqk, nw, h, o_raw, ms, kbar, qs, gl, Vd)
         ctx.cfg, ctx.lay, ctx.dims = cfg, lay, (B, T, HK, HV)
         ctx.set_materialize_grads(False)
         return out.view(B, T, HV, 128), ht
@@ -81,7 +81,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
     @torch.autograd.function.once_differentiable
     def backward(ctx, dy, dht):
         (q, k, v, x, beta, A_log, dt_bias, initial_state, ep_w, ep_gate, q_rstd, k_rstd, g_c, beta_e, A, Aqk, nw, h,
-         o_raw, ms, kbar, qs, gl) = ctx.saved_tensors
+         o_raw, ms, kbar, qs, gl, Vd) = ctx.saved_tensors
         cfg, lay = ctx.cfg, ctx.lay
         B, T, HK, HV = ctx.dims
         scale, vf, cp = cfg["scale"], cfg["state_v_first"], cfg["cp_context"]
@@ -116,7 +116,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
         else:
             dh, dVd, dh0 = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, dht=dht,
                                       state_v_first=vf, want_dh0=need_dh0)
-        Vd, dX, dbeta_w, dAqk, dL = ops.bwd_wy(lay, k, v, k_rstd, g_c, beta_e, A, h, d_o, dVd, HK, HV)
+        dX, dbeta_w, dAqk, dL = ops.bwd_wy(lay, k, v, k_rstd, g_c, beta_e, A, h, Vd, d_o, dVd, HK, HV)
         dq_v, dk_v, dgp, dbeta, dv = ops.bwd_tail(lay, q, k, q_rstd, k_rstd, g_c, beta_e, d_o, dX, Vd, h, dh, dAqk, dL,
                                                   dbeta_w, scale, HK, HV, beta, cfg["beta_mode"] == "sigmoid",
                                                   cfg["beta_scale"], dv_dtype=v.dtype)

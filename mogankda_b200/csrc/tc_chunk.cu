@@ -265,12 +265,12 @@ __device__ __forceinline__ void load_tile8(const uint8_t* hi, const uint8_t* lo,
 
 // ---------------------------------------------------------------------------------------------------------
 // bwd_wy.  With S the state entering the chunk, k~ = k 2^g, Ab = A diag(beta):
-//   X = V - k~ S        Vd = Ab X        dAqk = lower(dO Vd^T)
+//   X = V - k~ S        Vd = Ab X (saved by the forward pass)        dAqk = lower(dO Vd^T)
 //   dW = A^T dVd        dX = diag(beta) dW (= dV)       dbeta_w = rowsum(dW * X)
 //   dA = (dVd X^T) diag(beta)          dL = -strictlower(A^T dA A^T)
-// Six dependent products, each with a 128-wide axis on M (TMEM columns in brackets):
+// Five dependent products, each with a 128-wide axis on M (TMEM columns in brackets):
 //   G1 [0]    X^T[v x tok]  = V^T - S^T k~^T                       (A = the saved state tile as it is)
-//   G2 [64]   Vd^T[v x i]   = X^T (A diag(beta))^T
+//             Vd^T[v x i]   = X^T (A diag(beta))^T is not recomputed: the forward pass's Vd^T tile is fetched instead
 //   G4 [256]  dW^T[v x j]   = dVd^T A                              (both operands MN-major views of natural tiles)
 //   G3 [128]  [dO; dVd] [Vd; X]^T  -> rows 0..63 / cols 0..63 = dO Vd^T, rows 64..127 / cols 64..127 = dVd X^T
 //   G5 [320]  Y[a x j]      = (dVd X^T diag(beta)) A^T
@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     uint8_t* sXl = sVl + 16384;
     uint8_t* sAh = sXl + 16384;               // A [i][j]
     uint8_t* sAl = sAh + 8192;
-    uint8_t* sBh = sAl + 8192;                // A diag(beta) [i][j]; later Y [a][j]
+    uint8_t* sBh = sAl + 8192;                // Y [a][j]
     uint8_t* sBl = sBh + 8192;
 
     const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV, HK = p.L.HK;
@@ -310,13 +310,16 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
 
     if (tid < CH) sBeta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
     __shared__ uint64_t ldbar;
-    if (tid == 0) {   // S^T [v][K index] and A [i][j] arrive as ready-made operand tiles on one barrier
+    if (tid == 0) {   // S^T [v][K index], A [i][j] and the forward pass's Vd^T [v][i] arrive as ready-made operand tiles
         const size_t it = (size_t)c * HV + h;
+        const uint8_t* vd = reinterpret_cast<const uint8_t*>(p.Vd) + it * umma::CHUNK_TILE_BYTES;
         umma::mbar_init(&ldbar, 1);
         umma::fence_barrier_init();
-        umma::mbar_expect_tx(&ldbar, umma::STATE_TILE_BYTES + umma::QUARTER_TILE_BYTES);
-        umma::bulk_load(sAh, reinterpret_cast<const uint8_t*>(p.A) + it * umma::QUARTER_TILE_BYTES, umma::QUARTER_TILE_BYTES, &ldbar);
+        umma::mbar_expect_tx(&ldbar, umma::STATE_TILE_BYTES + umma::QUARTER_TILE_BYTES + umma::CHUNK_TILE_BYTES);
         umma::bulk_load(sSh, reinterpret_cast<const uint8_t*>(p.h) + it * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &ldbar);
+        umma::bulk_load(sAh, reinterpret_cast<const uint8_t*>(p.A) + it * umma::QUARTER_TILE_BYTES, umma::QUARTER_TILE_BYTES, &ldbar);
+        umma::bulk_load(sVh, vd, umma::CHUNK_TILE_BYTES / 2, &ldbar);                          // hi half, left column block
+        umma::bulk_load(sVl, vd + umma::CHUNK_TILE_BYTES / 2, umma::CHUNK_TILE_BYTES / 2, &ldbar);   // lo half
     }
     // everything the first three stages need from global memory is requested up front: k, g, A, then [dO; dVd] rows and
     // this thread's V column, which stay in registers until G1 has released the state tile
@@ -359,15 +362,6 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
         umma::gemm(tmem + 0, umma::opnd_k(sSh, sSl, 128), umma::opnd_k(sKh, sKl, 64), 128, 64, 128, 0u);
         umma::commit(&sh.bar);
     }
-    {   // A diag(beta) from the A tile that came with the state tile (rows past the end are identity rows: their beta is 0)
-        umma::mbar_wait(&ldbar, 0);
-        const int r = tid >> 3, k8 = tid & 7;
-        float a8[8];
-        load_tile8(sAh, sAl, 64, r, k8, a8);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a8[e] *= sBeta[k8 * 8 + e];
-        store_split8(sBh, sBl, 64, r, k8, a8);
-    }
     {
 #pragma unroll
         for (int n = 0; n < 4; ++n)
@@ -377,6 +371,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
             if (cg * 16 + j >= len) vv[j] = 0.f;
         MKDA_TRACE_AT(1, 3);
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;
+        umma::mbar_wait(&ldbar, 0);                            // long complete: makes the A tile visible to every reader below
         umma::fence_after_sync();
         MKDA_TRACE_AT(1, 4);
         float d[16], x0[8], x1[8];
@@ -389,39 +384,23 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     }
     MKDA_TRACE_AT(1, 5);
     tc_operands_ready(&sh);
-    if (umma::mma_issuer()) {
-        umma::gemm(tmem + 64, umma::opnd_k(sXh, sXl, 128), umma::opnd_k(sBh, sBl, 64), 128, 64, 64, 0u);
+    if (umma::mma_issuer()) {   // Vd^T is the forward pass's tile (the barrier it came on was awaited before G1): G4 and G3 go together
         umma::gemm(tmem + 256, umma::opnd_mn(sSh, sSl, 128, 64), umma::opnd_mn(sAh, sAl, 64), 128, 64, 64, 0u);
+        umma::gemm(tmem + 128, umma::opnd_k(sSh, sSl, 128), umma::opnd_mn(sVh, sVl, 128), 128, 128, 128, 0u);
         umma::commit(&sh.bar);
     }
     umma::mbar_wait(&sh.bar, phase); phase ^= 1;
     umma::fence_after_sync();
     MKDA_TRACE_AT(1, 6);
     {
-        float vd[16], dw[16], a0[8], a1[8];
-        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 64 + cg * 16), vd);
+        float dw[16];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 256 + cg * 16), dw);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const int t = cg * 16 + j;
-            if (t < len) {
-                const size_t off = ((size_t)(start + t) * HV + h) * 128 + row;
-                p.Vd[off] = vd[j];
-                p.dX[off] = sBeta[t] * dw[j];
-            }
-            if (j < 8) a0[j] = vd[j]; else a1[j - 8] = vd[j];
+            if (t < len) p.dX[((size_t)(start + t) * HV + h) * 128 + row] = sBeta[t] * dw[j];
         }
-        store_split8(sVh, sVl, 128, row, 2 * cg, a0);
-        store_split8(sVh, sVl, 128, row, 2 * cg + 1, a1);
     }
-    MKDA_TRACE_AT(1, 7);
-    tc_operands_ready(&sh);
-    if (umma::mma_issuer()) {
-        umma::gemm(tmem + 128, umma::opnd_k(sSh, sSl, 128), umma::opnd_mn(sVh, sVl, 128), 128, 128, 128, 0u);
-        umma::commit(&sh.bar);
-    }
-    umma::mbar_wait(&sh.bar, phase); phase ^= 1;
-    umma::fence_after_sync();
     MKDA_TRACE_AT(1, 8);
     if (q < 2) {                                   // rows i = row: dAqk = lower(dO Vd^T)
         float d[16];

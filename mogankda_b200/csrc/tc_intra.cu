@@ -394,7 +394,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     uint8_t* sSl = base + 32768;
     uint8_t* sTh = base + 65536;                       // state tile dS'^T
     uint8_t* sTl = base + 98304;
-    uint8_t* sOh = base + 131072;                      // [dO; dX] [2 x tok][v] as one 128-row tile (32 KB); rows 0-63 later Vd
+    uint8_t* sOh = base + 131072;                      // [dO; dX] [2 x tok][v] as one 128-row tile (32 KB); its first 32 KB later the Vd^T chunk tile
     uint8_t* sOl = base + 163840;
     // intra phase
     uint8_t* sKQ = base + KQ_OFF;
@@ -413,12 +413,17 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
     MKDA_TRACE_AT(5, 0);
 
-    // ---- state phase: the two state tiles arrive by asynchronous copy; dO, dX, Vd go through registers ----------------
+    // ---- state phase: the two state tiles arrive by asynchronous copy; dO, dX and the Vd^T tile go through registers ----------------
     if (tid == 0) {
         umma::fetch_state_tile(&ldS, sSh, p.h, (size_t)c * HV + h);
         umma::fetch_state_tile(&ldD, sTh, p.dh, (size_t)c * HV + h);
     }
-    float vV[2][8];
+    uint4 vV[4];                                       // the forward pass's Vd^T chunk tile, copied as it is (64 bytes per thread)
+    {
+        const uint4* vd = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.Vd) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES);
+#pragma unroll
+        for (int n = 0; n < 4; ++n) vV[n] = __ldg(vd + tid + n * 512);
+    }
     {
         float vO[2][8], vX[2][8];
 #pragma unroll
@@ -427,14 +432,13 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
             const size_t off = ((size_t)(start + rr) * HV + h) * 128 + (i & 15) * 8;
             ldg8(p.d_o, DODT, off, vO[n]);
             ldg8(p.dX, MKDA_F32, off, vX[n]);
-            ldg8(p.Vd, MKDA_F32, off, vV[n]);
         }
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
             const int i = tid + n * 512, r = i >> 4;
             if (r >= len) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) vO[n][e] = vX[n][e] = vV[n][e] = 0.f;
+                for (int e = 0; e < 8; ++e) vO[n][e] = vX[n][e] = 0.f;
             }
             store_split8(sOh, sOl, 128, r, i & 15, vO[n]);
             store_split8(sOh, sOl, 128, 64 + r, i & 15, vX[n]);
@@ -508,13 +512,10 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     MKDA_TRACE_AT(5, 3);
     umma::fence_after_sync();
 #pragma unroll
-    for (int n = 0; n < 2; ++n) {
-        const int i = tid + n * 512;
-        store_split8(sOh, sOl, 128, i >> 4, i & 15, vV[n]);
-    }
+    for (int n = 0; n < 4; ++n) reinterpret_cast<uint4*>(sOh)[tid + n * 512] = vV[n];     // hi 16 KB, then lo 16 KB
     publish();
-    if (umma::mma_issuer()) {
-        umma::gemm(tmem + 128, umma::opnd_mn(sTh, sTl, 128), umma::opnd_k(sOh, sOl, 128), 128, 64, 128, 0u);
+    if (umma::mma_issuer()) {   // B(n = token, k = v) is the MN-major view of the [v][token] tile
+        umma::gemm(tmem + 128, umma::opnd_mn(sTh, sTl, 128), umma::opnd_mn(sOh, sOh + 16384, 128), 128, 64, 128, 0u);
         umma::commit(&sh.bar);
     }
     MKDA_TRACE_AT(5, 4);

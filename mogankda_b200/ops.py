@@ -228,11 +228,12 @@ def bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, *, dht=None, seg_dht=None,
     return dh, dVd, dh0
 
 
-def bwd_wy(lay, k, v, k_rstd, g_c, beta_e, A, h, d_o, dVd, HK, HV):
+def bwd_wy(lay, k, v, k_rstd, g_c, beta_e, A, h, Vd, d_o, dVd, HK, HV):
+    """Vd: the forward pass's chunk tiles.  Returns (dX, dbeta_w, dAqk, dL)."""
     dev = k.device
     z = lambda *s: torch.empty(lay.TT, HV, *s, dtype=torch.float32, device=dev)      # noqa: E731
     alloc = torch.empty if lay.covers_all else torch.zeros
-    Vd, dAqk, dL, dbeta_w = z(128), z(64), z(64), z()
+    dAqk, dL, dbeta_w = z(64), z(64), z()
     dX = alloc(lay.TT, HV, 128, dtype=torch.float32, device=dev)
     p = STRUCTS["MkdaBwdWy"]()
     p.L = _layout_struct(lay, HK, HV)
@@ -241,7 +242,7 @@ def bwd_wy(lay, k, v, k_rstd, g_c, beta_e, A, h, d_o, dVd, HK, HV):
     p.d_o, p.do_dtype, p.dVd = _ptr(d_o), _dt(d_o), _ptr(dVd)
     p.Vd, p.dX, p.dbeta_w, p.dAqk, p.dL = _ptr(Vd), _ptr(dX), _ptr(dbeta_w), _ptr(dAqk), _ptr(dL)
     _lib.call("mkda_bwd_wy", p, _stream())
-    return Vd, dX, dbeta_w, dAqk, dL
+    return dX, dbeta_w, dAqk, dL
 
 
 def bwd_tail(lay, q, k, q_rstd, k_rstd, g_c, beta_e, d_o, dX, Vd, h, dh, dAqk, dL, dbeta_w, scale, HK, HV,

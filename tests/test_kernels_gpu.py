@@ -110,17 +110,17 @@ def test_bwd_dh(world):
 
 def test_bwd_wy(world):
     lv, fw, bw, f32, lay = world["lv"], world["fw"], world["bw"], world["f32"], world["lay"]
-    Vd, dX, dbw, dAqk, dL = ops.bwd_wy(lay, lv["k"], lv["v"], world["k_rstd"], f32(fw["g_c"]), world["be"],
-                                       pack_quarter_tiles(f32(fw["A"]), lay),
-                                       pack_state_tiles(f32(fw["h"])), world["do"], f32(bw["dVd"]), 2, 4)
-    for n, t in dict(Vd=Vd, dX=dX, dbeta_w=dbw, dAqk=dAqk, dL=dL).items():
+    dX, dbw, dAqk, dL = ops.bwd_wy(lay, lv["k"], lv["v"], world["k_rstd"], f32(fw["g_c"]), world["be"],
+                                   pack_quarter_tiles(f32(fw["A"]), lay), pack_state_tiles(f32(fw["h"])),
+                                   pack_chunk_tiles(f32(fw["Vd"]), lay), world["do"], f32(bw["dVd"]), 2, 4)
+    for n, t in dict(dX=dX, dbeta_w=dbw, dAqk=dAqk, dL=dL).items():
         _err(n, t, bw[n])
 
 
 def test_bwd_tail_gate_and_finish(world):
     lv, fw, bw, f32, lay, o = world["lv"], world["fw"], world["bw"], world["f32"], world["lay"], world["opts"]
     t_q, t_k, t_g, t_b, t_v = ops.bwd_tail(lay, lv["q"], lv["k"], world["q_rstd"], world["k_rstd"], f32(fw["g_c"]), world["be"],
-                                      world["do"], f32(bw["dX"]), f32(bw["Vd"]), pack_state_tiles(f32(fw["h"])),
+                                      world["do"], f32(bw["dX"]), pack_chunk_tiles(f32(fw["Vd"]), lay), pack_state_tiles(f32(fw["h"])),
                                       pack_state_tiles(f32(bw["dh"])), f32(bw["dAqk"]), f32(bw["dL"]), f32(bw["dbeta_w"]),
                                       world["scale"], 2, 4, lv["beta"], False, 1.0, dv_dtype=torch.bfloat16)
     assert torch.equal(t_v, f32(bw["dX"]).reshape(t_v.shape).to(torch.bfloat16))
