@@ -171,6 +171,8 @@ def chunk_delta_rule(q, k, v, g, beta, *, scale=None, initial_state=None, output
     unless ``gate_mode="precomputed"``, then the natural-log per-token decay, contract g >= -5); beta [B,T,HV].
     Returns ``(o, final_state)``: o in q.dtype, or float32 when ``output_norm`` is given.
     """
+    if cp_context is not None and getattr(cp_context, "cu_seqlens", None) is not None:
+        cu_seqlens = cp_context.cu_seqlens      # the context's local boundaries replace the argument (reference :87-120)
     _check_common(q, k, v, g, beta, initial_state, cu_seqlens)
     if gate_mode not in ops.GATE_MODES:
         raise ValueError(f"unknown gate_mode {gate_mode!r}")
@@ -187,8 +189,6 @@ def chunk_delta_rule(q, k, v, g, beta, *, scale=None, initial_state=None, output
     ep = output_norm
     if ep is not None and ep.get("act", "silu") not in ops.ACTS:
         raise ValueError(f"unknown act {ep.get('act')!r}")
-    if cp_context is not None and cu_seqlens is not None and cu_seqlens.numel() != 2:
-        raise ValueError("cross-GPU context parallelism handles one sequence per call")
     if cp_context is not None and q.shape[0] != 1:
         raise ValueError("inter-card CP requires B==1 (varlen).")
     B, T = q.shape[:2]

@@ -51,11 +51,6 @@ def _worker(rank, world, port, seg_counts, fail_rank):
         hi = lo + seg_counts[rank]
         ctx = cpmod.ContextParallel(dist.group.WORLD)
         lay = FakeLayout(seg_counts[rank])
-        if rank == fail_rank:
-            with pytest.raises(ValueError):
-                bad = FakeLayout(seg_counts[rank])
-                bad.NG = 2
-                ctx.forward_carry(H[lo:hi], M[lo:hi], h0, bad, HV)
         got = ctx.forward_carry(H[lo:hi].contiguous(), M[lo:hi].contiguous(), h0 if rank == 0 else None, lay, HV)
         X = h0[0].clone()
         for s in range(lo):
@@ -80,3 +75,81 @@ def _free_port():
 @pytest.mark.parametrize("seg_counts", [(3, 2), (1, 4)])
 def test_context_parallel_prefix_fold_two_ranks(seg_counts):
     mp.spawn(_worker, args=(2, _free_port(), seg_counts, 1), nprocs=2, join=True)
+
+
+class PackedLayout:
+    def __init__(self, groups):
+        self.NG, self.NS = len(groups), sum(groups)
+        off = [0]
+        for n in groups:
+            off.append(off[-1] + n)
+        self.grp_seg_off = torch.tensor(off, dtype=torch.int32)
+
+
+def _packed_worker(rank, world, port):
+    """Three sequences over two ranks: A (2 segments) on rank 0, B cut into 1 + 2 segments across the boundary, C
+    (1 segment) on rank 1."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mogankda_b200 import cp as cpmod, ops
+        ops.state_combine = combine_ref
+        g = torch.Generator().manual_seed(11)
+        rnd = lambda *s: torch.randn(*s, HV, D, D, generator=g, dtype=torch.float64)      # noqa: E731
+        H, M, Dl = rnd(6), rnd(6) * 0.3, rnd(6)          # segments: A0 A1 B0 | B1 B2 C0
+        h0, dht = rnd(3), rnd(3)                         # per global sequence A, B, C
+        fold = lambda X, segs: [X := M[s] @ X + H[s] for s in segs][-1]                    # noqa: E731
+        foldb = lambda G, segs: [G := M[s].transpose(-1, -2) @ G + Dl[s] for s in reversed(segs)][-1]   # noqa: E731
+        if rank == 0:
+            ctx = cpmod.ContextParallel(dist.group.WORLD, pre_num_ranks=0, post_num_ranks=1)
+            lay, lo, hi = PackedLayout([2, 1]), 0, 3
+            got = ctx.forward_carry(H[lo:hi].contiguous(), M[lo:hi].contiguous(), h0[:2].clone(), lay, HV)
+            torch.testing.assert_close(got, h0[:2])
+            gb = ctx.backward_carry(Dl[lo:hi].contiguous(), M[lo:hi].contiguous(), dht[:2].clone(), lay, HV)
+            torch.testing.assert_close(gb[0], dht[0])
+            torch.testing.assert_close(gb[1], foldb(dht[1].clone(), [3, 4]), rtol=1e-10, atol=1e-10)
+            d = torch.ones(2, HV, D, D, dtype=torch.float64)
+            assert ctx.finish_backward(d) is d
+        else:
+            ctx = cpmod.ContextParallel(dist.group.WORLD, pre_num_ranks=1, post_num_ranks=0)
+            lay, lo, hi = PackedLayout([2, 1]), 3, 6
+            junk = torch.cat([torch.full_like(h0[:1], 7.0), h0[2:3]])      # row 0 belongs to rank 0 and must be ignored
+            got = ctx.forward_carry(H[lo:hi].contiguous(), M[lo:hi].contiguous(), junk, lay, HV)
+            torch.testing.assert_close(got[0], fold(h0[1].clone(), [2]), rtol=1e-10, atol=1e-10)
+            torch.testing.assert_close(got[1], h0[2])
+            gb = ctx.backward_carry(Dl[lo:hi].contiguous(), M[lo:hi].contiguous(), dht[1:].clone(), lay, HV)
+            torch.testing.assert_close(gb, dht[1:])
+            d = ctx.finish_backward(torch.ones(2, HV, D, D, dtype=torch.float64))
+            assert float(d[0].abs().sum()) == 0 and float(d[1].min()) == 1
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_context_parallel_packed_batch_two_ranks():
+    mp.spawn(_packed_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+@pytest.mark.parametrize("cu,world", [([0, 300, 1200, 1400, 2048], 4), ([0, 2048], 4), ([0, 512, 1024, 2048], 4),
+                                      ([0, 5, 6, 100, 101, 128], 2), ([0, 64, 192], 3)])
+def test_partition_tokens_against_brute_force(cu, world):
+    """Every field of the equal-token split, derived token by token."""
+    from mogankda_b200.cp import partition_tokens
+    total = cu[-1]
+    part = total // world
+    seq_of = [next(i for i in range(len(cu) - 1) if cu[i] <= t < cu[i + 1]) for t in range(total)]
+    rank_of = [t // part for t in range(total)]
+    for r in range(world):
+        got = partition_tokens(torch.tensor(cu), world, r)
+        toks = [t for t in range(total) if rank_of[t] == r]
+        assert (got["rank_start"], got["rank_end"]) == (toks[0], toks[-1] + 1)
+        bounds = [0] + [i + 1 for i in range(part) if i == part - 1 or seq_of[toks[i]] != seq_of[toks[i + 1]]]
+        assert got["cu_seqlens"] == bounds
+        f, l = seq_of[toks[0]], seq_of[toks[-1]]
+        ranks_f = {rank_of[t] for t in range(cu[f], cu[f + 1])}
+        ranks_l = {rank_of[t] for t in range(cu[l], cu[l + 1])}
+        assert got["pre_num_ranks"] == r - min(ranks_f) and got["post_num_ranks"] == max(ranks_l) - r
+        assert got["is_first_rank"] == (min(ranks_f) == r) and got["is_last_rank"] == (max(ranks_l) == r)
+        assert got["pre_num_conv_tokens"] == toks[0] - cu[f]
+    with pytest.raises(AssertionError):
+        partition_tokens([0, 10, 60 * world + 1], world, 0)

@@ -88,3 +88,60 @@ def test_context_parallel_matches_global_oracle(world, T):
             check(f"{n}[{r}]", out[r][n], ref[n][:, a:b])
     check("ht", out[-1]["ht"], ref["ht"])
     check("dh0", out[0]["dh0"], ref["dh0"])
+
+
+def test_packed_batch_split_over_ranks_matches_global_oracle():
+    """Four sequences in 2048 tokens over four emulated ranks: one sequence spans three ranks, one rank holds the tail of a
+    sequence, a whole sequence and the head of the next.  Initial / final states and their gradients have one row per
+    local sequence; rows of sequences that started on an earlier rank are ignored / zero."""
+    from mogankda_b200.cp import build_cp_context, partition_tokens
+    cu, world = [0, 300, 1200, 1400, 2048], 4
+    lv, do, dht, opts, _ = make_inputs(B=1, T=cu[-1], HK=1, HV=2, cu=cu, dtype=torch.float32, gate="kimi", epi=None, seed=5)
+    kw = dict(gate_mode="kimi", beta_mode="sigmoid", beta_scale=2.0, use_qk_l2norm_in_kernel=True, output_final_state=True)
+    names = ("q", "k", "v", "g", "beta", "h0")
+    x = {n: t.double().clone().requires_grad_(True) for n, t in lv.items()}
+    o, ht = orc.chunked_delta_rule(x["q"], x["k"], x["v"], x["g"], x["beta"], A_log=x["A_log"], dt_bias=x["dt_bias"],
+                                   initial_state=x["h0"], cu_seqlens=opts["cu_seqlens"], **kw)
+    grads = torch.autograd.grad((o * do.double()).sum() + (ht * dht.double()).sum(), [x[n] for n in names])
+    ref = dict(o=o, ht=ht, **{"d" + n: g for n, g in zip(names, grads)})
+
+    parts = [partition_tokens(cu, world, r) for r in range(world)]
+    seqs = []                                          # global sequence ids of every rank's local sequences
+    for p in parts:
+        ids = [i for i in range(len(cu) - 1) if cu[i] < p["rank_end"] and cu[i + 1] > p["rank_start"]]
+        assert len(ids) == len(p["cu_seqlens"]) - 1
+        seqs.append(ids)
+    comm, out = ReplayComm(world), [None] * world
+    cu_dev = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    for replay in (False, True):
+        comm.replay = replay
+        for r, p in enumerate(parts):
+            a, b, ids = p["rank_start"], p["rank_end"], seqs[r]
+            ctx = build_cp_context(cu_dev, comm=comm.view(r), conv1d_kernel_size=4)
+            assert ctx.pre_num_ranks == p["pre_num_ranks"] and ctx.cu_seqlens.tolist() == p["cu_seqlens"]
+            assert ctx.conv_halo_tokens == min(3, p["pre_num_conv_tokens"])
+            loc = {n: t.clone().requires_grad_(True) for n, t in _slice(lv, a, b).items()}
+            h0 = lv["h0"][ids].clone()
+            if not p["is_first_rank"]:
+                h0[0] = 123.0                          # not this rank's input: must not matter
+            h0.requires_grad_(True)
+            o, ht = mk.chunk_kda(loc["q"], loc["k"], loc["v"], loc["g"], loc["beta"], A_log=loc["A_log"],
+                                 dt_bias=loc["dt_bias"], initial_state=h0, cp_context=ctx, **kw)
+            dht_loc = dht[ids].clone()
+            if not p["is_last_rank"]:
+                dht_loc[-1] = 0                        # the sequence ends on a later rank: its final state is not here
+            loss = (o.double() * do[:, a:b].double()).sum() + (ht.double() * dht_loc.double()).sum()
+            g = torch.autograd.grad(loss, [loc[n] for n in names[:5]] + [h0])
+            out[r] = dict(o=o.detach(), ht=ht.detach(), **{"d" + n: t for n, t in zip(names, g)})
+    for r, p in enumerate(parts):
+        a, b, ids = p["rank_start"], p["rank_end"], seqs[r]
+        check(f"o[{r}]", out[r]["o"], ref["o"][:, a:b])
+        for n in ("dq", "dk", "dv", "dg", "dbeta"):
+            check(f"{n}[{r}]", out[r][n], ref[n][:, a:b])
+        for j, s in enumerate(ids):
+            if cu[s + 1] <= b:                         # the sequence ends here: this rank reports its final state
+                check(f"ht[{r}][{j}]", out[r]["ht"][j], ref["ht"][s])
+            if cu[s] >= a:                             # it starts here: this rank owns the gradient of its initial state
+                check(f"dh0[{r}][{j}]", out[r]["dh0"][j], ref["dh0"][s])
+            else:
+                assert float(out[r]["dh0"][j].abs().max()) == 0.0

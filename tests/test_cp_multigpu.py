@@ -47,6 +47,26 @@ CHILD = textwrap.dedent("""
     if rank == world - 1:
         mx, mn = orc.rel_err(ht, ht_ref)
         assert mx <= 2e-3 and mn <= 2e-3, ("ht", mx, mn)
+
+    # the same tokens as a packed batch of three sequences, the middle one crossing the rank boundary
+    from mogankda_b200.cp import build_cp_context
+    cu = torch.tensor([0, 700, T - 1120, T], dtype=torch.int32, device="cuda")
+
+    def run_packed(a, b, ctx):
+        x = {n: t[:, a:b].contiguous().clone().requires_grad_(True) for n, t in lv.items() if n in names}
+        o, _ = mk.chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], A_log=lv["A_log"], dt_bias=lv["dt_bias"],
+                            cu_seqlens=None if ctx is not None else cu, cp_context=ctx, **dict(kw, output_final_state=False))
+        g = torch.autograd.grad((o.double() * do[:, a:b].double()).sum(), [x[n] for n in names])
+        return o.detach(), [t.detach() for t in g]
+
+    ctx = build_cp_context(cu, group=dist.group.WORLD)
+    assert ctx.pre_num_ranks == rank and ctx.num_seqs == 2
+    o, g = run_packed(rank * per, (rank + 1) * per, ctx)
+    o_ref, g_ref = run_packed(0, T, None)
+    for name, a, b in [("o", o, o_ref[:, sl])] + [("d" + n, x, y[:, sl]) for n, x, y in zip(names, g, g_ref)]:
+        mx, mn = orc.rel_err(a.float(), b.float())
+        worst = max(worst, mx)
+        assert mx <= 2e-3 + 2.0 ** -8 and mn <= 2e-3 + 1.6e-3, (rank, "packed " + name, mx, mn)
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank} ok worst {worst:.2e}")
