@@ -385,6 +385,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     __shared__ float sRed[4][CH];
     __shared__ float sDgl[DK];
     __shared__ float sCol[4][DK];
+    __shared__ float sRk[CH], sRq[CH];                 // L2-norm scales of the chunk's rows (0 past the end)
     __shared__ __align__(16) float sPart[16][DK];
     __shared__ uint64_t ldS, ldD;
     __shared__ __align__(16) float sGa[4][DK];         // cumsum rows of the four block anchors
@@ -411,6 +412,12 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     if (warp == 0) umma::tmem_alloc(&sh.tmem, 512);
     if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
     if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
+    if (tid >= CH && tid < 2 * CH) {
+        const int r = tid - CH;
+        const size_t tk = (size_t)(start + (r < len ? r : len - 1)) * HK + hk;
+        sRk[r] = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
+        sRq[r] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
+    }
     MKDA_TRACE_AT(5, 0);
 
     // ---- state phase: the two state tiles arrive by asynchronous copy; dO, dX and the Vd^T tile go through registers ----------------
@@ -459,8 +466,6 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         ldg8(p.k, QKDT, tk * 128 + k8 * 8, vk[n]);
         ldg8(p.q, QKDT, tk * 128 + k8 * 8, vq[n]);
         ldg8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vg[n]);
-        rk[n] = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
-        rq[n] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
     }
     {
         const int i = tid >> 3, k8 = tid & 7, ii = i < len ? i : len - 1;
@@ -532,6 +537,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
             *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8]) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
             *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8 + 4]) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
         }
+        rk[n] = sRk[r]; rq[n] = sRq[r];                // written before the first publish()
 #pragma unroll
         for (int e = 0; e < 8; ++e) { vk[n][e] *= rk[n]; vq[n][e] *= rq[n]; }
     }
@@ -601,15 +607,12 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     for (int r = 0; r < 16; ++r) {
         const int i = 16 * cg + r, ii = i < len ? i : len - 1;
         const size_t tk = (size_t)(start + ii) * HK + hk;
-        kq[r] = ld1(p.k, QKDT, tk * 128 + row) * (p.k_rstd ? p.k_rstd[tk] : 1.f);
-        qq[r] = ld1(p.q, QKDT, tk * 128 + row) * (p.q_rstd ? p.q_rstd[tk] : 1.f);
+        kq[r] = ld1(p.k, QKDT, tk * 128 + row) * (i < len ? sRk[i] : sRk[len - 1]);
+        qq[r] = ld1(p.q, QKDT, tk * 128 + row) * (i < len ? sRq[i] : sRq[len - 1]);
         gg[r] = p.g_c[((size_t)(start + ii) * HV + h) * 128 + row];
     }
 #pragma unroll
-    for (int I = 0; I < 4; ++I) {
-        const int a = 16 * I < len ? 16 * I : len - 1;
-        ga[I] = p.g_c[((size_t)(start + a) * HV + h) * 128 + row];
-    }
+    for (int I = 0; I < 4; ++I) ga[I] = sGa[I][row];   // anchor rows (the last valid row stands in for anchors past the end)
     const float gL = p.g_c[((size_t)(start + len - 1) * HV + h) * 128 + row];
     MKDA_TRACE_AT(5, 7);
     umma::mbar_wait(&sh.bar, 0);
