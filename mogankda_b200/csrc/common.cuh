@@ -40,6 +40,28 @@ __device__ __forceinline__ float4 ld4(const void* base, int dtype, size_t idx) {
     return r;
 }
 
+// 8 consecutive elements starting at element index `idx` (idx % 8 == 0): one 16-byte load for the 16-bit types
+__device__ __forceinline__ void ld8(const void* base, int dtype, size_t idx, float (&v)[8]) {
+    if (dtype == MKDA_F32) {
+        const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(base) + idx);
+        const float4 b = *reinterpret_cast<const float4*>(static_cast<const float*>(base) + idx + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        return;
+    }
+    const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + idx);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        if (dtype == MKDA_BF16) {
+            v[2 * e] = __uint_as_float(w[e] << 16);
+            v[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+        } else {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+            v[2 * e] = f.x; v[2 * e + 1] = f.y;
+        }
+    }
+}
+
 __device__ __forceinline__ float ld1(const void* base, int dtype, size_t idx) {
     if (dtype == MKDA_F32) return static_cast<const float*>(base)[idx];
     if (dtype == MKDA_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[idx]);

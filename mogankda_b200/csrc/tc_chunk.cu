@@ -45,8 +45,7 @@ __device__ __forceinline__ void stage_along_rows(uint8_t* hi, uint8_t* lo, int R
 }
 
 __device__ __forceinline__ void load8(const void* base, int dtype, size_t idx, float (&v)[8]) {   // idx % 8 == 0
-    const float4 a = ld4(base, dtype, idx), b = ld4(base, dtype, idx + 4);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    ld8(base, dtype, idx, v);
 }
 __device__ __forceinline__ void zero8(float (&v)[8]) {
 #pragma unroll

@@ -15,11 +15,6 @@ namespace mkda {
 
 using umma::store_split8;
 
-__device__ __forceinline__ void ld8(const void* base, int dtype, size_t idx, float (&v)[8]) {
-    const float4 a = ld4(base, dtype, idx), b = ld4(base, dtype, idx + 4);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-
 struct RecurShared {
     uint64_t bar;
     uint64_t ldw[2];       // arrival of the nw chunk tiles (bulk copies)
