@@ -134,7 +134,7 @@ __device__ __forceinline__ void invert_unit_lower(const float* __restrict__ sM, 
 }
 
 template <int DT>
-__global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd p) {
+__global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd p, const int ahead) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ IntraShared sh;
     __shared__ __align__(16) float sGa[5][DK];         // cumsum rows of the four block anchors, [4] = last valid row
@@ -172,6 +172,18 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         ldg8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vg[n]);
         rk[n] = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
         rq[n] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
+    }
+    if (tid < 256) {   // the rows of the CTA that is `ahead` places further in launch order are pulled into L2 meanwhile
+        const int nxt = blockIdx.y * gridDim.x + blockIdx.x + ahead, nc = nxt % (int)gridDim.x, nh = nxt / (int)gridDim.x;
+        const int kind = tid >> 6, r = tid & 63;
+        if (nh < HV && r < p.L.chunk_len[nc]) {
+            const size_t tok = (size_t)p.L.chunk_start[nc] + r, tv = tok * HV + nh, tk = tok * HK + nh / (HV / HK);
+            constexpr uint32_t RB = DT == MKDA_F32 ? 512 : 256;
+            if (kind == 0) umma::l2_prefetch(reinterpret_cast<const uint8_t*>(p.k) + tk * RB, RB);
+            if (kind == 1) umma::l2_prefetch(reinterpret_cast<const uint8_t*>(p.q) + tk * RB, RB);
+            if (kind == 2) umma::l2_prefetch(p.g_c + tv * 128, 512);
+            if (kind == 3) umma::l2_prefetch(reinterpret_cast<const uint8_t*>(p.v) + tv * RB, RB);
+        }
     }
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
@@ -741,7 +753,7 @@ template <int DT>
 static int launch_intra_fwd_tc_t(const MkdaIntraFwd* p, cudaStream_t stream) {
     auto kern = intra_fwd_tc_kernel<DT>;
     if (int e = ensure_smem((const void*)kern, INTRA_TC_SMEM, "intra_fwd")) return e;
-    kern<<<dim3(p->L.NC, p->L.HV), 512, INTRA_TC_SMEM, stream>>>(*p);
+    kern<<<dim3(p->L.NC, p->L.HV), 512, INTRA_TC_SMEM, stream>>>(*p, sm_count());
     return check_launch("intra_fwd");
 }
 int launch_intra_fwd_tc(const MkdaIntraFwd* p, cudaStream_t stream) {

@@ -203,6 +203,11 @@ __device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uin
 }
 __device__ __forceinline__ void bulk_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
+// Hint: bring `bytes` (multiple of 16) from the 16-byte aligned global address into L2; nothing waits for it.
+__device__ __forceinline__ void l2_prefetch(const void* gsrc, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(gsrc), "r"(bytes) : "memory");
+}
+
 // One thread: initialise `bar` and start the asynchronous fetch of state tile `idx` of the array `tiles` into `smem_dst`
 // (1024-byte aligned).  Waiters use mbar_wait(bar, 0) after a CTA-wide barrier that follows this call.
 __device__ __forceinline__ void fetch_state_tile(uint64_t* bar, void* smem_dst, const void* tiles, size_t idx) {
