@@ -47,13 +47,13 @@ __device__ __forceinline__ void gate_grad(int mode, float s, float E, float lb, 
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// forward: grid (NC, HV), 128 threads.  Warp w owns rows 16w..16w+15 of the chunk, lane l channels 4l..4l+3.
+// forward: grid NC x HV, heads fastest so that CTAs running together read one contiguous token range; 128 threads.  Warp w owns rows 16w..16w+15 of the chunk, lane l channels 4l..4l+3.
 // The chunk-local inclusive sum is (sum of the earlier warps' totals, in warp order) + (running sum inside the
 // warp): the association depends only on the row index, never on later rows.
 // ---------------------------------------------------------------------------------------------------------
 template <int XDT>
 __global__ void __launch_bounds__(128) gate_cumsum_fwd_kernel(const MkdaGateFwd p) {
-    const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV;
+    const int HV = p.L.HV, c = blockIdx.x / HV, h = blockIdx.x - c * HV;
     const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     __shared__ float4 tot[4][32];
@@ -105,11 +105,11 @@ __global__ void __launch_bounds__(128) gate_cumsum_fwd_kernel(const MkdaGateFwd 
 // ---------------------------------------------------------------------------------------------------------
 // backward: same tiling; suffix sums instead of prefix sums.
 // ---------------------------------------------------------------------------------------------------------
-// CTA (g, h) walks chunks g, g + gridDim.x, ... and keeps the parameter-gradient partials in registers, so the second
-// stage only has gridDim.x rows to add (fixed assignment and order: deterministic).
+// CTA (h, g), heads fastest, walks chunks g, g + gridDim.y, ... and keeps the parameter-gradient partials in registers, so the second
+// stage only has gridDim.y rows to add (fixed assignment and order: deterministic).
 template <int XDT>
 __global__ void __launch_bounds__(128) gate_bwd_kernel(const MkdaGateBwd p) {
-    const int h = blockIdx.y, HV = p.L.HV;
+    const int h = blockIdx.x, HV = p.L.HV;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     __shared__ float4 tot[4][32];
     __shared__ float4 red[2][4][32];
@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(128) gate_bwd_kernel(const MkdaGateBwd p) {
     float4 bias = splat4(0.f);
     if (p.dt_bias) bias = p.scalar_gate ? splat4(p.dt_bias[h]) : *reinterpret_cast<const float4*>(p.dt_bias + h * 128 + 4 * lane);
     float4 pa = splat4(0.f), pb = splat4(0.f);
-    for (int c = blockIdx.x; c < p.L.NC; c += gridDim.x) {
+    for (int c = blockIdx.y; c < p.L.NC; c += gridDim.y) {
         const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
         float4 vals[16];
 #pragma unroll
@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(128) gate_bwd_kernel(const MkdaGateBwd p) {
     if (warp == 0) {
         float4 sb = red[0][0][lane], sa = red[1][0][lane];
         for (int w = 1; w < 4; ++w) { sb = add4(sb, red[0][w][lane]); sa = add4(sa, red[1][w][lane]); }
-        const size_t ch = (size_t)blockIdx.x * HV + h;
+        const size_t ch = (size_t)blockIdx.y * HV + h;
         if (p.scalar_gate) {
             if (lane == 0) {
                 if (p.part_bias) p.part_bias[ch] = sb.x;
@@ -348,7 +348,7 @@ extern "C" int mkda_gate_cumsum_fwd(const MkdaGateFwd* p, void* stream) {
     if (p->mode != MKDA_GATE_PRECOMPUTED && !(p->lower_bound < 0.f)) return set_error(MKDA_ERR_ARG, "gate_cumsum_fwd: lower_bound must be < 0");
     if (p->beta_raw && !p->beta_out) return set_error(MKDA_ERR_ARG, "gate_cumsum_fwd: beta_out missing");
     if (p->L.NC == 0) return MKDA_OK;
-    const dim3 grid(p->L.NC, p->L.HV);
+    const int grid = p->L.NC * p->L.HV;
     switch (p->x_dtype) {
         case MKDA_F32: gate_cumsum_fwd_kernel<MKDA_F32><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
         case MKDA_BF16: gate_cumsum_fwd_kernel<MKDA_BF16><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
@@ -362,8 +362,8 @@ extern "C" int mkda_gate_bwd(const MkdaGateBwd* p, void* stream) {
     if (!p || !p->x || !p->dgp || !p->dx) return set_error(MKDA_ERR_ARG, "gate_bwd: null argument");
     if (p->L.NC == 0) return MKDA_OK;
     if (p->part_rows < 1) return set_error(MKDA_ERR_ARG, "gate_bwd: part_rows must be >= 1");
-    const dim3 grid(p->part_rows < p->L.NC ? p->part_rows : p->L.NC, p->L.HV);
-    if ((p->part_bias || p->part_alog) && (int)grid.x != p->part_rows)
+    const dim3 grid(p->L.HV, p->part_rows < p->L.NC ? p->part_rows : p->L.NC);
+    if ((p->part_bias || p->part_alog) && (int)grid.y != p->part_rows)
         return set_error(MKDA_ERR_ARG, "gate_bwd: part_rows must not exceed the number of chunks when partials are requested");
     switch (p->x_dtype) {
         case MKDA_F32: gate_bwd_kernel<MKDA_F32><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;

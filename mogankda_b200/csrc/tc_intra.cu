@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     uint8_t* sKB = base + OPND_BYTES;                  // kbar [tok][K index] hi + lo (32 KB), only copied out; under sM ...
     uint8_t* sQS = sKB + 32768;                        // scale q 2^g [tok][K index] hi + lo (32 KB), likewise
 
-    const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV, HK = p.L.HK;
+    const int HV = p.L.HV, HK = p.L.HK, c = blockIdx.x / HV, h = blockIdx.x - c * HV;     // heads fastest: CTAs that run together read neighbouring memory
     const int hk = h / (HV / HK);
     const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -174,9 +174,9 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         rq[n] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
     }
     if (tid < 256) {   // the rows of the CTA that is `ahead` places further in launch order are pulled into L2 meanwhile
-        const int nxt = blockIdx.y * gridDim.x + blockIdx.x + ahead, nc = nxt % (int)gridDim.x, nh = nxt / (int)gridDim.x;
+        const int nxt = blockIdx.x + ahead, nc = nxt / HV, nh = nxt - nc * HV;
         const int kind = tid >> 6, r = tid & 63;
-        if (nh < HV && r < p.L.chunk_len[nc]) {
+        if (nxt < (int)gridDim.x && r < p.L.chunk_len[nc]) {
             const size_t tok = (size_t)p.L.chunk_start[nc] + r, tv = tok * HV + nh, tk = tok * HK + nh / (HV / HK);
             constexpr uint32_t RB = DT == MKDA_F32 ? 512 : 256;
             if (kind == 0) umma::l2_prefetch(reinterpret_cast<const uint8_t*>(p.k) + tk * RB, RB);
@@ -414,7 +414,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
                                                        // rows 32 I + 16 + r = strictlower(dL)[16 I + r]; hi 16 KB + lo 16 KB
     uint8_t* sBd = sWD + 32768;                        // diag(beta) strictlower(dL) [i][j], hi 8 KB + lo 8 KB
 
-    const int c = blockIdx.x, h = blockIdx.y, HV = p.L.HV, HK = p.L.HK;
+    const int HV = p.L.HV, HK = p.L.HK, c = blockIdx.x / HV, h = blockIdx.x - c * HV;     // heads fastest: CTAs that run together read neighbouring memory
     const int hk = h / (HV / HK);
     const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -720,7 +720,7 @@ template <int QKDT, int DODT>
 static int launch_bwd_tail_tc_t(const MkdaBwdTail* p, cudaStream_t stream) {
     auto kern = bwd_tail_tc_kernel<QKDT, DODT>;
     if (int e = ensure_smem((const void*)kern, TAIL_SMEM, "bwd_tail")) return e;
-    kern<<<dim3(p->L.NC, p->L.HV), 512, TAIL_SMEM, stream>>>(*p);
+    kern<<<p->L.NC * p->L.HV, 512, TAIL_SMEM, stream>>>(*p);
     return check_launch("bwd_tail");
 }
 template <int QKDT>
@@ -753,7 +753,7 @@ template <int DT>
 static int launch_intra_fwd_tc_t(const MkdaIntraFwd* p, cudaStream_t stream) {
     auto kern = intra_fwd_tc_kernel<DT>;
     if (int e = ensure_smem((const void*)kern, INTRA_TC_SMEM, "intra_fwd")) return e;
-    kern<<<dim3(p->L.NC, p->L.HV), 512, INTRA_TC_SMEM, stream>>>(*p, sm_count());
+    kern<<<p->L.NC * p->L.HV, 512, INTRA_TC_SMEM, stream>>>(*p, sm_count());
     return check_launch("intra_fwd");
 }
 int launch_intra_fwd_tc(const MkdaIntraFwd* p, cudaStream_t stream) {
