@@ -134,8 +134,8 @@ KERNEL_BYTES = {
 # DRAM traffic per token per v-head measured by ncu on the 1B-shape case (profiles/counters_per_kernel_1b_shape.md),
 # bytes (dram read + write per launch / 131072 token-heads); it grows in proportion to tokens x heads.
 KERNEL_TRAFFIC = {
-    "mkda_intra_fwd": 3179, "mkda_recur_fwd": 2771, "mkda_out_fwd": 3351, "mkda_bwd_dh": 3612, "mkda_bwd_wy": 4592,
-    "mkda_bwd_tail": 6588, "mkda_gate_cumsum_fwd": 641, "mkda_epilogue_bwd": 1773, "mkda_qk_grad_finish": 653,
+    "mkda_intra_fwd": 3160, "mkda_recur_fwd": 2771, "mkda_out_fwd": 3351, "mkda_bwd_dh": 3612, "mkda_bwd_wy": 4588,
+    "mkda_bwd_tail": 6501, "mkda_gate_cumsum_fwd": 641, "mkda_epilogue_bwd": 1773, "mkda_qk_grad_finish": 653,
     "mkda_l2norm_rstd": 128,
 }
 
