@@ -65,12 +65,12 @@ class MkdaError(RuntimeError):
 _libs = {}
 
 
-def load(variant=""):
-    """Returns the loaded library (cached).  ``variant`` is the file-name suffix of an alternative build placed beside
-    the default one (development builds, e.g. with phase tracing compiled in)."""
+def load():
+    """Returns the loaded library (cached)."""
+    variant = ""
     if variant in _libs:
         return _libs[variant]
-    path = os.path.join(HERE, f"libmkda{variant}.so")
+    path = os.path.join(HERE, "libmkda.so")
     if not os.path.exists(path):
         raise MkdaError(f"{path} is missing: build it with `python -m mogankda_b200.build` (no CPU or library fallback exists)")
     lib = ctypes.CDLL(path)
@@ -88,16 +88,8 @@ def load(variant=""):
     return lib
 
 
-_variant = os.environ.get("MKDA_LIB_VARIANT", "")
-
-
-def set_variant(v):
-    global _variant
-    _variant = v
-
-
 def call(name, params, stream):
-    lib = load(_variant)
+    lib = load()
     rc = getattr(lib, name)(ctypes.byref(params), ctypes.c_void_p(stream))
     if rc != 0:
         raise MkdaError(f"{name} failed ({rc}): {lib.mkda_last_error().decode()}")
@@ -106,7 +98,7 @@ def call(name, params, stream):
 def device_status():
     """Synchronises the current device and returns 0 unless a bounded wait inside a tensor-core kernel ever expired (the
     kernels then ran on to their exit and their results are not to be trusted)."""
-    lib = load(_variant)
+    lib = load()
     lib.mkda_device_status.restype = ctypes.c_int
     lib.mkda_device_status.argtypes = []
     return int(lib.mkda_device_status())

@@ -42,7 +42,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
         A, Aqk, nw, u, kbar, qs, gl = ops.intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV)
         vf = cfg["state_v_first"]
         need_ht = cfg["output_final_state"]
-        ms = None
+        ms = m_first = None
         if lay.segmented or cp is not None:
             # pre-pass from zero: per-segment (state, transition); then the true entering state of every segment
             _, _, hs, ms = ops.recur_fwd(lay, nw, u, kbar, gl, HK, HV, store_h=False, store_vd=False,
@@ -51,7 +51,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
             if initial_state is not None:
                 carry = initial_state.transpose(-1, -2).contiguous() if vf else initial_state
             if cp is not None:
-                carry = cp.forward_carry(hs, ms, carry, lay, HV)
+                carry, m_first = cp.forward_carry(hs, ms, carry, lay, HV)
             s_in, _ = ops.state_combine(lay.grp_seg_off, lay.NG, lay.NS, HV, hs, ms, carry=carry, want_out=False)
             h, Vd, ht_seg, _ = ops.recur_fwd(lay, nw, u, kbar, gl, HK, HV, h0=s_in, state_v_first=False,
                                              want_ht=need_ht)
@@ -72,7 +72,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
                                  keep_raw=cfg["has_ep"] and need_bwd)
         if need_bwd:
             ctx.save_for_backward(q, k, v, x, beta, A_log, dt_bias, initial_state, ep_w, ep_gate, q_rstd, k_rstd,
-                                  g_c, beta_e, A, Aqk, nw, h, o_raw, ms, kbar, qs, gl, Vd)
+                                  g_c, beta_e, A, Aqk, nw, h, o_raw, ms, kbar, qs, gl, Vd, m_first)
         ctx.cfg, ctx.lay, ctx.dims = cfg, lay, (B, T, HK, HV)
         ctx.set_materialize_grads(False)
         return out.view(B, T, HV, 128), ht
@@ -81,7 +81,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
     @torch.autograd.function.once_differentiable
     def backward(ctx, dy, dht):
         (q, k, v, x, beta, A_log, dt_bias, initial_state, ep_w, ep_gate, q_rstd, k_rstd, g_c, beta_e, A, Aqk, nw, h,
-         o_raw, ms, kbar, qs, gl, Vd) = ctx.saved_tensors
+         o_raw, ms, kbar, qs, gl, Vd, m_first) = ctx.saved_tensors
         cfg, lay = ctx.cfg, ctx.lay
         B, T, HK, HV = ctx.dims
         scale, vf, cp = cfg["scale"], cfg["state_v_first"], cfg["cp_context"]
@@ -104,7 +104,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
             if dht is not None:
                 carry = dht.transpose(-1, -2).contiguous() if vf else dht
             if cp is not None:
-                carry = cp.backward_carry(dloc, ms, carry, lay, HV)
+                carry = cp.backward_carry(dloc, ms, carry, lay, HV, m_first)
             g_in, dh0 = ops.state_combine(lay.grp_seg_off, lay.NG, lay.NS, HV, dloc, ms, carry=carry, reverse=True,
                                           want_out=need_dh0 or cp is not None)
             ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, dht=g_in, want_dh0=False,

@@ -51,7 +51,6 @@ class ContextParallel:
             raise ValueError("pre_num_ranks / post_num_ranks reach outside the group")
         self.is_first_rank, self.is_last_rank = self.pre_num_ranks == 0, self.post_num_ranks == 0
         self.conv1d_kernel_size, self.pre_num_conv_tokens = conv1d_kernel_size, pre_num_conv_tokens
-        self._m_first = None
 
     @property
     def num_seqs(self):
@@ -89,7 +88,10 @@ class ContextParallel:
     def forward_carry(self, hs, ms, carry, lay, HV):
         """hs, ms [NS,HV,K,K]: per local segment (state reached from zero, transition).  ``carry`` = the caller's
         initial states of the local sequences ([NG,HV,K,V] or None); its first row is ignored unless the first local
-        sequence starts on this rank.  Returns the states entering the local sequences."""
+        sequence starts on this rank.  Returns ``(states entering the local sequences, m_first)``; ``m_first`` is the
+        transition of the first local sequence over this rank's slice, which the backward exchange sends to the earlier
+        ranks.  It belongs to this call, not to the context (one context serves every layer of a model): the caller keeps
+        it with its saved tensors and hands it to ``backward_carry``."""
         NG, K = lay.NG, ms.shape[-1]
         if carry is not None and not self.is_first_rank:
             carry = carry.clone()
@@ -97,22 +99,23 @@ class ContextParallel:
         _, h_all = ops.state_combine(lay.grp_seg_off, NG, lay.NS, HV, hs, ms, carry=carry, want_in=False)
         eye = torch.eye(K, dtype=ms.dtype, device=ms.device).expand(NG, HV, K, K).contiguous()
         _, m_all = ops.state_combine(lay.grp_seg_off, NG, lay.NS, HV, None, ms, carry=eye, want_in=False)
-        self._m_first = m_all[0]
+        m_first = m_all[0].clone()
         if self.world == 1:
-            return carry
+            return carry, m_first
         all_h, all_m = self._gather_pairs(h_all[NG - 1], m_all[NG - 1])       # every rank joins the collective
         if self.is_first_rank:
-            return carry
+            return carry, m_first
         lo = self.rank - self.pre_num_ranks
         s_in = self._fold(all_h[lo:self.rank], all_m[lo:self.rank], HV, False)
         out = carry if carry is not None else torch.zeros(NG, HV, K, K, dtype=ms.dtype, device=ms.device)
         out[0] = s_in[0]
-        return out
+        return out, m_first
 
-    def backward_carry(self, dloc, ms, carry, lay, HV):
+    def backward_carry(self, dloc, ms, carry, lay, HV, m_first):
         """dloc [NS,HV,K,K]: per local segment, gradient of the state entering it given zero from the right.
         ``carry`` = gradients of the local sequences' final states ([NG,HV,K,V] or None); its last row is ignored unless
-        the last local sequence ends on this rank.  Returns the gradients of the states leaving the local sequences."""
+        the last local sequence ends on this rank.  ``m_first``: what ``forward_carry`` returned for the same call.
+        Returns the gradients of the states leaving the local sequences."""
         NG, K = lay.NG, ms.shape[-1]
         if self.world == 1:
             return carry
@@ -120,7 +123,7 @@ class ContextParallel:
             carry = carry.clone()
             carry[NG - 1] = 0
         _, d_all = ops.state_combine(lay.grp_seg_off, NG, lay.NS, HV, dloc, ms, carry=carry, reverse=True, want_in=False)
-        all_d, all_m = self._gather_pairs(d_all[0], self._m_first)
+        all_d, all_m = self._gather_pairs(d_all[0], m_first)
         if self.is_last_rank:
             return carry
         lo, hi = self.rank + 1, self.rank + 1 + self.post_num_ranks

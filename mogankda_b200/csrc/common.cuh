@@ -206,36 +206,4 @@ __device__ __forceinline__ ChunkGeom chunk_geom(const int* chunk_start, const in
     return gmt;
 }
 
-// Stage a [CH][128] tile of a [TT, H, 128] tensor (head `h` of `H`) into shared memory as fp32 with leading
-// dimension LD; rows >= len are zero.  `rstd` (optional, [TT, H]) multiplies each row.  NTHR threads cooperate.
-template <int LD, int NTHR>
-__device__ __forceinline__ void stage_rows128(float* __restrict__ dst, const void* __restrict__ src, int dtype,
-                                              int start, int len, int H, int h, const float* __restrict__ rstd,
-                                              float mul = 1.f) {
-    for (int i = threadIdx.x; i < CH * 32; i += NTHR) {
-        const int r = i >> 5, c4 = (i & 31) * 4;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (r < len) {
-            const size_t row = (size_t)(start + r) * H + h;
-            v = ld4(src, dtype, row * 128 + c4);
-            float m = mul;
-            if (rstd) m *= rstd[row];
-            v.x *= m; v.y *= m; v.z *= m; v.w *= m;
-        }
-        *reinterpret_cast<float4*>(dst + r * LD + c4) = v;
-    }
-}
-
-// Stage a [CH][64] tile (rows of a [TT, H, 64] fp32 tensor).
-template <int LD, int NTHR>
-__device__ __forceinline__ void stage_rows64(float* __restrict__ dst, const float* __restrict__ src, int start,
-                                             int len, int H, int h) {
-    for (int i = threadIdx.x; i < CH * 16; i += NTHR) {
-        const int r = i >> 4, c4 = (i & 15) * 4;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (r < len) v = *reinterpret_cast<const float4*>(src + ((size_t)(start + r) * H + h) * 64 + c4);
-        *reinterpret_cast<float4*>(dst + r * LD + c4) = v;
-    }
-}
-
 }  // namespace mkda

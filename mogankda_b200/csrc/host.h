@@ -7,7 +7,8 @@
 namespace mkda {
 int set_error(int code, const char* msg);
 int check_launch(const char* what);
-// Raises the dynamic shared memory limit of `func` once per process; returns 0 or an error code.
+// Raises the dynamic shared memory limit of `func` (the attribute is set once per function and device; later calls
+// return at once); returns 0 or an error code.
 int ensure_smem(const void* func, int bytes, const char* what);
 // Number of SMs of the current device (cached per device).
 int sm_count();

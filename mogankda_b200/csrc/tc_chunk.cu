@@ -15,35 +15,6 @@ using umma::smem_u32;
 using umma::store_split8;
 using umma::tile_bytes;
 
-// Stage R x KT values with lanes walking along K (source contiguous along K): f(r, k8, v[8]) fills 8 consecutive k.
-template <int NTHR, class F>
-__device__ __forceinline__ void stage_along_k(uint8_t* hi, uint8_t* lo, int R, int KT, F f) {
-    const int nk8 = KT >> 3, total = R * nk8;
-    for (int i = threadIdx.x; i < total; i += 2 * NTHR) {
-        const int i2 = i + NTHR;
-        const int r = i / nk8, k8 = i - r * nk8, r2 = i2 / nk8, k82 = i2 - r2 * nk8;
-        float v[8], w[8];
-        f(r, k8, v);
-        if (i2 < total) f(r2, k82, w);
-        store_split8(hi, lo, R, r, k8, v);
-        if (i2 < total) store_split8(hi, lo, R, r2, k82, w);
-    }
-}
-// Stage with lanes walking along the rows (source contiguous along the row index: a transposed read).
-template <int NTHR, class F>
-__device__ __forceinline__ void stage_along_rows(uint8_t* hi, uint8_t* lo, int R, int KT, F f) {
-    const int nk8 = KT >> 3, total = R * nk8;
-    for (int i = threadIdx.x; i < total; i += 2 * NTHR) {
-        const int i2 = i + NTHR;
-        const int k8 = i / R, r = i - k8 * R, k82 = i2 / R, r2 = i2 - k82 * R;
-        float v[8], w[8];
-        f(r, k8, v);
-        if (i2 < total) f(r2, k82, w);
-        store_split8(hi, lo, R, r, k8, v);
-        if (i2 < total) store_split8(hi, lo, R, r2, k82, w);
-    }
-}
-
 __device__ __forceinline__ void load8(const void* base, int dtype, size_t idx, float (&v)[8]) {   // idx % 8 == 0
     ld8(base, dtype, idx, v);
 }
@@ -74,10 +45,6 @@ __device__ __forceinline__ void store_chunks(uint8_t* hi, uint8_t* lo, const flo
         const int r = ALONG_K ? i / nk8 : i % R, k8 = ALONG_K ? i % nk8 : i / R;
         store_split8(hi, lo, R, r, k8, v[n]);
     }
-}
-__device__ __forceinline__ void scale8(float (&v)[8], float m) {
-#pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] *= m;
 }
 
 struct TcShared {
@@ -209,9 +176,6 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
     tc_end(&sh, tmem, 64);
 }
 
-#ifdef MKDA_TRACE
-extern "C" int mkda_trace_read_chunk(long long* out) { return cudaMemcpyFromSymbol(out, umma::g_trace, sizeof(long long) * 8 * 24) == cudaSuccess ? 0 : -1; }
-#endif
 int tc_chunk_status(unsigned int* out) {
     return cudaMemcpyFromSymbol(out, umma::g_timeout_flag, sizeof(unsigned int)) == cudaSuccess ? 0 : -1;
 }
@@ -240,15 +204,6 @@ int launch_out_fwd_tc(const MkdaOutFwd* p, cudaStream_t stream) {
     }
     return set_error(MKDA_ERR_ARG, "out_fwd: unsupported dtype");
 }
-
-}  // namespace mkda
-
-namespace mkda {
-
-
-}  // namespace mkda
-
-namespace mkda {
 
 // reconstruct 8 fp32 values from the hi / lo tiles at (row r, chunk k8)
 __device__ __forceinline__ void load_tile8(const uint8_t* hi, const uint8_t* lo, int R, int r, int k8, float (&v)[8]) {
@@ -285,7 +240,6 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     __shared__ TcShared sh;
     __shared__ float sBeta[CH];
     __shared__ float sRed[2][CH];
-    MKDA_TRACE_AT(1, 0);
     uint8_t* base = tc_begin(smem_raw, &sh, 512);
     uint8_t* sSh = base;                      // S [kidx][v]; later [dO; dVd] [tok][v]
     uint8_t* sSl = sSh + 32768;
@@ -343,7 +297,6 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
             const int t = cg * 16 + j, tt = t < len ? t : len - 1;
             vv[j] = ld1(p.v, KVDT, ((size_t)(start + tt) * HV + h) * 128 + row);
         }
-        MKDA_TRACE_AT(1, 1);
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
             const int i = tid + n * 512, r = i >> 4;
@@ -354,7 +307,6 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
         }
         store_chunks<2, 512, true>(sKh, sKl, vK, 64, 128);
     }
-    MKDA_TRACE_AT(1, 2);
     const uint32_t tmem = tc_operands_ready(&sh);
     if (umma::mma_issuer()) {
         umma::mbar_wait(&ldbar, 0);                        // the state tile has landed
@@ -368,11 +320,9 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
 #pragma unroll
         for (int j = 0; j < 16; ++j)
             if (cg * 16 + j >= len) vv[j] = 0.f;
-        MKDA_TRACE_AT(1, 3);
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;
         umma::mbar_wait(&ldbar, 0);                            // long complete: makes the A tile visible to every reader below
         umma::fence_after_sync();
-        MKDA_TRACE_AT(1, 4);
         float d[16], x0[8], x1[8];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, cg * 16), d);
 #pragma unroll
@@ -381,7 +331,6 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
         store_split8(sXh, sXl, 128, row, 2 * cg + 1, x1);
         store_chunks<4, 512, true>(sSh, sSl, vT, 128, 128);      // S is dead: the region now holds [dO; dVd]
     }
-    MKDA_TRACE_AT(1, 5);
     tc_operands_ready(&sh);
     if (umma::mma_issuer()) {   // Vd^T is the forward pass's tile (the barrier it came on was awaited before G1): G4 and G3 go together
         umma::gemm(tmem + 256, umma::opnd_mn(sSh, sSl, 128, 64), umma::opnd_mn(sAh, sAl, 64), 128, 64, 64, 0u);
@@ -390,7 +339,6 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     }
     umma::mbar_wait(&sh.bar, phase); phase ^= 1;
     umma::fence_after_sync();
-    MKDA_TRACE_AT(1, 6);
     {
         float dw[16];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 256 + cg * 16), dw);
@@ -400,7 +348,6 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
             if (t < len) p.dX[((size_t)(start + t) * HV + h) * 128 + row] = sBeta[t] * dw[j];
         }
     }
-    MKDA_TRACE_AT(1, 8);
     if (q < 2) {                                   // rows i = row: dAqk = lower(dO Vd^T)
         float d[16];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + cg * 16), d);
@@ -439,7 +386,6 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
         store_split8(sKh, sKl, 128, i, 2 * cg, a0);
         store_split8(sKh, sKl, 128, i, 2 * cg + 1, a1);
     }
-    MKDA_TRACE_AT(1, 9);
     tc_operands_ready(&sh);
     if (tid < len) p.dbeta_w[(size_t)(start + tid) * HV + h] = sRed[0][tid] + sRed[1][tid];
     if (umma::mma_issuer()) {
@@ -448,7 +394,6 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     }
     umma::mbar_wait(&sh.bar, phase); phase ^= 1;
     umma::fence_after_sync();
-    MKDA_TRACE_AT(1, 10);
     if (q < 2) {
         float y[16], a0[8], a1[8];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 320 + cg * 16), y);
@@ -464,7 +409,6 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
     }
     umma::mbar_wait(&sh.bar, phase); phase ^= 1;
     umma::fence_after_sync();
-    MKDA_TRACE_AT(1, 11);
     if (q < 2) {
         float z[16];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 384 + cg * 16), z);      // warp-collective: never under a per-lane condition
@@ -476,9 +420,7 @@ __global__ void __launch_bounds__(512, 1) bwd_wy_tc_kernel(const MkdaBwdWy p) {
                                                               cg * 16 + j + 2 < row ? -z[j + 2] : 0.f, cg * 16 + j + 3 < row ? -z[j + 3] : 0.f);
         }
     }
-    MKDA_TRACE_AT(1, 12);
     tc_end(&sh, tmem, 512);
-    MKDA_TRACE_AT(1, 13);
 }
 
 template <int KVDT, int DODT>

@@ -156,7 +156,6 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
 
-    MKDA_TRACE_AT(3, 0);
     if (warp == 0) umma::tmem_alloc(&sh.tmem, 256);
     if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
     if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
@@ -199,12 +198,10 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
 #pragma unroll
         for (int e = 0; e < 8; ++e) { vk[n][e] *= rk[n]; vq[n][e] *= rq[n]; }
     }
-    MKDA_TRACE_AT(3, 1);
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem = sh.tmem;
-    MKDA_TRACE_AT(3, 2);
     // ---- operands ---------------------------------------------------------------------------------------------------
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
@@ -226,7 +223,6 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
             store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
         }
     }
-    MKDA_TRACE_AT(3, 3);
     publish();
     if (umma::mma_issuer()) {
 #pragma unroll
@@ -272,10 +268,8 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         umma::bulk_store(reinterpret_cast<uint8_t*>(p.kbar) + it * umma::CHUNK_TILE_BYTES, sKB, umma::CHUNK_TILE_BYTES);
         umma::bulk_store(reinterpret_cast<uint8_t*>(p.qs) + it * umma::CHUNK_TILE_BYTES, sQS, umma::CHUNK_TILE_BYTES);
     }
-    MKDA_TRACE_AT(3, 4);
     umma::mbar_wait(&sh.bar, 0);
     umma::fence_after_sync();
-    MKDA_TRACE_AT(3, 5);
     // phase-3 operands over the dead phase-1 tiles: beta k 2^g and beta v (rows past the end are zero)
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
@@ -303,9 +297,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         }
     }
     __syncthreads();
-    MKDA_TRACE_AT(3, 6);
     invert_unit_lower(sM, sInv, sh);
-    MKDA_TRACE_AT(3, 7);
     {   // A as the B operand of phase 3; A and Aqk also leave as ready-made [row][column] operand tiles (rows past the end:
         // identity rows of A, zero rows of Aqk)
         const int r = tid >> 3, k8 = tid & 7;
@@ -327,10 +319,8 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         umma::gemm(tmem + 192, umma::opnd_mn(sBv, sBv + 16384, 64), bA, 128, 64, 64, 0u);
         umma::commit(&sh.bar);
     }
-    MKDA_TRACE_AT(3, 8);
     umma::mbar_wait(&sh.bar, 1);
     umma::fence_after_sync();
-    MKDA_TRACE_AT(3, 9);
     {   // nw^T [K index][tok] leaves as a ready-made chunk tile (the serial kernels fetch it with one bulk copy; token
         // columns past the end are exact zeros: beta is 0 there)
         float a[16], n0[8], n1[8];
@@ -354,7 +344,6 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
             if (i < len) p.u[((size_t)(start + i) * HV + h) * 128 + row] = b[j];
         }
     }
-    MKDA_TRACE_AT(3, 10);
     if (tid == 0) umma::bulk_store_wait_read();
     umma::fence_before_sync();
     __syncthreads();
@@ -429,7 +418,6 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         sRk[r] = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
         sRq[r] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
     }
-    MKDA_TRACE_AT(5, 0);
 
     // ---- state phase: the two state tiles arrive by asynchronous copy; dO, dX and the Vd^T tile go through registers ----------------
     if (tid == 0) {
@@ -467,7 +455,6 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
             }
         }
     }
-    MKDA_TRACE_AT(5, 1);
     // intra phase inputs (k, q, g and the two 64 x 64 weights) are requested now and consumed after the state products
     float vk[2][8], vq[2][8], vg[2][8], rk[2], rq[2], wa[8], wl[8];
 #pragma unroll
@@ -486,7 +473,6 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     }
     publish();
     const uint32_t tmem = sh.tmem;
-    MKDA_TRACE_AT(5, 2);
     if (umma::mma_issuer()) {
         umma::mbar_wait(&ldS, 0);
         const umma::Opnd aS = umma::opnd_mn(sSh, sSl, 128);          // A(m = K index, k = v) of the [v][K index] tile
@@ -525,7 +511,6 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         }
     }
     umma::mbar_wait(&sh.bar, 0);                       // S dO^T and S dX^T done: the dO tile can be replaced by Vd
-    MKDA_TRACE_AT(5, 3);
     umma::fence_after_sync();
 #pragma unroll
     for (int n = 0; n < 4; ++n) reinterpret_cast<uint4*>(sOh)[tid + n * 512] = vV[n];     // hi 16 KB, then lo 16 KB
@@ -534,7 +519,6 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         umma::gemm(tmem + 128, umma::opnd_mn(sTh, sTl, 128), umma::opnd_mn(sOh, sOh + 16384, 128), 128, 64, 128, 0u);
         umma::commit(&sh.bar);
     }
-    MKDA_TRACE_AT(5, 4);
     if (tid < DK) {
         float t = 0.f;
 #pragma unroll
@@ -554,7 +538,6 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     }
     __syncthreads();
     umma::mbar_wait(&sh.bar, 1);                       // dS' Vd^T done: every state tile is dead
-    MKDA_TRACE_AT(5, 5);
     umma::fence_after_sync();
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
@@ -576,7 +559,6 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
             store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
         }
     }
-    MKDA_TRACE_AT(5, 6);
     {
         const int i = tid >> 3, k8 = tid & 7;
         const float bt = sh.beta[i];
@@ -594,9 +576,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + 16 + (i & 15), k8, d8);
         store_split8(sBd, sBd + 8192, 64, i, k8, b8);
     }
-    MKDA_TRACE_AT(5, 12);
     publish();
-    MKDA_TRACE_AT(5, 13);
     if (umma::mma_issuer()) {
 #pragma unroll
         for (int I = 0; I < 4; ++I) {
@@ -611,7 +591,6 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         }
         umma::commit(&sh.bar);
     }
-    MKDA_TRACE_AT(5, 14);
     // epilogue inputs for (channel `row`, rows 16 cg .. 16 cg + 15) are fetched while the products run
     float kq[16], qq[16], gg[16], ga[4];
 #pragma unroll
@@ -625,9 +604,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
 #pragma unroll
     for (int I = 0; I < 4; ++I) ga[I] = sGa[I][row];   // anchor rows (the last valid row stands in for anchors past the end)
     const float gL = p.g_c[((size_t)(start + len - 1) * HV + h) * 128 + row];
-    MKDA_TRACE_AT(5, 7);
     umma::mbar_wait(&sh.bar, 0);
-    MKDA_TRACE_AT(5, 8);
     umma::fence_after_sync();
 
     {   // column sum of the inter-chunk k gradient for the last row's gate term
@@ -641,7 +618,6 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     }
     __syncthreads();
     const float extra = ((sCol[0][row] + sCol[1][row]) + (sCol[2][row] + sCol[3][row])) + ex2f_(gL) * sDgl[row];
-    MKDA_TRACE_AT(5, 9);
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
         const int c0 = 16 * cg + 8 * hf;
@@ -699,7 +675,6 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         bsv[0] += __shfl_xor_sync(0xffffffffu, bsv[0], 1);
         if ((lane & 3) == 0) sRed[q][c0 + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = bsv[0];
     }
-    MKDA_TRACE_AT(5, 10);
     __syncthreads();
     if (tid < len) {
         const size_t th = (size_t)(start + tid) * HV + h;
@@ -713,7 +688,6 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     umma::fence_before_sync();
     __syncthreads();
     if (warp == 0) umma::tmem_dealloc(tmem, 512);
-    MKDA_TRACE_AT(5, 11);
 }
 
 template <int QKDT, int DODT>
@@ -742,9 +716,6 @@ int launch_bwd_tail_tc(const MkdaBwdTail* p, cudaStream_t stream) {
     return set_error(MKDA_ERR_ARG, "bwd_tail: unsupported dtype");
 }
 
-#ifdef MKDA_TRACE
-extern "C" int mkda_trace_read_intra(long long* out) { return cudaMemcpyFromSymbol(out, umma::g_trace, sizeof(long long) * 8 * 24) == cudaSuccess ? 0 : -1; }
-#endif
 int tc_intra_status(unsigned int* out) {
     return cudaMemcpyFromSymbol(out, umma::g_timeout_flag, sizeof(unsigned int)) == cudaSuccess ? 0 : -1;
 }

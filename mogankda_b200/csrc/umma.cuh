@@ -17,16 +17,6 @@ namespace umma {
 
 static __device__ unsigned int g_timeout_flag;      // one per translation unit, read back by mkda_device_status()
 
-// Optional phase tracing (development builds with -DMKDA_TRACE): CTA (200, 3) records clock64() at numbered points.
-#ifdef MKDA_TRACE
-static __device__ long long g_trace[8][24];
-#define MKDA_TRACE_AT(k, i) do { if (blockIdx.x == 200 && blockIdx.y == 3 && threadIdx.x == 0) ::mkda::umma::g_trace[k][i] = clock64(); } while (0)
-#define MKDA_TRACE_SERIAL(k, i) do { if (blockIdx.z == 40 && blockIdx.y == 3 && blockIdx.x == 0 && threadIdx.x == 0) ::mkda::umma::g_trace[k][i] = clock64(); } while (0)
-#else
-#define MKDA_TRACE_AT(k, i) do {} while (0)
-#define MKDA_TRACE_SERIAL(k, i) do {} while (0)
-#endif
-
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 // ---- operand tiles -------------------------------------------------------------------------------------------

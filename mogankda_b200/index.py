@@ -70,10 +70,15 @@ def build_tables(B, T, cu, seg_chunks=0):
                 covers_all=covered == B * T)
 
 
-SM_COUNT = 148               # B200
+def _sm_count(device=None):
+    """SMs of the device the kernels will run on (the library asks the runtime in the same way for its persistent
+    grids); 148 (B200) when no device is visible, so that the host logic stays testable on CPU."""
+    if torch.cuda.is_available():
+        return torch.cuda.get_device_properties(device if device is not None else torch.cuda.current_device()).multi_processor_count
+    return 148
 
 
-def wants_segments(chunks_per_seq, HV, seg_chunks):
+def wants_segments(chunks_per_seq, HV, seg_chunks, sm_count=None):
     """Segment-parallelism chooser: should sequences be cut into segments of ``seg_chunks`` chunks?
 
     The serial kernels run one CTA per (sequence or segment, v-head), one chunk step after another.  Uncut, their time is
@@ -86,11 +91,15 @@ def wants_segments(chunks_per_seq, HV, seg_chunks):
     longest = max(chunks_per_seq, default=0)
     if seg_chunks <= 0 or longest <= seg_chunks:
         return False
-    even_share = sum(chunks_per_seq) * HV / SM_COUNT
+    even_share = sum(chunks_per_seq) * HV / (sm_count or _sm_count())
     return longest > 2.5 * even_share
 
 
-_cache = {}
+# Entries: (static key, the cu_seqlens tensor itself, its version counter, layout).  The entry keeps the tensor alive
+# and is matched by identity, as the reference's ``tensor_cache`` does (mogan_kda/utils/index.py:33-85): a fresh
+# ``cu_seqlens`` that happens to land at the address of a freed one (the caching allocator hands blocks back in that
+# way every step) can never hit an old entry, and an in-place edit changes the version.
+_cache = []
 _CACHE_MAX = 16
 
 
@@ -98,15 +107,17 @@ def get_layout(B, T, cu_seqlens, device, seg_chunks=0, auto_heads=0):
     """Device tables, cached on (shape, identity + version of ``cu_seqlens``, segment policy) like the reference's
     ``tensor_cache`` (mogan_kda/utils/index.py:19-90).  A cache miss reads ``cu_seqlens`` back to the host.
     ``auto_heads`` > 0 lets ``wants_segments`` decide, for that many v-heads, whether ``seg_chunks`` is applied."""
-    key = (B, T, str(device), seg_chunks, auto_heads,
-           None if cu_seqlens is None else (cu_seqlens.data_ptr(), cu_seqlens._version, tuple(cu_seqlens.shape)))
-    hit = _cache.get(key)
-    if hit is not None:
-        return hit
+    key = (B, T, str(device), seg_chunks, auto_heads)
+    ver = None if cu_seqlens is None else cu_seqlens._version
+    for i, (k, ref, v, lay) in enumerate(_cache):
+        if k == key and ref is cu_seqlens and v == ver:
+            if i != len(_cache) - 1:
+                _cache.append(_cache.pop(i))          # most recently used last
+            return lay
     cu = None if cu_seqlens is None else [int(x) for x in cu_seqlens.tolist()]
     if auto_heads > 0:
         lens = [T] * B if cu is None else [e - s for s, e in zip(cu[:-1], cu[1:])]
-        if not wants_segments([-(-n // CHUNK) for n in lens], auto_heads, seg_chunks):
+        if not wants_segments([-(-n // CHUNK) for n in lens], auto_heads, seg_chunks, _sm_count(device) if str(device) != "cpu" else None):
             seg_chunks = 0
     tb = build_tables(B, T, cu, seg_chunks)
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)      # noqa: E731
@@ -116,6 +127,6 @@ def get_layout(B, T, cu_seqlens, device, seg_chunks=0, auto_heads=0):
                  seq_chunk_off=i32(tb["seq_chunk_off"]), seg_first=i32(tb["seg_first"]), seg_last=i32(tb["seg_last"]),
                  segmented=len(tb["seg_first"]) != tb["N"], covers_all=tb["covers_all"], host=tb)
     if len(_cache) >= _CACHE_MAX:
-        _cache.pop(next(iter(_cache)))
-    _cache[key] = lay
+        _cache.pop(0)
+    _cache.append((key, cu_seqlens, ver, lay))
     return lay

@@ -34,7 +34,7 @@ class FakeLayout:
         self.grp_seg_off = torch.tensor([0, ns], dtype=torch.int32)
 
 
-def _worker(rank, world, port, seg_counts, fail_rank):
+def _worker(rank, world, port, seg_counts):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -51,12 +51,16 @@ def _worker(rank, world, port, seg_counts, fail_rank):
         hi = lo + seg_counts[rank]
         ctx = cpmod.ContextParallel(dist.group.WORLD)
         lay = FakeLayout(seg_counts[rank])
-        got = ctx.forward_carry(H[lo:hi].contiguous(), M[lo:hi].contiguous(), h0 if rank == 0 else None, lay, HV)
+        got, m_first = ctx.forward_carry(H[lo:hi].contiguous(), M[lo:hi].contiguous(), h0 if rank == 0 else None, lay, HV)
+        # a second layer runs its forward pass on the SAME context before the first one's backward pass: the first
+        # layer's transition must come back from its own saved value, not from whatever the context saw last
+        ctx.forward_carry(H[lo:hi].flip(0).contiguous(), (M[lo:hi] * 0.5).contiguous(), None, lay, HV)
         X = h0[0].clone()
         for s in range(lo):
             X = M[s] @ X + H[s]
         torch.testing.assert_close(got[0], X, rtol=1e-10, atol=1e-10)
-        gotb = ctx.backward_carry(Dl[lo:hi].contiguous(), M[lo:hi].contiguous(), dht if rank == world - 1 else None, lay, HV)
+        gotb = ctx.backward_carry(Dl[lo:hi].contiguous(), M[lo:hi].contiguous(), dht if rank == world - 1 else None, lay, HV,
+                                  m_first)
         G = dht[0].clone()
         for s in reversed(range(hi, total)):
             G = M[s].transpose(-1, -2) @ G + Dl[s]
@@ -74,7 +78,7 @@ def _free_port():
 
 @pytest.mark.parametrize("seg_counts", [(3, 2), (1, 4)])
 def test_context_parallel_prefix_fold_two_ranks(seg_counts):
-    mp.spawn(_worker, args=(2, _free_port(), seg_counts, 1), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), seg_counts), nprocs=2, join=True)
 
 
 class PackedLayout:
@@ -103,9 +107,9 @@ def _packed_worker(rank, world, port):
         if rank == 0:
             ctx = cpmod.ContextParallel(dist.group.WORLD, pre_num_ranks=0, post_num_ranks=1)
             lay, lo, hi = PackedLayout([2, 1]), 0, 3
-            got = ctx.forward_carry(H[lo:hi].contiguous(), M[lo:hi].contiguous(), h0[:2].clone(), lay, HV)
+            got, mf = ctx.forward_carry(H[lo:hi].contiguous(), M[lo:hi].contiguous(), h0[:2].clone(), lay, HV)
             torch.testing.assert_close(got, h0[:2])
-            gb = ctx.backward_carry(Dl[lo:hi].contiguous(), M[lo:hi].contiguous(), dht[:2].clone(), lay, HV)
+            gb = ctx.backward_carry(Dl[lo:hi].contiguous(), M[lo:hi].contiguous(), dht[:2].clone(), lay, HV, mf)
             torch.testing.assert_close(gb[0], dht[0])
             torch.testing.assert_close(gb[1], foldb(dht[1].clone(), [3, 4]), rtol=1e-10, atol=1e-10)
             d = torch.ones(2, HV, D, D, dtype=torch.float64)
@@ -114,10 +118,10 @@ def _packed_worker(rank, world, port):
             ctx = cpmod.ContextParallel(dist.group.WORLD, pre_num_ranks=1, post_num_ranks=0)
             lay, lo, hi = PackedLayout([2, 1]), 3, 6
             junk = torch.cat([torch.full_like(h0[:1], 7.0), h0[2:3]])      # row 0 belongs to rank 0 and must be ignored
-            got = ctx.forward_carry(H[lo:hi].contiguous(), M[lo:hi].contiguous(), junk, lay, HV)
+            got, mf = ctx.forward_carry(H[lo:hi].contiguous(), M[lo:hi].contiguous(), junk, lay, HV)
             torch.testing.assert_close(got[0], fold(h0[1].clone(), [2]), rtol=1e-10, atol=1e-10)
             torch.testing.assert_close(got[1], h0[2])
-            gb = ctx.backward_carry(Dl[lo:hi].contiguous(), M[lo:hi].contiguous(), dht[1:].clone(), lay, HV)
+            gb = ctx.backward_carry(Dl[lo:hi].contiguous(), M[lo:hi].contiguous(), dht[1:].clone(), lay, HV, mf)
             torch.testing.assert_close(gb, dht[1:])
             d = ctx.finish_backward(torch.ones(2, HV, D, D, dtype=torch.float64))
             assert float(d[0].abs().sum()) == 0 and float(d[1].min()) == 1
@@ -153,3 +157,60 @@ def test_partition_tokens_against_brute_force(cu, world):
         assert got["pre_num_conv_tokens"] == toks[0] - cu[f]
     with pytest.raises(AssertionError):
         partition_tokens([0, 10, 60 * world + 1], world, 0)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# failure detection, injected on the host: no GPU is involved, nothing faults or hangs
+# ---------------------------------------------------------------------------------------------------------------
+def _failing_worker(rank, world, port, result):
+    """Rank 1 raises before the all-gather.  Rank 0 must come out of the collective with an exception within the
+    group's short timeout instead of waiting for ever; it reports what it saw through ``result``."""
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    from mogankda_b200 import cp as cpmod, ops
+    ops.state_combine = combine_ref
+    ctx = cpmod.ContextParallel(dist.group.WORLD)
+    if rank == 1:
+        os._exit(0)                      # the rank is gone before it joins the collective (no destroy, no barrier)
+    g = torch.Generator().manual_seed(3)
+    H = torch.randn(2, HV, D, D, generator=g, dtype=torch.float64)
+    M = torch.randn(2, HV, D, D, generator=g, dtype=torch.float64)
+    try:
+        ctx.forward_carry(H, M, None, FakeLayout(2), HV)
+        result.put("no error")
+    except Exception as e:               # noqa: BLE001  (gloo reports a lost peer as RuntimeError / DistBackendError)
+        result.put(type(e).__name__)
+
+
+def test_a_rank_that_leaves_before_the_exchange_gives_its_peer_an_error_not_a_hang():
+    ctxmp = mp.get_context("spawn")
+    result = ctxmp.Queue()
+    procs = [ctxmp.Process(target=_failing_worker, args=(r, 2, port, result)) for port in [_free_port()] for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=90)
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.kill()
+    assert not alive, "a rank hung in the collective after its peer had left"
+    assert result.get(timeout=5) != "no error"
+
+
+def test_cp_argument_errors_follow_the_reference():
+    """Token count not divisible by the world size, ranks outside the group, B != 1: the documented errors
+    (mogan_kda/ops/gated_delta_rule/chunk/cp/context.py:202-205)."""
+    from mogankda_b200 import cp as cpmod
+
+    class Comm:
+        rank, world = 1, 2
+
+    with pytest.raises(AssertionError, match="divisible by world_size"):
+        cpmod.partition_tokens([0, 100, 129], 2, 0)
+    with pytest.raises(ValueError, match="outside the group"):
+        cpmod.ContextParallel(comm=Comm(), pre_num_ranks=2)
+    with pytest.raises(ValueError, match="outside the group"):
+        cpmod.ContextParallel(comm=Comm(), post_num_ranks=1)
+    with pytest.raises(AssertionError, match="divisible by world_size"):
+        cpmod.build_cp_context(torch.tensor([0, 7, 13]), comm=Comm())

@@ -145,3 +145,41 @@ def test_packed_batch_split_over_ranks_matches_global_oracle():
                 check(f"dh0[{r}][{j}]", out[r]["dh0"][j], ref["dh0"][s])
             else:
                 assert float(out[r]["dh0"][j].abs().max()) == 0.0
+
+
+def test_two_layers_share_one_context():
+    """A model passes ONE context to every layer, and all forward passes run before the first backward pass.  Each
+    layer's backward exchange must use that layer's own transition, so two different problems pushed through the same
+    context object, then differentiated together, must each match their own global oracle."""
+    world, T = 2, 640
+    probs = [_problem(T, seed=41), _problem(T, seed=43)]
+    names = ("q", "k", "v", "g", "beta")
+    kw = dict(gate_mode="kimi", beta_mode="sigmoid", beta_scale=2.0, use_qk_l2norm_in_kernel=True)
+    refs = []
+    for lv, do, _, _ in probs:
+        x = {n: t.double().clone().requires_grad_(True) for n, t in lv.items()}
+        o, _ = orc.chunked_delta_rule(x["q"], x["k"], x["v"], x["g"], x["beta"], A_log=x["A_log"], dt_bias=x["dt_bias"], **kw)
+        grads = torch.autograd.grad((o * do.double()).sum(), [x[n] for n in names])
+        refs.append(dict(o=o, **{"d" + n: g for n, g in zip(names, grads)}))
+    per = T // world
+    comm, out = ReplayComm(world), {}
+    for replay in (False, True):
+        comm.replay = replay
+        for r in range(world):
+            a, b = r * per, (r + 1) * per
+            ctx = ContextParallel(comm=comm.view(r))            # one context for both layers of this rank
+            xs, loss = [], 0.0
+            for lv, do, _, _ in probs:
+                x = {n: t.clone().requires_grad_(True) for n, t in _slice(lv, a, b).items()}
+                o, _ = mk.chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], A_log=x["A_log"], dt_bias=x["dt_bias"],
+                                    cp_context=ctx, **kw)
+                loss = loss + (o.double() * do[:, a:b].double()).sum()
+                xs.append((x, o))
+            grads = torch.autograd.grad(loss, [x[n] for x, _ in xs for n in names])
+            for i, (x, o) in enumerate(xs):
+                out[(r, i)] = dict(o=o.detach(), **{"d" + n: grads[i * len(names) + j] for j, n in enumerate(names)})
+    for r in range(world):
+        a, b = r * per, (r + 1) * per
+        for i in range(2):
+            for n in ("o", "dq", "dk", "dv", "dg", "dbeta"):
+                check(f"layer {i} {n}[{r}]", out[(r, i)][n], refs[i][n][:, a:b])

@@ -51,15 +51,35 @@ def test_bad_cu_seqlens():
 def test_segment_chooser():
     from mogankda_b200.index import wants_segments
     # nothing longer than a segment: never cut
-    assert not wants_segments([8, 20, 32], 32, 32)
+    assert not wants_segments([8, 20, 32], 32, 32, sm_count=148)
     # one long sequence, few heads: the GPU cannot be filled without cutting
-    assert wants_segments([1024], 32, 32)
+    assert wants_segments([1024], 32, 32, sm_count=148)
     # many documents of similar length fill the GPU on their own
-    assert not wants_segments([40] * 100, 32, 32)
+    assert not wants_segments([40] * 100, 32, 32, sm_count=148)
     # a packed batch dominated by one document: its chain is far longer than the even share
-    assert wants_segments([940] + [4] * 34, 32, 32)
+    assert wants_segments([940] + [4] * 34, 32, 32, sm_count=148)
     # the same long document among enough other work is left alone
-    assert not wants_segments([100] + [30] * 300, 32, 32)
-    assert not wants_segments([], 32, 32) and not wants_segments([1000], 32, 0)
+    assert not wants_segments([100] + [30] * 300, 32, 32, sm_count=148)
+    assert not wants_segments([], 32, 32, sm_count=148) and not wants_segments([1000], 32, 0, sm_count=148)
     # four 256-chunk sequences x 16 heads leave SMs idle, but cutting would cost more than it spreads
-    assert not wants_segments([256] * 4, 16, 32)
+    assert not wants_segments([256] * 4, 16, 32, sm_count=148)
+
+
+def test_layout_cache_is_keyed_on_tensor_identity_not_on_its_address():
+    """A training loop builds a fresh ``cu_seqlens`` every step and the allocator usually hands back the block of the one
+    just freed: same address, same shape, version 0, different boundaries.  The cached tables must not be reused."""
+    import torch
+    from mogankda_b200 import index
+    a = torch.tensor([0, 100, 256], dtype=torch.int32)
+    la = index.get_layout(1, 256, a, "cpu")
+    assert index.get_layout(1, 256, a, "cpu") is la                    # same tensor object: a hit
+    ptr = a.data_ptr()
+    del a
+    fresh = [torch.tensor([0, 30, 256], dtype=torch.int32) for _ in range(4)]      # one of them may reuse the block
+    for b in fresh:
+        lb = index.get_layout(1, 256, b, "cpu")
+        assert lb is not la and lb.chunk_len.tolist()[0] == 30
+    assert any(e[1] is not None and e[1].data_ptr() == ptr for e in index._cache)  # the entry keeps its tensor alive
+    c = fresh[0]
+    c[1] = 64                                                           # in-place edit: the version counter moves
+    assert index.get_layout(1, 256, c, "cpu").chunk_len.tolist()[0] == 64
