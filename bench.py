@@ -121,21 +121,22 @@ KERNEL_FLOPS = {                      # per token per v-head
     "mkda_recur_fwd": 2 * F_KV,                       # nw S, kbar^T Vd
     "mkda_out_fwd": F_KV + F_CK,                      # q~ S, Aqk Vd
     "mkda_bwd_dh": F_CK + 3 * F_KV,                   # Aqk^T dO, kbar dS', q~^T dO, nw^T dVd
-    "mkda_bwd_wy": F_KV + 3 * F_CK + 2 * F_CC,        # k~ S, dO Vd^T, A^T dVd, dVd W^T, two C^3 products (Vd comes from the forward pass)
-    "mkda_bwd_tail": 3 * F_KV + 4 * F_CK,             # dO S^T, dX S^T, Vd dS'^T; row / column terms through Gamma and Q K^T
+    # k~ S, dO Vd^T, A^T dVd, dVd W^T, two C^3 products (Vd comes from the forward pass); dO S^T, dX S^T, Vd dS'^T; row / column
+    # terms through Gamma and Q K^T
+    "mkda_bwd_chunk": 4 * F_KV + 7 * F_CK + 2 * F_CC,
 }
 # Algorithmic bytes per token per v-head: each kernel's own tensor I/O at the default workload (bf16 q/k/v/gate,
 # fp32 intermediates, HV = 2 HK), every operand counted once.
 KERNEL_BYTES = {
     "mkda_gate_cumsum_fwd": 1024, "mkda_l2norm_rstd": 128, "mkda_intra_fwd": 3592, "mkda_recur_fwd": 3080,
-    "mkda_out_fwd": 3584, "mkda_epilogue_bwd": 2048, "mkda_bwd_dh": 3848, "mkda_bwd_wy": 4736,
-    "mkda_bwd_tail": 7168 + 256, "mkda_gate_bwd": 1536, "mkda_qk_grad_finish": 640,
+    "mkda_out_fwd": 3584, "mkda_epilogue_bwd": 2048, "mkda_bwd_dh": 4360,
+    "mkda_bwd_chunk": 6664, "mkda_gate_bwd": 1536, "mkda_qk_grad_finish": 640,
 }
 # DRAM traffic per token per v-head measured by ncu on the 1B-shape case (profiles/counters_per_kernel_1b_shape.md),
 # bytes (dram read + write per launch / 131072 token-heads); it grows in proportion to tokens x heads.
 KERNEL_TRAFFIC = {
-    "mkda_intra_fwd": 3160, "mkda_recur_fwd": 2771, "mkda_out_fwd": 3351, "mkda_bwd_dh": 3612, "mkda_bwd_wy": 4588,
-    "mkda_bwd_tail": 6501, "mkda_gate_cumsum_fwd": 641, "mkda_epilogue_bwd": 1773, "mkda_qk_grad_finish": 653,
+    "mkda_intra_fwd": 3160, "mkda_recur_fwd": 2771, "mkda_out_fwd": 3351, "mkda_bwd_dh": 3612,
+    "mkda_gate_cumsum_fwd": 641, "mkda_epilogue_bwd": 1773, "mkda_qk_grad_finish": 653,
     "mkda_l2norm_rstd": 128,
 }
 

@@ -66,7 +66,7 @@ typedef struct {
     const void* x; int x_dtype; int scalar_gate;
     const float* A_log; const float* dt_bias;
     int mode; float lower_bound;
-    const float* dgp;          /* [TT,HV,128] gradient w.r.t. the log2 cumsum as produced by mkda_bwd_tail */
+    const float* dgp;          /* [TT,HV,128] gradient w.r.t. the log2 cumsum as produced by mkda_bwd_chunk */
     void* dx; int dx_dtype;    /* [TT,HV,128] or [TT,HV] */
     int part_rows;             /* number of partial rows R (1 <= R <= NC): chunk c accumulates into row c % R */
     float* part_bias;          /* [R,HV,128] ([R,HV] scalar) partial sums of d/d(x+bias), or NULL */
@@ -230,50 +230,38 @@ typedef struct {
     const float* dht;          /* [*,HV,128,128] or NULL */
     const int* seg_dht;        /* [NS] row of dht per segment, -1 = zero; NULL = identity map */
     int state_v_first;         /* layout of dht / dh0 */
-    float* dh;                 /* [NC,HV] state tiles: gradient of the state leaving each chunk */
-    float* dVd;                /* [TT,HV,128] */
+    float* dh;                 /* [NC,HV] state tiles: gradient of the state leaving each chunk, or NULL (not stored) */
+    float* dVd_t;              /* [NC,HV] chunk tiles: dVd^T [v][token] (token columns past the end are zero), or NULL */
+    float* dO_t;               /* [NC,HV] row tiles: dO [token][v] as staged for the products (zero rows past the end), or NULL */
     float* dh0;                /* [NS,HV,128,128] gradient of the state entering each segment, or NULL */
 } MkdaBwdDh;
 int mkda_bwd_dh(const MkdaBwdDh* p, void* stream);
 
-/* Chunk-parallel gradients through Vd = A diag(beta)(V - k~ S).
- * Replaces K3a of bwd_post_kda (mogan_kda/ops/kimi_delta_rule/chunk/hopper/bwd_post.py:72-400). */
+/* Every gradient that is local to a (chunk, v-head) once the state gradients are known, in one kernel:
+ *  - through Vd = A diag(beta)(V - k~ S): dv, the WY part of dbeta, dAqk and dL (K3a of bwd_post_kda,
+ *    mogan_kda/ops/kimi_delta_rule/chunk/hopper/bwd_post.py:72-400);
+ *  - through the states: the row-local parts of dq, dk and of the gate gradient (K3b, .../bwd_post.py:412-766);
+ *  - through the decayed K K^T / Q K^T blocks (bwd_intra_kda, .../hopper/bwd_intra.py:529-600);
+ *  - the beta activation derivative (mogan_kda/ops/kimi_delta_rule/chunk/__init__.py:256-258).
+ * dX, dAqk, dL, the WY part of dbeta and the row-local partials, which the reference passes between those kernels through
+ * HBM, stay in shared / tensor memory.  Every tile operand (h, dh, Vd, A, dO, dVd) arrives by bulk copy. */
 typedef struct {
     MkdaLayout L;
-    const void* k; const void* v; int kv_dtype; const float* k_rstd;
+    const void* q; const void* k; const void* v; int qkv_dtype; const float* q_rstd; const float* k_rstd;
     const float* g_c; const float* beta;
     const float* A;            /* [NC,HV] quarter tiles as written by mkda_intra_fwd */
-    const float* h;            /* [NC,HV] state tiles */
-    const void* d_o; int do_dtype; const float* dVd;
-    const float* Vd;           /* [NC,HV] chunk tiles as written by mkda_recur_fwd in the forward pass */
-    float* dX;                 /* [TT,HV,128] = dv (fp32), an input of mkda_bwd_tail */
-    float* dbeta_w;            /* [TT,HV] */
-    float* dAqk; float* dL;    /* [TT,HV,64] */
-} MkdaBwdWy;
-int mkda_bwd_wy(const MkdaBwdWy* p, void* stream);
-
-/* Every gradient that is local to a (chunk, v-head) once the state gradients are known: through the states (row-local
- * parts of dq, dk and of the gate gradient) and through the decayed K K^T / Q K^T blocks, plus the beta activation
- * derivative.  Replaces K3b of bwd_post_kda (mogan_kda/ops/kimi_delta_rule/chunk/hopper/bwd_post.py:412-766),
- * bwd_intra_kda (mogan_kda/ops/kimi_delta_rule/chunk/hopper/bwd_intra.py:529-600) and the beta derivative
- * (mogan_kda/ops/kimi_delta_rule/chunk/__init__.py:256-258); the row-local partials the reference passes between the
- * two kernels through HBM stay in tensor memory. */
-typedef struct {
-    MkdaLayout L;
-    const void* q; const void* k; int qk_dtype; const float* q_rstd; const float* k_rstd;
-    const float* g_c; const float* beta;
-    const void* d_o; int do_dtype; const float* dX;
-    const float* Vd;           /* [NC,HV] chunk tiles as written by mkda_recur_fwd in the forward pass */
     const float* h; const float* dh;               /* state tiles, see MKDA_STATE_TILE_BYTES */
-    const float* dAqk; const float* dL; const float* dbeta_w;
+    const float* Vd;           /* [NC,HV] chunk tiles as written by mkda_recur_fwd in the forward pass */
+    const float* dO_t;         /* [NC,HV] row tiles as written by mkda_bwd_dh */
+    const float* dVd_t;        /* [NC,HV] chunk tiles as written by mkda_bwd_dh */
     float scale;
     const void* beta_raw; int beta_dtype; int beta_sigmoid; float beta_scale;
     float* dq_v; float* dk_v;  /* [TT,HV,128] per v-head */
     float* dgp;                /* [TT,HV,128] gradient w.r.t. the log2 cumsum */
     void* dbeta; int dbeta_dtype;
-    void* dv; int dv_dtype;    /* [TT,HV,128] dX again in the dtype of v (written from the staged rows), or NULL */
-} MkdaBwdTail;
-int mkda_bwd_tail(const MkdaBwdTail* p, void* stream);
+    void* dv; int dv_dtype;    /* [TT,HV,128] */
+} MkdaBwdChunk;
+int mkda_bwd_chunk(const MkdaBwdChunk* p, void* stream);
 
 /* Sum over the v-heads sharing a q/k head, then L2-norm backward; writes dq or dk in the input dtype.
  * Replaces group_reduce_vector (mogan_kda/ops/utils/group_reduce.py:60-79) and l2norm_bwd

@@ -99,7 +99,8 @@ class _DeltaRuleFunction(torch.autograd.Function):
             dht = dht.float().contiguous()
         need_dh0 = initial_state is not None and ctx.needs_input_grad[7]
         if lay.segmented or cp is not None:
-            dh, dVd, dloc = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV)
+            # pre-pass from zero: only the gradient entering each segment is wanted, nothing per chunk is stored
+            _, _, _, dloc = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, store=False)
             carry = None
             if dht is not None:
                 carry = dht.transpose(-1, -2).contiguous() if vf else dht
@@ -107,19 +108,16 @@ class _DeltaRuleFunction(torch.autograd.Function):
                 carry = cp.backward_carry(dloc, ms, carry, lay, HV, m_first)
             g_in, dh0 = ops.state_combine(lay.grp_seg_off, lay.NG, lay.NS, HV, dloc, ms, carry=carry, reverse=True,
                                           want_out=need_dh0 or cp is not None)
-            ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, dht=g_in, want_dh0=False,
-                       dh=dh, dVd=dVd)
+            dh, dVd_t, dO_t, _ = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, dht=g_in, want_dh0=False)
             if cp is not None:
                 dh0 = cp.finish_backward(dh0)
             if dh0 is not None and vf:
                 dh0 = dh0.transpose(-1, -2).contiguous()
         else:
-            dh, dVd, dh0 = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, dht=dht,
-                                      state_v_first=vf, want_dh0=need_dh0)
-        dX, dbeta_w, dAqk, dL = ops.bwd_wy(lay, k, v, k_rstd, g_c, beta_e, A, h, Vd, d_o, dVd, HK, HV)
-        dq_v, dk_v, dgp, dbeta, dv = ops.bwd_tail(lay, q, k, q_rstd, k_rstd, g_c, beta_e, d_o, dX, Vd, h, dh, dAqk, dL,
-                                                  dbeta_w, scale, HK, HV, beta, cfg["beta_mode"] == "sigmoid",
-                                                  cfg["beta_scale"], dv_dtype=v.dtype)
+            dh, dVd_t, dO_t, dh0 = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, dht=dht,
+                                              state_v_first=vf, want_dh0=need_dh0)
+        dq_v, dk_v, dgp, dbeta, dv = ops.bwd_chunk(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, A, h, dh, Vd, dO_t, dVd_t,
+                                                   scale, HK, HV, beta, cfg["beta_mode"] == "sigmoid", cfg["beta_scale"])
         dx, d_bias, d_alog = ops.gate_bwd(lay, x, dgp, cfg["gate_mode"], A_log, dt_bias, cfg["lower_bound"], HV,
                                           want_bias=dt_bias is not None and ctx.needs_input_grad[6],
                                           want_alog=A_log is not None and ctx.needs_input_grad[5])

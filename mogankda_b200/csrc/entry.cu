@@ -26,26 +26,18 @@ extern "C" int mkda_out_fwd(const MkdaOutFwd* p, void* stream) {
 }
 
 extern "C" int mkda_bwd_dh(const MkdaBwdDh* p, void* stream) {
-    if (!p || !p->d_o || !p->kbar || !p->qs || !p->gl || !p->Aqk || !p->nw || !p->dh || !p->dVd)
+    if (!p || !p->d_o || !p->kbar || !p->qs || !p->gl || !p->Aqk || !p->nw)
         return set_error(MKDA_ERR_ARG, "bwd_dh: null argument");
     if (p->L.NS == 0) return MKDA_OK;
     return launch_bwd_dh_tc(p, (cudaStream_t)stream);
 }
 
-extern "C" int mkda_bwd_wy(const MkdaBwdWy* p, void* stream) {
-    if (!p || !p->k || !p->v || !p->g_c || !p->beta || !p->A || !p->h || !p->d_o || !p->dVd || !p->Vd || !p->dX ||
-        !p->dbeta_w || !p->dAqk || !p->dL)
-        return set_error(MKDA_ERR_ARG, "bwd_wy: null argument");
+extern "C" int mkda_bwd_chunk(const MkdaBwdChunk* p, void* stream) {
+    if (!p || !p->q || !p->k || !p->v || !p->g_c || !p->beta || !p->A || !p->h || !p->dh || !p->Vd || !p->dO_t || !p->dVd_t ||
+        !p->dq_v || !p->dk_v || !p->dgp || !p->dbeta || !p->dv)
+        return set_error(MKDA_ERR_ARG, "bwd_chunk: null argument");
+    if (p->beta_sigmoid && !p->beta_raw) return set_error(MKDA_ERR_ARG, "bwd_chunk: sigmoid beta needs the raw input");
+    if (p->L.HK <= 0 || p->L.HV % p->L.HK) return set_error(MKDA_ERR_ARG, "bwd_chunk: HV must be a multiple of HK");
     if (p->L.NC == 0) return MKDA_OK;
-    return launch_bwd_wy_tc(p, (cudaStream_t)stream);
-}
-
-extern "C" int mkda_bwd_tail(const MkdaBwdTail* p, void* stream) {
-    if (!p || !p->q || !p->k || !p->g_c || !p->beta || !p->d_o || !p->dX || !p->Vd || !p->h || !p->dh || !p->dAqk || !p->dL ||
-        !p->dbeta_w || !p->dq_v || !p->dk_v || !p->dgp || !p->dbeta)
-        return set_error(MKDA_ERR_ARG, "bwd_tail: null argument");
-    if (p->beta_sigmoid && !p->beta_raw) return set_error(MKDA_ERR_ARG, "bwd_tail: sigmoid beta needs the raw input");
-    if (p->L.HK <= 0 || p->L.HV % p->L.HK) return set_error(MKDA_ERR_ARG, "bwd_tail: HV must be a multiple of HK");
-    if (p->L.NC == 0) return MKDA_OK;
-    return launch_bwd_tail_tc(p, (cudaStream_t)stream);
+    return launch_bwd_chunk_tc(p, (cudaStream_t)stream);
 }

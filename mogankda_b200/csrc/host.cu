@@ -70,13 +70,13 @@ extern "C" int mkda_device_status(void) {
     return (int)any;
 }
 extern "C" const char* mkda_last_error(void) { return mkda::g_err; }
-extern "C" int mkda_abi_version(void) { return 2; }
+extern "C" int mkda_abi_version(void) { return 3; }
 extern "C" int mkda_struct_sizes(int* out, int n) {
     const int sizes[] = {
         (int)sizeof(MkdaLayout),   (int)sizeof(MkdaGateFwd),  (int)sizeof(MkdaGateBwd),     (int)sizeof(MkdaReduce),
         (int)sizeof(MkdaL2Norm),   (int)sizeof(MkdaIntraFwd), (int)sizeof(MkdaRecurFwd),    (int)sizeof(MkdaOutFwd),
-        (int)sizeof(MkdaEpilogueBwd), (int)sizeof(MkdaEpilogueBwdNoAlloc), (int)sizeof(MkdaBwdDh), (int)sizeof(MkdaBwdWy),
-        (int)sizeof(MkdaBwdTail), (int)sizeof(MkdaQkGrad),   (int)sizeof(MkdaCombine), (int)sizeof(MkdaSelfTest)};
+        (int)sizeof(MkdaEpilogueBwd), (int)sizeof(MkdaEpilogueBwdNoAlloc), (int)sizeof(MkdaBwdDh), (int)sizeof(MkdaBwdChunk),
+        (int)sizeof(MkdaQkGrad),   (int)sizeof(MkdaCombine), (int)sizeof(MkdaSelfTest)};
     const int cnt = (int)(sizeof(sizes) / sizeof(sizes[0]));
     for (int i = 0; i < n && i < cnt; ++i) out[i] = sizes[i];
     return cnt;

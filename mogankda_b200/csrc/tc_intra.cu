@@ -351,8 +351,13 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// bwd_tail: every gradient that is local to a (chunk, v-head) once the state gradients are known.
-// State part.  With S / dS' the state entering / state-gradient leaving the chunk, up = 2^g, rest = 2^(g_L - g):
+// bwd_chunk: every gradient that is local to a (chunk, v-head) once the state gradients are known, in one CTA.
+//
+// WY part.  With S the state entering the chunk, k~ = k 2^g, Ab = A diag(beta):
+//   X = V - k~ S        Vd = Ab X (saved by the forward pass)        dAqk = lower(dO Vd^T)
+//   dW = A^T dVd        dX = diag(beta) dW (= dV)       dbeta_w = rowsum(dW * X)
+//   dA = (dVd X^T) diag(beta)          dL = -strictlower(A^T dA A^T)
+// State part.  With dS' the state gradient leaving the chunk, up = 2^g, rest = 2^(g_L - g):
 //   dq~ = scale dO S^T     dk~ = -dX S^T     dkbar = Vd dS'^T     dgl = rowsum_v(S * dS')
 //   dq_p = dq~ up          dk_p = dk~ up + dkbar rest
 //   dg_p = q~ dq~ + k~ dk~ - kbar dkbar;   last valid row += colsum(kbar dkbar) + gl dgl
@@ -360,57 +365,84 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
 //   dq_row_i = sum_j Wq_ij k_j E_ij                     T_i = sum_j dLs_ij k_j E_ij
 //   dk_col_j = sum_i (Wq_ij q_i + beta_i dLs_ij k_i) E_ij
 //   dq = dq_p + dq_row + scale dAqk_ii k       dk = dk_p + beta T + dk_col + scale dAqk_ii q
-//   dg' = dg_p + q dq_row + k beta T - k dk_col           dbeta_g = sum_c k T
+//   dg' = dg_p + q dq_row + k beta T - k dk_col           dbeta = dbeta_w + sum_c k T
 // E_ij is factored through the anchor a of i's 16-row block exactly as in the forward kernel.  Channels go on M.  Per row
 // block I (anchor a = 16 I):
 //   row terms   R_I^T[c][r]  = sum_j Kc_I[j][c] W[16 I + r][j]       W = Wq (-> dq_row) or dLs (-> T); N = 16 each
 //   col terms   C_I^T[c][j]  = sum_{i in I} Qr[i][c] Wq[i][j] + Kr[i][c] (beta dLs)[i][j]      N = 16 (I + 1)
 // then per thread (channel c, row block cg): dq_row = R 2^(g_i - g_a), T likewise, dk_col[j] = sum_{I >= cg} C_I 2^(g_aI - g_j).
-// All A operands are MN-major views of the untransposed Kc / [Kr; Qr] tiles and of the saved state tiles.
 //
-// The three state products
-//   Dq^T[c][t] = S dO^T      Dk^T[c][t] = S dX^T      Db^T[c][t] = dS' Vd^T         (channels c on M, K = 128 over v)
-// stay in tensor memory while the CTA rebuilds the intra-chunk operands over the dead state tiles and issues the
-// row / column products; one epilogue then combines all of them per (channel, row) and writes dq_v, dk_v and dgp once.
-// TMEM columns: Dq 0, Dk 64, Db 128, R_I 192 + 32 I, C_I 320 + {0, 16, 48, 96}.
+// Every tile operand arrives by bulk copy: S and dS' (state tiles), Vd^T (the forward pass's chunk tile), A (quarter tile),
+// dO (row tile) and dVd^T (chunk tile) as written by the reverse state chain.  Only k, q, g and v pass through registers.
+// Products (M = 128 throughout; a 64-row operand on M leaves lanes 64..127 of its accumulator undefined and unread):
+//   P1  X^T[v x tok]   = V^T - S^T k~^T                  P2  dW^T[v x j] = dVd^T A
+//   P3a D1[i x j]      = dO Vd^T                         P6a Dq^T[c x tok] = S dO^T
+//   P3b D2[64 + i][j]  = dVd X^T (operand shifted so that the result lands in lanes 64..127: both halves of the CTA read
+//                        their accumulators at the same time)        P6b Dk^T[c x tok] = S dX^T
+//   P4  Y[a x j]       = (D2 diag(beta)) A^T             P5  Z[i x j] = A^T Y         dL = -strictlower(Z)
+//   P7  Db^T[c x tok]  = dS' Vd^T                        then the row / column products of the intra-chunk part
+// dX, dAqk, dL and dbeta_w never leave the SM.
+//
+// Shared memory (U = 32 KB): S [0, 2U) | k~ -> X^T -> dS' hi [2U, 3U) | dO -> dX^T -> dS' lo [3U, 4U) | Vd^T [4U, 5U) |
+// A -> beta dLs [5U, 5U + 16K) | dVd^T -> (D2 beta | Y) -> [Wq; dLs] [5U + 16K, 6U + 16K); the intra-chunk operands
+// (column tiles, [Kr; Qr]) are rebuilt over [0, 4.5U) once the state products are done.
+// TMEM columns: X -> Y 0, dW -> Z 64, D1 128, Dq 192, D2 256, Dk 320, Db 384; later R_I 32 I, C_I {304, 448, 256, 128}.
 // ---------------------------------------------------------------------------------------------------------
-constexpr int TAIL_SMEM = 192 * 1024 + 1024;
-__host__ __device__ constexpr int dcol_off(int I) { return 320 + (I == 0 ? 0 : I == 1 ? 16 : I == 2 ? 48 : 96); }
+constexpr int BU = 32768;
+constexpr int BC_K = 2 * BU, BC_O = 3 * BU, BC_V = 4 * BU, BC_A = 5 * BU, BC_D = 5 * BU + 16384;
+constexpr int BWD_CHUNK_SMEM = 6 * BU + 16384 + 1024;
+static_assert(KQ_OFF + 65536 <= BC_A, "the intra-chunk operands must end below the weight tiles");
+__host__ __device__ constexpr int ccol_off(int I) { return I == 0 ? 304 : I == 1 ? 448 : I == 2 ? 256 : 128; }
 
-template <int QKDT, int DODT>
-__global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p) {
+struct BwdShared {
+    uint64_t barA, barB, barC, ld0, ld1;
+    uint32_t tmem;
+    float beta[CH];
+};
+
+template <int DT>
+__global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ IntraShared sh;
-    __shared__ float sDiag[CH];
+    __shared__ BwdShared sh;
+    __shared__ float sDiag[CH], sDbw[CH];
     __shared__ float sRed[4][CH];
+    __shared__ float sRedW[2][CH];
     __shared__ float sDgl[DK];
     __shared__ float sCol[4][DK];
     __shared__ float sRk[CH], sRq[CH];                 // L2-norm scales of the chunk's rows (0 past the end)
     __shared__ __align__(16) float sPart[16][DK];
-    __shared__ uint64_t ldS, ldD;
     __shared__ __align__(16) float sGa[4][DK];         // cumsum rows of the four block anchors
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    // state phase
-    uint8_t* sSh = base;                               // state tile S^T [v][K index] (hi, lo)
-    uint8_t* sSl = base + 32768;
-    uint8_t* sTh = base + 65536;                       // state tile dS'^T
-    uint8_t* sTl = base + 98304;
-    uint8_t* sOh = base + 131072;                      // [dO; dX] [2 x tok][v] as one 128-row tile (32 KB); its first 32 KB later the Vd^T chunk tile
-    uint8_t* sOl = base + 163840;
-    // intra phase
+    uint8_t* sS = base;                                // S^T [v][K index] state tile (hi, lo)
+    uint8_t* sK = base + BC_K;                         // k~ [tok][K index] -> X^T [v][tok] -> dS'^T hi
+    uint8_t* sO = base + BC_O;                         // dO [tok][v] -> dX^T [v][tok] -> dS'^T lo
+    uint8_t* sV = base + BC_V;                         // Vd^T [v][tok]
+    uint8_t* sA = base + BC_A;                         // A [i][j] -> diag(beta) strictlower(dL) [i][j]
+    uint8_t* sD = base + BC_D;                         // dVd^T [v][tok] -> D2 diag(beta) [a][b] | Y [a][j] -> [Wq; dLs] 128-row tile
+    uint8_t* sY = sD + 16384;
     uint8_t* sKQ = base + KQ_OFF;
-    uint8_t* sWD = base + OPND_BYTES;                  // 128-row tile [.][j]: rows 32 I + r = scale strictlower(dAqk)[16 I + r],
-                                                       // rows 32 I + 16 + r = strictlower(dL)[16 I + r]; hi 16 KB + lo 16 KB
-    uint8_t* sBd = sWD + 32768;                        // diag(beta) strictlower(dL) [i][j], hi 8 KB + lo 8 KB
+    uint8_t* sWD = sD;                                 // rows 32 I + r = scale strictlower(dAqk)[16 I + r], rows 32 I + 16 + r = strictlower(dL)[16 I + r]
+    uint8_t* sBd = sA;
 
     const int HV = p.L.HV, HK = p.L.HK, c = blockIdx.x / HV, h = blockIdx.x - c * HV;     // heads fastest: CTAs that run together read neighbouring memory
     const int hk = h / (HV / HK);
     const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
+    const size_t item = (size_t)c * HV + h;
 
     if (warp == 0) umma::tmem_alloc(&sh.tmem, 512);
-    if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
+    if (tid == 0) {
+        umma::mbar_init(&sh.barA, 1); umma::mbar_init(&sh.barB, 1); umma::mbar_init(&sh.barC, 1);
+        umma::mbar_init(&sh.ld0, 1); umma::mbar_init(&sh.ld1, 1);
+        umma::fence_barrier_init();
+        umma::mbar_expect_tx(&sh.ld0, umma::STATE_TILE_BYTES + umma::QUARTER_TILE_BYTES + 3 * umma::CHUNK_TILE_BYTES);
+        umma::bulk_load(sS, reinterpret_cast<const uint8_t*>(p.h) + item * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &sh.ld0);
+        umma::bulk_load(sD, reinterpret_cast<const uint8_t*>(p.dVd_t) + item * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld0);
+        umma::bulk_load(sA, reinterpret_cast<const uint8_t*>(p.A) + item * umma::QUARTER_TILE_BYTES, umma::QUARTER_TILE_BYTES, &sh.ld0);
+        umma::bulk_load(sO, reinterpret_cast<const uint8_t*>(p.dO_t) + item * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld0);
+        umma::bulk_load(sV, reinterpret_cast<const uint8_t*>(p.Vd) + item * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld0);
+    }
     if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
     if (tid >= CH && tid < 2 * CH) {
         const int r = tid - CH;
@@ -419,69 +451,151 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         sRq[r] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
     }
 
-    // ---- state phase: the two state tiles arrive by asynchronous copy; dO, dX and the Vd^T tile go through registers ----------------
-    if (tid == 0) {
-        umma::fetch_state_tile(&ldS, sSh, p.h, (size_t)c * HV + h);
-        umma::fetch_state_tile(&ldD, sTh, p.dh, (size_t)c * HV + h);
-    }
-    uint4 vV[4];                                       // the forward pass's Vd^T chunk tile, copied as it is (64 bytes per thread)
-    {
-        const uint4* vd = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.Vd) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES);
-#pragma unroll
-        for (int n = 0; n < 4; ++n) vV[n] = __ldg(vd + tid + n * 512);
-    }
-    {
-        float vO[2][8], vX[2][8];
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            const int i = tid + n * 512, r = i >> 4, rr = r < len ? r : len - 1;
-            const size_t off = ((size_t)(start + rr) * HV + h) * 128 + (i & 15) * 8;
-            ldg8(p.d_o, DODT, off, vO[n]);
-            ldg8(p.dX, MKDA_F32, off, vX[n]);
-        }
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            const int i = tid + n * 512, r = i >> 4;
-            if (r >= len) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) vO[n][e] = vX[n][e] = 0.f;
-            }
-            store_split8(sOh, sOl, 128, r, i & 15, vO[n]);
-            store_split8(sOh, sOl, 128, 64 + r, i & 15, vX[n]);
-            if (p.dv && r < len) {                     // dv in the dtype of v: the staged dX rows, 8 values per store
-                const size_t off = ((size_t)(start + r) * HV + h) * 128 + (i & 15) * 8;
-                st4(p.dv, p.dv_dtype, off, make_float4(vX[n][0], vX[n][1], vX[n][2], vX[n][3]));
-                st4(p.dv, p.dv_dtype, off + 4, make_float4(vX[n][4], vX[n][5], vX[n][6], vX[n][7]));
-            }
-        }
-    }
-    // intra phase inputs (k, q, g and the two 64 x 64 weights) are requested now and consumed after the state products
-    float vk[2][8], vq[2][8], vg[2][8], rk[2], rq[2], wa[8], wl[8];
+    // ---- k, g (now: k~ for P1) and q (later: the intra-chunk operands); this thread's column of V for X ---------------
+    float vk[2][8], vq[2][8], vg[2][8], vv[16];
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
         const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
         const size_t tk = (size_t)(start + rr) * HK + hk;
-        ldg8(p.k, QKDT, tk * 128 + k8 * 8, vk[n]);
-        ldg8(p.q, QKDT, tk * 128 + k8 * 8, vq[n]);
+        ldg8(p.k, DT, tk * 128 + k8 * 8, vk[n]);
         ldg8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vg[n]);
+        ldg8(p.q, DT, tk * 128 + k8 * 8, vq[n]);
     }
-    {
-        const int i = tid >> 3, k8 = tid & 7, ii = i < len ? i : len - 1;
-        const size_t o = ((size_t)(start + ii) * HV + h) * 64 + k8 * 8;
-        ldg8(p.dAqk, MKDA_F32, o, wa);
-        ldg8(p.dL, MKDA_F32, o, wl);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int t = cg * 16 + j, tt = t < len ? t : len - 1;
+        vv[j] = ld1(p.v, DT, ((size_t)(start + tt) * HV + h) * 128 + row);
     }
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+        const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
+        const size_t tk = (size_t)(start + rr) * HK + hk;
+        const float rk = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
+        const float rq = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
+        float t8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            vk[n][e] *= rk;
+            vq[n][e] *= rq;
+            t8[e] = vk[n][e] * ex2f_(vg[n][e]);
+        }
+        store_split8(sK, sK + 16384, 64, r, k8, t8);
+        if ((r & 15) == 0) {
+            *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8]) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
+            *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8 + 4]) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+        if (cg * 16 + j >= len) vv[j] = 0.f;
     publish();
     const uint32_t tmem = sh.tmem;
+
+    // ---- batch 1 ------------------------------------------------------------------------------------------------------------
     if (umma::mma_issuer()) {
-        umma::mbar_wait(&ldS, 0);
-        const umma::Opnd aS = umma::opnd_mn(sSh, sSl, 128);          // A(m = K index, k = v) of the [v][K index] tile
-        umma::gemm(tmem + 0, aS, umma::opnd_k(sOh, sOl, 128), 128, 128, 128, 0u);      // Dq | Dk in one N = 128 product
-        umma::commit(&sh.bar);
+        umma::mbar_wait(&sh.ld0, 0);
+        umma::gemm(tmem + 0, umma::opnd_k(sS, sS + BU, 128), umma::opnd_k(sK, sK + 16384, 64), 128, 64, 128, 0u);        // P1
+        umma::gemm(tmem + 64, umma::opnd_k(sD, sD + 16384, 128), umma::opnd_mn(sA, sA + 8192, 64), 128, 64, 64, 0u);     // P2
+        umma::commit(&sh.barA);
+        umma::gemm(tmem + 192, umma::opnd_mn(sS, sS + BU, 128), umma::opnd_k(sO, sO + 16384, 64), 128, 64, 128, 0u);     // P6a
+        umma::gemm(tmem + 128, umma::opnd_k(sO, sO + 16384, 64), umma::opnd_mn(sV, sV + 16384, 128), 128, 64, 128, 0u);  // P3a
+        umma::commit(&sh.barB);
+    }
+    umma::mbar_wait(&sh.barA, 0);
+    umma::mbar_wait(&sh.ld0, 0);                       // long complete: makes the copied tiles visible to the plain reads below
+    umma::fence_after_sync();
+    {
+        float d[16], x0[8], x1[8];
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, cg * 16), d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { x0[j] = vv[j] - d[j]; x1[j] = vv[8 + j] - d[8 + j]; }
+        store_split8(sK, sK + 16384, 128, row, 2 * cg, x0);            // k~ is dead: the region now holds X^T
+        store_split8(sK, sK + 16384, 128, row, 2 * cg + 1, x1);
+        float dw[16];
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 64 + cg * 16), dw);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int t = cg * 16 + j;
+            dw[j] *= sh.beta[t];                                       // dX = diag(beta) dW; beta is 0 past the end
+            if (t < len) st1(p.dv, p.dv_dtype, ((size_t)(start + t) * HV + h) * 128 + row, dw[j]);
+        }
+        umma::mbar_wait(&sh.barB, 0);                                  // P6a and P3a done: the dO tile is dead
+        umma::fence_after_sync();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { x0[j] = dw[j]; x1[j] = dw[8 + j]; }
+        store_split8(sO, sO + 16384, 128, row, 2 * cg, x0);
+        store_split8(sO, sO + 16384, 128, row, 2 * cg + 1, x1);
+    }
+    publish();
+    // ---- batch 2 ------------------------------------------------------------------------------------------------------------
+    if (umma::mma_issuer()) {
+        umma::Opnd aD = umma::opnd_mn(sD, sD + 16384, 128);            // (m = token, k = v) of the dVd^T tile, moved one 64-group up:
+        aD.hi -= 16384; aD.lo -= 16384;                                // rows 0..63 of the operand read the 16 KB in front of each half
+        umma::gemm(tmem + 256, aD, umma::opnd_mn(sK, sK + 16384, 128), 128, 64, 128, 0u);                                // P3b
+        umma::commit(&sh.barA);
+        umma::gemm(tmem + 320, umma::opnd_mn(sS, sS + BU, 128), umma::opnd_mn(sO, sO + 16384, 128), 128, 64, 128, 0u);   // P6b
+        umma::commit(&sh.barB);
+    }
+    umma::mbar_wait(&sh.barA, 1);
+    umma::fence_after_sync();
+    if (q >= 2) {                                      // rows i = row - 64 of D2 = dVd X^T: dbeta_w partials and D2 diag(beta)
+        const int i = row - 64;
+        float d[16], a0[8], a1[8];
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 256 + cg * 16), d);
+        umma::load_tile8(sA, sA + 8192, 64, i, 2 * cg, a0);
+        umma::load_tile8(sA, sA + 8192, 64, i, 2 * cg + 1, a1);
+        float pr[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            pr[j] = d[j] * (j < 8 ? a0[j] : a1[j - 8]);
+            const float da = d[j] * sh.beta[cg * 16 + j];
+            if (j < 8) a0[j] = da; else a1[j - 8] = da;
+        }
+        // sums over the 32 lanes for the 16 columns at once: every exchange halves the number of columns a lane carries
+        // (16 shuffles instead of 80); the lane whose bits 4..1 spell the column ends up with its sum
+#pragma unroll
+        for (int w = 8, bit = 16; w >= 1; w >>= 1, bit >>= 1) {
+#pragma unroll
+            for (int j = 0; j < w; ++j) {
+                const float recv = __shfl_xor_sync(0xffffffffu, (lane & bit) ? pr[j] : pr[j + w], bit);
+                pr[j] = ((lane & bit) ? pr[j + w] : pr[j]) + recv;
+            }
+        }
+        pr[0] += __shfl_xor_sync(0xffffffffu, pr[0], 1);
+        if ((lane & 1) == 0) sRedW[q - 2][cg * 16 + ((lane >> 1) & 15)] = pr[0];
+        store_split8(sD, sD + 8192, 64, i, 2 * cg, a0);               // dVd^T is dead (P3b done)
+        store_split8(sD, sD + 8192, 64, i, 2 * cg + 1, a1);
+    }
+    publish();
+    if (tid < CH) sDbw[tid] = sRedW[0][tid] + sRedW[1][tid];
+    if (umma::mma_issuer()) {
+        umma::gemm(tmem + 0, umma::opnd_k(sD, sD + 8192, 64), umma::opnd_k(sA, sA + 8192, 64), 128, 64, 64, 0u);          // P4
+        umma::commit(&sh.barA);
+        // X^T and dX^T are dead once P6b is done as well: the 64 KB they occupy receive the dS' tile
+        umma::mbar_wait(&sh.barB, 1);
+        umma::mbar_expect_tx(&sh.ld1, umma::STATE_TILE_BYTES);
+        umma::bulk_load(sK, reinterpret_cast<const uint8_t*>(p.dh) + item * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &sh.ld1);
+    }
+    umma::mbar_wait(&sh.barA, 0);
+    umma::fence_after_sync();
+    if (q < 2) {
+        float y[16], a0[8], a1[8];
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, cg * 16), y);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { a0[j] = y[j]; a1[j] = y[8 + j]; }
+        store_split8(sY, sY + 8192, 64, row, 2 * cg, a0);
+        store_split8(sY, sY + 8192, 64, row, 2 * cg + 1, a1);
+    }
+    publish();
+    if (umma::mma_issuer()) {
+        umma::gemm(tmem + 64, umma::opnd_mn(sA, sA + 8192, 64), umma::opnd_mn(sY, sY + 8192, 64), 128, 64, 64, 0u);       // P5
+        umma::commit(&sh.barA);
+        umma::mbar_wait(&sh.ld1, 0);
+        umma::gemm(tmem + 384, umma::opnd_mn(sK, sK + BU, 128), umma::opnd_mn(sV, sV + 16384, 128), 128, 64, 128, 0u);    // P7
+        umma::commit(&sh.barC);
     }
     {   // dgl[c] = sum_v S[c][v] dS'[c][v] from the two tiles: chunk (v row, 8 channels) per thread, four rows each
-        umma::mbar_wait(&ldS, 0);
-        umma::mbar_wait(&ldD, 0);
+        umma::mbar_wait(&sh.ld1, 0);
         float acc[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = 0.f;
@@ -489,8 +603,8 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
         for (int n = 0; n < 4; ++n) {
             const int i = tid + n * 512;
             const uint32_t off = umma::tile_chunk_offset(128, i >> 4, i & 15);
-            const uint4 a4 = *reinterpret_cast<const uint4*>(sSh + off), b4 = *reinterpret_cast<const uint4*>(sSl + off);
-            const uint4 c4 = *reinterpret_cast<const uint4*>(sTh + off), d4 = *reinterpret_cast<const uint4*>(sTl + off);
+            const uint4 a4 = *reinterpret_cast<const uint4*>(sS + off), b4 = *reinterpret_cast<const uint4*>(sS + BU + off);
+            const uint4 c4 = *reinterpret_cast<const uint4*>(sK + off), d4 = *reinterpret_cast<const uint4*>(sK + BU + off);
             const uint32_t ah[4] = {a4.x, a4.y, a4.z, a4.w}, al[4] = {b4.x, b4.y, b4.z, b4.w};
             const uint32_t dh[4] = {c4.x, c4.y, c4.z, c4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
@@ -510,35 +624,41 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
             *reinterpret_cast<float4*>(&sPart[warp][lane * 8 + 4]) = make_float4(acc[4], acc[5], acc[6], acc[7]);
         }
     }
-    umma::mbar_wait(&sh.bar, 0);                       // S dO^T and S dX^T done: the dO tile can be replaced by Vd
+    umma::mbar_wait(&sh.barA, 1);                      // Z done: A, D2 diag(beta) and Y are dead
     umma::fence_after_sync();
+    if (q < 2) {                                       // rows i = row of D1 = dO Vd^T and Z: the weights of the intra-chunk part
+        const int i = row;
+        const float bt = sh.beta[i];
+        float d[16], z[16];
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + cg * 16), d);
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 64 + cg * 16), z);
 #pragma unroll
-    for (int n = 0; n < 4; ++n) reinterpret_cast<uint4*>(sOh)[tid + n * 512] = vV[n];     // hi 16 KB, then lo 16 KB
-    publish();
-    if (umma::mma_issuer()) {   // B(n = token, k = v) is the MN-major view of the [v][token] tile
-        umma::gemm(tmem + 128, umma::opnd_mn(sTh, sTl, 128), umma::opnd_mn(sOh, sOh + 16384, 128), 128, 64, 128, 0u);
-        umma::commit(&sh.bar);
+        for (int hf = 0; hf < 2; ++hf) {
+            float w8[8], d8[8], b8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int j = cg * 16 + hf * 8 + e;
+                const bool lo = j < i && i < len;
+                w8[e] = lo ? p.scale * d[hf * 8 + e] : 0.f;
+                d8[e] = lo ? -z[hf * 8 + e] : 0.f;
+                b8[e] = bt * d8[e];
+                if (j == i) sDiag[i] = i < len ? p.scale * d[hf * 8 + e] : 0.f;
+            }
+            store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + (i & 15), 2 * cg + hf, w8);
+            store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + 16 + (i & 15), 2 * cg + hf, d8);
+            store_split8(sBd, sBd + 8192, 64, i, 2 * cg + hf, b8);
+        }
     }
+    __syncthreads();                                   // sPart complete
     if (tid < DK) {
         float t = 0.f;
 #pragma unroll
         for (int w = 0; w < 16; ++w) t += sPart[w][tid];
         sDgl[tid] = t;
     }
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-        const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
-        if ((r & 15) == 0) {
-            *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8]) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
-            *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8 + 4]) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
-        }
-        rk[n] = sRk[r]; rq[n] = sRq[r];                // written before the first publish()
-#pragma unroll
-        for (int e = 0; e < 8; ++e) { vk[n][e] *= rk[n]; vq[n][e] *= rq[n]; }
-    }
-    __syncthreads();
-    umma::mbar_wait(&sh.bar, 1);                       // dS' Vd^T done: every state tile is dead
+    umma::mbar_wait(&sh.barC, 0);                      // dS' Vd^T done: every state-phase tile is dead
     umma::fence_after_sync();
+    // ---- intra-chunk operands over the dead tiles ----------------------------------------------------------------------------------
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
         const int i = tid + n * 512, r = i >> 4, k8 = i & 15, I0 = r >> 4;
@@ -559,23 +679,6 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
             store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
         }
     }
-    {
-        const int i = tid >> 3, k8 = tid & 7;
-        const float bt = sh.beta[i];
-        float w8[8], d8[8], b8[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const int j = k8 * 8 + e;
-            const bool lo = j < i && i < len;
-            w8[e] = lo ? p.scale * wa[e] : 0.f;
-            d8[e] = lo ? wl[e] : 0.f;
-            b8[e] = bt * d8[e];
-            if (j == i) sDiag[i] = i < len ? p.scale * wa[e] : 0.f;
-        }
-        store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + (i & 15), k8, w8);
-        store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + 16 + (i & 15), k8, d8);
-        store_split8(sBd, sBd + 8192, 64, i, k8, b8);
-    }
     publish();
     if (umma::mma_issuer()) {
 #pragma unroll
@@ -583,13 +686,13 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
             const int nj = 16 * (I + 1);
             const umma::Opnd aKc = umma::opnd_mn(base + kc_off(I), base + kc_off(I) + kc_bytes(I), nj);
             // both row terms (dq_row | T) of the block in one N = 32 product
-            umma::gemm(tmem + 192 + 32 * I, aKc, umma::opnd_k(sWD, sWD + 16384, 128, 32 * I), 128, 32, nj, 0u);
-            umma::gemm(tmem + dcol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I + 16), umma::opnd_mn(sWD, sWD + 16384, 128, 32 * I),
+            umma::gemm(tmem + 32 * I, aKc, umma::opnd_k(sWD, sWD + 16384, 128, 32 * I), 128, 32, nj, 0u);
+            umma::gemm(tmem + ccol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I + 16), umma::opnd_mn(sWD, sWD + 16384, 128, 32 * I),
                        128, nj, 16, 0u);
-            umma::gemm(tmem + dcol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I), umma::opnd_mn(sBd, sBd + 8192, 64, 16 * I),
+            umma::gemm(tmem + ccol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I), umma::opnd_mn(sBd, sBd + 8192, 64, 16 * I),
                        128, nj, 16, 1u);
         }
-        umma::commit(&sh.bar);
+        umma::commit(&sh.barA);
     }
     // epilogue inputs for (channel `row`, rows 16 cg .. 16 cg + 15) are fetched while the products run
     float kq[16], qq[16], gg[16], ga[4];
@@ -597,19 +700,19 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     for (int r = 0; r < 16; ++r) {
         const int i = 16 * cg + r, ii = i < len ? i : len - 1;
         const size_t tk = (size_t)(start + ii) * HK + hk;
-        kq[r] = ld1(p.k, QKDT, tk * 128 + row) * (i < len ? sRk[i] : sRk[len - 1]);
-        qq[r] = ld1(p.q, QKDT, tk * 128 + row) * (i < len ? sRq[i] : sRq[len - 1]);
+        kq[r] = ld1(p.k, DT, tk * 128 + row) * (i < len ? sRk[i] : sRk[len - 1]);
+        qq[r] = ld1(p.q, DT, tk * 128 + row) * (i < len ? sRq[i] : sRq[len - 1]);
         gg[r] = p.g_c[((size_t)(start + ii) * HV + h) * 128 + row];
     }
 #pragma unroll
     for (int I = 0; I < 4; ++I) ga[I] = sGa[I][row];   // anchor rows (the last valid row stands in for anchors past the end)
     const float gL = p.g_c[((size_t)(start + len - 1) * HV + h) * 128 + row];
-    umma::mbar_wait(&sh.bar, 0);
+    umma::mbar_wait(&sh.barA, 0);
     umma::fence_after_sync();
 
     {   // column sum of the inter-chunk k gradient for the last row's gate term
         float ab[16];
-        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + 16 * cg), ab);
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 384 + 16 * cg), ab);
         float cs = 0.f;
 #pragma unroll
         for (int r = 0; r < 16; ++r)
@@ -622,18 +725,18 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     for (int hf = 0; hf < 2; ++hf) {
         const int c0 = 16 * cg + 8 * hf;
         float aq[8], ak[8], ab[8], vr[8], vt[8], dkc[8];
-        umma::tmem_ld8(umma::tmem_addr(tmem, warp, c0), aq);
-        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 64 + c0), ak);
-        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 128 + c0), ab);
-        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 192 + 32 * cg + 8 * hf), vr);
-        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 192 + 32 * cg + 16 + 8 * hf), vt);
+        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 192 + c0), aq);
+        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 320 + c0), ak);
+        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 384 + c0), ab);
+        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 32 * cg + 8 * hf), vr);
+        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 32 * cg + 16 + 8 * hf), vt);
 #pragma unroll
         for (int r = 0; r < 8; ++r) dkc[r] = 0.f;
 #pragma unroll
         for (int I = 0; I < 4; ++I) {
             if (I < cg) continue;                      // warp-uniform
             float c8[8];
-            umma::tmem_ld8(umma::tmem_addr(tmem, warp, dcol_off(I) + c0), c8);
+            umma::tmem_ld8(umma::tmem_addr(tmem, warp, ccol_off(I) + c0), c8);
 #pragma unroll
             for (int r = 0; r < 8; ++r) dkc[r] += c8[r] * ex2f_(ga[I] - gg[8 * hf + r]);
         }
@@ -678,7 +781,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     __syncthreads();
     if (tid < len) {
         const size_t th = (size_t)(start + tid) * HV + h;
-        float db = p.dbeta_w[th] + ((sRed[0][tid] + sRed[1][tid]) + (sRed[2][tid] + sRed[3][tid]));
+        float db = sDbw[tid] + ((sRed[0][tid] + sRed[1][tid]) + (sRed[2][tid] + sRed[3][tid]));
         if (p.beta_sigmoid) {
             const float sg = sigmoidf_(ld1(p.beta_raw, p.beta_dtype, th));
             db *= p.beta_scale * sg * (1.f - sg);
@@ -690,30 +793,20 @@ __global__ void __launch_bounds__(512, 1) bwd_tail_tc_kernel(const MkdaBwdTail p
     if (warp == 0) umma::tmem_dealloc(tmem, 512);
 }
 
-template <int QKDT, int DODT>
-static int launch_bwd_tail_tc_t(const MkdaBwdTail* p, cudaStream_t stream) {
-    auto kern = bwd_tail_tc_kernel<QKDT, DODT>;
-    if (int e = ensure_smem((const void*)kern, TAIL_SMEM, "bwd_tail")) return e;
-    kern<<<p->L.NC * p->L.HV, 512, TAIL_SMEM, stream>>>(*p);
-    return check_launch("bwd_tail");
+template <int DT>
+static int launch_bwd_chunk_tc_t(const MkdaBwdChunk* p, cudaStream_t stream) {
+    auto kern = bwd_chunk_tc_kernel<DT>;
+    if (int e = ensure_smem((const void*)kern, BWD_CHUNK_SMEM, "bwd_chunk")) return e;
+    kern<<<p->L.NC * p->L.HV, 512, BWD_CHUNK_SMEM, stream>>>(*p);
+    return check_launch("bwd_chunk");
 }
-template <int QKDT>
-static int launch_bwd_tail_tc_q(const MkdaBwdTail* p, cudaStream_t stream) {
-    switch (p->do_dtype) {
-        case MKDA_F32: return launch_bwd_tail_tc_t<QKDT, MKDA_F32>(p, stream);
-        case MKDA_BF16: return launch_bwd_tail_tc_t<QKDT, MKDA_BF16>(p, stream);
-        case MKDA_F16: return launch_bwd_tail_tc_t<QKDT, MKDA_F16>(p, stream);
+int launch_bwd_chunk_tc(const MkdaBwdChunk* p, cudaStream_t stream) {
+    switch (p->qkv_dtype) {
+        case MKDA_F32: return launch_bwd_chunk_tc_t<MKDA_F32>(p, stream);
+        case MKDA_BF16: return launch_bwd_chunk_tc_t<MKDA_BF16>(p, stream);
+        case MKDA_F16: return launch_bwd_chunk_tc_t<MKDA_F16>(p, stream);
     }
-    return set_error(MKDA_ERR_ARG, "bwd_tail: unsupported dtype");
-}
-
-int launch_bwd_tail_tc(const MkdaBwdTail* p, cudaStream_t stream) {
-    switch (p->qk_dtype) {
-        case MKDA_F32: return launch_bwd_tail_tc_q<MKDA_F32>(p, stream);
-        case MKDA_BF16: return launch_bwd_tail_tc_q<MKDA_BF16>(p, stream);
-        case MKDA_F16: return launch_bwd_tail_tc_q<MKDA_F16>(p, stream);
-    }
-    return set_error(MKDA_ERR_ARG, "bwd_tail: unsupported dtype");
+    return set_error(MKDA_ERR_ARG, "bwd_chunk: unsupported dtype");
 }
 
 int tc_intra_status(unsigned int* out) {

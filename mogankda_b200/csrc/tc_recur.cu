@@ -187,7 +187,7 @@ namespace mkda {
 // ---------------------------------------------------------------------------------------------------------
 // Reverse state-gradient chain on the tensor cores.  dSt[v lanes][K-index columns] (transposed, fp32, TMEM) is the
 // gradient of the state leaving the current chunk; per chunk, walking backwards:
-//   dVd^T[v x j] = dO^T Aqk + dSt kbar^T
+//   dVd^T[v x j] = dO^T Aqk + dSt kbar^T                 (saved as a chunk tile, with dO as a row tile, for mkda_bwd_chunk)
 //   dSt <- dSt diag(gl) + dO^T (scale q 2^g) + dVd^T nw
 // dO, Aqk, kbar, q~ and nw are staged untransposed; the views (K-major / MN-major) supply the transposes.
 // ---------------------------------------------------------------------------------------------------------
@@ -239,6 +239,7 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
             // Only dO goes through registers.
             const size_t it = (size_t)c * HV + h;
             if (tid == 0) {
+                umma::bulk_store_wait_read();              // the previous chunk's saved tiles (dS', dO, dVd^T) have left shared memory
                 umma::mbar_expect_tx(&sh.ldw[1], umma::QUARTER_TILE_BYTES + umma::CHUNK_TILE_BYTES);
                 umma::bulk_load(sAq, reinterpret_cast<const uint8_t*>(p.Aqk) + it * umma::QUARTER_TILE_BYTES, umma::QUARTER_TILE_BYTES, &sh.ldw[1]);
                 umma::bulk_load(sKb, reinterpret_cast<const uint8_t*>(p.kbar) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[1]);
@@ -247,24 +248,23 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
                 umma::bulk_load(sNw, reinterpret_cast<const uint8_t*>(p.nw) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[0]);
             }
             if (tid < DK) sh.gl[0][tid] = p.gl[it * 128 + tid];
-            float vo[2][8];
-#pragma unroll
-            for (int n = 0; n < 2; ++n) {
-                const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-                ld8(p.d_o, DODT, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vo[n]);
-            }
-#pragma unroll
-            for (int n = 0; n < 2; ++n) {
-                const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
-                if (r >= len) {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) vo[n][e] = 0.f;
-                }
-                store_split8(sDo, sDo + 16384, 64, r, k8, vo[n]);
-            }
         }
-        if (tid == 0) umma::bulk_store_wait_read();         // the previous chunk's saved tile has left shared memory
-        __syncthreads();                                   // sh.gl
+        float vo[2][8];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
+            ld8(p.d_o, DODT, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vo[n]);
+        }
+        __syncthreads();                                   // sh.gl is complete; no copy reads the dO or dS' tile any more
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
+            if (r >= len) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) vo[n][e] = 0.f;
+            }
+            store_split8(sDo, sDo + 16384, 64, r, k8, vo[n]);
+        }
         {   // gradient leaving the chunk: operand tile (saved as it is by the issuing thread below), decay
             float s[32];
             umma::tmem_ld32(umma::tmem_addr(tmem, warp, cg * 32), s);
@@ -282,8 +282,13 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
         }
         publish_operands();
         // the operand tile is also this chunk's saved gradient: one asynchronous 64 KB copy, awaited by the same thread
-        // before the tile is rebuilt in the next iteration (measured: starting it here is faster than after the products)
-        if (tid == 0) umma::bulk_store(reinterpret_cast<uint8_t*>(p.dh) + ((size_t)c * HV + h) * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
+        // before the tile is rebuilt in the next iteration (measured: starting it here is faster than after the products);
+        // the staged dO tile leaves the same way for the chunk-parallel kernel that follows
+        if (tid == 0) {
+            const size_t it = (size_t)c * HV + h;
+            if (p.dh) umma::bulk_store(reinterpret_cast<uint8_t*>(p.dh) + it * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
+            if (p.dO_t) umma::bulk_store(reinterpret_cast<uint8_t*>(p.dO_t) + it * umma::CHUNK_TILE_BYTES, sDo, umma::CHUNK_TILE_BYTES);
+        }
         if (umma::mma_issuer()) {
             umma::mbar_wait(&sh.ldw[1], ((c_end - 1 - c) & 1));               // this chunk's Aqk and kbar tiles have landed
             umma::gemm(tmem + 128, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sAq, sAq + 8192, 64), 128, 64, 64, 0u);
@@ -297,14 +302,16 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
             umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + cg * 16), d);
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                const int t = cg * 16 + j;
-                if (t < len) p.dVd[((size_t)(start + t) * HV + h) * 128 + row] = d[j];
                 if (j < 8) a0[j] = d[j]; else a1[j - 8] = d[j];
             }
             store_split8(sKb, sKb + 16384, 128, row, 2 * cg, a0);              // the kbar tile is dead: it becomes dVd^T
             store_split8(sKb, sKb + 16384, 128, row, 2 * cg + 1, a1);
         }
         publish_operands();
+        // dVd^T leaves as the chunk tile just built (token columns past the end are exact zeros: Aqk has no such column
+        // and kbar no such row)
+        if (tid == 0 && p.dVd_t)
+            umma::bulk_store(reinterpret_cast<uint8_t*>(p.dVd_t) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES, sKb, umma::CHUNK_TILE_BYTES);
         if (umma::mma_issuer()) {
             umma::gemm(tmem, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sQs, sQs + 16384, 64), 128, 128, 64, 1u);
             umma::mbar_wait(&sh.ldw[0], ((c_end - 1 - c) & 1));               // this chunk's q and nw tiles have landed

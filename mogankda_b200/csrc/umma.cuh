@@ -50,6 +50,18 @@ __device__ __forceinline__ void store_split8(uint8_t* hi, uint8_t* lo, int R, in
     *reinterpret_cast<uint4*>(lo + off) = make_uint4(l[0], l[1], l[2], l[3]);
 }
 
+// reconstruct 8 fp32 values from the hi / lo tiles at (row r, chunk k8)
+__device__ __forceinline__ void load_tile8(const uint8_t* hi, const uint8_t* lo, int R, int r, int k8, float (&v)[8]) {
+    const uint32_t off = tile_chunk_offset(R, r, k8);
+    const uint4 a = *reinterpret_cast<const uint4*>(hi + off), b = *reinterpret_cast<const uint4*>(lo + off);
+    const uint32_t hw[4] = {a.x, a.y, a.z, a.w}, lw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        v[2 * e] = __uint_as_float(hw[e] << 16) + __uint_as_float(lw[e] << 16);
+        v[2 * e + 1] = __uint_as_float(hw[e] & 0xffff0000u) + __uint_as_float(lw[e] & 0xffff0000u);
+    }
+}
+
 // ---- descriptors ---------------------------------------------------------------------------------------------
 // shared-memory matrix descriptor: K-major, SWIZZLE_128B, 8-row groups 1024 B apart (SBO = 64 x 16 B), version 1
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo16 = 1u) {

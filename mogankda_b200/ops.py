@@ -210,7 +210,10 @@ def epilogue_bwd(dy, o_raw, weight, gate, act, eps):
 
 
 def bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, *, dht=None, seg_dht=None,
-           state_v_first=False, want_dh0=True, segments=True, dh=None, dVd=None):
+           state_v_first=False, want_dh0=True, segments=True, store=True):
+    """Reverse state chain.  With ``store`` the per-chunk results leave as tiles for ``bwd_chunk``: dh (state tiles), dVd^T
+    (chunk tiles) and the staged dO (row tiles); a pre-pass that only wants the segment-level gradient passes
+    ``store=False``.  Returns (dh, dVd_t, dO_t, dh0)."""
     dev = nw.device
     NS = lay.NS if segments else lay.N
     p = STRUCTS["MkdaBwdDh"]()
@@ -218,55 +221,37 @@ def bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, *, dht=None, seg_dht=None,
     p.d_o, p.do_dtype = _ptr(d_o), _dt(d_o)
     p.kbar, p.qs, p.gl, p.Aqk, p.nw = _ptr(kbar), _ptr(qs), _ptr(gl), _ptr(Aqk), _ptr(nw)
     p.dht, p.seg_dht, p.state_v_first = _ptr(dht, torch.float32), _ptr(seg_dht, torch.int32), int(state_v_first)
-    if dh is None:
+    dh = dVd_t = dO_t = None
+    if store:
         dh = torch.empty(lay.NC, HV, 128, 128, dtype=torch.float32, device=dev)
-    if dVd is None:
-        dVd = torch.empty(lay.TT, HV, 128, dtype=torch.float32, device=dev)
+        dVd_t = torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=dev)
+        dO_t = torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=dev)
     dh0 = torch.empty(NS, HV, 128, 128, dtype=torch.float32, device=dev) if want_dh0 else None
-    p.dh, p.dVd, p.dh0 = _ptr(dh), _ptr(dVd), _ptr(dh0)
+    p.dh, p.dVd_t, p.dO_t, p.dh0 = _ptr(dh), _ptr(dVd_t), _ptr(dO_t), _ptr(dh0)
     _lib.call("mkda_bwd_dh", p, _stream())
-    return dh, dVd, dh0
+    return dh, dVd_t, dO_t, dh0
 
 
-def bwd_wy(lay, k, v, k_rstd, g_c, beta_e, A, h, Vd, d_o, dVd, HK, HV):
-    """Vd: the forward pass's chunk tiles.  Returns (dX, dbeta_w, dAqk, dL)."""
-    dev = k.device
-    z = lambda *s: torch.empty(lay.TT, HV, *s, dtype=torch.float32, device=dev)      # noqa: E731
-    alloc = torch.empty if lay.covers_all else torch.zeros
-    dAqk, dL, dbeta_w = z(64), z(64), z()
-    dX = alloc(lay.TT, HV, 128, dtype=torch.float32, device=dev)
-    p = STRUCTS["MkdaBwdWy"]()
-    p.L = _layout_struct(lay, HK, HV)
-    p.k, p.v, p.kv_dtype, p.k_rstd = _ptr(k), _ptr(v), _dt(k), _ptr(k_rstd)
-    p.g_c, p.beta, p.A, p.h = _ptr(g_c), _ptr(beta_e), _ptr(A), _ptr(h)
-    p.d_o, p.do_dtype, p.dVd = _ptr(d_o), _dt(d_o), _ptr(dVd)
-    p.Vd, p.dX, p.dbeta_w, p.dAqk, p.dL = _ptr(Vd), _ptr(dX), _ptr(dbeta_w), _ptr(dAqk), _ptr(dL)
-    _lib.call("mkda_bwd_wy", p, _stream())
-    return dX, dbeta_w, dAqk, dL
-
-
-def bwd_tail(lay, q, k, q_rstd, k_rstd, g_c, beta_e, d_o, dX, Vd, h, dh, dAqk, dL, dbeta_w, scale, HK, HV,
-             beta_raw, beta_sigmoid, beta_scale, dv_dtype=torch.float32):
-    """Gradients local to a (chunk, v-head): through the states and through the intra-chunk blocks, in one kernel."""
+def bwd_chunk(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, A, h, dh, Vd, dO_t, dVd_t, scale, HK, HV,
+              beta_raw, beta_sigmoid, beta_scale):
+    """Every gradient local to a (chunk, v-head), in one kernel.  Returns (dq_v, dk_v, dgp, dbeta, dv)."""
     dev = q.device
     alloc = torch.empty if lay.covers_all else torch.zeros
     z = lambda: alloc(lay.TT, HV, 128, dtype=torch.float32, device=dev)      # noqa: E731
     dq_v, dk_v, dgp = z(), z(), z()
     dbeta = alloc(lay.TT, HV, dtype=beta_raw.dtype, device=dev)
-    p = STRUCTS["MkdaBwdTail"]()
+    dv = alloc(lay.TT, HV, 128, dtype=v.dtype, device=dev)
+    p = STRUCTS["MkdaBwdChunk"]()
     p.L = _layout_struct(lay, HK, HV)
-    p.q, p.k, p.qk_dtype, p.q_rstd, p.k_rstd = _ptr(q), _ptr(k), _dt(q), _ptr(q_rstd), _ptr(k_rstd)
-    p.g_c, p.beta = _ptr(g_c), _ptr(beta_e)
-    p.d_o, p.do_dtype, p.dX, p.Vd, p.h, p.dh = _ptr(d_o), _dt(d_o), _ptr(dX), _ptr(Vd), _ptr(h), _ptr(dh)
-    p.dAqk, p.dL, p.dbeta_w, p.scale = _ptr(dAqk), _ptr(dL), _ptr(dbeta_w), scale
+    p.q, p.k, p.v, p.qkv_dtype, p.q_rstd, p.k_rstd = _ptr(q), _ptr(k), _ptr(v), _dt(q), _ptr(q_rstd), _ptr(k_rstd)
+    p.g_c, p.beta = _ptr(g_c, torch.float32), _ptr(beta_e, torch.float32)
+    p.A, p.h, p.dh, p.Vd, p.dO_t, p.dVd_t = _ptr(A), _ptr(h), _ptr(dh), _ptr(Vd), _ptr(dO_t), _ptr(dVd_t)
+    p.scale = scale
     p.beta_raw, p.beta_dtype = _ptr(beta_raw), _dt(beta_raw)
     p.beta_sigmoid, p.beta_scale = int(beta_sigmoid), float(beta_scale)
     p.dq_v, p.dk_v, p.dgp, p.dbeta, p.dbeta_dtype = _ptr(dq_v), _ptr(dk_v), _ptr(dgp), _ptr(dbeta), _dt(dbeta)
-    dv = dX
-    if dv_dtype != torch.float32:      # dv in the dtype of v, written by the kernel from the rows it stages anyway
-        dv = alloc(lay.TT, HV, 128, dtype=dv_dtype, device=dev)
-        p.dv, p.dv_dtype = _ptr(dv), _dt(dv)
-    _lib.call("mkda_bwd_tail", p, _stream())
+    p.dv, p.dv_dtype = _ptr(dv), _dt(dv)
+    _lib.call("mkda_bwd_chunk", p, _stream())
     return dq_v, dk_v, dgp, dbeta, dv
 
 
