@@ -66,7 +66,7 @@ typedef struct {
     const void* x; int x_dtype; int scalar_gate;
     const float* A_log; const float* dt_bias;
     int mode; float lower_bound;
-    const float* dgp;          /* [TT,HV,128] gradient w.r.t. the log2 cumsum as produced by mkda_bwd_chunk */
+    const float* dgp;          /* [NC,HV] fp32 [64][128] tiles: gradient w.r.t. the log2 cumsum as written by mkda_bwd_chunk */
     void* dx; int dx_dtype;    /* [TT,HV,128] or [TT,HV] */
     int part_rows;             /* number of partial rows R (1 <= R <= NC): chunk c accumulates into row c % R */
     float* part_bias;          /* [R,HV,128] ([R,HV] scalar) partial sums of d/d(x+bias), or NULL */
@@ -256,21 +256,22 @@ typedef struct {
     const float* dVd_t;        /* [NC,HV] chunk tiles as written by mkda_bwd_dh */
     float scale;
     const void* beta_raw; int beta_dtype; int beta_sigmoid; float beta_scale;
-    float* dq_v; float* dk_v;  /* [TT,HV,128] per v-head */
-    float* dgp;                /* [TT,HV,128] gradient w.r.t. the log2 cumsum */
+    float* dq_v; float* dk_v;  /* [NC,HV] fp32 [64 tokens][128] tiles per (chunk, v-head); rows past the end are zero */
+    float* dgp;                /* same form: gradient w.r.t. the log2 cumsum */
     void* dbeta; int dbeta_dtype;
-    void* dv; int dv_dtype;    /* [TT,HV,128] */
+    void* dv;                  /* [TT,HV,128] in qkv_dtype */
 } MkdaBwdChunk;
 int mkda_bwd_chunk(const MkdaBwdChunk* p, void* stream);
 
-/* Sum over the v-heads sharing a q/k head, then L2-norm backward; writes dq or dk in the input dtype.
- * Replaces group_reduce_vector (mogan_kda/ops/utils/group_reduce.py:60-79) and l2norm_bwd
+/* Sum over the v-heads sharing a q/k head, then L2-norm backward; writes dq and dk in the input dtype (one launch for
+ * both).  Replaces group_reduce_vector (mogan_kda/ops/utils/group_reduce.py:60-79) and l2norm_bwd
  * (mogan_kda/utils/math.py:38-72). */
 typedef struct {
-    int TT; int HK; int HV;
-    const float* d_v;          /* [TT,HV,128] */
-    const void* x; int x_dtype; const float* rstd;  /* raw q or k and its rstd (NULL = no L2 norm) */
-    void* dx; int dx_dtype;    /* [TT,HK,128] */
+    MkdaLayout L;
+    const float* dq_v; const float* dk_v;          /* [NC,HV] fp32 [64][128] tiles as written by mkda_bwd_chunk */
+    const void* q; const void* k; int x_dtype;     /* raw q, k [TT,HK,128] */
+    const float* q_rstd; const float* k_rstd;      /* [TT,HK], or NULL (no L2 norm) */
+    void* dq; void* dk;                            /* [TT,HK,128] in x_dtype; tokens outside every chunk are not written */
 } MkdaQkGrad;
 int mkda_qk_grad_finish(const MkdaQkGrad* p, void* stream);
 

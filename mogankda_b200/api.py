@@ -121,8 +121,8 @@ class _DeltaRuleFunction(torch.autograd.Function):
         dx, d_bias, d_alog = ops.gate_bwd(lay, x, dgp, cfg["gate_mode"], A_log, dt_bias, cfg["lower_bound"], HV,
                                           want_bias=dt_bias is not None and ctx.needs_input_grad[6],
                                           want_alog=A_log is not None and ctx.needs_input_grad[5])
-        dq = ops.qk_grad_finish(dq_v, q, q_rstd, HK, HV).view_as(q)
-        dk = ops.qk_grad_finish(dk_v, k, k_rstd, HK, HV).view_as(k)
+        dq, dk = ops.qk_grad_finish(lay, dq_v, dk_v, q, k, q_rstd, k_rstd, HK, HV)
+        dq, dk = dq.view_as(q), dk.view_as(k)
         dv = dv.view(B, T, HV, 128)
         if d_alog is not None:
             d_alog = d_alog.view_as(A_log).to(A_log.dtype)

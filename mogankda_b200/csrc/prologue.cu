@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(128) gate_bwd_kernel(const MkdaGateBwd p) {
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
             const int row = warp * 16 + r, rr = row < len ? row : len - 1;
-            vals[r] = *reinterpret_cast<const float4*>(p.dgp + ((size_t)(start + rr) * HV + h) * 128 + 4 * lane);
+            vals[r] = *reinterpret_cast<const float4*>(p.dgp + (((size_t)c * HV + h) * CH + rr) * 128 + 4 * lane);
         }
         float4 run = splat4(0.f);
 #pragma unroll
@@ -268,21 +268,41 @@ __global__ void __launch_bounds__(128) l2norm_rstd_kernel(const MkdaL2Norm p) {
     }
 }
 
-// GVA group sum (fixed order) + L2-norm backward: one warp per (token, q/k head).
+// GVA group sum (fixed order) + L2-norm backward.  Block (chunk, q/k head, which of q / k); warp w takes rows w, w + 4, ...
+// of the chunk.  The per-v-head gradients arrive as the fp32 [64][128] tiles written by the chunk backward.
 __global__ void __launch_bounds__(128) qk_grad_finish_kernel(const MkdaQkGrad p) {
-    const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (row >= p.TT * p.HK) return;
-    const int tok = row / p.HK, hk = row % p.HK, G = p.HV / p.HK;
-    float4 s = splat4(0.f);
-    for (int g = 0; g < G; ++g)
-        s = add4(s, *reinterpret_cast<const float4*>(p.d_v + ((size_t)tok * p.HV + hk * G + g) * 128 + 4 * lane));
-    if (p.rstd) {
-        const float rs = p.rstd[row];
-        const float4 y = scale4(ld4(p.x, p.x_dtype, (size_t)row * 128 + 4 * lane), rs);
-        const float dot = warp_sum(hsum4(mul4(s, y)));
-        s = make_float4((s.x - dot * y.x) * rs, (s.y - dot * y.y) * rs, (s.z - dot * y.z) * rs, (s.w - dot * y.w) * rs);
+    const int HK = p.L.HK, HV = p.L.HV, G = HV / HK;
+    const int c = blockIdx.x / HK, hk = blockIdx.x - c * HK, which = blockIdx.y;
+    const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* d_v = which ? p.dk_v : p.dq_v;
+    const void* x = which ? p.k : p.q;
+    const float* rstd = which ? p.k_rstd : p.q_rstd;
+    void* dx = which ? p.dk : p.dq;
+    for (int r0 = warp; r0 < len; r0 += 16) {
+        float4 s[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {                      // four rows in flight per warp
+            const int r = r0 + 4 * u, rr = r < len ? r : len - 1;
+            s[u] = splat4(0.f);
+            for (int g = 0; g < G; ++g)
+                s[u] = add4(s[u], *reinterpret_cast<const float4*>(d_v + (((size_t)c * HV + hk * G + g) * CH + rr) * 128 + 4 * lane));
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int r = r0 + 4 * u;
+            if (r >= len) break;                           // warp-uniform
+            const size_t rowi = (size_t)(start + r) * HK + hk;
+            float4 t = s[u];
+            if (rstd) {
+                const float rs = rstd[rowi];
+                const float4 y = scale4(ld4(x, p.x_dtype, rowi * 128 + 4 * lane), rs);
+                const float dot = warp_sum(hsum4(mul4(t, y)));
+                t = make_float4((t.x - dot * y.x) * rs, (t.y - dot * y.y) * rs, (t.z - dot * y.z) * rs, (t.w - dot * y.w) * rs);
+            }
+            st4(dx, p.x_dtype, rowi * 128 + 4 * lane, t);
+        }
     }
-    st4(p.dx, p.dx_dtype, (size_t)row * 128 + 4 * lane, s);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -398,10 +418,10 @@ extern "C" int mkda_l2norm_rstd(const MkdaL2Norm* p, void* stream) {
 }
 
 extern "C" int mkda_qk_grad_finish(const MkdaQkGrad* p, void* stream) {
-    if (!p || !p->d_v || !p->dx || (p->rstd && !p->x) || p->HK <= 0 || p->HV % p->HK) return set_error(MKDA_ERR_ARG, "qk_grad_finish: bad argument");
-    const int rows = p->TT * p->HK;
-    if (rows == 0) return MKDA_OK;
-    qk_grad_finish_kernel<<<(rows + 3) / 4, 128, 0, (cudaStream_t)stream>>>(*p);
+    if (!p || !p->dq_v || !p->dk_v || !p->dq || !p->dk || !p->q || !p->k || p->L.HK <= 0 || p->L.HV % p->L.HK)
+        return set_error(MKDA_ERR_ARG, "qk_grad_finish: bad argument");
+    if (p->L.NC == 0) return MKDA_OK;
+    qk_grad_finish_kernel<<<dim3(p->L.NC * p->L.HK, 2), 128, 0, (cudaStream_t)stream>>>(*p);
     return check_launch("qk_grad_finish");
 }
 

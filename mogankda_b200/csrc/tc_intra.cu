@@ -374,31 +374,59 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
 //
 // Every tile operand arrives by bulk copy: S and dS' (state tiles), Vd^T (the forward pass's chunk tile), A (quarter tile),
 // dO (row tile) and dVd^T (chunk tile) as written by the reverse state chain.  Only k, q, g and v pass through registers.
-// Products (M = 128 throughout; a 64-row operand on M leaves lanes 64..127 of its accumulator undefined and unread):
-//   P1  X^T[v x tok]   = V^T - S^T k~^T                  P2  dW^T[v x j] = dVd^T A
-//   P3a D1[i x j]      = dO Vd^T                         P6a Dq^T[c x tok] = S dO^T
+// Products (M = 128 throughout; a 64-row operand on M leaves lanes 64..127 of its accumulator undefined and unread), in
+// issue order:
+//   P7  Db^T[c x tok]  = dS' Vd^T        P6a Dq^T[c x tok] = S dO^T        P3a D1[i x j] = dO Vd^T      (dgl meanwhile)
+//   P1  X^T[v x tok]   = V^T - S^T k~^T  P2  dW^T[v x j] = dVd^T A         (k~ and dVd^T take the place of dS')
 //   P3b D2[64 + i][j]  = dVd X^T (operand shifted so that the result lands in lanes 64..127: both halves of the CTA read
-//                        their accumulators at the same time)        P6b Dk^T[c x tok] = S dX^T
+//                        their accumulators at the same time)              P6b Dk^T[c x tok] = S dX^T
 //   P4  Y[a x j]       = (D2 diag(beta)) A^T             P5  Z[i x j] = A^T Y         dL = -strictlower(Z)
-//   P7  Db^T[c x tok]  = dS' Vd^T                        then the row / column products of the intra-chunk part
-// dX, dAqk, dL and dbeta_w never leave the SM.
+//   then the row / column products of the intra-chunk part, whose operands are rebuilt over the dead tiles while P4 and
+//   P5 run.
+// dX, dAqk, dL and dbeta_w never leave the SM.  The three outputs per token and channel leave as fp32 [64 tokens][128]
+// tiles per (chunk, v-head), staged in shared memory and written by one bulk copy each.
 //
-// Shared memory (U = 32 KB): S [0, 2U) | k~ -> X^T -> dS' hi [2U, 3U) | dO -> dX^T -> dS' lo [3U, 4U) | Vd^T [4U, 5U) |
-// A -> beta dLs [5U, 5U + 16K) | dVd^T -> (D2 beta | Y) -> [Wq; dLs] [5U + 16K, 6U + 16K); the intra-chunk operands
-// (column tiles, [Kr; Qr]) are rebuilt over [0, 4.5U) once the state products are done.
+// Shared memory (U = 32 KB): S [0, 2U) | dS' [2U, 4U) -> k~ -> X^T [2U, 3U), dVd^T [3U, 4U) | dO -> dX^T [4U, 5U) |
+// A -> beta dLs [5U, 5U + 16K) | Vd^T -> dv rows -> (D2 beta | Y) -> [Wq; dLs] [5U + 16K, 6U + 16K); the intra-chunk operands (column
+// tiles, [Kr; Qr]) go to [0, 4.5U), the output tiles to [0, 3U).
 // TMEM columns: X -> Y 0, dW -> Z 64, D1 128, Dq 192, D2 256, Dk 320, Db 384; later R_I 32 I, C_I {304, 448, 256, 128}.
 // ---------------------------------------------------------------------------------------------------------
 constexpr int BU = 32768;
-constexpr int BC_K = 2 * BU, BC_O = 3 * BU, BC_V = 4 * BU, BC_A = 5 * BU, BC_D = 5 * BU + 16384;
+constexpr int BC_T = 2 * BU, BC_D = 3 * BU, BC_O = 4 * BU, BC_A = 5 * BU, BC_V = 5 * BU + 16384;
 constexpr int BWD_CHUNK_SMEM = 6 * BU + 16384 + 1024;
 static_assert(KQ_OFF + 65536 <= BC_A, "the intra-chunk operands must end below the weight tiles");
+// A 64-row (or 64-column) operand issued with M = 128 makes the tensor core read the 8 or 16 KB that follow its tile: A
+// lies in front of the last region, not at the end, so that every such read stays inside the allocation.
 __host__ __device__ constexpr int ccol_off(int I) { return I == 0 ? 304 : I == 1 ? 448 : I == 2 ? 256 : 128; }
 
 struct BwdShared {
-    uint64_t barA, barB, barC, ld0, ld1;
+    uint64_t barA, barB, barC, barD, ld0, ld1;
     uint32_t tmem;
     float beta[CH];
 };
+
+// the intra-chunk operands of rows `n` (this thread's n-th (row, 8-channel) pair): [Kr; Qr] and the column tiles
+__device__ __forceinline__ void stage_intra_operands(uint8_t* base, const float (*sGa)[DK], int tid, int n, const float (&vk)[8],
+                                                     const float (&vq)[8], const float (&vg)[8]) {
+    uint8_t* sKQ = base + KQ_OFF;
+    const int i = tid + n * 512, r = i >> 4, k8 = i & 15, I0 = r >> 4;
+    float ga[8], t8[8];
+    lds8(&sGa[I0][k8 * 8], ga);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) t8[e] = vk[e] * ex2f_(vg[e] - ga[e]);
+    store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + (r & 15), k8, t8);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) t8[e] = vq[e] * ex2f_(vg[e] - ga[e]);
+    store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + 16 + (r & 15), k8, t8);
+#pragma unroll
+    for (int I = 0; I < 4; ++I) {
+        if (I < I0) continue;
+        if (I > I0) lds8(&sGa[I][k8 * 8], ga);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) t8[e] = vk[e] * ex2f_(ga[e] - vg[e]);
+        store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
+    }
+}
 
 template <int DT>
 __global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk p) {
@@ -414,14 +442,16 @@ __global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk
     __shared__ __align__(16) float sGa[4][DK];         // cumsum rows of the four block anchors
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sS = base;                                // S^T [v][K index] state tile (hi, lo)
-    uint8_t* sK = base + BC_K;                         // k~ [tok][K index] -> X^T [v][tok] -> dS'^T hi
-    uint8_t* sO = base + BC_O;                         // dO [tok][v] -> dX^T [v][tok] -> dS'^T lo
-    uint8_t* sV = base + BC_V;                         // Vd^T [v][tok]
+    uint8_t* sT = base + BC_T;                         // dS'^T state tile; later:
+    uint8_t* sK = sT;                                  //   k~ [tok][K index] -> X^T [v][tok]
+    uint8_t* sD = base + BC_D;                         //   dVd^T [v][tok]
+    uint8_t* sO = base + BC_O;                         // dO [tok][v] -> dX^T [v][tok]
+    uint8_t* sV = base + BC_V;                         // Vd^T [v][tok] -> dv rows -> D2 diag(beta) [a][b] | Y [a][j] -> [Wq; dLs]
     uint8_t* sA = base + BC_A;                         // A [i][j] -> diag(beta) strictlower(dL) [i][j]
-    uint8_t* sD = base + BC_D;                         // dVd^T [v][tok] -> D2 diag(beta) [a][b] | Y [a][j] -> [Wq; dLs] 128-row tile
-    uint8_t* sY = sD + 16384;
+    uint8_t* sDA = sV;
+    uint8_t* sY = sV + 16384;
     uint8_t* sKQ = base + KQ_OFF;
-    uint8_t* sWD = sD;                                 // rows 32 I + r = scale strictlower(dAqk)[16 I + r], rows 32 I + 16 + r = strictlower(dL)[16 I + r]
+    uint8_t* sWD = sV;                                 // rows 32 I + r = scale strictlower(dAqk)[16 I + r], rows 32 I + 16 + r = strictlower(dL)[16 I + r]
     uint8_t* sBd = sA;
 
     const int HV = p.L.HV, HK = p.L.HK, c = blockIdx.x / HV, h = blockIdx.x - c * HV;     // heads fastest: CTAs that run together read neighbouring memory
@@ -433,15 +463,15 @@ __global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk
 
     if (warp == 0) umma::tmem_alloc(&sh.tmem, 512);
     if (tid == 0) {
-        umma::mbar_init(&sh.barA, 1); umma::mbar_init(&sh.barB, 1); umma::mbar_init(&sh.barC, 1);
+        umma::mbar_init(&sh.barA, 1); umma::mbar_init(&sh.barB, 1); umma::mbar_init(&sh.barC, 1); umma::mbar_init(&sh.barD, 1);
         umma::mbar_init(&sh.ld0, 1); umma::mbar_init(&sh.ld1, 1);
         umma::fence_barrier_init();
-        umma::mbar_expect_tx(&sh.ld0, umma::STATE_TILE_BYTES + umma::QUARTER_TILE_BYTES + 3 * umma::CHUNK_TILE_BYTES);
-        umma::bulk_load(sS, reinterpret_cast<const uint8_t*>(p.h) + item * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &sh.ld0);
-        umma::bulk_load(sD, reinterpret_cast<const uint8_t*>(p.dVd_t) + item * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld0);
-        umma::bulk_load(sA, reinterpret_cast<const uint8_t*>(p.A) + item * umma::QUARTER_TILE_BYTES, umma::QUARTER_TILE_BYTES, &sh.ld0);
-        umma::bulk_load(sO, reinterpret_cast<const uint8_t*>(p.dO_t) + item * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld0);
+        umma::mbar_expect_tx(&sh.ld0, 2 * umma::STATE_TILE_BYTES + umma::QUARTER_TILE_BYTES + 2 * umma::CHUNK_TILE_BYTES);
+        umma::bulk_load(sT, reinterpret_cast<const uint8_t*>(p.dh) + item * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &sh.ld0);
         umma::bulk_load(sV, reinterpret_cast<const uint8_t*>(p.Vd) + item * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld0);
+        umma::bulk_load(sS, reinterpret_cast<const uint8_t*>(p.h) + item * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &sh.ld0);
+        umma::bulk_load(sO, reinterpret_cast<const uint8_t*>(p.dO_t) + item * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld0);
+        umma::bulk_load(sA, reinterpret_cast<const uint8_t*>(p.A) + item * umma::QUARTER_TILE_BYTES, umma::QUARTER_TILE_BYTES, &sh.ld0);
     }
     if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
     if (tid >= CH && tid < 2 * CH) {
@@ -450,36 +480,68 @@ __global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk
         sRk[r] = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
         sRq[r] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
     }
-
-    // ---- k, g (now: k~ for P1) and q (later: the intra-chunk operands); this thread's column of V for X ---------------
-    float vk[2][8], vq[2][8], vg[2][8], vv[16];
+    // k and g are requested now and used once the first products are under way; v (this thread's column) likewise
+    float vk[2][8], vg[2][8], vv[16];
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
         const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-        const size_t tk = (size_t)(start + rr) * HK + hk;
-        ldg8(p.k, DT, tk * 128 + k8 * 8, vk[n]);
+        ldg8(p.k, DT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, vk[n]);
         ldg8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vg[n]);
-        ldg8(p.q, DT, tk * 128 + k8 * 8, vq[n]);
     }
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
         const int t = cg * 16 + j, tt = t < len ? t : len - 1;
         vv[j] = ld1(p.v, DT, ((size_t)(start + tt) * HV + h) * 128 + row);
     }
+    publish();
+    const uint32_t tmem = sh.tmem;
+
+    // ---- state products whose operands are all copies --------------------------------------------------------------------
+    if (umma::mma_issuer()) {
+        umma::mbar_wait(&sh.ld0, 0);
+        umma::gemm(tmem + 384, umma::opnd_mn(sT, sT + BU, 128), umma::opnd_mn(sV, sV + 16384, 128), 128, 64, 128, 0u);   // P7
+        umma::commit(&sh.barC);
+        umma::gemm(tmem + 192, umma::opnd_mn(sS, sS + BU, 128), umma::opnd_k(sO, sO + 16384, 64), 128, 64, 128, 0u);     // P6a
+        umma::gemm(tmem + 128, umma::opnd_k(sO, sO + 16384, 64), umma::opnd_mn(sV, sV + 16384, 128), 128, 64, 128, 0u);  // P3a
+        umma::commit(&sh.barD);
+    }
+    {   // dgl[c] = sum_v S[c][v] dS'[c][v] from the two tiles: chunk (v row, 8 channels) per thread, four rows each
+        umma::mbar_wait(&sh.ld0, 0);
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const int i = tid + n * 512;
+            const uint32_t off = umma::tile_chunk_offset(128, i >> 4, i & 15);
+            const uint4 a4 = *reinterpret_cast<const uint4*>(sS + off), b4 = *reinterpret_cast<const uint4*>(sS + BU + off);
+            const uint4 c4 = *reinterpret_cast<const uint4*>(sT + off), d4 = *reinterpret_cast<const uint4*>(sT + BU + off);
+            const uint32_t ah[4] = {a4.x, a4.y, a4.z, a4.w}, al[4] = {b4.x, b4.y, b4.z, b4.w};
+            const uint32_t dh[4] = {c4.x, c4.y, c4.z, c4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float s0 = __uint_as_float(ah[e] << 16) + __uint_as_float(al[e] << 16);
+                const float s1 = __uint_as_float(ah[e] & 0xffff0000u) + __uint_as_float(al[e] & 0xffff0000u);
+                const float d0 = __uint_as_float(dh[e] << 16) + __uint_as_float(dl[e] << 16);
+                const float d1 = __uint_as_float(dh[e] & 0xffff0000u) + __uint_as_float(dl[e] & 0xffff0000u);
+                acc[2 * e] = fmaf(s0, d0, acc[2 * e]);
+                acc[2 * e + 1] = fmaf(s1, d1, acc[2 * e + 1]);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 16);
+        if (lane < 16) {
+            *reinterpret_cast<float4*>(&sPart[warp][lane * 8]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            *reinterpret_cast<float4*>(&sPart[warp][lane * 8 + 4]) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        }
+    }
+    // scale k by its L2 statistics (rows past the end become zero); park the anchor rows of g
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
-        const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-        const size_t tk = (size_t)(start + rr) * HK + hk;
-        const float rk = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
-        const float rq = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
-        float t8[8];
+        const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
+        const float rk = sRk[r];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            vk[n][e] *= rk;
-            vq[n][e] *= rq;
-            t8[e] = vk[n][e] * ex2f_(vg[n][e]);
-        }
-        store_split8(sK, sK + 16384, 64, r, k8, t8);
+        for (int e = 0; e < 8; ++e) vk[n][e] *= rk;
         if ((r & 15) == 0) {
             *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8]) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
             *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8 + 4]) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
@@ -488,21 +550,43 @@ __global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk
 #pragma unroll
     for (int j = 0; j < 16; ++j)
         if (cg * 16 + j >= len) vv[j] = 0.f;
+    umma::mbar_wait(&sh.barC, 0);                      // dS' Vd^T done
+    umma::fence_after_sync();
+    __syncthreads();                                   // ... and every thread has read its part of dS': the tile is dead
+    if (tid == 0) {                                    // its second half receives dVd^T, its first half k~
+        umma::mbar_expect_tx(&sh.ld1, umma::CHUNK_TILE_BYTES);
+        umma::bulk_load(sD, reinterpret_cast<const uint8_t*>(p.dVd_t) + item * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld1);
+    }
+    if (tid < DK) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 16; ++w) t += sPart[w][tid];
+        sDgl[tid] = t;
+    }
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+        const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
+        float t8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(vg[n][e]);
+        store_split8(sK, sK + 16384, 64, r, k8, t8);
+    }
     publish();
-    const uint32_t tmem = sh.tmem;
-
-    // ---- batch 1 ------------------------------------------------------------------------------------------------------------
     if (umma::mma_issuer()) {
-        umma::mbar_wait(&sh.ld0, 0);
         umma::gemm(tmem + 0, umma::opnd_k(sS, sS + BU, 128), umma::opnd_k(sK, sK + 16384, 64), 128, 64, 128, 0u);        // P1
-        umma::gemm(tmem + 64, umma::opnd_k(sD, sD + 16384, 128), umma::opnd_mn(sA, sA + 8192, 64), 128, 64, 64, 0u);     // P2
         umma::commit(&sh.barA);
-        umma::gemm(tmem + 192, umma::opnd_mn(sS, sS + BU, 128), umma::opnd_k(sO, sO + 16384, 64), 128, 64, 128, 0u);     // P6a
-        umma::gemm(tmem + 128, umma::opnd_k(sO, sO + 16384, 64), umma::opnd_mn(sV, sV + 16384, 128), 128, 64, 128, 0u);  // P3a
+        umma::mbar_wait(&sh.ld1, 0);
+        umma::gemm(tmem + 64, umma::opnd_k(sD, sD + 16384, 128), umma::opnd_mn(sA, sA + 8192, 64), 128, 64, 64, 0u);     // P2
         umma::commit(&sh.barB);
     }
+    // q for the intra-chunk operands is requested while the products run
+    float vq[2][8];
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+        const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
+        ldg8(p.q, DT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, vq[n]);
+    }
     umma::mbar_wait(&sh.barA, 0);
-    umma::mbar_wait(&sh.ld0, 0);                       // long complete: makes the copied tiles visible to the plain reads below
     umma::fence_after_sync();
     {
         float d[16], x0[8], x1[8];
@@ -511,23 +595,25 @@ __global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk
         for (int j = 0; j < 8; ++j) { x0[j] = vv[j] - d[j]; x1[j] = vv[8 + j] - d[8 + j]; }
         store_split8(sK, sK + 16384, 128, row, 2 * cg, x0);            // k~ is dead: the region now holds X^T
         store_split8(sK, sK + 16384, 128, row, 2 * cg + 1, x1);
+        umma::mbar_wait(&sh.barB, 0);
+        umma::mbar_wait(&sh.barD, 0);                                  // P6a and P3a done long ago: the dO and Vd^T tiles are dead
+        umma::fence_after_sync();
         float dw[16];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 64 + cg * 16), dw);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            const int t = cg * 16 + j;
-            dw[j] *= sh.beta[t];                                       // dX = diag(beta) dW; beta is 0 past the end
-            if (t < len) st1(p.dv, p.dv_dtype, ((size_t)(start + t) * HV + h) * 128 + row, dw[j]);
+            dw[j] *= sh.beta[cg * 16 + j];                             // dX = diag(beta) dW; beta is 0 past the end
+            // dv rows are staged [tok][v] in the dtype of v over the dead Vd^T tile and leave with 16-byte stores below
+            if (DT == MKDA_F32) reinterpret_cast<float*>(sV)[(cg * 16 + j) * 128 + row] = dw[j];
+            else if (DT == MKDA_BF16) reinterpret_cast<__nv_bfloat16*>(sV)[(cg * 16 + j) * 128 + row] = __float2bfloat16_rn(dw[j]);
+            else reinterpret_cast<__half*>(sV)[(cg * 16 + j) * 128 + row] = __float2half_rn(dw[j]);
         }
-        umma::mbar_wait(&sh.barB, 0);                                  // P6a and P3a done: the dO tile is dead
-        umma::fence_after_sync();
 #pragma unroll
         for (int j = 0; j < 8; ++j) { x0[j] = dw[j]; x1[j] = dw[8 + j]; }
         store_split8(sO, sO + 16384, 128, row, 2 * cg, x0);
         store_split8(sO, sO + 16384, 128, row, 2 * cg + 1, x1);
     }
     publish();
-    // ---- batch 2 ------------------------------------------------------------------------------------------------------------
     if (umma::mma_issuer()) {
         umma::Opnd aD = umma::opnd_mn(sD, sD + 16384, 128);            // (m = token, k = v) of the dVd^T tile, moved one 64-group up:
         aD.hi -= 16384; aD.lo -= 16384;                                // rows 0..63 of the operand read the 16 KB in front of each half
@@ -536,7 +622,27 @@ __global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk
         umma::gemm(tmem + 320, umma::opnd_mn(sS, sS + BU, 128), umma::opnd_mn(sO, sO + 16384, 128), 128, 64, 128, 0u);   // P6b
         umma::commit(&sh.barB);
     }
+    {   // dv: 64 rows of 128 values
+        constexpr int ROWB = DT == MKDA_F32 ? 512 : 256;               // bytes per row
+        constexpr int PER = ROWB / 16;                                 // 16-byte pieces per row
+#pragma unroll
+        for (int n = 0; n < 64 * PER / 512; ++n) {
+            const int i = tid + n * 512, r = i / PER, pc = i % PER;
+            if (r < len) {
+                const uint4 val = *reinterpret_cast<const uint4*>(sV + r * ROWB + pc * 16);
+                *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.dv) + ((size_t)(start + r) * HV + h) * ROWB + pc * 16) = val;
+            }
+        }
+    }
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+        const float rq = sRq[(tid + n * 512) >> 4];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) vq[n][e] *= rq;
+    }
+    __syncthreads();                                   // the dv rows have left shared memory
     umma::mbar_wait(&sh.barA, 1);
+    umma::mbar_wait(&sh.barB, 1);                      // every state-phase tile except A is dead now
     umma::fence_after_sync();
     if (q >= 2) {                                      // rows i = row - 64 of D2 = dVd X^T: dbeta_w partials and D2 diag(beta)
         const int i = row - 64;
@@ -563,19 +669,16 @@ __global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk
         }
         pr[0] += __shfl_xor_sync(0xffffffffu, pr[0], 1);
         if ((lane & 1) == 0) sRedW[q - 2][cg * 16 + ((lane >> 1) & 15)] = pr[0];
-        store_split8(sD, sD + 8192, 64, i, 2 * cg, a0);               // dVd^T is dead (P3b done)
-        store_split8(sD, sD + 8192, 64, i, 2 * cg + 1, a1);
+        store_split8(sDA, sDA + 8192, 64, i, 2 * cg, a0);
+        store_split8(sDA, sDA + 8192, 64, i, 2 * cg + 1, a1);
     }
     publish();
     if (tid < CH) sDbw[tid] = sRedW[0][tid] + sRedW[1][tid];
     if (umma::mma_issuer()) {
-        umma::gemm(tmem + 0, umma::opnd_k(sD, sD + 8192, 64), umma::opnd_k(sA, sA + 8192, 64), 128, 64, 64, 0u);          // P4
+        umma::gemm(tmem + 0, umma::opnd_k(sDA, sDA + 8192, 64), umma::opnd_k(sA, sA + 8192, 64), 128, 64, 64, 0u);        // P4
         umma::commit(&sh.barA);
-        // X^T and dX^T are dead once P6b is done as well: the 64 KB they occupy receive the dS' tile
-        umma::mbar_wait(&sh.barB, 1);
-        umma::mbar_expect_tx(&sh.ld1, umma::STATE_TILE_BYTES);
-        umma::bulk_load(sK, reinterpret_cast<const uint8_t*>(p.dh) + item * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &sh.ld1);
     }
+    stage_intra_operands(base, sGa, tid, 0, vk[0], vq[0], vg[0]);     // over the dead S / X^T / dVd^T / dX^T tiles, while P4 runs
     umma::mbar_wait(&sh.barA, 0);
     umma::fence_after_sync();
     if (q < 2) {
@@ -590,40 +693,8 @@ __global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk
     if (umma::mma_issuer()) {
         umma::gemm(tmem + 64, umma::opnd_mn(sA, sA + 8192, 64), umma::opnd_mn(sY, sY + 8192, 64), 128, 64, 64, 0u);       // P5
         umma::commit(&sh.barA);
-        umma::mbar_wait(&sh.ld1, 0);
-        umma::gemm(tmem + 384, umma::opnd_mn(sK, sK + BU, 128), umma::opnd_mn(sV, sV + 16384, 128), 128, 64, 128, 0u);    // P7
-        umma::commit(&sh.barC);
     }
-    {   // dgl[c] = sum_v S[c][v] dS'[c][v] from the two tiles: chunk (v row, 8 channels) per thread, four rows each
-        umma::mbar_wait(&sh.ld1, 0);
-        float acc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-#pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            const int i = tid + n * 512;
-            const uint32_t off = umma::tile_chunk_offset(128, i >> 4, i & 15);
-            const uint4 a4 = *reinterpret_cast<const uint4*>(sS + off), b4 = *reinterpret_cast<const uint4*>(sS + BU + off);
-            const uint4 c4 = *reinterpret_cast<const uint4*>(sK + off), d4 = *reinterpret_cast<const uint4*>(sK + BU + off);
-            const uint32_t ah[4] = {a4.x, a4.y, a4.z, a4.w}, al[4] = {b4.x, b4.y, b4.z, b4.w};
-            const uint32_t dh[4] = {c4.x, c4.y, c4.z, c4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float s0 = __uint_as_float(ah[e] << 16) + __uint_as_float(al[e] << 16);
-                const float s1 = __uint_as_float(ah[e] & 0xffff0000u) + __uint_as_float(al[e] & 0xffff0000u);
-                const float d0 = __uint_as_float(dh[e] << 16) + __uint_as_float(dl[e] << 16);
-                const float d1 = __uint_as_float(dh[e] & 0xffff0000u) + __uint_as_float(dl[e] & 0xffff0000u);
-                acc[2 * e] = fmaf(s0, d0, acc[2 * e]);
-                acc[2 * e + 1] = fmaf(s1, d1, acc[2 * e + 1]);
-            }
-        }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 16);
-        if (lane < 16) {
-            *reinterpret_cast<float4*>(&sPart[warp][lane * 8]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-            *reinterpret_cast<float4*>(&sPart[warp][lane * 8 + 4]) = make_float4(acc[4], acc[5], acc[6], acc[7]);
-        }
-    }
+    stage_intra_operands(base, sGa, tid, 1, vk[1], vq[1], vg[1]);     // the other half, while P5 runs
     umma::mbar_wait(&sh.barA, 1);                      // Z done: A, D2 diag(beta) and Y are dead
     umma::fence_after_sync();
     if (q < 2) {                                       // rows i = row of D1 = dO Vd^T and Z: the weights of the intra-chunk part
@@ -647,36 +718,6 @@ __global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk
             store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + (i & 15), 2 * cg + hf, w8);
             store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + 16 + (i & 15), 2 * cg + hf, d8);
             store_split8(sBd, sBd + 8192, 64, i, 2 * cg + hf, b8);
-        }
-    }
-    __syncthreads();                                   // sPart complete
-    if (tid < DK) {
-        float t = 0.f;
-#pragma unroll
-        for (int w = 0; w < 16; ++w) t += sPart[w][tid];
-        sDgl[tid] = t;
-    }
-    umma::mbar_wait(&sh.barC, 0);                      // dS' Vd^T done: every state-phase tile is dead
-    umma::fence_after_sync();
-    // ---- intra-chunk operands over the dead tiles ----------------------------------------------------------------------------------
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-        const int i = tid + n * 512, r = i >> 4, k8 = i & 15, I0 = r >> 4;
-        float ga[8], t8[8];
-        lds8(&sGa[I0][k8 * 8], ga);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(vg[n][e] - ga[e]);
-        store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + (r & 15), k8, t8);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) t8[e] = vq[n][e] * ex2f_(vg[n][e] - ga[e]);
-        store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + 16 + (r & 15), k8, t8);
-#pragma unroll
-        for (int I = 0; I < 4; ++I) {
-            if (I < I0) continue;
-            if (I > I0) lds8(&sGa[I][k8 * 8], ga);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(ga[e] - vg[n][e]);
-            store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
         }
     }
     publish();
@@ -721,6 +762,10 @@ __global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk
     }
     __syncthreads();
     const float extra = ((sCol[0][row] + sCol[1][row]) + (sCol[2][row] + sCol[3][row])) + ex2f_(gL) * sDgl[row];
+    // the three outputs are staged as fp32 [tok][channel] tiles over the dead operands (rows past the end: zero)
+    float* oq = reinterpret_cast<float*>(base);
+    float* ok = oq + CH * DK;
+    float* og = ok + CH * DK;
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
         const int c0 = 16 * cg + 8 * hf;
@@ -749,14 +794,12 @@ __global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk
             const float dqt = p.scale * aq[r], dkt = -ak[r], dkb = ab[r];
             const float dqr = vr[r] * e, T = vt[r] * e, bt = sh.beta[i], dgn = sDiag[i];
             bsv[r] = kv * T;
-            if (i < len) {
-                float dg = qv * up * dqt + kv * up * dkt - kv * re * dkb;
-                if (i == len - 1) dg += extra;
-                const size_t off = ((size_t)(start + i) * HV + h) * 128 + row;
-                p.dq_v[off] = dqt * up + dqr + dgn * kv;
-                p.dk_v[off] = (dkt * up + dkb * re) + bt * T + dkc[r] + dgn * qv;
-                p.dgp[off] = dg + qv * dqr + kv * bt * T - kv * dkc[r];
-            }
+            float dg = qv * up * dqt + kv * up * dkt - kv * re * dkb;
+            if (i == len - 1) dg += extra;
+            const bool ok_row = i < len;
+            oq[i * DK + row] = ok_row ? dqt * up + dqr + dgn * kv : 0.f;
+            ok[i * DK + row] = ok_row ? (dkt * up + dkb * re) + bt * T + dkc[r] + dgn * qv : 0.f;
+            og[i * DK + row] = ok_row ? dg + qv * dqr + kv * bt * T - kv * dkc[r] : 0.f;
         }
         // sum over the 32 channels of this warp for the 8 rows at once: every exchange halves the number of rows a lane
         // carries (9 shuffles instead of 40); the lane whose bits 4..2 spell the row ends up with its sum
@@ -778,7 +821,14 @@ __global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk
         bsv[0] += __shfl_xor_sync(0xffffffffu, bsv[0], 1);
         if ((lane & 3) == 0) sRed[q][c0 + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = bsv[0];
     }
+    umma::fence_async_smem();
     __syncthreads();
+    if (tid == 0) {
+        const size_t ob = item * (size_t)(CH * DK);
+        umma::bulk_store(p.dq_v + ob, oq, CH * DK * 4);
+        umma::bulk_store(p.dk_v + ob, ok, CH * DK * 4);
+        umma::bulk_store(p.dgp + ob, og, CH * DK * 4);
+    }
     if (tid < len) {
         const size_t th = (size_t)(start + tid) * HV + h;
         float db = sDbw[tid] + ((sRed[0][tid] + sRed[1][tid]) + (sRed[2][tid] + sRed[3][tid]));
@@ -788,6 +838,7 @@ __global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk
         }
         st1(p.dbeta, p.dbeta_dtype, th, db);
     }
+    if (tid == 0) umma::bulk_store_wait_read();
     umma::fence_before_sync();
     __syncthreads();
     if (warp == 0) umma::tmem_dealloc(tmem, 512);

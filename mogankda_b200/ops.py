@@ -237,7 +237,7 @@ def bwd_chunk(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, A, h, dh, Vd, dO_t, dVd
     """Every gradient local to a (chunk, v-head), in one kernel.  Returns (dq_v, dk_v, dgp, dbeta, dv)."""
     dev = q.device
     alloc = torch.empty if lay.covers_all else torch.zeros
-    z = lambda: alloc(lay.TT, HV, 128, dtype=torch.float32, device=dev)      # noqa: E731
+    z = lambda: torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=dev)      # noqa: E731  (fp32 [64][128] tiles)
     dq_v, dk_v, dgp = z(), z(), z()
     dbeta = alloc(lay.TT, HV, dtype=beta_raw.dtype, device=dev)
     dv = alloc(lay.TT, HV, 128, dtype=v.dtype, device=dev)
@@ -250,21 +250,23 @@ def bwd_chunk(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, A, h, dh, Vd, dO_t, dVd
     p.beta_raw, p.beta_dtype = _ptr(beta_raw), _dt(beta_raw)
     p.beta_sigmoid, p.beta_scale = int(beta_sigmoid), float(beta_scale)
     p.dq_v, p.dk_v, p.dgp, p.dbeta, p.dbeta_dtype = _ptr(dq_v), _ptr(dk_v), _ptr(dgp), _ptr(dbeta), _dt(dbeta)
-    p.dv, p.dv_dtype = _ptr(dv), _dt(dv)
+    p.dv = _ptr(dv)
     _lib.call("mkda_bwd_chunk", p, _stream())
     return dq_v, dk_v, dgp, dbeta, dv
 
 
-def qk_grad_finish(d_v, x, rstd, HK, HV):
-    """d_v fp32 [TT,HV,128] -> gradient w.r.t. the raw q or k, [TT,HK,128] in x.dtype."""
-    TT = d_v.shape[0]
-    dx = torch.empty(TT, HK, 128, dtype=x.dtype, device=x.device)
+def qk_grad_finish(lay, dq_v, dk_v, q, k, q_rstd, k_rstd, HK, HV):
+    """dq_v, dk_v: fp32 [NC,HV,64,128] tiles -> gradients w.r.t. the raw q and k, [TT,HK,128] in their dtype."""
+    alloc = torch.empty if lay.covers_all else torch.zeros
+    dq = alloc(lay.TT, HK, 128, dtype=q.dtype, device=q.device)
+    dk = alloc(lay.TT, HK, 128, dtype=k.dtype, device=k.device)
     p = STRUCTS["MkdaQkGrad"]()
-    p.TT, p.HK, p.HV = TT, HK, HV
-    p.d_v, p.x, p.x_dtype, p.rstd = _ptr(d_v, torch.float32), _ptr(x), _dt(x), _ptr(rstd)
-    p.dx, p.dx_dtype = _ptr(dx), _dt(dx)
+    p.L = _layout_struct(lay, HK, HV)
+    p.dq_v, p.dk_v = _ptr(dq_v, torch.float32), _ptr(dk_v, torch.float32)
+    p.q, p.k, p.x_dtype, p.q_rstd, p.k_rstd = _ptr(q), _ptr(k), _dt(q), _ptr(q_rstd), _ptr(k_rstd)
+    p.dq, p.dk = _ptr(dq), _ptr(dk)
     _lib.call("mkda_qk_grad_finish", p, _stream())
-    return dx
+    return dq, dk
 
 
 def state_combine(grp_seg_off, NG, NS, HV, hs, ms, carry=None, reverse=False, want_out=True, want_in=True):

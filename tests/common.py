@@ -231,6 +231,23 @@ def unpack_row_tiles(T, lay, TT):
     return X
 
 
+def pack_plain_tiles(X, lay):
+    """token-major fp [TT, H, 128] -> fp32 [NC, H, 64, 128]: the rows of each chunk, unsplit (zero rows past the end)."""
+    H = X.shape[1]
+    out = torch.zeros(lay.NC, H, 64, 128, device=X.device)
+    for c, s0, n in _chunk_rows(lay):
+        out[c, :, :n] = X[s0:s0 + n].float().permute(1, 0, 2)
+    return out
+
+
+def unpack_plain_tiles(T, lay, TT):
+    X = torch.zeros(TT, T.shape[1], 128, device=T.device)
+    for c, s0, n in _chunk_rows(lay):
+        X[s0:s0 + n] = T[c, :, :n].permute(1, 0, 2)
+        assert float(T[c, :, n:].abs().sum()) == 0.0, "rows past the end of a chunk must be zero"
+    return X
+
+
 def scaled_operands(qn, kn, g_c, lay, scale):
     """fp64 reference of the state kernels' scaled operands from normalised q / k [TT,HK,128] and the log2 cumsum g_c
     [TT,HV,128]: kbar = k 2^(gL - g), qs = scale q 2^g (token-major [TT,HV,128]) and gl = 2^gL [NC,HV,128]."""

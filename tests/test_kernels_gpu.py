@@ -6,8 +6,8 @@ import torch
 from mogankda_b200 import ops
 from mogankda_b200.index import get_layout
 from oracle import kda_oracle as orc
-from tests.common import (VARLEN_CU, make_inputs, pack_chunk_tiles, pack_quarter_tiles, pack_row_tiles, pack_state_tiles,
-                          scaled_operands, unpack_chunk_tiles, unpack_quarter_tiles, unpack_row_tiles,
+from tests.common import (VARLEN_CU, make_inputs, pack_chunk_tiles, pack_quarter_tiles, pack_plain_tiles, pack_row_tiles, pack_state_tiles,
+                          scaled_operands, unpack_chunk_tiles, unpack_plain_tiles, unpack_quarter_tiles, unpack_row_tiles,
                           unpack_state_tiles)
 
 pytestmark = pytest.mark.gpu
@@ -124,7 +124,9 @@ def test_bwd_chunk_gate_and_finish(world):
                                            pack_row_tiles(world["do"], lay), pack_chunk_tiles(f32(bw["dVd"]), lay),
                                            world["scale"], 2, 4, lv["beta"], False, 1.0)
     _err("dv", t_v, bw["dX"].reshape(t_v.shape), KTOL if t_v.dtype == torch.float32 else 2.0 ** -8)
-    _err("dq_v", t_q, bw["dq_v"]); _err("dk_v", t_k, bw["dk_v"]); _err("dgp", t_g, bw["dgp"])
+    TT = world["TT"]
+    _err("dq_v", unpack_plain_tiles(t_q, lay, TT), bw["dq_v"]); _err("dk_v", unpack_plain_tiles(t_k, lay, TT), bw["dk_v"])
+    _err("dgp", unpack_plain_tiles(t_g, lay, TT), bw["dgp"])
     _err("dbeta", t_b, bw["dbeta"].reshape(world["TT"], 4))
     # gate backward (reverse cumsum folded in) against autograd of the oracle's gate
     x = lv["g"].double().requires_grad_(True)
@@ -132,7 +134,7 @@ def test_bwd_chunk_gate_and_finish(world):
     b = lv["dt_bias"].double().requires_grad_(True)
     gd = orc.gate_log_decay(x, o["gate_mode"], A, b, -5.0)
     rx, rA, rb = torch.autograd.grad((gd * bw["dg"]).sum(), [x, A, b])
-    dx, d_bias, d_alog = ops.gate_bwd(lay, lv["g"], f32(bw["dgp"]), o["gate_mode"], lv["A_log"], lv["dt_bias"], -5.0, 4,
+    dx, d_bias, d_alog = ops.gate_bwd(lay, lv["g"], pack_plain_tiles(f32(bw["dgp"]), lay), o["gate_mode"], lv["A_log"], lv["dt_bias"], -5.0, 4,
                                       True, True)
     _err("dx", dx, rx, 2e-4); _err("ddt_bias", d_bias.view_as(rb), rb, 5e-4); _err("dA_log", d_alog, rA, 5e-4)
     # GVA sum + L2-norm backward against autograd of the oracle's l2norm
@@ -140,7 +142,8 @@ def test_bwd_chunk_gate_and_finish(world):
     B, T = lv["q"].shape[:2]
     up = bw["dq_v"].reshape(B, T, 2, 2, 128).sum(3)
     (rq,) = torch.autograd.grad((orc.l2norm(qd) * up).sum(), [qd])
-    dq = ops.qk_grad_finish(f32(bw["dq_v"]), lv["q"], world["q_rstd"], 2, 4)
+    dq, _ = ops.qk_grad_finish(lay, pack_plain_tiles(f32(bw["dq_v"]), lay), pack_plain_tiles(f32(bw["dk_v"]), lay), lv["q"],
+                               lv["k"], world["q_rstd"], world["k_rstd"], 2, 4)
     tol = 1e-5 if lv["q"].dtype == torch.float32 else 2.0 ** -8
     _err("dq", dq.view_as(rq), rq, tol)
 
