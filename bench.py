@@ -48,8 +48,9 @@ def packed_cu(rows=8, row_len=8192, median=500.0, sigma=1.0, seed=0):
     return cu
 
 
-def make_workload(name, rank, device, pin=False):
-    """Returns (host tensors dict, options dict, description)."""
+def make_workload(name, rank, device, pin=False, tokens=65536):
+    """Returns (host tensors dict, options dict, description).  ``tokens``: length of this rank's slice of the long
+    document (``longdoc`` only)."""
     g = torch.Generator().manual_seed(rank)
     r = lambda *s: torch.randn(*s, generator=g)                               # noqa: E731
     if name in ("packed", "1b"):
@@ -67,19 +68,23 @@ def make_workload(name, rank, device, pin=False):
                 if name == "packed" else "1B shape: T=8192, docs 3000/2000/3192")
         dims = dict(tokens=T, HK=hk, HV=hv, docs=len(cu) - 1)
     elif name == "longdoc":
-        T = 65536
+        T = tokens
         t = dict(q=r(1, T, HK, D).bfloat16(), k=r(1, T, HK, D).bfloat16(), v=r(1, T, HV, D).bfloat16(),
                  g=r(1, T, HV, D), beta=r(1, T, HV), A_log=r(HV) * 0.1, dt_bias=r(HV, D) * 0.1)
         opts = dict(gate_mode="kimi", lower_bound=-5.0, beta_mode="sigmoid", beta_scale=1.0, l2=True, epi=None)
-        desc, dims = "one 65536-token document per GPU-shard, kimi gate", dict(tokens=T, HK=HK, HV=HV, docs=1)
+        desc, dims = f"one document, {T} tokens of it on this GPU, kimi gate", dict(tokens=T, HK=HK, HV=HV, docs=1)
     elif name == "gdn":
         B, T, H = 4, 16384, 16
         A_log, x = r(H) * 0.1, r(B, T, H)
         gdec = torch.clamp(-A_log.exp() * torch.nn.functional.softplus(x), min=-5.0)
-        t = dict(q=r(B, T, H, D).bfloat16(), k=r(B, T, H, D).bfloat16(), v=r(B, T, H, D).bfloat16(), g=gdec,
+        # q / k are L2-normalised before the call, as in the reference's own scalar-gate benchmark
+        # (benchmark/bench_gated_delta_rule.py:200-209): with raw N(0,1) keys (|k|^2 ~ 128) the delta rule diverges
+        # within a few dozen tokens in any arithmetic
+        nrm = lambda x: torch.nn.functional.normalize(x, dim=-1).bfloat16()       # noqa: E731
+        t = dict(q=nrm(r(B, T, H, D)), k=nrm(r(B, T, H, D)), v=r(B, T, H, D).bfloat16(), g=gdec,
                  beta=torch.sigmoid(r(B, T, H)), h0=r(B, H, D, D) * 0.02)
         opts = dict(gate_mode="precomputed", beta_mode="precomputed", beta_scale=1.0, l2=False, epi=None, gdn=True)
-        desc, dims = "scalar gate, B=4 x T=16384, H=16, [V,K] initial state", dict(tokens=B * T, HK=H, HV=H, docs=B)
+        desc, dims = "scalar gate, B=4 x T=16384, H=16, L2-normalised q / k, [V,K] initial state", dict(tokens=B * T, HK=H, HV=H, docs=B)
     else:
         raise SystemExit(f"unknown workload {name}")
     if pin:
@@ -218,6 +223,53 @@ class ClockSampler:
         return dict(sm_mhz=statistics.median(busy), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
 
 
+def time_workload(mk, name, rank, world, device, steps=5, warmup=3, cp=None, tokens=65536):
+    """Short device-timed run of another workload (same timing rules as the headline: warm-up, barrier + synchronise on
+    both sides, CUDA events, max over ranks).  Returns (ms per step, tokens per step on this rank)."""
+    import torch.distributed as dist
+    host, opts, _, dims = make_workload(name, rank, device, tokens=tokens)
+    dev = {n: x.to(device) for n, x in host.items()}
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        layer_step(mk, dev, opts, cp)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        layer_step(mk, dev, opts, cp)
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    del dev
+    return float(t.item()), dims["tokens"]
+
+
+def bind_to_gpu_numa_node(index):
+    """Best effort: run this process on the host cores of the NUMA node the GPU hangs off, so that the pinned buffers
+    allocated afterwards are on that node.  Returns the node or None."""
+    try:
+        pr = torch.cuda.get_device_properties(index)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = []
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            a, _, b = part.partition("-")
+            cpus += list(range(int(a), int(b or a) + 1))
+        os.sched_setaffinity(0, set(cpus) & os.sched_getaffinity(0) or os.sched_getaffinity(0))
+        return node
+    except Exception:                                       # noqa: BLE001  (no sysfs, no permission: leave the placement alone)
+        return None
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -248,12 +300,29 @@ def cpu_baseline(seconds=12.0):
                 sample=f"config 1 (B=1,T=256,HK=2,HV=4,D=128 fp32, token-by-token fp64 recurrence + autograd), median of {len(times) - 1} runs after 1 warm-up")
 
 
+def reference_function():
+    """The reference's own CPU implementation of the path: ``ref_chunk_delta_rule`` of its ``tests/ref_kda.py`` (pure torch,
+    fp64), imported by path from the checkout named by the environment variable MOGANKDA_REFERENCE_ROOT.  Without that
+    checkout (the usual case on a GPU box) the restatement in ``oracle/`` is timed instead.  Returns (fn, kind)."""
+    root = os.environ.get("MOGANKDA_REFERENCE_ROOT", "")
+    path = os.path.join(root, "tests", "ref_kda.py")
+    if root and os.path.exists(path):
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("ref_kda", path)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod.ref_chunk_delta_rule, "reference"
+    from oracle import kda_oracle as orc
+    return orc.recurrent_delta_rule, "port"
+
+
 def reference_arm(args, world, rank):
-    """CPU arm: the oracle port on a bounded sample (the first 128 tokens of each of the first documents) of the
-    default workload's shape (HK16/HV32/D128, eda gate, sigmoid beta x2, L2, silu epilogue)."""
+    """CPU arm: the reference's torch oracle (or its restatement, see ``reference_function``) on a bounded sample (the
+    first 128 tokens of every batch row) of the workload's shape (default: HK16/HV32/D128, eda gate, sigmoid beta x2, L2,
+    silu epilogue), all host threads."""
     if rank != 0:
         return
-    from oracle import kda_oracle as orc
+    fn, kind = reference_function()
     torch.set_num_threads(os.cpu_count() or 1)
     t, opts, desc, dims = make_workload(args.workload if args.workload != "longdoc" else "packed", 0, "cpu")
     T = 128
@@ -262,14 +331,14 @@ def reference_arm(args, world, rank):
     def step():
         lv = {n: (x.float().requires_grad_(True) if x.is_floating_point() else x) for n, x in cut.items()}
         if opts.get("gdn"):
-            o, _ = orc.recurrent_delta_rule(lv["q"], lv["k"], lv["v"], lv["g"], lv["beta"], initial_state=lv["h0"],
-                                            state_v_first=True, output_final_state=True)
+            o, _ = fn(lv["q"], lv["k"], lv["v"], lv["g"], lv["beta"], initial_state=lv["h0"],
+                      state_v_first=True, output_final_state=True)
         else:
             norm = dict(weight=lv["ep_w"], gate=lv["ep_gate"], act=opts["epi"]) if opts["epi"] else None
-            o, _ = orc.recurrent_delta_rule(lv["q"], lv["k"], lv["v"], lv["g"], lv["beta"], gate_mode=opts["gate_mode"],
-                                            A_log=lv.get("A_log"), dt_bias=lv.get("dt_bias"), lower_bound=-5.0,
-                                            beta_mode=opts["beta_mode"], beta_scale=opts["beta_scale"],
-                                            use_qk_l2norm_in_kernel=opts["l2"], output_norm=norm)
+            o, _ = fn(lv["q"], lv["k"], lv["v"], lv["g"], lv["beta"], gate_mode=opts["gate_mode"],
+                      A_log=lv.get("A_log"), dt_bias=lv.get("dt_bias"), lower_bound=-5.0,
+                      beta_mode=opts["beta_mode"], beta_scale=opts["beta_scale"],
+                      use_qk_l2norm_in_kernel=opts["l2"], output_norm=norm)
         o.sum().backward()
 
     ntok = cut["q"].shape[0] * T
@@ -280,14 +349,15 @@ def reference_arm(args, world, rank):
         step()
     dt = (time.time() - t0) / args.steps
     val = ntok / dt / 1e6
-    sample = f"first {T} tokens of every batch row of the workload, full head count, token-by-token fp64 recurrence + autograd"
+    sample = (f"first {T} tokens of every batch row of the workload, full head count, token-by-token fp64 recurrence + autograd"
+              + (" (the reference's tests/ref_kda.py)" if kind == "reference" else " (restatement of the reference's tests/ref_kda.py)"))
     print(json.dumps({
         "impl": "reference", "metric": "KDA fwd+bwd Mtok/s per layer", "value": val, "unit": "Mtok/s",
         "n_gpus": world, "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
         "config": {"workload": f"{args.workload}: {desc}", **dims, "D": D, "parallelism": "host cores (rank 0)",
                    "sample_tokens": ntok},
-        "cpu_baseline": dict(value=val, unit="Mtok/s", cores=torch.get_num_threads(), kind="port", sample=sample),
+        "cpu_baseline": dict(value=val, unit="Mtok/s", cores=torch.get_num_threads(), kind=kind, sample=sample),
         "e2e": {"value": val, "unit": "Mtok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0}))
 
@@ -300,6 +370,7 @@ def main():
     ap.add_argument("--workload", default="packed")
     ap.add_argument("--impl", default="mogankda_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the short runs of the other workloads")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -321,6 +392,7 @@ def main():
         from mogankda_b200.cp import ContextParallel
         cp = ContextParallel(dist.group.WORLD)
 
+    numa_node = bind_to_gpu_numa_node(local)
     host, opts, desc, dims = make_workload(args.workload, rank, device, pin=True)
     dev = {n: x.to(device) for n, x in host.items()}
     tokens_per_step = dims["tokens"]
@@ -375,6 +447,15 @@ def main():
 
         e2e_steps(2)
         barrier()
+        # the plain pinned-host -> device copy rate of the same buffers, all ranks at once, for attribution of `e2e`
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(3):
+            tmp = {n: x.to(device, non_blocking=True) for n, x in host.items()}
+        c1.record()
+        barrier()
+        ms_copy = c0.elapsed_time(c1) / 3
+        del tmp
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record()
         e2e_steps(args.steps)
@@ -385,10 +466,40 @@ def main():
         if _lib.device_status() != 0:
             raise SystemExit("a bounded wait inside a tensor-core kernel expired: the run is invalid")
 
-    tms = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)
+    tms = torch.tensor([ms, ms_e2e, ms_copy], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = tms.tolist()
+    ms, ms_e2e, ms_copy = tms.tolist()
+    del dev, host
+    torch.cuda.empty_cache()
+
+    # further workloads in the same record (short runs; every rank takes part, rank 0 reports)
+    extra = {}
+    if args.workload == "packed" and not args.no_extra:
+        if world == 1:
+            other = {}
+            for name in ("1b", "longdoc", "gdn"):
+                t_ms, ntok = time_workload(mk, name, rank, world, device)
+                other[name] = dict(ms_per_step=round(t_ms, 4), mtok_s=round(ntok / t_ms / 1e3, 4), tokens=ntok)
+            extra["other_workloads"] = other
+        else:
+            from mogankda_b200.cp import ContextParallel
+            ctx = ContextParallel(dist.group.WORLD)
+            cpk = {}
+            for mode, per_rank in (("weak", 65536), ("strong", 65536 // world)):
+                t1, _ = time_workload(mk, "longdoc", rank, world, device, tokens=per_rank)          # every GPU alone, no exchange
+                tw, _ = time_workload(mk, "longdoc", rank, world, device, cp=ctx, tokens=per_rank)  # one document over all ranks
+                tot = per_rank * world
+                if mode == "weak":          # per-GPU work fixed: the CP step against the same slice as a stand-alone document
+                    eff = t1 / tw
+                else:                       # total work fixed at 65536 tokens: against W times the one-GPU rate on the whole document
+                    t_full, _ = time_workload(mk, "longdoc", rank, world, device, tokens=tot)
+                    eff = t_full / (world * tw)
+                    cpk[mode + "_ms_1gpu_whole_document"] = round(t_full, 4)
+                cpk[mode] = dict(tokens_total=tot, tokens_per_rank=per_rank, ms_per_step=round(tw, 4),
+                                 mtok_s=round(tot / tw / 1e3, 4), ms_1gpu_same_tokens_per_rank=round(t1, 4),
+                                 efficiency=round(eff, 4))
+            extra["cp"] = cpk
     if rank == 0:
         peaks = measured_peaks()
         total_tokens = tokens_per_step * world * args.steps
@@ -418,10 +529,13 @@ def main():
                        "parallelism": ("cp%d" % world) if cp is not None else ("dp%d" % world),
                        "l2": "per-step working set (> 10 GB of inputs and intermediates) exceeds the 126 MB L2"},
             "e2e": {"value": total_tokens / (ms_e2e * 1e-3) / 1e6, "unit": "Mtok/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": 4},
+                    "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps,
+                    "plain_h2d_copy_ms": round(ms_copy, 3), "plain_h2d_copy_gbs": round(h2d / ms_copy / 1e6, 2),
+                    "host_numa_node": numa_node},
             "gpu_launches": launches, "roofline": roof, "clocks": clocks,
             "kernels_ms_per_step": {k: round(v[0] / args.steps, 4) for k, v in sorted(per_kernel.items(), key=lambda kv: -kv[1][0])},
         }
+        line.update(extra)
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line))

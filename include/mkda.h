@@ -301,8 +301,23 @@ typedef struct {
 } MkdaSelfTest;
 int mkda_selftest_umma(const MkdaSelfTest* p, void* stream);
 
-/* 0 if no bounded wait inside a tensor-core kernel has ever timed out on the current device, else 1 (synchronises). */
+/* Self-test of the bounded waits: a kernel whose only wait can never complete (a barrier nothing arrives on).  After at
+ * most `limit_cycles` SM clock cycles (1 .. 2^24, i.e. under 10 ms) every thread gives up, status[0] is set to 1, the
+ * kernel releases its tensor memory and returns; the device stays usable and the process-wide flag behind
+ * mkda_device_status() is not touched.  status[1] must stay 0.  No counterpart in the reference. */
+typedef struct {
+    int limit_cycles;
+    unsigned int* status;      /* [2] device words, zeroed by the caller */
+} MkdaSelfTestWait;
+int mkda_selftest_wait(const MkdaSelfTestWait* p, void* stream);
+
+/* Every wait inside a tensor-core kernel is bounded (about 70 ms); a wait that expires sets a device-side flag and the
+ * kernel runs on to its exit with undefined results.  mkda_device_status() synchronises the current device and returns
+ * 0 if no wait has expired since the flag was last cleared, else 1: poll it wherever the host synchronises anyway (end
+ * of a step, checkpoint).  While the flag is set later waits give up after ~35 us, so that a broken launch drains fast;
+ * mkda_device_status_clear() (synchronises) resets it and restores the long limit. */
 int mkda_device_status(void);
+int mkda_device_status_clear(void);
 
 const char* mkda_last_error(void);
 int mkda_abi_version(void);

@@ -13,7 +13,7 @@ HEADER = os.path.join(HERE, "..", "include", "mkda.h")
 ENTRY_POINTS = (
     "mkda_gate_cumsum_fwd", "mkda_gate_bwd", "mkda_reduce_partials", "mkda_l2norm_rstd", "mkda_intra_fwd",
     "mkda_recur_fwd", "mkda_out_fwd", "mkda_epilogue_bwd", "mkda_bwd_dh", "mkda_bwd_chunk",
-    "mkda_qk_grad_finish", "mkda_state_combine", "mkda_selftest_umma", "mkda_epilogue_bwd_noalloc",
+    "mkda_qk_grad_finish", "mkda_state_combine", "mkda_selftest_umma", "mkda_selftest_wait", "mkda_epilogue_bwd_noalloc",
 )
 ENUMS = {}
 STRUCTS = {}
@@ -103,3 +103,11 @@ def device_status():
     lib.mkda_device_status.argtypes = []
     return int(lib.mkda_device_status())
 
+
+
+def device_status_clear():
+    """Synchronises the current device and clears the expired-wait flag (restores the long wait limit)."""
+    lib = load()
+    lib.mkda_device_status_clear.restype = ctypes.c_int
+    lib.mkda_device_status_clear.argtypes = []
+    return int(lib.mkda_device_status_clear())

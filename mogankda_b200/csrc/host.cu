@@ -59,6 +59,7 @@ int ensure_smem(const void* func, int bytes, const char* what) {
 
 namespace mkda {
 int selftest_status(unsigned int* out);
+int selftest_status_clear();
 }
 extern "C" int mkda_device_status(void) {
     unsigned int f = 0, any = 0;
@@ -69,6 +70,15 @@ extern "C" int mkda_device_status(void) {
     if (mkda::tc_intra_status(&f) == 0) any |= f;
     return (int)any;
 }
+extern "C" int mkda_device_status_clear(void) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    int rc = 0;
+    rc |= mkda::selftest_status_clear();
+    rc |= mkda::tc_chunk_status_clear();
+    rc |= mkda::tc_recur_status_clear();
+    rc |= mkda::tc_intra_status_clear();
+    return rc;
+}
 extern "C" const char* mkda_last_error(void) { return mkda::g_err; }
 extern "C" int mkda_abi_version(void) { return 3; }
 extern "C" int mkda_struct_sizes(int* out, int n) {
@@ -76,7 +86,7 @@ extern "C" int mkda_struct_sizes(int* out, int n) {
         (int)sizeof(MkdaLayout),   (int)sizeof(MkdaGateFwd),  (int)sizeof(MkdaGateBwd),     (int)sizeof(MkdaReduce),
         (int)sizeof(MkdaL2Norm),   (int)sizeof(MkdaIntraFwd), (int)sizeof(MkdaRecurFwd),    (int)sizeof(MkdaOutFwd),
         (int)sizeof(MkdaEpilogueBwd), (int)sizeof(MkdaEpilogueBwdNoAlloc), (int)sizeof(MkdaBwdDh), (int)sizeof(MkdaBwdChunk),
-        (int)sizeof(MkdaQkGrad),   (int)sizeof(MkdaCombine), (int)sizeof(MkdaSelfTest)};
+        (int)sizeof(MkdaQkGrad),   (int)sizeof(MkdaCombine), (int)sizeof(MkdaSelfTest), (int)sizeof(MkdaSelfTestWait)};
     const int cnt = (int)(sizeof(sizes) / sizeof(sizes[0]));
     for (int i = 0; i < n && i < cnt; ++i) out[i] = sizes[i];
     return cnt;

@@ -14,10 +14,13 @@ int ensure_smem(const void* func, int bytes, const char* what);
 int sm_count();
 int launch_out_fwd_tc(const MkdaOutFwd* p, cudaStream_t stream);
 int tc_chunk_status(unsigned int* out);
+int tc_chunk_status_clear();
 int launch_recur_fwd_tc(const MkdaRecurFwd* p, cudaStream_t stream);
 int launch_bwd_dh_tc(const MkdaBwdDh* p, cudaStream_t stream);
 int tc_recur_status(unsigned int* out);
+int tc_recur_status_clear();
 int launch_intra_fwd_tc(const MkdaIntraFwd* p, cudaStream_t stream);
 int launch_bwd_chunk_tc(const MkdaBwdChunk* p, cudaStream_t stream);
 int tc_intra_status(unsigned int* out);
+int tc_intra_status_clear();
 }  // namespace mkda

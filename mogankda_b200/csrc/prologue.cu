@@ -3,6 +3,8 @@
 //   L2-norm statistics, GVA group sum + L2-norm backward, gated RMSNorm backward, deterministic partial reductions.
 // All of them move each tensor once with 128-bit accesses; one warp covers one 128-wide row.
 #include "common.cuh"
+#include <stdio.h>
+
 #include "host.h"
 
 namespace mkda {
@@ -456,8 +458,12 @@ extern "C" int mkda_epilogue_bwd_noalloc(const MkdaEpilogueBwdNoAlloc* p, void* 
     if (!p || !p->dy || !p->o_raw || !p->gate || !p->d_o || !p->dgate || !p->dweight)
         return set_error(MKDA_ERR_ARG, "epilogue_bwd_noalloc: null argument");
     if (p->rows < 0 || p->rows > MKDA_NOALLOC_MAX_ROWS)
-        return set_error(MKDA_ERR_ARG, "epilogue_bwd_noalloc: rows exceeds the built-in scratch (MKDA_NOALLOC_MAX_ROWS = 262144); "
-                                       "use mkda_epilogue_bwd with a caller-provided part_w");
+    {
+        static char msg[192];
+        snprintf(msg, sizeof(msg), "epilogue_bwd_noalloc: rows exceeds the built-in scratch (MKDA_NOALLOC_MAX_ROWS = %d); "
+                                   "use mkda_epilogue_bwd with a caller-provided part_w", MKDA_NOALLOC_MAX_ROWS);
+        return set_error(MKDA_ERR_ARG, msg);
+    }
     float* scratch = nullptr;
     if (int e = noalloc_scratch(&scratch)) return e;
     const int nblk = epilogue_part_rows(p->rows);

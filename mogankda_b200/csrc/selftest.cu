@@ -80,8 +80,30 @@ __global__ void __launch_bounds__(128, 1) selftest_umma_kernel(const MkdaSelfTes
     if (warp == 0) umma::tmem_dealloc(tmem, 128);
 }
 
+// A wait that nothing will ever satisfy: every thread waits on a barrier without arrivals for at most `limit_cycles`,
+// reports the expiry in the caller's own status word and leaves in good order (tensor memory released).
+__global__ void __launch_bounds__(128, 1) selftest_wait_kernel(const MkdaSelfTestWait p) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t tmem_slot;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    if (warp == 0) umma::tmem_alloc(&tmem_slot, 32);
+    if (tid == 0) { umma::mbar_init(&bar, 1); umma::fence_barrier_init(); }
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const bool ok = umma::mbar_wait_limited(&bar, 0, p.limit_cycles, p.status);
+    if (ok && tid == 0) p.status[1] = 1u;          // must never happen
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) umma::tmem_dealloc(tmem_slot, 32);
+}
+
 int selftest_status(unsigned int* out) {
     return cudaMemcpyFromSymbol(out, umma::g_timeout_flag, sizeof(unsigned int)) == cudaSuccess ? 0 : -1;
+}
+int selftest_status_clear() {
+    const unsigned int z = 0;
+    return cudaMemcpyToSymbol(umma::g_timeout_flag, &z, sizeof(z)) == cudaSuccess ? 0 : -1;
 }
 
 }  // namespace mkda
@@ -95,4 +117,11 @@ extern "C" int mkda_selftest_umma(const MkdaSelfTest* p, void* stream) {
     if (int e = ensure_smem((const void*)selftest_umma_kernel, smem, "selftest_umma")) return e;
     selftest_umma_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(*p);
     return check_launch("selftest_umma");
+}
+
+extern "C" int mkda_selftest_wait(const MkdaSelfTestWait* p, void* stream) {
+    if (!p || !p->status) return set_error(MKDA_ERR_ARG, "selftest_wait: null argument");
+    if (p->limit_cycles < 1 || p->limit_cycles > (1 << 24)) return set_error(MKDA_ERR_ARG, "selftest_wait: limit_cycles must be in [1, 2^24]");
+    selftest_wait_kernel<<<1, 128, 0, (cudaStream_t)stream>>>(*p);
+    return check_launch("selftest_wait");
 }

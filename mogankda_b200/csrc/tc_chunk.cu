@@ -145,6 +145,10 @@ __global__ void __launch_bounds__(512, 1) out_fwd_tc_kernel(const MkdaOutFwd p) 
 int tc_chunk_status(unsigned int* out) {
     return cudaMemcpyFromSymbol(out, umma::g_timeout_flag, sizeof(unsigned int)) == cudaSuccess ? 0 : -1;
 }
+int tc_chunk_status_clear() {
+    const unsigned int z = 0;
+    return cudaMemcpyToSymbol(umma::g_timeout_flag, &z, sizeof(z)) == cudaSuccess ? 0 : -1;
+}
 
 template <int GDT>
 static int launch_out_fwd_tc_t(const MkdaOutFwd* p, cudaStream_t stream) {

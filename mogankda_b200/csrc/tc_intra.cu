@@ -863,6 +863,10 @@ int launch_bwd_chunk_tc(const MkdaBwdChunk* p, cudaStream_t stream) {
 int tc_intra_status(unsigned int* out) {
     return cudaMemcpyFromSymbol(out, umma::g_timeout_flag, sizeof(unsigned int)) == cudaSuccess ? 0 : -1;
 }
+int tc_intra_status_clear() {
+    const unsigned int z = 0;
+    return cudaMemcpyToSymbol(umma::g_timeout_flag, &z, sizeof(z)) == cudaSuccess ? 0 : -1;
+}
 
 template <int DT>
 static int launch_intra_fwd_tc_t(const MkdaIntraFwd* p, cudaStream_t stream) {

@@ -172,6 +172,10 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
 int tc_recur_status(unsigned int* out) {
     return cudaMemcpyFromSymbol(out, umma::g_timeout_flag, sizeof(unsigned int)) == cudaSuccess ? 0 : -1;
 }
+int tc_recur_status_clear() {
+    const unsigned int z = 0;
+    return cudaMemcpyToSymbol(umma::g_timeout_flag, &z, sizeof(z)) == cudaSuccess ? 0 : -1;
+}
 
 int launch_recur_fwd_tc(const MkdaRecurFwd* p, cudaStream_t stream) {
     auto kern = recur_fwd_tc_kernel;

@@ -162,12 +162,12 @@ __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence
 __device__ __forceinline__ void commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Waits for the phase of `bar` with the given parity, for at most `limit` SM clock cycles.  On expiry 1 is written to
+// `*flag` and false is returned: the caller goes on (with garbage) to its exit, so a launch never hangs.  try_wait parks
+// the thread for at most the hinted microsecond per attempt, so waiting warps do not compete for issue slots with the
+// thread issuing MMAs.
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, long long limit, unsigned int* flag) {
     const uint32_t addr = smem_u32(bar);
-    // Bounded by wall time (SM clock): ~70 ms for the first wait that fails on a device, ~35 us afterwards, so a broken
-    // launch drains quickly instead of serialising one long timeout per CTA.  try_wait parks the thread for at most the
-    // hinted microsecond per attempt, so waiting warps do not compete for issue slots with the thread issuing MMAs.
-    const long long limit = *(volatile unsigned int*)&g_timeout_flag ? (1ll << 16) : (1ll << 27);
     const long long t0 = clock64();
     for (;;) {
         uint32_t ok;
@@ -177,8 +177,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         if (ok) return true;
         if (clock64() - t0 > limit) break;
     }
-    atomicExch(&g_timeout_flag, 1u);
+    atomicExch(flag, 1u);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    // Bounded by wall time (SM clock): ~70 ms for the first wait that fails on a device, ~35 us afterwards, so a broken
+    // launch drains quickly instead of serialising one long timeout per CTA.  The flag stays set until
+    // mkda_device_status_clear().
+    const long long limit = *(volatile unsigned int*)&g_timeout_flag ? (1ll << 16) : (1ll << 27);
+    return mbar_wait_limited(bar, parity, limit, &g_timeout_flag);
 }
 
 // ---- bulk copies of whole operand tiles ---------------------------------------------------------------------------

@@ -65,7 +65,7 @@ def test_packed_documents_match_standalone_runs_and_the_oracle(packed):
         assert torch.equal(o1, o[:, s:e]) and torch.equal(ht1, ht[n:n + 1])
         for name in ("q", "k", "v", "g", "beta", "ep_gate"):
             assert torch.equal(lv1[name].grad, lv[name].grad[:, s:e]), name
-        if e - s <= 400:        # oracle parity on the whole document (HK16 / HV32 / D128)
+        if e - s <= 1500:       # oracle parity on the whole document (HK16 / HV32 / D128)
             x = {k: t.double().clone().requires_grad_(True) if t.is_floating_point() else t for k, t in sub.items()}
             oo, _ = orc.chunked_delta_rule(x["q"], x["k"], x["v"], x["g"], x["beta"], gate_mode=opts["gate_mode"], A_log=x["A_log"],
                                            dt_bias=x["dt_bias"], beta_mode=opts["beta_mode"], beta_scale=opts["beta_scale"],

@@ -66,6 +66,18 @@ def test_chooser_cuts_a_skewed_packed_batch_and_results_agree():
     b = run(mk.chunk_kda, lv, do, dht, opts, None, auto_cp=False)
     for n in a:
         check(n, a[n], b[n].float())                                         # 16-bit results: both sides are rounded
+    # ... and, per document, with the oracle: the long (segmented) document and one short one, each run on its own
+    for d in (0, 7):
+        s, e = cu[d], cu[d + 1]
+        sub = {n: (t[:, s:e].contiguous() if t.dim() >= 3 and t.shape[1] == T else t) for n, t in lv.items()}
+        sub["h0"] = lv["h0"][d:d + 1]
+        o1 = dict(opts, cu_seqlens=None)
+        ref = run(orc.chunked_delta_rule, sub, do[:, s:e], dht[d:d + 1], o1, None, f64=True)
+        check(f"o[doc {d}]", a["o"][:, s:e], ref["o"])
+        check(f"ht[doc {d}]", a["ht"][d:d + 1], ref["ht"])
+        for n in ("dq", "dk", "dv", "dg", "dbeta"):
+            check(f"{n}[doc {d}]", a[n][:, s:e], ref[n])
+        check(f"dh0[doc {d}]", a["dh0"][d:d + 1], ref["dh0"])
 
 
 def test_api_errors_follow_the_reference_conventions():

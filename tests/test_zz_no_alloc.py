@@ -36,11 +36,31 @@ def _inputs(rows, dtype, seed):
 
 
 def test_noalloc_entry_point_matches_regular_one_on_two_calls_in_a_row():
-    for rows, dtype, act, seed in ((64 * 300 + 17, torch.bfloat16, "silu", 1), (200, torch.float32, "sigmoid", 2)):
+    # the third size is past 64 * MKDA_EPILOGUE_MAX_PART_ROWS rows, where a block walks more than one group of rows
+    assert 64 * 1300 + 5 > 64 * _lib.MKDA_EPILOGUE_MAX_PART_ROWS and 64 * 1300 + 5 <= _lib.MKDA_NOALLOC_MAX_ROWS
+    for rows, dtype, act, seed in ((64 * 300 + 17, torch.bfloat16, "silu", 1), (200, torch.float32, "sigmoid", 2),
+                                   (64 * 1300 + 5, torch.bfloat16, "silu", 3)):
         dy, o_raw, w, gate = _inputs(rows, dtype, seed)
         ref_do, ref_dgate, ref_dw = ops.epilogue_bwd(dy, o_raw, w, gate, act, 1e-6)
-        d_o, dgate, dw = _call_noalloc(dy, o_raw, w, gate, act, 1e-6)
+        # the property in the name: between building the argument struct and the end of the call no device memory is
+        # taken, neither from the driver nor from torch's caching allocator
+        d_o = torch.empty(rows, 128, dtype=torch.float32, device="cuda")
+        dgate = torch.empty_like(gate)
+        dw = torch.full((128,), float("nan"), dtype=torch.float32, device="cuda")
+        p = STRUCTS["MkdaEpilogueBwdNoAlloc"]()
+        p.rows = rows
+        p.dy, p.dy_dtype, p.o_raw = dy.data_ptr(), ops._dt(dy), o_raw.data_ptr()
+        p.norm_w, p.norm_w_dtype = w.data_ptr(), ops._dt(w)
+        p.gate, p.gate_dtype, p.act, p.eps = gate.data_ptr(), ops._dt(gate), ops.ACTS[act], 1e-6
+        p.d_o, p.dgate, p.dgate_dtype, p.dweight = d_o.data_ptr(), dgate.data_ptr(), ops._dt(dgate), dw.data_ptr()
+        stream = torch.cuda.current_stream().cuda_stream
+        _lib.call("mkda_epilogue_bwd_noalloc", p, stream)          # the first call on the device may look up the scratch address
         torch.cuda.synchronize()
+        free0, alloc0, reserved0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+        _lib.call("mkda_epilogue_bwd_noalloc", p, stream)
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free0
+        assert torch.cuda.memory_allocated() == alloc0 and torch.cuda.memory_reserved() == reserved0
         # same kernels, same summation tree: the results are expected to be identical, not merely close
         assert torch.equal(d_o, ref_do.view_as(d_o))
         assert torch.equal(dgate, ref_dgate)
@@ -56,3 +76,4 @@ def test_noalloc_entry_point_rejects_sizes_beyond_its_scratch():
         setattr(p, f, one.data_ptr())
     rc = lib.mkda_epilogue_bwd_noalloc(ctypes.byref(p), None)
     assert rc == _lib.MKDA_ERR_ARG and b"exceeds the built-in scratch" in lib.mkda_last_error()
+    assert str(_lib.MKDA_NOALLOC_MAX_ROWS).encode() in lib.mkda_last_error()
