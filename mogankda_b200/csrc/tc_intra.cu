@@ -400,7 +400,7 @@ static_assert(KQ_OFF + 65536 <= BC_A, "the intra-chunk operands must end below t
 __host__ __device__ constexpr int ccol_off(int I) { return I == 0 ? 304 : I == 1 ? 448 : I == 2 ? 256 : 128; }
 
 struct BwdShared {
-    uint64_t barA, barB, barC, barD, ld0, ld1;
+    uint64_t barA, barB, barC, barD, ld0, ld1, ld2;
     uint32_t tmem;
     float beta[CH];
 };
@@ -428,8 +428,16 @@ __device__ __forceinline__ void stage_intra_operands(uint8_t* base, const float 
     }
 }
 
+// CTAs are persistent: one per SM walks the items gridDim.x apart.  While the epilogue of an item runs, the next item's
+// dS', Vd^T and A tiles are already travelling (their regions are free by then); S and dO follow as soon as the output
+// tiles have left shared memory.  One elected lane of warp 0 issues every tensor-core product and the tile loads; lane 0
+// of warp 15 sends the output tiles off and requests S / dO of the next item.  (A 17th, issue-only warp was tried: five
+// warps on one SM sub-partition cap the kernel at 96 registers per thread and the spills cost far more than the overlap
+// returns.)
+constexpr int BWD_CHUNK_THREADS = 512;
+
 template <int DT>
-__global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk p) {
+__global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ BwdShared sh;
     __shared__ float sDiag[CH], sDbw[CH];
@@ -453,392 +461,428 @@ __global__ void __launch_bounds__(512, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk
     uint8_t* sKQ = base + KQ_OFF;
     uint8_t* sWD = sV;                                 // rows 32 I + r = scale strictlower(dAqk)[16 I + r], rows 32 I + 16 + r = strictlower(dL)[16 I + r]
     uint8_t* sBd = sA;
+    // output tiles, fp32 [tok][channel]: dq and dk over the dead S tile, dg over the dead dX^T tile (the dS' region
+    // between them already receives the next item's tile)
+    float* oq = reinterpret_cast<float*>(base);
+    float* ok = oq + CH * DK;
+    float* og = reinterpret_cast<float*>(sO);
 
-    const int HV = p.L.HV, HK = p.L.HK, c = blockIdx.x / HV, h = blockIdx.x - c * HV;     // heads fastest: CTAs that run together read neighbouring memory
-    const int hk = h / (HV / HK);
-    const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+    const int HV = p.L.HV, HK = p.L.HK;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
-    const size_t item = (size_t)c * HV + h;
+    const int total = p.L.NC * HV, stride = gridDim.x;
+    const bool sender = tid == 15 * 32;                // sends the output tiles off; requests S / dO of the next item
+
+    auto fetch_early = [&](size_t it) {                // dS', Vd^T, A: their regions are free once the intra-chunk products are done
+        umma::mbar_expect_tx(&sh.ld0, umma::STATE_TILE_BYTES + umma::CHUNK_TILE_BYTES + umma::QUARTER_TILE_BYTES);
+        umma::bulk_load(sT, reinterpret_cast<const uint8_t*>(p.dh) + it * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &sh.ld0);
+        umma::bulk_load(sV, reinterpret_cast<const uint8_t*>(p.Vd) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld0);
+        umma::bulk_load(sA, reinterpret_cast<const uint8_t*>(p.A) + it * umma::QUARTER_TILE_BYTES, umma::QUARTER_TILE_BYTES, &sh.ld0);
+    };
+    auto fetch_late = [&](size_t it) {                 // S, dO: their regions hold the output tiles until those have left
+        umma::mbar_expect_tx(&sh.ld2, umma::STATE_TILE_BYTES + umma::CHUNK_TILE_BYTES);
+        umma::bulk_load(sS, reinterpret_cast<const uint8_t*>(p.h) + it * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &sh.ld2);
+        umma::bulk_load(sO, reinterpret_cast<const uint8_t*>(p.dO_t) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld2);
+    };
 
     if (warp == 0) umma::tmem_alloc(&sh.tmem, 512);
     if (tid == 0) {
         umma::mbar_init(&sh.barA, 1); umma::mbar_init(&sh.barB, 1); umma::mbar_init(&sh.barC, 1); umma::mbar_init(&sh.barD, 1);
-        umma::mbar_init(&sh.ld0, 1); umma::mbar_init(&sh.ld1, 1);
+        umma::mbar_init(&sh.ld0, 1); umma::mbar_init(&sh.ld1, 1); umma::mbar_init(&sh.ld2, 1);
         umma::fence_barrier_init();
-        umma::mbar_expect_tx(&sh.ld0, 2 * umma::STATE_TILE_BYTES + umma::QUARTER_TILE_BYTES + 2 * umma::CHUNK_TILE_BYTES);
-        umma::bulk_load(sT, reinterpret_cast<const uint8_t*>(p.dh) + item * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &sh.ld0);
-        umma::bulk_load(sV, reinterpret_cast<const uint8_t*>(p.Vd) + item * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld0);
-        umma::bulk_load(sS, reinterpret_cast<const uint8_t*>(p.h) + item * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &sh.ld0);
-        umma::bulk_load(sO, reinterpret_cast<const uint8_t*>(p.dO_t) + item * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld0);
-        umma::bulk_load(sA, reinterpret_cast<const uint8_t*>(p.A) + item * umma::QUARTER_TILE_BYTES, umma::QUARTER_TILE_BYTES, &sh.ld0);
-    }
-    if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
-    if (tid >= CH && tid < 2 * CH) {
-        const int r = tid - CH;
-        const size_t tk = (size_t)(start + (r < len ? r : len - 1)) * HK + hk;
-        sRk[r] = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
-        sRq[r] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
-    }
-    // k and g are requested now and used once the first products are under way; v (this thread's column) likewise
-    float vk[2][8], vg[2][8], vv[16];
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-        const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-        ldg8(p.k, DT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, vk[n]);
-        ldg8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vg[n]);
-    }
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const int t = cg * 16 + j, tt = t < len ? t : len - 1;
-        vv[j] = ld1(p.v, DT, ((size_t)(start + tt) * HV + h) * 128 + row);
     }
     publish();
     const uint32_t tmem = sh.tmem;
+    if (tid == 0 && (int)blockIdx.x < total) fetch_early(blockIdx.x);
+    if (sender && (int)blockIdx.x < total) fetch_late(blockIdx.x);
+    // phase counters of the barriers (every thread walks the same sequence of phases)
+    uint32_t nA = 0, nB = 0, nC = 0, nD = 0, n0 = 0, n1 = 0, n2 = 0;
 
-    // ---- state products whose operands are all copies --------------------------------------------------------------------
-    if (umma::mma_issuer()) {
-        umma::mbar_wait(&sh.ld0, 0);
-        umma::gemm(tmem + 384, umma::opnd_mn(sT, sT + BU, 128), umma::opnd_mn(sV, sV + 16384, 128), 128, 64, 128, 0u);   // P7
-        umma::commit(&sh.barC);
-        umma::gemm(tmem + 192, umma::opnd_mn(sS, sS + BU, 128), umma::opnd_k(sO, sO + 16384, 64), 128, 64, 128, 0u);     // P6a
-        umma::gemm(tmem + 128, umma::opnd_k(sO, sO + 16384, 64), umma::opnd_mn(sV, sV + 16384, 128), 128, 64, 128, 0u);  // P3a
-        umma::commit(&sh.barD);
-    }
-    {   // dgl[c] = sum_v S[c][v] dS'[c][v] from the two tiles: chunk (v row, 8 channels) per thread, four rows each
-        umma::mbar_wait(&sh.ld0, 0);
-        float acc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-#pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            const int i = tid + n * 512;
-            const uint32_t off = umma::tile_chunk_offset(128, i >> 4, i & 15);
-            const uint4 a4 = *reinterpret_cast<const uint4*>(sS + off), b4 = *reinterpret_cast<const uint4*>(sS + BU + off);
-            const uint4 c4 = *reinterpret_cast<const uint4*>(sT + off), d4 = *reinterpret_cast<const uint4*>(sT + BU + off);
-            const uint32_t ah[4] = {a4.x, a4.y, a4.z, a4.w}, al[4] = {b4.x, b4.y, b4.z, b4.w};
-            const uint32_t dh[4] = {c4.x, c4.y, c4.z, c4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float s0 = __uint_as_float(ah[e] << 16) + __uint_as_float(al[e] << 16);
-                const float s1 = __uint_as_float(ah[e] & 0xffff0000u) + __uint_as_float(al[e] & 0xffff0000u);
-                const float d0 = __uint_as_float(dh[e] << 16) + __uint_as_float(dl[e] << 16);
-                const float d1 = __uint_as_float(dh[e] & 0xffff0000u) + __uint_as_float(dl[e] & 0xffff0000u);
-                acc[2 * e] = fmaf(s0, d0, acc[2 * e]);
-                acc[2 * e + 1] = fmaf(s1, d1, acc[2 * e + 1]);
+    for (int item = blockIdx.x; item < total; item += stride) {
+        const int c = item / HV, h = item - c * HV;    // heads fastest: CTAs that run together read neighbouring memory
+        const int hk = h / (HV / HK);
+        const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+        const bool more = item + stride < total;
+
+        // ---- state products whose operands are all copies | register loads, dgl ------------------------
+        if (umma::mma_issuer()) {
+            umma::mbar_wait(&sh.ld0, n0 & 1);
+            umma::fence_after_sync();
+            umma::gemm(tmem + 384, umma::opnd_mn(sT, sT + BU, 128), umma::opnd_mn(sV, sV + 16384, 128), 128, 64, 128, 0u);   // P7
+            umma::commit(&sh.barC);
+            umma::mbar_wait(&sh.ld2, n2 & 1);
+            umma::gemm(tmem + 192, umma::opnd_mn(sS, sS + BU, 128), umma::opnd_k(sO, sO + 16384, 64), 128, 64, 128, 0u);     // P6a
+            umma::gemm(tmem + 128, umma::opnd_k(sO, sO + 16384, 64), umma::opnd_mn(sV, sV + 16384, 128), 128, 64, 128, 0u);  // P3a
+            umma::commit(&sh.barD);
+        }
+        float vk[2][8], vg[2][8], vq[2][8], vv[16];
+        {
+            if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
+            if (tid >= CH && tid < 2 * CH) {
+                const int r = tid - CH;
+                const size_t tk = (size_t)(start + (r < len ? r : len - 1)) * HK + hk;
+                sRk[r] = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
+                sRq[r] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
             }
+            // k, g and this thread's column of v are requested now and used once the first products are under way
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
+                ldg8(p.k, DT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, vk[n]);
+                ldg8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vg[n]);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int t = cg * 16 + j, tt = t < len ? t : len - 1;
+                vv[j] = ld1(p.v, DT, ((size_t)(start + tt) * HV + h) * 128 + row);
+            }
+            // dgl[c] = sum_v S[c][v] dS'[c][v] from the two tiles: chunk (v row, 8 channels) per thread, four rows each
+            umma::mbar_wait(&sh.ld0, n0 & 1);
+            umma::mbar_wait(&sh.ld2, n2 & 1);
+            float acc[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                const int i = tid + n * 512;
+                const uint32_t off = umma::tile_chunk_offset(128, i >> 4, i & 15);
+                const uint4 a4 = *reinterpret_cast<const uint4*>(sS + off), b4 = *reinterpret_cast<const uint4*>(sS + BU + off);
+                const uint4 c4 = *reinterpret_cast<const uint4*>(sT + off), d4 = *reinterpret_cast<const uint4*>(sT + BU + off);
+                const uint32_t ah[4] = {a4.x, a4.y, a4.z, a4.w}, al[4] = {b4.x, b4.y, b4.z, b4.w};
+                const uint32_t dh[4] = {c4.x, c4.y, c4.z, c4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float s0 = __uint_as_float(ah[e] << 16) + __uint_as_float(al[e] << 16);
+                    const float s1 = __uint_as_float(ah[e] & 0xffff0000u) + __uint_as_float(al[e] & 0xffff0000u);
+                    const float d0 = __uint_as_float(dh[e] << 16) + __uint_as_float(dl[e] << 16);
+                    const float d1 = __uint_as_float(dh[e] & 0xffff0000u) + __uint_as_float(dl[e] & 0xffff0000u);
+                    acc[2 * e] = fmaf(s0, d0, acc[2 * e]);
+                    acc[2 * e + 1] = fmaf(s1, d1, acc[2 * e + 1]);
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 16);
+            if (lane < 16) {
+                *reinterpret_cast<float4*>(&sPart[warp][lane * 8]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                *reinterpret_cast<float4*>(&sPart[warp][lane * 8 + 4]) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (cg * 16 + j >= len) vv[j] = 0.f;
         }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 16);
-        if (lane < 16) {
-            *reinterpret_cast<float4*>(&sPart[warp][lane * 8]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-            *reinterpret_cast<float4*>(&sPart[warp][lane * 8 + 4]) = make_float4(acc[4], acc[5], acc[6], acc[7]);
-        }
-    }
-    // scale k by its L2 statistics (rows past the end become zero); park the anchor rows of g
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-        const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
-        const float rk = sRk[r];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) vk[n][e] *= rk;
-        if ((r & 15) == 0) {
-            *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8]) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
-            *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8 + 4]) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < 16; ++j)
-        if (cg * 16 + j >= len) vv[j] = 0.f;
-    umma::mbar_wait(&sh.barC, 0);                      // dS' Vd^T done
-    umma::fence_after_sync();
-    __syncthreads();                                   // ... and every thread has read its part of dS': the tile is dead
-    if (tid == 0) {                                    // its second half receives dVd^T, its first half k~
-        umma::mbar_expect_tx(&sh.ld1, umma::CHUNK_TILE_BYTES);
-        umma::bulk_load(sD, reinterpret_cast<const uint8_t*>(p.dVd_t) + item * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld1);
-    }
-    if (tid < DK) {
-        float t = 0.f;
-#pragma unroll
-        for (int w = 0; w < 16; ++w) t += sPart[w][tid];
-        sDgl[tid] = t;
-    }
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-        const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
-        float t8[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(vg[n][e]);
-        store_split8(sK, sK + 16384, 64, r, k8, t8);
-    }
-    publish();
-    if (umma::mma_issuer()) {
-        umma::gemm(tmem + 0, umma::opnd_k(sS, sS + BU, 128), umma::opnd_k(sK, sK + 16384, 64), 128, 64, 128, 0u);        // P1
-        umma::commit(&sh.barA);
-        umma::mbar_wait(&sh.ld1, 0);
-        umma::gemm(tmem + 64, umma::opnd_k(sD, sD + 16384, 128), umma::opnd_mn(sA, sA + 8192, 64), 128, 64, 64, 0u);     // P2
-        umma::commit(&sh.barB);
-    }
-    // q for the intra-chunk operands is requested while the products run
-    float vq[2][8];
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-        const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-        ldg8(p.q, DT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, vq[n]);
-    }
-    umma::mbar_wait(&sh.barA, 0);
-    umma::fence_after_sync();
-    {
-        float d[16], x0[8], x1[8];
-        umma::tmem_ld16(umma::tmem_addr(tmem, warp, cg * 16), d);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { x0[j] = vv[j] - d[j]; x1[j] = vv[8 + j] - d[8 + j]; }
-        store_split8(sK, sK + 16384, 128, row, 2 * cg, x0);            // k~ is dead: the region now holds X^T
-        store_split8(sK, sK + 16384, 128, row, 2 * cg + 1, x1);
-        umma::mbar_wait(&sh.barB, 0);
-        umma::mbar_wait(&sh.barD, 0);                                  // P6a and P3a done long ago: the dO and Vd^T tiles are dead
+        ++n0; ++n2;
+        umma::mbar_wait(&sh.barC, nC & 1); ++nC;           // dS' Vd^T done
         umma::fence_after_sync();
-        float dw[16];
-        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 64 + cg * 16), dw);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            dw[j] *= sh.beta[cg * 16 + j];                             // dX = diag(beta) dW; beta is 0 past the end
-            // dv rows are staged [tok][v] in the dtype of v over the dead Vd^T tile and leave with 16-byte stores below
-            if (DT == MKDA_F32) reinterpret_cast<float*>(sV)[(cg * 16 + j) * 128 + row] = dw[j];
-            else if (DT == MKDA_BF16) reinterpret_cast<__nv_bfloat16*>(sV)[(cg * 16 + j) * 128 + row] = __float2bfloat16_rn(dw[j]);
-            else reinterpret_cast<__half*>(sV)[(cg * 16 + j) * 128 + row] = __float2half_rn(dw[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { x0[j] = dw[j]; x1[j] = dw[8 + j]; }
-        store_split8(sO, sO + 16384, 128, row, 2 * cg, x0);
-        store_split8(sO, sO + 16384, 128, row, 2 * cg + 1, x1);
-    }
-    publish();
-    if (umma::mma_issuer()) {
-        umma::Opnd aD = umma::opnd_mn(sD, sD + 16384, 128);            // (m = token, k = v) of the dVd^T tile, moved one 64-group up:
-        aD.hi -= 16384; aD.lo -= 16384;                                // rows 0..63 of the operand read the 16 KB in front of each half
-        umma::gemm(tmem + 256, aD, umma::opnd_mn(sK, sK + 16384, 128), 128, 64, 128, 0u);                                // P3b
-        umma::commit(&sh.barA);
-        umma::gemm(tmem + 320, umma::opnd_mn(sS, sS + BU, 128), umma::opnd_mn(sO, sO + 16384, 128), 128, 64, 128, 0u);   // P6b
-        umma::commit(&sh.barB);
-    }
-    {   // dv: 64 rows of 128 values
-        constexpr int ROWB = DT == MKDA_F32 ? 512 : 256;               // bytes per row
-        constexpr int PER = ROWB / 16;                                 // 16-byte pieces per row
-#pragma unroll
-        for (int n = 0; n < 64 * PER / 512; ++n) {
-            const int i = tid + n * 512, r = i / PER, pc = i % PER;
-            if (r < len) {
-                const uint4 val = *reinterpret_cast<const uint4*>(sV + r * ROWB + pc * 16);
-                *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.dv) + ((size_t)(start + r) * HV + h) * ROWB + pc * 16) = val;
-            }
-        }
-    }
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-        const float rq = sRq[(tid + n * 512) >> 4];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) vq[n][e] *= rq;
-    }
-    __syncthreads();                                   // the dv rows have left shared memory
-    umma::mbar_wait(&sh.barA, 1);
-    umma::mbar_wait(&sh.barB, 1);                      // every state-phase tile except A is dead now
-    umma::fence_after_sync();
-    if (q >= 2) {                                      // rows i = row - 64 of D2 = dVd X^T: dbeta_w partials and D2 diag(beta)
-        const int i = row - 64;
-        float d[16], a0[8], a1[8];
-        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 256 + cg * 16), d);
-        umma::load_tile8(sA, sA + 8192, 64, i, 2 * cg, a0);
-        umma::load_tile8(sA, sA + 8192, 64, i, 2 * cg + 1, a1);
-        float pr[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            pr[j] = d[j] * (j < 8 ? a0[j] : a1[j - 8]);
-            const float da = d[j] * sh.beta[cg * 16 + j];
-            if (j < 8) a0[j] = da; else a1[j - 8] = da;
-        }
-        // sums over the 32 lanes for the 16 columns at once: every exchange halves the number of columns a lane carries
-        // (16 shuffles instead of 80); the lane whose bits 4..1 spell the column ends up with its sum
-#pragma unroll
-        for (int w = 8, bit = 16; w >= 1; w >>= 1, bit >>= 1) {
-#pragma unroll
-            for (int j = 0; j < w; ++j) {
-                const float recv = __shfl_xor_sync(0xffffffffu, (lane & bit) ? pr[j] : pr[j + w], bit);
-                pr[j] = ((lane & bit) ? pr[j + w] : pr[j]) + recv;
-            }
-        }
-        pr[0] += __shfl_xor_sync(0xffffffffu, pr[0], 1);
-        if ((lane & 1) == 0) sRedW[q - 2][cg * 16 + ((lane >> 1) & 15)] = pr[0];
-        store_split8(sDA, sDA + 8192, 64, i, 2 * cg, a0);
-        store_split8(sDA, sDA + 8192, 64, i, 2 * cg + 1, a1);
-    }
-    publish();
-    if (tid < CH) sDbw[tid] = sRedW[0][tid] + sRedW[1][tid];
-    if (umma::mma_issuer()) {
-        umma::gemm(tmem + 0, umma::opnd_k(sDA, sDA + 8192, 64), umma::opnd_k(sA, sA + 8192, 64), 128, 64, 64, 0u);        // P4
-        umma::commit(&sh.barA);
-    }
-    stage_intra_operands(base, sGa, tid, 0, vk[0], vq[0], vg[0]);     // over the dead S / X^T / dVd^T / dX^T tiles, while P4 runs
-    umma::mbar_wait(&sh.barA, 0);
-    umma::fence_after_sync();
-    if (q < 2) {
-        float y[16], a0[8], a1[8];
-        umma::tmem_ld16(umma::tmem_addr(tmem, warp, cg * 16), y);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { a0[j] = y[j]; a1[j] = y[8 + j]; }
-        store_split8(sY, sY + 8192, 64, row, 2 * cg, a0);
-        store_split8(sY, sY + 8192, 64, row, 2 * cg + 1, a1);
-    }
-    publish();
-    if (umma::mma_issuer()) {
-        umma::gemm(tmem + 64, umma::opnd_mn(sA, sA + 8192, 64), umma::opnd_mn(sY, sY + 8192, 64), 128, 64, 64, 0u);       // P5
-        umma::commit(&sh.barA);
-    }
-    stage_intra_operands(base, sGa, tid, 1, vk[1], vq[1], vg[1]);     // the other half, while P5 runs
-    umma::mbar_wait(&sh.barA, 1);                      // Z done: A, D2 diag(beta) and Y are dead
-    umma::fence_after_sync();
-    if (q < 2) {                                       // rows i = row of D1 = dO Vd^T and Z: the weights of the intra-chunk part
-        const int i = row;
-        const float bt = sh.beta[i];
-        float d[16], z[16];
-        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + cg * 16), d);
-        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 64 + cg * 16), z);
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-            float w8[8], d8[8], b8[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const int j = cg * 16 + hf * 8 + e;
-                const bool lo = j < i && i < len;
-                w8[e] = lo ? p.scale * d[hf * 8 + e] : 0.f;
-                d8[e] = lo ? -z[hf * 8 + e] : 0.f;
-                b8[e] = bt * d8[e];
-                if (j == i) sDiag[i] = i < len ? p.scale * d[hf * 8 + e] : 0.f;
-            }
-            store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + (i & 15), 2 * cg + hf, w8);
-            store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + 16 + (i & 15), 2 * cg + hf, d8);
-            store_split8(sBd, sBd + 8192, 64, i, 2 * cg + hf, b8);
-        }
-    }
-    publish();
-    if (umma::mma_issuer()) {
-#pragma unroll
-        for (int I = 0; I < 4; ++I) {
-            const int nj = 16 * (I + 1);
-            const umma::Opnd aKc = umma::opnd_mn(base + kc_off(I), base + kc_off(I) + kc_bytes(I), nj);
-            // both row terms (dq_row | T) of the block in one N = 32 product
-            umma::gemm(tmem + 32 * I, aKc, umma::opnd_k(sWD, sWD + 16384, 128, 32 * I), 128, 32, nj, 0u);
-            umma::gemm(tmem + ccol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I + 16), umma::opnd_mn(sWD, sWD + 16384, 128, 32 * I),
-                       128, nj, 16, 0u);
-            umma::gemm(tmem + ccol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I), umma::opnd_mn(sBd, sBd + 8192, 64, 16 * I),
-                       128, nj, 16, 1u);
-        }
-        umma::commit(&sh.barA);
-    }
-    // epilogue inputs for (channel `row`, rows 16 cg .. 16 cg + 15) are fetched while the products run
-    float kq[16], qq[16], gg[16], ga[4];
-#pragma unroll
-    for (int r = 0; r < 16; ++r) {
-        const int i = 16 * cg + r, ii = i < len ? i : len - 1;
-        const size_t tk = (size_t)(start + ii) * HK + hk;
-        kq[r] = ld1(p.k, DT, tk * 128 + row) * (i < len ? sRk[i] : sRk[len - 1]);
-        qq[r] = ld1(p.q, DT, tk * 128 + row) * (i < len ? sRq[i] : sRq[len - 1]);
-        gg[r] = p.g_c[((size_t)(start + ii) * HV + h) * 128 + row];
-    }
-#pragma unroll
-    for (int I = 0; I < 4; ++I) ga[I] = sGa[I][row];   // anchor rows (the last valid row stands in for anchors past the end)
-    const float gL = p.g_c[((size_t)(start + len - 1) * HV + h) * 128 + row];
-    umma::mbar_wait(&sh.barA, 0);
-    umma::fence_after_sync();
-
-    {   // column sum of the inter-chunk k gradient for the last row's gate term
-        float ab[16];
-        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 384 + 16 * cg), ab);
-        float cs = 0.f;
-#pragma unroll
-        for (int r = 0; r < 16; ++r)
-            if (16 * cg + r < len) cs += kq[r] * ex2f_(gL - gg[r]) * ab[r];
-        sCol[cg][row] = cs;
-    }
-    __syncthreads();
-    const float extra = ((sCol[0][row] + sCol[1][row]) + (sCol[2][row] + sCol[3][row])) + ex2f_(gL) * sDgl[row];
-    // the three outputs are staged as fp32 [tok][channel] tiles over the dead operands (rows past the end: zero)
-    float* oq = reinterpret_cast<float*>(base);
-    float* ok = oq + CH * DK;
-    float* og = ok + CH * DK;
-#pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-        const int c0 = 16 * cg + 8 * hf;
-        float aq[8], ak[8], ab[8], vr[8], vt[8], dkc[8];
-        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 192 + c0), aq);
-        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 320 + c0), ak);
-        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 384 + c0), ab);
-        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 32 * cg + 8 * hf), vr);
-        umma::tmem_ld8(umma::tmem_addr(tmem, warp, 32 * cg + 16 + 8 * hf), vt);
-#pragma unroll
-        for (int r = 0; r < 8; ++r) dkc[r] = 0.f;
-#pragma unroll
-        for (int I = 0; I < 4; ++I) {
-            if (I < cg) continue;                      // warp-uniform
-            float c8[8];
-            umma::tmem_ld8(umma::tmem_addr(tmem, warp, ccol_off(I) + c0), c8);
-#pragma unroll
-            for (int r = 0; r < 8; ++r) dkc[r] += c8[r] * ex2f_(ga[I] - gg[8 * hf + r]);
-        }
-        float bsv[8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            const int i = c0 + r, rr = 8 * hf + r;
-            const float g = gg[rr], kv = kq[rr], qv = qq[rr];
-            const float up = ex2f_(g), re = ex2f_(gL - g), e = ex2f_(g - ga[cg]);
-            const float dqt = p.scale * aq[r], dkt = -ak[r], dkb = ab[r];
-            const float dqr = vr[r] * e, T = vt[r] * e, bt = sh.beta[i], dgn = sDiag[i];
-            bsv[r] = kv * T;
-            float dg = qv * up * dqt + kv * up * dkt - kv * re * dkb;
-            if (i == len - 1) dg += extra;
-            const bool ok_row = i < len;
-            oq[i * DK + row] = ok_row ? dqt * up + dqr + dgn * kv : 0.f;
-            ok[i * DK + row] = ok_row ? (dkt * up + dkb * re) + bt * T + dkc[r] + dgn * qv : 0.f;
-            og[i * DK + row] = ok_row ? dg + qv * dqr + kv * bt * T - kv * dkc[r] : 0.f;
-        }
-        // sum over the 32 channels of this warp for the 8 rows at once: every exchange halves the number of rows a lane
-        // carries (9 shuffles instead of 40); the lane whose bits 4..2 spell the row ends up with its sum
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const float recv = __shfl_xor_sync(0xffffffffu, (lane & 16) ? bsv[r] : bsv[r + 4], 16);
-            bsv[r] = ((lane & 16) ? bsv[r + 4] : bsv[r]) + recv;
-        }
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            const float recv = __shfl_xor_sync(0xffffffffu, (lane & 8) ? bsv[r] : bsv[r + 2], 8);
-            bsv[r] = ((lane & 8) ? bsv[r + 2] : bsv[r]) + recv;
+        __syncthreads();                                   // ... and every thread has read its part of dS': the tile is dead
+        if (tid == 0) {                                        // its second half receives dVd^T, its first half k~
+            umma::mbar_expect_tx(&sh.ld1, umma::CHUNK_TILE_BYTES);
+            umma::bulk_load(sD, reinterpret_cast<const uint8_t*>(p.dVd_t) + (size_t)item * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld1);
         }
         {
-            const float recv = __shfl_xor_sync(0xffffffffu, (lane & 4) ? bsv[0] : bsv[1], 4);
-            bsv[0] = ((lane & 4) ? bsv[1] : bsv[0]) + recv;
+            if (tid < DK) {
+                float t = 0.f;
+#pragma unroll
+                for (int w = 0; w < 16; ++w) t += sPart[w][tid];
+                sDgl[tid] = t;
+            }
+            // scale k by its L2 statistics (rows past the end become zero); park the anchor rows of g; k~ = k 2^g
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
+                const float rk = sRk[r];
+                float t8[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { vk[n][e] *= rk; t8[e] = vk[n][e] * ex2f_(vg[n][e]); }
+                store_split8(sK, sK + 16384, 64, r, k8, t8);
+                if ((r & 15) == 0) {
+                    *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8]) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
+                    *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8 + 4]) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
+                }
+            }
         }
-        bsv[0] += __shfl_xor_sync(0xffffffffu, bsv[0], 2);
-        bsv[0] += __shfl_xor_sync(0xffffffffu, bsv[0], 1);
-        if ((lane & 3) == 0) sRed[q][c0 + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = bsv[0];
-    }
-    umma::fence_async_smem();
-    __syncthreads();
-    if (tid == 0) {
-        const size_t ob = item * (size_t)(CH * DK);
-        umma::bulk_store(p.dq_v + ob, oq, CH * DK * 4);
-        umma::bulk_store(p.dk_v + ob, ok, CH * DK * 4);
-        umma::bulk_store(p.dgp + ob, og, CH * DK * 4);
-    }
-    if (tid < len) {
-        const size_t th = (size_t)(start + tid) * HV + h;
-        float db = sDbw[tid] + ((sRed[0][tid] + sRed[1][tid]) + (sRed[2][tid] + sRed[3][tid]));
-        if (p.beta_sigmoid) {
-            const float sg = sigmoidf_(ld1(p.beta_raw, p.beta_dtype, th));
-            db *= p.beta_scale * sg * (1.f - sg);
+        publish();
+        if (umma::mma_issuer()) {
+            umma::gemm(tmem + 0, umma::opnd_k(sS, sS + BU, 128), umma::opnd_k(sK, sK + 16384, 64), 128, 64, 128, 0u);        // P1
+            umma::commit(&sh.barA);
+            umma::mbar_wait(&sh.ld1, n1 & 1);
+            umma::gemm(tmem + 64, umma::opnd_k(sD, sD + 16384, 128), umma::opnd_mn(sA, sA + 8192, 64), 128, 64, 64, 0u);     // P2
+            umma::commit(&sh.barB);
         }
-        st1(p.dbeta, p.dbeta_dtype, th, db);
+        ++n1;
+        {
+            // q for the intra-chunk operands is requested while the products run
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
+                ldg8(p.q, DT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, vq[n]);
+            }
+            umma::mbar_wait(&sh.barA, nA & 1);
+            umma::fence_after_sync();
+            float d[16], x0[8], x1[8];
+            umma::tmem_ld16(umma::tmem_addr(tmem, warp, cg * 16), d);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { x0[j] = vv[j] - d[j]; x1[j] = vv[8 + j] - d[8 + j]; }
+            store_split8(sK, sK + 16384, 128, row, 2 * cg, x0);            // k~ is dead: the region now holds X^T
+            store_split8(sK, sK + 16384, 128, row, 2 * cg + 1, x1);
+            umma::mbar_wait(&sh.barB, nB & 1);
+            umma::mbar_wait(&sh.barD, nD & 1);                             // P6a and P3a done long ago: the dO and Vd^T tiles are dead
+            umma::fence_after_sync();
+            float dw[16];
+            umma::tmem_ld16(umma::tmem_addr(tmem, warp, 64 + cg * 16), dw);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                dw[j] *= sh.beta[cg * 16 + j];                             // dX = diag(beta) dW; beta is 0 past the end
+                // dv rows are staged [tok][v] in the dtype of v over the dead Vd^T tile and leave with 16-byte stores below
+                if (DT == MKDA_F32) reinterpret_cast<float*>(sV)[(cg * 16 + j) * 128 + row] = dw[j];
+                else if (DT == MKDA_BF16) reinterpret_cast<__nv_bfloat16*>(sV)[(cg * 16 + j) * 128 + row] = __float2bfloat16_rn(dw[j]);
+                else reinterpret_cast<__half*>(sV)[(cg * 16 + j) * 128 + row] = __float2half_rn(dw[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { x0[j] = dw[j]; x1[j] = dw[8 + j]; }
+            store_split8(sO, sO + 16384, 128, row, 2 * cg, x0);
+            store_split8(sO, sO + 16384, 128, row, 2 * cg + 1, x1);
+        }
+        ++nA; ++nB; ++nD;
+        publish();
+        if (umma::mma_issuer()) {
+            umma::Opnd aD = umma::opnd_mn(sD, sD + 16384, 128);            // (m = token, k = v) of the dVd^T tile, moved one 64-group up:
+            aD.hi -= 16384; aD.lo -= 16384;                                // rows 0..63 of the operand read the 16 KB in front of each half
+            umma::gemm(tmem + 256, aD, umma::opnd_mn(sK, sK + 16384, 128), 128, 64, 128, 0u);                                // P3b
+            umma::commit(&sh.barA);
+            umma::gemm(tmem + 320, umma::opnd_mn(sS, sS + BU, 128), umma::opnd_mn(sO, sO + 16384, 128), 128, 64, 128, 0u);   // P6b
+            umma::commit(&sh.barB);
+        }
+        {
+            // dv: 64 rows of 128 values
+            constexpr int ROWB = DT == MKDA_F32 ? 512 : 256;               // bytes per row
+            constexpr int PER = ROWB / 16;                                 // 16-byte pieces per row
+#pragma unroll
+            for (int n = 0; n < 64 * PER / 512; ++n) {
+                const int i = tid + n * 512, r = i / PER, pc = i % PER;
+                if (r < len) {
+                    const uint4 val = *reinterpret_cast<const uint4*>(sV + r * ROWB + pc * 16);
+                    *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.dv) + ((size_t)(start + r) * HV + h) * ROWB + pc * 16) = val;
+                }
+            }
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const float rq = sRq[(tid + n * 512) >> 4];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) vq[n][e] *= rq;
+            }
+        }
+        __syncthreads();                                   // the dv rows have left shared memory
+        umma::mbar_wait(&sh.barA, nA & 1); ++nA;
+        umma::mbar_wait(&sh.barB, nB & 1); ++nB;           // every state-phase tile except A is dead now
+        umma::fence_after_sync();
+        if (q >= 2) {                           // rows i = row - 64 of D2 = dVd X^T: dbeta_w partials and D2 diag(beta)
+            const int i = row - 64;
+            float d[16], a0[8], a1[8];
+            umma::tmem_ld16(umma::tmem_addr(tmem, warp, 256 + cg * 16), d);
+            umma::load_tile8(sA, sA + 8192, 64, i, 2 * cg, a0);
+            umma::load_tile8(sA, sA + 8192, 64, i, 2 * cg + 1, a1);
+            float pr[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                pr[j] = d[j] * (j < 8 ? a0[j] : a1[j - 8]);
+                const float da = d[j] * sh.beta[cg * 16 + j];
+                if (j < 8) a0[j] = da; else a1[j - 8] = da;
+            }
+            // sums over the 32 lanes for the 16 columns at once: every exchange halves the number of columns a lane carries
+            // (16 shuffles instead of 80); the lane whose bits 4..1 spell the column ends up with its sum
+#pragma unroll
+            for (int w = 8, bit = 16; w >= 1; w >>= 1, bit >>= 1) {
+#pragma unroll
+                for (int j = 0; j < w; ++j) {
+                    const float recv = __shfl_xor_sync(0xffffffffu, (lane & bit) ? pr[j] : pr[j + w], bit);
+                    pr[j] = ((lane & bit) ? pr[j + w] : pr[j]) + recv;
+                }
+            }
+            pr[0] += __shfl_xor_sync(0xffffffffu, pr[0], 1);
+            if ((lane & 1) == 0) sRedW[q - 2][cg * 16 + ((lane >> 1) & 15)] = pr[0];
+            store_split8(sDA, sDA + 8192, 64, i, 2 * cg, a0);
+            store_split8(sDA, sDA + 8192, 64, i, 2 * cg + 1, a1);
+        }
+        publish();
+        if (umma::mma_issuer()) {
+            umma::gemm(tmem + 0, umma::opnd_k(sDA, sDA + 8192, 64), umma::opnd_k(sA, sA + 8192, 64), 128, 64, 64, 0u);        // P4
+            umma::commit(&sh.barA);
+        }
+        {
+            if (tid < CH) sDbw[tid] = sRedW[0][tid] + sRedW[1][tid];
+            stage_intra_operands(base, sGa, tid, 0, vk[0], vq[0], vg[0]);     // over the dead S / X^T / dVd^T / dX^T tiles, while P4 runs
+            umma::mbar_wait(&sh.barA, nA & 1);
+            umma::fence_after_sync();
+            if (q < 2) {
+                float y[16], a0[8], a1[8];
+                umma::tmem_ld16(umma::tmem_addr(tmem, warp, cg * 16), y);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { a0[j] = y[j]; a1[j] = y[8 + j]; }
+                store_split8(sY, sY + 8192, 64, row, 2 * cg, a0);
+                store_split8(sY, sY + 8192, 64, row, 2 * cg + 1, a1);
+            }
+        }
+        ++nA;
+        publish();
+        if (umma::mma_issuer()) {
+            umma::gemm(tmem + 64, umma::opnd_mn(sA, sA + 8192, 64), umma::opnd_mn(sY, sY + 8192, 64), 128, 64, 64, 0u);       // P5
+            umma::commit(&sh.barA);
+        }
+        {
+            stage_intra_operands(base, sGa, tid, 1, vk[1], vq[1], vg[1]);     // the other half, while P5 runs
+            umma::mbar_wait(&sh.barA, nA & 1);                 // Z done: A, D2 diag(beta) and Y are dead
+            umma::fence_after_sync();
+            if (q < 2) {                                       // rows i = row of D1 = dO Vd^T and Z: the weights of the intra-chunk part
+                const int i = row;
+                const float bt = sh.beta[i];
+                float d[16], z[16];
+                umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + cg * 16), d);
+                umma::tmem_ld16(umma::tmem_addr(tmem, warp, 64 + cg * 16), z);
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    float w8[8], d8[8], b8[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const int j = cg * 16 + hf * 8 + e;
+                        const bool lo = j < i && i < len;
+                        w8[e] = lo ? p.scale * d[hf * 8 + e] : 0.f;
+                        d8[e] = lo ? -z[hf * 8 + e] : 0.f;
+                        b8[e] = bt * d8[e];
+                        if (j == i) sDiag[i] = i < len ? p.scale * d[hf * 8 + e] : 0.f;
+                    }
+                    store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + (i & 15), 2 * cg + hf, w8);
+                    store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + 16 + (i & 15), 2 * cg + hf, d8);
+                    store_split8(sBd, sBd + 8192, 64, i, 2 * cg + hf, b8);
+                }
+            }
+        }
+        ++nA;
+        publish();
+        if (umma::mma_issuer()) {
+#pragma unroll
+            for (int I = 0; I < 4; ++I) {
+                const int nj = 16 * (I + 1);
+                const umma::Opnd aKc = umma::opnd_mn(base + kc_off(I), base + kc_off(I) + kc_bytes(I), nj);
+                // both row terms (dq_row | T) of the block in one N = 32 product
+                umma::gemm(tmem + 32 * I, aKc, umma::opnd_k(sWD, sWD + 16384, 128, 32 * I), 128, 32, nj, 0u);
+                umma::gemm(tmem + ccol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I + 16), umma::opnd_mn(sWD, sWD + 16384, 128, 32 * I),
+                           128, nj, 16, 0u);
+                umma::gemm(tmem + ccol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I), umma::opnd_mn(sBd, sBd + 8192, 64, 16 * I),
+                           128, nj, 16, 1u);
+            }
+            umma::commit(&sh.barA);
+            if (more) {                                        // every operand tile is dead once these products are done:
+                umma::mbar_wait(&sh.barA, nA & 1);             // the next item's dS', Vd^T and A start travelling under the epilogue
+                fetch_early((size_t)item + stride);
+            }
+        }
+        {
+            // epilogue inputs for (channel `row`, rows 16 cg .. 16 cg + 15) are fetched while the products run
+            float kq[16], qq[16], gg[16], ga[4];
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                const int i = 16 * cg + r, ii = i < len ? i : len - 1;
+                const size_t tk = (size_t)(start + ii) * HK + hk;
+                kq[r] = ld1(p.k, DT, tk * 128 + row) * (i < len ? sRk[i] : sRk[len - 1]);
+                qq[r] = ld1(p.q, DT, tk * 128 + row) * (i < len ? sRq[i] : sRq[len - 1]);
+                gg[r] = p.g_c[((size_t)(start + ii) * HV + h) * 128 + row];
+            }
+#pragma unroll
+            for (int I = 0; I < 4; ++I) ga[I] = sGa[I][row];   // anchor rows (the last valid row stands in for anchors past the end)
+            const float gL = p.g_c[((size_t)(start + len - 1) * HV + h) * 128 + row];
+            umma::mbar_wait(&sh.barA, nA & 1);
+            umma::fence_after_sync();
+            {   // column sum of the inter-chunk k gradient for the last row's gate term
+                float ab[16];
+                umma::tmem_ld16(umma::tmem_addr(tmem, warp, 384 + 16 * cg), ab);
+                float cs = 0.f;
+#pragma unroll
+                for (int r = 0; r < 16; ++r)
+                    if (16 * cg + r < len) cs += kq[r] * ex2f_(gL - gg[r]) * ab[r];
+                sCol[cg][row] = cs;
+            }
+            __syncthreads();
+            const float extra = ((sCol[0][row] + sCol[1][row]) + (sCol[2][row] + sCol[3][row])) + ex2f_(gL) * sDgl[row];
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const int c0 = 16 * cg + 8 * hf;
+                float aq[8], ak[8], ab[8], vr[8], vt[8], dkc[8];
+                umma::tmem_ld8(umma::tmem_addr(tmem, warp, 192 + c0), aq);
+                umma::tmem_ld8(umma::tmem_addr(tmem, warp, 320 + c0), ak);
+                umma::tmem_ld8(umma::tmem_addr(tmem, warp, 384 + c0), ab);
+                umma::tmem_ld8(umma::tmem_addr(tmem, warp, 32 * cg + 8 * hf), vr);
+                umma::tmem_ld8(umma::tmem_addr(tmem, warp, 32 * cg + 16 + 8 * hf), vt);
+#pragma unroll
+                for (int r = 0; r < 8; ++r) dkc[r] = 0.f;
+#pragma unroll
+                for (int I = 0; I < 4; ++I) {
+                    if (I < cg) continue;                      // warp-uniform
+                    float c8[8];
+                    umma::tmem_ld8(umma::tmem_addr(tmem, warp, ccol_off(I) + c0), c8);
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) dkc[r] += c8[r] * ex2f_(ga[I] - gg[8 * hf + r]);
+                }
+                float bsv[8];
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    const int i = c0 + r, rr = 8 * hf + r;
+                    const float g = gg[rr], kv = kq[rr], qv = qq[rr];
+                    const float up = ex2f_(g), re = ex2f_(gL - g), e = ex2f_(g - ga[cg]);
+                    const float dqt = p.scale * aq[r], dkt = -ak[r], dkb = ab[r];
+                    const float dqr = vr[r] * e, T = vt[r] * e, bt = sh.beta[i], dgn = sDiag[i];
+                    bsv[r] = kv * T;
+                    float dg = qv * up * dqt + kv * up * dkt - kv * re * dkb;
+                    if (i == len - 1) dg += extra;
+                    const bool ok_row = i < len;
+                    oq[i * DK + row] = ok_row ? dqt * up + dqr + dgn * kv : 0.f;
+                    ok[i * DK + row] = ok_row ? (dkt * up + dkb * re) + bt * T + dkc[r] + dgn * qv : 0.f;
+                    og[i * DK + row] = ok_row ? dg + qv * dqr + kv * bt * T - kv * dkc[r] : 0.f;
+                }
+                // sum over the 32 channels of this warp for the 8 rows at once: every exchange halves the number of rows a lane
+                // carries (9 shuffles instead of 40); the lane whose bits 4..2 spell the row ends up with its sum
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const float recv = __shfl_xor_sync(0xffffffffu, (lane & 16) ? bsv[r] : bsv[r + 4], 16);
+                    bsv[r] = ((lane & 16) ? bsv[r + 4] : bsv[r]) + recv;
+                }
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const float recv = __shfl_xor_sync(0xffffffffu, (lane & 8) ? bsv[r] : bsv[r + 2], 8);
+                    bsv[r] = ((lane & 8) ? bsv[r + 2] : bsv[r]) + recv;
+                }
+                {
+                    const float recv = __shfl_xor_sync(0xffffffffu, (lane & 4) ? bsv[0] : bsv[1], 4);
+                    bsv[0] = ((lane & 4) ? bsv[1] : bsv[0]) + recv;
+                }
+                bsv[0] += __shfl_xor_sync(0xffffffffu, bsv[0], 2);
+                bsv[0] += __shfl_xor_sync(0xffffffffu, bsv[0], 1);
+                if ((lane & 3) == 0) sRed[q][c0 + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = bsv[0];
+            }
+            umma::fence_async_smem();
+        }
+        ++nA;
+        umma::fence_before_sync();
+        __syncthreads();                                       // output tiles and sRed complete; every accumulator has been read
+        umma::fence_after_sync();
+        if (sender) {
+            const size_t ob = (size_t)item * (size_t)(CH * DK);
+            umma::bulk_store(p.dq_v + ob, oq, CH * DK * 4);
+            umma::bulk_store(p.dk_v + ob, ok, CH * DK * 4);
+            umma::bulk_store(p.dgp + ob, og, CH * DK * 4);
+            umma::bulk_store_wait_read();                      // the output tiles have left: S and dO of the next item may land
+            if (more) fetch_late((size_t)item + stride);
+        }
+        if (tid < len) {
+            const size_t th = (size_t)(start + tid) * HV + h;
+            float db = sDbw[tid] + ((sRed[0][tid] + sRed[1][tid]) + (sRed[2][tid] + sRed[3][tid]));
+            if (p.beta_sigmoid) {
+                const float sg = sigmoidf_(ld1(p.beta_raw, p.beta_dtype, th));
+                db *= p.beta_scale * sg * (1.f - sg);
+            }
+            st1(p.dbeta, p.dbeta_dtype, th, db);
+        }
+        __syncthreads();
     }
-    if (tid == 0) umma::bulk_store_wait_read();
     umma::fence_before_sync();
     __syncthreads();
     if (warp == 0) umma::tmem_dealloc(tmem, 512);
@@ -848,7 +892,8 @@ template <int DT>
 static int launch_bwd_chunk_tc_t(const MkdaBwdChunk* p, cudaStream_t stream) {
     auto kern = bwd_chunk_tc_kernel<DT>;
     if (int e = ensure_smem((const void*)kern, BWD_CHUNK_SMEM, "bwd_chunk")) return e;
-    kern<<<p->L.NC * p->L.HV, 512, BWD_CHUNK_SMEM, stream>>>(*p);
+    const int items = p->L.NC * p->L.HV;
+    kern<<<items < sm_count() ? items : sm_count(), BWD_CHUNK_THREADS, BWD_CHUNK_SMEM, stream>>>(*p);
     return check_launch("bwd_chunk");
 }
 int launch_bwd_chunk_tc(const MkdaBwdChunk* p, cudaStream_t stream) {
