@@ -93,12 +93,17 @@ int mkda_l2norm_rstd(const MkdaL2Norm* p, void* stream);
 /* Chunk-parallel WY preparation.  Per (chunk, v-head): decayed K K^T and Q K^T with per-16-row anchoring, the
  * unit-lower-triangular inverse, and the two products the recurrence consumes.
  * Replaces kkt_solve_kda (mogan_kda/ops/kimi_delta_rule/chunk/hopper/kkt_solve_kda.py:546-623) and bwd_w_kda
- * (.../hopper/bwd_prep.py:317-347). */
+ * (.../hopper/bwd_prep.py:317-347); with scalar_gate the gate-free K K^T with the decay applied afterwards, as kkt_solve +
+ * the G scaling of fused_gdr_fwd do (mogan_kda/ops/gated_delta_rule/chunk/blackwell/kkt_solve.py:105-121,
+ * blackwell/fused_fwd.py:425-445). */
 typedef struct {
     MkdaLayout L;
     const void* q; const void* k; const void* v; int qkv_dtype;
     const float* q_rstd; const float* k_rstd;      /* [TT,HK] or NULL */
     const float* g_c; const float* beta;           /* [TT,HV,128], [TT,HV] */
+    int scalar_gate;           /* 1: g_c holds the same value in all 128 channels of a (token, head) (one decay per token, as
+                                * mkda_gate_cumsum_fwd writes it for a [TT,HV] gate): the scalar-gate path is taken, which
+                                * accepts any decay <= 0; 0: per-channel path, contract: decay >= -5 per token */
     float scale;
     float* A;      /* [NC,HV] quarter tiles: (I + strictlower(diag(beta) Gamma))^-1 */
     float* Aqk;    /* [NC,HV] quarter tiles: scale * lower(Q K^T with decay) */
@@ -249,6 +254,7 @@ typedef struct {
     MkdaLayout L;
     const void* q; const void* k; const void* v; int qkv_dtype; const float* q_rstd; const float* k_rstd;
     const float* g_c; const float* beta;
+    int scalar_gate;           /* as in MkdaIntraFwd */
     const float* A;            /* [NC,HV] quarter tiles as written by mkda_intra_fwd */
     const float* h; const float* dh;               /* state tiles, see MKDA_STATE_TILE_BYTES */
     const float* Vd;           /* [NC,HV] chunk tiles as written by mkda_recur_fwd in the forward pass */

@@ -39,7 +39,8 @@ class _DeltaRuleFunction(torch.autograd.Function):
         g_c, beta_e = ops.gate_cumsum_fwd(lay, x, cfg["gate_mode"], A_log, dt_bias, cfg["lower_bound"], HV,
                                           beta_raw=beta, beta_sigmoid=cfg["beta_mode"] == "sigmoid",
                                           beta_scale=cfg["beta_scale"])
-        A, Aqk, nw, u, kbar, qs, gl = ops.intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV)
+        A, Aqk, nw, u, kbar, qs, gl = ops.intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV,
+                                                    scalar_gate=x.dim() == 3)
         vf = cfg["state_v_first"]
         need_ht = cfg["output_final_state"]
         ms = m_first = None
@@ -117,7 +118,8 @@ class _DeltaRuleFunction(torch.autograd.Function):
             dh, dVd_t, dO_t, dh0 = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, dht=dht,
                                               state_v_first=vf, want_dh0=need_dh0)
         dq_v, dk_v, dgp, dbeta, dv = ops.bwd_chunk(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, A, h, dh, Vd, dO_t, dVd_t,
-                                                   scale, HK, HV, beta, cfg["beta_mode"] == "sigmoid", cfg["beta_scale"])
+                                                   scale, HK, HV, beta, cfg["beta_mode"] == "sigmoid", cfg["beta_scale"],
+                                                   scalar_gate=x.dim() == 3)
         dx, d_bias, d_alog = ops.gate_bwd(lay, x, dgp, cfg["gate_mode"], A_log, dt_bias, cfg["lower_bound"], HV,
                                           want_bias=dt_bias is not None and ctx.needs_input_grad[6],
                                           want_alog=A_log is not None and ctx.needs_input_grad[5])

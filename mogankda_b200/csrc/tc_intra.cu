@@ -133,11 +133,16 @@ __device__ __forceinline__ void invert_unit_lower(const float* __restrict__ sM, 
     __syncthreads();
 }
 
-template <int DT>
+// SCALAR: the gate is one decay per token (the same cumsum in all 128 channels).  It then commutes with the contraction
+// over channels, Gamma_ij = (k_i . k_j) 2^(g_i - g_j), so the products are plain K K^T / Q K^T (one product over a stacked
+// [K; Q] tile) and the decay is applied to the accumulators, element by element and for i >= j only: nothing is anchored,
+// no exponent is ever positive, and any g <= 0 is in range (the per-channel path needs g >= -5 per token).
+template <int DT, bool SCALAR>
 __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd p, const int ahead) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ IntraShared sh;
     __shared__ __align__(16) float sGa[5][DK];         // cumsum rows of the four block anchors, [4] = last valid row
+    __shared__ float sGs[CH];                          // SCALAR: the cumsum of every row (rows past the end: the last valid one)
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sKQ = base + KQ_OFF;
     float* sM = reinterpret_cast<float*>(base + OPND_BYTES);
@@ -195,6 +200,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
             *reinterpret_cast<float4*>(&sGa[4][k8 * 8]) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
             *reinterpret_cast<float4*>(&sGa[4][k8 * 8 + 4]) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
         }
+        if (SCALAR && k8 == 0) sGs[r] = vg[n][0];
 #pragma unroll
         for (int e = 0; e < 8; ++e) { vk[n][e] *= rk[n]; vq[n][e] *= rq[n]; }
     }
@@ -203,32 +209,45 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     umma::fence_after_sync();
     const uint32_t tmem = sh.tmem;
     // ---- operands ---------------------------------------------------------------------------------------------------
+    if (SCALAR) {          // one stacked tile: rows 0..63 = k, rows 64..127 = q (L2 statistics applied, zero past the end)
 #pragma unroll
-    for (int n = 0; n < 2; ++n) {
-        const int i = tid + n * 512, r = i >> 4, k8 = i & 15, I0 = r >> 4;
-        float ga[8], t8[8];
-        lds8(&sGa[I0][k8 * 8], ga);
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
+            store_split8(sKQ, sKQ + 32768, 128, r, k8, vk[n]);
+            store_split8(sKQ, sKQ + 32768, 128, 64 + r, k8, vq[n]);
+        }
+    } else {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(vg[n][e] - ga[e]);
-        store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + (r & 15), k8, t8);
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4, k8 = i & 15, I0 = r >> 4;
+            float ga[8], t8[8];
+            lds8(&sGa[I0][k8 * 8], ga);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) t8[e] = vq[n][e] * ex2f_(vg[n][e] - ga[e]);
-        store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + 16 + (r & 15), k8, t8);
+            for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(vg[n][e] - ga[e]);
+            store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + (r & 15), k8, t8);
 #pragma unroll
-        for (int I = 0; I < 4; ++I) {
-            if (I < I0) continue;
-            if (I > I0) lds8(&sGa[I][k8 * 8], ga);
+            for (int e = 0; e < 8; ++e) t8[e] = vq[n][e] * ex2f_(vg[n][e] - ga[e]);
+            store_split8(sKQ, sKQ + 32768, 128, 32 * I0 + 16 + (r & 15), k8, t8);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(ga[e] - vg[n][e]);
-            store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
+            for (int I = 0; I < 4; ++I) {
+                if (I < I0) continue;
+                if (I > I0) lds8(&sGa[I][k8 * 8], ga);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(ga[e] - vg[n][e]);
+                store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
+            }
         }
     }
     publish();
     if (umma::mma_issuer()) {
+        if (SCALAR) {      // D[m][j]: lanes 0..63 = K K^T rows, lanes 64..127 = Q K^T rows; columns j = K rows of the same tile
+            umma::gemm(tmem, umma::opnd_k(sKQ, sKQ + 32768, 128), umma::opnd_k(sKQ, sKQ + 32768, 128), 128, 64, 128, 0u);
+        } else {
 #pragma unroll
-        for (int I = 0; I < 4; ++I)
-            umma::gemm(tmem + 32 * I, umma::opnd_k(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1)),
-                       umma::opnd_k(sKQ, sKQ + 32768, 128, 32 * I), 128, 32, 128, 0u);
+            for (int I = 0; I < 4; ++I)
+                umma::gemm(tmem + 32 * I, umma::opnd_k(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1)),
+                           umma::opnd_k(sKQ, sKQ + 32768, 128, 32 * I), 128, 32, 128, 0u);
+        }
         umma::commit(&sh.bar);
     }
     // v for phase 3 is fetched while the products run
@@ -286,7 +305,25 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     if (tid == 0) umma::bulk_store_wait_read();    // the two tiles under sM / sInv / sP have left shared memory
     __syncthreads();
     for (int i = tid; i < CH * MLD / 4; i += 512) reinterpret_cast<float4*>(sInv)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (q < 2) {                              // lane = column j, cg = row block I: Gamma / Q K^T entries (16 I + r, j)
+    if (SCALAR) {                             // lane = row (K rows, then Q rows), cg = 16 columns j: decay applied here, for i >= j only
+        float v[16];
+        umma::tmem_ld16(umma::tmem_addr(tmem, warp, 16 * cg), v);
+        const int i = row & 63;
+        const float gi = sGs[i], bi = sh.beta[i];
+        float* dst = (q < 2 ? sM : sP) + i * MLD + 16 * cg;
+#pragma unroll
+        for (int j4 = 0; j4 < 16; j4 += 4) {
+            float o4[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = 16 * cg + j4 + e;
+                const float E = ex2f_(fminf(gi - sGs[j], 0.f));
+                if (q < 2) o4[e] = j < i ? bi * v[j4 + e] * E : (j == i ? 1.f : 0.f);
+                else o4[e] = j <= i ? p.scale * v[j4 + e] * E : 0.f;
+            }
+            *reinterpret_cast<float4*>(dst + j4) = make_float4(o4[0], o4[1], o4[2], o4[3]);
+        }
+    } else if (q < 2) {                       // lane = column j, cg = row block I: Gamma / Q K^T entries (16 I + r, j)
         float v[32];
         umma::tmem_ld32(umma::tmem_addr(tmem, warp, 32 * cg), v);
 #pragma unroll
@@ -405,11 +442,18 @@ struct BwdShared {
     float beta[CH];
 };
 
-// the intra-chunk operands of rows `n` (this thread's n-th (row, 8-channel) pair): [Kr; Qr] and the column tiles
+// the intra-chunk operands of rows `n` (this thread's n-th (row, 8-channel) pair): [Kr; Qr] and the column tiles; with a
+// scalar gate just the stacked [K; Q] tile (rows 0..63 = k, 64..127 = q), the decay goes into the weights instead
+template <bool SCALAR>
 __device__ __forceinline__ void stage_intra_operands(uint8_t* base, const float (*sGa)[DK], int tid, int n, const float (&vk)[8],
                                                      const float (&vq)[8], const float (&vg)[8]) {
     uint8_t* sKQ = base + KQ_OFF;
     const int i = tid + n * 512, r = i >> 4, k8 = i & 15, I0 = r >> 4;
+    if (SCALAR) {
+        store_split8(sKQ, sKQ + 32768, 128, r, k8, vk);
+        store_split8(sKQ, sKQ + 32768, 128, 64 + r, k8, vq);
+        return;
+    }
     float ga[8], t8[8];
     lds8(&sGa[I0][k8 * 8], ga);
 #pragma unroll
@@ -436,7 +480,10 @@ __device__ __forceinline__ void stage_intra_operands(uint8_t* base, const float 
 // returns.)
 constexpr int BWD_CHUNK_THREADS = 512;
 
-template <int DT>
+// SCALAR (one decay per token): the intra-chunk part contracts the plain k / q rows with weights that already carry
+// E_ij = 2^(g_i - g_j) (i > j, never a positive exponent):  [dq_row | T]^T = K^T [Wq E; dLs E]^T (N = 128),
+// dk_col^T = Q^T (Wq E) + K^T (beta dLs E); no anchors, and any g <= 0 is in range.  TMEM: [dq_row | T] 0, dk_col 128.
+template <int DT, bool SCALAR>
 __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(const MkdaBwdChunk p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ BwdShared sh;
@@ -448,6 +495,7 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
     __shared__ float sRk[CH], sRq[CH];                 // L2-norm scales of the chunk's rows (0 past the end)
     __shared__ __align__(16) float sPart[16][DK];
     __shared__ __align__(16) float sGa[4][DK];         // cumsum rows of the four block anchors
+    __shared__ float sGs[CH];                          // SCALAR: the cumsum of every row (rows past the end: the last valid one)
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sS = base;                                // S^T [v][K index] state tile (hi, lo)
     uint8_t* sT = base + BC_T;                         // dS'^T state tile; later:
@@ -598,6 +646,7 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
                     *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8]) = make_float4(vg[n][0], vg[n][1], vg[n][2], vg[n][3]);
                     *reinterpret_cast<float4*>(&sGa[r >> 4][k8 * 8 + 4]) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
                 }
+                if (SCALAR && k8 == 0) sGs[r] = vg[n][0];
             }
         }
         publish();
@@ -710,7 +759,7 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
         }
         {
             if (tid < CH) sDbw[tid] = sRedW[0][tid] + sRedW[1][tid];
-            stage_intra_operands(base, sGa, tid, 0, vk[0], vq[0], vg[0]);     // over the dead S / X^T / dVd^T / dX^T tiles, while P4 runs
+            stage_intra_operands<SCALAR>(base, sGa, tid, 0, vk[0], vq[0], vg[0]);     // over the dead S / X^T / dVd^T / dX^T tiles, while P4 runs
             umma::mbar_wait(&sh.barA, nA & 1);
             umma::fence_after_sync();
             if (q < 2) {
@@ -729,7 +778,7 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
             umma::commit(&sh.barA);
         }
         {
-            stage_intra_operands(base, sGa, tid, 1, vk[1], vq[1], vg[1]);     // the other half, while P5 runs
+            stage_intra_operands<SCALAR>(base, sGa, tid, 1, vk[1], vq[1], vg[1]);     // the other half, while P5 runs
             umma::mbar_wait(&sh.barA, nA & 1);                 // Z done: A, D2 diag(beta) and Y are dead
             umma::fence_after_sync();
             if (q < 2) {                                       // rows i = row of D1 = dO Vd^T and Z: the weights of the intra-chunk part
@@ -738,6 +787,7 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
                 float d[16], z[16];
                 umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + cg * 16), d);
                 umma::tmem_ld16(umma::tmem_addr(tmem, warp, 64 + cg * 16), z);
+                const float gi = SCALAR ? sGs[i] : 0.f;
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     float w8[8], d8[8], b8[8];
@@ -745,13 +795,19 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
                     for (int e = 0; e < 8; ++e) {
                         const int j = cg * 16 + hf * 8 + e;
                         const bool lo = j < i && i < len;
-                        w8[e] = lo ? p.scale * d[hf * 8 + e] : 0.f;
-                        d8[e] = lo ? -z[hf * 8 + e] : 0.f;
+                        const float E = SCALAR ? ex2f_(fminf(gi - sGs[j], 0.f)) : 1.f;
+                        w8[e] = lo ? p.scale * d[hf * 8 + e] * E : 0.f;
+                        d8[e] = lo ? -z[hf * 8 + e] * E : 0.f;
                         b8[e] = bt * d8[e];
                         if (j == i) sDiag[i] = i < len ? p.scale * d[hf * 8 + e] : 0.f;
                     }
-                    store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + (i & 15), 2 * cg + hf, w8);
-                    store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + 16 + (i & 15), 2 * cg + hf, d8);
+                    if (SCALAR) {      // [Wq E; dLs E] stacked by rows
+                        store_split8(sWD, sWD + 16384, 128, i, 2 * cg + hf, w8);
+                        store_split8(sWD, sWD + 16384, 128, 64 + i, 2 * cg + hf, d8);
+                    } else {
+                        store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + (i & 15), 2 * cg + hf, w8);
+                        store_split8(sWD, sWD + 16384, 128, 32 * (i >> 4) + 16 + (i & 15), 2 * cg + hf, d8);
+                    }
                     store_split8(sBd, sBd + 8192, 64, i, 2 * cg + hf, b8);
                 }
             }
@@ -759,16 +815,22 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
         ++nA;
         publish();
         if (umma::mma_issuer()) {
+            if (SCALAR) {
+                umma::gemm(tmem + 0, umma::opnd_mn(sKQ, sKQ + 32768, 128, 0), umma::opnd_k(sWD, sWD + 16384, 128), 128, 128, 64, 0u);
+                umma::gemm(tmem + 128, umma::opnd_mn(sKQ, sKQ + 32768, 128, 64), umma::opnd_mn(sWD, sWD + 16384, 128, 0), 128, 64, 64, 0u);
+                umma::gemm(tmem + 128, umma::opnd_mn(sKQ, sKQ + 32768, 128, 0), umma::opnd_mn(sBd, sBd + 8192, 64, 0), 128, 64, 64, 1u);
+            } else {
 #pragma unroll
-            for (int I = 0; I < 4; ++I) {
-                const int nj = 16 * (I + 1);
-                const umma::Opnd aKc = umma::opnd_mn(base + kc_off(I), base + kc_off(I) + kc_bytes(I), nj);
-                // both row terms (dq_row | T) of the block in one N = 32 product
-                umma::gemm(tmem + 32 * I, aKc, umma::opnd_k(sWD, sWD + 16384, 128, 32 * I), 128, 32, nj, 0u);
-                umma::gemm(tmem + ccol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I + 16), umma::opnd_mn(sWD, sWD + 16384, 128, 32 * I),
-                           128, nj, 16, 0u);
-                umma::gemm(tmem + ccol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I), umma::opnd_mn(sBd, sBd + 8192, 64, 16 * I),
-                           128, nj, 16, 1u);
+                for (int I = 0; I < 4; ++I) {
+                    const int nj = 16 * (I + 1);
+                    const umma::Opnd aKc = umma::opnd_mn(base + kc_off(I), base + kc_off(I) + kc_bytes(I), nj);
+                    // both row terms (dq_row | T) of the block in one N = 32 product
+                    umma::gemm(tmem + 32 * I, aKc, umma::opnd_k(sWD, sWD + 16384, 128, 32 * I), 128, 32, nj, 0u);
+                    umma::gemm(tmem + ccol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I + 16), umma::opnd_mn(sWD, sWD + 16384, 128, 32 * I),
+                               128, nj, 16, 0u);
+                    umma::gemm(tmem + ccol_off(I), umma::opnd_mn(sKQ, sKQ + 32768, 128, 32 * I), umma::opnd_mn(sBd, sBd + 8192, 64, 16 * I),
+                               128, nj, 16, 1u);
+                }
             }
             umma::commit(&sh.barA);
             if (more) {                                        // every operand tile is dead once these products are done:
@@ -810,24 +872,30 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
                 umma::tmem_ld8(umma::tmem_addr(tmem, warp, 192 + c0), aq);
                 umma::tmem_ld8(umma::tmem_addr(tmem, warp, 320 + c0), ak);
                 umma::tmem_ld8(umma::tmem_addr(tmem, warp, 384 + c0), ab);
-                umma::tmem_ld8(umma::tmem_addr(tmem, warp, 32 * cg + 8 * hf), vr);
-                umma::tmem_ld8(umma::tmem_addr(tmem, warp, 32 * cg + 16 + 8 * hf), vt);
+                if (SCALAR) {
+                    umma::tmem_ld8(umma::tmem_addr(tmem, warp, c0), vr);
+                    umma::tmem_ld8(umma::tmem_addr(tmem, warp, 64 + c0), vt);
+                    umma::tmem_ld8(umma::tmem_addr(tmem, warp, 128 + c0), dkc);
+                } else {
+                    umma::tmem_ld8(umma::tmem_addr(tmem, warp, 32 * cg + 8 * hf), vr);
+                    umma::tmem_ld8(umma::tmem_addr(tmem, warp, 32 * cg + 16 + 8 * hf), vt);
 #pragma unroll
-                for (int r = 0; r < 8; ++r) dkc[r] = 0.f;
+                    for (int r = 0; r < 8; ++r) dkc[r] = 0.f;
 #pragma unroll
-                for (int I = 0; I < 4; ++I) {
-                    if (I < cg) continue;                      // warp-uniform
-                    float c8[8];
-                    umma::tmem_ld8(umma::tmem_addr(tmem, warp, ccol_off(I) + c0), c8);
+                    for (int I = 0; I < 4; ++I) {
+                        if (I < cg) continue;                  // warp-uniform
+                        float c8[8];
+                        umma::tmem_ld8(umma::tmem_addr(tmem, warp, ccol_off(I) + c0), c8);
 #pragma unroll
-                    for (int r = 0; r < 8; ++r) dkc[r] += c8[r] * ex2f_(ga[I] - gg[8 * hf + r]);
+                        for (int r = 0; r < 8; ++r) dkc[r] += c8[r] * ex2f_(ga[I] - gg[8 * hf + r]);
+                    }
                 }
                 float bsv[8];
 #pragma unroll
                 for (int r = 0; r < 8; ++r) {
                     const int i = c0 + r, rr = 8 * hf + r;
                     const float g = gg[rr], kv = kq[rr], qv = qq[rr];
-                    const float up = ex2f_(g), re = ex2f_(gL - g), e = ex2f_(g - ga[cg]);
+                    const float up = ex2f_(g), re = ex2f_(gL - g), e = SCALAR ? 1.f : ex2f_(g - ga[cg]);
                     const float dqt = p.scale * aq[r], dkt = -ak[r], dkb = ab[r];
                     const float dqr = vr[r] * e, T = vt[r] * e, bt = sh.beta[i], dgn = sDiag[i];
                     bsv[r] = kv * T;
@@ -888,19 +956,22 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
     if (warp == 0) umma::tmem_dealloc(tmem, 512);
 }
 
-template <int DT>
+template <int DT, bool SCALAR>
 static int launch_bwd_chunk_tc_t(const MkdaBwdChunk* p, cudaStream_t stream) {
-    auto kern = bwd_chunk_tc_kernel<DT>;
+    auto kern = bwd_chunk_tc_kernel<DT, SCALAR>;
     if (int e = ensure_smem((const void*)kern, BWD_CHUNK_SMEM, "bwd_chunk")) return e;
     const int items = p->L.NC * p->L.HV;
     kern<<<items < sm_count() ? items : sm_count(), BWD_CHUNK_THREADS, BWD_CHUNK_SMEM, stream>>>(*p);
     return check_launch("bwd_chunk");
 }
 int launch_bwd_chunk_tc(const MkdaBwdChunk* p, cudaStream_t stream) {
-    switch (p->qkv_dtype) {
-        case MKDA_F32: return launch_bwd_chunk_tc_t<MKDA_F32>(p, stream);
-        case MKDA_BF16: return launch_bwd_chunk_tc_t<MKDA_BF16>(p, stream);
-        case MKDA_F16: return launch_bwd_chunk_tc_t<MKDA_F16>(p, stream);
+    switch (p->qkv_dtype * 2 + (p->scalar_gate ? 1 : 0)) {
+        case MKDA_F32 * 2: return launch_bwd_chunk_tc_t<MKDA_F32, false>(p, stream);
+        case MKDA_BF16 * 2: return launch_bwd_chunk_tc_t<MKDA_BF16, false>(p, stream);
+        case MKDA_F16 * 2: return launch_bwd_chunk_tc_t<MKDA_F16, false>(p, stream);
+        case MKDA_F32 * 2 + 1: return launch_bwd_chunk_tc_t<MKDA_F32, true>(p, stream);
+        case MKDA_BF16 * 2 + 1: return launch_bwd_chunk_tc_t<MKDA_BF16, true>(p, stream);
+        case MKDA_F16 * 2 + 1: return launch_bwd_chunk_tc_t<MKDA_F16, true>(p, stream);
     }
     return set_error(MKDA_ERR_ARG, "bwd_chunk: unsupported dtype");
 }
@@ -913,18 +984,21 @@ int tc_intra_status_clear() {
     return cudaMemcpyToSymbol(umma::g_timeout_flag, &z, sizeof(z)) == cudaSuccess ? 0 : -1;
 }
 
-template <int DT>
+template <int DT, bool SCALAR>
 static int launch_intra_fwd_tc_t(const MkdaIntraFwd* p, cudaStream_t stream) {
-    auto kern = intra_fwd_tc_kernel<DT>;
+    auto kern = intra_fwd_tc_kernel<DT, SCALAR>;
     if (int e = ensure_smem((const void*)kern, INTRA_TC_SMEM, "intra_fwd")) return e;
     kern<<<p->L.NC * p->L.HV, 512, INTRA_TC_SMEM, stream>>>(*p, sm_count());
     return check_launch("intra_fwd");
 }
 int launch_intra_fwd_tc(const MkdaIntraFwd* p, cudaStream_t stream) {
-    switch (p->qkv_dtype) {
-        case MKDA_F32: return launch_intra_fwd_tc_t<MKDA_F32>(p, stream);
-        case MKDA_BF16: return launch_intra_fwd_tc_t<MKDA_BF16>(p, stream);
-        case MKDA_F16: return launch_intra_fwd_tc_t<MKDA_F16>(p, stream);
+    switch (p->qkv_dtype * 2 + (p->scalar_gate ? 1 : 0)) {
+        case MKDA_F32 * 2: return launch_intra_fwd_tc_t<MKDA_F32, false>(p, stream);
+        case MKDA_BF16 * 2: return launch_intra_fwd_tc_t<MKDA_BF16, false>(p, stream);
+        case MKDA_F16 * 2: return launch_intra_fwd_tc_t<MKDA_F16, false>(p, stream);
+        case MKDA_F32 * 2 + 1: return launch_intra_fwd_tc_t<MKDA_F32, true>(p, stream);
+        case MKDA_BF16 * 2 + 1: return launch_intra_fwd_tc_t<MKDA_BF16, true>(p, stream);
+        case MKDA_F16 * 2 + 1: return launch_intra_fwd_tc_t<MKDA_F16, true>(p, stream);
     }
     return set_error(MKDA_ERR_ARG, "intra_fwd: unsupported dtype");
 }

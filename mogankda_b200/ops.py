@@ -129,7 +129,7 @@ def l2norm_rstd(x, eps=1e-6):
     return rstd
 
 
-def intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV):
+def intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV, scalar_gate=False):
     dev = q.device
     z = lambda w: torch.empty(lay.TT, HV, w, dtype=torch.float32, device=dev)      # noqa: E731
     u = z(128)
@@ -143,6 +143,7 @@ def intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV):
     p.q, p.k, p.v, p.qkv_dtype = _ptr(q), _ptr(k), _ptr(v), _dt(q)
     p.q_rstd, p.k_rstd = _ptr(q_rstd), _ptr(k_rstd)
     p.g_c, p.beta, p.scale = _ptr(g_c, torch.float32), _ptr(beta_e, torch.float32), scale
+    p.scalar_gate = int(scalar_gate)
     p.A, p.Aqk, p.nw, p.u = _ptr(A), _ptr(Aqk), _ptr(nw), _ptr(u)
     p.kbar, p.qs, p.gl = _ptr(kbar), _ptr(qs), _ptr(gl)
     _lib.call("mkda_intra_fwd", p, _stream())
@@ -233,7 +234,7 @@ def bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, *, dht=None, seg_dht=None,
 
 
 def bwd_chunk(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, A, h, dh, Vd, dO_t, dVd_t, scale, HK, HV,
-              beta_raw, beta_sigmoid, beta_scale):
+              beta_raw, beta_sigmoid, beta_scale, scalar_gate=False):
     """Every gradient local to a (chunk, v-head), in one kernel.  Returns (dq_v, dk_v, dgp, dbeta, dv)."""
     dev = q.device
     alloc = torch.empty if lay.covers_all else torch.zeros
@@ -246,7 +247,7 @@ def bwd_chunk(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, A, h, dh, Vd, dO_t, dVd
     p.q, p.k, p.v, p.qkv_dtype, p.q_rstd, p.k_rstd = _ptr(q), _ptr(k), _ptr(v), _dt(q), _ptr(q_rstd), _ptr(k_rstd)
     p.g_c, p.beta = _ptr(g_c, torch.float32), _ptr(beta_e, torch.float32)
     p.A, p.h, p.dh, p.Vd, p.dO_t, p.dVd_t = _ptr(A), _ptr(h), _ptr(dh), _ptr(Vd), _ptr(dO_t), _ptr(dVd_t)
-    p.scale = scale
+    p.scale, p.scalar_gate = scale, int(scalar_gate)
     p.beta_raw, p.beta_dtype = _ptr(beta_raw), _dt(beta_raw)
     p.beta_sigmoid, p.beta_scale = int(beta_sigmoid), float(beta_scale)
     p.dq_v, p.dk_v, p.dgp, p.dbeta, p.dbeta_dtype = _ptr(dq_v), _ptr(dk_v), _ptr(dgp), _ptr(dbeta), _dt(dbeta)

@@ -146,3 +146,22 @@ def test_a_wait_that_cannot_complete_expires_and_leaves_the_device_usable():
     ref = A.double() @ Bm.double().T
     assert ((D.double() - ref).abs().max() / ref.abs().max()).item() < 5e-5
     assert mk.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_scalar_gate_accepts_any_decay(dtype):
+    """chunk_gated_delta_rule has no lower bound on the per-token decay (the reference's scalar kernels form
+    exp(g_i - g_j) for i >= j only, mogan_kda/ops/gated_delta_rule/chunk/blackwell/fused_fwd.py:425-445).  Decays of -20 and
+    -40 per token, next to mild ones, must neither overflow nor lose the entries that matter: every result against the oracle."""
+    from tests.common import make_inputs, run
+    lv, do, dht, opts, _ = make_inputs(B=2, T=300, HK=2, HV=4, dtype=dtype, gate="precomputed", scalar=True, beta="precomputed",
+                                       l2=False, epi=None, h0=True, seed=77)
+    g = torch.Generator().manual_seed(78)
+    mild = -0.3 * torch.rand(2, 300, 4, generator=g)
+    strong = torch.where(torch.rand(2, 300, 4, generator=g) < 0.15, -20.0 - 20.0 * torch.rand(2, 300, 4, generator=g), mild)
+    lv["g"] = strong.cuda()
+    opts = dict(opts, lower_bound=None)
+    got = run(mk.chunk_delta_rule, lv, do, dht, opts, None)
+    ref = run(orc.chunked_delta_rule, lv, do, dht, opts, None, f64=True)
+    for n, r in ref.items():
+        check(n, got[n], r)
