@@ -190,6 +190,24 @@ typedef struct {
 } MkdaEpilogueBwd;
 int mkda_epilogue_bwd(const MkdaEpilogueBwd* p, void* stream);
 
+/* Gated RMSNorm backward for the chunked backward pass: the same arithmetic as mkda_epilogue_bwd, addressed through the
+ * chunk tables; dO leaves as the row tile per (chunk, v-head) that mkda_bwd_dh and mkda_bwd_chunk fetch by bulk copy (rows
+ * past the end of a chunk are zero) instead of as fp32 rows.  CTA b walks the (chunk, head) items b, b + part_rows, ... and
+ * writes one partial row of d weight.  Replaces rmsnorm_gated_bwd (mogan_kda/ops/kimi_delta_rule/epilogue.py:193-205). */
+typedef struct {
+    MkdaLayout L;
+    const void* dy; int dy_dtype;                  /* [TT,HV,128] */
+    const float* o_raw;                            /* [TT,HV,128] */
+    const void* norm_w; int norm_w_dtype;
+    const void* gate; int gate_dtype;
+    int act; float eps;
+    float* dO_t;               /* [NC,HV] row tiles */
+    void* dgate; int dgate_dtype;                  /* [TT,HV,128]; tokens outside every chunk are not written */
+    int part_rows;             /* min(NC * HV, MKDA_EPILOGUE_MAX_PART_ROWS) */
+    float* part_w;             /* [part_rows,128] partial sums of d weight, or NULL */
+} MkdaEpilogueBwdTiles;
+int mkda_epilogue_bwd_tiles(const MkdaEpilogueBwdTiles* p, void* stream);
+
 /* Gated RMSNorm backward for callers that cannot allocate.  It has no counterpart in the reference (whose wrapper
  * creates the per-block weight-gradient partials with torch.empty on every call).
  *
@@ -226,7 +244,9 @@ int mkda_epilogue_bwd_noalloc(const MkdaEpilogueBwdNoAlloc* p, void* stream);
  * Replaces bwd_dh_kda (mogan_kda/ops/kimi_delta_rule/chunk/hopper/bwd_dh.py:390-448). */
 typedef struct {
     MkdaLayout L;
-    const void* d_o; int do_dtype;                 /* [TT,HV,128] */
+    const void* d_o; int do_dtype;                 /* [TT,HV,128], or NULL when dO_in_t is given */
+    const float* dO_in_t;      /* [NC,HV] row tiles of dO as written by mkda_epilogue_bwd_tiles, or NULL (then d_o is staged
+                                * through registers and, if dO_t is given, written there in tile form) */
     const float* kbar;         /* [NC,HV] row tiles as written by mkda_intra_fwd */
     const float* qs;           /* [NC,HV] row tiles as written by mkda_intra_fwd */
     const float* gl;           /* [NC,HV,128] as written by mkda_intra_fwd */
@@ -258,7 +278,7 @@ typedef struct {
     const float* A;            /* [NC,HV] quarter tiles as written by mkda_intra_fwd */
     const float* h; const float* dh;               /* state tiles, see MKDA_STATE_TILE_BYTES */
     const float* Vd;           /* [NC,HV] chunk tiles as written by mkda_recur_fwd in the forward pass */
-    const float* dO_t;         /* [NC,HV] row tiles as written by mkda_bwd_dh */
+    const float* dO_t;         /* [NC,HV] row tiles as written by mkda_bwd_dh or mkda_epilogue_bwd_tiles */
     const float* dVd_t;        /* [NC,HV] chunk tiles as written by mkda_bwd_dh */
     float scale;
     const void* beta_raw; int beta_dtype; int beta_sigmoid; float beta_scale;

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 HEADER = os.path.join(HERE, "..", "include", "mkda.h")
 ENTRY_POINTS = (
     "mkda_gate_cumsum_fwd", "mkda_gate_bwd", "mkda_reduce_partials", "mkda_l2norm_rstd", "mkda_intra_fwd",
-    "mkda_recur_fwd", "mkda_out_fwd", "mkda_epilogue_bwd", "mkda_bwd_dh", "mkda_bwd_chunk",
+    "mkda_recur_fwd", "mkda_out_fwd", "mkda_epilogue_bwd", "mkda_epilogue_bwd_tiles", "mkda_bwd_dh", "mkda_bwd_chunk",
     "mkda_qk_grad_finish", "mkda_state_combine", "mkda_selftest_umma", "mkda_selftest_wait", "mkda_epilogue_bwd_noalloc",
 )
 ENUMS = {}

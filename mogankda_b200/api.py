@@ -89,9 +89,9 @@ class _DeltaRuleFunction(torch.autograd.Function):
         if dy is None:
             dy = torch.zeros(B, T, HV, 128, dtype=torch.float32 if cfg["has_ep"] else q.dtype, device=q.device)
         dy = dy.contiguous()
-        dw = dgate = None
-        if cfg["has_ep"]:
-            d_o, dgate, dw = ops.epilogue_bwd(dy, o_raw, ep_w, ep_gate, cfg["ep_act"], cfg["ep_eps"])
+        dw = dgate = d_o = dO_in = None
+        if cfg["has_ep"]:      # dO leaves the epilogue backward in the tile form the tensor-core kernels fetch
+            dO_in, dgate, dw = ops.epilogue_bwd_tiles(lay, dy, o_raw, ep_w, ep_gate, cfg["ep_act"], cfg["ep_eps"], HV)
             if dw is not None:
                 dw = dw.to(ep_w.dtype)
         else:
@@ -101,7 +101,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
         need_dh0 = initial_state is not None and ctx.needs_input_grad[7]
         if lay.segmented or cp is not None:
             # pre-pass from zero: only the gradient entering each segment is wanted, nothing per chunk is stored
-            _, _, _, dloc = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, store=False)
+            _, _, _, dloc = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, store=False, dO_in_t=dO_in)
             carry = None
             if dht is not None:
                 carry = dht.transpose(-1, -2).contiguous() if vf else dht
@@ -109,14 +109,15 @@ class _DeltaRuleFunction(torch.autograd.Function):
                 carry = cp.backward_carry(dloc, ms, carry, lay, HV, m_first)
             g_in, dh0 = ops.state_combine(lay.grp_seg_off, lay.NG, lay.NS, HV, dloc, ms, carry=carry, reverse=True,
                                           want_out=need_dh0 or cp is not None)
-            dh, dVd_t, dO_t, _ = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, dht=g_in, want_dh0=False)
+            dh, dVd_t, dO_t, _ = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, dht=g_in, want_dh0=False,
+                                            dO_in_t=dO_in)
             if cp is not None:
                 dh0 = cp.finish_backward(dh0)
             if dh0 is not None and vf:
                 dh0 = dh0.transpose(-1, -2).contiguous()
         else:
             dh, dVd_t, dO_t, dh0 = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, dht=dht,
-                                              state_v_first=vf, want_dh0=need_dh0)
+                                              state_v_first=vf, want_dh0=need_dh0, dO_in_t=dO_in)
         dq_v, dk_v, dgp, dbeta, dv = ops.bwd_chunk(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, A, h, dh, Vd, dO_t, dVd_t,
                                                    scale, HK, HV, beta, cfg["beta_mode"] == "sigmoid", cfg["beta_scale"],
                                                    scalar_gate=x.dim() == 3)

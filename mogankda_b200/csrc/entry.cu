@@ -26,7 +26,7 @@ extern "C" int mkda_out_fwd(const MkdaOutFwd* p, void* stream) {
 }
 
 extern "C" int mkda_bwd_dh(const MkdaBwdDh* p, void* stream) {
-    if (!p || !p->d_o || !p->kbar || !p->qs || !p->gl || !p->Aqk || !p->nw)
+    if (!p || (!p->d_o && !p->dO_in_t) || !p->kbar || !p->qs || !p->gl || !p->Aqk || !p->nw)
         return set_error(MKDA_ERR_ARG, "bwd_dh: null argument");
     if (p->L.NS == 0) return MKDA_OK;
     return launch_bwd_dh_tc(p, (cudaStream_t)stream);

@@ -272,23 +272,39 @@ __global__ void __launch_bounds__(128) l2norm_rstd_kernel(const MkdaL2Norm p) {
 
 // GVA group sum (fixed order) + L2-norm backward.  Block (chunk, q/k head, which of q / k); warp w takes rows w, w + 4, ...
 // of the chunk.  The per-v-head gradients arrive as the fp32 [64][128] tiles written by the chunk backward.
+// GT = v-heads per q/k head when it is 1, 2 or 4 (the loads of a row group are then all issued before the first use), 0 = any.
+template <int GT>
 __global__ void __launch_bounds__(128) qk_grad_finish_kernel(const MkdaQkGrad p) {
-    const int HK = p.L.HK, HV = p.L.HV, G = HV / HK;
+    const int HK = p.L.HK, HV = p.L.HV, G = GT ? GT : HV / HK;
     const int c = blockIdx.x / HK, hk = blockIdx.x - c * HK, which = blockIdx.y;
     const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const float* d_v = which ? p.dk_v : p.dq_v;
+    const float* d_v = (which ? p.dk_v : p.dq_v) + ((size_t)c * HV + hk * G) * CH * 128 + 4 * lane;
     const void* x = which ? p.k : p.q;
     const float* rstd = which ? p.k_rstd : p.q_rstd;
     void* dx = which ? p.dk : p.dq;
     for (int r0 = warp; r0 < len; r0 += 16) {
-        float4 s[4];
+        float4 s[4], xr[4];
+        float rs[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {                      // four rows in flight per warp
             const int r = r0 + 4 * u, rr = r < len ? r : len - 1;
-            s[u] = splat4(0.f);
-            for (int g = 0; g < G; ++g)
-                s[u] = add4(s[u], *reinterpret_cast<const float4*>(d_v + (((size_t)c * HV + hk * G + g) * CH + rr) * 128 + 4 * lane));
+            const size_t rowi = (size_t)(start + rr) * HK + hk;
+            if (GT) {
+                float4 part[GT ? GT : 1];
+#pragma unroll
+                for (int g = 0; g < (GT ? GT : 1); ++g) part[g] = *reinterpret_cast<const float4*>(d_v + ((size_t)g * CH + rr) * 128);
+                s[u] = part[0];
+#pragma unroll
+                for (int g = 1; g < (GT ? GT : 1); ++g) s[u] = add4(s[u], part[g]);
+            } else {
+                s[u] = splat4(0.f);
+                for (int g = 0; g < G; ++g) s[u] = add4(s[u], *reinterpret_cast<const float4*>(d_v + ((size_t)g * CH + rr) * 128));
+            }
+            if (rstd) {
+                rs[u] = rstd[rowi];
+                xr[u] = ld4(x, p.x_dtype, rowi * 128 + 4 * lane);
+            }
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -297,10 +313,9 @@ __global__ void __launch_bounds__(128) qk_grad_finish_kernel(const MkdaQkGrad p)
             const size_t rowi = (size_t)(start + r) * HK + hk;
             float4 t = s[u];
             if (rstd) {
-                const float rs = rstd[rowi];
-                const float4 y = scale4(ld4(x, p.x_dtype, rowi * 128 + 4 * lane), rs);
+                const float4 y = scale4(xr[u], rs[u]);
                 const float dot = warp_sum(hsum4(mul4(t, y)));
-                t = make_float4((t.x - dot * y.x) * rs, (t.y - dot * y.y) * rs, (t.z - dot * y.z) * rs, (t.w - dot * y.w) * rs);
+                t = make_float4((t.x - dot * y.x) * rs[u], (t.y - dot * y.y) * rs[u], (t.z - dot * y.z) * rs[u], (t.w - dot * y.w) * rs[u]);
             }
             st4(dx, p.x_dtype, rowi * 128 + 4 * lane, t);
         }
@@ -353,6 +368,90 @@ __global__ void __launch_bounds__(128) epilogue_bwd_kernel(const MkdaEpilogueBwd
         for (int k = 1; k < 4; ++k) s = add4(s, red[k][lane]);
         *reinterpret_cast<float4*>(p.part_w + (size_t)blockIdx.x * 128 + 4 * lane) = s;
     }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// gated RMSNorm backward, chunk-structured: the same arithmetic as epilogue_bwd_kernel, but dO leaves as the bf16 hi / lo
+// row tile [64 tokens][128] per (chunk, v-head) that the tensor-core kernels of the backward pass fetch by bulk copy
+// (rows past the end of the chunk are zero), instead of as fp32 rows that each of them would have to convert again.
+// CTA b walks the items b, b + gridDim.x, ...; half a warp covers one row of 128 (8 values per lane = one 16-byte piece
+// of the tile), a warp two rows at a time.
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__global__ void __launch_bounds__(128) epilogue_bwd_tiles_kernel(const MkdaEpilogueBwdTiles p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane & 15, hw = lane >> 4;
+    __shared__ float red[8][128];
+    const int HV = p.L.HV, total = p.L.NC * HV;
+    float w8[8], dw8[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { w8[e] = 1.f; dw8[e] = 0.f; }
+    if (p.norm_w) ld8(p.norm_w, p.norm_w_dtype, 8 * sub, w8);
+    for (int item = blockIdx.x; item < total; item += gridDim.x) {
+        const int c = item / HV, h = item - c * HV;
+        const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+        uint8_t* tile = reinterpret_cast<uint8_t*>(p.dO_t) + (size_t)item * 32768;
+#pragma unroll 2
+        for (int it = 0; it < 8; ++it) {
+            const int r = it * 8 + warp * 2 + hw;
+            const uint32_t toff = ((sub >> 3) * 64 * 128) + (r >> 3) * 1024 + (r & 7) * 128 + (((sub & 7) ^ (r & 7)) << 4);
+            // rows past the end re-read the last valid row (so that the shuffles below run unconditionally) and are zeroed
+            const bool valid = r < len;
+            const size_t off = ((size_t)(start + (valid ? r : len - 1)) * HV + h) * 128 + 8 * sub;
+            float o[8], dy[8], z[8], dov[8];
+            ld8(p.o_raw, MKDA_F32, off, o);
+            ld8(p.dy, p.dy_dtype, off, dy);
+            ld8(p.gate, p.gate_dtype, off, z);
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = fmaf(o[e], o[e], ss);
+            const float rs = 1.f / sqrtf(half_warp_sum(ss) * (1.f / 128.f) + p.eps);
+            float n[8], dn[8], dz[8], m = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float sg = sigmoidf_(z[e]);
+                float a, da;
+                if (p.act == MKDA_ACT_SILU) { a = z[e] * sg; da = sg * (1.f + z[e] * (1.f - sg)); }
+                else { a = sg; da = sg * (1.f - sg); }
+                n[e] = o[e] * rs;
+                dn[e] = dy[e] * w8[e] * a;
+                m = fmaf(dn[e], n[e], m);
+                dz[e] = dy[e] * n[e] * w8[e] * da;
+                if (valid) dw8[e] = fmaf(dy[e] * n[e], a, dw8[e]);
+            }
+            m = half_warp_sum(m) * (1.f / 128.f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dov[e] = valid ? rs * (dn[e] - n[e] * m) : 0.f;
+            if (valid) {
+                st4(p.dgate, p.dgate_dtype, off, make_float4(dz[0], dz[1], dz[2], dz[3]));
+                st4(p.dgate, p.dgate_dtype, off + 4, make_float4(dz[4], dz[5], dz[6], dz[7]));
+            }
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 hb = __floats2bfloat162_rn(dov[2 * e], dov[2 * e + 1]);
+                hi[e] = *reinterpret_cast<uint32_t*>(&hb);
+                const float ra = dov[2 * e] - __uint_as_float(hi[e] << 16);
+                const float rb = dov[2 * e + 1] - __uint_as_float(hi[e] & 0xffff0000u);
+                __nv_bfloat162 lb = __floats2bfloat162_rn(ra, rb);
+                lo[e] = *reinterpret_cast<uint32_t*>(&lb);
+            }
+            *reinterpret_cast<uint4*>(tile + toff) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<uint4*>(tile + 16384 + toff) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        }
+    }
+    if (!p.part_w) return;
+    // per-CTA partial of d weight: the eight (warp, half) partials of every column, added in a fixed order
+#pragma unroll
+    for (int e = 0; e < 8; ++e) red[warp * 2 + hw][8 * sub + e] = dw8[e];
+    __syncthreads();
+    float t = red[0][threadIdx.x];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) t += red[k][threadIdx.x];
+    p.part_w[(size_t)blockIdx.x * 128 + threadIdx.x] = t;
 }
 
 }  // namespace mkda
@@ -423,7 +522,13 @@ extern "C" int mkda_qk_grad_finish(const MkdaQkGrad* p, void* stream) {
     if (!p || !p->dq_v || !p->dk_v || !p->dq || !p->dk || !p->q || !p->k || p->L.HK <= 0 || p->L.HV % p->L.HK)
         return set_error(MKDA_ERR_ARG, "qk_grad_finish: bad argument");
     if (p->L.NC == 0) return MKDA_OK;
-    qk_grad_finish_kernel<<<dim3(p->L.NC * p->L.HK, 2), 128, 0, (cudaStream_t)stream>>>(*p);
+    const dim3 grid(p->L.NC * p->L.HK, 2);
+    switch (p->L.HV / p->L.HK) {
+        case 1: qk_grad_finish_kernel<1><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
+        case 2: qk_grad_finish_kernel<2><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
+        case 4: qk_grad_finish_kernel<4><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
+        default: qk_grad_finish_kernel<0><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
+    }
     return check_launch("qk_grad_finish");
 }
 
@@ -481,6 +586,16 @@ extern "C" int mkda_epilogue_bwd_noalloc(const MkdaEpilogueBwdNoAlloc* p, void* 
     if (int e = check_launch("epilogue_bwd_noalloc")) return e;
     reduce_cols_kernel<<<4, dim3(32, 8), 0, (cudaStream_t)stream>>>(scratch, nblk, 128, p->dweight);
     return check_launch("epilogue_bwd_noalloc (reduce)");
+}
+
+extern "C" int mkda_epilogue_bwd_tiles(const MkdaEpilogueBwdTiles* p, void* stream) {
+    if (!p || !p->dy || !p->o_raw || !p->gate || !p->dO_t || !p->dgate) return set_error(MKDA_ERR_ARG, "epilogue_bwd_tiles: null argument");
+    const int items = p->L.NC * p->L.HV;
+    if (items == 0) return MKDA_OK;
+    const int grid = items < MKDA_EPILOGUE_MAX_PART_ROWS ? items : MKDA_EPILOGUE_MAX_PART_ROWS;
+    if (p->part_w && p->part_rows != grid) return set_error(MKDA_ERR_ARG, "epilogue_bwd_tiles: part_rows must be min(NC * HV, MKDA_EPILOGUE_MAX_PART_ROWS)");
+    epilogue_bwd_tiles_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(*p);
+    return check_launch("epilogue_bwd_tiles");
 }
 
 extern "C" int mkda_epilogue_bwd(const MkdaEpilogueBwd* p, void* stream) {

@@ -197,6 +197,9 @@ namespace mkda {
 // ---------------------------------------------------------------------------------------------------------
 constexpr int DH_TC_SMEM = 64 * 1024 + 32 * 1024 + 16 * 1024 + 3 * 32 * 1024 + 1024;
 
+// DODT = dtype of the dO rows staged through registers, or DO_TILE: dO arrives as the row tile written by the chunked
+// gated-RMSNorm backward and is fetched by bulk copy like the other operands.
+constexpr int DO_TILE = 3;
 template <int DODT>
 __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -244,7 +247,9 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
             const size_t it = (size_t)c * HV + h;
             if (tid == 0) {
                 umma::bulk_store_wait_read();              // the previous chunk's saved tiles (dS', dO, dVd^T) have left shared memory
-                umma::mbar_expect_tx(&sh.ldw[1], umma::QUARTER_TILE_BYTES + umma::CHUNK_TILE_BYTES);
+                umma::mbar_expect_tx(&sh.ldw[1], umma::QUARTER_TILE_BYTES + umma::CHUNK_TILE_BYTES + (DODT == DO_TILE ? umma::CHUNK_TILE_BYTES : 0u));
+                if (DODT == DO_TILE)
+                    umma::bulk_load(sDo, reinterpret_cast<const uint8_t*>(p.dO_in_t) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[1]);
                 umma::bulk_load(sAq, reinterpret_cast<const uint8_t*>(p.Aqk) + it * umma::QUARTER_TILE_BYTES, umma::QUARTER_TILE_BYTES, &sh.ldw[1]);
                 umma::bulk_load(sKb, reinterpret_cast<const uint8_t*>(p.kbar) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[1]);
                 umma::mbar_expect_tx(&sh.ldw[0], 2 * umma::CHUNK_TILE_BYTES);
@@ -254,20 +259,24 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
             if (tid < DK) sh.gl[0][tid] = p.gl[it * 128 + tid];
         }
         float vo[2][8];
+        if (DODT != DO_TILE) {
 #pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-            ld8(p.d_o, DODT, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vo[n]);
+            for (int n = 0; n < 2; ++n) {
+                const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
+                ld8(p.d_o, DODT == DO_TILE ? MKDA_F32 : DODT, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vo[n]);
+            }
         }
         __syncthreads();                                   // sh.gl is complete; no copy reads the dO or dS' tile any more
+        if (DODT != DO_TILE) {
 #pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
-            if (r >= len) {
+            for (int n = 0; n < 2; ++n) {
+                const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
+                if (r >= len) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) vo[n][e] = 0.f;
+                    for (int e = 0; e < 8; ++e) vo[n][e] = 0.f;
+                }
+                store_split8(sDo, sDo + 16384, 64, r, k8, vo[n]);
             }
-            store_split8(sDo, sDo + 16384, 64, r, k8, vo[n]);
         }
         {   // gradient leaving the chunk: operand tile (saved as it is by the issuing thread below), decay
             float s[32];
@@ -291,7 +300,7 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
         if (tid == 0) {
             const size_t it = (size_t)c * HV + h;
             if (p.dh) umma::bulk_store(reinterpret_cast<uint8_t*>(p.dh) + it * umma::STATE_TILE_BYTES, sAh, umma::STATE_TILE_BYTES);
-            if (p.dO_t) umma::bulk_store(reinterpret_cast<uint8_t*>(p.dO_t) + it * umma::CHUNK_TILE_BYTES, sDo, umma::CHUNK_TILE_BYTES);
+            if (DODT != DO_TILE && p.dO_t) umma::bulk_store(reinterpret_cast<uint8_t*>(p.dO_t) + it * umma::CHUNK_TILE_BYTES, sDo, umma::CHUNK_TILE_BYTES);
         }
         if (umma::mma_issuer()) {
             umma::mbar_wait(&sh.ldw[1], ((c_end - 1 - c) & 1));               // this chunk's Aqk and kbar tiles have landed
@@ -317,8 +326,8 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
         if (tid == 0 && p.dVd_t)
             umma::bulk_store(reinterpret_cast<uint8_t*>(p.dVd_t) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES, sKb, umma::CHUNK_TILE_BYTES);
         if (umma::mma_issuer()) {
-            umma::gemm(tmem, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sQs, sQs + 16384, 64), 128, 128, 64, 1u);
             umma::mbar_wait(&sh.ldw[0], ((c_end - 1 - c) & 1));               // this chunk's q and nw tiles have landed
+            umma::gemm(tmem, umma::opnd_mn(sDo, sDo + 16384, 64), umma::opnd_mn(sQs, sQs + 16384, 64), 128, 128, 64, 1u);
             umma::gemm(tmem, umma::opnd_k(sKb, sKb + 16384, 128), umma::opnd_k(sNw, sNw + 16384, 128), 128, 128, 64, 1u);
             umma::commit(&sh.bar);
         }
@@ -349,6 +358,7 @@ static int launch_bwd_dh_tc_t(const MkdaBwdDh* p, cudaStream_t stream) {
     return check_launch("bwd_dh");
 }
 int launch_bwd_dh_tc(const MkdaBwdDh* p, cudaStream_t stream) {
+    if (p->dO_in_t) return launch_bwd_dh_tc_t<DO_TILE>(p, stream);
     switch (p->do_dtype) {
         case MKDA_F32: return launch_bwd_dh_tc_t<MKDA_F32>(p, stream);
         case MKDA_BF16: return launch_bwd_dh_tc_t<MKDA_BF16>(p, stream);

@@ -210,25 +210,51 @@ def epilogue_bwd(dy, o_raw, weight, gate, act, eps):
     return d_o, dgate, dw
 
 
+def epilogue_bwd_tiles(lay, dy, o_raw, weight, gate, act, eps, HV):
+    """Gated RMSNorm backward addressed through the chunk tables.  -> (dO_t row tiles [NC,HV], dgate [like gate], dweight
+    fp32 [128] or None)."""
+    dev = o_raw.device
+    dO_t = torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=dev)
+    dgate = (torch.empty_like if lay.covers_all else torch.zeros_like)(gate)
+    nblk = min(lay.NC * HV, _lib.MKDA_EPILOGUE_MAX_PART_ROWS)
+    part = torch.empty(nblk, 128, dtype=torch.float32, device=dev) if weight is not None else None
+    p = STRUCTS["MkdaEpilogueBwdTiles"]()
+    p.L = _layout_struct(lay, 1, HV)
+    p.dy, p.dy_dtype, p.o_raw = _ptr(dy), _dt(dy), _ptr(o_raw, torch.float32)
+    if weight is not None:
+        p.norm_w, p.norm_w_dtype = _ptr(weight), _dt(weight)
+    p.gate, p.gate_dtype, p.act, p.eps = _ptr(gate), _dt(gate), ACTS[act], float(eps)
+    p.dO_t, p.dgate, p.dgate_dtype, p.part_rows, p.part_w = _ptr(dO_t), _ptr(dgate), _dt(dgate), nblk, _ptr(part)
+    _lib.call("mkda_epilogue_bwd_tiles", p, _stream())
+    dw = reduce_partials(part, nblk, 128) if part is not None else None
+    return dO_t, dgate, dw
+
+
 def bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, *, dht=None, seg_dht=None,
-           state_v_first=False, want_dh0=True, segments=True, store=True):
-    """Reverse state chain.  With ``store`` the per-chunk results leave as tiles for ``bwd_chunk``: dh (state tiles), dVd^T
-    (chunk tiles) and the staged dO (row tiles); a pre-pass that only wants the segment-level gradient passes
-    ``store=False``.  Returns (dh, dVd_t, dO_t, dh0)."""
+           state_v_first=False, want_dh0=True, segments=True, store=True, dO_in_t=None):
+    """Reverse state chain.  dO comes either as rows ``d_o`` [TT,HV,128] or as the row tiles ``dO_in_t`` of
+    ``epilogue_bwd_tiles``.  With ``store`` the per-chunk results leave as tiles for ``bwd_chunk``: dh (state tiles), dVd^T
+    (chunk tiles) and, for row input, the staged dO (row tiles); a pre-pass that only wants the segment-level gradient
+    passes ``store=False``.  Returns (dh, dVd_t, dO_t, dh0) with dO_t = ``dO_in_t`` when that was given."""
     dev = nw.device
     NS = lay.NS if segments else lay.N
     p = STRUCTS["MkdaBwdDh"]()
     p.L = _layout_struct(lay, HK, HV, segments)
-    p.d_o, p.do_dtype = _ptr(d_o), _dt(d_o)
+    if dO_in_t is not None:
+        p.dO_in_t = _ptr(dO_in_t, torch.float32)
+    else:
+        p.d_o, p.do_dtype = _ptr(d_o), _dt(d_o)
     p.kbar, p.qs, p.gl, p.Aqk, p.nw = _ptr(kbar), _ptr(qs), _ptr(gl), _ptr(Aqk), _ptr(nw)
     p.dht, p.seg_dht, p.state_v_first = _ptr(dht, torch.float32), _ptr(seg_dht, torch.int32), int(state_v_first)
-    dh = dVd_t = dO_t = None
+    dh = dVd_t = None
+    dO_t = dO_in_t
     if store:
         dh = torch.empty(lay.NC, HV, 128, 128, dtype=torch.float32, device=dev)
         dVd_t = torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=dev)
-        dO_t = torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=dev)
+        if dO_in_t is None:
+            dO_t = torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=dev)
     dh0 = torch.empty(NS, HV, 128, 128, dtype=torch.float32, device=dev) if want_dh0 else None
-    p.dh, p.dVd_t, p.dO_t, p.dh0 = _ptr(dh), _ptr(dVd_t), _ptr(dO_t), _ptr(dh0)
+    p.dh, p.dVd_t, p.dO_t, p.dh0 = _ptr(dh), _ptr(dVd_t), _ptr(None if dO_in_t is not None else dO_t), _ptr(dh0)
     _lib.call("mkda_bwd_dh", p, _stream())
     return dh, dVd_t, dO_t, dh0
 

@@ -220,11 +220,17 @@ def pack_row_tiles(X, lay):
     return out.view(torch.float32).reshape(lay.NC, H, 64, 128)
 
 
-def unpack_row_tiles(T, lay, TT):
+def row_tiles_dense(T, lay):
+    """float32-typed row tiles -> fp32 [NC, H, 64, 128] (hi + lo), the rows past the end of each chunk included."""
     H = T.shape[1]
     halves = T.contiguous().view(torch.bfloat16).reshape(lay.NC, H, 2, 64 * 128)
     idx = _row_tile_index().to(T.device)
-    dense = (halves[..., 0, idx].float() + halves[..., 1, idx].float()).reshape(lay.NC, H, 64, 128)
+    return (halves[..., 0, idx].float() + halves[..., 1, idx].float()).reshape(lay.NC, H, 64, 128)
+
+
+def unpack_row_tiles(T, lay, TT):
+    H = T.shape[1]
+    dense = row_tiles_dense(T, lay)
     X = torch.zeros(TT, H, 128, device=T.device)
     for c, s0, n in _chunk_rows(lay):
         X[s0:s0 + n] = dense[c, :, :n].permute(1, 0, 2)

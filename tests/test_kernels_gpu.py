@@ -6,7 +6,7 @@ import torch
 from mogankda_b200 import ops
 from mogankda_b200.index import get_layout
 from oracle import kda_oracle as orc
-from tests.common import (VARLEN_CU, make_inputs, pack_chunk_tiles, pack_quarter_tiles, pack_plain_tiles, pack_row_tiles, pack_state_tiles,
+from tests.common import (VARLEN_CU, make_inputs, pack_chunk_tiles, pack_quarter_tiles, pack_plain_tiles, pack_row_tiles, pack_state_tiles, row_tiles_dense,
                           scaled_operands, unpack_chunk_tiles, unpack_plain_tiles, unpack_quarter_tiles, unpack_row_tiles,
                           unpack_state_tiles)
 
@@ -109,6 +109,11 @@ def test_bwd_dh(world):
     _err("dVd", unpack_chunk_tiles(dVd_t, lay, world["TT"]), bw["dVd"])
     # the staged dO leaves as it was split for the products: hi + lo reproduces the fp32 input to 2^-16
     _err("dO", unpack_row_tiles(dO_t, lay, world["TT"]), world["do"], 2e-5)
+    # dO given as the row tiles of the chunked epilogue backward: same results, the tile is handed through
+    dh2, dVd2, dO2, dh02 = ops.bwd_dh(lay, None, world["kbar_t"], world["qs_t"], world["gl_t"],
+                                      pack_quarter_tiles(f32(fw["Aqk"]), lay), pack_chunk_tiles(f32(fw["nw"]), lay), 2, 4,
+                                      dht=world["dht"], dO_in_t=dO_t)
+    assert dO2 is dO_t and torch.equal(dh2, dh) and torch.equal(dVd2, dVd_t) and torch.equal(dh02, dh0)
     # a pre-pass that stores nothing still returns the segment-level gradient
     _, _, _, dh0b = ops.bwd_dh(lay, world["do"], world["kbar_t"], world["qs_t"], world["gl_t"],
                                pack_quarter_tiles(f32(fw["Aqk"]), lay), pack_chunk_tiles(f32(fw["nw"]), lay), 2, 4,
@@ -160,6 +165,15 @@ def test_epilogue_backward(world):
         d_o, dgate, dw = ops.epilogue_bwd(dy.contiguous(), f32(fw["o"]), lv["ep_w"], lv["ep_gate"], act, 1e-6)
         _err("do", d_o.view_as(ro), ro, 1e-5); _err("dw", dw, rw, 1e-5)
         _err("dgate", dgate.reshape(rz.shape), rz, 1e-5 if dgate.dtype == torch.float32 else 2.0 ** -8)
+        # the chunk-structured variant: dO as row tiles (hi + lo reproduces fp32 to 2^-16), same dgate and dw
+        lay = world["lay"]
+        dO_t, dgate2, dw2 = ops.epilogue_bwd_tiles(lay, dy.contiguous(), f32(fw["o"]), lv["ep_w"], lv["ep_gate"], act, 1e-6, 4)
+        _err("do (tiles)", unpack_row_tiles(dO_t, lay, world["TT"]), ro.reshape(world["TT"], 4, 128), 2e-5)
+        dense = row_tiles_dense(dO_t, lay)
+        for c, n in enumerate(lay.chunk_len.tolist()):                     # rows past the end of a chunk are exact zeros
+            assert float(dense[c, :, n:].abs().sum()) == 0.0
+        _err("dw (tiles)", dw2, rw, 1e-5)
+        _err("dgate (tiles)", dgate2.reshape(rz.shape), rz, 1e-5 if dgate2.dtype == torch.float32 else 2.0 ** -8)
 
 
 @pytest.mark.parametrize("mode", [0, 1, 2, 3])
