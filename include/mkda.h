@@ -108,7 +108,7 @@ typedef struct {
     float* A;      /* [NC,HV] quarter tiles: (I + strictlower(diag(beta) Gamma))^-1 */
     float* Aqk;    /* [NC,HV] quarter tiles: scale * lower(Q K^T with decay) */
     float* nw;     /* [NC,HV] chunk tiles: nw^T [K index][token], nw = -A (beta k 2^g) */
-    float* u;      /* [TT,HV,128]  A (beta v) */
+    float* u;      /* [NC,HV] chunk tiles: u^T [v][token], u = A (beta v) */
     float* kbar;   /* [NC,HV] row tiles: k 2^(gL - g) with gL the cumsum at the chunk's last token */
     float* qs;     /* [NC,HV] row tiles: scale q 2^g */
     float* gl;     /* [NC,HV,128] 2^gL, the decay of the state over the whole chunk */
@@ -125,8 +125,8 @@ int mkda_intra_fwd(const MkdaIntraFwd* p, void* stream);
 #define MKDA_STATE_TILE_BYTES 65536
 /* Chunk tile: the same idea for a [128][64 tokens] operand, MKDA_CHUNK_TILE_BYTES per (chunk, v-head): bf16 hi (16 KB)
  * then lo (16 KB), 128 rows x 128 bytes each, same swizzle.  Used for Vd^T [v][token] between mkda_recur_fwd and mkda_out_fwd
- * (token columns past the end of the chunk are zero), and for nw^T [K index][token]
- * between mkda_intra_fwd and the serial kernels.
+ * (token columns past the end of the chunk are zero), for nw^T [K index][token] and u^T [v][token]
+ * between mkda_intra_fwd and the serial kernels, and for dVd^T [v][token] between mkda_bwd_dh and mkda_bwd_chunk.
  * Row tile: the same 32 KB for a [64 tokens][128] operand (rows = tokens; hi 16 KB then lo 16 KB, each two column blocks of
  * 64 rows x 128 bytes): the scaled operands kbar and qs, token rows past the end of the chunk are zero. */
 #define MKDA_CHUNK_TILE_BYTES 32768
@@ -143,7 +143,7 @@ int mkda_intra_fwd(const MkdaIntraFwd* p, void* stream);
 typedef struct {
     MkdaLayout L;
     const float* nw;           /* [NC,HV] chunk tiles as written by mkda_intra_fwd */
-    const float* u;            /* [TT,HV,128] */
+    const float* u;            /* [NC,HV] chunk tiles as written by mkda_intra_fwd */
     const float* kbar;         /* [NC,HV] row tiles as written by mkda_intra_fwd */
     const float* gl;           /* [NC,HV,128] as written by mkda_intra_fwd */
     const float* h0;           /* [*,HV,128,128] or NULL */

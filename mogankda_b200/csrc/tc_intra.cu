@@ -372,15 +372,18 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     umma::fence_async_smem();
     __syncthreads();
     if (tid == 0) umma::bulk_store(reinterpret_cast<uint8_t*>(p.nw) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES, base, umma::CHUNK_TILE_BYTES);
-    {   // u goes out row-wise while the tile is being copied
-        float b[16];
+    {   // u^T [v][tok] leaves the same way (token columns past the end are exact zeros: A has identity rows there and
+        // beta v zero rows), built next to the nw tile while that one is being copied
+        float b[16], u0[8], u1[8];
         umma::tmem_ld16(umma::tmem_addr(tmem, warp, 192 + 16 * cg), b);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const int i = 16 * cg + j;
-            if (i < len) p.u[((size_t)(start + i) * HV + h) * 128 + row] = b[j];
-        }
+        for (int j = 0; j < 8; ++j) { u0[j] = b[j]; u1[j] = b[8 + j]; }
+        store_split8(base + 32768, base + 32768 + 16384, 128, row, 2 * cg, u0);
+        store_split8(base + 32768, base + 32768 + 16384, 128, row, 2 * cg + 1, u1);
     }
+    umma::fence_async_smem();
+    __syncthreads();
+    if (tid == 0) umma::bulk_store(reinterpret_cast<uint8_t*>(p.u) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES, base + 32768, umma::CHUNK_TILE_BYTES);
     if (tid == 0) umma::bulk_store_wait_read();
     umma::fence_before_sync();
     __syncthreads();

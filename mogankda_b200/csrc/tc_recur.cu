@@ -18,6 +18,7 @@ using umma::store_split8;
 struct RecurShared {
     uint64_t bar;
     uint64_t ldw[2];       // arrival of the nw chunk tiles (bulk copies)
+    uint64_t ldu;          // arrival of the u chunk tile
     uint32_t tmem;
     float gl[2][DK];
 };
@@ -29,7 +30,7 @@ __device__ __forceinline__ void publish_operands() {
     umma::fence_after_sync();
 }
 
-constexpr int RECUR_TC_SMEM = 64 * 1024 + 4 * 32 * 1024 + 1024;
+constexpr int RECUR_TC_SMEM = 64 * 1024 + 5 * 32 * 1024 + 1024;
 
 __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -39,6 +40,7 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
     uint8_t* sAl = sAh + 32768;
     uint8_t* sW[2] = {sAl + 32768, sAl + 32768 + 65536};            // nw^T chunk tile [K index][tok] (hi, lo 16 KB each); later Vd^T [v][tok]
     uint8_t* sK[2] = {sW[0] + 32768, sW[1] + 32768};                 // kbar row tile [tok][K index], fetched by bulk copy
+    uint8_t* sU = sAl + 32768 + 2 * 65536;                           // u^T chunk tile [v][tok] of the current chunk
 
     const bool trans = blockIdx.x == 1;
     const int h = blockIdx.y, seg = blockIdx.z, HV = p.L.HV;
@@ -47,7 +49,7 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
     const bool vf = p.state_v_first != 0;
 
     if (warp == 0) umma::tmem_alloc(&sh.tmem, 256);
-    if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::mbar_init(&sh.ldw[0], 1); umma::mbar_init(&sh.ldw[1], 1); umma::fence_barrier_init(); }
+    if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::mbar_init(&sh.ldw[0], 1); umma::mbar_init(&sh.ldw[1], 1); umma::mbar_init(&sh.ldu, 1); umma::fence_barrier_init(); }
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
@@ -83,17 +85,18 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
         if (tid < DK) sh.gl[buf][tid] = p.gl[it * 128 + tid];
     };
 
-    if (c_beg < c_end) fetch(c_beg, 0);
-    for (int c = c_beg; c < c_end; ++c) {
-        const int buf = (c - c_beg) & 1, start = p.L.chunk_start[c], len = p.L.chunk_len[c];
-        const bool more = c + 1 < c_end;
-        float uu[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const int t = cg * 16 + j, tt = t < len ? t : len - 1;
-            uu[j] = trans ? 0.f : p.u[((size_t)(start + tt) * HV + h) * 128 + row];
-            if (t >= len) uu[j] = 0.f;
+    // u^T of a chunk arrives as the chunk tile written by the intra-chunk kernel (one buffer: requested as soon as the
+    // previous chunk has consumed its own)
+    auto fetch_u = [&](int c) {
+        if (tid == 0 && !trans) {
+            umma::mbar_expect_tx(&sh.ldu, umma::CHUNK_TILE_BYTES);
+            umma::bulk_load(sU, reinterpret_cast<const uint8_t*>(p.u) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldu);
         }
+    };
+    if (c_beg < c_end) { fetch(c_beg, 0); fetch_u(c_beg); }
+    for (int c = c_beg; c < c_end; ++c) {
+        const int buf = (c - c_beg) & 1;
+        const bool more = c + 1 < c_end;
         if (tid == 0) umma::bulk_store_wait_read();         // the previous chunk's saved tiles have left shared memory
         if (more) fetch(c + 1, buf ^ 1);                    // ... so the other buffers (last read by chunk c - 1) take the next tiles
         __syncthreads();                                   // sh.gl[buf] is complete
@@ -128,15 +131,23 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
         {   // Vd^T = u^T + St nw^T as the operand tile A(m = v, k = tok)
             float d[16], a0[8], a1[8];
             umma::tmem_ld16(umma::tmem_addr(tmem, warp, 128 + cg * 16), d);
+            if (!trans) {
+                umma::mbar_wait(&sh.ldu, (c - c_beg) & 1);
+                umma::load_tile8(sU, sU + 16384, 128, row, 2 * cg, a0);
+                umma::load_tile8(sU, sU + 16384, 128, row, 2 * cg + 1, a1);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a0[j] = a1[j] = 0.f;
+            }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                const float vd = d[j] + uu[j];
-                if (j < 8) a0[j] = vd; else a1[j - 8] = vd;
+                if (j < 8) a0[j] += d[j]; else a1[j - 8] += d[j];
             }
             store_split8(sW[buf], sW[buf] + 16384, 128, row, 2 * cg, a0);       // the nw tile is dead: it becomes Vd^T
             store_split8(sW[buf], sW[buf] + 16384, 128, row, 2 * cg + 1, a1);
         }
         publish_operands();
+        if (more) fetch_u(c + 1);                           // every thread has read its part of the u tile
         // the Vd^T operand tile is also what the output kernel consumes: saved as it is (columns past the end are zero)
         if (tid == 0 && p.Vd && !trans)
             umma::bulk_store(reinterpret_cast<uint8_t*>(p.Vd) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES, sW[buf], umma::CHUNK_TILE_BYTES);

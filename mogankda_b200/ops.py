@@ -131,12 +131,10 @@ def l2norm_rstd(x, eps=1e-6):
 
 def intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV, scalar_gate=False):
     dev = q.device
-    z = lambda w: torch.empty(lay.TT, HV, w, dtype=torch.float32, device=dev)      # noqa: E731
-    u = z(128)
     A = torch.empty(lay.NC, HV, 32, 128, dtype=torch.float32, device=q.device)       # quarter tiles per (chunk, head)
     Aqk = torch.empty(lay.NC, HV, 32, 128, dtype=torch.float32, device=q.device)
     tile = lambda: torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=dev)      # noqa: E731  (32 KB per chunk, head)
-    nw, kbar, qs = tile(), tile(), tile()          # nw^T chunk tiles; kbar and scale q 2^g row tiles
+    nw, u, kbar, qs = tile(), tile(), tile(), tile()          # nw^T and u^T chunk tiles; kbar and scale q 2^g row tiles
     gl = torch.empty(lay.NC, HV, 128, dtype=torch.float32, device=dev)
     p = STRUCTS["MkdaIntraFwd"]()
     p.L = _layout_struct(lay, HK, HV)

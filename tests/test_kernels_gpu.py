@@ -65,6 +65,7 @@ def test_intra_fwd(world):
     _err("qs", unpack_row_tiles(qs, world["lay"], world["TT"]), world["qs"])
     _err("gl", gl, world["gl"])
     nw = unpack_chunk_tiles(nw, world["lay"], world["TT"])
+    u = unpack_chunk_tiles(u, world["lay"], world["TT"])
     A, Aqk = unpack_quarter_tiles(A, world["lay"], world["TT"]), unpack_quarter_tiles(Aqk, world["lay"], world["TT"])
     for n, t in dict(A=A, Aqk=Aqk, nw=nw, u=u).items():
         _err(n, t, fw[n])
@@ -79,7 +80,7 @@ def test_intra_fwd(world):
 
 def test_recurrence_and_output(world):
     lv, fw, f32, lay = world["lv"], world["fw"], world["f32"], world["lay"]
-    h, Vd, ht, _ = ops.recur_fwd(lay, pack_chunk_tiles(f32(fw["nw"]), lay), f32(fw["u"]), world["kbar_t"], world["gl_t"],
+    h, Vd, ht, _ = ops.recur_fwd(lay, pack_chunk_tiles(f32(fw["nw"]), lay), pack_chunk_tiles(f32(fw["u"]), lay), world["kbar_t"], world["gl_t"],
                                  2, 4, h0=lv["h0"])
     _err("h", unpack_state_tiles(h), fw["h"]); _err("Vd", unpack_chunk_tiles(Vd, lay, world["TT"]), fw["Vd"])
     _err("ht", ht, fw["ht"])
@@ -91,7 +92,7 @@ def test_recurrence_and_output(world):
 def test_transition_matrix_reproduces_the_state_pass(world):
     """State leaving a segment = transition @ state entering + state reached from zero (what the prefix combine uses)."""
     lv, fw, f32, lay = world["lv"], world["fw"], world["f32"], world["lay"]
-    args = (lay, pack_chunk_tiles(f32(fw["nw"]), lay), f32(fw["u"]), world["kbar_t"], world["gl_t"], 2, 4)
+    args = (lay, pack_chunk_tiles(f32(fw["nw"]), lay), pack_chunk_tiles(f32(fw["u"]), lay), world["kbar_t"], world["gl_t"], 2, 4)
     _, _, hs, ms = ops.recur_fwd(*args, store_h=False, store_vd=False, want_transition=True)
     _, _, ht, _ = ops.recur_fwd(*args, h0=lv["h0"], store_h=False, store_vd=False)
     _err("M h0 + h", ms.double() @ lv["h0"].double() + hs.double(), ht)
