@@ -137,13 +137,32 @@ KERNEL_BYTES = {
     "mkda_out_fwd": 3584, "mkda_epilogue_bwd": 2048, "mkda_bwd_dh": 4360,
     "mkda_bwd_chunk": 6664, "mkda_gate_bwd": 1536, "mkda_qk_grad_finish": 640,
 }
-# DRAM traffic per token per v-head measured by ncu on the 1B-shape case (profiles/counters_per_kernel_1b_shape.md),
-# bytes (dram read + write per launch / 131072 token-heads); it grows in proportion to tokens x heads.
-KERNEL_TRAFFIC = {
-    "mkda_intra_fwd": 3160, "mkda_recur_fwd": 2771, "mkda_out_fwd": 3351, "mkda_bwd_dh": 3612,
-    "mkda_gate_cumsum_fwd": 641, "mkda_epilogue_bwd": 1773, "mkda_qk_grad_finish": 653,
-    "mkda_l2norm_rstd": 128,
-}
+def load_kernel_traffic(path=os.path.join(ROOT, "profiles", "counters_per_kernel_1b_shape.md")):
+    """DRAM traffic per token per v-head of every kernel, read from the committed ncu summary (its table has the columns
+    `entry point`, `pass` and `B/token-head` = (dram read + write per launch) / token-heads of the captured case; traffic grows in
+    proportion to tokens x heads).  Rows of the pre-pass of a serial kernel are skipped; several launches of one entry point
+    are averaged.  Returns {} when the file is missing."""
+    out, cols = {}, None
+    if not os.path.exists(path):
+        return out
+    acc = {}
+    for line in open(path):
+        cells = [c.strip() for c in line.strip().strip("|").split("|")]
+        if "entry point" in cells and "B/token-head" in cells:
+            cols = {name: i for i, name in enumerate(cells)}
+            continue
+        if cols is None or len(cells) < len(cols) or not cells[0].startswith("`mkda_"):
+            continue
+        if cells[cols["pass"]] != "main":
+            continue
+        try:
+            acc.setdefault(cells[0].strip("`"), []).append(float(cells[cols["B/token-head"]]))
+        except ValueError:
+            continue
+    return {k: sum(v) / len(v) for k, v in acc.items()}
+
+
+KERNEL_TRAFFIC = load_kernel_traffic()
 
 
 class LaunchRecorder:

@@ -138,7 +138,7 @@ __device__ __forceinline__ void invert_unit_lower(const float* __restrict__ sM, 
 // [K; Q] tile) and the decay is applied to the accumulators, element by element and for i >= j only: nothing is anchored,
 // no exponent is ever positive, and any g <= 0 is in range (the per-channel path needs g >= -5 per token).
 template <int DT, bool SCALAR>
-__global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd p, const int ahead) {
+__global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ IntraShared sh;
     __shared__ __align__(16) float sGa[5][DK];         // cumsum rows of the four block anchors, [4] = last valid row
@@ -155,40 +155,42 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     uint8_t* sKB = base + OPND_BYTES;                  // kbar [tok][K index] hi + lo (32 KB), only copied out; under sM ...
     uint8_t* sQS = sKB + 32768;                        // scale q 2^g [tok][K index] hi + lo (32 KB), likewise
 
-    const int HV = p.L.HV, HK = p.L.HK, c = blockIdx.x / HV, h = blockIdx.x - c * HV;     // heads fastest: CTAs that run together read neighbouring memory
-    const int hk = h / (HV / HK);
-    const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+    const int HV = p.L.HV, HK = p.L.HK, total = p.L.NC * HV, stride = gridDim.x;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
 
+    // Persistent: one CTA per SM walks the (chunk, v-head) items gridDim.x apart, heads fastest.  The k, q, g rows (and beta,
+    // the L2 statistics) of the NEXT item are requested into registers as soon as the current item has no more use for
+    // its own, half way through the item, so that they travel while the inverse and the second products run.
+    float vk[2][8], vq[2][8], vg[2][8], rk[2], rq[2], beta_r = 0.f;
+    auto load_inputs = [&](int it) {
+        const int c = it / HV, h = it - c * HV, hk = h / (HV / HK);
+        const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+        if (tid < CH) beta_r = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
+            const size_t tk = (size_t)(start + rr) * HK + hk;
+            ldg8(p.k, DT, tk * 128 + k8 * 8, vk[n]);
+            ldg8(p.q, DT, tk * 128 + k8 * 8, vq[n]);
+            ldg8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vg[n]);
+            rk[n] = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
+            rq[n] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
+        }
+    };
     if (warp == 0) umma::tmem_alloc(&sh.tmem, 256);
     if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
-    if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
+    if ((int)blockIdx.x < total) load_inputs(blockIdx.x);
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem = sh.tmem;
 
-    // ---- phase 0: fetch k, q, g (2 (row, chunk) pairs per thread); park the anchor rows of g in shared memory ----
-    float vk[2][8], vq[2][8], vg[2][8], rk[2], rq[2];
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-        const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-        const size_t tk = (size_t)(start + rr) * HK + hk;
-        ldg8(p.k, DT, tk * 128 + k8 * 8, vk[n]);
-        ldg8(p.q, DT, tk * 128 + k8 * 8, vq[n]);
-        ldg8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vg[n]);
-        rk[n] = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
-        rq[n] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
-    }
-    if (tid < 256) {   // the rows of the CTA that is `ahead` places further in launch order are pulled into L2 meanwhile
-        const int nxt = blockIdx.x + ahead, nc = nxt / HV, nh = nxt - nc * HV;
-        const int kind = tid >> 6, r = tid & 63;
-        if (nxt < (int)gridDim.x && r < p.L.chunk_len[nc]) {
-            const size_t tok = (size_t)p.L.chunk_start[nc] + r, tv = tok * HV + nh, tk = tok * HK + nh / (HV / HK);
-            constexpr uint32_t RB = DT == MKDA_F32 ? 512 : 256;
-            if (kind == 0) umma::l2_prefetch(reinterpret_cast<const uint8_t*>(p.k) + tk * RB, RB);
-            if (kind == 1) umma::l2_prefetch(reinterpret_cast<const uint8_t*>(p.q) + tk * RB, RB);
-            if (kind == 2) umma::l2_prefetch(p.g_c + tv * 128, 512);
-            if (kind == 3) umma::l2_prefetch(reinterpret_cast<const uint8_t*>(p.v) + tv * RB, RB);
-        }
-    }
+    for (int item = blockIdx.x; item < total; item += stride) {
+    const int c = item / HV, h = item - c * HV;
+    const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+    // ---- phase 0: this item's k, q, g are in registers; park the anchor rows of g in shared memory ----
+    if (tid < CH) sh.beta[tid] = beta_r;
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
         const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
@@ -204,10 +206,10 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
 #pragma unroll
         for (int e = 0; e < 8; ++e) { vk[n][e] *= rk[n]; vq[n][e] *= rq[n]; }
     }
+    if (tid == 0) umma::bulk_store_wait_read();        // the previous item's tiles have left shared memory
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
-    const uint32_t tmem = sh.tmem;
     // ---- operands ---------------------------------------------------------------------------------------------------
     if (SCALAR) {          // one stacked tile: rows 0..63 = k, rows 64..127 = q (L2 statistics applied, zero past the end)
 #pragma unroll
@@ -302,6 +304,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         for (int e = 0; e < 8; ++e) t8[e] = b * vv[n][e];
         store_split8(sBv, sBv + 16384, 64, r, k8, t8);
     }
+    if (item + stride < total) load_inputs(item + stride);     // k, q, g, beta of the next item start travelling
     if (tid == 0) umma::bulk_store_wait_read();    // the two tiles under sM / sInv / sP have left shared memory
     __syncthreads();
     for (int i = tid; i < CH * MLD / 4; i += 512) reinterpret_cast<float4*>(sInv)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -384,6 +387,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     umma::fence_async_smem();
     __syncthreads();
     if (tid == 0) umma::bulk_store(reinterpret_cast<uint8_t*>(p.u) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES, base + 32768, umma::CHUNK_TILE_BYTES);
+    }   // items
     if (tid == 0) umma::bulk_store_wait_read();
     umma::fence_before_sync();
     __syncthreads();
@@ -991,7 +995,8 @@ template <int DT, bool SCALAR>
 static int launch_intra_fwd_tc_t(const MkdaIntraFwd* p, cudaStream_t stream) {
     auto kern = intra_fwd_tc_kernel<DT, SCALAR>;
     if (int e = ensure_smem((const void*)kern, INTRA_TC_SMEM, "intra_fwd")) return e;
-    kern<<<p->L.NC * p->L.HV, 512, INTRA_TC_SMEM, stream>>>(*p, sm_count());
+    const int items = p->L.NC * p->L.HV;
+    kern<<<items < sm_count() ? items : sm_count(), 512, INTRA_TC_SMEM, stream>>>(*p);
     return check_launch("intra_fwd");
 }
 int launch_intra_fwd_tc(const MkdaIntraFwd* p, cudaStream_t stream) {
