@@ -134,8 +134,8 @@ KERNEL_FLOPS = {                      # per token per v-head
 # fp32 intermediates, HV = 2 HK), every operand counted once.
 KERNEL_BYTES = {
     "mkda_gate_cumsum_fwd": 1024, "mkda_l2norm_rstd": 128, "mkda_intra_fwd": 3592, "mkda_recur_fwd": 3080,
-    "mkda_out_fwd": 3584, "mkda_epilogue_bwd": 2048, "mkda_bwd_dh": 4360,
-    "mkda_bwd_chunk": 6664, "mkda_gate_bwd": 1536, "mkda_qk_grad_finish": 640,
+    "mkda_out_fwd": 3584, "mkda_epilogue_bwd_tiles": 2048, "mkda_epilogue_bwd": 2048, "mkda_bwd_dh": 3848,
+    "mkda_bwd_chunk": 6664, "mkda_gate_bwd": 1536, "mkda_qk_grad_finish": 1536,
 }
 def load_kernel_traffic(path=os.path.join(ROOT, "profiles", "counters_per_kernel_1b_shape.md")):
     """DRAM traffic per token per v-head of every kernel, read from the committed ncu summary (its table has the columns
