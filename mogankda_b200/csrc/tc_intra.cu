@@ -48,6 +48,10 @@ constexpr int MLD = 68;
 // byte offsets of the column-operand tiles (hi; lo follows hi) inside the operand region
 __host__ __device__ constexpr int kc_off(int I) { return I == 0 ? 0 : I == 1 ? 8192 : I == 2 ? 24576 : 49152; }
 __host__ __device__ constexpr int kc_bytes(int I) { return 16 * (I + 1) * 128 * 2; }          // one of hi / lo
+// forward kernel: the same four column tiles stacked by rows into one 160-row tile (hi 40 KB, then lo)
+__host__ __device__ constexpr int kc_row(int I) { return I == 0 ? 0 : I == 1 ? 16 : I == 2 ? 48 : 96; }
+constexpr int KC_ALL_ROWS = 160;
+constexpr int KC_ALL_BYTES = KC_ALL_ROWS * 128 * 2;        // one of hi / lo
 constexpr int KQ_OFF = 81920;                              // [128][128] hi 32 KB, lo 32 KB
 constexpr int OPND_BYTES = KQ_OFF + 65536;                 // 144 KB
 constexpr int INTRA_TC_SMEM = OPND_BYTES + 65536 + 1024;      // operands + (two 32 KB hand-over tiles, later sM / sInv / sP)
@@ -236,7 +240,7 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
                 if (I > I0) lds8(&sGa[I][k8 * 8], ga);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) t8[e] = vk[n][e] * ex2f_(ga[e] - vg[n][e]);
-                store_split8(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1), r, k8, t8);
+                store_split8(base, base + KC_ALL_BYTES, KC_ALL_ROWS, kc_row(I) + r, k8, t8);      // the four column tiles stacked by rows
             }
         }
     }
@@ -245,10 +249,10 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         if (SCALAR) {      // D[m][j]: lanes 0..63 = K K^T rows, lanes 64..127 = Q K^T rows; columns j = K rows of the same tile
             umma::gemm(tmem, umma::opnd_k(sKQ, sKQ + 32768, 128), umma::opnd_k(sKQ, sKQ + 32768, 128), 128, 64, 128, 0u);
         } else {
-#pragma unroll
-            for (int I = 0; I < 4; ++I)
-                umma::gemm(tmem + 32 * I, umma::opnd_k(base + kc_off(I), base + kc_off(I) + kc_bytes(I), 16 * (I + 1)),
-                           umma::opnd_k(sKQ, sKQ + 32768, 128, 32 * I), 128, 32, 128, 0u);
+            // ONE product over the stacked column tiles: D[32 I + t][kc_row(I') + j].  Only the blocks I' = I are meaningful (the
+            // anchors of the two operands match there) and read back; the others are finite and ignored.  An MMA costs
+            // (4 KB of A + 32 N bytes of B) / 128 B per cycle, so N = 160 once is far cheaper than N = 32 four times.
+            umma::gemm(tmem, umma::opnd_k(sKQ, sKQ + 32768, 128), umma::opnd_k(base, base + KC_ALL_BYTES, KC_ALL_ROWS), 128, KC_ALL_ROWS, 128, 0u);
         }
         umma::commit(&sh.bar);
     }
@@ -326,14 +330,25 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
             }
             *reinterpret_cast<float4*>(dst + j4) = make_float4(o4[0], o4[1], o4[2], o4[3]);
         }
-    } else if (q < 2) {                       // lane = column j, cg = row block I: Gamma / Q K^T entries (16 I + r, j)
-        float v[32];
-        umma::tmem_ld32(umma::tmem_addr(tmem, warp, 32 * cg), v);
+    } else {                                  // warp quadrant = row block I (lanes: 16 rows of Gamma, then 16 rows of Q K^T), cg = 16 columns j
+        const int I = q, i = 16 * I + (lane & 15);
+        const bool isq = lane >= 16;
+        float v[16];
 #pragma unroll
-        for (int r = 0; r < 16; ++r) {
-            const int i = 16 * cg + r;
-            sM[i * MLD + row] = row < i ? sh.beta[i] * v[r] : (row == i ? 1.f : 0.f);
-            sP[i * MLD + row] = row <= i ? p.scale * v[16 + r] : 0.f;
+        for (int e = 0; e < 16; ++e) v[e] = 0.f;
+        if (cg <= I) umma::tmem_ld16(umma::tmem_addr(tmem, warp, kc_row(I) + 16 * cg), v);      // warp-uniform condition
+        const float bi = sh.beta[i];
+        float* dst = (isq ? sP : sM) + i * MLD + 16 * cg;
+#pragma unroll
+        for (int j4 = 0; j4 < 16; j4 += 4) {
+            float o4[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = 16 * cg + j4 + e;
+                if (isq) o4[e] = j <= i ? p.scale * v[j4 + e] : 0.f;
+                else o4[e] = j < i ? bi * v[j4 + e] : (j == i ? 1.f : 0.f);
+            }
+            *reinterpret_cast<float4*>(dst + j4) = make_float4(o4[0], o4[1], o4[2], o4[3]);
         }
     }
     __syncthreads();

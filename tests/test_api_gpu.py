@@ -53,6 +53,44 @@ def test_option_matrix(case):
     compare(got, ref)
 
 
+def _all_pairs_cover():
+    """A small set of option combinations in which every pair of values of two different options occurs at least once:
+    greedy cover over seeded random candidates (the reference builds its matrix the same way, tests/kda_common.py:73-94)."""
+    import itertools
+    import random
+    factors = dict(gate=["eda", "kimi", "gdn", "precomputed"], scalar=[False, True], beta=["sigmoid", "precomputed"],
+                   HV=[2, 4], vfirst=[False, True], l2=[True, False], epi=[None, "silu", "sigmoid"], h0=[True, False],
+                   dtype=[torch.bfloat16, torch.float32, torch.float16], varlen=[False, True])
+    names = list(factors)
+    todo = {((a, va), (b, vb)) for a, b in itertools.combinations(names, 2) for va in factors[a] for vb in factors[b]}
+    rng, cases = random.Random(1234), []
+    while todo:
+        best, gain = None, -1
+        for _ in range(200):
+            cand = {n: rng.choice(v) for n, v in factors.items()}
+            g = sum(1 for (a, va), (b, vb) in todo if cand[a] == va and cand[b] == vb)
+            if g > gain:
+                best, gain = cand, g
+        todo = {p for p in todo if not (best[p[0][0]] == p[0][1] and best[p[1][0]] == p[1][1])}
+        cases.append(best)
+    return cases
+
+
+def _cover_id(c):
+    return "-".join(str(v).replace("torch.", "") for v in c.values())
+
+
+@pytest.mark.parametrize("case", _all_pairs_cover(), ids=_cover_id)
+def test_option_pairs_cover(case):
+    case = dict(case)
+    vfirst, varlen = case.pop("vfirst"), case.pop("varlen")
+    kw = dict(cu=VARLEN_CU, T=704) if varlen else dict(B=2, T=200)
+    lv, do, dht, opts, epi = make_inputs(seed=sum(map(ord, _cover_id(case))), **kw, **case)
+    got = run(mk.chunk_delta_rule, lv, do, dht, opts, epi, vfirst=vfirst)
+    ref = run(orc.chunked_delta_rule, lv, do, dht, opts, epi, f64=True, vfirst=vfirst)
+    compare(got, ref)
+
+
 @pytest.mark.parametrize("P", [1, 15, 17, 63, 77, 193])
 def test_prefix_invariance_is_bitwise(P):
     """Outputs of the first P tokens, and (with dO = 0 from row P on) the token gradients of those rows, do not change
