@@ -196,7 +196,9 @@ int mkda_epilogue_bwd(const MkdaEpilogueBwd* p, void* stream);
  * writes one partial row of d weight.  Replaces rmsnorm_gated_bwd (mogan_kda/ops/kimi_delta_rule/epilogue.py:193-205). */
 typedef struct {
     MkdaLayout L;
-    const void* dy; int dy_dtype;                  /* [TT,HV,128] */
+    const void* dy; int dy_dtype;                  /* element (row, c) of [TT*HV, 128] at dy[row * dy_row_stride + c * dy_col_stride] */
+    int dy_row_stride; int dy_col_stride;          /* in elements: (128, 1) for a contiguous gradient; a gradient that autograd
+                                                    * hands over as a broadcast view (strides 0) is read as it is, not copied */
     const float* o_raw;                            /* [TT,HV,128] */
     const void* norm_w; int norm_w_dtype;
     const void* gate; int gate_dtype;

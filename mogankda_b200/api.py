@@ -88,7 +88,8 @@ class _DeltaRuleFunction(torch.autograd.Function):
         scale, vf, cp = cfg["scale"], cfg["state_v_first"], cfg["cp_context"]
         if dy is None:
             dy = torch.zeros(B, T, HV, 128, dtype=torch.float32 if cfg["has_ep"] else q.dtype, device=q.device)
-        dy = dy.contiguous()
+        if not cfg["has_ep"]:
+            dy = dy.contiguous()      # with the epilogue, dy is read through its strides (a broadcast gradient is not copied)
         dw = dgate = d_o = dO_in = None
         if cfg["has_ep"]:      # dO leaves the epilogue backward in the tile form the tensor-core kernels fetch
             dO_in, dgate, dw = ops.epilogue_bwd_tiles(lay, dy, o_raw, ep_w, ep_gate, cfg["ep_act"], cfg["ep_eps"], HV)

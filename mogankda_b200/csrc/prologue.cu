@@ -54,7 +54,7 @@ __device__ __forceinline__ void gate_grad(int mode, float s, float E, float lb, 
 // warp): the association depends only on the row index, never on later rows.
 // ---------------------------------------------------------------------------------------------------------
 template <int XDT>
-__global__ void __launch_bounds__(128) gate_cumsum_fwd_kernel(const MkdaGateFwd p) {
+__global__ void __launch_bounds__(128, 5) gate_cumsum_fwd_kernel(const MkdaGateFwd p) {
     const int HV = p.L.HV, c = blockIdx.x / HV, h = blockIdx.x - c * HV;
     const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(128) gate_cumsum_fwd_kernel(const MkdaGateFwd 
 // CTA (h, g), heads fastest, walks chunks g, g + gridDim.y, ... and keeps the parameter-gradient partials in registers, so the second
 // stage only has gridDim.y rows to add (fixed assignment and order: deterministic).
 template <int XDT>
-__global__ void __launch_bounds__(128) gate_bwd_kernel(const MkdaGateBwd p) {
+__global__ void __launch_bounds__(128, 4) gate_bwd_kernel(const MkdaGateBwd p) {
     const int h = blockIdx.x, HV = p.L.HV;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     __shared__ float4 tot[4][32];
@@ -382,6 +382,8 @@ __device__ __forceinline__ float half_warp_sum(float v) {
     for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
+// DYMODE: how dy is addressed: 0 = dense rows (16-byte loads), 1 = one value per row (column stride 0), 2 = any strides
+template <int DYMODE>
 __global__ void __launch_bounds__(128) epilogue_bwd_tiles_kernel(const MkdaEpilogueBwdTiles p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane & 15, hw = lane >> 4;
     __shared__ float red[8][128];
@@ -403,7 +405,19 @@ __global__ void __launch_bounds__(128) epilogue_bwd_tiles_kernel(const MkdaEpilo
             const size_t off = ((size_t)(start + (valid ? r : len - 1)) * HV + h) * 128 + 8 * sub;
             float o[8], dy[8], z[8], dov[8];
             ld8(p.o_raw, MKDA_F32, off, o);
-            ld8(p.dy, p.dy_dtype, off, dy);
+            {
+                const size_t drow = ((size_t)(start + (valid ? r : len - 1)) * HV + h) * (size_t)p.dy_row_stride;
+                if (DYMODE == 0) {
+                    ld8(p.dy, p.dy_dtype, drow + 8 * sub, dy);
+                } else if (DYMODE == 1) {
+                    const float d = ld1(p.dy, p.dy_dtype, drow);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) dy[e] = d;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) dy[e] = ld1(p.dy, p.dy_dtype, drow + (size_t)(8 * sub + e) * p.dy_col_stride);
+                }
+            }
             ld8(p.gate, p.gate_dtype, off, z);
             float ss = 0.f;
 #pragma unroll
@@ -590,11 +604,15 @@ extern "C" int mkda_epilogue_bwd_noalloc(const MkdaEpilogueBwdNoAlloc* p, void* 
 
 extern "C" int mkda_epilogue_bwd_tiles(const MkdaEpilogueBwdTiles* p, void* stream) {
     if (!p || !p->dy || !p->o_raw || !p->gate || !p->dO_t || !p->dgate) return set_error(MKDA_ERR_ARG, "epilogue_bwd_tiles: null argument");
+    if (p->dy_row_stride < 0 || p->dy_col_stride < 0 || (p->dy_col_stride == 1 && p->dy_row_stride % 8))
+        return set_error(MKDA_ERR_ARG, "epilogue_bwd_tiles: dy strides must be >= 0 (row stride a multiple of 8 when the rows are dense)");
     const int items = p->L.NC * p->L.HV;
     if (items == 0) return MKDA_OK;
     const int grid = items < MKDA_EPILOGUE_MAX_PART_ROWS ? items : MKDA_EPILOGUE_MAX_PART_ROWS;
     if (p->part_w && p->part_rows != grid) return set_error(MKDA_ERR_ARG, "epilogue_bwd_tiles: part_rows must be min(NC * HV, MKDA_EPILOGUE_MAX_PART_ROWS)");
-    epilogue_bwd_tiles_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(*p);
+    if (p->dy_col_stride == 1) epilogue_bwd_tiles_kernel<0><<<grid, 128, 0, (cudaStream_t)stream>>>(*p);
+    else if (p->dy_col_stride == 0) epilogue_bwd_tiles_kernel<1><<<grid, 128, 0, (cudaStream_t)stream>>>(*p);
+    else epilogue_bwd_tiles_kernel<2><<<grid, 128, 0, (cudaStream_t)stream>>>(*p);
     return check_launch("epilogue_bwd_tiles");
 }
 

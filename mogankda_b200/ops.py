@@ -208,17 +208,45 @@ def epilogue_bwd(dy, o_raw, weight, gate, act, eps):
     return d_o, dgate, dw
 
 
+def rows_strides(t):
+    """(row stride, column stride) in elements if ``t`` [..., 128] can be addressed as rows x 128 with one stride per axis
+    (contiguous tensors, and broadcast views such as the gradient autograd produces for ``o.sum()``), else None."""
+    st, sz = t.stride(), t.shape
+    row = None
+    for d in range(t.dim() - 2, -1, -1):          # collapse the leading dims from the inside out
+        if sz[d] == 1:
+            continue
+        if row is None:
+            row, span = st[d], st[d] * sz[d]
+        elif st[d] == span:
+            span = st[d] * sz[d]
+        else:
+            return None
+    row = 0 if row is None else row
+    col = st[-1]
+    if row < 0 or col < 0 or (col == 1 and row % 8) or t.storage_offset() * t.element_size() % 16:
+        return None
+    return row, col
+
+
 def epilogue_bwd_tiles(lay, dy, o_raw, weight, gate, act, eps, HV):
-    """Gated RMSNorm backward addressed through the chunk tables.  -> (dO_t row tiles [NC,HV], dgate [like gate], dweight
-    fp32 [128] or None)."""
+    """Gated RMSNorm backward addressed through the chunk tables.  ``dy`` is read through its strides (see
+    ``rows_strides``); anything else is made contiguous first.  -> (dO_t row tiles [NC,HV], dgate [like gate], dweight fp32
+    [128] or None)."""
     dev = o_raw.device
+    strides = rows_strides(dy)
+    if strides is None:
+        dy, strides = dy.contiguous(), (128, 1)
     dO_t = torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=dev)
     dgate = (torch.empty_like if lay.covers_all else torch.zeros_like)(gate)
     nblk = min(lay.NC * HV, _lib.MKDA_EPILOGUE_MAX_PART_ROWS)
     part = torch.empty(nblk, 128, dtype=torch.float32, device=dev) if weight is not None else None
     p = STRUCTS["MkdaEpilogueBwdTiles"]()
     p.L = _layout_struct(lay, 1, HV)
-    p.dy, p.dy_dtype, p.o_raw = _ptr(dy), _dt(dy), _ptr(o_raw, torch.float32)
+    if not dy.is_cuda:
+        raise RuntimeError("mogankda_b200 kernels need CUDA tensors (there is no CPU fallback)")
+    p.dy, p.dy_dtype, p.o_raw = dy.data_ptr(), _dt(dy), _ptr(o_raw, torch.float32)
+    p.dy_row_stride, p.dy_col_stride = strides
     if weight is not None:
         p.norm_w, p.norm_w_dtype = _ptr(weight), _dt(weight)
     p.gate, p.gate_dtype, p.act, p.eps = _ptr(gate), _dt(gate), ACTS[act], float(eps)

@@ -175,6 +175,15 @@ def test_epilogue_backward(world):
             assert float(dense[c, :, n:].abs().sum()) == 0.0
         _err("dw (tiles)", dw2, rw, 1e-5)
         _err("dgate (tiles)", dgate2.reshape(rz.shape), rz, 1e-5 if dgate2.dtype == torch.float32 else 2.0 ** -8)
+        # dy is read through its strides: a broadcast gradient (what autograd hands over for o.sum()) and a column-strided one
+        # give bit for bit what their contiguous copies give
+        wide = torch.randn(world["TT"], 4, 256, device="cuda")
+        for view in (torch.full((), 0.75, device="cuda").expand(world["TT"], 4, 128), wide[..., ::2],
+                     torch.randn(world["TT"], 4, 1, device="cuda").expand(world["TT"], 4, 128)):
+            assert not view.is_contiguous() and ops.rows_strides(view) is not None
+            a = ops.epilogue_bwd_tiles(lay, view, f32(fw["o"]), lv["ep_w"], lv["ep_gate"], act, 1e-6, 4)
+            b = ops.epilogue_bwd_tiles(lay, view.contiguous(), f32(fw["o"]), lv["ep_w"], lv["ep_gate"], act, 1e-6, 4)
+            assert all(torch.equal(x, y) for x, y in zip(a, b))
 
 
 @pytest.mark.parametrize("mode", [0, 1, 2, 3])
