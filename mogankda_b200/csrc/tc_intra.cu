@@ -41,8 +41,9 @@ struct IntraShared {
     uint64_t bar;
     uint32_t tmem;
     float beta[CH];
-    __align__(16) float T[32][34];
+    __align__(16) float T[32][36];
 };
+constexpr int TLD = 36;
 
 constexpr int MLD = 68;
 // byte offsets of the column-operand tiles (hi; lo follows hi) inside the operand region
@@ -56,6 +57,31 @@ constexpr int KQ_OFF = 81920;                              // [128][128] hi 32 K
 constexpr int OPND_BYTES = KQ_OFF + 65536;                 // 144 KB
 constexpr int INTRA_TC_SMEM = OPND_BYTES + 65536 + 1024;      // operands + (two 32 KB hand-over tiles, later sM / sInv / sP)
 static_assert(3 * CH * MLD * 4 <= 65536, "sM / sInv / sP must fit under the hand-over tiles");
+
+// out[2][4] = A[2 rows][KD] * B[KD][4 columns] with fp32 FMAs in ascending k (the order every entry of the inverse has always
+// been summed in); A rows are `lda` floats apart, B rows `ldb`; all pointers 16-byte aligned.  A 2 x 4 register tile needs
+// 6 shared loads per 32 FMAs: the merges below are bound by shared-memory load issue, not by arithmetic.
+template <int KD>
+__device__ __forceinline__ void mm_tile_2x4(const float* __restrict__ A, int lda, const float* __restrict__ B, int ldb, float (&out)[2][4]) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) out[i][j] = 0.f;
+#pragma unroll
+    for (int k4 = 0; k4 < KD; k4 += 4) {
+        const float4 a0 = *reinterpret_cast<const float4*>(A + k4), a1 = *reinterpret_cast<const float4*>(A + lda + k4);
+        const float am[2][4] = {{a0.x, a0.y, a0.z, a0.w}, {a1.x, a1.y, a1.z, a1.w}};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float4 b4 = *reinterpret_cast<const float4*>(B + (k4 + k) * ldb);
+            const float bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) out[i][j] = fmaf(am[i][k], bv[j], out[i][j]);
+        }
+    }
+}
 
 // Inverse of the unit lower-triangular 64 x 64 matrix sM into sInv (fp32, fixed summation order) by recursive halving:
 // the four 16 x 16 diagonal blocks by forward substitution, then the off-diagonal block of each 32 x 32 half and finally
@@ -77,62 +103,41 @@ __device__ __forceinline__ void invert_unit_lower(const float* __restrict__ sM, 
         for (int r = 0; r < 16; ++r) sInv[(o + r) * MLD + o + lane] = x[r];
     }
     __syncthreads();
-    {   // 16 x 16 blocks (1, 0) and (3, 2): thread = (half, r, c)
-        const int hb = tid >> 8, r = (tid >> 4) & 15, c = tid & 15;
+    {   // 16 x 16 blocks (1, 0) and (3, 2): 32 threads per block, thread = (row pair, column quad)
+        const int hb = tid >> 5, rp = (tid >> 2) & 7, cq = tid & 3;
         const int ro = 32 * hb + 16, co = 32 * hb;            // block origin; A^-1 at (co, co), B^-1 at (ro, ro)
-        float t = 0.f;
+        float o[2][4];
+        if (tid < 64) {
+            mm_tile_2x4<16>(sM + (ro + 2 * rp) * MLD + co, MLD, sInv + co * MLD + co + 4 * cq, MLD, o);
 #pragma unroll
-        for (int e4 = 0; e4 < 16; e4 += 4) {
-            const float4 m4 = *reinterpret_cast<const float4*>(sM + (ro + r) * MLD + co + e4);
-            t = fmaf(m4.x, sInv[(co + e4) * MLD + co + c], t);
-            t = fmaf(m4.y, sInv[(co + e4 + 1) * MLD + co + c], t);
-            t = fmaf(m4.z, sInv[(co + e4 + 2) * MLD + co + c], t);
-            t = fmaf(m4.w, sInv[(co + e4 + 3) * MLD + co + c], t);
+            for (int i = 0; i < 2; ++i)
+                *reinterpret_cast<float4*>(&sh.T[16 * hb + 2 * rp + i][4 * cq]) = make_float4(o[i][0], o[i][1], o[i][2], o[i][3]);
         }
-        sh.T[16 * hb + r][c] = t;
         __syncthreads();
-        float x = 0.f;
+        if (tid < 64) {
+            mm_tile_2x4<16>(sInv + (ro + 2 * rp) * MLD + ro, MLD, &sh.T[16 * hb][4 * cq], TLD, o);
 #pragma unroll
-        for (int e4 = 0; e4 < 16; e4 += 4) {
-            const float4 m4 = *reinterpret_cast<const float4*>(sInv + (ro + r) * MLD + ro + e4);
-            x = fmaf(m4.x, sh.T[16 * hb + e4][c], x);
-            x = fmaf(m4.y, sh.T[16 * hb + e4 + 1][c], x);
-            x = fmaf(m4.z, sh.T[16 * hb + e4 + 2][c], x);
-            x = fmaf(m4.w, sh.T[16 * hb + e4 + 3][c], x);
+            for (int i = 0; i < 2; ++i)
+                *reinterpret_cast<float4*>(sInv + (ro + 2 * rp + i) * MLD + co + 4 * cq) = make_float4(-o[i][0], -o[i][1], -o[i][2], -o[i][3]);
         }
-        sInv[(ro + r) * MLD + co + c] = -x;
     }
     __syncthreads();
-    {   // 32 x 32 block (rows 32.., columns 0..31): thread = (r, two columns); 128- and 64-bit shared loads keep the
-        // load count per product term low (this step is bound by shared-memory load issue)
-        const int r = tid >> 4, c = (tid & 15) * 2;
-        float t0 = 0.f, t1 = 0.f;
+    {   // 32 x 32 block (rows 32.., columns 0..31): 128 threads, thread = (row pair, column quad)
+        const int rp = tid >> 3, cq = tid & 7;
+        float o[2][4];
+        if (tid < 128) {
+            mm_tile_2x4<32>(sM + (32 + 2 * rp) * MLD, MLD, sInv + 4 * cq, MLD, o);
 #pragma unroll
-        for (int e4 = 0; e4 < 32; e4 += 4) {
-            const float4 m4 = *reinterpret_cast<const float4*>(sM + (32 + r) * MLD + e4);
-            const float m[4] = {m4.x, m4.y, m4.z, m4.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float2 a = *reinterpret_cast<const float2*>(sInv + (e4 + k) * MLD + c);
-                t0 = fmaf(m[k], a.x, t0);
-                t1 = fmaf(m[k], a.y, t1);
-            }
+            for (int i = 0; i < 2; ++i)
+                *reinterpret_cast<float4*>(&sh.T[2 * rp + i][4 * cq]) = make_float4(o[i][0], o[i][1], o[i][2], o[i][3]);
         }
-        *reinterpret_cast<float2*>(&sh.T[r][c]) = make_float2(t0, t1);
         __syncthreads();
-        float x0 = 0.f, x1 = 0.f;
+        if (tid < 128) {
+            mm_tile_2x4<32>(sInv + (32 + 2 * rp) * MLD + 32, MLD, &sh.T[0][4 * cq], TLD, o);
 #pragma unroll
-        for (int e4 = 0; e4 < 32; e4 += 4) {
-            const float4 m4 = *reinterpret_cast<const float4*>(sInv + (32 + r) * MLD + 32 + e4);
-            const float m[4] = {m4.x, m4.y, m4.z, m4.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float2 a = *reinterpret_cast<const float2*>(&sh.T[e4 + k][c]);
-                x0 = fmaf(m[k], a.x, x0);
-                x1 = fmaf(m[k], a.y, x1);
-            }
+            for (int i = 0; i < 2; ++i)
+                *reinterpret_cast<float4*>(sInv + (32 + 2 * rp + i) * MLD + 4 * cq) = make_float4(-o[i][0], -o[i][1], -o[i][2], -o[i][3]);
         }
-        *reinterpret_cast<float2*>(sInv + (32 + r) * MLD + c) = make_float2(-x0, -x1);
     }
     __syncthreads();
 }
