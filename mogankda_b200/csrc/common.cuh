@@ -62,6 +62,51 @@ __device__ __forceinline__ void ld8(const void* base, int dtype, size_t idx, flo
     }
 }
 
+// The same eight elements as raw bytes (one 16-byte piece, two for fp32), widened later by unpack8.  A conversion next to the
+// load makes the thread wait for the data there and then; a load whose bytes are only parked in registers stays in flight
+// until its first real use, which may be a whole phase (or the top of the next item) later.
+struct Raw8 { uint4 a, b; };
+template <int DT>
+__device__ __forceinline__ void ldraw8(const void* base, size_t idx, Raw8& r) {
+    if (DT == MKDA_F32) {
+        r.a = *reinterpret_cast<const uint4*>(static_cast<const float*>(base) + idx);
+        r.b = *reinterpret_cast<const uint4*>(static_cast<const float*>(base) + idx + 4);
+    } else {
+        r.a = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + idx);
+    }
+}
+template <int DT>
+__device__ __forceinline__ void unpack8(const Raw8& r, float (&v)[8]) {
+    if (DT == MKDA_F32) {
+        v[0] = __uint_as_float(r.a.x); v[1] = __uint_as_float(r.a.y); v[2] = __uint_as_float(r.a.z); v[3] = __uint_as_float(r.a.w);
+        v[4] = __uint_as_float(r.b.x); v[5] = __uint_as_float(r.b.y); v[6] = __uint_as_float(r.b.z); v[7] = __uint_as_float(r.b.w);
+        return;
+    }
+    const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        if (DT == MKDA_BF16) {
+            v[2 * e] = __uint_as_float(w[e] << 16);
+            v[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+        } else {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+            v[2 * e] = f.x; v[2 * e + 1] = f.y;
+        }
+    }
+}
+// one element, raw (zero-extended for the 16-bit types) and widened later
+template <int DT>
+__device__ __forceinline__ uint32_t ldraw1(const void* base, size_t idx) {
+    if (DT == MKDA_F32) return static_cast<const uint32_t*>(base)[idx];
+    return static_cast<const uint16_t*>(base)[idx];
+}
+template <int DT>
+__device__ __forceinline__ float unpack1(uint32_t w) {
+    if (DT == MKDA_F32) return __uint_as_float(w);
+    if (DT == MKDA_BF16) return __uint_as_float(w << 16);
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(w)));
+}
+
 __device__ __forceinline__ float ld1(const void* base, int dtype, size_t idx) {
     if (dtype == MKDA_F32) return static_cast<const float*>(base)[idx];
     if (dtype == MKDA_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[idx]);

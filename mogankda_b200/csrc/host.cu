@@ -1,4 +1,5 @@
 // Error reporting and ABI self-description.
+#include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -34,6 +35,38 @@ int sm_count() {
         cached[dev] = n;
     }
     return cached[dev];
+}
+
+int make_rows_map(CUtensorMap* out, const void* base, int elem_bytes, unsigned long long rows, unsigned long long row_elems, const char* what) {
+    typedef CUresult (*Encode)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                               const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static Encode encode = nullptr;                    // resolved through the runtime: the library does not link against the driver
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+            (void)cudaGetLastError();
+            snprintf(g_err, sizeof(g_err), "%s: the driver does not provide cuTensorMapEncodeTiled", what);
+            return MKDA_ERR_LAUNCH;
+        }
+        encode = reinterpret_cast<Encode>(fn);
+    }
+    const unsigned long long pitch = row_elems * (unsigned long long)elem_bytes;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch & 15) || row_elems < 128 || rows == 0) {
+        snprintf(g_err, sizeof(g_err), "%s: tensor not 16-byte aligned for tiled copies", what);
+        return MKDA_ERR_ARG;
+    }
+    const cuuint64_t gdim[2] = {row_elems, rows};
+    const cuuint64_t gstride[1] = {pitch};
+    const cuuint32_t box[2] = {128, 64}, estr[2] = {1, 1};
+    const CUresult r = encode(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), gdim,
+                              gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_err, sizeof(g_err), "%s: cuTensorMapEncodeTiled failed (%d)", what, (int)r);
+        return MKDA_ERR_LAUNCH;
+    }
+    return MKDA_OK;
 }
 
 int ensure_smem(const void* func, int bytes, const char* what) {

@@ -1,5 +1,6 @@
 // Host-side helpers shared by the launchers: error text behind mkda_last_error() and launch checking.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include "../../include/mkda.h"
@@ -10,6 +11,11 @@ int check_launch(const char* what);
 // Raises the dynamic shared memory limit of `func` (the attribute is set once per function and device; later calls
 // return at once); returns 0 or an error code.
 int ensure_smem(const void* func, int bytes, const char* what);
+// Tensor map over a row-major [rows][row_elems] tensor of 2- or 4-byte elements whose boxes are 64 rows x 128 elements, not
+// swizzled: one tiled TMA copy then brings 64 strided 128-element rows (token rows of one head) into shared memory as a dense
+// [64][128] block.  Rows past the end of the tensor read as zeros.  Returns 0, or an error code when the tensor cannot be
+// described (base not 16-byte aligned, row pitch not a multiple of 16 bytes, or the driver lacks the encoder).
+int make_rows_map(CUtensorMap* out, const void* base, int elem_bytes, unsigned long long rows, unsigned long long row_elems, const char* what);
 // Number of SMs of the current device (cached per device).
 int sm_count();
 int launch_out_fwd_tc(const MkdaOutFwd* p, cudaStream_t stream);

@@ -38,7 +38,7 @@ __device__ __forceinline__ void publish() {
 }
 
 struct IntraShared {
-    uint64_t bar;
+    uint64_t bar, ldin;
     uint32_t tmem;
     float beta[CH];
     __align__(16) float T[32][36];
@@ -55,8 +55,18 @@ constexpr int KC_ALL_ROWS = 160;
 constexpr int KC_ALL_BYTES = KC_ALL_ROWS * 128 * 2;        // one of hi / lo
 constexpr int KQ_OFF = 81920;                              // [128][128] hi 32 KB, lo 32 KB
 constexpr int OPND_BYTES = KQ_OFF + 65536;                 // 144 KB
-constexpr int INTRA_TC_SMEM = OPND_BYTES + 65536 + 1024;      // operands + (two 32 KB hand-over tiles, later sM / sInv / sP)
-static_assert(3 * CH * MLD * 4 <= 65536, "sM / sInv / sP must fit under the hand-over tiles");
+// The 16-bit k, q and the g rows of the NEXT item arrive by tiled copy (one 64 x 128 box per tensor) while the current item's
+// inverse and second products run: k and g rows in the upper 48 KB of the [Kr; Qr] tile, dead once the first products are
+// done, q rows behind sP.  They are read back into registers before the next item's operands are staged over them.  (Loads
+// into registers at that point are accepted only as fast as their data returns and occupied every thread for a fifth of
+// the item; one small bulk copy per row is slower still.)
+struct IntraMaps { CUtensorMap k, q, g; };
+constexpr int RAW_K = 98304;                               // [64][128] 16-bit, 16 KB
+constexpr int RAW_G = RAW_K + 16384;                       // [64][128] fp32, 32 KB
+constexpr int RAW_Q = OPND_BYTES + 53248;                  // [64][128] 16-bit, 16 KB
+constexpr int INTRA_TC_SMEM = RAW_Q + 16384 + 1024;        // operands + (two 32 KB hand-over tiles, later sM / sInv / sP) + q rows
+static_assert(RAW_G + 32768 <= OPND_BYTES, "k / g rows must fit in the dead part of the operand region");
+static_assert(3 * CH * MLD * 4 <= 53248, "sM / sInv / sP must end below the q rows");
 
 // out[2][4] = A[2 rows][KD] * B[KD][4 columns] with fp32 FMAs in ascending k (the order every entry of the inverse has always
 // been summed in); A rows are `lda` floats apart, B rows `ldb`; all pointers 16-byte aligned.  A 2 x 4 register tile needs
@@ -146,8 +156,8 @@ __device__ __forceinline__ void invert_unit_lower(const float* __restrict__ sM, 
 // over channels, Gamma_ij = (k_i . k_j) 2^(g_i - g_j), so the products are plain K K^T / Q K^T (one product over a stacked
 // [K; Q] tile) and the decay is applied to the accumulators, element by element and for i >= j only: nothing is anchored,
 // no exponent is ever positive, and any g <= 0 is in range (the per-channel path needs g >= -5 per token).
-template <int DT, bool SCALAR>
-__global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd p) {
+template <int DT, bool SCALAR, bool TMA>
+__global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd p, const __grid_constant__ IntraMaps maps) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ IntraShared sh;
     __shared__ __align__(16) float sGa[5][DK];         // cumsum rows of the four block anchors, [4] = last valid row
@@ -171,35 +181,57 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     // Persistent: one CTA per SM walks the (chunk, v-head) items gridDim.x apart, heads fastest.  The k, q, g rows (and beta,
     // the L2 statistics) of the NEXT item are requested into registers as soon as the current item has no more use for
     // its own, half way through the item, so that they travel while the inverse and the second products run.
+    // k and q stay raw (unconverted) in registers until the item starts, so that nothing waits for them here.
+    constexpr bool BULK = TMA && DT != MKDA_F32;       // fp32 rows would not fit: they travel through registers
     float vk[2][8], vq[2][8], vg[2][8], rk[2], rq[2], beta_r = 0.f;
+    Raw8 wk[2], wq[2];
+    uint32_t nin = 0;                                  // phase counter of the input-row barrier
     auto load_inputs = [&](int it) {
         const int c = it / HV, h = it - c * HV, hk = h / (HV / HK);
         const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
         if (tid < CH) beta_r = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
+        if (BULK && tid == 64) {                       // rows past the chunk's end belong to the next sequence (or read as zeros) and are never used
+            umma::mbar_expect_tx(&sh.ldin, 16384u + 16384u + 32768u);
+            umma::tma_load_rows(base + RAW_K, &maps.k, hk * 128, start, &sh.ldin);
+            umma::tma_load_rows(base + RAW_Q, &maps.q, hk * 128, start, &sh.ldin);
+            umma::tma_load_rows(base + RAW_G, &maps.g, h * 128, start, &sh.ldin);
+        }
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
             const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
             const size_t tk = (size_t)(start + rr) * HK + hk;
-            ldg8(p.k, DT, tk * 128 + k8 * 8, vk[n]);
-            ldg8(p.q, DT, tk * 128 + k8 * 8, vq[n]);
-            ldg8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vg[n]);
+            if (!BULK) {
+                ldraw8<DT>(p.k, tk * 128 + k8 * 8, wk[n]);
+                ldraw8<DT>(p.q, tk * 128 + k8 * 8, wq[n]);
+                ldg8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vg[n]);
+            }
             rk[n] = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
             rq[n] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
         }
     };
     if (warp == 0) umma::tmem_alloc(&sh.tmem, 256);
-    if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::fence_barrier_init(); }
-    if ((int)blockIdx.x < total) load_inputs(blockIdx.x);
+    if (tid == 0) { umma::mbar_init(&sh.bar, 1); umma::mbar_init(&sh.ldin, 1); umma::fence_barrier_init(); }
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem = sh.tmem;
+    if ((int)blockIdx.x < total) load_inputs(blockIdx.x);
 
     for (int item = blockIdx.x; item < total; item += stride) {
     const int c = item / HV, h = item - c * HV;
     const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
-    // ---- phase 0: this item's k, q, g are in registers; park the anchor rows of g in shared memory ----
+    // ---- phase 0: this item's k, q, g rows into registers; park the anchor rows of g in shared memory ----
     if (tid < CH) sh.beta[tid] = beta_r;
+    if (BULK) {
+        umma::mbar_wait(&sh.ldin, nin & 1); ++nin;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
+            wk[n].a = *reinterpret_cast<const uint4*>(base + RAW_K + rr * 256 + k8 * 16);
+            wq[n].a = *reinterpret_cast<const uint4*>(base + RAW_Q + rr * 256 + k8 * 16);
+            lds8(reinterpret_cast<const float*>(base + RAW_G + rr * 512 + k8 * 32), vg[n]);
+        }
+    }
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
         const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
@@ -212,6 +244,8 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
             *reinterpret_cast<float4*>(&sGa[4][k8 * 8 + 4]) = make_float4(vg[n][4], vg[n][5], vg[n][6], vg[n][7]);
         }
         if (SCALAR && k8 == 0) sGs[r] = vg[n][0];
+        unpack8<DT>(wk[n], vk[n]);
+        unpack8<DT>(wq[n], vq[n]);
 #pragma unroll
         for (int e = 0; e < 8; ++e) { vk[n][e] *= rk[n]; vq[n][e] *= rq[n]; }
     }
@@ -262,11 +296,11 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
         umma::commit(&sh.bar);
     }
     // v for phase 3 is fetched while the products run
-    float vv[2][8];
+    Raw8 wv[2];
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
         const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-        ldg8(p.v, DT, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vv[n]);
+        ldraw8<DT>(p.v, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, wv[n]);
     }
     // ... and so are the hand-over tiles, built and sent off in the shadow of the products
     // The state kernels' scaled operands, as ready-made tiles: kbar = k 2^(gL - g) (gL = last valid row) and scale q 2^g,
@@ -309,13 +343,14 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
 #pragma unroll
         for (int e = 0; e < 8; ++e) t8[e] = b * vk[n][e] * ex2f_(vg[n][e]);
         store_split8(sBk, sBk + 16384, 64, r, k8, t8);
+        unpack8<DT>(wv[n], t8);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) t8[e] = b * vv[n][e];
+        for (int e = 0; e < 8; ++e) t8[e] *= b;
         store_split8(sBv, sBv + 16384, 64, r, k8, t8);
     }
-    if (item + stride < total) load_inputs(item + stride);     // k, q, g, beta of the next item start travelling
-    if (tid == 0) umma::bulk_store_wait_read();    // the two tiles under sM / sInv / sP have left shared memory
+    if (tid == 0) umma::bulk_store_wait_read();    // the two tiles under sM / sInv / sP (and the q rows) have left shared memory
     __syncthreads();
+    if (item + stride < total) load_inputs(item + stride);     // k, q, g, beta of the next item start travelling
     for (int i = tid; i < CH * MLD / 4; i += 512) reinterpret_cast<float4*>(sInv)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (SCALAR) {                             // lane = row (K rows, then Q rows), cg = 16 columns j: decay applied here, for i >= j only
         float v[16];
@@ -591,6 +626,8 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
             umma::commit(&sh.barD);
         }
         float vk[2][8], vg[2][8], vq[2][8], vv[16];
+        Raw8 wk[2], wq[2];                                 // k, q and v stay raw until their first use: no thread waits for them where they are requested
+        uint32_t wv[16];
         {
             if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
             if (tid >= CH && tid < 2 * CH) {
@@ -603,13 +640,13 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
                 const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-                ldg8(p.k, DT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, vk[n]);
+                ldraw8<DT>(p.k, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, wk[n]);
                 ldg8(p.g_c, MKDA_F32, ((size_t)(start + rr) * HV + h) * 128 + k8 * 8, vg[n]);
             }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const int t = cg * 16 + j, tt = t < len ? t : len - 1;
-                vv[j] = ld1(p.v, DT, ((size_t)(start + tt) * HV + h) * 128 + row);
+                wv[j] = ldraw1<DT>(p.v, ((size_t)(start + tt) * HV + h) * 128 + row);
             }
             // dgl[c] = sum_v S[c][v] dS'[c][v] from the two tiles: chunk (v row, 8 channels) per thread, four rows each
             umma::mbar_wait(&sh.ld0, n0 & 1);
@@ -642,8 +679,7 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
                 *reinterpret_cast<float4*>(&sPart[warp][lane * 8 + 4]) = make_float4(acc[4], acc[5], acc[6], acc[7]);
             }
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-                if (cg * 16 + j >= len) vv[j] = 0.f;
+            for (int j = 0; j < 16; ++j) vv[j] = cg * 16 + j < len ? unpack1<DT>(wv[j]) : 0.f;
         }
         ++n0; ++n2;
         umma::mbar_wait(&sh.barC, nC & 1); ++nC;           // dS' Vd^T done
@@ -666,6 +702,7 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
                 const int i = tid + n * 512, r = i >> 4, k8 = i & 15;
                 const float rk = sRk[r];
                 float t8[8];
+                unpack8<DT>(wk[n], vk[n]);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) { vk[n][e] *= rk; t8[e] = vk[n][e] * ex2f_(vg[n][e]); }
                 store_split8(sK, sK + 16384, 64, r, k8, t8);
@@ -690,7 +727,7 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
                 const int i = tid + n * 512, r = i >> 4, k8 = i & 15, rr = r < len ? r : len - 1;
-                ldg8(p.q, DT, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, vq[n]);
+                ldraw8<DT>(p.q, ((size_t)(start + rr) * HK + hk) * 128 + k8 * 8, wq[n]);
             }
             umma::mbar_wait(&sh.barA, nA & 1);
             umma::fence_after_sync();
@@ -743,6 +780,7 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
                 const float rq = sRq[(tid + n * 512) >> 4];
+                unpack8<DT>(wq[n], vq[n]);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) vq[n][e] *= rq;
             }
@@ -1011,13 +1049,24 @@ int tc_intra_status_clear() {
     return cudaMemcpyToSymbol(umma::g_timeout_flag, &z, sizeof(z)) == cudaSuccess ? 0 : -1;
 }
 
-template <int DT, bool SCALAR>
-static int launch_intra_fwd_tc_t(const MkdaIntraFwd* p, cudaStream_t stream) {
-    auto kern = intra_fwd_tc_kernel<DT, SCALAR>;
+template <int DT, bool SCALAR, bool TMA>
+static int launch_intra_fwd_tc_tt(const MkdaIntraFwd* p, const IntraMaps& maps, cudaStream_t stream) {
+    auto kern = intra_fwd_tc_kernel<DT, SCALAR, TMA>;
     if (int e = ensure_smem((const void*)kern, INTRA_TC_SMEM, "intra_fwd")) return e;
     const int items = p->L.NC * p->L.HV;
-    kern<<<items < sm_count() ? items : sm_count(), 512, INTRA_TC_SMEM, stream>>>(*p);
+    kern<<<items < sm_count() ? items : sm_count(), 512, INTRA_TC_SMEM, stream>>>(*p, maps);
     return check_launch("intra_fwd");
+}
+template <int DT, bool SCALAR>
+static int launch_intra_fwd_tc_t(const MkdaIntraFwd* p, cudaStream_t stream) {
+    IntraMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    // 16-bit rows travel by tiled copy when the tensors can be described (16-byte aligned); otherwise through registers
+    if (DT != MKDA_F32 && make_rows_map(&maps.k, p->k, 2, (unsigned long long)p->L.TT, (unsigned long long)p->L.HK * 128, "intra_fwd") == MKDA_OK &&
+        make_rows_map(&maps.q, p->q, 2, (unsigned long long)p->L.TT, (unsigned long long)p->L.HK * 128, "intra_fwd") == MKDA_OK &&
+        make_rows_map(&maps.g, p->g_c, 4, (unsigned long long)p->L.TT, (unsigned long long)p->L.HV * 128, "intra_fwd") == MKDA_OK)
+        return launch_intra_fwd_tc_tt<DT, SCALAR, true>(p, maps, stream);
+    return launch_intra_fwd_tc_tt<DT, SCALAR, false>(p, maps, stream);
 }
 int launch_intra_fwd_tc(const MkdaIntraFwd* p, cudaStream_t stream) {
     switch (p->qkv_dtype * 2 + (p->scalar_gate ? 1 : 0)) {

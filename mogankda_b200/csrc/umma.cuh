@@ -205,6 +205,13 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  :: "r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+// Tiled copy of one 64 x 128 box of a row tensor (host.h: make_rows_map) starting at element column x (x times the element
+// size a multiple of 16 bytes) and row y; lands as a dense [64][128] block at the 128-byte aligned `smem_dst`, completion
+// counted in bytes (the whole box, rows past the tensor's end included) on `bar`.
+__device__ __forceinline__ void tma_load_rows(void* smem_dst, const void* tmap, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 :: "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
 // shared -> global; the source must stay untouched until bulk_store_wait_read() returns in the issuing thread
 __device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" :: "l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
