@@ -186,9 +186,15 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     float vk[2][8], vq[2][8], vg[2][8], rk[2], rq[2], beta_r = 0.f;
     Raw8 wk[2], wq[2];
     uint32_t nin = 0;                                  // phase counter of the input-row barrier
+    // the chunk table entries are read one item ahead of load_inputs: every address of an item depends on them
+    int cur_start = 0, cur_len = 1, next_start = 0, next_len = 1;
+    auto table_ahead = [&](int it) {
+        if (it < total) { next_start = p.L.chunk_start[it / HV]; next_len = p.L.chunk_len[it / HV]; }
+    };
     auto load_inputs = [&](int it) {
         const int c = it / HV, h = it - c * HV, hk = h / (HV / HK);
-        const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+        const int start = next_start, len = next_len;
+        cur_start = start; cur_len = len;
         if (tid < CH) beta_r = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
         if (BULK && tid == 64) {                       // rows past the chunk's end belong to the next sequence (or read as zeros) and are never used
             umma::mbar_expect_tx(&sh.ldin, 16384u + 16384u + 32768u);
@@ -215,11 +221,13 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem = sh.tmem;
+    table_ahead(blockIdx.x);
     if ((int)blockIdx.x < total) load_inputs(blockIdx.x);
 
     for (int item = blockIdx.x; item < total; item += stride) {
     const int c = item / HV, h = item - c * HV;
-    const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+    const int start = cur_start, len = cur_len;
+    table_ahead(item + stride);
     // ---- phase 0: this item's k, q, g rows into registers; park the anchor rows of g in shared memory ----
     if (tid < CH) sh.beta[tid] = beta_r;
     if (BULK) {
@@ -483,11 +491,11 @@ __global__ void __launch_bounds__(512, 1) intra_fwd_tc_kernel(const MkdaIntraFwd
 //   then the row / column products of the intra-chunk part, whose operands are rebuilt over the dead tiles while P4 and
 //   P5 run.
 // dX, dAqk, dL and dbeta_w never leave the SM.  The three outputs per token and channel leave as fp32 [64 tokens][128]
-// tiles per (chunk, v-head), staged in shared memory and written by one bulk copy each.
+// tiles per (chunk, v-head), written from registers (128 consecutive bytes per warp and token).
 //
 // Shared memory (U = 32 KB): S [0, 2U) | dS' [2U, 4U) -> k~ -> X^T [2U, 3U), dVd^T [3U, 4U) | dO -> dX^T [4U, 5U) |
 // A -> beta dLs [5U, 5U + 16K) | Vd^T -> dv rows -> (D2 beta | Y) -> [Wq; dLs] [5U + 16K, 6U + 16K); the intra-chunk operands (column
-// tiles, [Kr; Qr]) go to [0, 4.5U), the output tiles to [0, 3U).
+// tiles, [Kr; Qr]) go to [0, 4.5U).
 // TMEM columns: X -> Y 0, dW -> Z 64, D1 128, Dq 192, D2 256, Dk 320, Db 384; later R_I 32 I, C_I {304, 448, 256, 128}.
 // ---------------------------------------------------------------------------------------------------------
 constexpr int BU = 32768;
@@ -534,12 +542,12 @@ __device__ __forceinline__ void stage_intra_operands(uint8_t* base, const float 
     }
 }
 
-// CTAs are persistent: one per SM walks the items gridDim.x apart.  While the epilogue of an item runs, the next item's
-// dS', Vd^T and A tiles are already travelling (their regions are free by then); S and dO follow as soon as the output
-// tiles have left shared memory.  One elected lane of warp 0 issues every tensor-core product and the tile loads; lane 0
-// of warp 15 sends the output tiles off and requests S / dO of the next item.  (A 17th, issue-only warp was tried: five
-// warps on one SM sub-partition cap the kernel at 96 registers per thread and the spills cost far more than the overlap
-// returns.)
+// CTAs are persistent: one per SM walks the items gridDim.x apart.  The epilogue of an item touches no tile in shared
+// memory (it reads accumulators and global memory and writes global memory), so all five tiles of the next item travel
+// while it runs.  (Output tiles staged in shared memory and sent by bulk copy kept the S and dO regions busy until the very
+// end of the item, and the next item then began by waiting for 96 KB.)  One elected lane of warp 0 issues every
+// tensor-core product and the tile loads.  (A 17th, issue-only warp was tried: five warps on one SM sub-partition cap the
+// kernel at 96 registers per thread and the spills cost far more than the overlap returns.)
 constexpr int BWD_CHUNK_THREADS = 512;
 
 // SCALAR (one decay per token): the intra-chunk part contracts the plain k / q rows with weights that already carry
@@ -571,17 +579,11 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
     uint8_t* sKQ = base + KQ_OFF;
     uint8_t* sWD = sV;                                 // rows 32 I + r = scale strictlower(dAqk)[16 I + r], rows 32 I + 16 + r = strictlower(dL)[16 I + r]
     uint8_t* sBd = sA;
-    // output tiles, fp32 [tok][channel]: dq and dk over the dead S tile, dg over the dead dX^T tile (the dS' region
-    // between them already receives the next item's tile)
-    float* oq = reinterpret_cast<float*>(base);
-    float* ok = oq + CH * DK;
-    float* og = reinterpret_cast<float*>(sO);
 
     const int HV = p.L.HV, HK = p.L.HK;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
     const int total = p.L.NC * HV, stride = gridDim.x;
-    const bool sender = tid == 15 * 32;                // sends the output tiles off; requests S / dO of the next item
 
     auto fetch_early = [&](size_t it) {                // dS', Vd^T, A: their regions are free once the intra-chunk products are done
         umma::mbar_expect_tx(&sh.ld0, umma::STATE_TILE_BYTES + umma::CHUNK_TILE_BYTES + umma::QUARTER_TILE_BYTES);
@@ -589,7 +591,7 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
         umma::bulk_load(sV, reinterpret_cast<const uint8_t*>(p.Vd) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld0);
         umma::bulk_load(sA, reinterpret_cast<const uint8_t*>(p.A) + it * umma::QUARTER_TILE_BYTES, umma::QUARTER_TILE_BYTES, &sh.ld0);
     };
-    auto fetch_late = [&](size_t it) {                 // S, dO: their regions hold the output tiles until those have left
+    auto fetch_late = [&](size_t it) {                 // S, dO
         umma::mbar_expect_tx(&sh.ld2, umma::STATE_TILE_BYTES + umma::CHUNK_TILE_BYTES);
         umma::bulk_load(sS, reinterpret_cast<const uint8_t*>(p.h) + it * umma::STATE_TILE_BYTES, umma::STATE_TILE_BYTES, &sh.ld2);
         umma::bulk_load(sO, reinterpret_cast<const uint8_t*>(p.dO_t) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ld2);
@@ -603,16 +605,19 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
     }
     publish();
     const uint32_t tmem = sh.tmem;
-    if (tid == 0 && (int)blockIdx.x < total) fetch_early(blockIdx.x);
-    if (sender && (int)blockIdx.x < total) fetch_late(blockIdx.x);
+    if (tid == 0 && (int)blockIdx.x < total) { fetch_early(blockIdx.x); fetch_late(blockIdx.x); }
     // phase counters of the barriers (every thread walks the same sequence of phases)
     uint32_t nA = 0, nB = 0, nC = 0, nD = 0, n0 = 0, n1 = 0, n2 = 0;
+    // the chunk table entries are read one item ahead: every address of an item depends on them
+    int next_start = 0, next_len = 1;
+    if ((int)blockIdx.x < total) { next_start = p.L.chunk_start[blockIdx.x / HV]; next_len = p.L.chunk_len[blockIdx.x / HV]; }
 
     for (int item = blockIdx.x; item < total; item += stride) {
         const int c = item / HV, h = item - c * HV;    // heads fastest: CTAs that run together read neighbouring memory
         const int hk = h / (HV / HK);
-        const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+        const int start = next_start, len = next_len;
         const bool more = item + stride < total;
+        if (more) { next_start = p.L.chunk_start[(item + stride) / HV]; next_len = p.L.chunk_len[(item + stride) / HV]; }
 
         // ---- state products whose operands are all copies | register loads, dgl ------------------------
         if (umma::mma_issuer()) {
@@ -629,13 +634,6 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
         Raw8 wk[2], wq[2];                                 // k, q and v stay raw until their first use: no thread waits for them where they are requested
         uint32_t wv[16];
         {
-            if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
-            if (tid >= CH && tid < 2 * CH) {
-                const int r = tid - CH;
-                const size_t tk = (size_t)(start + (r < len ? r : len - 1)) * HK + hk;
-                sRk[r] = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
-                sRq[r] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
-            }
             // k, g and this thread's column of v are requested now and used once the first products are under way
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
@@ -647,6 +645,14 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
             for (int j = 0; j < 16; ++j) {
                 const int t = cg * 16 + j, tt = t < len ? t : len - 1;
                 wv[j] = ldraw1<DT>(p.v, ((size_t)(start + tt) * HV + h) * 128 + row);
+            }
+            // (after the large requests: these few threads wait for their values in order to park them in shared memory)
+            if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
+            if (tid >= CH && tid < 2 * CH) {
+                const int r = tid - CH;
+                const size_t tk = (size_t)(start + (r < len ? r : len - 1)) * HK + hk;
+                sRk[r] = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
+                sRq[r] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
             }
             // dgl[c] = sum_v S[c][v] dS'[c][v] from the two tiles: chunk (v row, 8 channels) per thread, four rows each
             umma::mbar_wait(&sh.ld0, n0 & 1);
@@ -898,9 +904,10 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
                 }
             }
             umma::commit(&sh.barA);
-            if (more) {                                        // every operand tile is dead once these products are done:
-                umma::mbar_wait(&sh.barA, nA & 1);             // the next item's dS', Vd^T and A start travelling under the epilogue
-                fetch_early((size_t)item + stride);
+            if (more) {                                        // every operand tile is dead once these products are done (the epilogue
+                umma::mbar_wait(&sh.barA, nA & 1);             // reads accumulators and writes global memory): all five tiles of the
+                fetch_early((size_t)item + stride);            // next item travel under it
+                fetch_late((size_t)item + stride);
             }
         }
         {
@@ -930,6 +937,12 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
             }
             __syncthreads();
             const float extra = ((sCol[0][row] + sCol[1][row]) + (sCol[2][row] + sCol[3][row])) + ex2f_(gL) * sDgl[row];
+            // the three outputs per (token, channel) go straight to their fp32 [64 tokens][128] tiles: a warp writes 128
+            // consecutive bytes per token, and shared memory stays free for the next item's tiles
+            const size_t ob = (size_t)item * (size_t)(CH * DK) + row;
+            float* __restrict__ oq = p.dq_v + ob;
+            float* __restrict__ ok = p.dk_v + ob;
+            float* __restrict__ og = p.dgp + ob;
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
                 const int c0 = 16 * cg + 8 * hf;
@@ -967,9 +980,9 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
                     float dg = qv * up * dqt + kv * up * dkt - kv * re * dkb;
                     if (i == len - 1) dg += extra;
                     const bool ok_row = i < len;
-                    oq[i * DK + row] = ok_row ? dqt * up + dqr + dgn * kv : 0.f;
-                    ok[i * DK + row] = ok_row ? (dkt * up + dkb * re) + bt * T + dkc[r] + dgn * qv : 0.f;
-                    og[i * DK + row] = ok_row ? dg + qv * dqr + kv * bt * T - kv * dkc[r] : 0.f;
+                    oq[i * DK] = ok_row ? dqt * up + dqr + dgn * kv : 0.f;
+                    ok[i * DK] = ok_row ? (dkt * up + dkb * re) + bt * T + dkc[r] + dgn * qv : 0.f;
+                    og[i * DK] = ok_row ? dg + qv * dqr + kv * bt * T - kv * dkc[r] : 0.f;
                 }
                 // sum over the 32 channels of this warp for the 8 rows at once: every exchange halves the number of rows a lane
                 // carries (9 shuffles instead of 40); the lane whose bits 4..2 spell the row ends up with its sum
@@ -991,20 +1004,11 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
                 bsv[0] += __shfl_xor_sync(0xffffffffu, bsv[0], 1);
                 if ((lane & 3) == 0) sRed[q][c0 + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = bsv[0];
             }
-            umma::fence_async_smem();
         }
         ++nA;
         umma::fence_before_sync();
-        __syncthreads();                                       // output tiles and sRed complete; every accumulator has been read
+        __syncthreads();                                       // sRed complete; every accumulator has been read
         umma::fence_after_sync();
-        if (sender) {
-            const size_t ob = (size_t)item * (size_t)(CH * DK);
-            umma::bulk_store(p.dq_v + ob, oq, CH * DK * 4);
-            umma::bulk_store(p.dk_v + ob, ok, CH * DK * 4);
-            umma::bulk_store(p.dgp + ob, og, CH * DK * 4);
-            umma::bulk_store_wait_read();                      // the output tiles have left: S and dO of the next item may land
-            if (more) fetch_late((size_t)item + stride);
-        }
         if (tid < len) {
             const size_t th = (size_t)(start + tid) * HV + h;
             float db = sDbw[tid] + ((sRed[0][tid] + sRed[1][tid]) + (sRed[2][tid] + sRed[3][tid]));
