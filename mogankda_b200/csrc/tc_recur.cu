@@ -74,7 +74,10 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
 
     const int c_beg = p.L.seg_chunk_off[seg], c_end = p.L.seg_chunk_off[seg + 1];
     // nw^T and kbar arrive as the ready-made tiles written by the intra-chunk kernel: two bulk copies per chunk on one
-    // barrier (thread 0); the 128 decay factors of the chunk are copied by the first four warps
+    // barrier (thread 0).  The 128 decay factors of the chunk are read by the first four warps into a register and parked
+    // in shared memory a phase later: a load stored at once would make those warps (and, at the next barrier, everybody)
+    // wait for it in every step of the chain.
+    float gl_next = 0.f;
     auto fetch = [&](int c, int buf) {
         const size_t it = (size_t)c * HV + h;
         if (tid == 0) {
@@ -82,7 +85,7 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
             umma::bulk_load(sW[buf], reinterpret_cast<const uint8_t*>(p.nw) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[buf]);
             umma::bulk_load(sK[buf], reinterpret_cast<const uint8_t*>(p.kbar) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[buf]);
         }
-        if (tid < DK) sh.gl[buf][tid] = p.gl[it * 128 + tid];
+        if (tid < DK) gl_next = p.gl[it * 128 + tid];
     };
 
     // u^T of a chunk arrives as the chunk tile written by the intra-chunk kernel (one buffer: requested as soon as the
@@ -93,13 +96,17 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
             umma::bulk_load(sU, reinterpret_cast<const uint8_t*>(p.u) + ((size_t)c * HV + h) * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldu);
         }
     };
-    if (c_beg < c_end) { fetch(c_beg, 0); fetch_u(c_beg); }
+    if (c_beg < c_end) {
+        fetch(c_beg, 0);
+        fetch_u(c_beg);
+        if (tid < DK) sh.gl[0][tid] = gl_next;
+    }
     for (int c = c_beg; c < c_end; ++c) {
         const int buf = (c - c_beg) & 1;
         const bool more = c + 1 < c_end;
         if (tid == 0) umma::bulk_store_wait_read();         // the previous chunk's saved tiles have left shared memory
         if (more) fetch(c + 1, buf ^ 1);                    // ... so the other buffers (last read by chunk c - 1) take the next tiles
-        __syncthreads();                                   // sh.gl[buf] is complete
+        __syncthreads();                                   // sh.gl[buf] is complete; the saved state tile has left
         {   // state entering the chunk: operand tile (optionally saved as it is by the issuing thread below), decay
             float s[32];
             umma::tmem_ld32(umma::tmem_addr(tmem, warp, cg * 32), s);
@@ -115,6 +122,7 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
             umma::tmem_st32(umma::tmem_addr(tmem, warp, cg * 32), s);
             umma::tmem_wait_st();
         }
+        if (more && tid < DK) sh.gl[buf ^ 1][tid] = gl_next;   // read at the top of the next iteration, after several barriers
         publish_operands();
         if (umma::mma_issuer()) {
             umma::mbar_wait(&sh.ldw[buf], ((c - c_beg) >> 1) & 1);            // this chunk's nw and kbar tiles have landed
@@ -250,8 +258,13 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
         umma::tmem_wait_st();
     }
     const int c_beg = p.L.seg_chunk_off[seg], c_end = p.L.seg_chunk_off[seg + 1];
+    // decay factors: the next chunk's are read into a register one iteration ahead and parked in shared memory after the
+    // state tile has been built (a load stored at once would be waited for in every step of the chain)
+    float gl_next = 0.f;
+    if (c_beg < c_end && tid < DK) sh.gl[0][tid] = p.gl[((size_t)(c_end - 1) * HV + h) * 128 + tid];
     for (int c = c_end - 1; c >= c_beg; --c) {
-        const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
+        const int start = DODT != DO_TILE ? p.L.chunk_start[c] : 0, len = DODT != DO_TILE ? p.L.chunk_len[c] : CH;
+        const int par = (c_end - 1 - c) & 1;
         {   // Five of the six operands arrive as ready-made tiles (their last readers, the previous chunk's products, are
             // done): Aqk and kbar for the first product on one barrier, scale q 2^g and nw^T for the second on the other.
             // Only dO goes through registers.
@@ -267,7 +280,7 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
                 umma::bulk_load(sQs, reinterpret_cast<const uint8_t*>(p.qs) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[0]);
                 umma::bulk_load(sNw, reinterpret_cast<const uint8_t*>(p.nw) + it * umma::CHUNK_TILE_BYTES, umma::CHUNK_TILE_BYTES, &sh.ldw[0]);
             }
-            if (tid < DK) sh.gl[0][tid] = p.gl[it * 128 + tid];
+            if (c > c_beg && tid < DK) gl_next = p.gl[(it - HV) * 128 + tid];
         }
         float vo[2][8];
         if (DODT != DO_TILE) {
@@ -300,10 +313,11 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
                 store_split8(sAh, sAl, 128, row, cg * 4 + i, v8);
             }
 #pragma unroll
-            for (int j = 0; j < 32; ++j) s[j] *= sh.gl[0][cg * 32 + j];
+            for (int j = 0; j < 32; ++j) s[j] *= sh.gl[par][cg * 32 + j];
             umma::tmem_st32(umma::tmem_addr(tmem, warp, cg * 32), s);
             umma::tmem_wait_st();
         }
+        if (c > c_beg && tid < DK) sh.gl[par ^ 1][tid] = gl_next;
         publish_operands();
         // the operand tile is also this chunk's saved gradient: one asynchronous 64 KB copy, awaited by the same thread
         // before the tile is rebuilt in the next iteration (measured: starting it here is faster than after the products);
