@@ -154,6 +154,9 @@ typedef struct {
     float* ht;                 /* [NS,HV,128,128] state leaving each segment, or NULL */
     int want_transition;
     float* mt;                 /* [NS,HV,128,128] transition (row = output K index), needs want_transition */
+    const int* warm_start;     /* [NS,HV] from mkda_warmup_chunks, or NULL.  A pass from zero (the segment pre-pass) may start
+                                * at this chunk instead of the segment's first one; where it does, the transition is written
+                                * as zero without being computed. */
 } MkdaRecurFwd;
 int mkda_recur_fwd(const MkdaRecurFwd* p, void* stream);
 
@@ -261,6 +264,8 @@ typedef struct {
     float* dVd_t;              /* [NC,HV] chunk tiles: dVd^T [v][token] (token columns past the end are zero), or NULL */
     float* dO_t;               /* [NC,HV] row tiles: dO [token][v] as staged for the products (zero rows past the end), or NULL */
     float* dh0;                /* [NS,HV,128,128] gradient of the state entering each segment, or NULL */
+    const int* warm_end;       /* [NS,HV] from mkda_warmup_chunks, or NULL: a reverse pass from zero (the segment pre-pass)
+                                * may start below this chunk index instead of at the segment's last chunk */
 } MkdaBwdDh;
 int mkda_bwd_dh(const MkdaBwdDh* p, void* stream);
 
@@ -320,6 +325,26 @@ typedef struct {
     float* s_out;              /* [NG,HV,128,128] value leaving the last (first) segment of each group, or NULL */
 } MkdaCombine;
 int mkda_state_combine(const MkdaCombine* p, void* stream);
+
+/* Warm-up truncation of the segment pre-passes.  The state entering a chunk reaches the end of its segment multiplied, per
+ * key channel, by the decay of all chunks from there on.  Where the slowest channel's accumulated decay is already below
+ * the threshold, what came before cannot be seen at the segment's end and a pass from zero need not visit it:
+ *   warm_start[seg][h] = the last chunk c of the segment with  max_channel sum_{c' >= c} log2 gl[c'] < threshold_log2
+ *                        (the segment's first chunk if there is none: nothing is skipped),
+ *   warm_end[seg][h]   = one past the first chunk c with  max_channel sum_{c' <= c} log2 gl[c'] < threshold_log2
+ *                        (one past the segment's last chunk if there is none), for the reverse chain.
+ * An approximation with relative error 2^threshold_log2 in the segment-level states (the per-chunk main passes stay exact
+ * given their entering state).  Follows get_warmup_chunks
+ * (mogan_kda/ops/gated_delta_rule/chunk/blackwell/cp_fwd.py:81-115, threshold -10 in natural-log units there), extended to
+ * the per-channel gate through the maximum over channels. */
+typedef struct {
+    MkdaLayout L;
+    const float* gl;           /* [NC,HV,128] as written by mkda_intra_fwd */
+    float threshold_log2;
+    int* warm_start;           /* [NS,HV] */
+    int* warm_end;             /* [NS,HV] */
+} MkdaWarmup;
+int mkda_warmup_chunks(const MkdaWarmup* p, void* stream);
 
 /* Self-test of the tensor-core path: D[128,N] = A[128,K] B[N,K]^T (fp32 in, bf16 hi/lo split, fp32 out); N, K in
  * {64, 128}.  No counterpart in the reference; used by the tests to validate the tcgen05 plumbing in isolation. */

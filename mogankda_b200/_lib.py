@@ -13,7 +13,7 @@ HEADER = os.path.join(HERE, "..", "include", "mkda.h")
 ENTRY_POINTS = (
     "mkda_gate_cumsum_fwd", "mkda_gate_bwd", "mkda_reduce_partials", "mkda_l2norm_rstd", "mkda_intra_fwd",
     "mkda_recur_fwd", "mkda_out_fwd", "mkda_epilogue_bwd", "mkda_epilogue_bwd_tiles", "mkda_bwd_dh", "mkda_bwd_chunk",
-    "mkda_qk_grad_finish", "mkda_state_combine", "mkda_selftest_umma", "mkda_selftest_wait", "mkda_epilogue_bwd_noalloc",
+    "mkda_qk_grad_finish", "mkda_state_combine", "mkda_warmup_chunks", "mkda_selftest_umma", "mkda_selftest_wait", "mkda_epilogue_bwd_noalloc",
 )
 ENUMS = {}
 STRUCTS = {}

@@ -8,6 +8,10 @@ Differences that are extensions, not changes of meaning:
   * q / k / v may also be float32 (the reference kernels take bf16 / fp16 only); outputs follow the input dtype.
   * context parallelism exists for the per-channel gate as well (``cp_context`` from ``mogankda_b200.cp``).
   * a scalar gate [B,T,HV] goes through the same kernels with the decay broadcast over the key channels.
+  * ``warmup_threshold`` (natural-log units, e.g. -10.0; default None = exact): warm-up truncation of the segment
+    pre-passes.  The reference applies it inside its intra-card context parallelism with a fixed -10
+    (mogan_kda/ops/gated_delta_rule/chunk/cp/preprocess.py:121-139); here it is an explicit choice because it is an
+    approximation (relative error e^threshold in the states handed between segments).
 """
 import torch
 
@@ -43,11 +47,14 @@ class _DeltaRuleFunction(torch.autograd.Function):
                                                     scalar_gate=x.dim() == 3)
         vf = cfg["state_v_first"]
         need_ht = cfg["output_final_state"]
-        ms = m_first = None
+        ms = m_first = warm_end = None
         if lay.segmented or cp is not None:
             # pre-pass from zero: per-segment (state, transition); then the true entering state of every segment
+            warm_start = None
+            if cfg["warmup"] is not None:
+                warm_start, warm_end = ops.warmup_chunks(lay, gl, HK, HV, cfg["warmup"])
             _, _, hs, ms = ops.recur_fwd(lay, nw, u, kbar, gl, HK, HV, store_h=False, store_vd=False,
-                                         want_transition=True)
+                                         want_transition=True, warm_start=warm_start)
             carry = None
             if initial_state is not None:
                 carry = initial_state.transpose(-1, -2).contiguous() if vf else initial_state
@@ -73,7 +80,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
                                  keep_raw=cfg["has_ep"] and need_bwd)
         if need_bwd:
             ctx.save_for_backward(q, k, v, x, beta, A_log, dt_bias, initial_state, ep_w, ep_gate, q_rstd, k_rstd,
-                                  g_c, beta_e, A, Aqk, nw, h, o_raw, ms, kbar, qs, gl, Vd, m_first)
+                                  g_c, beta_e, A, Aqk, nw, h, o_raw, ms, kbar, qs, gl, Vd, m_first, warm_end)
         ctx.cfg, ctx.lay, ctx.dims = cfg, lay, (B, T, HK, HV)
         ctx.set_materialize_grads(False)
         return out.view(B, T, HV, 128), ht
@@ -82,7 +89,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
     @torch.autograd.function.once_differentiable
     def backward(ctx, dy, dht):
         (q, k, v, x, beta, A_log, dt_bias, initial_state, ep_w, ep_gate, q_rstd, k_rstd, g_c, beta_e, A, Aqk, nw, h,
-         o_raw, ms, kbar, qs, gl, Vd, m_first) = ctx.saved_tensors
+         o_raw, ms, kbar, qs, gl, Vd, m_first, warm_end) = ctx.saved_tensors
         cfg, lay = ctx.cfg, ctx.lay
         B, T, HK, HV = ctx.dims
         scale, vf, cp = cfg["scale"], cfg["state_v_first"], cfg["cp_context"]
@@ -102,7 +109,8 @@ class _DeltaRuleFunction(torch.autograd.Function):
         need_dh0 = initial_state is not None and ctx.needs_input_grad[7]
         if lay.segmented or cp is not None:
             # pre-pass from zero: only the gradient entering each segment is wanted, nothing per chunk is stored
-            _, _, _, dloc = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, store=False, dO_in_t=dO_in)
+            _, _, _, dloc = ops.bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, store=False, dO_in_t=dO_in,
+                                       warm_end=warm_end)
             carry = None
             if dht is not None:
                 carry = dht.transpose(-1, -2).contiguous() if vf else dht
@@ -166,7 +174,7 @@ def _check_common(q, k, v, g, beta, initial_state, cu_seqlens):
 def chunk_delta_rule(q, k, v, g, beta, *, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None,
                      state_v_first=False, gate_mode="precomputed", A_log=None, dt_bias=None, lower_bound=-5.0,
                      beta_mode="precomputed", beta_scale=1.0, use_qk_l2norm_in_kernel=False, output_norm=None,
-                     auto_cp=True, cp_context=None):
+                     auto_cp=True, cp_context=None, warmup_threshold=None):
     """Unified delta rule (mogan_kda/ops/kimi_delta_rule/chunk/__init__.py:297-349).
 
     q, k [B,T,HK,128]; v [B,T,HV,128]; g [B,T,HV,128] per-channel or [B,T,HV] scalar gate input (raw pre-activation
@@ -193,6 +201,8 @@ def chunk_delta_rule(q, k, v, g, beta, *, scale=None, initial_state=None, output
         raise ValueError(f"unknown act {ep.get('act')!r}")
     if cp_context is not None and q.shape[0] != 1:
         raise ValueError("inter-card CP requires B==1 (varlen).")
+    if warmup_threshold is not None and not float(warmup_threshold) < 0.0:
+        raise ValueError("warmup_threshold must be negative (natural-log units, e.g. -10.0) or None")
     B, T = q.shape[:2]
     cfg = dict(scale=float(q.shape[-1] ** -0.5 if scale is None else scale), output_final_state=output_final_state,
                cu_seqlens=cu_seqlens, state_v_first=state_v_first, gate_mode=gate_mode, lower_bound=lower_bound,
@@ -201,7 +211,7 @@ def chunk_delta_rule(q, k, v, g, beta, *, scale=None, initial_state=None, output
                ep_eps=None if ep is None else ep.get("eps", 1e-6),
                seg_chunks=AUTO_SEGMENT_CHUNKS if (cp_context is not None or auto_cp) else 0,
                seg_auto=cp_context is None,          # without CP the chooser in index.wants_segments decides
-               cp_context=cp_context)
+               cp_context=cp_context, warmup=None if warmup_threshold is None else float(warmup_threshold))
     ep_gate = None if ep is None else ep["gate"].contiguous()
     ep_w = None if ep is None else ep.get("weight")
     return _DeltaRuleFunction.apply(q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(),
@@ -217,7 +227,8 @@ def chunk_kda(q, k, v, g, beta, **kwargs):
 
 def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
                            use_qk_l2norm_in_kernel=False, cu_seqlens=None, head_first=False, state_v_first=False,
-                           auto_cp=True, enable_fwd_cp_cache=True, cp_context=None, force_intra_cp=False):
+                           auto_cp=True, enable_fwd_cp_cache=True, cp_context=None, force_intra_cp=False,
+                           warmup_threshold=None):
     """Scalar-gate delta rule (mogan_kda/ops/gated_delta_rule/chunk/__init__.py:313-469).  g [B,T,HV] is the per-token
     natural-log decay, beta [B,T,HV] the effective beta."""
     assert q.dtype == k.dtype == v.dtype
@@ -227,4 +238,4 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
     return chunk_delta_rule(q, k, v, g, beta, scale=scale, initial_state=initial_state,
                             output_final_state=output_final_state, cu_seqlens=cu_seqlens,
                             state_v_first=state_v_first, use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel,
-                            auto_cp=auto_cp or force_intra_cp, cp_context=cp_context)
+                            auto_cp=auto_cp or force_intra_cp, cp_context=cp_context, warmup_threshold=warmup_threshold)

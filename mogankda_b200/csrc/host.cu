@@ -113,13 +113,13 @@ extern "C" int mkda_device_status_clear(void) {
     return rc;
 }
 extern "C" const char* mkda_last_error(void) { return mkda::g_err; }
-extern "C" int mkda_abi_version(void) { return 3; }
+extern "C" int mkda_abi_version(void) { return 4; }
 extern "C" int mkda_struct_sizes(int* out, int n) {
     const int sizes[] = {
         (int)sizeof(MkdaLayout),   (int)sizeof(MkdaGateFwd),  (int)sizeof(MkdaGateBwd),     (int)sizeof(MkdaReduce),
         (int)sizeof(MkdaL2Norm),   (int)sizeof(MkdaIntraFwd), (int)sizeof(MkdaRecurFwd),    (int)sizeof(MkdaOutFwd),
         (int)sizeof(MkdaEpilogueBwd), (int)sizeof(MkdaEpilogueBwdTiles), (int)sizeof(MkdaEpilogueBwdNoAlloc), (int)sizeof(MkdaBwdDh), (int)sizeof(MkdaBwdChunk),
-        (int)sizeof(MkdaQkGrad),   (int)sizeof(MkdaCombine), (int)sizeof(MkdaSelfTest), (int)sizeof(MkdaSelfTestWait)};
+        (int)sizeof(MkdaQkGrad),   (int)sizeof(MkdaCombine), (int)sizeof(MkdaWarmup), (int)sizeof(MkdaSelfTest), (int)sizeof(MkdaSelfTestWait)};
     const int cnt = (int)(sizeof(sizes) / sizeof(sizes[0]));
     for (int i = 0; i < n && i < cnt; ++i) out[i] = sizes[i];
     return cnt;

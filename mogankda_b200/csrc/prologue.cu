@@ -468,6 +468,28 @@ __global__ void __launch_bounds__(128) epilogue_bwd_tiles_kernel(const MkdaEpilo
     p.part_w[(size_t)blockIdx.x * 128 + threadIdx.x] = t;
 }
 
+// Warm-up truncation table: one CTA per (segment, v-head), one thread per key channel (see MkdaWarmup).
+// gl = 2^gL may have underflowed to zero: log2 gives -inf, i.e. fully decayed.
+__global__ void __launch_bounds__(128) warmup_chunks_kernel(const MkdaWarmup p) {
+    const int seg = blockIdx.x, h = blockIdx.y, ch = threadIdx.x, HV = p.L.HV;
+    const int c_beg = p.L.seg_chunk_off[seg], c_end = p.L.seg_chunk_off[seg + 1];
+    int ws = c_beg, we = c_end;
+    float acc = 0.f;
+    for (int c = c_end - 1; c > c_beg; --c) {              // forward pass: decay from chunk c to the segment's end
+        acc += log2f(p.gl[((size_t)c * HV + h) * 128 + ch]);
+        if (__syncthreads_and(acc < p.threshold_log2)) { ws = c; break; }
+    }
+    acc = 0.f;
+    for (int c = c_beg; c < c_end - 1; ++c) {              // reverse pass: decay from the segment's start through chunk c
+        acc += log2f(p.gl[((size_t)c * HV + h) * 128 + ch]);
+        if (__syncthreads_and(acc < p.threshold_log2)) { we = c + 1; break; }
+    }
+    if (ch == 0) {
+        p.warm_start[seg * HV + h] = ws;
+        p.warm_end[seg * HV + h] = we;
+    }
+}
+
 }  // namespace mkda
 
 using namespace mkda;
@@ -476,6 +498,14 @@ using namespace mkda;
 static int epilogue_part_rows(int rows) {
     const int groups = (rows + 63) / 64;
     return groups < MKDA_EPILOGUE_MAX_PART_ROWS ? groups : MKDA_EPILOGUE_MAX_PART_ROWS;
+}
+
+extern "C" int mkda_warmup_chunks(const MkdaWarmup* p, void* stream) {
+    if (!p || !p->gl || !p->warm_start || !p->warm_end || !p->L.seg_chunk_off) return set_error(MKDA_ERR_ARG, "warmup_chunks: null argument");
+    if (!(p->threshold_log2 < 0.f)) return set_error(MKDA_ERR_ARG, "warmup_chunks: the threshold must be negative");
+    if (p->L.NS == 0 || p->L.HV == 0) return MKDA_OK;
+    warmup_chunks_kernel<<<dim3(p->L.NS, p->L.HV), 128, 0, (cudaStream_t)stream>>>(*p);
+    return check_launch("warmup_chunks");
 }
 
 extern "C" int mkda_gate_cumsum_fwd(const MkdaGateFwd* p, void* stream) {

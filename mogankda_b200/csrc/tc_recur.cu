@@ -56,15 +56,24 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
     const uint32_t tmem = sh.tmem;
     uint32_t phase = 0;
 
+    // Warm-up truncation (a pass from zero only): where the decay accumulated from chunk warm_start to the segment's end
+    // hides everything before it, the pass starts there; the transition is then zero and its CTA visits no chunk.
+    int c_beg = p.L.seg_chunk_off[seg];
+    const int c_end = p.L.seg_chunk_off[seg + 1];
+    bool cut = false;
+    if (p.warm_start) {
+        const int w = p.warm_start[seg * HV + h];
+        if (w > c_beg) { cut = true; c_beg = trans ? c_end : w; }
+    }
     {   // initial state: columns [32 cg, 32 cg + 32) of row `row`
         float s[32];
         const int h0row = p.seg_h0 ? p.seg_h0[seg] : seg;
-        const float* h0 = (!trans && p.h0 && h0row >= 0) ? p.h0 + ((size_t)h0row * HV + h) * DK * DV : nullptr;
+        const float* h0 = (!trans && !cut && p.h0 && h0row >= 0) ? p.h0 + ((size_t)h0row * HV + h) * DK * DV : nullptr;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
             const int kk = cg * 32 + j;
             float v = 0.f;
-            if (trans) v = (kk == row) ? 1.f : 0.f;
+            if (trans) v = (kk == row && !cut) ? 1.f : 0.f;
             else if (h0) v = vf ? h0[(size_t)row * DK + kk] : h0[(size_t)kk * DV + row];
             s[j] = v;
         }
@@ -72,7 +81,6 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
         umma::tmem_wait_st();
     }
 
-    const int c_beg = p.L.seg_chunk_off[seg], c_end = p.L.seg_chunk_off[seg + 1];
     // nw^T and kbar arrive as the ready-made tiles written by the intra-chunk kernel: two bulk copies per chunk on one
     // barrier (thread 0).  The 128 decay factors of the chunk are read by the first four warps into a register and parked
     // in shared memory a phase later: a load stored at once would make those warps (and, at the next barrier, everybody)
@@ -245,10 +253,19 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
     const uint32_t tmem = sh.tmem;
     uint32_t phase = 0;
 
+    // Warm-up truncation (a pass from zero only): the reverse chain starts below chunk warm_end where the decay accumulated
+    // over the segment's first chunks hides every later contribution from the segment's entrance.
+    const int c_beg = p.L.seg_chunk_off[seg];
+    int c_end = p.L.seg_chunk_off[seg + 1];
+    bool cut = false;
+    if (p.warm_end) {
+        const int w = p.warm_end[seg * HV + h];
+        if (w < c_end) { cut = true; c_end = w; }
+    }
     {
         float s[32];
         const int drow = p.seg_dht ? p.seg_dht[seg] : seg;
-        const float* src = (p.dht && drow >= 0) ? p.dht + ((size_t)drow * HV + h) * DK * DV : nullptr;
+        const float* src = (p.dht && drow >= 0 && !cut) ? p.dht + ((size_t)drow * HV + h) * DK * DV : nullptr;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
             const int kk = cg * 32 + j;
@@ -257,7 +274,6 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
         umma::tmem_st32(umma::tmem_addr(tmem, warp, cg * 32), s);
         umma::tmem_wait_st();
     }
-    const int c_beg = p.L.seg_chunk_off[seg], c_end = p.L.seg_chunk_off[seg + 1];
     // decay factors: the next chunk's are read into a register one iteration ahead and parked in shared memory after the
     // state tile has been built (a load stored at once would be waited for in every step of the chain)
     float gl_next = 0.f;

@@ -148,9 +148,23 @@ def intra_fwd(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, scale, HK, HV, scalar_g
     return A, Aqk, nw, u, kbar, qs, gl
 
 
+def warmup_chunks(lay, gl, HK, HV, threshold):
+    """Warm-up truncation table of the segment pre-passes for a decay threshold in natural-log units (the reference's
+    default is -10).  Returns int32 (warm_start [NS,HV], warm_end [NS,HV]); see ``MkdaWarmup`` in include/mkda.h."""
+    dev = gl.device
+    ws = torch.empty(lay.NS, HV, dtype=torch.int32, device=dev)
+    we = torch.empty(lay.NS, HV, dtype=torch.int32, device=dev)
+    p = STRUCTS["MkdaWarmup"]()
+    p.L = _layout_struct(lay, HK, HV)
+    p.gl, p.threshold_log2, p.warm_start, p.warm_end = _ptr(gl), float(threshold) * 1.4426950408889634, _ptr(ws), _ptr(we)
+    _lib.call("mkda_warmup_chunks", p, _stream())
+    return ws, we
+
+
 def recur_fwd(lay, nw, u, kbar, gl, HK, HV, *, h0=None, seg_h0=None, state_v_first=False, store_h=True,
-              store_vd=True, want_ht=True, want_transition=False, segments=True):
+              store_vd=True, want_ht=True, want_transition=False, segments=True, warm_start=None):
     """Runs the serial state pass over the layout's segments (or whole sequences with ``segments=False``).
+    ``warm_start`` (from ``warmup_chunks``) shortens a pass from zero.
     Returns (h [NC,HV] state tiles or None, Vd [NC,HV] chunk tiles or None, ht [NS,HV,128,128] or None, mt or None)."""
     dev = nw.device
     NS = lay.NS if segments else lay.N
@@ -163,6 +177,10 @@ def recur_fwd(lay, nw, u, kbar, gl, HK, HV, *, h0=None, seg_h0=None, state_v_fir
     ht = torch.empty(NS, HV, 128, 128, dtype=torch.float32, device=dev) if want_ht else None
     mt = torch.empty(NS, HV, 128, 128, dtype=torch.float32, device=dev) if want_transition else None
     p.h, p.Vd, p.ht, p.want_transition, p.mt = _ptr(h), _ptr(Vd), _ptr(ht), int(want_transition), _ptr(mt)
+    if warm_start is not None:
+        if h0 is not None or store_h or store_vd or not segments:
+            raise ValueError("warm_start applies to a pass from zero that stores nothing per chunk")
+        p.warm_start = _ptr(warm_start, torch.int32)
     _lib.call("mkda_recur_fwd", p, _stream())
     return h, Vd, ht, mt
 
@@ -257,7 +275,7 @@ def epilogue_bwd_tiles(lay, dy, o_raw, weight, gate, act, eps, HV):
 
 
 def bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, *, dht=None, seg_dht=None,
-           state_v_first=False, want_dh0=True, segments=True, store=True, dO_in_t=None):
+           state_v_first=False, want_dh0=True, segments=True, store=True, dO_in_t=None, warm_end=None):
     """Reverse state chain.  dO comes either as rows ``d_o`` [TT,HV,128] or as the row tiles ``dO_in_t`` of
     ``epilogue_bwd_tiles``.  With ``store`` the per-chunk results leave as tiles for ``bwd_chunk``: dh (state tiles), dVd^T
     (chunk tiles) and, for row input, the staged dO (row tiles); a pre-pass that only wants the segment-level gradient
@@ -281,6 +299,10 @@ def bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, *, dht=None, seg_dht=None,
             dO_t = torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=dev)
     dh0 = torch.empty(NS, HV, 128, 128, dtype=torch.float32, device=dev) if want_dh0 else None
     p.dh, p.dVd_t, p.dO_t, p.dh0 = _ptr(dh), _ptr(dVd_t), _ptr(None if dO_in_t is not None else dO_t), _ptr(dh0)
+    if warm_end is not None:
+        if dht is not None or store or not segments:
+            raise ValueError("warm_end applies to a reverse pass from zero that stores nothing per chunk")
+        p.warm_end = _ptr(warm_end, torch.int32)
     _lib.call("mkda_bwd_dh", p, _stream())
     return dh, dVd_t, dO_t, dh0
 

@@ -37,7 +37,7 @@ def test_struct_sizes_match_header(lib):
     assert lib.mkda_struct_sizes(sizes, n) == n
     for i, name in enumerate(_lib.STRUCT_ORDER):
         assert sizes[i] == ctypes.sizeof(_lib.STRUCTS[name]), name
-    assert lib.mkda_abi_version() == 3
+    assert lib.mkda_abi_version() == 4
 
 
 def test_null_arguments_are_rejected_without_launch(lib):
