@@ -524,20 +524,22 @@ def main():
             ctx = ContextParallel(dist.group.WORLD)
             cpk = {}
             for mode, per_rank in (("weak", 65536), ("strong", 65536 // world)):
-                t1, _ = time_workload(mk, "longdoc", rank, world, device, tokens=per_rank)          # every GPU alone, no exchange
+                (t1, t1_tr), _ = time_workload(mk, "longdoc", rank, world, device, tokens=per_rank,
+                                               truncated=True)                                     # every GPU alone, no exchange
                 (tw, tw_tr), _ = time_workload(mk, "longdoc", rank, world, device, cp=ctx, tokens=per_rank,
                                                truncated=True)                                     # one document over all ranks
                 tot = per_rank * world
                 if mode == "weak":          # per-GPU work fixed: the CP step against the same slice as a stand-alone document
-                    eff = t1 / tw
+                    eff, eff_tr = t1 / tw, t1_tr / tw_tr
                 else:                       # total work fixed at 65536 tokens: against W times the one-GPU rate on the whole document
-                    t_full, _ = time_workload(mk, "longdoc", rank, world, device, tokens=tot)
-                    eff = t_full / (world * tw)
+                    (t_full, t_full_tr), _ = time_workload(mk, "longdoc", rank, world, device, tokens=tot, truncated=True)
+                    eff, eff_tr = t_full / (world * tw), t_full_tr / (world * tw_tr)
                     cpk[mode + "_ms_1gpu_whole_document"] = round(t_full, 4)
-                eff_tr = eff * tw / tw_tr           # same exact one-GPU baseline, truncated pre-passes on the CP side
+                    cpk[mode + "_ms_1gpu_whole_document_truncated"] = round(t_full_tr, 4)
                 cpk[mode] = dict(tokens_total=tot, tokens_per_rank=per_rank, ms_per_step=round(tw, 4),
                                  mtok_s=round(tot / tw / 1e3, 4), ms_1gpu_same_tokens_per_rank=round(t1, 4),
                                  efficiency=round(eff, 4), ms_per_step_truncated=round(tw_tr, 4),
+                                 ms_1gpu_same_tokens_per_rank_truncated=round(t1_tr, 4),
                                  efficiency_truncated=round(eff_tr, 4), warmup_threshold=WARMUP_THRESHOLD)
             extra["cp"] = cpk
     if rank == 0:
