@@ -34,7 +34,8 @@ class _DeltaRuleFunction(torch.autograd.Function):
         B, T, HK, K = q.shape
         HV = v.shape[2]
         dev = q.device
-        lay = get_layout(B, T, cfg["cu_seqlens"], dev, cfg["seg_chunks"], HV if cfg["seg_auto"] else 0)
+        lay = get_layout(B, T, cfg["cu_seqlens"], dev, cfg["seg_chunks"], HV if cfg["seg_auto"] else 0,
+                         2.5 if cfg["warmup"] is None else 1.25)
         cp = cfg["cp_context"]
         scale = cfg["scale"]
         q_rstd = k_rstd = None

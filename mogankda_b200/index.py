@@ -78,21 +78,22 @@ def _sm_count(device=None):
     return 148
 
 
-def wants_segments(chunks_per_seq, HV, seg_chunks, sm_count=None):
+def wants_segments(chunks_per_seq, HV, seg_chunks, sm_count=None, cost_ratio=2.5):
     """Segment-parallelism chooser: should sequences be cut into segments of ``seg_chunks`` chunks?
 
     The serial kernels run one CTA per (sequence or segment, v-head), one chunk step after another.  Uncut, their time is
     set by the longest sequence (critical path) unless there is so much work that the even share of all chunk steps over
     the SMs is longer still.  Cutting spreads the steps evenly but adds the state + transition pre-pass in the forward
     direction and a second pass in the backward direction, about 2.5 x the serial work over a layer step, plus the prefix
-    combine.  So: cut when the critical path is longer than 2.5 even shares.  Decided from the lengths alone (host), never
-    from data; it plays the role of the reference's intra-card CP decision
+    combine.  So: cut when the critical path is longer than 2.5 even shares (``cost_ratio``; 1.25 when the caller allows
+    warm-up truncation, which shortens the two extra passes to a few chunks wherever the gate decays).  Decided from the
+    lengths alone (host), never from data; it plays the role of the reference's intra-card CP decision
     (mogan_kda/ops/gated_delta_rule/chunk/cp/context.py:252-283, cp/autocp/decision.py:54-123)."""
     longest = max(chunks_per_seq, default=0)
     if seg_chunks <= 0 or longest <= seg_chunks:
         return False
     even_share = sum(chunks_per_seq) * HV / (sm_count or _sm_count())
-    return longest > 2.5 * even_share
+    return longest > cost_ratio * even_share
 
 
 # Entries: (static key, the cu_seqlens tensor itself, its version counter, layout).  The entry keeps the tensor alive
@@ -103,11 +104,11 @@ _cache = []
 _CACHE_MAX = 16
 
 
-def get_layout(B, T, cu_seqlens, device, seg_chunks=0, auto_heads=0):
+def get_layout(B, T, cu_seqlens, device, seg_chunks=0, auto_heads=0, cost_ratio=2.5):
     """Device tables, cached on (shape, identity + version of ``cu_seqlens``, segment policy) like the reference's
     ``tensor_cache`` (mogan_kda/utils/index.py:19-90).  A cache miss reads ``cu_seqlens`` back to the host.
     ``auto_heads`` > 0 lets ``wants_segments`` decide, for that many v-heads, whether ``seg_chunks`` is applied."""
-    key = (B, T, str(device), seg_chunks, auto_heads)
+    key = (B, T, str(device), seg_chunks, auto_heads, cost_ratio)
     ver = None if cu_seqlens is None else cu_seqlens._version
     for i, (k, ref, v, lay) in enumerate(_cache):
         if k == key and ref is cu_seqlens and v == ver:
@@ -117,7 +118,8 @@ def get_layout(B, T, cu_seqlens, device, seg_chunks=0, auto_heads=0):
     cu = None if cu_seqlens is None else [int(x) for x in cu_seqlens.tolist()]
     if auto_heads > 0:
         lens = [T] * B if cu is None else [e - s for s, e in zip(cu[:-1], cu[1:])]
-        if not wants_segments([-(-n // CHUNK) for n in lens], auto_heads, seg_chunks, _sm_count(device) if str(device) != "cpu" else None):
+        if not wants_segments([-(-n // CHUNK) for n in lens], auto_heads, seg_chunks, _sm_count(device) if str(device) != "cpu" else None,
+                              cost_ratio):
             seg_chunks = 0
     tb = build_tables(B, T, cu, seg_chunks)
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)      # noqa: E731

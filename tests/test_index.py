@@ -63,6 +63,9 @@ def test_segment_chooser():
     assert not wants_segments([], 32, 32, sm_count=148) and not wants_segments([1000], 32, 0, sm_count=148)
     # four 256-chunk sequences x 16 heads leave SMs idle, but cutting would cost more than it spreads
     assert not wants_segments([256] * 4, 16, 32, sm_count=148)
+    # ... unless warm-up truncation makes the extra passes short (the caller then passes the lower cost ratio)
+    assert wants_segments([256] * 4, 16, 32, sm_count=148, cost_ratio=1.25)
+    assert not wants_segments([40] * 100, 32, 32, sm_count=148, cost_ratio=1.25)
 
 
 def test_layout_cache_is_keyed_on_tensor_identity_not_on_its_address():
