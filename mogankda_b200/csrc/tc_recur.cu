@@ -83,8 +83,8 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
 
     // nw^T and kbar arrive as the ready-made tiles written by the intra-chunk kernel: two bulk copies per chunk on one
     // barrier (thread 0).  The 128 decay factors of the chunk are read by the first four warps into a register and parked
-    // in shared memory a phase later: a load stored at once would make those warps (and, at the next barrier, everybody)
-    // wait for it in every step of the chain.
+    // in shared memory at the end of the step: a load stored at once would make those warps (and, at the next barrier,
+    // everybody) wait for it in every step of the chain.
     float gl_next = 0.f;
     auto fetch = [&](int c, int buf) {
         const size_t it = (size_t)c * HV + h;
@@ -130,7 +130,6 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
             umma::tmem_st32(umma::tmem_addr(tmem, warp, cg * 32), s);
             umma::tmem_wait_st();
         }
-        if (more && tid < DK) sh.gl[buf ^ 1][tid] = gl_next;   // read at the top of the next iteration, after several barriers
         publish_operands();
         if (umma::mma_issuer()) {
             umma::mbar_wait(&sh.ldw[buf], ((c - c_beg) >> 1) & 1);            // this chunk's nw and kbar tiles have landed
@@ -173,6 +172,7 @@ __global__ void __launch_bounds__(512, 1) recur_fwd_tc_kernel(const MkdaRecurFwd
         }
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;
         umma::fence_after_sync();
+        if (more && tid < DK) sh.gl[buf ^ 1][tid] = gl_next;   // requested a whole step ago; read after the barrier at the top
     }
     if (tid == 0) umma::bulk_store_wait_read();
     {   // state leaving the segment
@@ -274,8 +274,8 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
         umma::tmem_st32(umma::tmem_addr(tmem, warp, cg * 32), s);
         umma::tmem_wait_st();
     }
-    // decay factors: the next chunk's are read into a register one iteration ahead and parked in shared memory after the
-    // state tile has been built (a load stored at once would be waited for in every step of the chain)
+    // decay factors: the next chunk's are read into a register one iteration ahead and parked in shared memory at the end
+    // of the step (a load stored at once would be waited for in every step of the chain)
     float gl_next = 0.f;
     if (c_beg < c_end && tid < DK) sh.gl[0][tid] = p.gl[((size_t)(c_end - 1) * HV + h) * 128 + tid];
     for (int c = c_end - 1; c >= c_beg; --c) {
@@ -333,7 +333,6 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
             umma::tmem_st32(umma::tmem_addr(tmem, warp, cg * 32), s);
             umma::tmem_wait_st();
         }
-        if (c > c_beg && tid < DK) sh.gl[par ^ 1][tid] = gl_next;
         publish_operands();
         // the operand tile is also this chunk's saved gradient: one asynchronous 64 KB copy, awaited by the same thread
         // before the tile is rebuilt in the next iteration (measured: starting it here is faster than after the products);
@@ -374,6 +373,7 @@ __global__ void __launch_bounds__(512, 1) bwd_dh_tc_kernel(const MkdaBwdDh p) {
         }
         umma::mbar_wait(&sh.bar, phase); phase ^= 1;
         umma::fence_after_sync();
+        if (c > c_beg && tid < DK) sh.gl[par ^ 1][tid] = gl_next;   // requested a whole step ago; read after the barrier at the top
     }
     if (tid == 0) umma::bulk_store_wait_read();
     if (p.dh0) {
