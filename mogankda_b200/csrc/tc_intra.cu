@@ -646,13 +646,15 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
                 const int t = cg * 16 + j, tt = t < len ? t : len - 1;
                 wv[j] = ldraw1<DT>(p.v, ((size_t)(start + tt) * HV + h) * 128 + row);
             }
-            // (after the large requests: these few threads wait for their values in order to park them in shared memory)
-            if (tid < CH) sh.beta[tid] = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
+            // beta and the L2 statistics of the rows: requested now, parked in shared memory after the dgl sums (a value
+            // stored at once would be waited for here)
+            float small0 = 0.f, small1 = 0.f;
+            if (tid < CH) small0 = tid < len ? p.beta[(size_t)(start + tid) * HV + h] : 0.f;
             if (tid >= CH && tid < 2 * CH) {
                 const int r = tid - CH;
                 const size_t tk = (size_t)(start + (r < len ? r : len - 1)) * HK + hk;
-                sRk[r] = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
-                sRq[r] = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
+                small0 = r < len ? (p.k_rstd ? p.k_rstd[tk] : 1.f) : 0.f;
+                small1 = r < len ? (p.q_rstd ? p.q_rstd[tk] : 1.f) : 0.f;
             }
             // dgl[c] = sum_v S[c][v] dS'[c][v] from the two tiles: chunk (v row, 8 channels) per thread, four rows each
             umma::mbar_wait(&sh.ld0, n0 & 1);
@@ -686,6 +688,8 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
             }
 #pragma unroll
             for (int j = 0; j < 16; ++j) vv[j] = cg * 16 + j < len ? unpack1<DT>(wv[j]) : 0.f;
+            if (tid < CH) sh.beta[tid] = small0;
+            if (tid >= CH && tid < 2 * CH) { sRk[tid - CH] = small0; sRq[tid - CH] = small1; }
         }
         ++n0; ++n2;
         umma::mbar_wait(&sh.barC, nC & 1); ++nC;           // dS' Vd^T done
