@@ -97,7 +97,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
         if dy is None:
             dy = torch.zeros(B, T, HV, 128, dtype=torch.float32 if cfg["has_ep"] else q.dtype, device=q.device)
         if not cfg["has_ep"]:
-            dy = dy.contiguous()      # with the epilogue, dy is read through its strides (a broadcast gradient is not copied)
+            dy = ops.aligned(dy)      # with the epilogue, dy is read through its strides (a broadcast gradient is not copied)
         dw = dgate = d_o = dO_in = None
         if cfg["has_ep"]:      # dO leaves the epilogue backward in the tile form the tensor-core kernels fetch
             dO_in, dgate, dw = ops.epilogue_bwd_tiles(lay, dy, o_raw, ep_w, ep_gate, cfg["ep_act"], cfg["ep_eps"], HV)
@@ -106,7 +106,7 @@ class _DeltaRuleFunction(torch.autograd.Function):
         else:
             d_o = dy
         if dht is not None:
-            dht = dht.float().contiguous()
+            dht = ops.aligned(dht.float())
         need_dh0 = initial_state is not None and ctx.needs_input_grad[7]
         if lay.segmented or cp is not None:
             # pre-pass from zero: only the gradient entering each segment is wanted, nothing per chunk is stored
@@ -213,10 +213,13 @@ def chunk_delta_rule(q, k, v, g, beta, *, scale=None, initial_state=None, output
                seg_chunks=AUTO_SEGMENT_CHUNKS if (cp_context is not None or auto_cp) else 0,
                seg_auto=cp_context is None,          # without CP the chooser in index.wants_segments decides
                cp_context=cp_context, warmup=None if warmup_threshold is None else float(warmup_threshold))
-    ep_gate = None if ep is None else ep["gate"].contiguous()
+    ep_gate = None if ep is None else ep["gate"]
     ep_w = None if ep is None else ep.get("weight")
-    return _DeltaRuleFunction.apply(q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(),
-                                    beta.contiguous(), A_log, dt_bias, initial_state, ep_w, ep_gate, cfg)
+    # contiguous and 16-byte aligned operands (a contiguous view at an odd storage offset is copied): what the kernels'
+    # vector loads and bulk copies need; the small parameter tensors are realigned where they are used
+    al = ops.aligned
+    return _DeltaRuleFunction.apply(al(q), al(k), al(v), al(g), al(beta), A_log, dt_bias, al(initial_state), ep_w,
+                                    al(ep_gate), cfg)
 
 
 def chunk_kda(q, k, v, g, beta, **kwargs):

@@ -32,6 +32,9 @@ def _ptr(t, dtype=None):
         raise RuntimeError("kernel operands must be contiguous")
     if dtype is not None and t.dtype != dtype:
         raise TypeError(f"expected {dtype}, got {t.dtype}")
+    if t.data_ptr() % 16:
+        raise RuntimeError("kernel operands must be 16-byte aligned (the kernels use 16-byte vector loads and bulk copies); "
+                           "pass inputs through ops.aligned()")
     return t.data_ptr()
 
 
@@ -50,8 +53,17 @@ def _layout_struct(lay: Layout, HK, HV, segments=True):
     return L
 
 
+def aligned(t):
+    """``t`` made contiguous and 16-byte aligned: a contiguous view at an odd storage offset (a slice of a flat parameter
+    buffer, say) is copied.  The caller keeps the result alive until its launch is enqueued."""
+    if t is None:
+        return None
+    t = t.contiguous()
+    return t if t.data_ptr() % 16 == 0 else t.clone()
+
+
 def _f32(t):
-    return None if t is None else t.float().contiguous()
+    return None if t is None else aligned(t.float())
 
 
 def gate_cumsum_fwd(lay, x, mode, A_log, dt_bias, lower_bound, HV, beta_raw=None, beta_sigmoid=False, beta_scale=1.0):
@@ -195,7 +207,7 @@ def out_fwd(lay, qs, Aqk, Vd, h, HK, HV, out_dtype, norm=None, keep_raw=False):
     p.L = _layout_struct(lay, HK, HV)
     p.qs, p.Aqk, p.Vd, p.h = _ptr(qs), _ptr(Aqk), _ptr(Vd), _ptr(h)
     if norm is not None:
-        w, gate = norm.get("weight"), norm["gate"]
+        w, gate = aligned(norm.get("weight")), aligned(norm["gate"])
         p.has_norm = 1
         if w is not None:
             p.norm_w, p.norm_w_dtype = _ptr(w), _dt(w)
@@ -208,6 +220,7 @@ def out_fwd(lay, qs, Aqk, Vd, h, HK, HV, out_dtype, norm=None, keep_raw=False):
 
 def epilogue_bwd(dy, o_raw, weight, gate, act, eps):
     """-> (do fp32 [rows,128], dgate [like gate], dweight fp32 [128] or None)."""
+    weight, gate = aligned(weight), aligned(gate)
     rows = o_raw.numel() // 128
     dev = o_raw.device
     d_o = torch.empty(rows, 128, dtype=torch.float32, device=dev)
@@ -251,10 +264,11 @@ def epilogue_bwd_tiles(lay, dy, o_raw, weight, gate, act, eps, HV):
     """Gated RMSNorm backward addressed through the chunk tables.  ``dy`` is read through its strides (see
     ``rows_strides``); anything else is made contiguous first.  -> (dO_t row tiles [NC,HV], dgate [like gate], dweight fp32
     [128] or None)."""
+    weight, gate = aligned(weight), aligned(gate)
     dev = o_raw.device
     strides = rows_strides(dy)
     if strides is None:
-        dy, strides = dy.contiguous(), (128, 1)
+        dy, strides = aligned(dy), (128, 1)
     dO_t = torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=dev)
     dgate = (torch.empty_like if lay.covers_all else torch.zeros_like)(gate)
     nblk = min(lay.NC * HV, _lib.MKDA_EPILOGUE_MAX_PART_ROWS)

@@ -229,3 +229,33 @@ def test_gated_delta_rule_entry_point():
 
     compare(run(via_gdr, lv, do, dht, opts, epi, vfirst=True),
             run(orc.chunked_delta_rule, lv, do, dht, opts, epi, f64=True, vfirst=True))
+
+
+def test_inputs_at_odd_storage_offsets_are_accepted():
+    """Contiguous views that start 4 bytes into their storage (slices of a flat buffer) are not 16-byte aligned; the
+    kernels' vector loads need that, so such inputs are copied on the way in.  Same results, bit for bit, gradients too."""
+    lv, do, dht, opts, epi = make_inputs(B=1, T=200, dtype=torch.bfloat16, gate="eda", seed=21)
+
+    def call(x):
+        kw = dict(opts, A_log=x["A_log"], dt_bias=x["dt_bias"], initial_state=x["h0"],
+                  output_norm=dict(weight=x["ep_w"], gate=x["ep_gate"], act=epi, eps=1e-6))
+        o, ht = mk.chunk_delta_rule(x["q"], x["k"], x["v"], x["g"], x["beta"], **kw)
+        return o, ht, (o.double() * do.double()).sum() + (ht.double() * dht.double()).sum()
+
+    plain = {n: t.clone().requires_grad_(True) for n, t in lv.items()}
+    o0, ht0, loss0 = call(plain)
+    g0 = torch.autograd.grad(loss0, list(plain.values()))
+
+    flats, odd = {}, {}
+    for n, t in lv.items():
+        shift = 4 // t.element_size()
+        flat = torch.zeros(t.numel() + shift, dtype=t.dtype, device=t.device)
+        flat[shift:] = t.reshape(-1)
+        flats[n] = flat.requires_grad_(True)
+        odd[n] = flats[n][shift:].view(t.shape)
+        assert odd[n].is_contiguous() and odd[n].data_ptr() % 16 == 4
+    o1, ht1, loss1 = call(odd)
+    g1 = torch.autograd.grad(loss1, list(flats.values()))
+    assert torch.equal(o0, o1) and torch.equal(ht0, ht1)
+    for (n, t), a, b in zip(lv.items(), g0, g1):
+        assert torch.equal(a.reshape(-1), b[4 // t.element_size():]), n
