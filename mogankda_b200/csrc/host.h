@@ -1,5 +1,6 @@
 // Host-side helpers shared by the launchers: error text behind mkda_last_error() and launch checking.
 #pragma once
+#include <stdint.h>
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -16,6 +17,12 @@ int ensure_smem(const void* func, int bytes, const char* what);
 // [64][128] block.  Rows past the end of the tensor read as zeros.  Returns 0, or an error code when the tensor cannot be
 // described (base not 16-byte aligned, row pitch not a multiple of 16 bytes, or the driver lacks the encoder).
 int make_rows_map(CUtensorMap* out, const void* base, int elem_bytes, unsigned long long rows, unsigned long long row_elems, const char* what);
+// True if any of the (possibly null) pointers is not 16-byte aligned: the kernels read and write their tensors with
+// 16-byte vector accesses and bulk copies, and a misaligned address would fault the device instead of returning an error.
+template <typename... P>
+inline bool any_misaligned(P... ptrs) {
+    return (((reinterpret_cast<uintptr_t>(static_cast<const void*>(ptrs)) & 15) != 0) || ...);
+}
 // Number of SMs of the current device (cached per device).
 int sm_count();
 int launch_out_fwd_tc(const MkdaOutFwd* p, cudaStream_t stream);

@@ -510,6 +510,7 @@ extern "C" int mkda_warmup_chunks(const MkdaWarmup* p, void* stream) {
 
 extern "C" int mkda_gate_cumsum_fwd(const MkdaGateFwd* p, void* stream) {
     if (!p || !p->x || !p->g_c || p->L.NC < 0) return set_error(MKDA_ERR_ARG, "gate_cumsum_fwd: null argument");
+    if (any_misaligned(p->g_c) || (!p->scalar_gate && any_misaligned(p->x, p->dt_bias))) return set_error(MKDA_ERR_ARG, "gate_cumsum_fwd: tensors must be 16-byte aligned");
     if (p->mode != MKDA_GATE_PRECOMPUTED && !(p->lower_bound < 0.f)) return set_error(MKDA_ERR_ARG, "gate_cumsum_fwd: lower_bound must be < 0");
     if (p->beta_raw && !p->beta_out) return set_error(MKDA_ERR_ARG, "gate_cumsum_fwd: beta_out missing");
     if (p->L.NC == 0) return MKDA_OK;
@@ -525,6 +526,7 @@ extern "C" int mkda_gate_cumsum_fwd(const MkdaGateFwd* p, void* stream) {
 
 extern "C" int mkda_gate_bwd(const MkdaGateBwd* p, void* stream) {
     if (!p || !p->x || !p->dgp || !p->dx) return set_error(MKDA_ERR_ARG, "gate_bwd: null argument");
+    if (any_misaligned(p->dgp) || (!p->scalar_gate && any_misaligned(p->x, p->dx, p->dt_bias))) return set_error(MKDA_ERR_ARG, "gate_bwd: tensors must be 16-byte aligned");
     if (p->L.NC == 0) return MKDA_OK;
     if (p->part_rows < 1) return set_error(MKDA_ERR_ARG, "gate_bwd: part_rows must be >= 1");
     const dim3 grid(p->L.HV, p->part_rows < p->L.NC ? p->part_rows : p->L.NC);
@@ -551,6 +553,7 @@ extern "C" int mkda_reduce_partials(const MkdaReduce* p, void* stream) {
 
 extern "C" int mkda_l2norm_rstd(const MkdaL2Norm* p, void* stream) {
     if (!p || !p->x || !p->rstd) return set_error(MKDA_ERR_ARG, "l2norm_rstd: null argument");
+    if (any_misaligned(p->x)) return set_error(MKDA_ERR_ARG, "l2norm_rstd: x must be 16-byte aligned");
     if (p->rows == 0) return MKDA_OK;
     const int grid = (p->rows + 31) / 32;
     switch (p->dtype) {
@@ -565,6 +568,7 @@ extern "C" int mkda_l2norm_rstd(const MkdaL2Norm* p, void* stream) {
 extern "C" int mkda_qk_grad_finish(const MkdaQkGrad* p, void* stream) {
     if (!p || !p->dq_v || !p->dk_v || !p->dq || !p->dk || !p->q || !p->k || p->L.HK <= 0 || p->L.HV % p->L.HK)
         return set_error(MKDA_ERR_ARG, "qk_grad_finish: bad argument");
+    if (any_misaligned(p->dq_v, p->dk_v, p->dq, p->dk, p->q, p->k)) return set_error(MKDA_ERR_ARG, "qk_grad_finish: tensors must be 16-byte aligned");
     if (p->L.NC == 0) return MKDA_OK;
     const dim3 grid(p->L.NC * p->L.HK, 2);
     switch (p->L.HV / p->L.HK) {
@@ -634,6 +638,8 @@ extern "C" int mkda_epilogue_bwd_noalloc(const MkdaEpilogueBwdNoAlloc* p, void* 
 
 extern "C" int mkda_epilogue_bwd_tiles(const MkdaEpilogueBwdTiles* p, void* stream) {
     if (!p || !p->dy || !p->o_raw || !p->gate || !p->dO_t || !p->dgate) return set_error(MKDA_ERR_ARG, "epilogue_bwd_tiles: null argument");
+    if (any_misaligned(p->o_raw, p->gate, p->norm_w, p->dO_t, p->dgate) || (p->dy_col_stride == 1 && any_misaligned(p->dy)))
+        return set_error(MKDA_ERR_ARG, "epilogue_bwd_tiles: tensors must be 16-byte aligned");
     if (p->dy_row_stride < 0 || p->dy_col_stride < 0 || (p->dy_col_stride == 1 && p->dy_row_stride % 8))
         return set_error(MKDA_ERR_ARG, "epilogue_bwd_tiles: dy strides must be >= 0 (row stride a multiple of 8 when the rows are dense)");
     const int items = p->L.NC * p->L.HV;

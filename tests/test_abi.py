@@ -69,3 +69,22 @@ def test_product_does_not_import_the_oracle():
     for fn in os.listdir(pkg):
         if fn.endswith(".py"):
             assert "oracle" not in open(os.path.join(pkg, fn)).read(), fn
+
+
+def test_entry_points_reject_misaligned_tensors_without_launching():
+    """The kernels use 16-byte vector accesses and bulk copies: a misaligned device address must come back as an error
+    code, not as a device fault.  Checked with fake addresses on a machine without a GPU: the check precedes any launch."""
+    import ctypes
+    from mogankda_b200 import _lib
+    lib = _lib.load()
+    p = _lib.STRUCTS["MkdaL2Norm"]()
+    p.x, p.dtype, p.rows, p.eps, p.rstd = 0x10004, 1, 4, 1e-6, 0x20000
+    assert lib.mkda_l2norm_rstd(ctypes.byref(p), None) == -1
+    assert b"16-byte aligned" in lib.mkda_last_error()
+    q = _lib.STRUCTS["MkdaQkGrad"]()
+    q.L.HK, q.L.HV, q.L.NC = 1, 1, 1
+    for f in ("dq_v", "dk_v", "q", "k", "dq"):
+        setattr(q, f, 0x30000)
+    q.dk = 0x30008
+    assert lib.mkda_qk_grad_finish(ctypes.byref(q), None) == -1
+    assert b"16-byte aligned" in lib.mkda_last_error()
