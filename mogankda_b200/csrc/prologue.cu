@@ -109,70 +109,65 @@ __global__ void __launch_bounds__(128, 5) gate_cumsum_fwd_kernel(const MkdaGateF
 // ---------------------------------------------------------------------------------------------------------
 // CTA (h, g), heads fastest, walks chunks g, g + gridDim.y, ... and keeps the parameter-gradient partials in registers, so the second
 // stage only has gridDim.y rows to add (fixed assignment and order: deterministic).
+// 16 warps of four rows each: 64 registers per thread, so two CTAs (half of the SM's thread slots) are resident and their
+// loads, special-function work and stores overlap (four warps of sixteen rows needed 128 registers: a quarter of the slots).
+constexpr int GB_WARPS = 16, GB_ROWS = CH / GB_WARPS;
 template <int XDT>
-__global__ void __launch_bounds__(128, 4) gate_bwd_kernel(const MkdaGateBwd p) {
+__global__ void __launch_bounds__(32 * GB_WARPS, 2) gate_bwd_kernel(const MkdaGateBwd p) {
     const int h = blockIdx.x, HV = p.L.HV;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    __shared__ float4 tot[4][32];
-    __shared__ float4 red[2][4][32];
+    __shared__ float4 tot[GB_WARPS][32];
+    __shared__ float4 red[2][GB_WARPS][32];
     const float E = p.A_log ? expf(p.A_log[h]) : 1.f;
     float4 bias = splat4(0.f);
     if (p.dt_bias) bias = p.scalar_gate ? splat4(p.dt_bias[h]) : *reinterpret_cast<const float4*>(p.dt_bias + h * 128 + 4 * lane);
     float4 pa = splat4(0.f), pb = splat4(0.f);
     for (int c = blockIdx.y; c < p.L.NC; c += gridDim.y) {
         const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
-        float4 vals[16];
+        float4 vals[GB_ROWS], xs[GB_ROWS];
 #pragma unroll
-        for (int r = 0; r < 16; ++r) {
-            const int row = warp * 16 + r, rr = row < len ? row : len - 1;
+        for (int r = 0; r < GB_ROWS; ++r) {
+            const int row = warp * GB_ROWS + r, rr = row < len ? row : len - 1;
             vals[r] = *reinterpret_cast<const float4*>(p.dgp + (((size_t)c * HV + h) * CH + rr) * 128 + 4 * lane);
+            const size_t th = (size_t)(start + rr) * HV + h;
+            xs[r] = p.scalar_gate ? splat4(ld1(p.x, XDT, th)) : ld4(p.x, XDT, th * 128 + 4 * lane);
         }
         float4 run = splat4(0.f);
 #pragma unroll
-        for (int r = 15; r >= 0; --r) {
-            if (warp * 16 + r < len) run = add4(run, vals[r]);
+        for (int r = GB_ROWS - 1; r >= 0; --r) {
+            if (warp * GB_ROWS + r < len) run = add4(run, vals[r]);
             vals[r] = run;
         }
         __syncthreads();                                   // previous chunk's readers of tot are done
         tot[warp][lane] = run;
         __syncthreads();
         float4 post = splat4(0.f);
-        for (int w = 3; w > warp; --w) post = add4(post, tot[w][lane]);
+        for (int w = GB_WARPS - 1; w > warp; --w) post = add4(post, tot[w][lane]);
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            float4 xs[8];
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                const int row = warp * 16 + half * 8 + r, rr = row < len ? row : len - 1;
-                const size_t th = (size_t)(start + rr) * HV + h;
-                xs[r] = p.scalar_gate ? splat4(ld1(p.x, XDT, th)) : ld4(p.x, XDT, th * 128 + 4 * lane);
-            }
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                const int row = warp * 16 + half * 8 + r;
-                if (row >= len) continue;                       // warp-uniform
-                const size_t th = (size_t)(start + row) * HV + h;
-                const float4 dg = add4(vals[half * 8 + r], post);
-                if (p.scalar_gate) {
-                    const float dgs = warp_sum(hsum4(dg));
-                    float ds, dA;
-                    gate_grad(p.mode, xs[r].x + bias.x, E, p.lower_bound, ds, dA);
-                    const float dxs = dgs * ds;
-                    if (lane == 0) st1(p.dx, p.dx_dtype, th, dxs);
-                    pb.x += dxs;
-                    pa.x += dgs * dA;
-                } else {
-                    const float4 xv = add4(xs[r], bias);
-                    float4 ds, dA;
-                    gate_grad(p.mode, xv.x, E, p.lower_bound, ds.x, dA.x);
-                    gate_grad(p.mode, xv.y, E, p.lower_bound, ds.y, dA.y);
-                    gate_grad(p.mode, xv.z, E, p.lower_bound, ds.z, dA.z);
-                    gate_grad(p.mode, xv.w, E, p.lower_bound, ds.w, dA.w);
-                    const float4 dxv = mul4(dg, ds);
-                    st4(p.dx, p.dx_dtype, th * 128 + 4 * lane, dxv);
-                    pb = add4(pb, dxv);
-                    pa = add4(pa, mul4(dg, dA));
-                }
+        for (int r = 0; r < GB_ROWS; ++r) {
+            const int row = warp * GB_ROWS + r;
+            if (row >= len) continue;                       // warp-uniform
+            const size_t th = (size_t)(start + row) * HV + h;
+            const float4 dg = add4(vals[r], post);
+            if (p.scalar_gate) {
+                const float dgs = warp_sum(hsum4(dg));
+                float ds, dA;
+                gate_grad(p.mode, xs[r].x + bias.x, E, p.lower_bound, ds, dA);
+                const float dxs = dgs * ds;
+                if (lane == 0) st1(p.dx, p.dx_dtype, th, dxs);
+                pb.x += dxs;
+                pa.x += dgs * dA;
+            } else {
+                const float4 xv = add4(xs[r], bias);
+                float4 ds, dA;
+                gate_grad(p.mode, xv.x, E, p.lower_bound, ds.x, dA.x);
+                gate_grad(p.mode, xv.y, E, p.lower_bound, ds.y, dA.y);
+                gate_grad(p.mode, xv.z, E, p.lower_bound, ds.z, dA.z);
+                gate_grad(p.mode, xv.w, E, p.lower_bound, ds.w, dA.w);
+                const float4 dxv = mul4(dg, ds);
+                st4(p.dx, p.dx_dtype, th * 128 + 4 * lane, dxv);
+                pb = add4(pb, dxv);
+                pa = add4(pa, mul4(dg, dA));
             }
         }
     }
@@ -182,7 +177,7 @@ __global__ void __launch_bounds__(128, 4) gate_bwd_kernel(const MkdaGateBwd p) {
     __syncthreads();
     if (warp == 0) {
         float4 sb = red[0][0][lane], sa = red[1][0][lane];
-        for (int w = 1; w < 4; ++w) { sb = add4(sb, red[0][w][lane]); sa = add4(sa, red[1][w][lane]); }
+        for (int w = 1; w < GB_WARPS; ++w) { sb = add4(sb, red[0][w][lane]); sa = add4(sa, red[1][w][lane]); }
         const size_t ch = (size_t)blockIdx.y * HV + h;
         if (p.scalar_gate) {
             if (lane == 0) {
@@ -533,9 +528,9 @@ extern "C" int mkda_gate_bwd(const MkdaGateBwd* p, void* stream) {
     if ((p->part_bias || p->part_alog) && (int)grid.y != p->part_rows)
         return set_error(MKDA_ERR_ARG, "gate_bwd: part_rows must not exceed the number of chunks when partials are requested");
     switch (p->x_dtype) {
-        case MKDA_F32: gate_bwd_kernel<MKDA_F32><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
-        case MKDA_BF16: gate_bwd_kernel<MKDA_BF16><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
-        case MKDA_F16: gate_bwd_kernel<MKDA_F16><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
+        case MKDA_F32: gate_bwd_kernel<MKDA_F32><<<grid, 32 * GB_WARPS, 0, (cudaStream_t)stream>>>(*p); break;
+        case MKDA_BF16: gate_bwd_kernel<MKDA_BF16><<<grid, 32 * GB_WARPS, 0, (cudaStream_t)stream>>>(*p); break;
+        case MKDA_F16: gate_bwd_kernel<MKDA_F16><<<grid, 32 * GB_WARPS, 0, (cudaStream_t)stream>>>(*p); break;
         default: return set_error(MKDA_ERR_ARG, "gate_bwd: unsupported dtype");
     }
     return check_launch("gate_bwd");
