@@ -141,7 +141,7 @@ KERNEL_FLOPS = {                      # per token per v-head
 KERNEL_BYTES = {
     "mkda_gate_cumsum_fwd": 1024, "mkda_l2norm_rstd": 128, "mkda_intra_fwd": 3592, "mkda_recur_fwd": 3080,
     "mkda_out_fwd": 3584, "mkda_epilogue_bwd_tiles": 2048, "mkda_epilogue_bwd": 2048, "mkda_bwd_dh": 3848,
-    "mkda_bwd_chunk": 6664, "mkda_gate_bwd": 1536, "mkda_qk_grad_finish": 1536,
+    "mkda_bwd_chunk": 6152, "mkda_gate_bwd": 1536, "mkda_qk_grad_finish": 1024,      # dq / dk tiles are per q/k head: 512 B per v-head
 }
 def load_kernel_traffic(path=os.path.join(ROOT, "profiles", "counters_per_kernel_1b_shape.md")):
     """DRAM traffic per token per v-head of every kernel, read from the committed ncu summary (its table has the columns

@@ -289,8 +289,10 @@ typedef struct {
     const float* dVd_t;        /* [NC,HV] chunk tiles as written by mkda_bwd_dh */
     float scale;
     const void* beta_raw; int beta_dtype; int beta_sigmoid; float beta_scale;
-    float* dq_v; float* dk_v;  /* [NC,HV] fp32 [64 tokens][128] tiles per (chunk, v-head); rows past the end are zero */
-    float* dgp;                /* same form: gradient w.r.t. the log2 cumsum */
+    float* dq_v; float* dk_v;  /* [NC,HK] fp32 [64 tokens][128] tiles per (chunk, q/k head): the contributions of the HV / HK
+                                * v-heads of the head are added up in the tile (first one stored, the others added in
+                                * order, by the one CTA that owns the head's group); rows past the end are zero */
+    float* dgp;                /* [NC,HV] tiles of the same form per (chunk, v-head): gradient w.r.t. the log2 cumsum */
     void* dbeta; int dbeta_dtype;
     void* dv;                  /* [TT,HV,128] in qkv_dtype */
 } MkdaBwdChunk;
@@ -301,7 +303,8 @@ int mkda_bwd_chunk(const MkdaBwdChunk* p, void* stream);
  * (mogan_kda/utils/math.py:38-72). */
 typedef struct {
     MkdaLayout L;
-    const float* dq_v; const float* dk_v;          /* [NC,HV] fp32 [64][128] tiles as written by mkda_bwd_chunk */
+    const float* dq_v; const float* dk_v;          /* [NC,HK] fp32 [64][128] tiles as written by mkda_bwd_chunk (summed over
+                                                    * the v-heads of each q/k head) */
     const void* q; const void* k; int x_dtype;     /* raw q, k [TT,HK,128] */
     const float* q_rstd; const float* k_rstd;      /* [TT,HK], or NULL (no L2 norm) */
     void* dq; void* dk;                            /* [TT,HK,128] in x_dtype; tokens outside every chunk are not written */

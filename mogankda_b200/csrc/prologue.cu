@@ -265,16 +265,15 @@ __global__ void __launch_bounds__(128) l2norm_rstd_kernel(const MkdaL2Norm p) {
     }
 }
 
-// GVA group sum (fixed order) + L2-norm backward.  Block (chunk, q/k head, which of q / k); warp w takes rows w, w + 4, ...
-// of the chunk.  The per-v-head gradients arrive as the fp32 [64][128] tiles written by the chunk backward.
-// GT = v-heads per q/k head when it is 1, 2 or 4 (the loads of a row group are then all issued before the first use), 0 = any.
-template <int GT>
+// L2-norm backward of the q / k gradients.  Block (chunk, q/k head, which of q / k); warp w takes rows w, w + 4, ... of the
+// chunk.  The gradients arrive as the fp32 [64][128] tiles of the chunk backward, already summed over the v-heads of the
+// q/k head (the chunk backward adds them up where it writes them).
 __global__ void __launch_bounds__(128) qk_grad_finish_kernel(const MkdaQkGrad p) {
-    const int HK = p.L.HK, HV = p.L.HV, G = GT ? GT : HV / HK;
+    const int HK = p.L.HK;
     const int c = blockIdx.x / HK, hk = blockIdx.x - c * HK, which = blockIdx.y;
     const int start = p.L.chunk_start[c], len = p.L.chunk_len[c];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const float* d_v = (which ? p.dk_v : p.dq_v) + ((size_t)c * HV + hk * G) * CH * 128 + 4 * lane;
+    const float* d_v = (which ? p.dk_v : p.dq_v) + ((size_t)c * HK + hk) * CH * 128 + 4 * lane;
     const void* x = which ? p.k : p.q;
     const float* rstd = which ? p.k_rstd : p.q_rstd;
     void* dx = which ? p.dk : p.dq;
@@ -285,17 +284,7 @@ __global__ void __launch_bounds__(128) qk_grad_finish_kernel(const MkdaQkGrad p)
         for (int u = 0; u < 4; ++u) {                      // four rows in flight per warp
             const int r = r0 + 4 * u, rr = r < len ? r : len - 1;
             const size_t rowi = (size_t)(start + rr) * HK + hk;
-            if (GT) {
-                float4 part[GT ? GT : 1];
-#pragma unroll
-                for (int g = 0; g < (GT ? GT : 1); ++g) part[g] = *reinterpret_cast<const float4*>(d_v + ((size_t)g * CH + rr) * 128);
-                s[u] = part[0];
-#pragma unroll
-                for (int g = 1; g < (GT ? GT : 1); ++g) s[u] = add4(s[u], part[g]);
-            } else {
-                s[u] = splat4(0.f);
-                for (int g = 0; g < G; ++g) s[u] = add4(s[u], *reinterpret_cast<const float4*>(d_v + ((size_t)g * CH + rr) * 128));
-            }
+            s[u] = *reinterpret_cast<const float4*>(d_v + (size_t)rr * 128);
             if (rstd) {
                 rs[u] = rstd[rowi];
                 xr[u] = ld4(x, p.x_dtype, rowi * 128 + 4 * lane);
@@ -566,12 +555,7 @@ extern "C" int mkda_qk_grad_finish(const MkdaQkGrad* p, void* stream) {
     if (any_misaligned(p->dq_v, p->dk_v, p->dq, p->dk, p->q, p->k)) return set_error(MKDA_ERR_ARG, "qk_grad_finish: tensors must be 16-byte aligned");
     if (p->L.NC == 0) return MKDA_OK;
     const dim3 grid(p->L.NC * p->L.HK, 2);
-    switch (p->L.HV / p->L.HK) {
-        case 1: qk_grad_finish_kernel<1><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
-        case 2: qk_grad_finish_kernel<2><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
-        case 4: qk_grad_finish_kernel<4><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
-        default: qk_grad_finish_kernel<0><<<grid, 128, 0, (cudaStream_t)stream>>>(*p); break;
-    }
+    qk_grad_finish_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(*p);
     return check_launch("qk_grad_finish");
 }
 

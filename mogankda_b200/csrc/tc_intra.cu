@@ -514,6 +514,11 @@ struct BwdShared {
 
 // the intra-chunk operands of rows `n` (this thread's n-th (row, 8-channel) pair): [Kr; Qr] and the column tiles; with a
 // scalar gate just the stacked [K; Q] tile (rows 0..63 = k, 64..127 = q), the decay goes into the weights instead
+// fire-and-forget fp32 addition in global memory
+__device__ __forceinline__ void red_add(float* addr, float v) {
+    asm volatile("red.global.add.f32 [%0], %1;" :: "l"(addr), "f"(v) : "memory");
+}
+
 template <bool SCALAR>
 __device__ __forceinline__ void stage_intra_operands(uint8_t* base, const float (*sGa)[DK], int tid, int n, const float (&vk)[8],
                                                      const float (&vq)[8], const float (&vg)[8]) {
@@ -583,7 +588,7 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
     const int HV = p.L.HV, HK = p.L.HK;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
-    const int total = p.L.NC * HV, stride = gridDim.x;
+    const int stride = gridDim.x;
 
     auto fetch_early = [&](size_t it) {                // dS', Vd^T, A: their regions are free once the intra-chunk products are done
         umma::mbar_expect_tx(&sh.ld0, umma::STATE_TILE_BYTES + umma::CHUNK_TILE_BYTES + umma::QUARTER_TILE_BYTES);
@@ -605,19 +610,31 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
     }
     publish();
     const uint32_t tmem = sh.tmem;
-    if (tid == 0 && (int)blockIdx.x < total) { fetch_early(blockIdx.x); fetch_late(blockIdx.x); }
+    if (tid == 0 && (int)blockIdx.x < p.L.NC * HK) {       // the first item of this CTA: group blockIdx.x, its first v-head
+        const size_t it0 = (size_t)(blockIdx.x / HK) * HV + (size_t)(blockIdx.x % HK) * (HV / HK);
+        fetch_early(it0);
+        fetch_late(it0);
+    }
     // phase counters of the barriers (every thread walks the same sequence of phases)
     uint32_t nA = 0, nB = 0, nC = 0, nD = 0, n0 = 0, n1 = 0, n2 = 0;
+    // A CTA walks (chunk, q/k head) groups gridDim.x apart (heads fastest: CTAs that run together read neighbouring
+    // memory) and, inside a group, the G = HV / HK v-heads that share the q/k head one after the other.  Their dq and dk
+    // contributions are summed where they are written: the first v-head of a group stores its fp32 tile, the others add to it
+    // (red.global.add.f32 by the same thread to the same address, in the fixed order of the v-heads: deterministic, and
+    // the same association as a separate sum would use).  The tile lives in L2 between the two passes.
+    const int G = HV / HK, ngroups = p.L.NC * HK;
     // the chunk table entries are read one item ahead: every address of an item depends on them
     int next_start = 0, next_len = 1;
-    if ((int)blockIdx.x < total) { next_start = p.L.chunk_start[blockIdx.x / HV]; next_len = p.L.chunk_len[blockIdx.x / HV]; }
+    if ((int)blockIdx.x < ngroups) { next_start = p.L.chunk_start[blockIdx.x / HK]; next_len = p.L.chunk_len[blockIdx.x / HK]; }
 
-    for (int item = blockIdx.x; item < total; item += stride) {
-        const int c = item / HV, h = item - c * HV;    // heads fastest: CTAs that run together read neighbouring memory
-        const int hk = h / (HV / HK);
+    for (int grp = blockIdx.x, j = 0; grp < ngroups; ) {
+        const int c = grp / HK, hk = grp - c * HK, h = hk * G + j;
+        const int item = c * HV + h;
         const int start = next_start, len = next_len;
-        const bool more = item + stride < total;
-        if (more) { next_start = p.L.chunk_start[(item + stride) / HV]; next_len = p.L.chunk_len[(item + stride) / HV]; }
+        // the item after this one: the next v-head of the group, else the first v-head of this CTA's next group
+        const bool last_of_group = j + 1 == G;
+        const bool more = !last_of_group || grp + stride < ngroups;
+        if (last_of_group && more) { next_start = p.L.chunk_start[(grp + stride) / HK]; next_len = p.L.chunk_len[(grp + stride) / HK]; }
 
         // ---- state products whose operands are all copies | register loads, dgl ------------------------
         if (umma::mma_issuer()) {
@@ -910,8 +927,13 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
             umma::commit(&sh.barA);
             if (more) {                                        // every operand tile is dead once these products are done (the epilogue
                 umma::mbar_wait(&sh.barA, nA & 1);             // reads accumulators and writes global memory): all five tiles of the
-                fetch_early((size_t)item + stride);            // next item travel under it
-                fetch_late((size_t)item + stride);
+                size_t next_item = (size_t)item + 1;           // next item travel under it
+                if (last_of_group) {
+                    const int ng = grp + stride, nc = ng / HK;
+                    next_item = (size_t)nc * HV + (size_t)(ng - nc * HK) * G;
+                }
+                fetch_early(next_item);
+                fetch_late(next_item);
             }
         }
         {
@@ -944,9 +966,11 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
             // the three outputs per (token, channel) go straight to their fp32 [64 tokens][128] tiles: a warp writes 128
             // consecutive bytes per token, and shared memory stays free for the next item's tiles
             const size_t ob = (size_t)item * (size_t)(CH * DK) + row;
-            float* __restrict__ oq = p.dq_v + ob;
-            float* __restrict__ ok = p.dk_v + ob;
+            const size_t obk = ((size_t)c * HK + hk) * (size_t)(CH * DK) + row;      // dq / dk: one tile per q/k head
+            float* __restrict__ oq = p.dq_v + obk;
+            float* __restrict__ ok = p.dk_v + obk;
             float* __restrict__ og = p.dgp + ob;
+            const bool first_of_group = j == 0;
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
                 const int c0 = 16 * cg + 8 * hf;
@@ -984,8 +1008,10 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
                     float dg = qv * up * dqt + kv * up * dkt - kv * re * dkb;
                     if (i == len - 1) dg += extra;
                     const bool ok_row = i < len;
-                    oq[i * DK] = ok_row ? dqt * up + dqr + dgn * kv : 0.f;
-                    ok[i * DK] = ok_row ? (dkt * up + dkb * re) + bt * T + dkc[r] + dgn * qv : 0.f;
+                    const float dq_e = ok_row ? dqt * up + dqr + dgn * kv : 0.f;
+                    const float dk_e = ok_row ? (dkt * up + dkb * re) + bt * T + dkc[r] + dgn * qv : 0.f;
+                    if (first_of_group) { oq[i * DK] = dq_e; ok[i * DK] = dk_e; }
+                    else { red_add(oq + i * DK, dq_e); red_add(ok + i * DK, dk_e); }
                     og[i * DK] = ok_row ? dg + qv * dqr + kv * bt * T - kv * dkc[r] : 0.f;
                 }
                 // sum over the 32 channels of this warp for the 8 rows at once: every exchange halves the number of rows a lane
@@ -1023,6 +1049,7 @@ __global__ void __launch_bounds__(BWD_CHUNK_THREADS, 1) bwd_chunk_tc_kernel(cons
             st1(p.dbeta, p.dbeta_dtype, th, db);
         }
         __syncthreads();
+        if (last_of_group) { j = 0; grp += stride; } else ++j;
     }
     umma::fence_before_sync();
     __syncthreads();
@@ -1033,8 +1060,8 @@ template <int DT, bool SCALAR>
 static int launch_bwd_chunk_tc_t(const MkdaBwdChunk* p, cudaStream_t stream) {
     auto kern = bwd_chunk_tc_kernel<DT, SCALAR>;
     if (int e = ensure_smem((const void*)kern, BWD_CHUNK_SMEM, "bwd_chunk")) return e;
-    const int items = p->L.NC * p->L.HV;
-    kern<<<items < sm_count() ? items : sm_count(), BWD_CHUNK_THREADS, BWD_CHUNK_SMEM, stream>>>(*p);
+    const int groups = p->L.NC * p->L.HK;              // a CTA takes whole (chunk, q/k head) groups
+    kern<<<groups < sm_count() ? groups : sm_count(), BWD_CHUNK_THREADS, BWD_CHUNK_SMEM, stream>>>(*p);
     return check_launch("bwd_chunk");
 }
 int launch_bwd_chunk_tc(const MkdaBwdChunk* p, cudaStream_t stream) {

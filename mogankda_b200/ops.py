@@ -323,11 +323,12 @@ def bwd_dh(lay, d_o, kbar, qs, gl, Aqk, nw, HK, HV, *, dht=None, seg_dht=None,
 
 def bwd_chunk(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, A, h, dh, Vd, dO_t, dVd_t, scale, HK, HV,
               beta_raw, beta_sigmoid, beta_scale, scalar_gate=False):
-    """Every gradient local to a (chunk, v-head), in one kernel.  Returns (dq_v, dk_v, dgp, dbeta, dv)."""
+    """Every gradient local to a (chunk, v-head), in one kernel.  Returns (dq_v, dk_v, dgp, dbeta, dv); dq_v / dk_v are
+    fp32 [64][128] tiles per (chunk, q/k head), already summed over the v-heads of the head, dgp per (chunk, v-head)."""
     dev = q.device
     alloc = torch.empty if lay.covers_all else torch.zeros
-    z = lambda: torch.empty(lay.NC, HV, 64, 128, dtype=torch.float32, device=dev)      # noqa: E731  (fp32 [64][128] tiles)
-    dq_v, dk_v, dgp = z(), z(), z()
+    z = lambda H: torch.empty(lay.NC, H, 64, 128, dtype=torch.float32, device=dev)      # noqa: E731  (fp32 [64][128] tiles)
+    dq_v, dk_v, dgp = z(HK), z(HK), z(HV)
     dbeta = alloc(lay.TT, HV, dtype=beta_raw.dtype, device=dev)
     dv = alloc(lay.TT, HV, 128, dtype=v.dtype, device=dev)
     p = STRUCTS["MkdaBwdChunk"]()
@@ -345,7 +346,10 @@ def bwd_chunk(lay, q, k, v, q_rstd, k_rstd, g_c, beta_e, A, h, dh, Vd, dO_t, dVd
 
 
 def qk_grad_finish(lay, dq_v, dk_v, q, k, q_rstd, k_rstd, HK, HV):
-    """dq_v, dk_v: fp32 [NC,HV,64,128] tiles -> gradients w.r.t. the raw q and k, [TT,HK,128] in their dtype."""
+    """dq_v, dk_v: fp32 [NC,HK,64,128] tiles (summed over the v-heads of each q/k head) -> gradients w.r.t. the raw q and
+    k, [TT,HK,128] in their dtype."""
+    if tuple(dq_v.shape[:2]) != (lay.NC, HK) or tuple(dk_v.shape[:2]) != (lay.NC, HK):
+        raise ValueError("qk_grad_finish takes one tile per (chunk, q/k head)")
     alloc = torch.empty if lay.covers_all else torch.zeros
     dq = alloc(lay.TT, HK, 128, dtype=q.dtype, device=q.device)
     dk = alloc(lay.TT, HK, 128, dtype=k.dtype, device=k.device)

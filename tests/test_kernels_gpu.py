@@ -131,7 +131,9 @@ def test_bwd_chunk_gate_and_finish(world):
                                            world["scale"], 2, 4, lv["beta"], False, 1.0)
     _err("dv", t_v, bw["dX"].reshape(t_v.shape), KTOL if t_v.dtype == torch.float32 else 2.0 ** -8)
     TT = world["TT"]
-    _err("dq_v", unpack_plain_tiles(t_q, lay, TT), bw["dq_v"]); _err("dk_v", unpack_plain_tiles(t_k, lay, TT), bw["dk_v"])
+    # dq / dk leave summed over the two v-heads of each q/k head
+    _err("dq_v", unpack_plain_tiles(t_q, lay, TT), bw["dq_v"].reshape(TT, 2, 2, 128).sum(2))
+    _err("dk_v", unpack_plain_tiles(t_k, lay, TT), bw["dk_v"].reshape(TT, 2, 2, 128).sum(2))
     _err("dgp", unpack_plain_tiles(t_g, lay, TT), bw["dgp"])
     _err("dbeta", t_b, bw["dbeta"].reshape(world["TT"], 4))
     # gate backward (reverse cumsum folded in) against autograd of the oracle's gate
@@ -148,7 +150,8 @@ def test_bwd_chunk_gate_and_finish(world):
     B, T = lv["q"].shape[:2]
     up = bw["dq_v"].reshape(B, T, 2, 2, 128).sum(3)
     (rq,) = torch.autograd.grad((orc.l2norm(qd) * up).sum(), [qd])
-    dq, _ = ops.qk_grad_finish(lay, pack_plain_tiles(f32(bw["dq_v"]), lay), pack_plain_tiles(f32(bw["dk_v"]), lay), lv["q"],
+    dq, _ = ops.qk_grad_finish(lay, pack_plain_tiles(f32(up.reshape(B * T, 2, 128)), lay),
+                               pack_plain_tiles(f32(bw["dk_v"].reshape(B * T, 2, 2, 128).sum(2)), lay), lv["q"],
                                lv["k"], world["q_rstd"], world["k_rstd"], 2, 4)
     tol = 1e-5 if lv["q"].dtype == torch.float32 else 2.0 ** -8
     _err("dq", dq.view_as(rq), rq, tol)
